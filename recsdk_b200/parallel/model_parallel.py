@@ -1,0 +1,147 @@
+"""``DistributedModelParallel``: shards embedding collections according to a plan and data-parallelises
+everything else.
+
+* Unsharded ``EmbeddingBagCollection`` children are replaced by ``ShardedEmbeddingBagCollection``
+  (fused peer-memory backend on CUDA) built from the plan entries of that module path.
+* Dense parameters that live in flat buffers (``FusedMLP``, ``LogitHead``) get their gradient buffers
+  re-homed into ONE peer-mapped allocation; ``sync_dense_grads()`` averages it across ranks with the
+  in-kernel all-reduce (multimem through NVSwitch when a multicast mapping exists).  Remaining dense
+  parameters fall back to ``torch.distributed.all_reduce``.
+* ``fused_optimizer`` is the ``CombinedOptimizer`` of the sparse in-backward optimizers (no-op ``step``).
+
+Mirrors the role of TorchRec's DMP in the reference's user flow
+(``docs/en/torch/torch_rec_v1/03_quick_start/quick_start.md:239-262``).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..modules.embedding_modules import EmbeddingBagCollection
+from ..ops import embedding_ops as E
+from ..optim import CombinedOptimizer
+from .comm import PeerGroup, ShardingEnv
+from .embeddingbag import ParameterSharding, ShardedEmbeddingBagCollection
+from .planner import ShardingPlan
+
+
+def _optimizer_spec_from_params(ebc: nn.Module, default: Optional[E.OptimizerSpec]) -> E.OptimizerSpec:
+    """Translate ``apply_optimizer_in_backward`` annotations into a fused sparse optimizer spec."""
+    for p in ebc.parameters():
+        classes = getattr(p, "_optimizer_classes", None)
+        if classes:
+            cls, kw = classes[0], getattr(p, "_optimizer_kwargs", [{}])[0]
+            if issubclass(cls, torch.optim.Adagrad):
+                kind = E.OPT_ROWWISE_ADAGRAD if kw.get("rowwise", True) else E.OPT_ADAGRAD
+                return E.OptimizerSpec(kind=kind, lr=kw.get("lr", 0.01), eps=kw.get("eps", 1e-10),
+                                       weight_decay=kw.get("weight_decay", 0.0),
+                                       initial_accumulator_value=kw.get("initial_accumulator_value", 0.0))
+            if issubclass(cls, torch.optim.Adam):
+                b = kw.get("betas", (0.9, 0.999))
+                return E.OptimizerSpec(kind=E.OPT_ADAM, lr=kw.get("lr", 1e-3), eps=kw.get("eps", 1e-8), beta1=b[0],
+                                       beta2=b[1], weight_decay=kw.get("weight_decay", 0.0))
+            if issubclass(cls, torch.optim.SGD):
+                return E.OptimizerSpec(kind=E.OPT_SGD, lr=kw.get("lr", 0.01), weight_decay=kw.get("weight_decay", 0.0))
+    return default or E.OptimizerSpec()
+
+
+class DistributedModelParallel(nn.Module):
+    def __init__(self, module: nn.Module, env: Optional[ShardingEnv] = None, device: Optional[torch.device] = None,
+                 plan: Optional[ShardingPlan] = None, sharders=None, peer: Optional[PeerGroup] = None,
+                 sparse_optimizer: Optional[E.OptimizerSpec] = None, out_dtype: torch.dtype = torch.bfloat16,
+                 max_local_batch: int = 0, one_hot: bool = False, init_seed: Optional[int] = None) -> None:
+        super().__init__()
+        self.env = env or ShardingEnv.from_process_group(None)
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.world, self.rank = self.env.world_size, self.env.rank
+        self.peer = peer
+        if self.world > 1 and self.device.type == "cuda" and peer is None:
+            self.peer = PeerGroup(self.env.process_group, self.device)
+        self.plan = plan or ShardingPlan({})
+        self.sharded_modules: List[ShardedEmbeddingBagCollection] = []
+        self._shard(module, "", sparse_optimizer, out_dtype, max_local_batch, one_hot, init_seed)
+        self.module = module
+        for m in module.modules():
+            if isinstance(m, ShardedEmbeddingBagCollection) and m not in self.sharded_modules:
+                self.sharded_modules.append(m)
+        self._grad_buf = None
+        self._grad_elems = 0
+        self._rehome_dense_grads()
+        self._sharded_param_ids = {id(p) for sm in self.sharded_modules for p in sm.parameters()}
+        self._broadcast_dense()
+
+    # ------------------------------------------------------------------ sharding
+    def _shard(self, parent: nn.Module, prefix: str, spec, out_dtype, max_local_batch, one_hot, init_seed) -> None:
+        for name, child in list(parent.named_children()):
+            path = prefix + name
+            if isinstance(child, EmbeddingBagCollection):
+                entries: Dict[str, ParameterSharding] = self.plan.get_module_plan(path)
+                sharded = ShardedEmbeddingBagCollection(
+                    child.embedding_bag_configs(), entries, self.env, self.device,
+                    _optimizer_spec_from_params(child, spec), peer=self.peer, out_dtype=out_dtype,
+                    max_local_batch=max_local_batch, one_hot=one_hot, init_weights=True)
+                if init_seed is not None:
+                    sharded.reset_parameters(seed=init_seed)
+                elif not child.is_meta():
+                    sharded.load_from_unsharded(child)
+                setattr(parent, name, sharded)
+                self.sharded_modules.append(sharded)
+            elif isinstance(child, ShardedEmbeddingBagCollection):
+                continue
+            else:
+                self._shard(child, path + ".", spec, out_dtype, max_local_batch, one_hot, init_seed)
+
+    # ------------------------------------------------------------- dense grads
+    def _flat_modules(self) -> List[nn.Module]:
+        return [m for m in self.module.modules() if hasattr(m, "flat_grad") and hasattr(m, "set_grad_buffer")]
+
+    def _rehome_dense_grads(self) -> None:
+        mods = self._flat_modules()
+        if self.world == 1 or not mods or self.device.type != "cuda":
+            return
+        sizes = [(m.flat_grad.numel() + 63) // 64 * 64 for m in mods]
+        total = sum(sizes)
+        self._grad_buf = self.peer.alloc(total * 4, zero=True)
+        flat = self._grad_buf.local.view(torch.float32)
+        off = 0
+        for m, s in zip(mods, sizes):
+            m.set_grad_buffer(flat[off:off + m.flat_grad.numel()])
+            off += s
+        self._grad_elems = total
+
+    @torch.no_grad()
+    def _broadcast_dense(self) -> None:
+        if self.world == 1 or self.env.process_group is None:
+            return
+        for p in self.module.parameters():
+            if id(p) in self._sharded_param_ids:
+                continue
+            dist.broadcast(p.data, src=0, group=self.env.process_group)
+        for m in self.module.modules():
+            if hasattr(m, "sync_shadow"):
+                m.sync_shadow()
+
+    def sync_dense_grads(self) -> None:
+        """Average dense gradients over the data-parallel ranks (call between backward and step)."""
+        if self.world == 1:
+            return
+        if self._grad_buf is not None:
+            self.peer.allreduce_mean_f32(self._grad_buf, self._grad_elems, scale=1.0)
+        for p in self.module.parameters():
+            if p.grad is not None and id(p) not in self._sharded_param_ids:
+                dist.all_reduce(p.grad, group=self.env.process_group)
+
+    # ------------------------------------------------------------------- misc
+    @property
+    def fused_optimizer(self) -> CombinedOptimizer:
+        return CombinedOptimizer([m.fused_optimizer for m in self.sharded_modules])
+
+    def forward(self, *args, **kwargs):
+        return self.module(*args, **kwargs)
+
+    def dense_named_parameters(self) -> Dict[str, nn.Parameter]:
+        return {n: p for n, p in self.module.named_parameters()
+                if id(p) not in self._sharded_param_ids and p.requires_grad}
