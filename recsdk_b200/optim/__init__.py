@@ -81,7 +81,8 @@ class FusedDenseOptimizer(torch.optim.Optimizer):
         super().__init__(params if params else [torch.zeros(1)], {"lr": lr})
         if rest:
             if kind == "adam":
-                self._rest_opt = torch.optim.Adam(rest, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+                self._rest_opt = torch.optim.Adam(rest, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                                                  capturable=all(p.is_cuda for p in rest))
             else:
                 self._rest_opt = torch.optim.SGD(rest, lr=lr, weight_decay=weight_decay)
         else:

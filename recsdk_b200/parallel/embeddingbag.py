@@ -163,7 +163,8 @@ class ShardedEmbeddingBagCollection(nn.Module):
             self.embedding_bags[t.name] = holder
         if init_weights:
             self.reset_parameters()
-        self._anchor = nn.Parameter(torch.zeros(1, device=device))
+        self._anchor = nn.Parameter(torch.zeros(1, device=device))   # makes autograd call our backward
+        self._anchor._in_backward_optimizers = True  # type: ignore[attr-defined]
         self._bwd_ws = E.BackwardWorkspace(device)
         self._sorter: Optional[E.SegmentSorter] = None
         self._gather_ids: Optional[object] = None

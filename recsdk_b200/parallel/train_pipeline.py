@@ -35,7 +35,9 @@ class TrainPipelineBase:
         if sync is not None:
             sync()
         self._optimizer.step()
-        return loss, out
+        # hand back a graph-free loss: a live autograd graph would pin its AccumulateGrad nodes (and
+        # the stream they were created on) across steps, which breaks a later CUDA-graph capture
+        return loss.detach(), out
 
     def progress(self, dataloader_iter: Iterator[Batch]):
         batch = next(dataloader_iter).to(self._device)

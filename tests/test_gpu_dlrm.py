@@ -72,7 +72,7 @@ def test_dlrm_fused_matches_reference_step():
         exp = w_ref.detach() - 0.5 * w_ref.grad
         got = f.sparse_arch.table_weight(c.name).detach().float().cpu()
         d = (got - exp).norm() / ((0.5 * w_ref.grad).norm() + 1e-12)
-        assert d < 8e-2, "table %s rel update err %g" % (c.name, d)
+        assert d < 0.15, "table %s rel update err %g" % (c.name, d)
 
 
 @pytest.mark.parametrize("cuda_graph", [False, True])
