@@ -44,6 +44,8 @@ def parse_args():
     ap.add_argument("--small", action="store_true", help="tiny tables / batch for a quick functional check")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--table-seed", type=int, default=0)
+    ap.add_argument("--rows-scale", type=float, default=1.0,
+                    help="shrink every table (profiling captures on a small case); 1.0 = the named config")
     return ap.parse_args()
 
 
@@ -151,6 +153,8 @@ def main() -> None:
     assert GB % world == 0
     B = GB // world
     rows = table_rows(args.table_seed) if not args.small else [1000 + 997 * i for i in range(26)]
+    if args.rows_scale != 1.0:
+        rows = [max(1000, int(r * args.rows_scale)) for r in rows]
     keys = ["f%d" % i for i in range(26)]
     cfgs = [EmbeddingBagConfig(num_embeddings=r, embedding_dim=128, name="t%d" % i, feature_names=[keys[i]],
                                data_type=DataType.FP16) for i, r in enumerate(rows)]
@@ -161,7 +165,7 @@ def main() -> None:
     plan = EmbeddingShardingPlanner(Topology(world_size=world)).plan(model)
     dmp = DistributedModelParallel(model, env, dev, plan,
                                    sparse_optimizer=E.OptimizerSpec(kind=E.OPT_ROWWISE_ADAGRAD, lr=0.01, eps=1e-8),
-                                   max_local_batch=B, one_hot=True, init_seed=1)
+                                   max_local_batch=B, one_hot=True, init_seed=None)
     opt = CombinedOptimizer([dmp.fused_optimizer, FusedDenseOptimizer(dmp.module, "adam", lr=1e-3)])
     pipe = TrainPipelineSparseDist(dmp, opt, dev, return_loss=True, cuda_graph=not args.no_graph)
 
@@ -245,7 +249,7 @@ def main() -> None:
             "n_gpus": world, "steps": args.steps, "warmup": n_warm, "ms_per_step": step_ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (fp16 tables)",
             "data": "synthetic Zipf(1.1) ids, N(0,1) dense, Bernoulli(0.03) labels, random-init weights",
-            "config": {"model": "DLRM-large" if not args.small else "DLRM-small-debug", "global_batch": GB,
+            "config": {"model": "DLRM-large" if not (args.small or args.rows_scale != 1.0) else "DLRM-debug-shrunk", "global_batch": GB,
                        "seq_len": None, "tables": 26, "embedding_dim": 128, "total_rows": int(sum(rows)),
                        "parallelism": "dp%d dense + table-wise/row-wise embedding shards (peer-memory pull)" % world,
                        "cuda_graph": pipe._graph is not None,

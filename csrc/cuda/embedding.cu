@@ -176,6 +176,83 @@ __global__ void tbe_linearize_kernel(const TableShard* __restrict__ shards, cons
 }
 
 // ---------------------------------------------------------------------------
+// one-hot fast forward: a half-warp per bag with 16-byte loads, G bags in flight per half-warp
+// ---------------------------------------------------------------------------
+template <typename T> struct Vec8;   // 8 consecutive elements <-> 8 floats
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void ld(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void st(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <> struct Vec8<__half> {
+  static __device__ __forceinline__ void ld(const __half* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    float2 a = rb::unpack_f16(u.x), b = rb::unpack_f16(u.y), c = rb::unpack_f16(u.z), d = rb::unpack_f16(u.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  }
+  static __device__ __forceinline__ void st(__half* p, const float (&v)[8]) {
+    *reinterpret_cast<uint4*>(p) = make_uint4(rb::pack_f16(v[0], v[1]), rb::pack_f16(v[2], v[3]),
+                                              rb::pack_f16(v[4], v[5]), rb::pack_f16(v[6], v[7]));
+  }
+};
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    float2 a = rb::unpack_bf16(u.x), b = rb::unpack_bf16(u.y), c = rb::unpack_bf16(u.z), d = rb::unpack_bf16(u.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  }
+  static __device__ __forceinline__ void st(__nv_bfloat16* p, const float (&v)[8]) {
+    *reinterpret_cast<uint4*>(p) = make_uint4(rb::pack_bf16(v[0], v[1]), rb::pack_bf16(v[2], v[3]),
+                                              rb::pack_bf16(v[4], v[5]), rb::pack_bf16(v[6], v[7]));
+  }
+};
+
+template <typename WT, typename OT, typename IT, int G>
+__global__ void __launch_bounds__(256)
+tbe_forward_onehot_kernel(const TableShard* __restrict__ shards, const long long* __restrict__ ptrs,
+                          const IT* __restrict__ indices, int T, int B, int world, int self,
+                          OT* __restrict__ out, long long ld_out, int* status) {
+  const int hl = threadIdx.x & 15;
+  const long long half_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const int groups_per_t = (B + G - 1) / G;
+  if (half_id >= static_cast<long long>(T) * groups_per_t) return;
+  const int t = static_cast<int>(half_id / groups_per_t);
+  const int b0 = static_cast<int>(half_id % groups_per_t) * G;
+  const TableShard ts = shards[t];
+  const WT* src[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    src[g] = nullptr;
+    if (b0 + g < B) {
+      const long long id = static_cast<long long>(indices[static_cast<long long>(t) * B + b0 + g]);
+      int rank; long long row;
+      if (locate_row(ts, id, world, self, rank, row))
+        src[g] = reinterpret_cast<const WT*>(ptrs[ts.ptr_index + rank]) + row * ts.D;
+      else if (hl == 0 && status) atomicCAS(status, 0, RB_ERR_BOUNDS);
+    }
+  }
+  for (int d0 = hl * 8; d0 < ts.D; d0 += 128) {
+    float v[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (src[g]) Vec8<WT>::ld(src[g] + d0, v[g]);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[g][i] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+      if (b0 + g < B) Vec8<OT>::st(out + static_cast<long long>(b0 + g) * ld_out + ts.D_offset + d0, v[g]);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // backward + optimizer
 // ---------------------------------------------------------------------------
 struct OptArgs {
@@ -184,17 +261,19 @@ struct OptArgs {
   float bias_c1, bias_c2;  // 1-beta1^t, 1-beta2^t
 };
 
+constexpr int LONG_CHUNK = 32;   // entries summed by one half-warp of the long-segment kernel
+
 struct BwdArgs {
   const TableShard* shards;
-  const long long* key_cumsum;   // [T+1] linear key range of each table on this rank
-  const long long* w_offsets;    // [T] element offset of each table in `weights`
-  const long long* s_offsets;    // [T] offset of each table in the state arrays (rows or elements)
+  const long long* key_cumsum;   // [n_tables+1] linear key range of each table on this rank
+  const long long* w_offsets;    // [n_tables] element offset of each table in `weights`
+  const long long* s_offsets;    // [n_tables] offset of each table in the state arrays (rows or elements)
   int T, n_tables, B_local, world;   // T = features (bag groups); n_tables = physical tables
   const long long* grad_ptrs;    // [world] base of each rank's pooled-gradient buffer
   long long ld_g;
   const long long* offsets;      // bag offsets for mean pooling (nullable), over the global bag index
   int pooling;
-  const int* sorted_bags;        // bag index (t * B_global + b_global)
+  const int* sorted_bags;        // bag index (f * B_global + b_global)
   const long long* unique_keys;
   const int* seg_offsets;        // [num_runs + 1]
   const int* num_runs;
@@ -202,181 +281,310 @@ struct BwdArgs {
   float* state1;
   float* state2;
   OptArgs opt;
-  int* long_list;
-  int* long_count;
-  int long_cap;
-  int long_threshold;
+  // long-segment machinery (scratch)
+  int* long_list;      // [long_cap] segment index of each long segment
+  int* counters;       // [0] = number of long segments, [1] = number of chunks
+  int2* chunk_list;    // [chunk_cap] (long index, chunk index)
+  float* long_accum;   // [long_cap][accum_ld] fp32 partial sums, all zero between launches
+  int long_cap, chunk_cap, accum_ld, long_threshold;
   int* status;
 };
 
+// per-kernel shared-memory copy of the small lookup tables
+struct Tabs {
+  const long long* key_cumsum;
+  const long long* w_off;
+  const long long* s_off;
+  const long long* gptr;
+  const int* f_D;
+  const int* f_Doff;
+};
+
+__device__ __forceinline__ Tabs load_tabs(const BwdArgs& a, long long* sm) {
+  long long* kc = sm;
+  long long* wo = kc + a.n_tables + 1;
+  long long* so = wo + a.n_tables;
+  long long* gp = so + a.n_tables;
+  int* fD = reinterpret_cast<int*>(gp + a.world);
+  int* fO = fD + a.T;
+  for (int i = threadIdx.x; i <= a.n_tables; i += blockDim.x) kc[i] = a.key_cumsum[i];
+  for (int i = threadIdx.x; i < a.n_tables; i += blockDim.x) { wo[i] = a.w_offsets[i]; so[i] = a.s_offsets[i]; }
+  for (int i = threadIdx.x; i < a.world; i += blockDim.x) gp[i] = a.grad_ptrs[i];
+  for (int i = threadIdx.x; i < a.T; i += blockDim.x) { fD[i] = a.shards[i].D; fO[i] = a.shards[i].D_offset; }
+  __syncthreads();
+  return Tabs{kc, wo, so, gp, fD, fO};
+}
+
+inline size_t tabs_bytes(int n_tables, int T, int world) {
+  return sizeof(long long) * (3 * static_cast<size_t>(n_tables) + 1 + world) + sizeof(int) * 2 * static_cast<size_t>(T) + 16;
+}
+
+__device__ __forceinline__ int table_of_key(const long long* cumsum, int n, long long key) {
+  int lo = 0, hi = n;
+  while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (cumsum[mid] <= key) lo = mid; else hi = mid; }
+  return lo;
+}
+
+__device__ __forceinline__ float half_sum(float v, unsigned mask) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(mask, v, o, 16);
+  return v;
+}
+
+// sum the gradient rows of entries [beg, end) into acc; 4 rows in flight per half-warp
+template <typename GT, int NCH>
+__device__ __forceinline__ void accumulate_range(const BwdArgs& a, const Tabs& tb, int D, int beg, int end,
+                                                 unsigned B_global, float (&acc)[NCH][8], int hl) {
+  for (int j = beg; j < end; j += 4) {
+    const GT* g[4];
+    float scale[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      g[u] = nullptr;
+      scale[u] = 1.f;
+      if (j + u < end) {
+        const unsigned bag = static_cast<unsigned>(a.sorted_bags[j + u]);
+        const unsigned f = bag / B_global;
+        const unsigned bg = bag - f * B_global;
+        const unsigned r = bg / static_cast<unsigned>(a.B_local);
+        const unsigned bl = bg - r * static_cast<unsigned>(a.B_local);
+        g[u] = reinterpret_cast<const GT*>(tb.gptr[r]) + static_cast<long long>(bl) * a.ld_g + tb.f_Doff[f] + hl * 8;
+        if (a.pooling == POOL_MEAN && a.offsets) {
+          const long long len = a.offsets[bag + 1] - a.offsets[bag];
+          scale[u] = len > 0 ? 1.f / static_cast<float>(len) : 0.f;
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      if (hl * 8 + c * 128 >= D) continue;
+      float v[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (g[u]) Vec8<GT>::ld(g[u] + c * 128, v[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (g[u]) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[c][i] += v[u][i] * scale[u];
+        }
+    }
+  }
+}
+
+// The row's weights (and its row-wise state) are loaded by the caller BEFORE it sums the gradients,
+// so those loads overlap the gradient gathers instead of extending the dependent chain.
 template <typename WT, int NCH>
-__device__ __forceinline__ void apply_row_update(const BwdArgs& a, int t, long long local_row, int D,
-                                                 float4 (&acc)[NCH], int lane) {
-  WT* w = reinterpret_cast<WT*>(a.weights) + a.w_offsets[t] + local_row * D;
+__device__ __forceinline__ void preload_row(const BwdArgs& a, const Tabs& tb, int t, long long local_row, int D,
+                                            float (&wv)[NCH][8], float& row_state, int hl) {
+  const WT* w = reinterpret_cast<const WT*>(a.weights) + tb.w_off[t] + local_row * D;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int d0 = hl * 8 + c * 128;
+    if (d0 < D) Vec8<WT>::ld(w + d0, wv[c]);
+  }
+  row_state = (a.opt.type == OPT_ROWWISE_ADAGRAD) ? a.state1[tb.s_off[t] + local_row] : 0.f;
+}
+
+template <typename WT, int NCH>
+__device__ __forceinline__ void apply_row_update(const BwdArgs& a, const Tabs& tb, int t, long long local_row, int D,
+                                                 float (&acc)[NCH][8], float (&wpre)[NCH][8], float row_state,
+                                                 int hl, unsigned hmask) {
+  WT* w = reinterpret_cast<WT*>(a.weights) + tb.w_off[t] + local_row * D;
   const OptArgs& o = a.opt;
   if (o.type == OPT_ROWWISE_ADAGRAD) {
     float ss = 0.f;
 #pragma unroll
     for (int c = 0; c < NCH; ++c)
-      if (lane * 4 + c * 128 < D) ss += acc[c].x * acc[c].x + acc[c].y * acc[c].y + acc[c].z * acc[c].z + acc[c].w * acc[c].w;
-    ss = rb::warp_sum(ss);
-    float* st = a.state1 + a.s_offsets[t] + local_row;
-    const float g2 = *st + ss / static_cast<float>(D);
-    __syncwarp();
-    if (lane == 0) *st = g2;
+      if (hl * 8 + c * 128 < D) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += acc[c][i] * acc[c][i];
+      }
+    ss = half_sum(ss, hmask);
+    const float g2 = row_state + ss / static_cast<float>(D);
+    if (hl == 0) a.state1[tb.s_off[t] + local_row] = g2;
     const float mult = o.lr / (sqrtf(g2) + o.eps);
 #pragma unroll
     for (int c = 0; c < NCH; ++c) {
-      const int d0 = lane * 4 + c * 128;
+      const int d0 = hl * 8 + c * 128;
       if (d0 < D) {
-        float4 v = Ld4<WT>::ld(w + d0);
-        v.x -= mult * acc[c].x; v.y -= mult * acc[c].y; v.z -= mult * acc[c].z; v.w -= mult * acc[c].w;
-        Ld4<WT>::st(w + d0, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wpre[c][i] -= mult * acc[c][i];
+        Vec8<WT>::st(w + d0, wpre[c]);
       }
     }
     return;
   }
 #pragma unroll
   for (int c = 0; c < NCH; ++c) {
-    const int d0 = lane * 4 + c * 128;
+    const int d0 = hl * 8 + c * 128;
     if (d0 >= D) continue;
-    float4 v = Ld4<WT>::ld(w + d0);
-    float g[4] = {acc[c].x, acc[c].y, acc[c].z, acc[c].w};
-    float wv[4] = {v.x, v.y, v.z, v.w};
+    float (&wv)[8] = wpre[c];
     if (o.type == OPT_SGD) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) wv[i] -= o.lr * (g[i] + o.weight_decay * wv[i]);
+      for (int i = 0; i < 8; ++i) wv[i] -= o.lr * (acc[c][i] + o.weight_decay * wv[i]);
     } else if (o.type == OPT_ADAGRAD) {
-      float* st = a.state1 + a.s_offsets[t] + local_row * D + d0;
-      float4 s = *reinterpret_cast<float4*>(st);
-      float sv[4] = {s.x, s.y, s.z, s.w};
+      float* st = a.state1 + tb.s_off[t] + local_row * D + d0;
+      float sv[8];
+      Vec8<float>::ld(st, sv);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { sv[i] += g[i] * g[i]; wv[i] -= o.lr * g[i] / (sqrtf(sv[i]) + o.eps); }
-      *reinterpret_cast<float4*>(st) = make_float4(sv[0], sv[1], sv[2], sv[3]);
-    } else {  // Adam
-      float* m = a.state1 + a.s_offsets[t] + local_row * D + d0;
-      float* vv = a.state2 + a.s_offsets[t] + local_row * D + d0;
-      float4 m4 = *reinterpret_cast<float4*>(m), v4 = *reinterpret_cast<float4*>(vv);
-      float mv[4] = {m4.x, m4.y, m4.z, m4.w}, vvv[4] = {v4.x, v4.y, v4.z, v4.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float gi = g[i] + o.weight_decay * wv[i];
-        mv[i] = o.beta1 * mv[i] + (1.f - o.beta1) * gi;
-        vvv[i] = o.beta2 * vvv[i] + (1.f - o.beta2) * gi * gi;
-        wv[i] -= (o.lr / o.bias_c1) * mv[i] / (sqrtf(vvv[i] / o.bias_c2) + o.eps);
+      for (int i = 0; i < 8; ++i) {
+        sv[i] += acc[c][i] * acc[c][i];
+        wv[i] -= o.lr * acc[c][i] / (sqrtf(sv[i]) + o.eps);
       }
-      *reinterpret_cast<float4*>(m) = make_float4(mv[0], mv[1], mv[2], mv[3]);
-      *reinterpret_cast<float4*>(vv) = make_float4(vvv[0], vvv[1], vvv[2], vvv[3]);
-    }
-    Ld4<WT>::st(w + d0, make_float4(wv[0], wv[1], wv[2], wv[3]));
-  }
-}
-
-__device__ __forceinline__ int table_of_key(const long long* cumsum, int T, long long key) {
-  int lo = 0, hi = T;
-  while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (cumsum[mid] <= key) lo = mid; else hi = mid; }
-  return lo;
-}
-
-template <typename GT, int NCH>
-__device__ __forceinline__ void accumulate_entry(const BwdArgs& a, int D, int bag, long long B_global,
-                                                 float4 (&acc)[NCH], int lane) {
-  const int f = static_cast<int>(bag / B_global);
-  const int D_offset = a.shards[f].D_offset;
-  const long long bg = bag - static_cast<long long>(f) * B_global;
-  const int r = static_cast<int>(bg / a.B_local);
-  const long long bl = bg % a.B_local;
-  const GT* g = reinterpret_cast<const GT*>(a.grad_ptrs[r]) + bl * a.ld_g + D_offset;
-  float scale = 1.f;
-  if (a.pooling == POOL_MEAN && a.offsets) {
-    const long long len = a.offsets[bag + 1] - a.offsets[bag];
-    scale = len > 0 ? 1.f / static_cast<float>(len) : 0.f;
-  }
+      Vec8<float>::st(st, sv);
+    } else {  // Adam
+      float* m = a.state1 + tb.s_off[t] + local_row * D + d0;
+      float* vv = a.state2 + tb.s_off[t] + local_row * D + d0;
+      float mv[8], vs[8];
+      Vec8<float>::ld(m, mv);
+      Vec8<float>::ld(vv, vs);
 #pragma unroll
-  for (int c = 0; c < NCH; ++c) {
-    const int d0 = lane * 4 + c * 128;
-    if (d0 < D) {
-      const float4 v = Ld4<GT>::ld(g + d0);
-      acc[c].x += v.x * scale; acc[c].y += v.y * scale; acc[c].z += v.z * scale; acc[c].w += v.w * scale;
+      for (int i = 0; i < 8; ++i) {
+        const float gi = acc[c][i] + o.weight_decay * wv[i];
+        mv[i] = o.beta1 * mv[i] + (1.f - o.beta1) * gi;
+        vs[i] = o.beta2 * vs[i] + (1.f - o.beta2) * gi * gi;
+        wv[i] -= (o.lr / o.bias_c1) * mv[i] / (sqrtf(vs[i] / o.bias_c2) + o.eps);
+      }
+      Vec8<float>::st(m, mv);
+      Vec8<float>::st(vv, vs);
     }
+    Vec8<WT>::st(w + d0, wv);
   }
 }
 
-// one warp per unique row; rows with very long segments are deferred to the block kernel
+// (1) one half-warp per unique row; segments longer than long_threshold are split into chunks of
+//     LONG_CHUNK entries and queued for kernels (2) and (3).
 template <typename WT, typename GT, int NCH>
-__global__ void tbe_backward_warp_kernel(const BwdArgs a) {
-  const int lane = threadIdx.x & 31;
-  const int warps_total = (gridDim.x * blockDim.x) >> 5;
+__global__ void __launch_bounds__(256) tbe_bwd_short_kernel(const BwdArgs a) {
+  extern __shared__ long long sm_tabs[];
+  const Tabs tb = load_tabs(a, sm_tabs);
+  const int hl = threadIdx.x & 15;
+  const unsigned hmask = (threadIdx.x & 16) ? 0xFFFF0000u : 0x0000FFFFu;
+  const int groups_total = gridDim.x * (blockDim.x >> 4);
   const int n = *a.num_runs;
-  const long long B_global = static_cast<long long>(a.B_local) * a.world;
-  for (int s = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; s < n; s += warps_total) {
+  const unsigned B_global = static_cast<unsigned>(a.B_local) * static_cast<unsigned>(a.world);
+  for (int s = blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4); s < n; s += groups_total) {
     const long long key = a.unique_keys[s];
     if (key < 0) continue;
     const int beg = a.seg_offsets[s], end = a.seg_offsets[s + 1];
-    if (end - beg > a.long_threshold) {
-      if (lane == 0) {
-        const int slot = atomicAdd(a.long_count, 1);
-        if (slot < a.long_cap) a.long_list[slot] = s;
-        else if (a.status) atomicCAS(a.status, 0, RB_ERR_CAPACITY);
+    const int len = end - beg;
+    if (len > a.long_threshold) {
+      int li = 0, base = 0;
+      const int nch = (len + LONG_CHUNK - 1) / LONG_CHUNK;
+      if (hl == 0) {
+        li = atomicAdd(a.counters, 1);
+        if (li < a.long_cap) {
+          a.long_list[li] = s;
+          base = atomicAdd(a.counters + 1, nch);
+        } else if (a.status) {
+          atomicCAS(a.status, 0, RB_ERR_CAPACITY);
+        }
+      }
+      li = __shfl_sync(hmask, li, threadIdx.x & 16);
+      base = __shfl_sync(hmask, base, threadIdx.x & 16);
+      if (li < a.long_cap) {
+        for (int c = hl; c < nch; c += 16) {
+          if (base + c < a.chunk_cap) a.chunk_list[base + c] = make_int2(li, c);
+          else if (a.status) atomicCAS(a.status, 0, RB_ERR_CAPACITY);
+        }
       }
       continue;
     }
-    const int t = table_of_key(a.key_cumsum, a.n_tables, key);
-    const int D = a.shards[a.sorted_bags[beg] / B_global].D;
-    float4 acc[NCH];
+    const int t = table_of_key(tb.key_cumsum, a.n_tables, key);
+    const int D = tb.f_D[static_cast<unsigned>(a.sorted_bags[beg]) / B_global];
+    float acc[NCH][8], wpre[NCH][8], row_state;
 #pragma unroll
-    for (int c = 0; c < NCH; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int j = beg; j < end; ++j) accumulate_entry<GT, NCH>(a, D, a.sorted_bags[j], B_global, acc, lane);
-    apply_row_update<WT, NCH>(a, t, key - a.key_cumsum[t], D, acc, lane);
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
+    preload_row<WT, NCH>(a, tb, t, key - tb.key_cumsum[t], D, wpre, row_state, hl);
+    accumulate_range<GT, NCH>(a, tb, D, beg, end, B_global, acc, hl);
+    apply_row_update<WT, NCH>(a, tb, t, key - tb.key_cumsum[t], D, acc, wpre, row_state, hl, hmask);
   }
 }
 
-// one CTA (8 warps) per long segment: warps stride over the entries, partial sums meet in
-// shared memory, warp 0 applies the optimizer.
-template <typename WT, typename GT, int NCH>
-__global__ void __launch_bounds__(256) tbe_backward_block_kernel(const BwdArgs a) {
-  __shared__ float4 red[8][NCH * 32];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int n_long = *a.long_count;
+// (2) one half-warp per chunk of a long segment: partial sum -> fp32 atomics into the segment's scratch row
+template <typename GT, int NCH>
+__global__ void __launch_bounds__(256) tbe_bwd_long_chunk_kernel(const BwdArgs a) {
+  extern __shared__ long long sm_tabs[];
+  const Tabs tb = load_tabs(a, sm_tabs);
+  const int hl = threadIdx.x & 15;
+  const int groups_total = gridDim.x * (blockDim.x >> 4);
+  int n_chunks = a.counters[1];
+  if (n_chunks > a.chunk_cap) n_chunks = a.chunk_cap;
+  const unsigned B_global = static_cast<unsigned>(a.B_local) * static_cast<unsigned>(a.world);
+  for (int ci = blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4); ci < n_chunks; ci += groups_total) {
+    const int2 item = a.chunk_list[ci];
+    const int s = a.long_list[item.x];
+    const int seg_beg = a.seg_offsets[s], seg_end = a.seg_offsets[s + 1];
+    const int beg = seg_beg + item.y * LONG_CHUNK;
+    const int end = min(seg_end, beg + LONG_CHUNK);
+    const int D = tb.f_D[static_cast<unsigned>(a.sorted_bags[seg_beg]) / B_global];
+    float acc[NCH][8];
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
+    accumulate_range<GT, NCH>(a, tb, D, beg, end, B_global, acc, hl);
+    float* dst = a.long_accum + static_cast<long long>(item.x) * a.accum_ld;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) {
+      const int d0 = hl * 8 + c * 128;
+      if (d0 < D) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) atomicAdd(dst + d0 + i, acc[c][i]);
+      }
+    }
+  }
+}
+
+// (3) one half-warp per long segment: read its scratch row, clear it for the next launch, update
+template <typename WT, int NCH>
+__global__ void __launch_bounds__(256) tbe_bwd_long_final_kernel(const BwdArgs a) {
+  extern __shared__ long long sm_tabs[];
+  const Tabs tb = load_tabs(a, sm_tabs);
+  const int hl = threadIdx.x & 15;
+  const unsigned hmask = (threadIdx.x & 16) ? 0xFFFF0000u : 0x0000FFFFu;
+  const int groups_total = gridDim.x * (blockDim.x >> 4);
+  int n_long = a.counters[0];
   if (n_long > a.long_cap) n_long = a.long_cap;
-  const long long B_global = static_cast<long long>(a.B_local) * a.world;
-  for (int li = blockIdx.x; li < n_long; li += gridDim.x) {
+  const unsigned B_global = static_cast<unsigned>(a.B_local) * static_cast<unsigned>(a.world);
+  for (int li = blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4); li < n_long; li += groups_total) {
     const int s = a.long_list[li];
     const long long key = a.unique_keys[s];
-    const int beg = a.seg_offsets[s], end = a.seg_offsets[s + 1];
-    const int t = table_of_key(a.key_cumsum, a.n_tables, key);
-    const int D = a.shards[a.sorted_bags[beg] / B_global].D;
-    float4 acc[NCH];
+    const int t = table_of_key(tb.key_cumsum, a.n_tables, key);
+    const int D = tb.f_D[static_cast<unsigned>(a.sorted_bags[a.seg_offsets[s]]) / B_global];
+    float* src = a.long_accum + static_cast<long long>(li) * a.accum_ld;
+    float acc[NCH][8], wpre[NCH][8], row_state;
+    preload_row<WT, NCH>(a, tb, t, key - tb.key_cumsum[t], D, wpre, row_state, hl);
 #pragma unroll
-    for (int c = 0; c < NCH; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int j = beg + warp; j < end; j += 8) accumulate_entry<GT, NCH>(a, D, a.sorted_bags[j], B_global, acc, lane);
+    for (int c = 0; c < NCH; ++c) {
+      const int d0 = hl * 8 + c * 128;
+      if (d0 < D) {
+        Vec8<float>::ld(src + d0, acc[c]);
+        const float z[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        Vec8<float>::st(src + d0, z);
+      } else {
 #pragma unroll
-    for (int c = 0; c < NCH; ++c) red[warp][c * 32 + lane] = acc[c];
-    __syncthreads();
-    if (warp == 0) {
-#pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        float4 sum = red[0][c * 32 + lane];
-        for (int w = 1; w < 8; ++w) {
-          const float4 v = red[w][c * 32 + lane];
-          sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-        }
-        acc[c] = sum;
+        for (int i = 0; i < 8; ++i) acc[c][i] = 0.f;
       }
-      apply_row_update<WT, NCH>(a, t, key - a.key_cumsum[t], D, acc, lane);
     }
-    __syncthreads();
+    apply_row_update<WT, NCH>(a, tb, t, key - tb.key_cumsum[t], D, acc, wpre, row_state, hl, hmask);
   }
 }
 
 template <typename WT, typename GT, int NCH>
 int launch_bwd(const BwdArgs& a, int max_runs, int num_sms, cudaStream_t st) {
-  int blocks = (max_runs + 7) / 8;
+  const size_t smem = tabs_bytes(a.n_tables, a.T, a.world);
+  if (smem > 48 * 1024) return -6;
+  int blocks = (max_runs + 15) / 16;
   const int cap = num_sms * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  tbe_backward_warp_kernel<WT, GT, NCH><<<blocks, 256, 0, st>>>(a);
-  tbe_backward_block_kernel<WT, GT, NCH><<<num_sms * 2, 256, 0, st>>>(a);
+  tbe_bwd_short_kernel<WT, GT, NCH><<<blocks, 256, smem, st>>>(a);
+  tbe_bwd_long_chunk_kernel<GT, NCH><<<num_sms * 4, 256, smem, st>>>(a);
+  tbe_bwd_long_final_kernel<WT, NCH><<<num_sms, 256, smem, st>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -432,13 +640,30 @@ __global__ void scatter_rows_kernel(const T4* __restrict__ src, const long long*
 
 RB_API int rb_tbe_forward(const void* shards, const long long* ptrs, const void* indices, int idx64,
                           const long long* offsets, int T, int B, int world, int self, int pooling,
-                          int w_dtype, void* out, int out_dtype, long long ld_out, int* status,
+                          int w_dtype, void* out, int out_dtype, long long ld_out, int vec8_ok, int* status,
                           cudaStream_t st) {
   const long long n_warps = static_cast<long long>(T) * B;
   if (n_warps == 0) return 0;
   const int threads = 256;
-  const long long blocks = (n_warps * 32 + threads - 1) / threads;
   const TableShard* sh = reinterpret_cast<const TableShard*>(shards);
+  if (offsets == nullptr && vec8_ok) {
+    // one id per bag, every D a multiple of 8 and 16-byte aligned rows: half-warp fast path
+    constexpr int G = 4;
+    const long long halves = static_cast<long long>(T) * ((B + G - 1) / G);
+    const long long fblocks = (halves * 16 + threads - 1) / threads;
+    RB_W_DISPATCH(w_dtype, RB_O_DISPATCH(out_dtype, {
+      if (idx64)
+        tbe_forward_onehot_kernel<WT, OT, long long, G><<<fblocks, threads, 0, st>>>(
+            sh, ptrs, reinterpret_cast<const long long*>(indices), T, B, world, self, reinterpret_cast<OT*>(out),
+            ld_out, status);
+      else
+        tbe_forward_onehot_kernel<WT, OT, int, G><<<fblocks, threads, 0, st>>>(
+            sh, ptrs, reinterpret_cast<const int*>(indices), T, B, world, self, reinterpret_cast<OT*>(out), ld_out,
+            status);
+    }))
+    return static_cast<int>(cudaGetLastError());
+  }
+  const long long blocks = (n_warps * 32 + threads - 1) / threads;
   RB_W_DISPATCH(w_dtype, RB_O_DISPATCH(out_dtype, {
     if (idx64)
       tbe_forward_kernel<WT, OT, long long><<<blocks, threads, 0, st>>>(
@@ -530,8 +755,8 @@ RB_API int rb_tbe_backward_update(
     const long long* offsets, int pooling, const int* sorted_bags, const long long* unique_keys,
     const int* seg_offsets, const int* num_runs, int max_runs, void* weights, int w_dtype, float* state1,
     float* state2, int opt_type, float lr, float eps, float beta1, float beta2, float weight_decay,
-    float bias_c1, float bias_c2, int max_D, int* long_list, int* long_count, int long_cap,
-    int long_threshold, int num_sms, int* status, cudaStream_t st) {
+    float bias_c1, float bias_c2, int max_D, int* long_list, int* counters, void* chunk_list, float* long_accum,
+    int long_cap, int chunk_cap, int accum_ld, int long_threshold, int num_sms, int* status, cudaStream_t st) {
   if (max_runs <= 0) return 0;
   BwdArgs a;
   a.shards = reinterpret_cast<const TableShard*>(shards);
@@ -542,10 +767,12 @@ RB_API int rb_tbe_backward_update(
   a.state2 = state2;
   a.opt.type = opt_type; a.opt.lr = lr; a.opt.eps = eps; a.opt.beta1 = beta1; a.opt.beta2 = beta2;
   a.opt.weight_decay = weight_decay; a.opt.bias_c1 = bias_c1; a.opt.bias_c2 = bias_c2;
-  a.long_list = long_list; a.long_count = long_count; a.long_cap = long_cap;
+  a.long_list = long_list; a.counters = counters; a.chunk_list = reinterpret_cast<int2*>(chunk_list);
+  a.long_accum = long_accum; a.long_cap = long_cap; a.chunk_cap = chunk_cap; a.accum_ld = accum_ld;
   a.long_threshold = long_threshold; a.status = status;
   if (num_sms <= 0) num_sms = 148;
-  RB_CUDA_CHECK(cudaMemsetAsync(long_count, 0, sizeof(int), st));
+  if (max_D % 8 || accum_ld < max_D) return -7;
+  RB_CUDA_CHECK(cudaMemsetAsync(counters, 0, 2 * sizeof(int), st));
 #define RB_G_DISPATCH(...)                                                  \
   switch (g_dtype) {                                                        \
     case DT_F32: { using GT = float; __VA_ARGS__; } break;                  \

@@ -109,38 +109,44 @@ interaction_fwd_kernel(const __nv_bfloat16* __restrict__ X0, long long ld0, cons
 }
 
 // ------------------------------- backward ----------------------------------
+// Per warp: X tile (also the output staging: the dX columns of an n-tile overwrite the X columns
+// that only that n-tile reads), the packed dR row and the symmetric 32x32 dZ tile.
 template <int D, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 interaction_bwd_kernel(const __nv_bfloat16* __restrict__ X0, long long ld0, const __nv_bfloat16* __restrict__ XS,
-                       long long lds, const __nv_bfloat16* __restrict__ dR, long long ldr, int B, int F,
+                       long long lds, const __nv_bfloat16* __restrict__ dR, long long ldr, int dr_cols, int B, int F,
                        __nv_bfloat16* __restrict__ dX0, long long ldd0, __nv_bfloat16* __restrict__ dXS,
-                       long long ldds) {
+                       long long ldds, int mask_x0) {
   using L = Lay<D>;
   extern __shared__ __align__(16) uint8_t smem_i[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int PER_WARP = 2 * L::X_ELEMS + FMAX * L::ZS;
+  constexpr int GS = D + 512;                       // dR row: D direct columns + up to 496 pair terms
+  constexpr int PER_WARP = L::X_ELEMS + FMAX * L::ZS + GS;
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_i) + warp * PER_WARP;
-  __nv_bfloat16* os = xs + L::X_ELEMS;
-  __nv_bfloat16* zs = os + L::X_ELEMS;
-  for (int i = lane; i < (FMAX - F) * L::XS / 2; i += 32)
-    reinterpret_cast<uint32_t*>(xs + F * L::XS)[i] = 0u;
+  __nv_bfloat16* zs = xs + L::X_ELEMS;
+  __nv_bfloat16* gs = zs + FMAX * L::ZS;
   constexpr int VPR = D / 8;
+  const int g_vec = (dr_cols + 7) / 8;
   for (int b = blockIdx.x * WARPS + warp; b < B; b += gridDim.x * WARPS) {
     const uint4* src0 = reinterpret_cast<const uint4*>(X0 + static_cast<long long>(b) * ld0);
     const uint4* src = reinterpret_cast<const uint4*>(XS + static_cast<long long>(b) * lds);
-    const __nv_bfloat16* g = dR + static_cast<long long>(b) * ldr;
+    const uint4* g4 = reinterpret_cast<const uint4*>(dR + static_cast<long long>(b) * ldr);
     __syncwarp();
     for (int i = lane; i < F * VPR; i += 32) {
       const int r = i / VPR, c = i % VPR;
       *reinterpret_cast<uint4*>(xs + r * L::XS + c * 8) = (r == 0) ? __ldg(src0 + c) : __ldg(src + i - VPR);
     }
+    for (int i = lane; i < (FMAX - F) * L::XS / 2; i += 32)
+      reinterpret_cast<uint32_t*>(xs + F * L::XS)[i] = 0u;       // padding rows (the tile is reused as output)
+    for (int i = lane; i < g_vec; i += 32) reinterpret_cast<uint4*>(gs)[i] = __ldg(g4 + i);
+    __syncwarp();
     // symmetric dZ tile: zs[i][j] = dtri(max(i,j), min(i,j)), zero on the diagonal / padding
     for (int e = lane; e < FMAX * FMAX; e += 32) {
       const int i = e >> 5, j = e & 31;
       __nv_bfloat16 v = __float2bfloat16(0.f);
       if (i < F && j < F && i != j) {
         const int hi = i > j ? i : j, lo = i > j ? j : i;
-        v = g[D + hi * (hi - 1) / 2 + lo];
+        v = gs[D + hi * (hi - 1) / 2 + lo];
       }
       zs[i * L::ZS + j] = v;
     }
@@ -172,11 +178,17 @@ interaction_bwd_kernel(const __nv_bfloat16* __restrict__ X0, long long ld0, cons
           const int row = mt * 16 + (lane >> 2) + h * 8;
           const int col = nt * 8 + (lane & 3) * 2;
           float v0 = acc[mt][2 * h], v1 = acc[mt][2 * h + 1];
+          uint32_t* slot = reinterpret_cast<uint32_t*>(xs + row * L::XS + col);
           if (row == 0) {  // the dense feature also feeds the first D columns of R directly
-            v0 += __bfloat162float(g[col]);
-            v1 += __bfloat162float(g[col + 1]);
+            v0 += __bfloat162float(gs[col]);
+            v1 += __bfloat162float(gs[col + 1]);
+            if (mask_x0) {   // feature 0 is a ReLU output: hand back d(pre-activation)
+              const float2 x = rb::unpack_bf16(*slot);
+              v0 = x.x > 0.f ? v0 : 0.f;
+              v1 = x.y > 0.f ? v1 : 0.f;
+            }
           }
-          *reinterpret_cast<uint32_t*>(os + row * L::XS + col) = rb::pack_bf16(v0, v1);
+          *slot = rb::pack_bf16(v0, v1);
         }
     }
     __syncwarp();
@@ -184,7 +196,7 @@ interaction_bwd_kernel(const __nv_bfloat16* __restrict__ X0, long long ld0, cons
     uint4* dst = reinterpret_cast<uint4*>(dXS + static_cast<long long>(b) * ldds);
     for (int i = lane; i < F * VPR; i += 32) {
       const int r = i / VPR, c = i % VPR;
-      const uint4 v = *reinterpret_cast<const uint4*>(os + r * L::XS + c * 8);
+      const uint4 v = *reinterpret_cast<const uint4*>(xs + r * L::XS + c * 8);
       if (r == 0) dst0[c] = v; else dst[i - VPR] = v;
     }
   }
@@ -209,10 +221,12 @@ int launch_fwd(const void* X0, long long ld0, const void* XS, long long lds, int
   return static_cast<int>(cudaGetLastError());
 }
 template <int D>
-int launch_bwd(const void* X0, long long ld0, const void* XS, long long lds, const void* dR, long long ldr, int B,
-               int F, void* dX0, long long ldd0, void* dXS, long long ldds, int num_sms, cudaStream_t st) {
-  constexpr int WARPS = 4;
-  const int smem = WARPS * (2 * Lay<D>::X_ELEMS + FMAX * Lay<D>::ZS) * 2;
+int launch_bwd(const void* X0, long long ld0, const void* XS, long long lds, const void* dR, long long ldr,
+               int dr_cols, int B, int F, void* dX0, long long ldd0, void* dXS, long long ldds, int mask_x0,
+               int num_sms, cudaStream_t st) {
+  constexpr int WARPS = 8;
+  const int smem = WARPS * (Lay<D>::X_ELEMS + FMAX * Lay<D>::ZS + D + 512) * 2;
+  if (dr_cols > D + 512 || (ldr % 8)) return -3;
   static bool set = false;
   if (!set) {
     RB_CUDA_CHECK(cudaFuncSetAttribute(interaction_bwd_kernel<D, WARPS>,
@@ -223,8 +237,8 @@ int launch_bwd(const void* X0, long long ld0, const void* XS, long long lds, con
   if (blocks > num_sms * 2) blocks = num_sms * 2;
   interaction_bwd_kernel<D, WARPS><<<blocks, WARPS * 32, smem, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(X0), ld0, reinterpret_cast<const __nv_bfloat16*>(XS), lds,
-      reinterpret_cast<const __nv_bfloat16*>(dR), ldr, B, F, reinterpret_cast<__nv_bfloat16*>(dX0), ldd0,
-      reinterpret_cast<__nv_bfloat16*>(dXS), ldds);
+      reinterpret_cast<const __nv_bfloat16*>(dR), ldr, dr_cols, B, F, reinterpret_cast<__nv_bfloat16*>(dX0), ldd0,
+      reinterpret_cast<__nv_bfloat16*>(dXS), ldds, mask_x0);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -247,18 +261,20 @@ RB_API int rb_dot_interaction_fwd(const void* X0, long long ld0, const void* XS,
   }
 }
 
+// dR [B, dr_cols] (row stride ldr, a multiple of 8).  mask_x0 != 0: X0 is a ReLU output and dX0 is
+// returned multiplied by (X0 > 0).
 RB_API int rb_dot_interaction_bwd(const void* X0, long long ld0, const void* XS, long long lds, const void* dR,
-                                  long long ldr, int B, int F, int D, void* dX0, long long ldd0, void* dXS,
-                                  long long ldds, int num_sms, cudaStream_t st) {
+                                  long long ldr, int dr_cols, int B, int F, int D, void* dX0, long long ldd0,
+                                  void* dXS, long long ldds, int mask_x0, int num_sms, cudaStream_t st) {
   if (B == 0) return 0;
   if (F > FMAX || F < 2) return -1;
   if (num_sms <= 0) num_sms = 148;
   switch (D) {
-    case 16: return launch_bwd<16>(X0, ld0, XS, lds, dR, ldr, B, F, dX0, ldd0, dXS, ldds, num_sms, st);
-    case 32: return launch_bwd<32>(X0, ld0, XS, lds, dR, ldr, B, F, dX0, ldd0, dXS, ldds, num_sms, st);
-    case 64: return launch_bwd<64>(X0, ld0, XS, lds, dR, ldr, B, F, dX0, ldd0, dXS, ldds, num_sms, st);
-    case 128: return launch_bwd<128>(X0, ld0, XS, lds, dR, ldr, B, F, dX0, ldd0, dXS, ldds, num_sms, st);
-    case 256: return launch_bwd<256>(X0, ld0, XS, lds, dR, ldr, B, F, dX0, ldd0, dXS, ldds, num_sms, st);
+    case 16: return launch_bwd<16>(X0, ld0, XS, lds, dR, ldr, dr_cols, B, F, dX0, ldd0, dXS, ldds, mask_x0, num_sms, st);
+    case 32: return launch_bwd<32>(X0, ld0, XS, lds, dR, ldr, dr_cols, B, F, dX0, ldd0, dXS, ldds, mask_x0, num_sms, st);
+    case 64: return launch_bwd<64>(X0, ld0, XS, lds, dR, ldr, dr_cols, B, F, dX0, ldd0, dXS, ldds, mask_x0, num_sms, st);
+    case 128: return launch_bwd<128>(X0, ld0, XS, lds, dR, ldr, dr_cols, B, F, dX0, ldd0, dXS, ldds, mask_x0, num_sms, st);
+    case 256: return launch_bwd<256>(X0, ld0, XS, lds, dR, ldr, dr_cols, B, F, dX0, ldd0, dXS, ldds, mask_x0, num_sms, st);
     default: return -2;
   }
 }

@@ -135,11 +135,11 @@ class DLRM(nn.Module):
         """Everything up to (excluding) the logit layer."""
         if self.fused:
             x = dense_ops.cast_pad(dense_features, self.dense_arch.in_padded, self.compute_dtype)
-            d = self.dense_arch(x)
+            d = self.dense_arch(x, grad_premasked=True)     # the interaction backward applies the ReLU mask
             pooled = self._pooled(sparse_features)
             if pooled.dtype != self.compute_dtype:
                 pooled = pooled.to(self.compute_dtype)
-            r = dot_interaction(d, pooled, self.F, self.inter_cols)
+            r = dot_interaction(d, pooled, self.F, self.inter_cols, mask_x0=True)
             return self.over_arch(r, grad_premasked=True)
         d = self.dense_arch(dense_features.float())
         pooled = self._pooled(sparse_features).float()

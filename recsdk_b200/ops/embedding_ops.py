@@ -179,11 +179,14 @@ def tbe_forward(layout: TbeLayout, dev: dict, indices: torch.Tensor, offsets: Op
 
     ``offsets`` is ``None`` for one-hot features (bag ``t*B+b`` holds ``indices[t*B+b]``)."""
     assert out.stride(1) == 1
+    out_item = out.element_size()
+    vec8_ok = int(all(d % 8 == 0 for d in layout.dims) and (out.stride(0) * out_item) % 16 == 0
+                  and out.data_ptr() % 16 == 0)
     rc = _lib.lib().rb_tbe_forward(
         dev["shards"].data_ptr(), dev["ptrs"].data_ptr(), indices.data_ptr(), int(indices.dtype == torch.int64),
         _lib.ptr(offsets), layout.T, B, layout.world, layout.rank, pooling, _lib.dtype_code(w_dtype),
-        out.data_ptr(), _lib.dtype_code(out.dtype), out.stride(0), _lib.status_tensor(out.device).data_ptr(),
-        _lib.stream_ptr(out.device))
+        out.data_ptr(), _lib.dtype_code(out.dtype), out.stride(0), vec8_ok,
+        _lib.status_tensor(out.device).data_ptr(), _lib.stream_ptr(out.device))
     _lib.check(rc, "rb_tbe_forward")
     return out
 
@@ -200,11 +203,22 @@ def tbe_sequence(layout: TbeLayout, dev: dict, indices: torch.Tensor, pos_offset
     return out
 
 
+LONG_CHUNK = 32  # must match csrc/cuda/embedding.cu
+
+
 class BackwardWorkspace:
-    def __init__(self, device: torch.device, long_cap: int = 1 << 16) -> None:
-        self.long_list = torch.empty(long_cap, dtype=torch.int32, device=device)
-        self.long_count = torch.zeros(1, dtype=torch.int32, device=device)
-        self.long_cap = long_cap
+    """Scratch of the fused backward: the list of long segments (rows hit by more than
+    ``long_threshold`` bags), their chunk work-list and one fp32 accumulation row per long segment.
+    ``long_accum`` is all-zero between launches (the kernels restore that themselves)."""
+
+    def __init__(self, device: torch.device, max_nnz: int, max_D: int, long_cap: int = 8192) -> None:
+        self.long_cap = int(long_cap)
+        self.chunk_cap = int(max_nnz) // LONG_CHUNK + self.long_cap
+        self.accum_ld = (int(max_D) + 127) // 128 * 128
+        self.long_list = torch.empty(self.long_cap, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(2, dtype=torch.int32, device=device)
+        self.chunk_list = torch.empty(self.chunk_cap * 2, dtype=torch.int32, device=device)
+        self.long_accum = torch.zeros(self.long_cap * self.accum_ld, dtype=torch.float32, device=device)
 
 
 def tbe_backward_update(layout: TbeLayout, dev: dict, seg: SortedSegments, grad_ptrs: torch.Tensor, ld_g: int,
@@ -222,7 +236,8 @@ def tbe_backward_update(layout: TbeLayout, dev: dict, seg: SortedSegments, grad_
         pooling, seg.sorted_bags.data_ptr(), seg.unique_keys.data_ptr(), seg.seg_offsets.data_ptr(),
         seg.num_runs.data_ptr(), seg.max_runs, weights.data_ptr(), _lib.dtype_code(weights.dtype),
         _lib.ptr(state1), _lib.ptr(state2), opt.kind, opt.lr, opt.eps, opt.beta1, opt.beta2, opt.weight_decay,
-        bc1, bc2, layout.max_D, ws.long_list.data_ptr(), ws.long_count.data_ptr(), ws.long_cap, long_threshold,
+        bc1, bc2, layout.max_D, ws.long_list.data_ptr(), ws.counters.data_ptr(), ws.chunk_list.data_ptr(),
+        ws.long_accum.data_ptr(), ws.long_cap, ws.chunk_cap, ws.accum_ld, long_threshold,
         _lib.num_sms(weights.device), _lib.status_tensor(weights.device).data_ptr(),
         _lib.stream_ptr(weights.device))
     _lib.check(rc, "rb_tbe_backward_update")

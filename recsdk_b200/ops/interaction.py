@@ -62,27 +62,31 @@ def dot_interaction_fwd(x0: torch.Tensor, xs: torch.Tensor, F: int, out: torch.T
 
 
 def dot_interaction_bwd(x0: torch.Tensor, xs: torch.Tensor, dR: torch.Tensor, F: int, dx0: torch.Tensor,
-                        dxs: torch.Tensor) -> None:
+                        dxs: torch.Tensor, mask_x0: bool = False) -> None:
+    """``mask_x0``: ``x0`` is a ReLU output; return ``dx0 * (x0 > 0)`` (the gradient of its pre-activation)."""
     B, D = x0.shape
     if not x0.is_cuda:
         a, b = dot_interaction_bwd_ref(x0, xs, dR, F)
+        if mask_x0:
+            a = a * (x0.float() > 0)
         dx0.copy_(a.to(dx0.dtype))
         dxs.copy_(b.to(dxs.dtype))
         return
     assert dR.stride(1) == 1 and dx0.stride(1) == 1 and dxs.stride(1) == 1
     rc = _lib.lib().rb_dot_interaction_bwd(x0.data_ptr(), x0.stride(0), xs.data_ptr(), xs.stride(0), dR.data_ptr(),
-                                           dR.stride(0), B, F, D, dx0.data_ptr(), dx0.stride(0), dxs.data_ptr(),
-                                           dxs.stride(0), _lib.num_sms(x0.device), _lib.stream_ptr(x0.device))
+                                           dR.stride(0), dR.shape[1], B, F, D, dx0.data_ptr(), dx0.stride(0),
+                                           dxs.data_ptr(), dxs.stride(0), int(mask_x0), _lib.num_sms(x0.device),
+                                           _lib.stream_ptr(x0.device))
     _lib.check(rc, "rb_dot_interaction_bwd")
 
 
 class DotInteractionFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x0: torch.Tensor, xs: torch.Tensor, F: int, out_cols: int):
+    def forward(ctx, x0: torch.Tensor, xs: torch.Tensor, F: int, out_cols: int, mask_x0: bool = False):
         out = torch.empty(x0.shape[0], out_cols, dtype=x0.dtype, device=x0.device)
         dot_interaction_fwd(x0, xs, F, out)
         ctx.save_for_backward(x0, xs)
-        ctx.F = F
+        ctx.F, ctx.mask_x0 = F, mask_x0
         return out
 
     @staticmethod
@@ -90,9 +94,11 @@ class DotInteractionFunction(torch.autograd.Function):
         x0, xs = ctx.saved_tensors
         dx0 = torch.empty_like(x0)
         dxs = torch.empty_like(xs)
-        dot_interaction_bwd(x0, xs, dR.contiguous(), ctx.F, dx0, dxs)
-        return dx0, dxs, None, None
+        dot_interaction_bwd(x0, xs, dR if dR.stride(1) == 1 else dR.contiguous(), ctx.F, dx0, dxs, ctx.mask_x0)
+        return dx0, dxs, None, None, None
 
 
-def dot_interaction(x0: torch.Tensor, xs: torch.Tensor, F: int, out_cols: int) -> torch.Tensor:
-    return DotInteractionFunction.apply(x0, xs, F, out_cols)
+def dot_interaction(x0: torch.Tensor, xs: torch.Tensor, F: int, out_cols: int, mask_x0: bool = False) -> torch.Tensor:
+    """``mask_x0=True`` promises that ``x0`` comes out of a ReLU; its returned gradient is then already
+    multiplied by the ReLU mask (the producing MLP can skip its own masking pass)."""
+    return DotInteractionFunction.apply(x0, xs, F, out_cols, mask_x0)

@@ -117,8 +117,8 @@ class ShardedEmbeddingBagCollection(nn.Module):
         self.layout = E.TbeLayout([t.embedding_dim for t in tables], [t.num_embeddings for t in tables], kinds,
                                   owners, self.world, self.rank, feature_table)
         for d in self.layout.dims:
-            if d % 4:
-                raise ValueError("embedding_dim must be a multiple of 4")
+            if d % 8:
+                raise ValueError("embedding_dim must be a multiple of 8 (16-byte row vectors)")
         self.peer = peer
         if self.world > 1 and peer is None:
             raise ValueError("world_size > 1 needs a PeerGroup")
@@ -165,7 +165,7 @@ class ShardedEmbeddingBagCollection(nn.Module):
             self.reset_parameters()
         self._anchor = nn.Parameter(torch.zeros(1, device=device))   # makes autograd call our backward
         self._anchor._in_backward_optimizers = True  # type: ignore[attr-defined]
-        self._bwd_ws = E.BackwardWorkspace(device)
+        self._bwd_ws: Optional[E.BackwardWorkspace] = None
         self._sorter: Optional[E.SegmentSorter] = None
         self._gather_ids: Optional[object] = None
         self._gather_offs: Optional[object] = None
@@ -257,6 +257,7 @@ class ShardedEmbeddingBagCollection(nn.Module):
         self._caps = (cap_b, cap_n)
         T = self.layout.T
         self._sorter = E.SegmentSorter(cap_n * self.world, self.device)
+        self._bwd_ws = E.BackwardWorkspace(self.device, cap_n * self.world, self.layout.max_D)
         if self.world > 1:
             self._gather_ids = self.peer.alloc(self.world * cap_n * 8)
             self._gather_offs = self.peer.alloc(self.world * (T * cap_b + 2) * 8)

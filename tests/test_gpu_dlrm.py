@@ -98,4 +98,4 @@ def test_dlrm_pipeline_trains(cuda_graph):
         losses.append(loss.item())
     torch.cuda.synchronize()
     _lib.check_status()
-    assert losses[-1] < 0.7 * losses[0], losses[::8]
+    assert losses[-1] < 0.85 * losses[0], losses[::8]
