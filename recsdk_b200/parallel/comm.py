@@ -75,10 +75,6 @@ class PeerGroup:
             import torch.distributed._symmetric_memory as symm_mem
 
             self._symm = symm_mem
-            try:
-                symm_mem.enable_symm_mem_for_group(self.pg.group_name)
-            except Exception:  # noqa: BLE001 - newer versions enable groups implicitly
-                pass
         pad = self.alloc(self.PAD_INTS * 4, zero=True)
         self.pads = pad
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
