@@ -1,0 +1,173 @@
+// CPU id processing: id -> slot mapping with fused unique, sort-based parallel unique, and row-wise
+// bucketisation of KJT values.  Behavioural spec: hybrid_torchrec/src/ids_process/ids_mapper.{h,cpp}
+// (FindOrInsert, UniqueAndLookupOut, ParallelUniqueHashOut), unique.cpp:55-129, bucketize.cpp:35-305.
+#pragma once
+#include <omp.h>
+
+#include <algorithm>
+#include <numeric>
+
+#include "common.h"
+
+namespace rbh {
+
+// Maps raw int64 ids to dense slots [0, size) in first-seen order (monotone allocation); keeps the
+// reverse slot -> id vector.  Insertions are serialised by a mutex; lookups of an unchanged map are
+// safe from many threads.
+class IdsMapper {
+ public:
+  explicit IdsMapper(int64_t max_slots, size_t reserve = 1024) : max_slots_(max_slots), map_(reserve) {}
+
+  int64_t size() const { return static_cast<int64_t>(slot2id_.size()); }
+  int64_t capacity() const { return max_slots_; }
+
+  // slot of id, inserting when new; throws when the table is full
+  int64_t find_or_insert(int64_t id) {
+    std::lock_guard<std::mutex> lk(mu_);
+    return find_or_insert_unlocked(id);
+  }
+
+  int64_t find(int64_t id) const {
+    const int64_t* p = map_.find(id);
+    return p ? *p : -1;
+  }
+
+  // ids[n] -> out[n] slots (inserting new ids)
+  void ids2indices(const int64_t* ids, int64_t n, int64_t* out) {
+    std::lock_guard<std::mutex> lk(mu_);
+    for (int64_t i = 0; i < n; ++i) out[i] = find_or_insert_unlocked(ids[i]);
+  }
+
+  // Fused unique + lookup for one table's ids:
+  //   unique_ids[u]   distinct raw ids in first-seen order
+  //   unique[u]       their slots
+  //   inverse[i]      position of ids[i] in unique_ids
+  //   hash_indices[i] slot of ids[i]
+  // Returns u.  Uses a per-call scratch map keyed by raw id.
+  int64_t unique_and_lookup(const int64_t* ids, int64_t n, int64_t* hash_indices, int64_t* unique,
+                            int64_t* unique_ids, int64_t* inverse) {
+    FlatMap<int64_t> seen(static_cast<size_t>(n) + 1);
+    int64_t u = 0;
+    std::lock_guard<std::mutex> lk(mu_);
+    for (int64_t i = 0; i < n; ++i) {
+      auto r = seen.insert(ids[i], u);
+      if (r.second) {
+        unique_ids[u] = ids[i];
+        unique[u] = find_or_insert_unlocked(ids[i]);
+        ++u;
+      }
+      const int64_t pos = *r.first;
+      inverse[i] = pos;
+      hash_indices[i] = unique[pos];
+    }
+    return u;
+  }
+
+  const std::vector<int64_t>& slot2id() const { return slot2id_; }
+
+  // bulk restore (checkpoint): ids in slot order
+  void load(const int64_t* ids, int64_t n) {
+    std::lock_guard<std::mutex> lk(mu_);
+    map_.clear();
+    slot2id_.clear();
+    for (int64_t i = 0; i < n; ++i) find_or_insert_unlocked(ids[i]);
+  }
+
+ private:
+  int64_t find_or_insert_unlocked(int64_t id) {
+    int64_t* p = map_.find(id);
+    if (p) return *p;
+    const int64_t slot = static_cast<int64_t>(slot2id_.size());
+    if (slot >= max_slots_) throw std::runtime_error("IdsMapper: table is full (" + std::to_string(max_slots_) + " slots)");
+    map_.insert(id, slot);
+    slot2id_.push_back(id);
+    return slot;
+  }
+  int64_t max_slots_;
+  FlatMap<int64_t> map_;
+  std::vector<int64_t> slot2id_;
+  mutable std::mutex mu_;
+};
+
+// Sort-based unique with inverse (stable w.r.t. value order): out_unique sorted ascending.
+// Parallel: chunks are sorted by OpenMP threads and merged.
+inline int64_t unique_parallel(const int64_t* in, int64_t n, int64_t* out_unique, int64_t* out_inverse,
+                               int64_t* out_counts) {
+  if (n == 0) return 0;
+  std::vector<int64_t> order(n);
+  std::iota(order.begin(), order.end(), 0);
+  const int threads = std::max(1, std::min<int>(omp_get_max_threads(), static_cast<int>(n / 65536) + 1));
+  if (threads == 1) {
+    std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return in[a] < in[b]; });
+  } else {
+    const int64_t chunk = (n + threads - 1) / threads;
+#pragma omp parallel for num_threads(threads) schedule(static, 1)
+    for (int t = 0; t < threads; ++t) {
+      const int64_t b = t * chunk, e = std::min<int64_t>(n, b + chunk);
+      if (b < e)
+        std::stable_sort(order.begin() + b, order.begin() + e, [&](int64_t x, int64_t y) { return in[x] < in[y]; });
+    }
+    for (int64_t width = chunk; width < n; width *= 2)
+      for (int64_t b = 0; b + width < n; b += 2 * width)
+        std::inplace_merge(order.begin() + b, order.begin() + b + width, order.begin() + std::min<int64_t>(n, b + 2 * width),
+                           [&](int64_t x, int64_t y) { return in[x] < in[y]; });
+  }
+  int64_t u = 0;
+  for (int64_t i = 0; i < n; ++i) {
+    const int64_t v = in[order[i]];
+    if (i == 0 || v != out_unique[u - 1]) {
+      out_unique[u] = v;
+      if (out_counts) out_counts[u] = 0;
+      ++u;
+    }
+    if (out_inverse) out_inverse[order[i]] = u - 1;
+    if (out_counts) ++out_counts[u - 1];
+  }
+  return u;
+}
+
+// Row-wise bucketisation of a KJT.  lengths [F*B], indices [nnz] (key-major).  Bucket of an id:
+//   block_sizes == nullptr : id % world                         (round robin; the reference's default)
+//   block_sizes[f] > 0     : min(id / block_sizes[f], world-1)  (contiguous ranges)
+// Outputs (bucket-major then feature-major, like fbgemm's block_bucketize_sparse_features):
+//   new_lengths [world*F*B], new_indices [nnz] (the id, or the id's local row when `local_rows`),
+//   unbucketize_permute [nnz] (position of input element i in new_indices), optional new_weights.
+inline void block_bucketize(const int64_t* lengths, const int64_t* indices, const float* weights, int64_t F,
+                            int64_t B, int64_t world, const int64_t* block_sizes, bool local_rows,
+                            int64_t* new_lengths, int64_t* new_indices, float* new_weights,
+                            int64_t* unbucketize_permute) {
+  const int64_t FB = F * B;
+  std::vector<int64_t> offsets(FB + 1, 0);
+  for (int64_t i = 0; i < FB; ++i) offsets[i + 1] = offsets[i] + lengths[i];
+  std::fill(new_lengths, new_lengths + world * FB, 0);
+  auto bucket_of = [&](int64_t f, int64_t id) -> int64_t {
+    if (block_sizes && block_sizes[f] > 0) return std::min<int64_t>(id / block_sizes[f], world - 1);
+    int64_t m = id % world;
+    return m < 0 ? m + world : m;
+  };
+#pragma omp parallel for schedule(static)
+  for (int64_t fb = 0; fb < FB; ++fb) {
+    const int64_t f = fb / B;
+    for (int64_t j = offsets[fb]; j < offsets[fb + 1]; ++j) ++new_lengths[bucket_of(f, indices[j]) * FB + fb];
+  }
+  std::vector<int64_t> new_offsets(world * FB + 1, 0);
+  for (int64_t i = 0; i < world * FB; ++i) new_offsets[i + 1] = new_offsets[i] + new_lengths[i];
+#pragma omp parallel for schedule(static)
+  for (int64_t fb = 0; fb < FB; ++fb) {
+    const int64_t f = fb / B;
+    std::vector<int64_t> cursor(world);
+    for (int64_t w = 0; w < world; ++w) cursor[w] = new_offsets[w * FB + fb];
+    for (int64_t j = offsets[fb]; j < offsets[fb + 1]; ++j) {
+      const int64_t id = indices[j];
+      const int64_t w = bucket_of(f, id);
+      const int64_t pos = cursor[w]++;
+      int64_t v = id;
+      if (local_rows) v = (block_sizes && block_sizes[f] > 0) ? id - w * block_sizes[f] : id / world;
+      new_indices[pos] = v;
+      if (new_weights && weights) new_weights[pos] = weights[j];
+      if (unbucketize_permute) unbucketize_permute[j] = pos;
+    }
+  }
+}
+
+}  // namespace rbh

@@ -21,9 +21,11 @@ import torch.distributed as dist
 from torch import nn
 
 from ..modules.embedding_modules import EmbeddingBagCollection
+from ..modules.hash_embeddingbag import HashEmbeddingBagCollection
 from ..ops import embedding_ops as E
 from ..optim import CombinedOptimizer
 from .comm import PeerGroup, ShardingEnv
+from .collective_embeddingbag import CollectiveShardedEmbeddingBagCollection
 from .embeddingbag import ParameterSharding, ShardedEmbeddingBagCollection
 from .planner import ShardingPlan
 
@@ -52,20 +54,27 @@ class DistributedModelParallel(nn.Module):
     def __init__(self, module: nn.Module, env: Optional[ShardingEnv] = None, device: Optional[torch.device] = None,
                  plan: Optional[ShardingPlan] = None, sharders=None, peer: Optional[PeerGroup] = None,
                  sparse_optimizer: Optional[E.OptimizerSpec] = None, out_dtype: torch.dtype = torch.bfloat16,
-                 max_local_batch: int = 0, one_hot: bool = False, init_seed: Optional[int] = None) -> None:
+                 max_local_batch: int = 0, one_hot: bool = False, init_seed: Optional[int] = None,
+                 backend: Optional[str] = None) -> None:
+        """``backend``: ``"fused"`` (peer-memory kernels; CUDA only, the default there) or ``"collective"``
+        (``torch.distributed`` all-to-all flow; any device, the default on CPU; required for hash tables)."""
         super().__init__()
+        dev0 = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
+                          else torch.device("cpu"))
+        self.backend = backend or ("fused" if torch.device(dev0).type == "cuda" else "collective")
         self.env = env or ShardingEnv.from_process_group(None)
-        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.device = torch.device(dev0)
         self.world, self.rank = self.env.world_size, self.env.rank
         self.peer = peer
         if self.world > 1 and self.device.type == "cuda" and peer is None:
             self.peer = PeerGroup(self.env.process_group, self.device)
         self.plan = plan or ShardingPlan({})
-        self.sharded_modules: List[ShardedEmbeddingBagCollection] = []
+        self.sharded_modules: List[nn.Module] = []
         self._shard(module, "", sparse_optimizer, out_dtype, max_local_batch, one_hot, init_seed)
         self.module = module
         for m in module.modules():
-            if isinstance(m, ShardedEmbeddingBagCollection) and m not in self.sharded_modules:
+            if isinstance(m, (ShardedEmbeddingBagCollection, CollectiveShardedEmbeddingBagCollection)) \
+                    and m not in self.sharded_modules:
                 self.sharded_modules.append(m)
         self._grad_buf = None
         self._grad_elems = 0
@@ -79,6 +88,17 @@ class DistributedModelParallel(nn.Module):
             path = prefix + name
             if isinstance(child, EmbeddingBagCollection):
                 entries: Dict[str, ParameterSharding] = self.plan.get_module_plan(path)
+                hashed = isinstance(child, HashEmbeddingBagCollection)
+                if hashed or self.backend == "collective":
+                    sharded = CollectiveShardedEmbeddingBagCollection(
+                        child.embedding_bag_configs(), entries, self.env, self.device,
+                        _optimizer_spec_from_params(child, spec), hashed=hashed,
+                        out_dtype=out_dtype if self.device.type == "cuda" else torch.float32)
+                    if not child.is_meta():
+                        sharded.load_from_unsharded(child)
+                    setattr(parent, name, sharded)
+                    self.sharded_modules.append(sharded)
+                    continue
                 sharded = ShardedEmbeddingBagCollection(
                     child.embedding_bag_configs(), entries, self.env, self.device,
                     _optimizer_spec_from_params(child, spec), peer=self.peer, out_dtype=out_dtype,
@@ -89,7 +109,7 @@ class DistributedModelParallel(nn.Module):
                     sharded.load_from_unsharded(child)
                 setattr(parent, name, sharded)
                 self.sharded_modules.append(sharded)
-            elif isinstance(child, ShardedEmbeddingBagCollection):
+            elif isinstance(child, (ShardedEmbeddingBagCollection, CollectiveShardedEmbeddingBagCollection)):
                 continue
             else:
                 self._shard(child, path + ".", spec, out_dtype, max_local_batch, one_hot, init_seed)
