@@ -1,0 +1,18 @@
+"""Dynamic (hash-table backed) embeddings: the ``dynamic_emb`` API surface on the GPU hash table."""
+from .batched_dynamicemb_table import BatchedDynamicEmbeddingTablesV2
+from .dump_load import DynamicEmbDump, DynamicEmbLoad, get_score, incremental_dump, set_score
+from .dynamicemb_config import (DynamicEmbCheckMode, DynamicEmbInitializerArgs, DynamicEmbInitializerMode,
+                                DynamicEmbPoolingMode, DynamicEmbScoreStrategy, DynamicEmbTableOptions, EmbOptimType,
+                                convert_optimizer_type, get_constraint_capacity)
+from .embedding import DynamicEmbeddingBagCollection, DynamicEmbeddingCollection
+from .hkv import EvictStrategy, HKVTable, HostDynamicTable, InitializerArgs, InitMode, OptimizerType
+from .key_value_table import DiskStorage, KeyValueTable, Storage, TableStorage
+
+__all__ = [
+    "BatchedDynamicEmbeddingTablesV2", "DynamicEmbDump", "DynamicEmbLoad", "get_score", "incremental_dump", "set_score",
+    "DynamicEmbCheckMode", "DynamicEmbInitializerArgs", "DynamicEmbInitializerMode", "DynamicEmbPoolingMode",
+    "DynamicEmbScoreStrategy", "DynamicEmbTableOptions", "EmbOptimType", "convert_optimizer_type",
+    "get_constraint_capacity", "DynamicEmbeddingBagCollection", "DynamicEmbeddingCollection", "EvictStrategy", "HKVTable",
+    "HostDynamicTable", "InitializerArgs", "InitMode", "OptimizerType", "DiskStorage", "KeyValueTable", "Storage",
+    "TableStorage",
+]

@@ -336,6 +336,9 @@ class HostDynamicTable:
         status = []
         evk, evs, evr = [], [], []
         for k, s in zip(ks, sc):
+            if k == EMPTY_KEY:
+                status.append(ST_MISSING)
+                continue
             if k in self.rows:
                 status.append(ST_FOUND)
                 self._touch(k, s, False)
@@ -353,7 +356,8 @@ class HostDynamicTable:
             ev = (torch.tensor(evk, dtype=torch.int64), torch.tensor(evs, dtype=torch.int64),
                   torch.from_numpy(np.stack(evr)) if evr else torch.zeros(0, self.row_dim),
                   torch.tensor([len(evk)], dtype=torch.int32))
-        return keys.clone(), torch.tensor(status, dtype=torch.uint8), ev
+        st = torch.tensor(status, dtype=torch.uint8)
+        return torch.where(st == ST_MISSING, torch.full_like(keys, -1), keys), st, ev
 
     def find(self, keys: torch.Tensor, update_score: bool = False, scores=None):
         found = torch.tensor([k in self.rows for k in keys.tolist()], dtype=torch.bool)

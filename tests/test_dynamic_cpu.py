@@ -1,0 +1,123 @@
+"""Dynamic embedding stack on the CPU (dictionary-backed table): training math vs the A100 golden losses
+recorded with upstream dynamicemb v25.09 (reference: dynamic_emb/tests/precision_consistency/scenario.py and
+golden/reference_v25.09.json), dump / load round trip incl. a world-size change, admission, caching + disk tier."""
+import numpy as np
+import pytest
+import torch
+
+from recsdk_b200.dynamic import (DiskStorage, DynamicEmbDump, DynamicEmbeddingBagCollection, DynamicEmbInitializerArgs,
+                                 DynamicEmbInitializerMode, DynamicEmbLoad, DynamicEmbScoreStrategy, DynamicEmbTableOptions,
+                                 OptimizerType, get_score, incremental_dump, set_score)
+from recsdk_b200.modules.embedding_configs import EmbeddingBagConfig
+from recsdk_b200.parallel.comm import ShardingEnv
+from recsdk_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+GOLDEN = {
+    OptimizerType.SGD: [280655424.0, 44904868.0, 7184778.5, 1149564.5, 183930.21875],
+    OptimizerType.ADAM: [280655424.0, 280547328.0, 280439232.0, 280331136.0, 280223104.0],
+    OptimizerType.ADAGRAD: [280655424.0, 280547328.0, 280470880.0, 280408512.0, 280354464.0],
+    OptimizerType.ROWWISE_ADAGRAD: [280655424.0, 280547328.0, 280470880.0, 280408512.0, 280354464.0],
+}
+
+
+def _lcg_ids(seed, n):
+    x, out = seed, []
+    for _ in range(n):
+        x = (1103515245 * x + 12345) & 0x7FFFFFFF
+        out.append(x % 1024)
+    return out
+
+
+def _scenario_batch():
+    # 2 tables / features, batch 8, 3 ids per bag, ids from an LCG seeded 1234 + feature
+    vals = [_lcg_ids(1234 + i, 8 * 3) for i in range(2)]
+    return KeyedJaggedTensor(["cate_0", "cate_1"], torch.tensor(vals[0] + vals[1], dtype=torch.int64),
+                             lengths=torch.full((16,), 3, dtype=torch.int64), stride=8)
+
+
+def _make(opt, **kw):
+    cfgs = [EmbeddingBagConfig(num_embeddings=1024, embedding_dim=8, name="t_%d" % i, feature_names=["cate_%d" % i])
+            for i in range(2)]
+    options = {c.name: DynamicEmbTableOptions(
+        initializer_args=DynamicEmbInitializerArgs(mode=DynamicEmbInitializerMode.DEBUG),
+        score_strategy=DynamicEmbScoreStrategy.STEP, **kw) for c in cfgs}
+    return DynamicEmbeddingBagCollection(cfgs, options, ShardingEnv(1, 0), torch.device("cpu"), optimizer_type=opt,
+                                         learning_rate=0.1, eps=1e-8)
+
+
+@pytest.mark.parametrize("opt", list(GOLDEN))
+def test_precision_consistency_golden(opt):
+    m = _make(opt)
+    kjt = _scenario_batch()
+    losses = []
+    for _ in range(5):
+        out = m(kjt).values()
+        loss = (out * out).sum()
+        loss.backward()
+        losses.append(loss.item())
+    tol = 4e-5 if opt == OptimizerType.ADAM else 5e-7   # fp32 summation-order noise (1-2 ULP)
+    for got, want in zip(losses, GOLDEN[opt]):
+        assert abs(got - want) <= tol * abs(want) + 1e-3, (losses, GOLDEN[opt])
+
+
+def test_dump_load_roundtrip_and_scores(tmp_path):
+    m = _make(OptimizerType.ADAM)
+    kjt = _scenario_batch()
+    for _ in range(3):
+        (m(kjt).values() ** 2).sum().backward()
+    assert get_score(m)[""]["t_0"] == 3
+    DynamicEmbDump(str(tmp_path / "ck"), m, optim=True)
+    m2 = _make(OptimizerType.ADAM)
+    loaded = DynamicEmbLoad(str(tmp_path / "ck"), m2, optim=True)
+    assert loaded[""]["t_0"] == m.table("t_0").size()
+    a = (m(kjt).values() ** 2).sum()
+    b = (m2(kjt).values() ** 2).sum()
+    assert torch.allclose(a, b, rtol=1e-6)
+    a.backward(); b.backward()                                    # optimizer state travelled too
+    assert torch.allclose((m(kjt).values() ** 2).sum(), (m2(kjt).values() ** 2).sum(), rtol=1e-6)
+    # different world size on load: rank 1 of 2 keeps odd keys only
+    m3 = _make(OptimizerType.ADAM)
+    m3.rank, m3.world = 1, 2
+    m3.load(str(tmp_path / "ck" / "root"))
+    keys, _, _ = m3.lookup.export_keys_values("t_0")
+    assert keys.numel() and (keys % 2 == 1).all()
+    with pytest.raises(FileExistsError):
+        DynamicEmbDump(str(tmp_path / "ck"), m)
+    k = get_score(m)[""]["t_0"]                                  # STEP strategy: score = global step
+    inc, cur = incremental_dump(m, k + 1)
+    assert inc[""]["t_0"][0].numel() == 0 and cur[""]["t_0"] == k
+    (m(kjt).values() ** 2).sum().backward()
+    inc, _ = incremental_dump(m, k + 1)                          # only what the last step touched
+    assert inc[""]["t_0"][0].numel() == m.table("t_0").size()
+    set_score(m, 10)
+    assert get_score(m)[""]["t_1"] == 10
+
+
+def test_admission_threshold():
+    m = _make(OptimizerType.SGD, admit_threshold=2)
+    kjt = _scenario_batch()
+    first = m(kjt).values()
+    assert first.abs().sum().item() == 0 and m.table("t_0").size() == 0        # first sighting: default value
+    second = m(kjt).values()
+    assert second.abs().sum().item() > 0 and m.table("t_0").size() > 0
+
+
+def test_caching_with_disk_storage(tmp_path):
+    cfgs = [EmbeddingBagConfig(num_embeddings=64, embedding_dim=8, name="t", feature_names=["f"])]
+    disk = DiskStorage("t", [str(tmp_path / "d0")], 8)
+    opts = {"t": DynamicEmbTableOptions(initializer_args=DynamicEmbInitializerArgs(mode=DynamicEmbInitializerMode.DEBUG),
+                                        caching=True, external_storage=disk, max_capacity=16, init_capacity=16)}
+    m = DynamicEmbeddingBagCollection(cfgs, opts, ShardingEnv(1, 0), torch.device("cpu"), optimizer_type=OptimizerType.SGD,
+                                      learning_rate=0.5)
+    seen = {}
+    for step in range(6):
+        ids = torch.arange(step * 10, step * 10 + 16, dtype=torch.int64)
+        kjt = KeyedJaggedTensor(["f"], ids, lengths=torch.ones(16, dtype=torch.int64), stride=16)
+        out = m(kjt).values()
+        for i, k in enumerate(ids.tolist()):
+            if k in seen:
+                assert torch.allclose(out[i], seen[k]), "row of key %d changed across cache eviction" % k
+        out.sum().backward()
+        for i, k in enumerate(ids.tolist()):
+            seen[k] = out[i].detach() - 0.5
+    assert disk.size() > 0 and m.table("t").table.size() <= 16
