@@ -1,0 +1,94 @@
+"""HSTU attention forward kernel (tcgen05) vs the fp32 PyTorch statement of the reference golden."""
+import pytest
+import torch
+
+from recsdk_b200.ops import _lib
+from recsdk_b200.ops import hstu_attention as HA
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda", 0)
+
+
+def _jagged(lens, H, D, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    T = sum(lens)
+    mk = lambda: (torch.randn(T, H, D, generator=g, device=DEV) * 0.5).bfloat16()  # noqa: E731
+    off = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device=DEV)
+    return mk(), mk(), mk(), off
+
+
+def _close(a, b, tol=5e-3):
+    err = (a.float() - b.float()).abs().max().item()
+    scale = b.float().abs().max().item() + 1e-6
+    assert err <= tol * scale + tol, "max err %g vs scale %g" % (err, scale)
+
+
+@pytest.mark.parametrize("lens,H,D", [([128], 1, 64), ([200, 37, 513, 1], 2, 64), ([300, 129], 2, 128), ([1000, 64, 700], 4, 64)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_fwd_causal(lens, H, D, bias):
+    q, k, v, off = _jagged(lens, H, D, 1)
+    kw = {}
+    if bias:
+        g = torch.Generator().manual_seed(2)
+        ts = torch.cat([torch.cumsum(torch.randint(1, 5000, (n,), generator=g), 0) for n in lens]).float().to(DEV)
+        kw = dict(ts=ts, ts_w=(torch.randn(65, generator=g) * 0.5).to(DEV), ts_divisor=0.301,
+                  pos_w=(torch.randn(512, generator=g) * 0.5).to(DEV))
+    alpha, scale = 1.0 / D ** 0.5, 1.0 / max(lens)
+    out = HA.hstu_attn_fwd(q, k, v, off, off, max(lens), alpha, scale, True, **kw)
+    ref = HA.hstu_attention_ref(q, k, v, off, off, alpha, scale, True, **kw)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    _close(out, ref)
+
+
+def test_fwd_context_targets_noncausal_and_delta():
+    lens = [400, 260, 129]
+    q, k, v, off = _jagged(lens, 2, 64, 3)
+    alpha, scale = 0.125, 1.0 / 400
+    nc = torch.tensor([10, 0, 3], device=DEV)
+    nt = torch.tensor([100, 130, 5], device=DEV)
+    for gs in (1, 7):
+        out = HA.hstu_attn_fwd(q, k, v, off, off, 400, alpha, scale, True, nc, nt, gs)
+        ref = HA.hstu_attention_ref(q, k, v, off, off, alpha, scale, True, nc, nt, gs)
+        _close(out, ref)
+    out = HA.hstu_attn_fwd(q, k, v, off, off, 400, alpha, scale, False)
+    _close(out, HA.hstu_attention_ref(q, k, v, off, off, alpha, scale, False))
+    # delta: queries are the last rows of every sequence
+    qlens = [50, 260, 1]
+    qoff = torch.tensor([0, 50, 310, 311], device=DEV)
+    qs = torch.cat([q[off[b + 1] - qlens[b]:off[b + 1]] for b in range(3)])
+    out = HA.hstu_attn_fwd(qs, k, v, qoff, off, 260, alpha, scale, True)
+    ref_full = HA.hstu_attention_ref(q, k, v, off, off, alpha, scale, True)
+    ref = torch.cat([ref_full[off[b + 1] - qlens[b]:off[b + 1]] for b in range(3)])
+    _close(out, ref)
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
+def test_fwd_paged_matches_jagged():
+    H, D, page = 2, 64, 64
+    lens = [300, 64, 130]
+    qlens = [172, 64, 2]
+    q, k, v, off = _jagged(lens, H, D, 5)
+    n_pages = sum((n + page - 1) // page for n in lens) + 3
+    cache = torch.zeros(n_pages, 2, page, H, D, dtype=torch.bfloat16, device=DEV)
+    perm = torch.randperm(n_pages).tolist()
+    page_ids, indptr, cur = [], [0], 0
+    for b, n in enumerate(lens):
+        for pg in range((n + page - 1) // page):
+            pid = perm[cur]; cur += 1
+            page_ids.append(pid)
+            lo, hi = pg * page, min(n, (pg + 1) * page)
+            cache[pid, 0, : hi - lo] = k[off[b] + lo: off[b] + hi]
+            cache[pid, 1, : hi - lo] = v[off[b] + lo: off[b] + hi]
+        indptr.append(len(page_ids))
+    qoff = torch.tensor([0, 172, 236, 238], device=DEV)
+    qs = torch.cat([q[off[b + 1] - qlens[b]:off[b + 1]] for b in range(3)])
+    nt = torch.tensor([100, 0, 1], device=DEV)
+    out = HA.hstu_attention_paged(qs, cache, qoff, off, torch.tensor(page_ids, device=DEV), torch.tensor(indptr, device=DEV),
+                                  page, 172, 0.125, 1 / 300, nt, 1)
+    ref_full = HA.hstu_attention_ref(q, k, v, off, off, 0.125, 1 / 300, True, None, nt, 1)
+    ref = torch.cat([ref_full[off[b + 1] - qlens[b]:off[b + 1]] for b in range(3)])
+    torch.cuda.synchronize()
+    _lib.check_status()
+    _close(out, ref)
