@@ -1,0 +1,407 @@
+// HSTU jagged SiLU attention, backward, on tcgen05 / TMEM (sm_100a), head dim 64.
+//
+// One CTA owns one (sequence, head, 128-key block), keeps its K and V tiles in shared memory and the
+// dK / dV accumulators in TMEM, and walks the query blocks that attend to those keys.  Everything is
+// computed in the transposed orientation (rows = keys), so that each activation thread owns one key row:
+//
+//   S^T  = K Q^T            tcgen05.mma (A = K smem, B = Q smem)                 -> TMEM
+//   dP^T = V dO^T           tcgen05.mma (A = V smem, B = dO smem)                -> TMEM
+//   x = alpha (S + bias);  P^T = SiLU(x) scale mask;  dS^T = dP^T scale mask alpha sigma(x)(1 + x(1 - sigma(x)))
+//        written as packed bf16 over the S^T / dP^T columns they came from (tcgen05.st), dS^T also into
+//        shared memory as an MN-major operand
+//   dV  += P^T  dO          tcgen05.mma (A = P^T in TMEM,  B = dO smem, MN-major)
+//   dK  += dS^T Q           tcgen05.mma (A = dS^T in TMEM, B = Q smem,  MN-major)
+//   dQ_partial = dS K       tcgen05.mma (A = dS^T smem MN-major, B = K smem MN-major) -> TMEM -> fp32
+//                           vector atomics into the dQ accumulator
+// The bias gradients (dBias = dS) are reduced per CTA in shared memory - run-length per key row for the
+// monotone time buckets, conflict-free atomics for the Toeplitz position table - and flushed once.
+// Every mbarrier wait is bounded.
+//
+// Math: build/presmoke/hstu/hstu_common.py:387-477 of the reference; kernel structure is this library's.
+#include "common.cuh"
+
+namespace {
+
+constexpr int BQ = 128, BKV = 128, D = 64;
+constexpr int TILE = 128 * 128;            // bytes of one [128][64] bf16 tile
+
+struct HstuBwdParams {
+  const int* q_offsets; const int* k_offsets;
+  int B, H;
+  float alpha, scale;
+  int causal;
+  const int* num_context; const int* num_target; int target_group_size;
+  const float* ts; const float* ts_w; int num_buckets; float ts_divisor;
+  const float* pos_w; int pos_len;
+  float* dq32; long long ld_dq;            // fp32 accumulator [Tq][ld_dq]
+  void* dk; void* dv; long long ld_dkv;    // bf16 [Tk][ld_dkv]
+  float* d_ts_w; float* d_pos_w;
+  int* status;
+};
+
+__device__ __forceinline__ bool attends(int pi, int j, int len, int causal, int nctx, int ntgt, int gs) {
+  if (j >= len) return false;
+  if (!causal) return true;
+  bool ok = j <= pi;
+  if (nctx > 0 && pi < nctx && j < len - ntgt) ok = true;
+  if (ntgt > 0 && gs > 0) {
+    const int t0 = len - ntgt;
+    if (pi >= t0 && j >= t0) ok = (j <= pi) && ((pi - t0) / gs == (j - t0) / gs);
+  }
+  return ok;
+}
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+constexpr int POS_HIST = 4096;
+constexpr int SMEM_BYTES = TILE * 8 /*K,V,2x(Q,dO),dS(2 chunks)*/ + 4 * 2 * 128 * 4 /*ts*/ + 768 /*ts_w*/ + 768 /*d ts_w*/ +
+                           POS_HIST * 4 + 256 /*barriers*/ + 1024;
+
+__global__ void __launch_bounds__(256, 1)
+hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const HstuBwdParams p) {
+  const int b = blockIdx.y / p.H, h = blockIdx.y % p.H;
+  const int kb = blockIdx.x;
+  const int q_start = p.q_offsets[b], len_q = p.q_offsets[b + 1] - q_start;
+  const int k_start = p.k_offsets[b], len_k = p.k_offsets[b + 1] - k_start;
+  if (kb * BKV >= len_k || len_q == 0) return;
+  const int delta = len_k - len_q;
+  const int nctx = p.num_context ? p.num_context[b] : 0;
+  const int ntgt = p.num_target ? p.num_target[b] : 0;
+  const int gs = p.target_group_size;
+  const int qb_total = (len_q + BQ - 1) / BQ;
+  int qb_first = 0;
+  if (p.causal && nctx == 0) {
+    const int first_row = kb * BKV - delta;                       // first query row whose position reaches this block
+    qb_first = first_row <= 0 ? 0 : first_row / BQ;
+  }
+  const int n_iter = qb_total - qb_first;
+  if (n_iter <= 0) {
+    // keys that no query attends to still need zero gradients
+    for (int e = threadIdx.x; e < BKV * D; e += blockDim.x) {
+      const int r = e / D, c = e % D;
+      if (kb * BKV + r < len_k) {
+        const long long o = static_cast<long long>(k_start + kb * BKV + r) * p.ld_dkv + h * D + c;
+        reinterpret_cast<__nv_bfloat16*>(p.dk)[o] = __float2bfloat16(0.f);
+        reinterpret_cast<__nv_bfloat16*>(p.dv)[o] = __float2bfloat16(0.f);
+      }
+    }
+    return;
+  }
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* k_s = smem;
+  uint8_t* v_s = smem + TILE;
+  uint8_t* qdo_s = smem + 2 * TILE;                                // stage s: Q at 2s, dO at 2s+1
+  uint8_t* ds_s = smem + 6 * TILE;                                 // 2 chunks of [128 keys][64 q]
+  float* ts_s = reinterpret_cast<float*>(smem + 8 * TILE);         // [4 warps][2][128]
+  float* tsw_s = ts_s + 1024;                                      // [192]
+  float* dtsw_s = tsw_s + 192;                                     // [192]
+  float* dpos_s = dtsw_s + 192;                                    // [POS_HIST]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(dpos_s + POS_HIST);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;       // [2]
+  uint64_t* qdo_empty = bars + 3;      // [2]
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* act_done = bars + 6;
+  uint64_t* dq_full = bars + 7;
+  uint64_t* dq_empty = bars + 8;
+  uint64_t* dkv_full = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool want_dpos = p.d_pos_w != nullptr && p.pos_w != nullptr;
+  const bool want_dts = p.d_ts_w != nullptr && p.ts_w != nullptr && p.ts != nullptr;
+  if (threadIdx.x == 0) {
+    rb::mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) { rb::mbar_init(&qdo_full[s], 1); rb::mbar_init(&qdo_empty[s], 1); }
+    rb::mbar_init(sdp_full, 1); rb::mbar_init(act_done, 128); rb::mbar_init(dq_full, 1); rb::mbar_init(dq_empty, 128);
+    rb::mbar_init(dkv_full, 1);
+    *abort_flag = 0;
+    rb::mbar_fence_init();
+  }
+  if (warp == 2) { rb::tmem_alloc(tmem_slot, 512); rb::tmem_relinquish(); }
+  for (int i = threadIdx.x; i < 192; i += blockDim.x) {
+    tsw_s[i] = (p.ts_w && i <= p.num_buckets) ? p.ts_w[i] : 0.f;
+    dtsw_s[i] = 0.f;
+  }
+  for (int i = threadIdx.x; i < POS_HIST; i += blockDim.x) dpos_s[i] = 0.f;
+  rb::tc_fence_before();
+  __syncthreads();
+  rb::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  // columns: S^T / P^T [0,128), dP^T / dS^T [128,256), dV [256,320), dK [320,384), dQ [384,448)
+  const uint32_t T_ST = tmem, T_DP = tmem + 128, T_DV = tmem + 256, T_DK = tmem + 320, T_DQ = tmem + 384;
+
+  if (warp == 0 && lane == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    rb::mbar_expect_tx(kv_full, 2 * TILE);
+    for (int half = 0; half < 2; ++half) {
+      rb::tma_load_2d(k_s + half * 8192, &tm_k, kv_full, h * D, k_start + kb * BKV + half * 64);
+      rb::tma_load_2d(v_s + half * 8192, &tm_v, kv_full, h * D, k_start + kb * BKV + half * 64);
+    }
+    for (int t = 0; t < n_iter; ++t) {
+      const int st = t & 1, qb = qb_first + t;
+      if (!rb::mbar_wait(&qdo_empty[st], ((t >> 1) & 1) ^ 1, abort_flag, p.status)) goto done;
+      rb::mbar_expect_tx(&qdo_full[st], 2 * TILE);
+      for (int half = 0; half < 2; ++half) {
+        rb::tma_load_2d(qdo_s + (2 * st) * TILE + half * 8192, &tm_q, &qdo_full[st], h * D, q_start + qb * BQ + half * 64);
+        rb::tma_load_2d(qdo_s + (2 * st + 1) * TILE + half * 8192, &tm_do, &qdo_full[st], h * D, q_start + qb * BQ + half * 64);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t id_kk = rb::umma_idesc(128, 128, 0, 0, 1);      // both operands contraction-major
+    const uint32_t id_tn = rb::umma_idesc(128, D, 0, 1, 1);        // A in TMEM, B MN-major
+    const uint32_t id_nn = rb::umma_idesc(128, D, 1, 1, 1);        // A and B MN-major
+    const uint32_t k_addr = rb::smem_u32(k_s), v_addr = rb::smem_u32(v_s), ds_addr = rb::smem_u32(ds_s);
+    if (!rb::mbar_wait(kv_full, 0, abort_flag, p.status)) goto done;
+    for (int t = 0; t < n_iter; ++t) {
+      const int st = t & 1;
+      const uint32_t q_addr = rb::smem_u32(qdo_s + (2 * st) * TILE), do_addr = q_addr + TILE;
+      if (!rb::mbar_wait(&qdo_full[st], (t >> 1) & 1, abort_flag, p.status)) goto done;
+      rb::tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        rb::umma_f16_ss(T_ST, rb::umma_smem_desc(k_addr + kk * 32, 16, 1024), rb::umma_smem_desc(q_addr + kk * 32, 16, 1024),
+                        id_kk, kk > 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        rb::umma_f16_ss(T_DP, rb::umma_smem_desc(v_addr + kk * 32, 16, 1024), rb::umma_smem_desc(do_addr + kk * 32, 16, 1024),
+                        id_kk, kk > 0 ? 1u : 0u);
+      }
+      rb::umma_commit(sdp_full);
+      if (!rb::mbar_wait(act_done, t & 1, abort_flag, p.status)) goto done;
+      if (t > 0 && !rb::mbar_wait(dq_empty, (t - 1) & 1, abort_flag, p.status)) goto done;   // dQ tile drained
+      rb::tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < BQ / 16; ++kk) {
+        rb::umma_f16_ts(T_DV, T_ST + kk * 8, rb::umma_smem_desc(do_addr + kk * 2048, 16384, 1024), id_tn,
+                        (t > 0 || kk > 0) ? 1u : 0u);
+      }
+#pragma unroll
+      for (int kk = 0; kk < BQ / 16; ++kk) {
+        rb::umma_f16_ts(T_DK, T_DP + kk * 8, rb::umma_smem_desc(q_addr + kk * 2048, 16384, 1024), id_tn,
+                        (t > 0 || kk > 0) ? 1u : 0u);
+      }
+#pragma unroll
+      for (int kk = 0; kk < BKV / 16; ++kk) {
+        rb::umma_f16_ss(T_DQ, rb::umma_smem_desc(ds_addr + kk * 2048, 16384, 1024),
+                        rb::umma_smem_desc(k_addr + kk * 2048, 16384, 1024), id_nn, kk > 0 ? 1u : 0u);
+      }
+      rb::umma_commit(&qdo_empty[st]);
+      rb::umma_commit(dq_full);
+    }
+    rb::umma_commit(dkv_full);
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ activation, dQ drain, dK / dV store
+    const int ew = warp & 3;
+    const int row = ew * 32 + lane;                                 // key row of this thread
+    const int j = kb * BKV + row;
+    const uint32_t lane_sel = static_cast<uint32_t>(ew * 32) << 16;
+    const bool has_t = p.ts != nullptr && p.ts_w != nullptr;
+    const bool has_p = p.pos_w != nullptr;
+    const float ts_j = has_t ? p.ts[k_start + min(j, len_k - 1)] : 0.f;
+    const float inv_div = 1.f / p.ts_divisor;
+    const float sa = p.scale * p.alpha;
+    for (int t = 0; t < n_iter; ++t) {
+      const int qb = qb_first + t;
+      float* my_ts = ts_s + (ew * 2 + (t & 1)) * 128;
+      if (has_t) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int pi = qb * BQ + q4 * 32 + lane + delta;
+          my_ts[q4 * 32 + lane] = (pi < len_k && pi >= 0) ? __ldg(p.ts + k_start + pi) : 0.f;
+        }
+        __syncwarp();
+      }
+      bool ok = rb::mbar_wait(sdp_full, t & 1, abort_flag, p.status);
+      if (!__all_sync(0xffffffffu, ok)) goto done;
+      rb::tc_fence_after();
+      int run_bucket = -1;
+      float run_sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rd[32];
+        rb::tmem_ld_32x32(T_ST + lane_sel + c * 32, rs);
+        rb::tmem_ld_32x32(T_DP + lane_sel + c * 32, rd);
+        rb::tmem_ld_wait();
+        uint32_t pk[16], dk16[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pv[2], dsv[2];
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int il = c * 32 + e + q;                           // query row inside the block
+            const int i_local = qb * BQ + il;
+            const int pi = i_local + delta;
+            float s = __uint_as_float(rs[e + q]);
+            int bk = 0;
+            if (has_t) {
+              const float a = fminf(fmaxf(fabsf(my_ts[il] - ts_j), 1.f), 7.0e16f);
+              bk = min(max(static_cast<int>(__logf(a) * inv_div), 0), p.num_buckets);
+              s += tsw_s[bk];
+            }
+            const int dd = min(max(pi - j, 0), p.pos_len - 1);
+            if (has_p) s += __ldg(p.pos_w + dd);
+            const float x = s * p.alpha;
+            float th;
+            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * x));
+            const float sig = 0.5f * th + 0.5f;
+            const bool on = i_local < len_q && attends(pi, j, len_k, p.causal, nctx, ntgt, gs);
+            const float pval = on ? x * sig * p.scale : 0.f;
+            const float ds = on ? __uint_as_float(rd[e + q]) * sa * sig * (1.f + x * (1.f - sig)) : 0.f;
+            // dBias = dS, accumulated with the precision the matmuls see (bf16)
+            const float ds_r = __bfloat162float(__float2bfloat16(ds));
+            if (want_dts) {
+              if (bk != run_bucket) {
+                if (run_bucket >= 0 && run_sum != 0.f) atomicAdd(dtsw_s + run_bucket, run_sum);
+                run_bucket = bk; run_sum = 0.f;
+              }
+              run_sum += ds_r;
+            }
+            if (want_dpos && on) atomicAdd(dpos_s + min(dd, POS_HIST - 1), ds_r);
+            pv[q] = pval; dsv[q] = ds;
+          }
+          pk[e >> 1] = rb::pack_bf16(pv[0], pv[1]);
+          dk16[e >> 1] = rb::pack_bf16(dsv[0], dsv[1]);
+        }
+        rb::tmem_st_32x16(T_ST + lane_sel + c * 16, pk);             // P^T over the S^T columns already consumed
+        rb::tmem_st_32x16(T_DP + lane_sel + c * 16, dk16);           // dS^T over dP^T
+        // dS^T row -> shared memory, MN-major operand layout (two 64-query chunks, 128-byte swizzle)
+        uint8_t* dst = ds_s + (c >> 1) * TILE + row * 128;
+#pragma unroll
+        for (int v4 = 0; v4 < 4; ++v4) {
+          const int u = ((c & 1) * 4 + v4) ^ (row & 7);
+          *reinterpret_cast<uint4*>(dst + u * 16) = make_uint4(dk16[4 * v4], dk16[4 * v4 + 1], dk16[4 * v4 + 2], dk16[4 * v4 + 3]);
+        }
+      }
+      if (want_dts && run_bucket >= 0 && run_sum != 0.f) atomicAdd(dtsw_s + run_bucket, run_sum);
+      rb::tmem_st_wait();
+      fence_async_smem();
+      rb::tc_fence_before();
+      rb::mbar_arrive(act_done);
+      // ---- drain the dQ tile of this pair: rows = queries
+      ok = rb::mbar_wait(dq_full, t & 1, abort_flag, p.status);
+      if (!__all_sync(0xffffffffu, ok)) goto done;
+      rb::tc_fence_after();
+      const int iq = qb * BQ + row;
+      float* dq_row = p.dq32 + static_cast<long long>(q_start + iq) * p.ld_dq + h * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        rb::tmem_ld_32x32(T_DQ + lane_sel + c * 32, r);
+        rb::tmem_ld_wait();
+        if (iq < len_q) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            red_add_v4(dq_row + c * 32 + e, __uint_as_float(r[e]), __uint_as_float(r[e + 1]), __uint_as_float(r[e + 2]),
+                       __uint_as_float(r[e + 3]));
+        }
+      }
+      rb::tc_fence_before();
+      rb::mbar_arrive(dq_empty);
+    }
+    {
+      bool ok = rb::mbar_wait(dkv_full, 0, abort_flag, p.status);
+      if (!__all_sync(0xffffffffu, ok)) goto done;
+      rb::tc_fence_after();
+      __nv_bfloat16* dk_row = reinterpret_cast<__nv_bfloat16*>(p.dk) + static_cast<long long>(k_start + j) * p.ld_dkv + h * D;
+      __nv_bfloat16* dv_row = reinterpret_cast<__nv_bfloat16*>(p.dv) + static_cast<long long>(k_start + j) * p.ld_dkv + h * D;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          rb::tmem_ld_32x32((which ? T_DK : T_DV) + lane_sel + c * 32, r);
+          rb::tmem_ld_wait();
+          if (j < len_k) {
+            __nv_bfloat16* o = (which ? dk_row : dv_row) + c * 32;
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              uint4 w;
+              w.x = rb::pack_bf16(__uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+              w.y = rb::pack_bf16(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3]));
+              w.z = rb::pack_bf16(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5]));
+              w.w = rb::pack_bf16(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7]));
+              *reinterpret_cast<uint4*>(o + e) = w;
+            }
+          }
+        }
+      }
+    }
+  }
+done:
+  __syncwarp();
+  rb::tc_fence_before();
+  __syncthreads();
+  if (warp == 2) rb::tmem_dealloc(tmem, 512);
+  // flush the bias-gradient histograms of this CTA
+  if (want_dts) for (int i = threadIdx.x; i <= p.num_buckets && i < 192; i += blockDim.x) if (dtsw_s[i] != 0.f) atomicAdd(p.d_ts_w + i, dtsw_s[i]);
+  if (want_dpos) for (int i = threadIdx.x; i < p.pos_len && i < POS_HIST; i += blockDim.x) if (dpos_s[i] != 0.f) atomicAdd(p.d_pos_w + i, dpos_s[i]);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess) return nullptr;
+  return fn = reinterpret_cast<EncodeTiledFn>(sym);
+}
+int make_map(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -1;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstr[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {64, 64};
+  cuuint32_t es[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstr, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -2;
+}
+
+}  // namespace
+
+// q, dO [Tq][ld_q / ld_do], k, v [Tk][ld_k] bf16 with head h at columns h*64.  dq32 is an fp32 accumulator the
+// caller zeroed; dk, dv are bf16 [Tk][ld_dkv]; d_ts_w / d_pos_w fp32 accumulators (nullable).
+RB_API int rb_hstu_attn_bwd(const void* q, long long ld_q, const void* dout, long long ld_do, long long Tq, const void* k,
+                            const void* v, long long ld_k, long long Tk, const int* q_offsets, const int* k_offsets,
+                            int B, int H, int D_, int max_len_k, float alpha, float scale, int causal,
+                            const int* num_context, const int* num_target, int target_group_size, const float* ts,
+                            const float* ts_w, int num_buckets, float ts_divisor, const float* pos_w, int pos_len,
+                            float* dq32, long long ld_dq, void* dk, void* dv, long long ld_dkv, float* d_ts_w,
+                            float* d_pos_w, int* status, cudaStream_t st) {
+  if (B == 0 || H == 0 || max_len_k <= 0) return 0;
+  if (D_ != D || (ld_q % 8) || (ld_k % 8) || (ld_do % 8) || (ld_dkv % 8) || (ld_dq % 4)) return -3;
+  if (num_buckets >= 192 || pos_len > POS_HIST) return -4;
+  HstuBwdParams p;
+  p.q_offsets = q_offsets; p.k_offsets = k_offsets; p.B = B; p.H = H; p.alpha = alpha; p.scale = scale; p.causal = causal;
+  p.num_context = num_context; p.num_target = num_target; p.target_group_size = target_group_size; p.ts = ts; p.ts_w = ts_w;
+  p.num_buckets = num_buckets; p.ts_divisor = ts_divisor > 0.f ? ts_divisor : 1.f; p.pos_w = pos_w; p.pos_len = pos_len > 0 ? pos_len : 1;
+  p.dq32 = dq32; p.ld_dq = ld_dq; p.dk = dk; p.dv = dv; p.ld_dkv = ld_dkv; p.d_ts_w = d_ts_w; p.d_pos_w = d_pos_w; p.status = status;
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_map(&tq, q, Tq, static_cast<long long>(H) * D, ld_q))) return rc;
+  if ((rc = make_map(&tdo, dout, Tq, static_cast<long long>(H) * D, ld_do))) return rc;
+  if ((rc = make_map(&tk, k, Tk, static_cast<long long>(H) * D, ld_k))) return rc;
+  if ((rc = make_map(&tv, v, Tk, static_cast<long long>(H) * D, ld_k))) return rc;
+  static bool set = false;
+  if (!set) {
+    RB_CUDA_CHECK(cudaFuncSetAttribute(hstu_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    set = true;
+  }
+  dim3 grid((max_len_k + BKV - 1) / BKV, B * H);
+  hstu_bwd_kernel<<<grid, 256, SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -5,8 +5,9 @@ with ``x = alpha (Q K^T + bias)``, ``P = SiLU(x) scale mask``: ``dV = P^T dO``, 
 ``dS = dP scale mask alpha sigma(x) (1 + x (1 - sigma(x)))``, ``dQ = dS K``, ``dK = dS^T Q``, ``dBias = dS``
 (scatter-added into the time-bucket and position tables).
 
-This module evaluates those formulas per sequence with batched PyTorch matmuls in fp32 (chunked over query
-rows so the [H, chunk, len] score block stays small).
+``hstu_attn_bwd`` runs the tcgen05 kernel (``csrc/cuda/hstu_attention_bwd.cu``: head dim 64, bf16, CUDA);
+``hstu_attn_bwd_ref`` evaluates the same formulas per sequence with batched PyTorch matmuls in fp32 (chunked
+over query rows so the [H, chunk, len] score block stays small) and serves every other case and the tests.
 """
 from __future__ import annotations
 
@@ -14,11 +15,48 @@ from typing import Optional
 
 import torch
 
+from . import _lib
 from .hstu_attention import hstu_mask, time_buckets
 
 
 def hstu_attn_bwd(dout, q, k, v, q_offsets, k_offsets, alpha: float, scale: float, causal: bool, num_context,
-                  num_target, gs: int, ts, ts_w, ts_divisor: float, pos_w, chunk: int = 1024):
+                  num_target, gs: int, ts, ts_w, ts_divisor: float, pos_w, max_len_k: Optional[int] = None):
+    """-> (dq, dk, dv, d_ts_w, d_pos_w)."""
+    ok = (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[2] == 64 and v.shape[2] == 64 and k.shape[1] == q.shape[1]
+          and (pos_w is None or pos_w.numel() <= 4096) and (ts_w is None or ts_w.numel() <= 192))
+    if not ok:
+        return hstu_attn_bwd_ref(dout, q, k, v, q_offsets, k_offsets, alpha, scale, causal, num_context, num_target, gs,
+                                 ts, ts_w, ts_divisor, pos_w)
+    dev = q.device
+    Tq, H, D = q.shape
+    Tk = k.shape[0]
+    i32 = lambda t: None if t is None else t.to(device=dev, dtype=torch.int32).contiguous()  # noqa: E731
+    f32 = lambda t: None if t is None else t.to(device=dev, dtype=torch.float32).contiguous()  # noqa: E731
+    qo, ko = i32(q_offsets), i32(k_offsets)
+    if max_len_k is None:
+        max_len_k = int((ko[1:] - ko[:-1]).max().item())
+    dout = dout if (dout.stride(2) == 1 and dout.stride(1) == D) else dout.contiguous()
+    assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D and k.stride(0) == v.stride(0)
+    dq32 = torch.zeros(Tq, H * D, dtype=torch.float32, device=dev)
+    dk = torch.empty(Tk, H, D, dtype=q.dtype, device=dev)
+    dv = torch.empty(Tk, H, D, dtype=q.dtype, device=dev)
+    ts_, tsw_, pw_ = f32(ts), f32(ts_w), f32(pos_w)
+    dtw = torch.zeros_like(tsw_) if (tsw_ is not None and ts_ is not None) else None
+    dpw = torch.zeros_like(pw_) if pw_ is not None else None
+    nc, nt = i32(num_context), i32(num_target)
+    rc = _lib.lib().rb_hstu_attn_bwd(
+        q.data_ptr(), q.stride(0), dout.data_ptr(), dout.stride(0), Tq, k.data_ptr(), v.data_ptr(), k.stride(0), Tk,
+        qo.data_ptr(), ko.data_ptr(), qo.numel() - 1, H, D, max_len_k, float(alpha), float(scale), int(causal),
+        _lib.ptr(nc), _lib.ptr(nt), int(gs), _lib.ptr(ts_), _lib.ptr(tsw_), (tsw_.numel() - 1) if tsw_ is not None else 0,
+        float(ts_divisor), _lib.ptr(pw_), pw_.numel() if pw_ is not None else 0, dq32.data_ptr(), dq32.stride(0),
+        dk.data_ptr(), dv.data_ptr(), dk.stride(0), _lib.ptr(dtw), _lib.ptr(dpw), _lib.status_tensor(dev).data_ptr(),
+        _lib.stream_ptr(dev))
+    _lib.check(rc, "rb_hstu_attn_bwd")
+    return dq32.view(Tq, H, D).to(q.dtype), dk, dv, dtw, dpw
+
+
+def hstu_attn_bwd_ref(dout, q, k, v, q_offsets, k_offsets, alpha: float, scale: float, causal: bool, num_context,
+                      num_target, gs: int, ts, ts_w, ts_divisor: float, pos_w, chunk: int = 1024):
     H, D = q.shape[1], q.shape[2]
     dq = torch.zeros_like(q, dtype=torch.float32)
     dk = torch.zeros_like(k, dtype=torch.float32)
