@@ -56,10 +56,10 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 constexpr int POS_HIST = 4096;
-constexpr int SMEM_BYTES = TILE * 8 /*K,V,2x(Q,dO),dS(2 chunks)*/ + 4 * 2 * 128 * 4 /*ts*/ + 768 /*ts_w*/ + 768 /*d ts_w*/ +
+constexpr int SMEM_BYTES = TILE * 8 /*K,V,2x(Q,dO),dS(2 chunks)*/ + 16 * 2 * 32 * 4 /*ts*/ + 768 /*ts_w*/ + 768 /*d ts_w*/ +
                            POS_HIST * 4 + 256 /*barriers*/ + 1024;
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(640, 1)
 hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                 const HstuBwdParams p) {
@@ -113,6 +113,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* dkv_full = bars + 9;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* quarter_bar = bars + 11;   // [4] the four warps of one TMEM lane quarter meet here once per tile
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool want_dpos = p.d_pos_w != nullptr && p.pos_w != nullptr;
@@ -120,8 +121,9 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     rb::mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { rb::mbar_init(&qdo_full[s], 1); rb::mbar_init(&qdo_empty[s], 1); }
-    rb::mbar_init(sdp_full, 1); rb::mbar_init(act_done, 128); rb::mbar_init(dq_full, 1); rb::mbar_init(dq_empty, 128);
+    rb::mbar_init(sdp_full, 1); rb::mbar_init(act_done, 512); rb::mbar_init(dq_full, 1); rb::mbar_init(dq_empty, 512);
     rb::mbar_init(dkv_full, 1);
+    for (int i = 0; i < 4; ++i) rb::mbar_init(&quarter_bar[i], 128);
     *abort_flag = 0;
     rb::mbar_fence_init();
   }
@@ -201,7 +203,9 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     rb::umma_commit(dkv_full);
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ activation, dQ drain, dK / dV store
+    // warp = 4 + 4*grp + ew: ew = TMEM lane quarter (32 key rows), grp = 32-query column chunk
     const int ew = warp & 3;
+    const int grp = (warp - 4) >> 2;
     const int row = ew * 32 + lane;                                 // key row of this thread
     const int j = kb * BKV + row;
     const uint32_t lane_sel = static_cast<uint32_t>(ew * 32) << 16;
@@ -212,13 +216,10 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const float sa = p.scale * p.alpha;
     for (int t = 0; t < n_iter; ++t) {
       const int qb = qb_first + t;
-      float* my_ts = ts_s + (ew * 2 + (t & 1)) * 128;
+      float* my_ts = ts_s + ((warp - 4) * 2 + (t & 1)) * 32;
       if (has_t) {
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int pi = qb * BQ + q4 * 32 + lane + delta;
-          my_ts[q4 * 32 + lane] = (pi < len_k && pi >= 0) ? __ldg(p.ts + k_start + pi) : 0.f;
-        }
+        const int pi = qb * BQ + grp * 32 + lane + delta;
+        my_ts[lane] = (pi < len_k && pi >= 0) ? __ldg(p.ts + k_start + pi) : 0.f;
         __syncwarp();
       }
       bool ok = rb::mbar_wait(sdp_full, t & 1, abort_flag, p.status);
@@ -226,8 +227,8 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       rb::tc_fence_after();
       int run_bucket = -1;
       float run_sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      {
+        const int c = grp;
         uint32_t rs[32], rd[32];
         rb::tmem_ld_32x32(T_ST + lane_sel + c * 32, rs);
         rb::tmem_ld_32x32(T_DP + lane_sel + c * 32, rd);
@@ -244,7 +245,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             float s = __uint_as_float(rs[e + q]);
             int bk = 0;
             if (has_t) {
-              const float a = fminf(fmaxf(fabsf(my_ts[il] - ts_j), 1.f), 7.0e16f);
+              const float a = fminf(fmaxf(fabsf(my_ts[e + q] - ts_j), 1.f), 7.0e16f);
               bk = min(max(static_cast<int>(__logf(a) * inv_div), 0), p.num_buckets);
               s += tsw_s[bk];
             }
@@ -272,6 +273,13 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           pk[e >> 1] = rb::pack_bf16(pv[0], pv[1]);
           dk16[e >> 1] = rb::pack_bf16(dsv[0], dsv[1]);
         }
+        // P^T / dS^T overwrite S^T / dP^T columns that OTHER warps of this lane quarter read: wait until all
+        // four column groups of the quarter have their chunks in registers (bounded, like every wait here)
+        rb::tc_fence_before();
+        rb::mbar_arrive(&quarter_bar[ew]);
+        ok = rb::mbar_wait(&quarter_bar[ew], t & 1, abort_flag, p.status);
+        if (!__all_sync(0xffffffffu, ok)) goto done;
+        rb::tc_fence_after();
         rb::tmem_st_32x16(T_ST + lane_sel + c * 16, pk);             // P^T over the S^T columns already consumed
         rb::tmem_st_32x16(T_DP + lane_sel + c * 16, dk16);           // dS^T over dP^T
         // dS^T row -> shared memory, MN-major operand layout (two 64-query chunks, 128-byte swizzle)
@@ -293,8 +301,8 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       rb::tc_fence_after();
       const int iq = qb * BQ + row;
       float* dq_row = p.dq32 + static_cast<long long>(q_start + iq) * p.ld_dq + h * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      if (grp < D / 32) {
+        const int c = grp;
         uint32_t r[32];
         rb::tmem_ld_32x32(T_DQ + lane_sel + c * 32, r);
         rb::tmem_ld_wait();
@@ -314,10 +322,10 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       rb::tc_fence_after();
       __nv_bfloat16* dk_row = reinterpret_cast<__nv_bfloat16*>(p.dk) + static_cast<long long>(k_start + j) * p.ld_dkv + h * D;
       __nv_bfloat16* dv_row = reinterpret_cast<__nv_bfloat16*>(p.dv) + static_cast<long long>(k_start + j) * p.ld_dkv + h * D;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+      {
+        const int which = grp >> 1;                                   // groups 0,1 store dV, groups 2,3 store dK
+        {
+          const int c = grp & 1;
           uint32_t r[32];
           rb::tmem_ld_32x32((which ? T_DK : T_DV) + lane_sel + c * 32, r);
           rb::tmem_ld_wait();
@@ -402,6 +410,6 @@ RB_API int rb_hstu_attn_bwd(const void* q, long long ld_q, const void* dout, lon
     set = true;
   }
   dim3 grid((max_len_k + BKV - 1) / BKV, B * H);
-  hstu_bwd_kernel<<<grid, 256, SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+  hstu_bwd_kernel<<<grid, 640, SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
   return static_cast<int>(cudaGetLastError());
 }

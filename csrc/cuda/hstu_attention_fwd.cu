@@ -6,7 +6,7 @@
 //   * TMA (64-row boxes, 128-byte swizzle) brings Q once and K/V blocks through a ring; K/V may come from
 //     a jagged [T, H*D] tensor or from a paged KV cache [pages][2][page][H*D] through a page table,
 //   * S = Q K^T is a 128x128xD tcgen05.mma into one of two TMEM S buffers,
-//   * four activation warps read S with tcgen05.ld, add the relative position / time bias computed on the
+//   * sixteen activation warps (four per TMEM lane quarter, one 32-column chunk each) read S with tcgen05.ld, add the relative position / time bias computed on the
 //     fly from the bucket tables (never materialising a [B,H,S,S] bias), apply alpha, SiLU, scale and the
 //     causal / contextual / target-group mask, and write P as packed bf16 back into TMEM (tcgen05.st),
 //   * O += P V is a tcgen05.mma whose A operand is P in TMEM and whose B operand is the V tile in shared
@@ -72,7 +72,7 @@ __device__ __forceinline__ bool attends(int pi, int j, int len, int causal, int 
 }
 
 template <int D>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(640, 1)
 hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const HstuFwdParams p) {
   using C = FwdCfg<D>;
@@ -127,7 +127,7 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     rb::mbar_init(q_full, 1);
     for (int s = 0; s < C::STAGES; ++s) { rb::mbar_init(&kv_full[s], 1); rb::mbar_init(&kv_empty[s], 1); }
-    for (int i = 0; i < 2; ++i) { rb::mbar_init(&s_full[i], 1); rb::mbar_init(&p_full[i], 128); rb::mbar_init(&p_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { rb::mbar_init(&s_full[i], 1); rb::mbar_init(&p_full[i], 512); rb::mbar_init(&p_empty[i], 1); }
     rb::mbar_init(o_full, 1);
     *abort_flag = 0;
     rb::mbar_fence_init();
@@ -214,7 +214,10 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     rb::umma_commit(o_full);
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ activation + output
+    // warp = 4 + 4*grp + ew: ew selects the TMEM lane quarter (32 query rows), grp the 32-key column chunk.
+    // One CTA per SM (TMEM), so the elementwise work needs this many warps to keep the issue slots busy.
     const int ew = warp & 3;
+    const int grp = (warp - 4) >> 2;
     const int row = ew * 32 + lane;
     const int i_local = qblk * BQ + row;
     const int pi = i_local + delta;
@@ -225,13 +228,10 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const float inv_div = 1.f / p.ts_divisor;
     for (int t = 0; t < n_iter; ++t) {
       const int kb = kb_of(t), buf = t & 1;
-      float* my_ts = ts_s + (ew * 2 + buf) * 128;                   // private to this warp: no CTA-level sync
+      float* my_ts = ts_s + ((warp - 4) * 2 + buf) * 32;            // private to this warp: no CTA-level sync
       if (has_bias_t) {
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int j = kb * BKV + q4 * 32 + lane;
-          my_ts[q4 * 32 + lane] = j < len_k ? __ldg(p.ts + k_start + j) : 0.f;
-        }
+        const int j = kb * BKV + grp * 32 + lane;
+        my_ts[lane] = j < len_k ? __ldg(p.ts + k_start + j) : 0.f;
         __syncwarp();
       }
       bool ok = rb::mbar_wait(&s_full[buf], (t >> 1) & 1, abort_flag, p.status);
@@ -240,8 +240,8 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       rb::tc_fence_after();
       // fast path: a block strictly below the diagonal of an ordinary causal row block needs no mask
       const bool full = p.causal && ntgt == 0 && (kb * BKV + BKV - 1 <= pi_lo) && (kb * BKV + BKV <= len_k);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      {
+        const int c = grp;
         uint32_t r[32];
         rb::tmem_ld_32x32(T_S + buf * 128 + lane_sel + c * 32, r);
         rb::tmem_ld_wait();
@@ -255,7 +255,7 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const int j = kb * BKV + jl;
             float x = __uint_as_float(r[e + q]);
             if (has_bias_t) {
-              const float a = fminf(fmaxf(fabsf(ts_i - my_ts[jl]), 1.f), 7.0e16f);
+              const float a = fminf(fmaxf(fabsf(ts_i - my_ts[e + q]), 1.f), 7.0e16f);
               const int bk = min(max(static_cast<int>(__logf(a) * inv_div), 0), p.num_buckets);
               x += tsw_s[bk];
             }
@@ -277,8 +277,8 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (!__all_sync(0xffffffffu, ok)) goto done;
       rb::tc_fence_after();
       __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(q_start + i_local) * p.ld_o + h * D;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      if (grp < D / 32) {
+        const int c = grp;
         uint32_t r[32];
         rb::tmem_ld_32x32(T_O + lane_sel + c * 32, r);
         rb::tmem_ld_wait();
@@ -337,7 +337,7 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
     set = true;
   }
   dim3 grid(max_qblocks, p.B * p.H);
-  hstu_fwd_kernel<D><<<grid, 256, C::SMEM_BYTES, st>>>(tq, tk, tv, p);
+  hstu_fwd_kernel<D><<<grid, 640, C::SMEM_BYTES, st>>>(tq, tk, tv, p);
   return static_cast<int>(cudaGetLastError());
 }
 
