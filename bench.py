@@ -39,7 +39,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
-    ap.add_argument("--model", default="dlrm", choices=["dlrm", "hstu"])
+    ap.add_argument("--model", default="dlrm", choices=["dlrm", "hstu", "hstu-infer"])
     ap.add_argument("--global-batch", type=int, default=65536)
     ap.add_argument("--small", action="store_true", help="tiny tables / batch for a quick functional check")
     ap.add_argument("--no-graph", action="store_true")
@@ -120,6 +120,11 @@ def main() -> None:
         from recsdk_b200.models.hstu_bench import run_hstu_bench
 
         run_hstu_bench(args)
+        return
+    if args.model == "hstu-infer":
+        from recsdk_b200.models.hstu_bench import run_hstu_inference_bench
+
+        run_hstu_inference_bench(args)
         return
 
     import torch

@@ -825,3 +825,32 @@ RB_API int rb_scatter_rows(const void* src, const long long* idx, long long n, l
   }
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------
+// dst[dst_idx[i]] = src[src_idx[i]] for rows of row_bytes (a multiple of 16).  Either side may be pinned
+// host memory (mapped into the device address space), so one launch moves a whole layer of KV pages between the
+// host chunk pool and the paged device cache without a staging buffer.
+__global__ void copy_rows_kernel(const uint4* __restrict__ src, const long long* __restrict__ src_idx,
+                                 uint4* __restrict__ dst, const long long* __restrict__ dst_idx, long long n, int v) {
+  const long long total = n * v;
+  for (long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; t < total;
+       t += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = t / v;
+    const int c = static_cast<int>(t - r * v);
+    dst[dst_idx[r] * v + c] = src[src_idx[r] * v + c];
+  }
+}
+
+RB_API int rb_copy_rows(const void* src, const long long* src_idx, void* dst, const long long* dst_idx, long long n,
+                        long long row_bytes, int num_sms, cudaStream_t st) {
+  if (n == 0) return 0;
+  if (row_bytes % 16) return -1;
+  if (num_sms <= 0) num_sms = 148;
+  const int v = static_cast<int>(row_bytes / 16);
+  const long long total = n * v;
+  const long long want = (total + 255) / 256;
+  const int blocks = static_cast<int>(want < num_sms * 8LL ? want : num_sms * 8LL);
+  copy_rows_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(src), src_idx, reinterpret_cast<uint4*>(dst),
+                                           dst_idx, n, v);
+  return static_cast<int>(cudaGetLastError());
+}

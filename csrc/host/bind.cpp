@@ -341,6 +341,7 @@ PYBIND11_MODULE(_C_host, m) {
       })
       .def("pages_of", [](const KVPageAllocator& a, int64_t uid) { return to_array(a.pages_of(uid)); })
       .def("evict", &KVPageAllocator::evict)
+      .def("truncate", &KVPageAllocator::truncate)
       .def("evict_offloaded", &KVPageAllocator::evict_offloaded)
       .def("evict_all", &KVPageAllocator::evict_all);
 

@@ -72,6 +72,24 @@ class KVPageAllocator {
     offloaded_pages_ -= n;
   }
 
+  // forget the tokens at and beyond new_total (e.g. scratch tokens that were appended for one request only)
+  void truncate(int64_t uid, int new_total) {
+    auto it = users_.find(uid);
+    if (it == users_.end()) return;
+    User& u = it->second;
+    if (new_total <= u.start) { if (u.offload_lock == 0) evict(uid); return; }
+    if (new_total >= u.start + u.length) return;
+    const int keep = ceil_div(new_total - u.start, page_);
+    for (size_t p = static_cast<size_t>(keep); p < u.pages.size(); ++p) free_.push_back(u.pages[p]);
+    u.pages.resize(static_cast<size_t>(keep));
+    u.length = new_total - u.start;
+    if (u.offloaded > new_total) {
+      offloaded_pages_ -= offloaded_pages_of(u);
+      u.offloaded = new_total;
+      offloaded_pages_ += offloaded_pages_of(u);
+    }
+  }
+
   void evict_all() {
     users_.clear();
     lru_.clear();

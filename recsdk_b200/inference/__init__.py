@@ -1,0 +1,9 @@
+"""Inference-side components: the paged KV-cache manager (device pages + pinned host chunk tier)."""
+from .kvcache_manager import (GPUKVCacheManager, HostKVStorageErrorCode, HostKVStorageManagerBase, HostKVTaskHandle,
+                              HostKVTaskStatus, HostKVWaitResult, KVCacheConfig, KVCacheManager, KVCacheMetadata,
+                              KVCacheOffloadMode, KVIndexMeta, KVLookupResult, NativeHostKVCacheManager, NPUKVCacheManager,
+                              get_kvcache_config)
+
+__all__ = ["GPUKVCacheManager", "HostKVStorageErrorCode", "HostKVStorageManagerBase", "HostKVTaskHandle", "HostKVTaskStatus",
+           "HostKVWaitResult", "KVCacheConfig", "KVCacheManager", "KVCacheMetadata", "KVCacheOffloadMode", "KVIndexMeta",
+           "KVLookupResult", "NativeHostKVCacheManager", "NPUKVCacheManager", "get_kvcache_config"]

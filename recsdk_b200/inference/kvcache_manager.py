@@ -1,0 +1,670 @@
+"""Paged KV-cache manager for HSTU-style generative-recommender inference.
+
+Per request batch: ``lookup_kvcache`` (what is cached where) -> ``allocate_kvcache`` (pages for the whole
+history, packed metadata on the device) -> ``onboard_launch`` (host-resident prefixes travel host -> device on a
+side stream, layer by layer) -> per layer: ``handle.stream_wait_layer(l)``, ``append_kvcache`` of the new tokens,
+paged attention -> ``offload_launch`` (full chunks that only live on the device are copied to pinned host
+memory) -> ``offload_try_wait``.  Failures of the host tier degrade to recomputation (``fail_open``) or raise
+(``fail_close``); page locks are released on every path.
+
+API surface and behaviour follow the reference (``inference/kvcache_manager/recsys_kvcache_manager/*.py``,
+``src/npu_kvcache_manager_impl.cpp``, ``src/native_host_kvcache_manager_impl.cpp``, ``docs/codeview.md``).
+The page allocator and the host chunk index are native (``csrc/host/kvcache.h``); the device kernels are in
+``csrc/cuda/hstu_misc.cu`` (append, positions) and ``csrc/cuda/embedding.cu`` (``rb_copy_rows``).  Unlike the
+reference's staging-buffer pipeline (H2D copy, then a scatter kernel), the host pool is stored page-major in
+pinned memory and ONE kernel per layer moves pages directly between it and the paged cache through the unified
+address space, so a transfer costs one launch per layer whatever the batch.
+"""
+from __future__ import annotations
+
+import abc
+import dataclasses
+import enum
+import time
+from typing import Any, Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from ..host import host
+from ..ops import _lib
+from ..ops import embedding_ops as E
+
+
+class KVCacheOffloadMode(str, enum.Enum):
+    LAZY = "lazy"
+    EAGER = "eager"
+
+
+class HostKVStorageBackend(str, enum.Enum):
+    NATIVE_HOST = "native_host"
+
+
+class HostKVStorageFailPolicy(str, enum.Enum):
+    FAIL_OPEN = "fail_open"
+    FAIL_CLOSE = "fail_close"
+
+
+@dataclasses.dataclass
+class KVCacheConfig:
+    num_layers: int
+    num_heads: int
+    head_dim: int
+    page_size: int
+    offload_chunksize: int
+    num_primary_cache_pages: int
+    num_buffer_pages: int
+    host_capacity_per_layer: int          # bytes of pinned host memory per layer
+    max_batch_size: int
+    max_seq_len: int
+    dtype: torch.dtype
+    device: Any
+    host_kvstorage_backend: str = HostKVStorageBackend.NATIVE_HOST.value
+    onload_timeout_ms: float = 0.0
+    offload_timeout_ms: float = 1000.0
+    offload_mode: str = KVCacheOffloadMode.LAZY.value
+    host_kvstorage_fail_policy: str = HostKVStorageFailPolicy.FAIL_OPEN.value
+    extra_configs: Dict[str, Any] = dataclasses.field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        if self.offload_chunksize % self.page_size:
+            raise ValueError("offload_chunksize must be a multiple of page_size")
+        if self.head_dim not in (64, 128, 256, 512):
+            raise ValueError("head_dim must be one of 64, 128, 256, 512")
+        if self.host_kvstorage_backend != HostKVStorageBackend.NATIVE_HOST.value:
+            raise ValueError("unknown host_kvstorage_backend %r" % (self.host_kvstorage_backend,))
+
+    def torch_device(self) -> torch.device:
+        if isinstance(self.device, torch.device):
+            return self.device
+        if isinstance(self.device, int):
+            return torch.device("cuda", self.device) if torch.cuda.is_available() else torch.device("cpu")
+        return torch.device(self.device)
+
+
+def get_kvcache_config(num_layers, num_heads, head_dim, page_size, offload_chunksize, num_primary_cache_pages,
+                       num_buffer_pages, host_capacity_per_layer, max_batch_size, max_seq_len, dtype, device,
+                       host_kvstorage_backend=HostKVStorageBackend.NATIVE_HOST.value, onload_timeout_ms=0.0,
+                       offload_timeout_ms=0.0, offload_mode=KVCacheOffloadMode.LAZY.value,
+                       host_kvstorage_fail_policy=HostKVStorageFailPolicy.FAIL_OPEN.value, extra_configs=None) -> KVCacheConfig:
+    return KVCacheConfig(num_layers, num_heads, head_dim, page_size, offload_chunksize, num_primary_cache_pages,
+                         num_buffer_pages, host_capacity_per_layer, max_batch_size, max_seq_len, dtype, device,
+                         host_kvstorage_backend, onload_timeout_ms, offload_timeout_ms, offload_mode,
+                         host_kvstorage_fail_policy, dict(extra_configs or {}))
+
+
+@dataclasses.dataclass
+class KVIndexMeta:
+    user_ids: torch.Tensor            # int64 [B] (host)
+    sequence_lengths: torch.Tensor    # int32 [B] total history length per user (host)
+
+
+@dataclasses.dataclass
+class KVLookupResult:
+    user_ids: torch.Tensor
+    cached_start_indices: torch.Tensor      # merged view over both tiers
+    cached_lengths: torch.Tensor
+    npu_cached_start_indices: Optional[torch.Tensor] = None
+    npu_cached_lengths: Optional[torch.Tensor] = None
+    host_cached_start_indices: Optional[torch.Tensor] = None
+    host_cached_lengths: Optional[torch.Tensor] = None
+    token_ids: Optional[torch.Tensor] = None
+    token_mask: Optional[torch.Tensor] = None
+    extra: Dict[str, Any] = dataclasses.field(default_factory=dict)
+
+    @staticmethod
+    def merge(user_ids, dev_start, dev_len, host_start, host_len) -> "KVLookupResult":
+        """Usable cached prefix = [0, max(device end, host end)): the host tier always starts at token 0 and the
+        device only drops a prefix after it reached the host, so the two ranges never leave a gap."""
+        end = torch.maximum(dev_start + dev_len, host_start + host_len)
+        return KVLookupResult(user_ids, torch.zeros_like(end), end, dev_start, dev_len, host_start, host_len)
+
+
+@dataclasses.dataclass
+class KVCacheMetadata:
+    page_ids_npu_buffer: torch.Tensor
+    metadata_npu_buffer: torch.Tensor
+    kv_indices: torch.Tensor
+    kv_indptr: torch.Tensor
+    kv_last_page_len: torch.Tensor
+    total_history_lengths: torch.Tensor
+    total_history_offsets: torch.Tensor
+    new_history_offsets: torch.Tensor
+    batch_indices: torch.Tensor
+    position: torch.Tensor
+    new_history_nnz: int
+    new_history_nnz_npu: torch.Tensor
+    kv_seqlens: Optional[torch.Tensor] = None
+    kv_seqlen_offsets: Optional[torch.Tensor] = None
+    kv_cache_table: Optional[torch.Tensor] = None
+    kv_onload_handle: Any = None
+    max_seqlen: int = 0
+    onboard_slot_mappings: Any = None
+    onboard_task_ids: Any = None
+    host_page_indptr: Optional[List[int]] = None      # host copies, for planning transfers without a D2H read
+    host_page_ids: Optional[np.ndarray] = None
+
+
+class HostKVTaskStatus(enum.Enum):
+    UNINITIALIZED = "uninitialized"
+    SKIPPED = "skipped"
+    LAUNCHED = "launched"
+    READY = "ready"
+    EVENT_READY = "event_ready"
+    TIMEOUT = "timeout"
+    FAILED = "failed"
+    CANCELLED = "cancelled"
+
+
+class HostKVStorageErrorCode(str, enum.Enum):
+    LOOKUP_FAILED = "lookup_failed"
+    LOOKUP_MISSING_TOKENS = "lookup_missing_tokens"
+    ONBOARD_TASK_NOT_FOUND = "onboard_task_not_found"
+    ONBOARD_WAIT_FAILED = "onboard_wait_failed"
+    ONBOARD_TIMEOUT = "onboard_timeout"
+    OFFLOAD_TASK_NOT_FOUND = "offload_task_not_found"
+    OFFLOAD_WAIT_FAILED = "offload_wait_failed"
+    OFFLOAD_TIMEOUT = "offload_timeout"
+    OFFLOAD_NO_SPACE = "offload_no_space"
+    CANCEL_FAILED = "cancel_failed"
+
+
+@dataclasses.dataclass
+class HostKVTaskHandle:
+    user_ids: Optional[torch.Tensor] = None
+    handle: Any = None
+    status: HostKVTaskStatus = HostKVTaskStatus.UNINITIALIZED
+    metadata: Optional[Dict[str, Any]] = None
+    time_launched: Optional[float] = None
+    is_layerwise: bool = False
+    layer_events: Optional[List[Any]] = None
+
+    def stream_wait_layer(self, layer_idx: int) -> None:
+        """Make the current stream wait until layer ``layer_idx`` of an onboard task has landed in its pages."""
+        if self.layer_events and self.layer_events[layer_idx] is not None:
+            torch.cuda.current_stream().wait_event(self.layer_events[layer_idx])
+
+
+@dataclasses.dataclass
+class HostKVWaitResult:
+    status: HostKVTaskStatus
+    error_code: Optional[HostKVStorageErrorCode] = None
+    message: str = ""
+    failed_mask: Optional[torch.Tensor] = None
+    failed_user_ids: Optional[List[int]] = None
+
+
+class HostKVStorageManagerBase(abc.ABC):
+    """Contract of a host KV tier (reference ``host_kvstorage_manager.py``)."""
+
+    @abc.abstractmethod
+    def register_npu_cache_tables(self, cache_table_list: List[torch.Tensor]) -> None: ...
+
+    @abc.abstractmethod
+    def build_index_meta(self, user_ids: torch.Tensor, sequence_lengths: torch.Tensor) -> KVIndexMeta: ...
+
+    @abc.abstractmethod
+    def lookup_kvcache(self, index_meta: KVIndexMeta) -> Tuple[torch.Tensor, torch.Tensor]: ...
+
+    @abc.abstractmethod
+    def onboard_kvcache_launch(self, index_meta, lookup_result, kvcache_metadata) -> HostKVTaskHandle: ...
+
+    @abc.abstractmethod
+    def onboard_kvcache_wait(self, task_handle: HostKVTaskHandle) -> HostKVWaitResult: ...
+
+    @abc.abstractmethod
+    def offload_kvcache_launch(self, user_ids, start_indices, page_lists, index_meta=None, kvcache_metadata=None) -> HostKVTaskHandle: ...
+
+    @abc.abstractmethod
+    def offload_kvcache_wait(self, task_handle: HostKVTaskHandle) -> HostKVWaitResult: ...
+
+    @abc.abstractmethod
+    def finish_task(self, task_handle: HostKVTaskHandle) -> List[int]: ...
+
+    @abc.abstractmethod
+    def cancel_task(self, task_handle: HostKVTaskHandle) -> bool: ...
+
+    @abc.abstractmethod
+    def evict(self, user_ids: torch.Tensor) -> None: ...
+
+    @abc.abstractmethod
+    def evict_all(self) -> None: ...
+
+
+def _np64(t: torch.Tensor) -> np.ndarray:
+    return np.ascontiguousarray(t.detach().cpu().numpy().astype(np.int64))
+
+
+def _np32(t: torch.Tensor) -> np.ndarray:
+    return np.ascontiguousarray(t.detach().cpu().numpy().astype(np.int32))
+
+
+# =============================================================================== device tier
+class GPUKVCacheManager:
+    """Owns the cache tensor ``[layers, pages, 2, page_size, heads, head_dim]`` and the native page allocator."""
+
+    def __init__(self, cfg: KVCacheConfig) -> None:
+        self.cfg = cfg
+        self.device = cfg.torch_device()
+        self.impl = host().KVPageAllocator(cfg.page_size, cfg.offload_chunksize, cfg.num_primary_cache_pages,
+                                           cfg.num_buffer_pages, cfg.max_batch_size, cfg.max_seq_len)
+        self.cache = torch.zeros(cfg.num_layers, cfg.num_primary_cache_pages, 2, cfg.page_size, cfg.num_heads, cfg.head_dim,
+                                 dtype=cfg.dtype, device=self.device)
+        self.max_offload_pages = int(cfg.extra_configs.get("max_offload_pages", cfg.num_primary_cache_pages))
+
+    def get_cache_table(self, layer: int) -> torch.Tensor:
+        return self.cache[layer]
+
+    def lookup(self, user_ids: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        s, l = self.impl.lookup(_np64(user_ids))
+        return torch.from_numpy(s.astype(np.int32)), torch.from_numpy(l.astype(np.int32))
+
+    def allocate(self, user_ids: torch.Tensor, total_lens: torch.Tensor, host_cached_lens: torch.Tensor) -> KVCacheMetadata:
+        B = user_ids.numel()
+        pages, meta, nnz = self.impl.allocate(_np64(user_ids), _np32(total_lens), _np32(host_cached_lens))
+        nnz = int(nnz)
+        dev = self.device
+        cuda = dev.type == "cuda"
+        pages_t, meta_t = torch.from_numpy(pages.astype(np.int32)), torch.from_numpy(meta.astype(np.int32))
+        if cuda:
+            pages_t, meta_t = pages_t.pin_memory(), meta_t.pin_memory()
+        page_buf = pages_t.to(dev, non_blocking=True)
+        buf = torch.empty(5 * B + 4 + 2 * nnz, dtype=torch.int32, device=dev)
+        buf[: 5 * B + 4].copy_(meta_t, non_blocking=True)
+        indptr = buf[0:B + 1]
+        last = buf[B + 1:2 * B + 1]
+        tot_len = buf[2 * B + 1:3 * B + 1]
+        tot_off = buf[3 * B + 1:4 * B + 2]
+        new_off = buf[4 * B + 3:5 * B + 4]
+        bidx = buf[5 * B + 4:5 * B + 4 + nnz]
+        pos = buf[5 * B + 4 + nnz:5 * B + 4 + 2 * nnz]
+        if nnz:
+            if cuda:
+                rc = _lib.lib().rb_kv_positions(new_off.data_ptr(), tot_len.data_ptr(), B, bidx.data_ptr(), pos.data_ptr(),
+                                                _lib.stream_ptr(dev))
+                _lib.check(rc, "rb_kv_positions")
+            else:
+                no, tl = new_off.tolist(), tot_len.tolist()
+                for b in range(B):
+                    n = no[b + 1] - no[b]
+                    bidx[no[b]:no[b + 1]] = b
+                    pos[no[b]:no[b + 1]] = torch.arange(tl[b] - n, tl[b], dtype=torch.int32)
+        return KVCacheMetadata(page_buf, buf, page_buf, indptr, last, tot_len, tot_off, new_off, bidx, pos, nnz,
+                               buf[4 * B + 2:4 * B + 3], kv_seqlens=tot_len, kv_seqlen_offsets=tot_off,
+                               max_seqlen=int(total_lens.max().item()) if B else 0,
+                               host_page_indptr=meta[: B + 1].tolist(), host_page_ids=np.asarray(pages, dtype=np.int64))
+
+    def append_kvcache(self, layer: int, k: torch.Tensor, v: torch.Tensor, md: KVCacheMetadata) -> None:
+        """Write the new tokens' K/V ``[nnz, heads, head_dim]`` of one layer into their pages."""
+        nnz = md.new_history_nnz
+        if nnz == 0:
+            return
+        cache = self.cache[layer]
+        row_bytes = self.cfg.num_heads * self.cfg.head_dim * cache.element_size()
+        if cache.is_cuda:
+            k, v = k.contiguous(), v.contiguous()
+            rc = _lib.lib().rb_kv_append_paged(k.data_ptr(), v.data_ptr(), md.batch_indices.data_ptr(), md.position.data_ptr(),
+                                               md.kv_indices.data_ptr(), md.kv_indptr.data_ptr(), nnz, self.cfg.page_size,
+                                               row_bytes, cache.data_ptr(), _lib.num_sms(cache.device), _lib.stream_ptr(cache.device))
+            _lib.check(rc, "rb_kv_append_paged")
+            return
+        ps = self.cfg.page_size
+        b, p = md.batch_indices.long(), md.position.long()
+        page = md.kv_indices.long()[md.kv_indptr.long()[b] + p // ps]
+        cache[page, 0, p % ps] = k.to(cache.dtype)
+        cache[page, 1, p % ps] = v.to(cache.dtype)
+
+    put = append_kvcache
+
+    # ---- offload bookkeeping (thin wrappers over the native allocator)
+    def check_for_offload(self, user_ids: torch.Tensor) -> torch.Tensor:
+        return torch.from_numpy(np.asarray(self.impl.check_for_offload(_np64(user_ids), self.max_offload_pages), dtype=np.int64))
+
+    def acquire_offload_pages(self, user_ids: torch.Tensor, offloaded_lengths: Optional[torch.Tensor] = None, always_offload=False):
+        u, s, pages = self.impl.acquire_offload_pages(_np64(user_ids), None if offloaded_lengths is None else _np32(offloaded_lengths),
+                                                      always_offload)
+        return (torch.from_numpy(np.asarray(u, dtype=np.int64)), torch.from_numpy(np.asarray(s, dtype=np.int32)),
+                [np.asarray(p, dtype=np.int64) for p in pages])
+
+    def release_offload_pages(self, user_ids, start, lengths, done: List[int]) -> None:
+        self.impl.release_offload_pages(_np64(user_ids), _np32(start), _np32(lengths), np.asarray(done, dtype=np.uint8))
+
+    def revoke_onboard_pages(self, user_ids, start, lengths) -> None:
+        self.impl.revoke_onboard_pages(_np64(user_ids), _np32(start), _np32(lengths))
+
+    def evict(self, user_ids: torch.Tensor) -> None:
+        for u in user_ids.tolist():
+            self.impl.evict(int(u))
+
+    def truncate(self, user_ids: torch.Tensor, lengths: torch.Tensor) -> None:
+        """Drop every token at or beyond ``lengths[i]`` of user i (request-scoped tokens such as ranking candidates)."""
+        for u, n in zip(user_ids.tolist(), lengths.tolist()):
+            self.impl.truncate(int(u), int(n))
+
+    def evict_all(self) -> None:
+        self.impl.evict_all()
+
+
+NPUKVCacheManager = GPUKVCacheManager   # the name the reference API uses for the device tier
+
+
+# =============================================================================== host tier
+class NativeHostKVCacheManager(HostKVStorageManagerBase):
+    """Pinned host chunk store, page-major: ``pool[chunk, layer, page_in_chunk, 2, page_size * heads * head_dim]``.
+    A row of the flattened pool is one K or V page, the same unit as a row of the flattened device cache, so
+    moving a layer is one ``copy_rows`` launch on a side stream followed by one event."""
+
+    def __init__(self, cfg: KVCacheConfig) -> None:
+        self.cfg = cfg
+        self.device = cfg.torch_device()
+        self.cuda = self.device.type == "cuda"
+        hd = cfg.num_heads * cfg.head_dim
+        item = torch.empty(0, dtype=cfg.dtype).element_size()
+        self.row_elems = cfg.page_size * hd
+        self.ppc = cfg.offload_chunksize // cfg.page_size
+        chunk_bytes_per_layer = 2 * cfg.offload_chunksize * hd * item
+        self.num_chunks = max(1, int(cfg.host_capacity_per_layer // chunk_bytes_per_layer))
+        self.index = host().HostChunkIndex(self.num_chunks, cfg.offload_chunksize)
+        self.pool = torch.zeros(self.num_chunks, cfg.num_layers, self.ppc, 2, self.row_elems, dtype=cfg.dtype, pin_memory=self.cuda)
+        self.pool_rows = self.pool.view(-1, self.row_elems)
+        self.cache_rows: List[torch.Tensor] = []
+        if self.cuda:
+            self.onboard_stream, self.offload_stream = torch.cuda.Stream(self.device), torch.cuda.Stream(self.device)
+        self.fail_next_offload = False        # test hook: the next offload reports a failed copy (host-side injection)
+        self.fail_next_onboard = False
+
+    def register_npu_cache_tables(self, cache_table_list: List[torch.Tensor]) -> None:
+        self.cache_rows = [t.view(-1, self.row_elems) for t in cache_table_list]        # rows: (page, kv)
+
+    def build_index_meta(self, user_ids, sequence_lengths) -> KVIndexMeta:
+        return KVIndexMeta(user_ids.cpu().long(), sequence_lengths.cpu().int())
+
+    def lookup_kvcache(self, index_meta: KVIndexMeta):
+        s, l = self.index.lookup(_np64(index_meta.user_ids))
+        return torch.from_numpy(s.astype(np.int32)), torch.from_numpy(l.astype(np.int32))
+
+    def _pool_rows_of(self, chunks: np.ndarray, layer: int) -> np.ndarray:
+        """Row numbers, in token order, of all (page, kv) rows of ``chunks`` for ``layer``."""
+        per = self.ppc * 2
+        base = (chunks.astype(np.int64) * self.cfg.num_layers + layer) * per
+        return (base[:, None] + np.arange(per, dtype=np.int64)[None, :]).reshape(-1)
+
+    @staticmethod
+    def _cache_rows_of(pages: np.ndarray) -> np.ndarray:
+        p = pages.astype(np.int64)
+        return np.stack([p * 2, p * 2 + 1], axis=1).reshape(-1)
+
+    def _idx(self, a: np.ndarray) -> torch.Tensor:
+        t = torch.from_numpy(a)
+        return t.pin_memory().to(self.device, non_blocking=True) if self.cuda else t
+
+    def onboard_kvcache_launch(self, index_meta, lookup_result, kvcache_metadata) -> HostKVTaskHandle:
+        """Copy every host-resident prefix that the device does not hold into the pages just allocated for it."""
+        cfg = self.cfg
+        uids = index_meta.user_ids.tolist()
+        dev_start = lookup_result.npu_cached_start_indices.tolist()
+        dev_len = lookup_result.npu_cached_lengths.tolist()
+        host_len = lookup_result.host_cached_lengths.tolist()
+        indptr, page_ids = kvcache_metadata.host_page_indptr, kvcache_metadata.host_page_ids
+        jobs = []                                   # (uid, tokens, chunk ids, destination pages)
+        for b, u in enumerate(uids):
+            need = host_len[b] if dev_len[b] == 0 else min(dev_start[b], host_len[b])
+            need = (need // cfg.offload_chunksize) * cfg.offload_chunksize
+            if need <= 0:
+                continue
+            chunks = np.asarray(self.index.chunks_of(int(u), 0, need), dtype=np.int64)
+            if len(chunks) * cfg.offload_chunksize < need:
+                raise RuntimeError("host index lost chunks of user %d between lookup and onboard" % u)
+            jobs.append((int(u), need, chunks, page_ids[indptr[b]: indptr[b] + need // cfg.page_size]))
+        h = HostKVTaskHandle(index_meta.user_ids, status=HostKVTaskStatus.SKIPPED, time_launched=time.time(), is_layerwise=True,
+                             metadata={"jobs": [(u, n) for u, n, _c, _p in jobs]})
+        if not jobs:
+            return h
+        if self.fail_next_onboard:
+            self.fail_next_onboard = False
+            raise RuntimeError("injected onboard failure")
+        dst = self._idx(np.concatenate([self._cache_rows_of(p) for _u, _n, _c, p in jobs]))
+        src_all = self._idx(np.stack([np.concatenate([self._pool_rows_of(c, layer) for _u, _n, c, _p in jobs])
+                                      for layer in range(cfg.num_layers)]))
+        events: List[Any] = [None] * cfg.num_layers
+        if self.cuda:
+            self.onboard_stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.onboard_stream):
+                for layer in range(cfg.num_layers):
+                    E.copy_rows(self.pool_rows, src_all[layer], self.cache_rows[layer], dst, self.device)
+                    events[layer] = torch.cuda.Event()
+                    events[layer].record(self.onboard_stream)
+            dst.record_stream(self.onboard_stream)
+            src_all.record_stream(self.onboard_stream)
+        else:
+            for layer in range(cfg.num_layers):
+                E.copy_rows(self.pool_rows, src_all[layer], self.cache_rows[layer], dst)
+        h.layer_events, h.status = events, HostKVTaskStatus.LAUNCHED
+        return h
+
+    def _poll(self, events, limit_ms: float) -> bool:
+        t0 = time.time()
+        for ev in events or []:
+            if ev is None:
+                continue
+            while not ev.query():
+                if limit_ms > 0 and (time.time() - t0) * 1e3 > limit_ms:
+                    return False
+                time.sleep(0.0001)
+        return True
+
+    def onboard_kvcache_wait(self, task_handle: HostKVTaskHandle) -> HostKVWaitResult:
+        if task_handle.status == HostKVTaskStatus.SKIPPED:
+            return HostKVWaitResult(HostKVTaskStatus.SKIPPED)
+        if not self._poll(task_handle.layer_events, self.cfg.onload_timeout_ms):
+            task_handle.status = HostKVTaskStatus.TIMEOUT
+            return HostKVWaitResult(HostKVTaskStatus.TIMEOUT, HostKVStorageErrorCode.ONBOARD_TIMEOUT, "onboard timed out")
+        task_handle.status = HostKVTaskStatus.READY
+        return HostKVWaitResult(HostKVTaskStatus.READY)
+
+    def offload_kvcache_launch(self, user_ids, start_indices, page_lists, index_meta=None, kvcache_metadata=None) -> HostKVTaskHandle:
+        """Copy whole chunks (``start`` is chunk-aligned by construction) from device pages into new host chunks."""
+        cfg = self.cfg
+        uids, starts = user_ids.tolist(), start_indices.tolist()
+        pinned = [int(u) for u in uids]
+        plan, lengths, no_space = [], [], []
+        for u, s, pages in zip(uids, starts, page_lists):
+            n_chunks = len(pages) // self.ppc
+            n_tok = n_chunks * cfg.offload_chunksize
+            chunks = np.asarray(self.index.append(int(u), int(s), n_tok, pinned), dtype=np.int64) if n_tok > 0 else np.zeros(0, np.int64)
+            if n_tok > 0 and len(chunks) == 0:
+                no_space.append(int(u))
+                lengths.append(0)
+                continue
+            if n_tok > 0:
+                plan.append((int(u), chunks, np.asarray(pages[: n_chunks * self.ppc], dtype=np.int64)))
+            lengths.append(n_tok)
+        h = HostKVTaskHandle(user_ids, status=HostKVTaskStatus.LAUNCHED, time_launched=time.time(),
+                             metadata={"plan": plan, "lengths": lengths, "starts": starts, "no_space": no_space})
+        if not plan:
+            h.status = HostKVTaskStatus.SKIPPED
+            return h
+        src = self._idx(np.concatenate([self._cache_rows_of(p) for _u, _c, p in plan]))
+        dst_all = self._idx(np.stack([np.concatenate([self._pool_rows_of(c, layer) for _u, c, _p in plan])
+                                      for layer in range(cfg.num_layers)]))
+        if self.cuda:
+            self.offload_stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.offload_stream):
+                for layer in range(cfg.num_layers):
+                    E.copy_rows(self.cache_rows[layer], src, self.pool_rows, dst_all[layer], self.device)
+                ev = torch.cuda.Event()
+                ev.record(self.offload_stream)
+            src.record_stream(self.offload_stream)
+            dst_all.record_stream(self.offload_stream)
+            h.layer_events = [ev]
+        else:
+            for layer in range(cfg.num_layers):
+                E.copy_rows(self.cache_rows[layer], src, self.pool_rows, dst_all[layer])
+        return h
+
+    def offload_kvcache_wait(self, task_handle: HostKVTaskHandle) -> HostKVWaitResult:
+        no_space = (task_handle.metadata or {}).get("no_space") or None
+        code = HostKVStorageErrorCode.OFFLOAD_NO_SPACE if no_space else None
+        if task_handle.status == HostKVTaskStatus.SKIPPED:
+            return HostKVWaitResult(HostKVTaskStatus.SKIPPED, code, failed_user_ids=no_space)
+        if self.fail_next_offload:
+            self.fail_next_offload = False
+            if self.cuda:
+                self.offload_stream.synchronize()
+            task_handle.status = HostKVTaskStatus.FAILED
+            return HostKVWaitResult(HostKVTaskStatus.FAILED, HostKVStorageErrorCode.OFFLOAD_WAIT_FAILED, "injected copy failure")
+        if not self._poll(task_handle.layer_events, self.cfg.offload_timeout_ms):
+            task_handle.status = HostKVTaskStatus.TIMEOUT
+            return HostKVWaitResult(HostKVTaskStatus.TIMEOUT, HostKVStorageErrorCode.OFFLOAD_TIMEOUT, "offload timed out")
+        task_handle.status = HostKVTaskStatus.READY
+        return HostKVWaitResult(HostKVTaskStatus.READY, code, failed_user_ids=no_space)
+
+    def finish_task(self, task_handle: HostKVTaskHandle) -> List[int]:
+        """-> per user 1 (offloaded) / 0 (not).  A failed, timed-out or cancelled task gives its chunks back; a
+        timed-out copy may still be writing, so the stream is drained before the chunks can be reused."""
+        plan = task_handle.metadata.get("plan", []) if task_handle.metadata else []
+        ok = task_handle.status == HostKVTaskStatus.READY
+        if not ok and plan:
+            if self.cuda:
+                self.offload_stream.synchronize()
+            for u, chunks, _p in plan:
+                self.index.rollback(u, len(chunks))
+        done_users = {u for u, _c, _p in plan} if ok else set()
+        return [1 if int(u) in done_users else 0 for u in task_handle.user_ids.tolist()]
+
+    def cancel_task(self, task_handle: HostKVTaskHandle) -> bool:
+        task_handle.status = HostKVTaskStatus.CANCELLED
+        self.finish_task(task_handle)
+        return True
+
+    def evict(self, user_ids: torch.Tensor) -> None:
+        for u in user_ids.tolist():
+            self.index.evict(int(u))
+
+    def evict_all(self) -> None:
+        self.index.evict_all()
+
+
+# =============================================================================== orchestration
+class KVCacheManager:
+    def __init__(self, npu_kvcache_manager: GPUKVCacheManager, host_kvstorage_manager: Optional[HostKVStorageManagerBase],
+                 offload_mode: str = KVCacheOffloadMode.LAZY.value,
+                 host_kvstorage_fail_policy: str = HostKVStorageFailPolicy.FAIL_OPEN.value) -> None:
+        self.gpu, self.host = npu_kvcache_manager, host_kvstorage_manager
+        self.offload_mode, self.fail_policy = offload_mode, host_kvstorage_fail_policy
+        if self.host is not None:
+            self.host.register_npu_cache_tables([self.gpu.get_cache_table(l) for l in range(self.gpu.cfg.num_layers)])
+        self._pending_offload: Optional[Tuple[HostKVTaskHandle, torch.Tensor, torch.Tensor, torch.Tensor]] = None
+        self.stats = {"onboard_failures": 0, "offload_failures": 0, "offload_timeouts": 0, "offloaded_tokens": 0,
+                      "onboarded_tokens": 0}
+
+    @classmethod
+    def from_config(cls, cfg: KVCacheConfig) -> "KVCacheManager":
+        hostm = NativeHostKVCacheManager(cfg) if cfg.host_capacity_per_layer > 0 else None
+        return cls(GPUKVCacheManager(cfg), hostm, cfg.offload_mode, cfg.host_kvstorage_fail_policy)
+
+    def _fail(self, what: str, res: HostKVWaitResult) -> None:
+        if self.fail_policy == HostKVStorageFailPolicy.FAIL_CLOSE.value:
+            raise RuntimeError("%s failed: %s %s" % (what, res.error_code, res.message))
+
+    def lookup_kvcache(self, user_ids: torch.Tensor, sequence_lengths: torch.Tensor) -> Tuple[KVIndexMeta, KVLookupResult]:
+        meta = KVIndexMeta(user_ids.cpu().long(), sequence_lengths.cpu().int())
+        ds, dl = self.gpu.lookup(meta.user_ids)
+        if self.host is not None:
+            hs, hl = self.host.lookup_kvcache(meta)
+        else:
+            hs, hl = torch.zeros_like(ds), torch.zeros_like(dl)
+        return meta, KVLookupResult.merge(meta.user_ids, ds, dl, hs, hl)
+
+    def allocate_kvcache(self, index_meta: KVIndexMeta, lookup_results: KVLookupResult,
+                         output_kvcache_metadata: Optional[KVCacheMetadata] = None) -> KVCacheMetadata:
+        md = self.gpu.allocate(index_meta.user_ids, index_meta.sequence_lengths,
+                               torch.minimum(lookup_results.host_cached_lengths, index_meta.sequence_lengths))
+        md.kv_cache_table = self.gpu.cache
+        return md
+
+    def _onboard_need(self, lookup_result: KVLookupResult) -> torch.Tensor:
+        c = self.gpu.cfg.offload_chunksize
+        need = torch.where(lookup_result.npu_cached_lengths == 0, lookup_result.host_cached_lengths,
+                           torch.minimum(lookup_result.npu_cached_start_indices, lookup_result.host_cached_lengths))
+        return (need // c) * c
+
+    def onboard_launch(self, index_meta, lookup_result, kvcache_metadata) -> HostKVTaskHandle:
+        if self.host is None:
+            return HostKVTaskHandle(index_meta.user_ids, status=HostKVTaskStatus.SKIPPED)
+        try:
+            h = self.host.onboard_kvcache_launch(index_meta, lookup_result, kvcache_metadata)
+        except Exception as e:  # noqa: BLE001 - the host tier is best effort under fail_open
+            self.stats["onboard_failures"] += 1
+            self._fail("onboard", HostKVWaitResult(HostKVTaskStatus.FAILED, HostKVStorageErrorCode.ONBOARD_WAIT_FAILED, str(e)))
+            return HostKVTaskHandle(index_meta.user_ids, status=HostKVTaskStatus.FAILED,
+                                    metadata={"need": self._onboard_need(lookup_result)})
+        kvcache_metadata.kv_onload_handle = h
+        self.stats["onboarded_tokens"] += sum(n for _u, n in h.metadata["jobs"])
+        return h
+
+    def onboard_try_wait(self, handle: HostKVTaskHandle) -> HostKVWaitResult:
+        if self.host is None or handle.status in (HostKVTaskStatus.SKIPPED, HostKVTaskStatus.FAILED):
+            return HostKVWaitResult(handle.status)
+        res = self.host.onboard_kvcache_wait(handle)
+        if res.status not in (HostKVTaskStatus.READY, HostKVTaskStatus.SKIPPED):
+            self.stats["onboard_failures"] += 1
+            self._fail("onboard", res)
+        return res
+
+    onboard_wait = onboard_try_wait
+
+    def revoke_failed_onboard(self, index_meta: KVIndexMeta, lookup_result: KVLookupResult) -> None:
+        """After a failed onboard the request is recomputed from token 0: drop the pages that were reserved for the
+        host prefix so the device range no longer claims tokens that never arrived."""
+        need = self._onboard_need(lookup_result)
+        self.gpu.revoke_onboard_pages(index_meta.user_ids, torch.zeros_like(need), need)
+
+    def offload_launch(self, index_meta: KVIndexMeta, kvcache_metadata: Optional[KVCacheMetadata] = None) -> Optional[HostKVTaskHandle]:
+        if self.host is None:
+            return None
+        if self._pending_offload is not None:
+            self.offload_try_wait()
+        cands = index_meta.user_ids
+        if self.offload_mode != KVCacheOffloadMode.EAGER.value:
+            cands = self.gpu.check_for_offload(index_meta.user_ids)
+        if cands.numel() == 0:
+            return None
+        _hs, hl = self.host.lookup_kvcache(KVIndexMeta(cands, torch.zeros(cands.numel(), dtype=torch.int32)))
+        uids, starts, pages = self.gpu.acquire_offload_pages(cands, hl.int(), False)
+        if uids.numel() == 0:
+            return None
+        h = self.host.offload_kvcache_launch(uids, starts, pages, index_meta, kvcache_metadata)
+        lengths = torch.tensor(h.metadata["lengths"], dtype=torch.int32)
+        self._pending_offload = (h, uids, starts, lengths)
+        return h
+
+    def offload_try_wait(self) -> Optional[HostKVWaitResult]:
+        if self._pending_offload is None:
+            return None
+        h, uids, starts, lengths = self._pending_offload
+        self._pending_offload = None
+        res = self.host.offload_kvcache_wait(h)
+        done = self.host.finish_task(h)
+        self.gpu.release_offload_pages(uids, starts, lengths, done)       # locks are released on every path
+        if res.status == HostKVTaskStatus.READY:
+            self.stats["offloaded_tokens"] += int(sum(l for l, d in zip(lengths.tolist(), done) if d))
+        elif res.status == HostKVTaskStatus.TIMEOUT:
+            self.stats["offload_timeouts"] += 1
+            self._fail("offload", res)
+        elif res.status == HostKVTaskStatus.FAILED:
+            self.stats["offload_failures"] += 1
+            self._fail("offload", res)
+        return res
+
+    def evict(self, user_ids: torch.Tensor, for_npu: bool = True, for_host: bool = True) -> None:
+        if for_npu:
+            self.gpu.evict(user_ids)
+        if for_host and self.host is not None:
+            self.host.evict(user_ids)
+
+    def evict_all(self, for_npu: bool = True, for_host: bool = True) -> None:
+        if for_npu:
+            self.gpu.evict_all()
+        if for_host and self.host is not None:
+            self.host.evict_all()

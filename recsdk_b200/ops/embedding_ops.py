@@ -293,3 +293,19 @@ def reference_pooled_forward(tables: List[torch.Tensor], indices: torch.Tensor, 
             rows.append(v)
         outs.append(torch.stack(rows))
     return torch.cat(outs, dim=1)
+
+
+def copy_rows(src: torch.Tensor, src_idx: torch.Tensor, dst: torch.Tensor, dst_idx: torch.Tensor,
+              device: Optional[torch.device] = None) -> None:
+    """``dst[dst_idx[i]] = src[src_idx[i]]`` over 2-D row-major tensors.  With ``device`` a CUDA device, either
+    tensor may be pinned host memory: the kernel reads / writes it through the unified address space."""
+    if device is None or device.type != "cuda":
+        dst[dst_idx.to(dst.device)] = src[src_idx.to(src.device)].to(dst.device)
+        return
+    assert src.is_contiguous() and dst.is_contiguous() and src.shape[1:] == dst.shape[1:] and src.dtype == dst.dtype
+    assert (src.is_cuda or src.is_pinned()) and (dst.is_cuda or dst.is_pinned())
+    assert src_idx.is_cuda and dst_idx.is_cuda and src_idx.dtype == torch.int64 and dst_idx.dtype == torch.int64
+    row_bytes = src[0].numel() * src.element_size()
+    rc = _lib.lib().rb_copy_rows(src.data_ptr(), src_idx.data_ptr(), dst.data_ptr(), dst_idx.data_ptr(), src_idx.numel(),
+                                 row_bytes, _lib.num_sms(device), _lib.stream_ptr(device))
+    _lib.check(rc, "rb_copy_rows")

@@ -1,0 +1,140 @@
+"""Kernel micro-benchmarks (CUDA-event timing, warm-up, L2 flushed between iterations).
+
+    python -m recsdk_b200.utils.microbench gemm --m 65536 --n 1024 --k 1024
+    python -m recsdk_b200.utils.microbench hstu_fwd --seqs 8 --len 2048 --heads 8 [--bias]
+    python -m recsdk_b200.utils.microbench hstu_bwd --seqs 8 --len 2048 --heads 8 [--bias]
+    python -m recsdk_b200.utils.microbench tbe_fwd --rows 20000000 --batch 65536 --tables 26
+
+Prints one JSON line with the measured time and the achieved rate against the measured peaks
+(``MEASURED_PEAKS.json`` at the repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).
+Small cases of these commands are what the ncu captures under ``profiles/`` were taken on.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+
+def _peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("hbm_gbs", 6650.0) * 1e9, d.get("bf16_tflops", 1590.0) * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+def _time(fn, iters: int, warmup: int = 3) -> float:
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")      # > 126 MB L2
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "hstu_fwd", "hstu_bwd", "tbe_fwd", "interaction"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=1024)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--a-mn", action="store_true")
+    ap.add_argument("--b-mn", action="store_true")
+    ap.add_argument("--splits", type=int, default=1)
+    ap.add_argument("--seqs", type=int, default=8)
+    ap.add_argument("--len", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=8)
+    ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--rows", type=int, default=10_000_000)
+    ap.add_argument("--batch", type=int, default=65536)
+    ap.add_argument("--tables", type=int, default=26)
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    from ..ops import _lib, gemm
+
+    hbm, flops, src = _peaks()
+    dev = torch.device("cuda", 0)
+    out = {"what": a.what, "peaks": src}
+    if a.what == "gemm":
+        A = torch.randn((a.k, a.m) if a.a_mn else (a.m, a.k), device=dev).bfloat16()
+        B = torch.randn((a.k, a.n) if a.b_mn else (a.n, a.k), device=dev).bfloat16()
+        bias = torch.randn(a.n, device=dev)
+        if a.splits > 1:
+            C = torch.zeros(a.m, a.n, device=dev)
+            fn = lambda: gemm.gemm16(A, B, a_mn=a.a_mn, b_mn=a.b_mn, out=C, epi=gemm.EPI_F32_ATOMIC, splits=a.splits)  # noqa: E731
+        else:
+            C = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=dev)
+            fn = lambda: gemm.gemm16(A, B, a_mn=a.a_mn, b_mn=a.b_mn, out=C, bias=bias, epi=gemm.EPI_RELU)  # noqa: E731
+        ms = _time(fn, a.iters)
+        fl = 2.0 * a.m * a.n * a.k
+        out.update(ms=ms, tflops=fl / ms / 1e9, frac_of_peak=fl / (ms / 1e3) / flops, shape=[a.m, a.n, a.k])
+    elif a.what in ("hstu_fwd", "hstu_bwd"):
+        from ..ops import hstu_attention as HA
+        from ..ops.hstu_attention_bwd import hstu_attn_bwd
+
+        H, D, L, S = a.heads, 64, a.len, a.seqs
+        T = S * L
+        q, k, v = [(torch.randn(T, H, D, device=dev) * 0.5).bfloat16() for _ in range(3)]
+        off = torch.arange(0, T + 1, L, device=dev)
+        kw = dict(ts=None, ts_w=None, ts_divisor=0.301, pos_w=None)
+        if a.bias:
+            kw = dict(ts=torch.cumsum(torch.rand(T, device=dev) * 3600, 0), ts_w=torch.randn(129, device=dev) * 0.1,
+                      ts_divisor=0.301, pos_w=torch.randn(4096, device=dev) * 0.1)
+        if a.what == "hstu_fwd":
+            o = torch.empty_like(q)
+            fn = lambda: HA.hstu_attn_fwd(q, k, v, off, off, L, 0.125, 1.0 / L, True, out=o, **kw)  # noqa: E731
+            mm = 2
+        else:
+            do = torch.randn_like(q)
+            fn = lambda: hstu_attn_bwd(do, q, k, v, off, off, 0.125, 1.0 / L, True, None, None, 0, kw["ts"], kw["ts_w"],  # noqa: E731
+                                       0.301, kw["pos_w"], max_len_k=L)
+            mm = 5
+        ms = _time(fn, a.iters)
+        pairs = S * H * (L * (L + 128) / 2)                     # causal (block-granular) score elements
+        fl = pairs * D * 2 * mm
+        out.update(ms=ms, tflops=fl / ms / 1e9, score_elems_per_s=pairs / (ms / 1e3), shape=[S, L, H, D], bias=a.bias)
+    elif a.what == "tbe_fwd":
+        from ..ops import embedding_ops as E
+
+        T, B, D = a.tables, a.batch, 128
+        rows = a.rows // T
+        lay = E.TbeLayout([D] * T, [rows] * T, [E.SH_LOCAL] * T, [0] * T, 1, 0)
+        w = torch.randn(T * rows * D, device=dev).half()
+        d = lay.device_tensors(dev, [w.data_ptr()], 2)
+        idx = torch.randint(0, rows, (T * B,), device=dev)
+        o = torch.empty(B, T * D, dtype=torch.bfloat16, device=dev)
+        fn = lambda: E.tbe_forward(lay, d, idx, None, B, E.POOL_SUM, torch.float16, o)  # noqa: E731
+        ms = _time(fn, a.iters)
+        by = T * B * D * 2 * 2 + T * B * 8
+        out.update(ms=ms, gbs=by / ms / 1e6, frac_of_peak=by / (ms / 1e3) / hbm)
+    else:
+        from ..ops import interaction as I
+
+        B, F, D = a.batch, 27, 128
+        x0 = torch.randn(B, D, device=dev).bfloat16()
+        xs = torch.randn(B, (F - 1) * D, device=dev).bfloat16()
+        o = torch.empty(B, 480, dtype=torch.bfloat16, device=dev)
+        fn = lambda: I.dot_interaction_fwd(x0, xs, F, o)  # noqa: E731
+        ms = _time(fn, a.iters)
+        by = B * F * D * 2 + B * 480 * 2
+        out.update(ms=ms, gbs=by / ms / 1e6, frac_of_peak=by / (ms / 1e3) / hbm)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    sys.exit(main())
