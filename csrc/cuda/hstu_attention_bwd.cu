@@ -36,6 +36,7 @@ struct HstuBwdParams {
   float* dq32; long long ld_dq;            // fp32 accumulator [Tq][ld_dq]
   void* dk; void* dv; long long ld_dkv;    // bf16 [Tk][ld_dkv]
   float* d_ts_w; float* d_pos_w;
+  int bucket_cap;                          // min(num_buckets, floor(log(7e16) / divisor))
   int* status;
 };
 
@@ -57,8 +58,67 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 
 constexpr int POS_HIST = 4096;
 constexpr int SMEM_BYTES = TILE * 8 /*K,V,2x(Q,dO),dS(2 chunks)*/ + 16 * 2 * 32 * 4 /*ts*/ + 768 /*ts_w*/ + 768 /*d ts_w*/ +
-                           POS_HIST * 4 + 256 /*barriers*/ + 1024;
+                           POS_HIST * 4 + 256 /*barriers*/ + 16 * 64 * 4 /*distance-bias windows*/ + 1024;
 
+// One warp's 32 (keys, one per thread) x 32 (queries, e) chunk: S^T, dP^T -> P^T, dS^T (packed bf16) and the bias
+// gradient partial sums.  With h = alpha (S + bias) / 2 and th = tanh(h):
+//   P  = scale SiLU(2h)                 = hs + hs th,                hs = h scale
+//   dS = dP scale alpha SiLU'(2h)       = dP (sg + sg g),            sg = scale alpha (1 + th) / 2,  g = h - h th
+// dts: run-length sums per thread (the bucket of |ts_i - ts_j| changes slowly along a key row);
+// dpos: the chunk's anti-diagonals (i - j constant) are summed across lanes with one shuffle per element: lane o owns
+//       diagonals o and o + 32 of the 63, element (e, lane) lies on diagonal e - lane + 31.
+template <bool BT, bool BP, bool WDT, bool WDP, bool MASKED>
+__device__ __forceinline__ void bwd_chunk(const uint32_t (&rs)[16], const uint32_t (&rd)[16], uint32_t* pk, uint32_t* dk16, int e0,
+                                          int& run_bucket, float& run_sum, float ts_j, const float* my_ts, const float* tsw_s, float* dtsw_s, const float* my_pos,
+                                          int lane, float k_log, int cap, float half_alpha, float scale, float half_sa, int pi0,
+                                          int i0, int j, int len_q, int len_k, int causal, int nctx, int ntgt, int gs,
+                                          float& acc_lo, float& acc_hi) {
+#pragma unroll
+  for (int e = 0; e < 16; e += 2) {
+    float pv[2], dsv[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int ee = e0 + e + q;                                   // query column inside the 32-wide chunk
+      float s = __uint_as_float(rs[e + q]);
+      int bk = 0;
+      if (BT) {
+        const float a = fmaxf(fabsf(my_ts[ee] - ts_j), 1.f);
+        bk = min(static_cast<int>(__log2f(a) * k_log), cap);
+        s += tsw_s[bk];
+      }
+      if (BP) s += my_pos[ee + 31 - lane];
+      const float h = s * half_alpha;
+      float th;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(h));
+      const float hs = h * scale;
+      float pval = fmaf(hs, th, hs);
+      const float g = fmaf(-h, th, h);
+      const float sg = fmaf(half_sa, th, half_sa);
+      float ds = __uint_as_float(rd[e + q]) * fmaf(sg, g, sg);
+      if (MASKED) {
+        const bool on = (i0 + ee < len_q) && attends(pi0 + ee, j, len_k, causal, nctx, ntgt, gs);
+        if (!on) { pval = 0.f; ds = 0.f; }
+      }
+      if (WDT) {
+        if (bk != run_bucket) {
+          if (run_bucket >= 0 && run_sum != 0.f) atomicAdd(dtsw_s + run_bucket, run_sum);
+          run_bucket = bk; run_sum = 0.f;
+        }
+        run_sum += ds;
+      }
+      if (WDP) {
+        const int src = (ee + 31 - lane) & 31;
+        const float got = __shfl_sync(0xffffffffu, ds, src);
+        if (src < ee) acc_hi += got; else acc_lo += got;
+      }
+      pv[q] = pval; dsv[q] = ds;
+    }
+    pk[e >> 1] = rb::pack_bf16(pv[0], pv[1]);
+    dk16[e >> 1] = rb::pack_bf16(dsv[0], dsv[1]);
+  }
+}
+
+template <bool BT, bool BP, bool WDT, bool WDP>
 __global__ void __launch_bounds__(640, 1)
 hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -102,7 +162,8 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   float* tsw_s = ts_s + 1024;                                      // [192]
   float* dtsw_s = tsw_s + 192;                                     // [192]
   float* dpos_s = dtsw_s + 192;                                    // [POS_HIST]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(dpos_s + POS_HIST);
+  float* pos_s = dpos_s + POS_HIST;                                // [16 warps][64] distance-bias windows
+  uint64_t* bars = reinterpret_cast<uint64_t*>(pos_s + 16 * 64);
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = bars + 1;       // [2]
   uint64_t* qdo_empty = bars + 3;      // [2]
@@ -116,8 +177,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* quarter_bar = bars + 11;   // [4] the four warps of one TMEM lane quarter meet here once per tile
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool want_dpos = p.d_pos_w != nullptr && p.pos_w != nullptr;
-  const bool want_dts = p.d_ts_w != nullptr && p.ts_w != nullptr && p.ts != nullptr;
+  constexpr bool want_dpos = WDP, want_dts = WDT;
   if (threadIdx.x == 0) {
     rb::mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { rb::mbar_init(&qdo_full[s], 1); rb::mbar_init(&qdo_empty[s], 1); }
@@ -209,69 +269,70 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int row = ew * 32 + lane;                                 // key row of this thread
     const int j = kb * BKV + row;
     const uint32_t lane_sel = static_cast<uint32_t>(ew * 32) << 16;
-    const bool has_t = p.ts != nullptr && p.ts_w != nullptr;
-    const bool has_p = p.pos_w != nullptr;
-    const float ts_j = has_t ? p.ts[k_start + min(j, len_k - 1)] : 0.f;
-    const float inv_div = 1.f / p.ts_divisor;
-    const float sa = p.scale * p.alpha;
+    const float ts_j = BT ? p.ts[k_start + min(j, len_k - 1)] : 0.f;
+    const float k_log = 0.69314718f / p.ts_divisor;
+    const float half_alpha = 0.5f * p.alpha;
+    const float half_sa = 0.5f * p.scale * p.alpha;
+    const int j0w = kb * BKV + ew * 32;                               // key of lane 0
+    float* my_pos = pos_s + (warp - 4) * 64;
+    auto load_ts = [&](int t) -> float {
+      const int pi = (qb_first + t) * BQ + grp * 32 + lane + delta;
+      return (t < n_iter && pi < len_k && pi >= 0) ? __ldg(p.ts + k_start + pi) : 0.f;
+    };
+    auto load_pos = [&](int t, int w) -> float {
+      const int d = (qb_first + t) * BQ + grp * 32 + delta - j0w - 31 + w;
+      return t < n_iter ? __ldg(p.pos_w + min(max(d, 0), p.pos_len - 1)) : 0.f;
+    };
+    float ts_nxt = BT ? load_ts(0) : 0.f;
+    float pos_nxt0 = BP ? load_pos(0, lane) : 0.f, pos_nxt1 = BP ? load_pos(0, lane + 32) : 0.f;
+    // time-bucket gradient: a key row meets its buckets in long runs (|ts_i - ts_j| grows with i), so the running sum
+    // lives across tiles and reaches shared memory only when the bucket changes
+    int run_bucket = -1;
+    float run_sum = 0.f;
     for (int t = 0; t < n_iter; ++t) {
       const int qb = qb_first + t;
       float* my_ts = ts_s + ((warp - 4) * 2 + (t & 1)) * 32;
-      if (has_t) {
-        const int pi = qb * BQ + grp * 32 + lane + delta;
-        my_ts[lane] = (pi < len_k && pi >= 0) ? __ldg(p.ts + k_start + pi) : 0.f;
+      if (BT || BP) {
+        __syncwarp();
+        if (BT) { my_ts[lane] = ts_nxt; ts_nxt = load_ts(t + 1); }
+        if (BP) {
+          my_pos[lane] = pos_nxt0; my_pos[lane + 32] = pos_nxt1;
+          pos_nxt0 = load_pos(t + 1, lane); pos_nxt1 = load_pos(t + 1, lane + 32);
+        }
         __syncwarp();
       }
       bool ok = rb::mbar_wait(sdp_full, t & 1, abort_flag, p.status);
       if (!__all_sync(0xffffffffu, ok)) goto done;
       rb::tc_fence_after();
-      int run_bucket = -1;
-      float run_sum = 0.f;
+      // a tile strictly below the diagonal with no ragged edge needs no mask
+      const bool full = p.causal && ntgt == 0 && (kb * BKV + BKV - 1 <= qb * BQ + delta) && (kb * BKV + BKV <= len_k) &&
+                        (qb * BQ + BQ <= len_q);
       {
         const int c = grp;
-        uint32_t rs[32], rd[32];
-        rb::tmem_ld_32x32(T_ST + lane_sel + c * 32, rs);
-        rb::tmem_ld_32x32(T_DP + lane_sel + c * 32, rd);
-        rb::tmem_ld_wait();
         uint32_t pk[16], dk16[16];
+        const int i0 = qb * BQ + c * 32, pi0 = i0 + delta;
+        float acc_lo = 0.f, acc_hi = 0.f;
+        // two halves of 16 query columns keep the live registers under the 640-thread budget
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float pv[2], dsv[2];
-#pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const int il = c * 32 + e + q;                           // query row inside the block
-            const int i_local = qb * BQ + il;
-            const int pi = i_local + delta;
-            float s = __uint_as_float(rs[e + q]);
-            int bk = 0;
-            if (has_t) {
-              const float a = fminf(fmaxf(fabsf(my_ts[e + q] - ts_j), 1.f), 7.0e16f);
-              bk = min(max(static_cast<int>(__logf(a) * inv_div), 0), p.num_buckets);
-              s += tsw_s[bk];
-            }
-            const int dd = min(max(pi - j, 0), p.pos_len - 1);
-            if (has_p) s += __ldg(p.pos_w + dd);
-            const float x = s * p.alpha;
-            float th;
-            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * x));
-            const float sig = 0.5f * th + 0.5f;
-            const bool on = i_local < len_q && attends(pi, j, len_k, p.causal, nctx, ntgt, gs);
-            const float pval = on ? x * sig * p.scale : 0.f;
-            const float ds = on ? __uint_as_float(rd[e + q]) * sa * sig * (1.f + x * (1.f - sig)) : 0.f;
-            // dBias = dS, accumulated with the precision the matmuls see (bf16)
-            const float ds_r = __bfloat162float(__float2bfloat16(ds));
-            if (want_dts) {
-              if (bk != run_bucket) {
-                if (run_bucket >= 0 && run_sum != 0.f) atomicAdd(dtsw_s + run_bucket, run_sum);
-                run_bucket = bk; run_sum = 0.f;
-              }
-              run_sum += ds_r;
-            }
-            if (want_dpos && on) atomicAdd(dpos_s + min(dd, POS_HIST - 1), ds_r);
-            pv[q] = pval; dsv[q] = ds;
-          }
-          pk[e >> 1] = rb::pack_bf16(pv[0], pv[1]);
-          dk16[e >> 1] = rb::pack_bf16(dsv[0], dsv[1]);
+        for (int half = 0; half < 2; ++half) {
+          uint32_t rs[16], rd[16];
+          rb::tmem_ld_32x16(T_ST + lane_sel + c * 32 + half * 16, rs);
+          rb::tmem_ld_32x16(T_DP + lane_sel + c * 32 + half * 16, rd);
+          rb::tmem_ld_wait();
+          if (full)
+            bwd_chunk<BT, BP, WDT, WDP, false>(rs, rd, pk + half * 8, dk16 + half * 8, half * 16, run_bucket, run_sum, ts_j, my_ts,
+                                               tsw_s, dtsw_s, my_pos, lane, k_log, p.bucket_cap, half_alpha, p.scale, half_sa, pi0,
+                                               i0, j, len_q, len_k, p.causal, nctx, ntgt, gs, acc_lo, acc_hi);
+          else
+            bwd_chunk<BT, BP, WDT, WDP, true>(rs, rd, pk + half * 8, dk16 + half * 8, half * 16, run_bucket, run_sum, ts_j, my_ts,
+                                              tsw_s, dtsw_s, my_pos, lane, k_log, p.bucket_cap, half_alpha, p.scale, half_sa, pi0,
+                                              i0, j, len_q, len_k, p.causal, nctx, ntgt, gs, acc_lo, acc_hi);
+        }
+        if (WDP) {
+          const int hi_idx = min(p.pos_len, POS_HIST) - 1;
+          const int base = pi0 - j0w - 31;
+          if (acc_lo != 0.f) atomicAdd(dpos_s + min(max(base + lane, 0), hi_idx), acc_lo);
+          if (acc_hi != 0.f) atomicAdd(dpos_s + min(max(base + lane + 32, 0), hi_idx), acc_hi);
         }
         // P^T / dS^T overwrite S^T / dP^T columns that OTHER warps of this lane quarter read: wait until all
         // four column groups of the quarter have their chunks in registers (bounded, like every wait here)
@@ -290,7 +351,6 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           *reinterpret_cast<uint4*>(dst + u * 16) = make_uint4(dk16[4 * v4], dk16[4 * v4 + 1], dk16[4 * v4 + 2], dk16[4 * v4 + 3]);
         }
       }
-      if (want_dts && run_bucket >= 0 && run_sum != 0.f) atomicAdd(dtsw_s + run_bucket, run_sum);
       rb::tmem_st_wait();
       fence_async_smem();
       rb::tc_fence_before();
@@ -316,6 +376,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       rb::tc_fence_before();
       rb::mbar_arrive(dq_empty);
     }
+    if (WDT && run_bucket >= 0 && run_sum != 0.f) atomicAdd(dtsw_s + run_bucket, run_sum);
     {
       bool ok = rb::mbar_wait(dkv_full, 0, abort_flag, p.status);
       if (!__all_sync(0xffffffffu, ok)) goto done;
@@ -379,6 +440,18 @@ int make_map(CUtensorMap* m, const void* base, long long rows, long long cols, l
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -2;
 }
 
+template <bool BT, bool BP, bool WDT, bool WDP>
+int launch_bwd(dim3 grid, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+               const HstuBwdParams& p, cudaStream_t st) {
+  static bool set = false;
+  if (!set) {
+    RB_CUDA_CHECK(cudaFuncSetAttribute(hstu_bwd_kernel<BT, BP, WDT, WDP>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    set = true;
+  }
+  hstu_bwd_kernel<BT, BP, WDT, WDP><<<grid, 640, SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace
 
 // q, dO [Tq][ld_q / ld_do], k, v [Tk][ld_k] bf16 with head h at columns h*64.  dq32 is an fp32 accumulator the
@@ -404,12 +477,24 @@ RB_API int rb_hstu_attn_bwd(const void* q, long long ld_q, const void* dout, lon
   if ((rc = make_map(&tdo, dout, Tq, static_cast<long long>(H) * D, ld_do))) return rc;
   if ((rc = make_map(&tk, k, Tk, static_cast<long long>(H) * D, ld_k))) return rc;
   if ((rc = make_map(&tv, v, Tk, static_cast<long long>(H) * D, ld_k))) return rc;
-  static bool set = false;
-  if (!set) {
-    RB_CUDA_CHECK(cudaFuncSetAttribute(hstu_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    set = true;
+  {
+    const int hi = static_cast<int>(38.787f / p.ts_divisor);         // log(7e16) / divisor
+    p.bucket_cap = num_buckets < hi ? num_buckets : hi;
   }
   dim3 grid((max_len_k + BKV - 1) / BKV, B * H);
-  hstu_bwd_kernel<<<grid, 640, SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-  return static_cast<int>(cudaGetLastError());
+  const bool bt = ts != nullptr && ts_w != nullptr, bp = pos_w != nullptr;
+  const int vt = !bt ? 0 : (d_ts_w ? 2 : 1), vp = !bp ? 0 : (d_pos_w ? 2 : 1);
+#define RB_BWD(BT_, WDT_, BP_, WDP_) return launch_bwd<BT_, BP_, WDT_, WDP_>(grid, tq, tk, tv, tdo, p, st)
+  switch (vt * 3 + vp) {
+    case 0: RB_BWD(false, false, false, false);
+    case 1: RB_BWD(false, false, true, false);
+    case 2: RB_BWD(false, false, true, true);
+    case 3: RB_BWD(true, false, false, false);
+    case 4: RB_BWD(true, false, true, false);
+    case 5: RB_BWD(true, false, true, true);
+    case 6: RB_BWD(true, true, false, false);
+    case 7: RB_BWD(true, true, true, false);
+    default: RB_BWD(true, true, true, true);
+  }
+#undef RB_BWD
 }

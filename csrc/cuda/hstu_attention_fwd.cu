@@ -42,6 +42,7 @@ struct HstuFwdParams {
   // paged K/V
   const int* page_ids; const int* page_indptr; int page_size;
   int box_rows;              // rows per TMA box for K/V (64, or page_size when smaller)
+  int bucket_cap;            // min(num_buckets, floor(log(7e16) / divisor)): replaces the clamp of |dt| from above
   int* status;
 };
 
@@ -49,14 +50,8 @@ template <int D> struct FwdCfg {
   static constexpr int CH = D / 64;                       // 64-column swizzle chunks per row
   static constexpr int TILE_BYTES = BQ * 128 * CH;        // one Q, K or V tile
   static constexpr int STAGES = (D == 64) ? 3 : 2;
-  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 6144 + 1024;
+  static constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * STAGES) + 6144 + 4096 + 1024;
 };
-
-__device__ __forceinline__ float silu_fast(float x) {
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
-  return x * (0.5f * t + 0.5f);
-}
 
 // mask of (query position pi, key position j) inside a sequence of len keys
 __device__ __forceinline__ bool attends(int pi, int j, int len, int causal, int nctx, int ntgt, int gs) {
@@ -71,7 +66,40 @@ __device__ __forceinline__ bool attends(int pi, int j, int len, int causal, int 
   return ok;
 }
 
-template <int D>
+
+// One warp's 32 x 32 chunk of S -> P.  Thread = query row, e = key column of the chunk.
+//   bias_t : tsw[min(int(log2(max(|ts_i - ts_j|, 1)) * k_log), cap)]      (k_log = ln 2 / divisor)
+//   bias_p : window[lane + 31 - e], the warp's pre-clamped slice of pos_w (distance = pi - j)
+//   silu(alpha x) * scale = hs + hs * tanh(h),  h = x * alpha / 2,  hs = h * scale
+template <bool BT, bool BP, bool MASKED>
+__device__ __forceinline__ void activate_chunk(const uint32_t (&r)[32], uint32_t (&pk)[16], float ts_i, const float* my_ts,
+                                               const float* tsw_s, const float* my_pos, int lane, float k_log, int cap,
+                                               float half_alpha, float scale, int pi, int j0, int len_k, int causal,
+                                               int nctx, int ntgt, int gs) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    float v2[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      float x = __uint_as_float(r[e + q]);
+      if (BT) {
+        const float a = fmaxf(fabsf(ts_i - my_ts[e + q]), 1.f);
+        x += tsw_s[min(static_cast<int>(__log2f(a) * k_log), cap)];
+      }
+      if (BP) x += my_pos[lane + 31 - (e + q)];
+      const float h = x * half_alpha;
+      float t;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+      const float hs = h * scale;
+      x = fmaf(hs, t, hs);
+      if (MASKED && !attends(pi, j0 + e + q, len_k, causal, nctx, ntgt, gs)) x = 0.f;
+      v2[q] = x;
+    }
+    pk[e >> 1] = rb::pack_bf16(v2[0], v2[1]);
+  }
+}
+
+template <int D, bool BT, bool BP>
 __global__ void __launch_bounds__(640, 1)
 hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const HstuFwdParams p) {
@@ -112,6 +140,7 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* tail = kv_s + 2 * C::STAGES * C::TILE_BYTES;
   float* ts_s = reinterpret_cast<float*>(tail);                     // [4 warps][2][128] key timestamps
   float* tsw_s = ts_s + 1024;                                       // [<= 192] time-bucket weights
+  float* pos_s = reinterpret_cast<float*>(tail + 6144);             // [16 warps][64] distance-bias windows
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 5120);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;
@@ -133,7 +162,7 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     rb::mbar_fence_init();
   }
   if (warp == 2) { rb::tmem_alloc(tmem_slot, 512); rb::tmem_relinquish(); }
-  if (p.ts_w) for (int i = threadIdx.x; i <= p.num_buckets && i < 192; i += blockDim.x) tsw_s[i] = p.ts_w[i];
+  if (BT) for (int i = threadIdx.x; i <= p.num_buckets && i < 192; i += blockDim.x) tsw_s[i] = p.ts_w[i];
   rb::tc_fence_before();
   __syncthreads();
   rb::tc_fence_after();
@@ -222,16 +251,32 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int i_local = qblk * BQ + row;
     const int pi = i_local + delta;
     const uint32_t lane_sel = static_cast<uint32_t>(ew * 32) << 16;
-    const bool has_bias_t = p.ts != nullptr && p.ts_w != nullptr;
-    const bool has_bias_p = p.pos_w != nullptr;
-    const float ts_i = has_bias_t ? p.ts[k_start + min(pi, len_k - 1)] : 0.f;
-    const float inv_div = 1.f / p.ts_divisor;
+    const float ts_i = BT ? p.ts[k_start + min(pi, len_k - 1)] : 0.f;
+    const float k_log = 0.69314718f / p.ts_divisor;
+    const float half_alpha = 0.5f * p.alpha;
+    const int pi0 = qblk * BQ + ew * 32 + delta;                      // key position of this warp's first row
+    float* my_pos = pos_s + (warp - 4) * 64;
+    // operands of the next iteration are fetched one iteration ahead so their latency hides behind the math
+    auto load_ts = [&](int t) -> float {
+      const int j = kb_of(t) * BKV + grp * 32 + lane;
+      return (t < n_iter && j < len_k) ? __ldg(p.ts + k_start + j) : 0.f;
+    };
+    auto load_pos = [&](int t, int w) -> float {
+      const int d = pi0 - (kb_of(t) * BKV + grp * 32) - 31 + w;
+      return t < n_iter ? __ldg(p.pos_w + min(max(d, 0), p.pos_len - 1)) : 0.f;
+    };
+    float ts_nxt = BT ? load_ts(0) : 0.f;
+    float pos_nxt0 = BP ? load_pos(0, lane) : 0.f, pos_nxt1 = BP ? load_pos(0, lane + 32) : 0.f;
     for (int t = 0; t < n_iter; ++t) {
       const int kb = kb_of(t), buf = t & 1;
       float* my_ts = ts_s + ((warp - 4) * 2 + buf) * 32;            // private to this warp: no CTA-level sync
-      if (has_bias_t) {
-        const int j = kb * BKV + grp * 32 + lane;
-        my_ts[lane] = j < len_k ? __ldg(p.ts + k_start + j) : 0.f;
+      if (BT || BP) {
+        __syncwarp();
+        if (BT) { my_ts[lane] = ts_nxt; ts_nxt = load_ts(t + 1); }
+        if (BP) {
+          my_pos[lane] = pos_nxt0; my_pos[lane + 32] = pos_nxt1;
+          pos_nxt0 = load_pos(t + 1, lane); pos_nxt1 = load_pos(t + 1, lane + 32);
+        }
         __syncwarp();
       }
       bool ok = rb::mbar_wait(&s_full[buf], (t >> 1) & 1, abort_flag, p.status);
@@ -246,26 +291,13 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         rb::tmem_ld_32x32(T_S + buf * 128 + lane_sel + c * 32, r);
         rb::tmem_ld_wait();
         uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float v2[2];
-#pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const int jl = c * 32 + e + q;
-            const int j = kb * BKV + jl;
-            float x = __uint_as_float(r[e + q]);
-            if (has_bias_t) {
-              const float a = fminf(fmaxf(fabsf(ts_i - my_ts[e + q]), 1.f), 7.0e16f);
-              const int bk = min(max(static_cast<int>(__logf(a) * inv_div), 0), p.num_buckets);
-              x += tsw_s[bk];
-            }
-            if (has_bias_p) x += __ldg(p.pos_w + min(max(pi - j, 0), p.pos_len - 1));
-            x = silu_fast(x * p.alpha) * p.scale;
-            if (!full && !attends(pi, j, len_k, p.causal, nctx, ntgt, gs)) x = 0.f;
-            v2[q] = x;
-          }
-          pk[e >> 1] = rb::pack_bf16(v2[0], v2[1]);
-        }
+        const int j0 = kb * BKV + c * 32;
+        if (full)
+          activate_chunk<BT, BP, false>(r, pk, ts_i, my_ts, tsw_s, my_pos, lane, k_log, p.bucket_cap, half_alpha, p.scale, pi, j0,
+                                        len_k, p.causal, nctx, ntgt, gs);
+        else
+          activate_chunk<BT, BP, true>(r, pk, ts_i, my_ts, tsw_s, my_pos, lane, k_log, p.bucket_cap, half_alpha, p.scale, pi, j0,
+                                       len_k, p.causal, nctx, ntgt, gs);
         rb::tmem_st_32x16(T_P + buf * 64 + lane_sel + c * 16, pk);
       }
       rb::tmem_st_wait();
@@ -327,17 +359,17 @@ int make_map(CUtensorMap* m, const void* base, long long rows, long long cols, l
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -2;
 }
 
-template <int D>
+template <int D, bool BT, bool BP>
 int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const HstuFwdParams& p,
                int max_qblocks, cudaStream_t st) {
   using C = FwdCfg<D>;
   static bool set = false;
   if (!set) {
-    RB_CUDA_CHECK(cudaFuncSetAttribute(hstu_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    RB_CUDA_CHECK(cudaFuncSetAttribute(hstu_fwd_kernel<D, BT, BP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     set = true;
   }
   dim3 grid(max_qblocks, p.B * p.H);
-  hstu_fwd_kernel<D><<<grid, 640, C::SMEM_BYTES, st>>>(tq, tk, tv, p);
+  hstu_fwd_kernel<D, BT, BP><<<grid, 640, C::SMEM_BYTES, st>>>(tq, tk, tv, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -361,6 +393,10 @@ RB_API int rb_hstu_attn_fwd(const void* q, long long ld_q, long long Tq, const v
   p.alpha = alpha; p.scale = scale; p.causal = causal; p.num_context = num_context; p.num_target = num_target;
   p.target_group_size = target_group_size; p.ts = ts; p.ts_w = ts_w; p.num_buckets = num_buckets;
   p.ts_divisor = ts_divisor > 0.f ? ts_divisor : 1.f; p.pos_w = pos_w; p.pos_len = pos_len;
+  {
+    const int hi = static_cast<int>(38.787f / p.ts_divisor);         // log(7e16) / divisor
+    p.bucket_cap = num_buckets < hi ? num_buckets : hi;
+  }
   p.page_ids = page_ids; p.page_indptr = page_indptr; p.page_size = page_size; p.status = status;
   CUtensorMap tq, tk, tv;
   int rc = make_map(&tq, q, Tq, static_cast<long long>(H) * D, ld_q, 64);
@@ -380,6 +416,13 @@ RB_API int rb_hstu_attn_fwd(const void* q, long long ld_q, long long Tq, const v
     if (rc) return rc;
   }
   const int max_qblocks = (max_len_q + BQ - 1) / BQ;
-  if (D == 64) return launch_fwd<64>(tq, tk, tv, p, max_qblocks, st);
-  return launch_fwd<128>(tq, tk, tv, p, max_qblocks, st);
+  const bool bt = ts != nullptr && ts_w != nullptr, bp = pos_w != nullptr;
+#define RB_FWD(DD)                                                                  \
+  (bt ? (bp ? launch_fwd<DD, true, true>(tq, tk, tv, p, max_qblocks, st)            \
+            : launch_fwd<DD, true, false>(tq, tk, tv, p, max_qblocks, st))          \
+      : (bp ? launch_fwd<DD, false, true>(tq, tk, tv, p, max_qblocks, st)           \
+            : launch_fwd<DD, false, false>(tq, tk, tv, p, max_qblocks, st)))
+  if (D == 64) return RB_FWD(64);
+  return RB_FWD(128);
+#undef RB_FWD
 }

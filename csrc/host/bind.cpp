@@ -289,6 +289,9 @@ PYBIND11_MODULE(_C_host, m) {
       })
       .def("get_key", [](EmbcacheManager& mg, size_t t, int64_t off, int64_t version) { return mg.swap_manager(t).get_key(off, version); })
       .def("host_size", [](EmbcacheManager& mg, size_t t) { return mg.host_table(t).size(); })
+      .def("invalidate_cache", &EmbcacheManager::invalidate_cache)
+      .def("cache_capacity", [](EmbcacheManager& mg, size_t t) { return mg.swap_manager(t).capacity(); })
+      .def("cache_size", [](EmbcacheManager& mg, size_t t) { return mg.swap_manager(t).size(); })
       .def("host_export", [](EmbcacheManager& mg, size_t t) {
         std::vector<int64_t> k;
         std::vector<float> r;

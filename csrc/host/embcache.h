@@ -500,6 +500,12 @@ class EmbcacheManager {
     tb.host.erase(ev.data(), static_cast<int64_t>(ev.size()));
     return ev;
   }
+  // forget every device-resident row of table t without writing it back (after a checkpoint load)
+  void invalidate_cache(size_t t) {
+    std::vector<int64_t> k, o;
+    tables_.at(t)->swap.resident(k, o);
+    tables_.at(t)->swap.remove_keys(k.data(), static_cast<int64_t>(k.size()));
+  }
   SwapManager& swap_manager(size_t t) { return tables_.at(t)->swap; }
   HostEmbTable& host_table(size_t t) { return tables_.at(t)->host; }
   FeatureFilter& feature_filter(size_t t) { return tables_.at(t)->filter; }

@@ -1,0 +1,11 @@
+"""Multi-tier embedding tables: device-memory cache of hot rows over a host-DRAM table, admission / eviction."""
+from .configs import (POLICY_COUNT, POLICY_SHOW_CLICK, AdmitAndEvictConfig, EmbCacheEmbeddingBagConfig, EmbCacheEmbeddingConfig,
+                      InitializerType, ShowClickParams)
+from .embedding_bag import (EmbCacheEmbeddingBagCollection, EmbCacheEmbeddingBagCollectionSharder,
+                            EmbCacheShardedEmbeddingBagCollection, calculate_caches)
+from .saver import Saver
+from .train_pipeline import EmbCacheTrainPipelineSparseDist
+
+__all__ = ["POLICY_COUNT", "POLICY_SHOW_CLICK", "AdmitAndEvictConfig", "EmbCacheEmbeddingBagConfig", "EmbCacheEmbeddingConfig",
+           "InitializerType", "ShowClickParams", "EmbCacheEmbeddingBagCollection", "EmbCacheEmbeddingBagCollectionSharder",
+           "EmbCacheShardedEmbeddingBagCollection", "calculate_caches", "Saver", "EmbCacheTrainPipelineSparseDist"]

@@ -1,0 +1,319 @@
+"""Multi-tier embedding collections: the full table lives in host DRAM (native ``EmbcacheManager``), a cache of
+hot rows (weights and optimizer state) lives in device memory, and every step swaps the rows the batch needs in
+and the least recently needed ones out.
+
+``EmbCacheEmbeddingBagCollection`` / ``EmbCacheEmbeddingCollection`` are the unsharded declarations (they size the
+device cache); ``EmbCacheShardedEmbeddingBagCollection`` does the work: row-wise (``id % world``) input
+distribution, per-table swap planning on the native thread pool, gather of victims / scatter of incoming rows on
+the device, pooled lookup over the cache with the sparse update applied in backward, and pooled output
+distribution.  Keys that the admission filter rejects read slot 0, which holds ``not_admitted_default_value`` and
+is never trained.  Reference: ``torchrec_embcache/distributed/embedding_bag.py:171-337`` (cache sizing
+``:308-337``), ``:340-850``; ``embedding.py:587-625`` (not-admitted ids); swap stages
+``train_pipeline.py:424-537``.
+"""
+from __future__ import annotations
+
+import os
+import time
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+from torch import nn
+
+from ..host import host
+from ..modules.embedding_configs import PoolingType
+from ..ops import embedding_ops as E
+from ..parallel.collective_embeddingbag import CollectiveShardedEmbeddingBagCollection
+from ..parallel.comm import ShardingEnv
+from ..parallel.embeddingbag import ParameterSharding
+from ..sparse.jagged_tensor import KeyedJaggedTensor, KeyedTensor
+from .configs import POLICY_SHOW_CLICK, EmbCacheEmbeddingBagConfig, InitializerType
+
+DEFAULT_CACHE_BYTES = 16 << 30
+MAX_CACHE_BYTES = 64 << 30
+
+_OPTIM_NUM = {E.OPT_SGD: 0, E.OPT_ADAGRAD: 1, E.OPT_ADAM: 2}
+
+
+def _cache_budget_bytes() -> int:
+    try:
+        v = int(os.environ.get("EMBCACHE_SIZE_ON_DEVICE_MEM", DEFAULT_CACHE_BYTES))
+    except ValueError:
+        v = DEFAULT_CACHE_BYTES
+    return max(1, min(v, MAX_CACHE_BYTES))
+
+
+def calculate_caches(tables: Sequence, world_size: int, batch_size: int, multi_hot_sizes: Sequence[int], optim_num: int
+                     ) -> List[int]:
+    """Device-cache rows per table.  The floor is what two in-flight batches can touch
+    (``hot * 2 * batch * world`` rows); the device budget (``EMBCACHE_SIZE_ON_DEVICE_MEM``, default 16 GiB, at most
+    64 GiB) scales every table by the same factor above that floor, never beyond the table itself."""
+    floor_rows = [max(1, int(h)) * 2 * batch_size * world_size for h in multi_hot_sizes]
+    min_bytes = sum(r * t.embedding_dim * 4 * (optim_num + 1) for r, t in zip(floor_rows, tables))
+    scale = max(1.0, _cache_budget_bytes() / max(min_bytes, 1))
+    return [int(min(t.num_embeddings + 1, max(r, int(r * scale)))) for r, t in zip(floor_rows, tables)]
+
+
+class EmbCacheEmbeddingBagCollection(nn.Module):
+    """Unsharded declaration: validates the tables and computes the device-cache sizes.  ``forward`` exists for
+    single-process use (it builds a world-size-1 sharded module on first call)."""
+
+    def __init__(self, tables: List[EmbCacheEmbeddingBagConfig], world_size: int, batch_size: int, multi_hot_sizes: List[int],
+                 is_weighted: bool = False, need_accumulate_offset: bool = True, device=None,
+                 embedding_optimizer_cls=torch.optim.Adagrad) -> None:
+        super().__init__()
+        if is_weighted:
+            raise ValueError("weighted embcache tables are not supported")
+        if len(multi_hot_sizes) != len(tables):
+            raise ValueError("multi_hot_sizes needs one entry per table")
+        names = [t.name for t in tables]
+        if len(set(names)) != len(names):
+            raise ValueError("duplicate table names")
+        for t in tables:
+            if t.embedding_dim % 8 or not (8 <= t.embedding_dim <= 4096):
+                raise ValueError("embedding_dim must be a multiple of 8 in [8, 4096]")
+        self.tables, self.world_size, self.batch_size = list(tables), world_size, batch_size
+        self.multi_hot_sizes = list(multi_hot_sizes)
+        self.need_accumulate_offset = need_accumulate_offset
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self.embedding_optimizer_cls = embedding_optimizer_cls
+        self._sharded: Optional[EmbCacheShardedEmbeddingBagCollection] = None
+
+    def embedding_bag_configs(self):
+        return self.tables
+
+    def is_weighted(self) -> bool:
+        return False
+
+    def optimizer_spec(self, **kw) -> E.OptimizerSpec:
+        kind = {torch.optim.SGD: E.OPT_SGD, torch.optim.Adagrad: E.OPT_ADAGRAD, torch.optim.Adam: E.OPT_ADAM}.get(
+            self.embedding_optimizer_cls)
+        if kind is None:
+            raise ValueError("embcache tables train with SGD, Adagrad or Adam")
+        return E.OptimizerSpec(kind=kind, **kw)
+
+    def cache_rows(self, optim_num: int) -> List[int]:
+        return calculate_caches(self.tables, self.world_size, self.batch_size, self.multi_hot_sizes, optim_num)
+
+    def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
+        if self._sharded is None:
+            self._sharded = EmbCacheShardedEmbeddingBagCollection(self, ShardingEnv(1, 0, None), self.device, self.optimizer_spec())
+        return self._sharded(features)
+
+
+class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollection):
+    def __init__(self, module: EmbCacheEmbeddingBagCollection, env: ShardingEnv, device, optimizer_spec: Optional[E.OptimizerSpec] = None,
+                 cache_rows: Optional[List[int]] = None, threads: int = 4) -> None:
+        spec = optimizer_spec or module.optimizer_spec()
+        if spec.kind not in _OPTIM_NUM:
+            raise ValueError("embcache tables train with SGD, Adagrad or Adam")
+        self.optim_num = _OPTIM_NUM[spec.kind]
+        rows = cache_rows or module.cache_rows(self.optim_num)
+        # the parent allocates one weight tensor per table with `local_rows` rows: make that the cache size
+        import copy
+
+        cache_tables = []
+        for t, r in zip(module.tables, rows):
+            c = copy.copy(t)
+            c.num_embeddings = int(r) * env.world_size                 # row-wise split -> r rows on this rank
+            cache_tables.append(c)
+        plan = {t.name: ParameterSharding("row_wise", row_partition="mod") for t in module.tables}
+        super().__init__(cache_tables, plan, env, torch.device(device), spec, hashed=True, init_weights=False)
+        self.mappers = None
+        self.full_tables = list(module.tables)
+        self.cache_rows_per_table = [int(r) for r in rows]
+        cfgs = []
+        for t, r in zip(module.tables, rows):
+            c = host().EmbConfig()
+            c.table_name, c.emb_dim, c.optim_num, c.cache_size = t.name, t.embedding_dim, self.optim_num, int(r)
+            ic = host().InitializerConfig()
+            it = getattr(t, "initializer_type", InitializerType.LINEAR)
+            ic.type = {InitializerType.LINEAR: host().InitializerType.LINEAR,
+                       InitializerType.TRUNCATED_NORMAL: host().InitializerType.TRUNCATED_NORMAL,
+                       InitializerType.UNIFORM: host().InitializerType.UNIFORM}[it]
+            ic.min, ic.max = t.get_weight_init_min(), t.get_weight_init_max()
+            ic.mean, ic.stddev = getattr(t, "weight_init_mean", 0.0), getattr(t, "weight_init_stddev", 0.05)
+            ic.seed = 1234 + env.rank
+            c.init = ic
+            ae = getattr(t, "admit_and_evict_config", None)
+            if ae is not None:
+                a = host().AdmitEvictConfig()
+                a.admit_threshold, a.evict_threshold = ae.admit_threshold, ae.evict_threshold
+                a.policy = 1 if ae.policy_type == POLICY_SHOW_CLICK else 0
+                p = ae.show_click_params
+                a.alpha, a.beta, a.sc_admit_threshold = p.alpha, p.beta, p.admit_threshold
+                a.evict_percentage, a.score_decay = p.evict_percentage, p.score_decay
+                c.admit_evict = a
+            c.is_incremental = bool(getattr(t, "is_incremental", False))
+            cfgs.append(c)
+        self.manager = host().EmbcacheManager(cfgs, threads)
+        self.admit = [bool(getattr(t, "admit_and_evict_config", None) and t.admit_and_evict_config.is_admit_enabled())
+                      for t in module.tables]
+        self.evict = [bool(getattr(t, "admit_and_evict_config", None) and t.admit_and_evict_config.is_evict_enabled())
+                      for t in module.tables]
+        self.default_value = [getattr(getattr(t, "admit_and_evict_config", None), "not_admitted_default_value", 0.0)
+                              for t in module.tables]
+        self.swap_step = 0
+        self.stats = {"swap_in": 0, "swap_out": 0}
+        self._prepared: Dict[int, tuple] = {}                  # id(features) -> context made ahead of time
+        self._swap_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        with torch.no_grad():
+            for ti, t in enumerate(self.tables):
+                self.embedding_bags[t.name].weight.zero_()
+
+    # -- state rows <-> host rows ------------------------------------------------------------------------
+    def _gather_cache_rows(self, ti: int, offs: torch.Tensor) -> torch.Tensor:
+        w = self.embedding_bags[self.tables[ti].name].weight.data
+        parts = [E.gather_rows(w, offs)]
+        st = self.state[ti]
+        for k in ("state1", "state2")[: self.optim_num]:
+            parts.append(E.gather_rows(st[k], offs))
+        return torch.cat(parts, dim=1) if len(parts) > 1 else parts[0]
+
+    def _scatter_cache_rows(self, ti: int, offs: torch.Tensor, rows: torch.Tensor) -> None:
+        D = self.tables[ti].embedding_dim
+        w = self.embedding_bags[self.tables[ti].name].weight.data
+        E.scatter_rows(rows[:, :D].contiguous(), offs, w)
+        st = self.state[ti]
+        for j, k in enumerate(("state1", "state2")[: self.optim_num]):
+            E.scatter_rows(rows[:, (j + 1) * D:(j + 2) * D].contiguous(), offs, st[k])
+
+    # -- the swap ----------------------------------------------------------------------------------------
+    def compute_swap_info_async(self, ti: int, keys: np.ndarray):
+        return self.manager.compute_swap_info_async(ti, keys, self.swap_step)
+
+    def apply_swap(self, ti: int, info: Dict[str, np.ndarray]) -> None:
+        """Victims device -> host, incoming rows host -> device."""
+        dev = self.device
+        so_k, so_o = info["swapout_keys"], info["swapout_offs"]
+        if so_k.size:
+            rows = self._gather_cache_rows(ti, torch.from_numpy(so_o).to(dev))
+            self.manager.embedding_update(ti, so_k, rows.float().cpu().numpy())
+            self.stats["swap_out"] += int(so_k.size)
+        si_k, si_o = info["swapin_keys"], info["swapin_offs"]
+        if si_k.size:
+            rows = torch.from_numpy(self.manager.embedding_lookup(ti, si_k))
+            if dev.type == "cuda":
+                rows = rows.pin_memory().to(dev, non_blocking=True)
+            self._scatter_cache_rows(ti, torch.from_numpy(si_o).to(dev), rows)
+            self.stats["swap_in"] += int(si_k.size)
+        if self.admit[ti]:
+            w = self.embedding_bags[self.tables[ti].name].weight.data
+            w[0].fill_(self.default_value[ti])
+
+    def post_input_dist(self, lengths: torch.Tensor, ids: torch.Tensor):
+        """Raw ids (this rank's share of the global batch) -> device-cache slots."""
+        self.swap_step += 1
+        W, F, B = lengths.shape
+        seg = lengths.sum(dim=2).reshape(-1).cpu().numpy()
+        seg_off = np.concatenate([[0], np.cumsum(seg)])
+        ids_np = ids.cpu().numpy().astype(np.int64)
+        tab_pos: List[List[np.ndarray]] = [[] for _ in self.tables]
+        for s in range(W):
+            for f in range(F):
+                tab_pos[self.feature_table[f]].append(np.arange(seg_off[s * F + f], seg_off[s * F + f + 1]))
+        pos = [np.concatenate(p) if p else np.zeros(0, dtype=np.int64) for p in tab_pos]
+        now = int(time.time())
+        futs = []
+        for ti, p in enumerate(pos):
+            keys = ids_np[p]
+            if self.admit[ti] or self.evict[ti]:
+                uk, cnt = np.unique(keys, return_counts=True)
+                if self.admit[ti]:
+                    self.manager.statistics_key_count(ti, uk, cnt.astype(np.int64), None)
+                if self.evict[ti]:
+                    self.manager.record_timestamp(ti, uk, np.full(uk.shape, now, dtype=np.int64))
+            futs.append(self.compute_swap_info_async(ti, keys))
+        out = np.empty_like(ids_np)
+        for ti, p in enumerate(pos):
+            info = futs[ti].get()
+            self.apply_swap(ti, info)
+            out[p] = info["batch_offs"]
+        return torch.from_numpy(out).to(ids.device)
+
+    # -- pipelining ------------------------------------------------------------------------------------------
+    def prefetch(self, features: KeyedJaggedTensor) -> None:
+        """Input distribution and the whole swap for a batch that will be consumed later.  Safe while the previous
+        batch is still in flight: the swap manager never hands out slots that the current or previous batch use.
+        Device work runs on the module's swap stream; ``forward`` makes the compute stream wait for it."""
+        if self._swap_stream is not None:
+            self._swap_stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self._swap_stream):
+                ctx = self._prepare(features)
+                ev = torch.cuda.Event()
+                ev.record(self._swap_stream)
+        else:
+            ctx, ev = self._prepare(features), None
+        self._prepared[id(features)] = ctx + (ev,)
+
+    def _prepare(self, features: KeyedJaggedTensor):
+        lengths, ids, B = self.input_dist(features)
+        slots = self.post_input_dist(lengths, ids)
+        orig = features.lengths().view(len(self.feature_names), B).to(self.device)
+        return lengths, slots, B, orig
+
+    def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
+        ctx = self._prepared.pop(id(features), None)
+        if ctx is None:
+            lengths, slots, B, orig = self._prepare(features)
+        else:
+            lengths, slots, B, orig, ev = ctx
+            if ev is not None:
+                torch.cuda.current_stream(self.device).wait_event(ev)
+        return self.compute_and_output_dist(lengths, slots, B, orig)
+
+    def _apply_update(self, ti: int, rows: torch.Tensor, grads: torch.Tensor) -> None:
+        if self.admit[ti]:                                   # slot 0 = "not admitted": never trained
+            keep = rows != 0
+            rows, grads = rows[keep], grads[keep]
+        super()._apply_update(ti, rows, grads)
+
+    # -- eviction / checkpoint helpers -------------------------------------------------------------------
+    def host_embedding_evict(self) -> Dict[str, int]:
+        out = {}
+        for ti, t in enumerate(self.full_tables):
+            if self.evict[ti]:
+                out[t.name] = int(self.manager.evict_features(ti).size)
+        return out
+
+    @torch.no_grad()
+    def embedding_to_host(self) -> None:
+        """Write every device-resident row back to the host table (before a save)."""
+        for ti in range(len(self.tables)):
+            keys, offs = self.manager.resident(ti)
+            if keys.size:
+                rows = self._gather_cache_rows(ti, torch.from_numpy(offs).to(self.device))
+                self.manager.embedding_update(ti, keys, rows.float().cpu().numpy())
+
+    def invalidate_device_cache(self) -> None:
+        for ti in range(len(self.tables)):
+            self.manager.invalidate_cache(ti)
+
+    def host_rows(self, name: str, keys: Sequence[int]) -> torch.Tensor:
+        """Current value ``[len(keys), dim * (1 + optim_num)]`` of rows wherever they live (device cache first)."""
+        ti = [t.name for t in self.full_tables].index(name)
+        self.embedding_to_host()
+        return torch.from_numpy(self.manager.embedding_lookup(ti, np.asarray(keys, dtype=np.int64)))
+
+
+class EmbCacheEmbeddingBagCollectionSharder:
+    """``shard(module, env, device)`` -> sharded module; row-wise is the only sharding
+    (reference ``sharding/embedding_sharder.py:70-132``)."""
+
+    def __init__(self, cpu_device=None, cpu_env: Optional[ShardingEnv] = None, npu_device=None, npu_env: Optional[ShardingEnv] = None,
+                 fused_params: Optional[dict] = None, qcomm_codecs_registry=None) -> None:
+        self.cpu_device, self.cpu_env, self.device, self.env = cpu_device, cpu_env, npu_device, npu_env
+        self.fused_params = dict(fused_params or {})
+
+    def sharding_types(self, compute_device_type: str = "cuda") -> List[str]:
+        return ["row_wise"]
+
+    @property
+    def module_type(self):
+        return EmbCacheEmbeddingBagCollection
+
+    def shard(self, module: EmbCacheEmbeddingBagCollection, params=None, env: Optional[ShardingEnv] = None, device=None):
+        spec = module.optimizer_spec(**{k: v for k, v in self.fused_params.items() if k in ("lr", "eps", "beta1", "beta2", "weight_decay")})
+        return EmbCacheShardedEmbeddingBagCollection(module, env or self.env or ShardingEnv(1, 0, None),
+                                                     device or self.device or module.device, spec)

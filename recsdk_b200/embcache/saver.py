@@ -1,0 +1,99 @@
+"""Checkpointing of multi-tier tables: every rank flushes its device cache to the host table and writes its
+keys / embeddings / optimizer state / filter state under ``<dir>/<table>/rank<r>/``; after a barrier rank 0
+merges the rank directories into one file set per table and writes ``meta.ini``; loading re-shards by
+``key % world_size`` so the world size may change between save and load.  Incremental saves hold only the keys
+touched since the previous save.  Reference: ``torchrec_embcache/saver.py:31-171``; file layout
+``csrc/embedding_cache/embcache_manager.cpp:549-618`` (save), ``:620-800`` (merge), ``:905-981`` (load).
+"""
+from __future__ import annotations
+
+import configparser
+import os
+import shutil
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .train_pipeline import embcache_modules
+
+META = "meta.ini"
+
+
+class Saver:
+    def __init__(self, process_group=None) -> None:
+        self.pg = process_group
+
+    def _world(self):
+        if dist.is_available() and dist.is_initialized():
+            return dist.get_world_size(self.pg), dist.get_rank(self.pg)
+        return 1, 0
+
+    def _barrier(self) -> None:
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier(group=self.pg)
+
+    def save(self, module: torch.nn.Module, path: str, incremental: bool = False) -> str:
+        world, rank = self._world()
+        mods = embcache_modules(module)
+        if not mods:
+            raise ValueError("module holds no embcache tables")
+        step = max(m.swap_step for m in mods)
+        out = os.path.join(path, "%s_%010d" % ("incremental" if incremental else "full", step))
+        if rank == 0:
+            os.makedirs(out, exist_ok=True)
+        self._barrier()
+        for m in mods:
+            m.embedding_to_host()
+            m.manager.save(out, rank, incremental)
+        self._barrier()
+        if rank == 0:
+            tables: List[str] = []
+            for m in mods:
+                m.manager.merge_files(out, world)
+                for t in m.full_tables:
+                    tables.append(t.name)
+                    for r in range(world):
+                        shutil.rmtree(os.path.join(out, t.name, "rank%d" % r), ignore_errors=True)
+            cp = configparser.ConfigParser()
+            cp["meta"] = {"world_size": str(world), "step": str(step), "incremental": str(int(incremental)),
+                          "tables": ",".join(tables)}
+            with open(os.path.join(out, META), "w") as f:
+                cp.write(f)
+        self._barrier()
+        return out
+
+    def load(self, module: torch.nn.Module, path: str, incremental: bool = False) -> None:
+        world, rank = self._world()
+        if not os.path.exists(os.path.join(path, META)):
+            raise FileNotFoundError("%s has no %s: not a finished checkpoint" % (path, META))
+        cp = configparser.ConfigParser()
+        cp.read(os.path.join(path, META))
+        if bool(int(cp["meta"].get("incremental", "0"))) != incremental:
+            raise ValueError("checkpoint kind (full / incremental) does not match the request")
+        for m in embcache_modules(module):
+            if not incremental:
+                m.invalidate_device_cache()
+            else:
+                m.embedding_to_host()
+                m.invalidate_device_cache()
+            m.manager.load(path, rank, world)
+        self._barrier()
+
+    @staticmethod
+    def get_latest_load_path(path: str, incremental: Optional[bool] = None) -> Optional[str]:
+        best, best_step = None, -1
+        if not os.path.isdir(path):
+            return None
+        for d in os.listdir(path):
+            full = os.path.join(path, d)
+            if not os.path.exists(os.path.join(full, META)):
+                continue
+            cp = configparser.ConfigParser()
+            cp.read(os.path.join(full, META))
+            if incremental is not None and bool(int(cp["meta"].get("incremental", "0"))) != incremental:
+                continue
+            step = int(cp["meta"].get("step", "0"))
+            if step > best_step:
+                best, best_step = full, step
+        return best

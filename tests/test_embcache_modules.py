@@ -1,0 +1,116 @@
+"""Multi-tier tables: a tiny device cache over the host table must train exactly like a plain full table
+(rows migrate between tiers with their optimizer state), survive save / load, and honour admission."""
+import numpy as np
+import torch
+
+from recsdk_b200.embcache import (AdmitAndEvictConfig, EmbCacheEmbeddingBagCollection, EmbCacheEmbeddingBagConfig,
+                                  EmbCacheShardedEmbeddingBagCollection, EmbCacheTrainPipelineSparseDist, Saver)
+from recsdk_b200.ops import embedding_ops as E
+from recsdk_b200.parallel.comm import ShardingEnv
+from recsdk_b200.sparse.jagged_tensor import KeyedJaggedTensor
+
+
+def _tables(**kw):
+    return [EmbCacheEmbeddingBagConfig(num_embeddings=1000, embedding_dim=8, name="t0", feature_names=["f0"], **kw),
+            EmbCacheEmbeddingBagConfig(num_embeddings=500, embedding_dim=16, name="t1", feature_names=["f1", "f2"], **kw)]
+
+
+def _batch(g, B=6):
+    lens = torch.randint(1, 4, (3 * B,), generator=g)
+    vals = torch.randint(0, 60, (int(lens.sum()),), generator=g)
+    return KeyedJaggedTensor(["f0", "f1", "f2"], vals, lengths=lens)
+
+
+def _sharded(tables, cache_rows, opt=torch.optim.Adagrad, lr=0.1):
+    ebc = EmbCacheEmbeddingBagCollection(tables, 1, 6, [3, 3], device="cpu", embedding_optimizer_cls=opt)
+    return EmbCacheShardedEmbeddingBagCollection(ebc, ShardingEnv(1, 0, None), "cpu", ebc.optimizer_spec(lr=lr), cache_rows=cache_rows)
+
+
+def _train(m, steps, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(40, generator=torch.Generator().manual_seed(9))
+    losses = []
+    for _ in range(steps):
+        kt = m(_batch(g))
+        loss = (kt.values() * w).sum(dim=1).pow(2).mean()
+        loss.backward()
+        losses.append(float(loss))
+    return losses
+
+
+def test_small_cache_equals_big_cache():
+    for opt in (torch.optim.Adagrad, torch.optim.Adam, torch.optim.SGD):
+        small = _sharded(_tables(), [40, 64], opt)       # forces swaps every step (60 distinct ids, 2 features)
+        big = _sharded(_tables(), [1001, 501], opt)
+        la, lb = _train(small, 12), _train(big, 12)
+        assert np.allclose(la, lb, rtol=1e-5, atol=1e-6), (opt, la, lb)
+        assert small.stats["swap_out"] > 0 and big.stats["swap_out"] == 0
+        keys = list(range(60))
+        assert torch.allclose(small.host_rows("t1", keys), big.host_rows("t1", keys), atol=1e-6)
+
+
+def test_save_load_roundtrip(tmp_path):
+    m = _sharded(_tables(), [40, 64])
+    _train(m, 6)
+    saver = Saver()
+    out = saver.save(m, str(tmp_path))
+    assert Saver.get_latest_load_path(str(tmp_path)) == out
+    ref_rows = m.host_rows("t0", list(range(60))).clone()
+    m2 = _sharded(_tables(), [40, 64])
+    saver.load(m2, out)
+    assert torch.allclose(m2.host_rows("t0", list(range(60))), ref_rows)
+    # training continues identically after the reload
+    assert np.allclose(_train(m, 4, seed=5), _train(m2, 4, seed=5), rtol=1e-5)
+
+
+def test_admission_default_value_and_no_training():
+    ae = AdmitAndEvictConfig(admit_threshold=3, not_admitted_default_value=0.5)
+    m = _sharded(_tables(admit_and_evict_config=ae), [64, 64])
+    kjt = KeyedJaggedTensor(["f0", "f1", "f2"], torch.tensor([7, 8, 8]), lengths=torch.tensor([1, 1, 1]))
+    for step in range(4):
+        out = m(kjt).values()
+        out.sum().backward()
+        if step < 2:                                     # seen fewer than 3 times: the default row, untrained
+            assert torch.allclose(out[0, :8], torch.full((8,), 0.5))
+    assert not torch.allclose(m(kjt).values()[0, :8], torch.full((8,), 0.5))
+
+
+def test_pipeline_prefetch_matches_sync():
+    class Model(torch.nn.Module):
+        def __init__(self, emb):
+            super().__init__()
+            self.emb = emb
+            self.w = torch.nn.Parameter(torch.randn(40, generator=torch.Generator().manual_seed(9)))
+
+        def forward(self, batch):
+            loss = (self.emb(batch.sparse_features).values() * self.w).sum(dim=1).pow(2).mean()
+            return loss, loss.detach()
+
+    class B:
+        def __init__(self, k):
+            self.sparse_features = k
+
+        def to(self, device, non_blocking=False):
+            return self
+
+    def run(pipelined):
+        torch.manual_seed(0)
+        model = Model(_sharded(_tables(), [40, 64]))
+        opt = torch.optim.SGD([model.w], lr=0.01)
+        g = torch.Generator().manual_seed(3)
+        data = iter([B(_batch(g)) for _ in range(8)])
+        losses = []
+        if pipelined:
+            pipe = EmbCacheTrainPipelineSparseDist(model, opt, "cpu", "cpu", return_loss=True)
+            for _ in range(8):
+                losses.append(float(pipe.progress(data)[0]))
+        else:
+            for b in data:
+                opt.zero_grad()
+                loss, _ = model(b)
+                loss.backward()
+                opt.step()
+                losses.append(float(loss))
+        return losses
+
+    assert np.allclose(run(True), run(False), rtol=1e-5)
