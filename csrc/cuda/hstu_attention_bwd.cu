@@ -73,6 +73,8 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t (&rs)[16], const uint32
                                           int lane, float k_log, int cap, float half_alpha, float scale, float half_sa, int pi0,
                                           int i0, int j, int len_q, int len_k, int causal, int nctx, int ntgt, int gs,
                                           float& acc_lo, float& acc_hi) {
+  // phase A: straight-line math for 16 elements (no branches, so the loads and MUFU ops of different elements overlap)
+  uint32_t bkp[4] = {0u, 0u, 0u, 0u};                              // time buckets, one byte each
 #pragma unroll
   for (int e = 0; e < 16; e += 2) {
     float pv[2], dsv[2];
@@ -80,11 +82,11 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t (&rs)[16], const uint32
     for (int q = 0; q < 2; ++q) {
       const int ee = e0 + e + q;                                   // query column inside the 32-wide chunk
       float s = __uint_as_float(rs[e + q]);
-      int bk = 0;
       if (BT) {
         const float a = fmaxf(fabsf(my_ts[ee] - ts_j), 1.f);
-        bk = min(static_cast<int>(__log2f(a) * k_log), cap);
+        const int bk = min(static_cast<int>(__log2f(a) * k_log), cap);
         s += tsw_s[bk];
+        if (WDT) bkp[(e + q) >> 2] |= static_cast<uint32_t>(bk) << (8 * ((e + q) & 3));
       }
       if (BP) s += my_pos[ee + 31 - lane];
       const float h = s * half_alpha;
@@ -97,24 +99,36 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t (&rs)[16], const uint32
       float ds = __uint_as_float(rd[e + q]) * fmaf(sg, g, sg);
       if (MASKED) {
         const bool on = (i0 + ee < len_q) && attends(pi0 + ee, j, len_k, causal, nctx, ntgt, gs);
-        if (!on) { pval = 0.f; ds = 0.f; }
+        pval = on ? pval : 0.f;
+        ds = on ? ds : 0.f;
+      }
+      pv[q] = pval; dsv[q] = ds;
+    }
+    pk[e >> 1] = rb::pack_bf16(pv[0], pv[1]);
+    dk16[e >> 1] = rb::pack_bf16(dsv[0], dsv[1]);
+  }
+  // phase B: bias gradients from the bf16 dS (the values the dK / dQ matmuls see)
+  if (WDT || WDP) {
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const uint32_t w = dk16[e >> 1];
+      const float ds = __uint_as_float((e & 1) ? (w & 0xffff0000u) : (w << 16));
+      if (WDP) {
+        const int ee = e0 + e;
+        const int src = (ee + 31 - lane) & 31;
+        const float got = __shfl_sync(0xffffffffu, ds, src);
+        acc_hi += src < ee ? got : 0.f;
+        acc_lo += src < ee ? 0.f : got;
       }
       if (WDT) {
+        const int bk = static_cast<int>((bkp[e >> 2] >> (8 * (e & 3))) & 0xffu);
         if (bk != run_bucket) {
           if (run_bucket >= 0 && run_sum != 0.f) atomicAdd(dtsw_s + run_bucket, run_sum);
           run_bucket = bk; run_sum = 0.f;
         }
         run_sum += ds;
       }
-      if (WDP) {
-        const int src = (ee + 31 - lane) & 31;
-        const float got = __shfl_sync(0xffffffffu, ds, src);
-        if (src < ee) acc_hi += got; else acc_lo += got;
-      }
-      pv[q] = pval; dsv[q] = ds;
     }
-    pk[e >> 1] = rb::pack_bf16(pv[0], pv[1]);
-    dk16[e >> 1] = rb::pack_bf16(dsv[0], dsv[1]);
   }
 }
 

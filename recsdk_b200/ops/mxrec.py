@@ -1,0 +1,327 @@
+"""``torch.ops.mxrec.*``: the reference's operator names and argument orders, bound to this library's kernels.
+
+Importing this module registers the schemas (``cust_op/framework/torch_plugin/torch_library/*`` of the reference:
+``hstu/hstu_dense.cpp:157-173``, ``hstu/hstu_jagged.cpp:188-246``, ``hstu/hstu_paged.cpp:75-94``,
+``in_linear_silu/in_linear_silu.cpp:191-197``, ``relative_attn_bias/*.cpp``, ``ln_mul/ln_mul.cpp:69``,
+``norm_multiply_dropout.cpp:180``, ``token_mixing.cpp:63``, ``concat_jagged_tensor.cpp:245-255``,
+``multislice_concat.cpp:121``, ``gather_for_rank1.cpp:93-94``, ``reverse_sequence.cpp:85``,
+``split_embedding_codegen_forward_unweighted.cpp:123-142``).  ``mask_type``: 0 lower-triangular, 1 upper-triangular
+(unsupported, as in the reference), 2 none, 3 custom mask tensor.
+
+The tcgen05 attention kernels evaluate the relative position / time bias themselves; a materialised ``attn_bias``
+or a custom ``mask`` tensor is served by the fp32 PyTorch statement of the same math.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+
+from . import gemm, hstu_ops
+from .hstu_attention import hstu_attention, hstu_attention_paged, hstu_attention_ref
+from .hstu_attention_bwd import hstu_attn_bwd
+
+_LIB = torch.library.Library("mxrec", "DEF")
+_REGISTERED = set()
+
+
+def _def(schema: str, fn) -> None:
+    """Forward ops are registered as composite-implicit so that autograd flows through the differentiable functions
+    they call; ops that write into an argument or are themselves backward passes get an explicit kernel."""
+    name = schema.split("(")[0]
+    if name in _REGISTERED:
+        return
+    _LIB.define(schema)
+    explicit = "backward" in name or "(a!)" in schema
+    _LIB.impl(name, fn, "CompositeExplicitAutograd" if explicit else "CompositeImplicitAutograd")
+    _REGISTERED.add(name)
+
+
+# ------------------------------------------------------------------------------------------------ HSTU attention
+def _dense_ref(q, k, v, mask, attn_bias, mask_type, silu_scale, alpha=1.0):
+    """[B,S,N,D] tensors; fp32 math; returns (out, P-derivative pieces are recomputed by autograd)."""
+    B, S, N, D = q.shape
+    s = torch.einsum("bind,bjnd->bnij", q.float(), k.float())
+    if attn_bias is not None:
+        s = s + attn_bias.float()
+    scale = silu_scale if silu_scale != 0.0 else 1.0 / S
+    p = torch.nn.functional.silu(s * alpha) * scale
+    if mask_type == 0:
+        p = p * torch.tril(torch.ones(S, k.shape[1], device=q.device))
+    elif mask_type == 1:
+        raise NotImplementedError("upper-triangular masks are not supported")
+    elif mask_type == 3:
+        if mask is None:
+            raise ValueError("mask_type 3 needs a mask tensor")
+        p = p * mask.float()
+    return torch.einsum("bnij,bjnd->bind", p.to(q.dtype).float(), v.float()).to(q.dtype)
+
+
+def hstu_dense(q, k, v, mask=None, attn_bias=None, mask_type: int = 0, max_seq_len: int = 0, silu_scale: float = 0.0):
+    B, S, N, D = q.shape
+    if attn_bias is None and mask_type in (0, 2) and q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and k.shape[1] == S:
+        offs = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=q.device)
+        out = hstu_attention(q.reshape(B * S, N, D), k.reshape(B * S, N, D), v.reshape(B * S, N, D), offs, max_len_q=S, alpha=1.0,
+                             scale=silu_scale if silu_scale != 0.0 else 1.0 / S, causal=mask_type == 0)
+        return out.view(B, S, N, D)
+    return _dense_ref(q, k, v, mask, attn_bias, mask_type, silu_scale)
+
+
+def hstu_dense_backward(grad, q, k, v, mask=None, attn_bias=None, mask_type: int = 0, max_seq_len: int = 0, silu_scale: float = 0.0):
+    B, S, N, D = q.shape
+    if attn_bias is None and mask_type in (0, 2) and q.is_cuda and q.dtype == torch.bfloat16 and D == 64:
+        offs = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=q.device)
+        dq, dk, dv, _, _ = hstu_attn_bwd(grad.reshape(B * S, N, D), q.reshape(B * S, N, D), k.reshape(B * S, N, D), v.reshape(B * S, N, D),
+                                         offs, offs, 1.0, silu_scale if silu_scale != 0.0 else 1.0 / S, mask_type == 0, None, None, 0,
+                                         None, None, 1.0, None, max_len_k=S)
+        return dq.view_as(q), dk.view_as(k), dv.view_as(v), torch.zeros(0, device=q.device, dtype=q.dtype)
+    with torch.enable_grad():
+        qq, kk, vv = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+        bb = attn_bias.detach().float().requires_grad_(True) if attn_bias is not None else None
+        out = _dense_ref(qq, kk, vv, mask, bb, mask_type, silu_scale)
+        gs = torch.autograd.grad(out, [qq, kk, vv] + ([bb] if bb is not None else []), grad.float())
+    dbias = gs[3].to(q.dtype) if bb is not None else torch.zeros(0, device=q.device, dtype=q.dtype)
+    return gs[0].to(q.dtype), gs[1].to(q.dtype), gs[2].to(q.dtype), dbias
+
+
+def _jagged_common(q, k, v, mask, attn_bias, mask_type, max_seq_len, silu_scale, seq_offset, seq_offset_k, num_context, num_target,
+                   target_group_size, alpha):
+    if mask_type == 1:
+        raise NotImplementedError("upper-triangular masks are not supported")
+    scale = silu_scale if silu_scale != 0.0 else 1.0 / max(max_seq_len, 1)
+    if attn_bias is not None or mask_type == 3:
+        # materialised bias / custom mask: padded fp32 path
+        return _jagged_ref_bias(q, k, v, mask, attn_bias, mask_type, scale, seq_offset, seq_offset_k, num_context, num_target,
+                                target_group_size, alpha)
+    return hstu_attention(q, k, v, seq_offset, seq_offset_k, max_len_q=max_seq_len, alpha=alpha, scale=scale, causal=mask_type == 0,
+                          num_context=num_context, num_target=num_target, target_group_size=target_group_size)
+
+
+def _jagged_ref_bias(q, k, v, mask, attn_bias, mask_type, scale, qo, ko, num_context, num_target, gs, alpha):
+    from .hstu_attention import hstu_mask
+
+    out = torch.zeros_like(q, dtype=torch.float32)
+    ql, kl = qo.tolist(), ko.tolist()
+    for b in range(len(ql) - 1):
+        lq, lk = ql[b + 1] - ql[b], kl[b + 1] - kl[b]
+        if lq == 0:
+            continue
+        s = torch.einsum("ind,jnd->nij", q[ql[b]:ql[b + 1]].float(), k[kl[b]:kl[b + 1]].float())
+        if attn_bias is not None:
+            s = s + attn_bias[b, :, :lq, :lk].float()
+        p = torch.nn.functional.silu(s * alpha) * scale
+        if mask_type == 3:
+            m = mask[b, :, :lq, :lk].float() if mask.dim() == 4 else mask[b, :lq, :lk].float()[None]
+        else:
+            nc = int(num_context[b]) if num_context is not None else 0
+            nt = int(num_target[b]) if num_target is not None else 0
+            m = hstu_mask(lq, lk, mask_type == 0, nc, nt, gs, q.device)[None]
+        p = (p * m).to(q.dtype).float()
+        out[ql[b]:ql[b + 1]] = torch.einsum("nij,jnd->ind", p, v[kl[b]:kl[b + 1]].float())
+    return out.to(q.dtype)
+
+
+def hstu_jagged_equal(q, k, v, mask=None, attn_bias=None, mask_type: int = 0, max_seq_len: int = 0, silu_scale: float = 0.0,
+                      seq_offset=None, num_context=None, num_target=None, target_group_size: int = 0, alpha: float = 1.0,
+                      deterministic: bool = False):
+    return _jagged_common(q, k, v, mask, attn_bias, mask_type, max_seq_len, silu_scale, seq_offset, seq_offset, num_context,
+                          num_target, target_group_size, alpha)
+
+
+def hstu_jagged_delta(q, k, v, mask=None, attn_bias=None, mask_type: int = 0, max_seq_len: int = 0, max_seq_len_k: int = 0,
+                      silu_scale: float = 0.0, seq_offset=None, seq_offset_k=None, num_context=None, num_target=None,
+                      target_group_size: int = 0, alpha: float = 1.0, deterministic: bool = False):
+    return _jagged_common(q, k, v, mask, attn_bias, mask_type, max_seq_len, silu_scale, seq_offset, seq_offset_k, num_context,
+                          num_target, target_group_size, alpha)
+
+
+def _jagged_backward(grad, q, k, v, mask, attn_bias, mask_type, max_seq_len, silu_scale, qo, ko, num_context, num_target, gs, alpha):
+    scale = silu_scale if silu_scale != 0.0 else 1.0 / max(max_seq_len, 1)
+    if attn_bias is None and mask_type in (0, 2):
+        dq, dk, dv, _, _ = hstu_attn_bwd(grad, q, k, v, qo, ko, alpha, scale, mask_type == 0, num_context, num_target, gs, None, None,
+                                         1.0, None)
+        return dq, dk, dv, torch.zeros(0, device=q.device, dtype=q.dtype)
+    with torch.enable_grad():
+        qq, kk, vv = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+        bb = attn_bias.detach().float().requires_grad_(True) if attn_bias is not None else None
+        out = _jagged_ref_bias(qq, kk, vv, mask, bb, mask_type, scale, qo, ko, num_context, num_target, gs, alpha)
+        g = torch.autograd.grad(out, [qq, kk, vv] + ([bb] if bb is not None else []), grad.float())
+    dbias = g[3].to(q.dtype) if bb is not None else torch.zeros(0, device=q.device, dtype=q.dtype)
+    return g[0].to(q.dtype), g[1].to(q.dtype), g[2].to(q.dtype), dbias
+
+
+def hstu_jagged_backward_equal(grad, q, k, v, mask=None, attn_bias=None, mask_type: int = 0, max_seq_len: int = 0,
+                               silu_scale: float = 0.0, seq_offset=None, num_context=None, num_target=None,
+                               target_group_size: int = 0, alpha: float = 1.0, deterministic: bool = False):
+    return _jagged_backward(grad, q, k, v, mask, attn_bias, mask_type, max_seq_len, silu_scale, seq_offset, seq_offset, num_context,
+                            num_target, target_group_size, alpha)
+
+
+def hstu_jagged_backward_delta(grad, q, k, v, mask=None, attn_bias=None, mask_type: int = 0, max_seq_len: int = 0,
+                               max_seq_len_k: int = 0, silu_scale: float = 0.0, seq_offset=None, seq_offset_k=None,
+                               num_context=None, num_target=None, target_group_size: int = 0, alpha: float = 1.0,
+                               deterministic: bool = False):
+    return _jagged_backward(grad, q, k, v, mask, attn_bias, mask_type, max_seq_len, silu_scale, seq_offset, seq_offset_k, num_context,
+                            num_target, target_group_size, alpha)
+
+
+def hstu_paged(q, k, v, kv_cache, mask=None, attn_bias=None, mask_type: int = 0, max_seq_len: int = 0, max_seq_len_k: int = 0,
+               silu_scale: float = 0.0, seq_offset=None, seq_offset_k=None, seq_offset_t=None, page_offsets=None, page_ids=None,
+               last_page_len=None, num_target=None, target_group_size: int = 0, alpha: float = 1.0, deterministic: bool = False):
+    """``q`` / ``k`` / ``v``: the new tokens ``[nnz, N, D]`` (``seq_offset``); ``kv_cache`` ``[pages, 2, page, N, D]``
+    holds the history and has room for the new tokens, which are appended here before the attention runs
+    (``seq_offset_k``: total key lengths; ``seq_offset_t`` is unused: targets are given by ``num_target``)."""
+    page_size = kv_cache.shape[2]
+    N, D = q.shape[1], q.shape[2]
+    qo, ko = seq_offset.to(torch.int64), seq_offset_k.to(torch.int64)
+    lens_q, lens_k = qo[1:] - qo[:-1], ko[1:] - ko[:-1]
+    bidx = torch.repeat_interleave(torch.arange(lens_q.numel(), device=q.device), lens_q)
+    pos = torch.arange(q.shape[0], device=q.device) - qo[:-1][bidx] + (lens_k - lens_q)[bidx]
+    page = page_ids.long()[page_offsets.long()[bidx] + pos // page_size]
+    kv_cache[page, 0, pos % page_size] = k
+    kv_cache[page, 1, pos % page_size] = v
+    scale = silu_scale if silu_scale != 0.0 else 1.0 / max(max_seq_len_k, 1)
+    if q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and attn_bias is None and mask_type == 0:
+        return hstu_attention_paged(q, kv_cache, seq_offset, seq_offset_k, page_ids, page_offsets, page_size, max_seq_len, alpha, scale,
+                                    num_target=num_target, target_group_size=target_group_size)
+    ks, vs = [], []
+    po = page_offsets.tolist()
+    for b in range(lens_k.numel()):
+        pg = page_ids[po[b]:po[b + 1]].long()
+        ks.append(kv_cache[pg, 0].reshape(-1, N, D)[: int(lens_k[b])])
+        vs.append(kv_cache[pg, 1].reshape(-1, N, D)[: int(lens_k[b])])
+    return hstu_attention_ref(q, torch.cat(ks), torch.cat(vs), seq_offset, seq_offset_k, alpha, scale, True, None, num_target,
+                              target_group_size)
+
+
+# ------------------------------------------------------------------------------------------------ in_linear_silu
+def in_linear_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], attr_dict: List[int]) -> List[torch.Tensor]:
+    """``SiLU(x W^T + b)`` split column-wise into ``len(attr_dict)`` tensors (U, V, Q, K for HSTU)."""
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16):
+        y = gemm.gemm16(x.contiguous(), weight.contiguous(), bias=None if bias is None else bias.float(), epi=gemm.EPI_SILU)
+    else:
+        y = torch.nn.functional.silu(torch.nn.functional.linear(x.float(), weight.float(), None if bias is None else bias.float())).to(x.dtype)
+    return list(torch.split(y, list(attr_dict), dim=1))
+
+
+def in_linear_silu_backward(x, weight, bias, user_grad, value_grad, query_grad, key_grad, linear_output, attr_dict: List[int]):
+    """-> [dx, dweight, dbias]; ``linear_output`` is the pre-activation ``x W^T + b``."""
+    dy = torch.cat([user_grad, value_grad, query_grad, key_grad], dim=1).float()
+    z = linear_output.float()
+    sg = torch.sigmoid(z)
+    dz = dy * (sg * (1 + z * (1 - sg)))
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16):
+        dz16 = dz.to(x.dtype)
+        dx = gemm.gemm16(dz16, weight.contiguous(), b_mn=True)
+        dw = torch.zeros(weight.shape, dtype=torch.float32, device=x.device)
+        gemm.gemm16(dz16, x.contiguous(), a_mn=True, b_mn=True, out=dw, epi=gemm.EPI_F32_ATOMIC,
+                    splits=gemm.pick_splits(weight.shape[0], weight.shape[1], x.shape[0]))
+        dw = dw.to(weight.dtype)
+    else:
+        dx = (dz @ weight.float()).to(x.dtype)
+        dw = (dz.t() @ x.float()).to(weight.dtype)
+    db = dz.sum(0).to(bias.dtype) if bias is not None else torch.zeros(0, device=x.device)
+    return [dx, dw, db]
+
+
+# ------------------------------------------------------------------------------------------------ small ops
+def relative_attn_bias_time_with_index(timestamps, timestamps_weights, bucket_divisor: float) -> List[torch.Tensor]:
+    out, idx = hstu_ops.relative_attn_bias_time(timestamps, timestamps_weights, bucket_divisor, with_index=True)
+    return [out, idx]
+
+
+def norm_multiply_dropout(x, u, weight, bias, eps: float = 1e-5, dropout_ratio: float = 0.0) -> List[torch.Tensor]:
+    return [hstu_ops.ln_mul(x, u, weight, bias, eps, dropout_ratio)]
+
+
+def concat_2d_jagged(max_seq_len: int, values_a, values_b, offsets_a, offsets_b):
+    return hstu_ops.concat_2d_jagged(values_a, values_b, offsets_a, offsets_b)
+
+
+def split_2d_jagged(values, max_seq_len: int, offsets_a, offsets_b) -> Tuple[torch.Tensor, torch.Tensor]:
+    return hstu_ops.split_2d_jagged(values, offsets_a, offsets_b)
+
+
+def multislice_concat(x, concat_num: int, concat_size: List[int], slice_begin: List[int]):
+    return hstu_ops.multislice_concat(x, list(slice_begin)[:concat_num], list(concat_size)[:concat_num])
+
+
+def index_select_for_rank1_backward(grad, x, index) -> List[torch.Tensor]:
+    dx = torch.zeros_like(x, dtype=torch.float32)
+    dx.index_add_(0, index.long(), grad.float())
+    return [dx.to(x.dtype)]
+
+
+def split_embedding_codegen_forward_unweighted_cuda(dev_weights, uvm_weights, lxu_cache_weights, weights_placements, weights_offsets,
+                                                    D_offsets, total_D: int, max_D: int, indices, offsets, pooling_mode: int,
+                                                    lxu_cache_locations, uvm_cache_stats, output_dtype: int, is_experimental: bool,
+                                                    hash_indices=None, offset_per_key=None, rows_per_table=None):
+    """FBGEMM-TBE-compatible lookup over one flat weight buffer.  ``pooling_mode``: 0 sum, 1 mean, 2 none;
+    ``hash_indices``, when given, replace ``indices`` (ids already mapped to rows)."""
+    from . import embedding_ops as E
+
+    idx = (hash_indices if hash_indices is not None else indices).long()
+    T = D_offsets.numel() - 1
+    dims = (D_offsets[1:] - D_offsets[:-1]).tolist()
+    B = (offsets.numel() - 1) // T
+    w_off = weights_offsets.tolist()
+    rows = list(rows_per_table.tolist()) if rows_per_table is not None else \
+        [((w_off[t + 1] if t + 1 < T else dev_weights.numel()) - w_off[t]) // dims[t] for t in range(T)]
+    tables = [dev_weights[w_off[t]: w_off[t] + rows[t] * dims[t]].view(rows[t], dims[t]) for t in range(T)]
+    if pooling_mode == 2:
+        off = offsets.tolist()
+        out = torch.zeros(idx.numel(), max_D, dtype=torch.float32, device=dev_weights.device)
+        for t in range(T):
+            a, b = off[t * B], off[(t + 1) * B]
+            out[a:b, : dims[t]] = tables[t][idx[a:b]].float()
+        return out
+    return E.reference_pooled_forward(tables, idx, offsets.long(), B, ["mean" if pooling_mode == 1 else "sum"] * T)
+
+
+_def("hstu_dense(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, int max_seq_len=0, "
+     "float silu_scale=0.0) -> Tensor", hstu_dense)
+_def("hstu_dense_backward(Tensor grad, Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
+     "int max_seq_len=0, float silu_scale=0.0) -> (Tensor, Tensor, Tensor, Tensor)", hstu_dense_backward)
+_def("hstu_jagged.equal(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, int max_seq_len=0, "
+     "float silu_scale=0.0, Tensor? seq_offset=None, Tensor? num_context=None, Tensor? num_target=None, int target_group_size=0, "
+     "float alpha=1.0, bool deterministic=False) -> Tensor", hstu_jagged_equal)
+_def("hstu_jagged.delta(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, int max_seq_len=0, "
+     "int max_seq_len_k=0, float silu_scale=0.0, Tensor? seq_offset=None, Tensor? seq_offset_k=None, Tensor? num_context=None, "
+     "Tensor? num_target=None, int target_group_size=0, float alpha=1.0, bool deterministic=False) -> Tensor", hstu_jagged_delta)
+_def("hstu_jagged_backward.equal(Tensor grad, Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
+     "int max_seq_len=0, float silu_scale=0.0, Tensor? seq_offset=None, Tensor? num_context=None, Tensor? num_target=None, "
+     "int target_group_size=0, float alpha=1.0, bool deterministic=False) -> (Tensor, Tensor, Tensor, Tensor)", hstu_jagged_backward_equal)
+_def("hstu_jagged_backward.delta(Tensor grad, Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
+     "int max_seq_len=0, int max_seq_len_k=0, float silu_scale=0.0, Tensor? seq_offset=None, Tensor? seq_offset_k=None, "
+     "Tensor? num_context=None, Tensor? num_target=None, int target_group_size=0, float alpha=1.0, bool deterministic=False) "
+     "-> (Tensor, Tensor, Tensor, Tensor)", hstu_jagged_backward_delta)
+_def("hstu_paged(Tensor q, Tensor k, Tensor v, Tensor(a!) kv_cache, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
+     "int max_seq_len=0, int max_seq_len_k=0, float silu_scale=0.0, Tensor? seq_offset=None, Tensor? seq_offset_k=None, "
+     "Tensor? seq_offset_t=None, Tensor? page_offsets=None, Tensor? page_ids=None, Tensor? last_page_len=None, Tensor? num_target=None, "
+     "int target_group_size=0, float alpha=1.0, bool deterministic=False) -> Tensor", hstu_paged)
+_def("in_linear_silu(Tensor x, Tensor weight, Tensor? bias, int[] attr_dict) -> Tensor[]", in_linear_silu)
+_def("in_linear_silu_backward(Tensor x, Tensor weight, Tensor? bias, Tensor user_grad, Tensor value_grad, Tensor query_grad, "
+     "Tensor key_grad, Tensor linear_output, int[] attr_dict) -> Tensor[]", in_linear_silu_backward)
+_def("relative_attn_bias_pos(Tensor rel_pos_bias, Tensor identity, int[] past_valid_lens) -> Tensor", hstu_ops.relative_attn_bias_pos)
+_def("relative_attn_bias_time(Tensor timestamps, Tensor timestamps_weights, float bucket_divisor) -> Tensor",
+     lambda t, w, d: hstu_ops.relative_attn_bias_time(t, w, d))
+_def("relative_attn_bias_time_with_index(Tensor timestamps, Tensor timestamps_weights, float bucket_divisor) -> Tensor[]",
+     relative_attn_bias_time_with_index)
+_def("relative_attn_bias_time_backward(Tensor rab_time_grad, Tensor bucket_timestamps, int num_buckets) -> Tensor",
+     hstu_ops.relative_attn_bias_time_backward)
+_def("ln_mul(Tensor x, Tensor u, Tensor gamma, Tensor beta) -> Tensor", lambda x, u, g, b: hstu_ops.ln_mul(x, u, g, b))
+_def("norm_multiply_dropout(Tensor x, Tensor u, Tensor weight, Tensor bias, float eps=1e-05, float dropout_ratio=0.0) -> Tensor[]",
+     norm_multiply_dropout)
+_def("token_mixing(Tensor x, Tensor gamma, Tensor beta, float epsilon=1e-07) -> Tensor", hstu_ops.token_mixing)
+_def("concat_2d_jagged(int max_seq_len, Tensor values_a, Tensor values_b, Tensor offsets_a, Tensor offsets_b) -> (Tensor, Tensor)",
+     concat_2d_jagged)
+_def("split_2d_jagged(Tensor values, int max_seq_len, Tensor offsets_a, Tensor offsets_b) -> (Tensor, Tensor)", split_2d_jagged)
+_def("multislice_concat(Tensor input, int concat_num, int[] concat_size, int[] slice_begin) -> Tensor", multislice_concat)
+_def("gather_for_rank1(Tensor x, Tensor index) -> Tensor", hstu_ops.gather_for_rank1)
+_def("index_select_for_rank1_backward(Tensor grad, Tensor x, Tensor index) -> Tensor[]", index_select_for_rank1_backward)
+_def("reverse_sequence(Tensor input, Tensor seq_lengths) -> Tensor", hstu_ops.reverse_sequence)
+_def("split_embedding_codegen_forward_unweighted_cuda(Tensor dev_weights, Tensor uvm_weights, Tensor lxu_cache_weights, "
+     "Tensor weights_placements, Tensor weights_offsets, Tensor D_offsets, int total_D, int max_D, Tensor indices, Tensor offsets, "
+     "int pooling_mode, Tensor lxu_cache_locations, Tensor uvm_cache_stats, int output_dtype, bool is_experimental, "
+     "Tensor? hash_indices=None, Tensor? offset_per_key=None, Tensor? rows_per_table=None) -> Tensor",
+     split_embedding_codegen_forward_unweighted_cuda)

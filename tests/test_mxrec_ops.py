@@ -1,0 +1,94 @@
+"""``torch.ops.mxrec.*`` registrations: names resolve, argument orders work, results match direct math (CPU)."""
+import torch
+
+import recsdk_b200.ops.mxrec  # noqa: F401  (registers the operators)
+from recsdk_b200.ops.hstu_attention import hstu_attention_ref
+
+
+def test_hstu_dense_and_backward():
+    torch.manual_seed(0)
+    B, S, N, D = 2, 12, 2, 16
+    q, k, v = (torch.randn(B, S, N, D) * 0.5 for _ in range(3))
+    out = torch.ops.mxrec.hstu_dense(q, k, v, None, None, 0, S, 0.0)
+    offs = torch.arange(0, (B + 1) * S, S)
+    ref = hstu_attention_ref(q.reshape(B * S, N, D), k.reshape(B * S, N, D), v.reshape(B * S, N, D), offs, offs, 1.0, 1.0 / S)
+    assert torch.allclose(out.reshape(B * S, N, D), ref, atol=1e-5)
+    bias = torch.randn(B, N, S, S) * 0.1
+    g = torch.randn_like(out)
+    dq, dk, dv, db = torch.ops.mxrec.hstu_dense_backward(g, q, k, v, None, bias, 0, S, 0.0)
+    qq, bb = q.clone().requires_grad_(True), bias.clone().requires_grad_(True)
+    o2 = torch.ops.mxrec.hstu_dense(qq, k, v, None, bb, 0, S, 0.0)
+    o2.backward(g)
+    assert torch.allclose(dq, qq.grad, atol=1e-5) and torch.allclose(db, bb.grad, atol=1e-5)
+
+
+def test_hstu_jagged_overloads_and_paged():
+    torch.manual_seed(1)
+    N, D = 2, 16
+    qo = torch.tensor([0, 5, 9])
+    ko = torch.tensor([0, 8, 15])
+    q = torch.randn(9, N, D) * 0.5
+    k, v = torch.randn(15, N, D) * 0.5, torch.randn(15, N, D) * 0.5
+    nt = torch.tensor([2, 1])
+    out = torch.ops.mxrec.hstu_jagged.delta(q, k, v, None, None, 0, 5, 8, 0.1, qo, ko, None, nt, 1, 0.5, False)
+    ref = hstu_attention_ref(q, k, v, qo, ko, 0.5, 0.1, True, None, nt, 1)
+    assert torch.allclose(out, ref, atol=1e-5)
+    eq = torch.ops.mxrec.hstu_jagged.equal(k, k, v, None, None, 0, 8, 0.1, ko, None, None, 0, 1.0, False)
+    assert torch.allclose(eq, hstu_attention_ref(k, k, v, ko, ko, 1.0, 0.1), atol=1e-5)
+    g = torch.randn_like(out)
+    dq, dk, dv, _ = torch.ops.mxrec.hstu_jagged_backward.delta(g, q, k, v, None, None, 0, 5, 8, 0.1, qo, ko, None, nt, 1, 0.5, False)
+    qq = q.clone().requires_grad_(True)
+    hstu_attention_ref(qq, k, v, qo, ko, 0.5, 0.1, True, None, nt, 1).backward(g)
+    assert torch.allclose(dq, qq.grad, atol=1e-4)
+    # paged: history in the cache, the op appends the new tokens and attends
+    page = 4
+    cache = torch.zeros(8, 2, page, N, D)
+    page_ids = torch.tensor([0, 1, 5, 6])
+    page_off = torch.tensor([0, 2, 4])
+    hist = [3, 3]
+    for b in range(2):
+        for t in range(hist[b]):
+            pg = page_ids[page_off[b] + t // page]
+            cache[pg, 0, t % page] = k[ko[b] + t]
+            cache[pg, 1, t % page] = v[ko[b] + t]
+    ko2 = torch.tensor([0, 8, 7 + 8]) if False else torch.tensor([0, 8, 8 + 7])
+    newk = torch.cat([k[3:8], k[11:15]])
+    newv = torch.cat([v[3:8], v[11:15]])
+    qn = torch.randn(9, N, D)
+    out = torch.ops.mxrec.hstu_paged(qn, newk, newv, cache, None, None, 0, 5, 8, 0.1, qo, ko2, None, page_off, page_ids, None, None, 0,
+                                     1.0, False)
+    ref = hstu_attention_ref(qn, k, v, qo, ko2, 1.0, 0.1)
+    assert torch.allclose(out, ref, atol=1e-5)
+
+
+def test_in_linear_silu_and_small_ops():
+    torch.manual_seed(2)
+    x, w, b = torch.randn(7, 12), torch.randn(20, 12), torch.randn(20)
+    outs = torch.ops.mxrec.in_linear_silu(x, w, b, [4, 6, 5, 5])
+    z = x @ w.t() + b
+    assert [o.shape[1] for o in outs] == [4, 6, 5, 5] and torch.allclose(torch.cat(outs, 1), torch.nn.functional.silu(z), atol=1e-5)
+    gs = [torch.randn_like(o) for o in outs]
+    dx, dw, db = torch.ops.mxrec.in_linear_silu_backward(x, w, b, gs[0], gs[1], gs[2], gs[3], z, [4, 6, 5, 5])
+    xx, ww, bb = (t.clone().requires_grad_(True) for t in (x, w, b))
+    torch.nn.functional.silu(xx @ ww.t() + bb).backward(torch.cat(gs, 1))
+    assert torch.allclose(dx, xx.grad, atol=1e-4) and torch.allclose(dw, ww.grad, atol=1e-4) and torch.allclose(db, bb.grad, atol=1e-4)
+    ts = torch.sort(torch.randint(0, 10000, (2, 6))).values
+    tw = torch.randn(3, 9)
+    rab, idx = torch.ops.mxrec.relative_attn_bias_time_with_index(ts, tw, 0.5)
+    assert rab.shape == (3, 2, 6, 6) and torch.equal(torch.ops.mxrec.relative_attn_bias_time(ts, tw, 0.5), rab)
+    dwt = torch.ops.mxrec.relative_attn_bias_time_backward(torch.ones_like(rab), idx, 8)
+    assert dwt.shape == (3, 9) and float(dwt.sum()) == 3 * 2 * 36
+    y = torch.ops.mxrec.ln_mul(x, torch.ones_like(x), torch.ones(12), torch.zeros(12))
+    assert torch.allclose(y, torch.nn.functional.layer_norm(x, (12,)), atol=1e-5)
+    assert torch.equal(torch.ops.mxrec.gather_for_rank1(b, torch.tensor([3, 1])), b[[3, 1]])
+    assert torch.equal(torch.ops.mxrec.multislice_concat(x, 2, [2, 3], [0, 5]), torch.cat([x[:, :2], x[:, 5:8]], 1))
+    r = torch.ops.mxrec.reverse_sequence(torch.arange(12.).view(2, 6, 1), torch.tensor([3, 6]))
+    assert r[0, :3, 0].tolist() == [2, 1, 0] and r[1, :, 0].tolist() == [11, 10, 9, 8, 7, 6]
+    # TBE-compatible lookup over one flat buffer
+    wflat = torch.randn(5 * 4 + 3 * 8)
+    out = torch.ops.mxrec.split_embedding_codegen_forward_unweighted_cuda(
+        wflat, wflat[:0], wflat[:0], torch.zeros(2, dtype=torch.int32), torch.tensor([0, 20]), torch.tensor([0, 4, 12]), 12, 8,
+        torch.tensor([0, 4, 1, 2, 2]), torch.tensor([0, 2, 3, 4, 5]), 0, torch.zeros(0, dtype=torch.int32), torch.zeros(0), 0, False,
+        None, None, torch.tensor([5, 3]))
+    t0, t1 = wflat[:20].view(5, 4), wflat[20:].view(3, 8)
+    assert torch.allclose(out[0, :4], t0[0] + t0[4]) and torch.allclose(out[1, 4:], t1[2])
