@@ -7,6 +7,8 @@ from .dynamicemb_config import (DynamicEmbCheckMode, DynamicEmbInitializerArgs, 
 from .embedding import DynamicEmbeddingBagCollection, DynamicEmbeddingCollection
 from .hkv import EvictStrategy, HKVTable, HostDynamicTable, InitializerArgs, InitMode, OptimizerType
 from .key_value_table import DiskStorage, KeyValueTable, Storage, TableStorage
+from .planner import (DynamicEmbeddingBagCollectionSharder, DynamicEmbeddingCollectionSharder, DynamicEmbeddingShardingPlanner,
+                      DynamicEmbParameterConstraints, DynamicEmbParameterSharding)
 
 __all__ = [
     "BatchedDynamicEmbeddingTablesV2", "DynamicEmbDump", "DynamicEmbLoad", "get_score", "incremental_dump", "set_score",
@@ -14,5 +16,6 @@ __all__ = [
     "DynamicEmbScoreStrategy", "DynamicEmbTableOptions", "EmbOptimType", "convert_optimizer_type",
     "get_constraint_capacity", "DynamicEmbeddingBagCollection", "DynamicEmbeddingCollection", "EvictStrategy", "HKVTable",
     "HostDynamicTable", "InitializerArgs", "InitMode", "OptimizerType", "DiskStorage", "KeyValueTable", "Storage",
-    "TableStorage",
+    "TableStorage", "DynamicEmbeddingBagCollectionSharder", "DynamicEmbeddingCollectionSharder", "DynamicEmbeddingShardingPlanner",
+    "DynamicEmbParameterConstraints", "DynamicEmbParameterSharding",
 ]

@@ -69,6 +69,7 @@ class DistributedModelParallel(nn.Module):
         if self.world > 1 and self.device.type == "cuda" and peer is None:
             self.peer = PeerGroup(self.env.process_group, self.device)
         self.plan = plan or ShardingPlan({})
+        self.sharders = list(sharders or [])
         self.sharded_modules: List[nn.Module] = []
         self._shard(module, "", sparse_optimizer, out_dtype, max_local_batch, one_hot, init_seed)
         self.module = module
@@ -86,6 +87,11 @@ class DistributedModelParallel(nn.Module):
     def _shard(self, parent: nn.Module, prefix: str, spec, out_dtype, max_local_batch, one_hot, init_seed) -> None:
         for name, child in list(parent.named_children()):
             path = prefix + name
+            custom = self._custom_shard(child, path)
+            if custom is not None:
+                setattr(parent, name, custom)
+                self.sharded_modules.append(custom)
+                continue
             if isinstance(child, EmbeddingBagCollection):
                 entries: Dict[str, ParameterSharding] = self.plan.get_module_plan(path)
                 hashed = isinstance(child, HashEmbeddingBagCollection)
@@ -113,6 +119,19 @@ class DistributedModelParallel(nn.Module):
                 continue
             else:
                 self._shard(child, path + ".", spec, out_dtype, max_local_batch, one_hot, init_seed)
+
+    def _custom_shard(self, child: nn.Module, path: str) -> Optional[nn.Module]:
+        """User-supplied sharders (objects with ``module_type`` and ``shard(module, params, env, device)``; an optional
+        ``handles(module, params)`` narrows the match) take precedence over the built-in table sharding."""
+        for s in self.sharders:
+            mt = getattr(s, "module_type", None)
+            if mt is None or not isinstance(child, mt):
+                continue
+            params = self.plan.get_module_plan(path)
+            if hasattr(s, "handles") and not s.handles(child, params):
+                continue
+            return s.shard(child, params, self.env, self.device)
+        return None
 
     # ------------------------------------------------------------- dense grads
     def _flat_modules(self) -> List[nn.Module]:
@@ -157,7 +176,7 @@ class DistributedModelParallel(nn.Module):
     # ------------------------------------------------------------------- misc
     @property
     def fused_optimizer(self) -> CombinedOptimizer:
-        return CombinedOptimizer([m.fused_optimizer for m in self.sharded_modules])
+        return CombinedOptimizer([m.fused_optimizer for m in self.sharded_modules if hasattr(m, "fused_optimizer")])
 
     def forward(self, *args, **kwargs):
         return self.module(*args, **kwargs)

@@ -1,0 +1,34 @@
+import torch
+
+from recsdk_b200.sparse.jagged_tensor import KeyedJaggedTensor
+from recsdk_b200.sparse.kjt_extensions import (ExtendedJaggedTensor, KeyedJaggedTensorWithCount, KeyedJaggedTensorWithLookHelper,
+                                               KeyedJaggedTensorWithTimestamp)
+
+
+def test_side_tensors_follow_values():
+    vals = torch.tensor([10, 11, 12, 13, 14, 15])
+    lens = torch.tensor([1, 2, 0, 3])                      # 2 keys x batch 2
+    k = KeyedJaggedTensorWithLookHelper(["a", "b"], vals, lengths=lens, hash_indices=vals * 2, unique_inverse=vals - 10,
+                                        unique_indices=torch.tensor([7, 8]), unique_offset=torch.tensor([0, 1, 2]))
+    a, b = k.split([1, 1])
+    assert a.hash_indices.tolist() == [20, 22, 24] and b.hash_indices.tolist() == [26, 28, 30]
+    assert b.unique_indices.tolist() == [7, 8] and isinstance(b, KeyedJaggedTensorWithLookHelper)
+    p = k.permute([1, 0])
+    assert p.keys() == ["b", "a"] and p.values().tolist() == [13, 14, 15, 10, 11, 12] and p.unique_inverse.tolist() == [3, 4, 5, 0, 1, 2]
+    moved = k.to(torch.device("cpu"))
+    assert moved.hash_indices.tolist() == k.hash_indices.tolist() and moved["a"].values().tolist() == [10, 11, 12]
+    t = KeyedJaggedTensorWithTimestamp(["a", "b"], vals, lengths=lens, timestamps=vals + 100)
+    assert t.split([1, 1])[1].timestamps.tolist() == [113, 114, 115]
+    try:
+        KeyedJaggedTensorWithTimestamp(["a"], vals, lengths=torch.tensor([6]), timestamps=vals[:2])
+        assert False
+    except ValueError:
+        pass
+
+
+def test_dedup_with_counts_and_extended_jt():
+    k = KeyedJaggedTensor(["a"], torch.tensor([5, 5, 7, 9, 9, 9]), lengths=torch.tensor([3, 3]))
+    d = KeyedJaggedTensorWithCount.dedup(k)
+    assert d.values().tolist() == [5, 7, 9] and d.counts.tolist() == [2, 1, 3] and d.lengths().tolist() == [2, 1]
+    e = ExtendedJaggedTensor(torch.arange(4.), lengths=torch.tensor([1, 3]), extras={"ts": torch.arange(4) + 50})
+    assert e.to(torch.device("cpu")).extras["ts"].tolist() == [50, 51, 52, 53]
