@@ -156,8 +156,6 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
                               for t in module.tables]
         self.swap_step = 0
         self.stats = {"swap_in": 0, "swap_out": 0}
-        self._prepared: Dict[int, tuple] = {}                  # id(features) -> context made ahead of time
-        self._swap_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
         with torch.no_grad():
             for ti, t in enumerate(self.tables):
                 self.embedding_bags[t.name].weight.zero_()
@@ -231,37 +229,6 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
             self.apply_swap(ti, info)
             out[p] = info["batch_offs"]
         return torch.from_numpy(out).to(ids.device)
-
-    # -- pipelining ------------------------------------------------------------------------------------------
-    def prefetch(self, features: KeyedJaggedTensor) -> None:
-        """Input distribution and the whole swap for a batch that will be consumed later.  Safe while the previous
-        batch is still in flight: the swap manager never hands out slots that the current or previous batch use.
-        Device work runs on the module's swap stream; ``forward`` makes the compute stream wait for it."""
-        if self._swap_stream is not None:
-            self._swap_stream.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(self._swap_stream):
-                ctx = self._prepare(features)
-                ev = torch.cuda.Event()
-                ev.record(self._swap_stream)
-        else:
-            ctx, ev = self._prepare(features), None
-        self._prepared[id(features)] = ctx + (ev,)
-
-    def _prepare(self, features: KeyedJaggedTensor):
-        lengths, ids, B = self.input_dist(features)
-        slots = self.post_input_dist(lengths, ids)
-        orig = features.lengths().view(len(self.feature_names), B).to(self.device)
-        return lengths, slots, B, orig
-
-    def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
-        ctx = self._prepared.pop(id(features), None)
-        if ctx is None:
-            lengths, slots, B, orig = self._prepare(features)
-        else:
-            lengths, slots, B, orig, ev = ctx
-            if ev is not None:
-                torch.cuda.current_stream(self.device).wait_event(ev)
-        return self.compute_and_output_dist(lengths, slots, B, orig)
 
     def _apply_update(self, ti: int, rows: torch.Tensor, grads: torch.Tensor) -> None:
         if self.admit[ti]:                                   # slot 0 = "not admitted": never trained

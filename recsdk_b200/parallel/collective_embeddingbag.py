@@ -124,10 +124,17 @@ class _PooledLookup(torch.autograd.Function):
 class CollectiveShardedEmbeddingBagCollection(nn.Module):
     def __init__(self, tables: List[EmbeddingBagConfig], plan: Dict[str, ParameterSharding], env: ShardingEnv,
                  device: torch.device, optimizer_spec: Optional[E.OptimizerSpec] = None, hashed: bool = False,
-                 out_dtype: torch.dtype = torch.float32, init_weights: bool = True) -> None:
+                 out_dtype: torch.dtype = torch.float32, init_weights: bool = True,
+                 input_env: Optional[ShardingEnv] = None) -> None:
+        """``input_env``: optional host-side (gloo) environment; when given, the id exchange of ``input_dist`` runs on
+        it with CPU tensors, so it can be issued from a background thread ahead of time without interleaving with the
+        device collectives of the running step."""
         super().__init__()
         self.tables, self.env, self.device = list(tables), env, torch.device(device)
         self.world, self.rank, self.pg = env.world_size, env.rank, env.process_group
+        self.input_pg = input_env.process_group if input_env is not None else None
+        self._prepared: Dict[int, tuple] = {}
+        self._prefetch_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
         self.opt = optimizer_spec or E.OptimizerSpec()
         self.hashed, self.out_dtype = hashed, out_dtype
         self.feature_names: List[str] = []
@@ -280,14 +287,20 @@ class CollectiveShardedEmbeddingBagCollection(nn.Module):
         new_lengths, new_ids, _perm = self._in_pool.submit(self._bucketize, features).result()
         if self.world == 1:
             return new_lengths.view(1, F, B).to(self.device), new_ids.to(self.device), B
-        send_lengths = new_lengths.to(self.device).contiguous()
+        host_side = self.input_pg is not None
+        xdev, xpg = (torch.device("cpu"), self.input_pg) if host_side else (self.device, self.pg)
+        send_lengths = new_lengths.to(xdev).contiguous()
         recv_lengths = torch.empty_like(send_lengths)
-        dist.all_to_all_single(recv_lengths, send_lengths, group=self.pg)          # splits: F*B per rank
+        dist.all_to_all_single(recv_lengths, send_lengths, group=xpg)              # splits: F*B per rank
         in_splits = new_lengths.sum(dim=1).tolist()
         out_splits = recv_lengths.view(self.world, -1).sum(dim=1).tolist()
-        send_ids = new_ids.to(self.device)
+        send_ids = new_ids.to(xdev)
         recv_ids = send_ids.new_empty(int(sum(out_splits)))
-        dist.all_to_all_single(recv_ids, send_ids, out_splits, in_splits, group=self.pg)
+        dist.all_to_all_single(recv_ids, send_ids, out_splits, in_splits, group=xpg)
+        if host_side and not self.hashed:
+            recv_lengths, recv_ids = recv_lengths.to(self.device, non_blocking=True), recv_ids.to(self.device, non_blocking=True)
+        elif host_side:
+            recv_lengths = recv_lengths.to(self.device, non_blocking=True)         # ids stay on the host for the id mapper
         return recv_lengths.view(self.world, F, B), recv_ids, B
 
     def post_input_dist(self, lengths: torch.Tensor, ids: torch.Tensor):
@@ -372,8 +385,32 @@ class CollectiveShardedEmbeddingBagCollection(nn.Module):
             out = out * scale
         return KeyedTensor(self.feature_names, self.layout.feature_dims, out.to(self.out_dtype))
 
-    def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
+    # ----------------------------------------------------------------- pipelining
+    def _prepare(self, features: KeyedJaggedTensor):
         lengths, ids, B = self.input_dist(features)
         ids = self.post_input_dist(lengths, ids)
         orig = features.lengths().view(len(self.feature_names), B).to(self.device)
+        return lengths, ids.to(self.device), B, orig
+
+    def prefetch(self, features: KeyedJaggedTensor) -> None:
+        """Run input distribution and id mapping for a batch that ``forward`` will consume later (matched by the
+        identity of ``features``).  Device work goes to a side stream; ``forward`` makes the compute stream wait."""
+        if self._prefetch_stream is not None:
+            self._prefetch_stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self._prefetch_stream):
+                ctx = self._prepare(features)
+                ev = torch.cuda.Event()
+                ev.record(self._prefetch_stream)
+        else:
+            ctx, ev = self._prepare(features), None
+        self._prepared[id(features)] = ctx + (ev,)
+
+    def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
+        ctx = self._prepared.pop(id(features), None)
+        if ctx is None:
+            lengths, ids, B, orig = self._prepare(features)
+        else:
+            lengths, ids, B, orig, ev = ctx
+            if ev is not None:
+                torch.cuda.current_stream(self.device).wait_event(ev)
         return self.compute_and_output_dist(lengths, ids, B, orig)

@@ -53,18 +53,33 @@ def _split(b: Batch, rank, world) -> Batch:
     return Batch(b.dense_features[rank * Bl:(rank + 1) * Bl], kjt, b.labels[rank * Bl:(rank + 1) * Bl])
 
 
-def _train(rank, world, hashed, batches, plan=None, pg=None):
+def _train(rank, world, hashed, batches, plan=None, pg=None, hybrid=False):
     cfgs, model = _model(hashed)
     model.global_batch_size = BL * 2
     env = ShardingEnv(world, rank, pg)
     if plan is None:
         cons = {c.name: ParameterConstraints(sharding_types=["row_wise"], compute_kernels=["fused"]) for c in cfgs}
         plan = EmbeddingShardingPlanner(Topology(world_size=world, compute_device="cpu"), cons).plan(model)
-    dmp = DistributedModelParallel(model, env, torch.device("cpu"), plan,
+    sharders = None
+    if hybrid:
+        from recsdk_b200.parallel import get_default_hybrid_sharders
+        from recsdk_b200.optim import apply_optimizer_in_backward
+
+        host_pg = dist.new_group(backend="gloo")
+        sharders = get_default_hybrid_sharders(ShardingEnv.from_process_group(host_pg))
+        # the sharder reads the sparse optimizer the way the reference flow declares it
+        apply_optimizer_in_backward(torch.optim.Adagrad, model.model.sparse_arch.parameters(), {"lr": 0.01, "eps": 1e-8})
+    dmp = DistributedModelParallel(model, env, torch.device("cpu"), plan, sharders=sharders,
                                    sparse_optimizer=E.OptimizerSpec(kind=E.OPT_ROWWISE_ADAGRAD, lr=0.01, eps=1e-8))
     dense = KeyedOptimizerWrapper(dmp.dense_named_parameters(), lambda p: torch.optim.SGD(p, lr=0.1))
     opt = CombinedOptimizer([dmp.fused_optimizer, dense])
-    pipe = TrainPipelineSparseDist(dmp, opt, torch.device("cpu"), return_loss=True)
+    if hybrid:
+        from recsdk_b200.parallel import HybridTrainPipelineSparseDist
+
+        assert dmp.module.model.sparse_arch.input_pg is not None
+        pipe = HybridTrainPipelineSparseDist(dmp, opt, torch.device("cpu"), return_loss=True, pipe_n_batch=3)
+    else:
+        pipe = TrainPipelineSparseDist(dmp, opt, torch.device("cpu"), return_loss=True)
     it = iter([_split(b, rank, world) if world > 1 else b for b in batches])
     losses, logits = [], None
     for _ in range(STEPS):
@@ -81,7 +96,7 @@ def _batches(hashed):
     return [data.make_batch() for _ in range(STEPS)]
 
 
-def _worker(rank, world, hashed, mixed, init_file, ret):
+def _worker(rank, world, hashed, mixed, init_file, ret, hybrid=False):
     dist.init_process_group("gloo", init_method="file://" + init_file, rank=rank, world_size=world)
     try:
         torch.set_num_threads(2)
@@ -95,7 +110,7 @@ def _worker(rank, world, hashed, mixed, init_file, ret):
                 tabs["t%d" % i] = ParameterSharding(k, ranks=[i % world] if k == "table_wise" else None,
                                                     row_partition="block" if i == 3 else "mod")
             plan = ShardingPlan({"model.sparse_arch": tabs})
-        dmp, losses, logits = _train(rank, world, hashed, batches, plan, dist.group.WORLD)
+        dmp, losses, logits = _train(rank, world, hashed, batches, plan, dist.group.WORLD, hybrid)
         dist.all_reduce(losses)
         _, ref_losses, ref_logits = _train(0, 1, hashed, batches)
         ok = torch.allclose(losses, ref_losses, rtol=1e-4, atol=1e-4)
@@ -115,3 +130,11 @@ def test_dlrm_small_gloo_world2_matches_golden(hashed, mixed):
         mp.spawn(_worker, args=(2, hashed, mixed, os.path.join(d, "init"), ret), nprocs=2, join=True)
         assert ret.get(0) and ret.get(1), (ret.get("losses"), ret.get("ref"))
         assert ret["losses"][-1] < ret["losses"][0]
+
+
+def test_hybrid_host_input_dist_pipeline_matches_golden():
+    """Hash tables, id exchange on a separate gloo group from a worker thread three batches ahead."""
+    with tempfile.TemporaryDirectory() as d:
+        ret = mp.Manager().dict()
+        mp.spawn(_worker, args=(2, True, False, os.path.join(d, "init"), ret, True), nprocs=2, join=True)
+        assert ret.get(0) and ret.get(1), (ret.get("losses"), ret.get("ref"))
