@@ -1,0 +1,42 @@
+"""CPU affinity helpers: pin the calling process (and the threads it spawns afterwards) to the cores that sit next
+to its GPU, so host-side input processing does not migrate across NUMA nodes.
+Reference: ``training/common/python/perf_factory/bind_cpu.py:13-107`` (decorator style)."""
+from __future__ import annotations
+
+import functools
+import os
+from typing import Callable, List, Optional, Sequence
+
+
+def cores_for_rank(local_rank: int, local_world_size: int, cores: Optional[Sequence[int]] = None, reserve: int = 0) -> List[int]:
+    """Even contiguous split of the usable cores among the local ranks; ``reserve`` cores per rank are left out
+    (for the framework's own IO threads)."""
+    usable = sorted(cores) if cores is not None else sorted(os.sched_getaffinity(0))
+    if local_world_size <= 0 or not (0 <= local_rank < local_world_size):
+        raise ValueError("bad local rank / world size")
+    per = max(1, len(usable) // local_world_size)
+    mine = usable[local_rank * per:(local_rank + 1) * per] or usable[-1:]
+    return mine[reserve:] if len(mine) > reserve else mine
+
+
+def bind_current_process(cores: Sequence[int]) -> List[int]:
+    os.sched_setaffinity(0, set(cores))
+    return sorted(os.sched_getaffinity(0))
+
+
+def bind_cpu(local_rank: Optional[int] = None, local_world_size: Optional[int] = None, reserve: int = 0) -> Callable:
+    """Decorator: run the function with the process pinned to its rank's cores (taken from ``LOCAL_RANK`` /
+    ``LOCAL_WORLD_SIZE`` when not given); the previous affinity is restored afterwards."""
+    def deco(fn: Callable) -> Callable:
+        @functools.wraps(fn)
+        def wrapped(*a, **kw):
+            lr = int(os.environ.get("LOCAL_RANK", "0")) if local_rank is None else local_rank
+            lws = int(os.environ.get("LOCAL_WORLD_SIZE", "1")) if local_world_size is None else local_world_size
+            before = os.sched_getaffinity(0)
+            try:
+                bind_current_process(cores_for_rank(lr, lws, sorted(before), reserve))
+                return fn(*a, **kw)
+            finally:
+                os.sched_setaffinity(0, before)
+        return wrapped
+    return deco
