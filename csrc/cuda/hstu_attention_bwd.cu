@@ -64,7 +64,7 @@ constexpr int SMEM_BYTES = TILE * 8 /*K,V,2x(Q,dO),dS(2 chunks)*/ + 16 * 2 * 32 
 // gradient partial sums.  With h = alpha (S + bias) / 2 and th = tanh(h):
 //   P  = scale SiLU(2h)                 = hs + hs th,                hs = h scale
 //   dS = dP scale alpha SiLU'(2h)       = dP (sg + sg g),            sg = scale alpha (1 + th) / 2,  g = h - h th
-// dts: run-length sums per thread (the bucket of |ts_i - ts_j| changes slowly along a key row);
+// dts: run-length sums per thread (the bucket of |ts_i - ts_j| changes slowly along a key row), kept across tiles;
 // dpos: the chunk's anti-diagonals (i - j constant) are summed across lanes with one shuffle per element: lane o owns
 //       diagonals o and o + 32 of the 63, element (e, lane) lies on diagonal e - lane + 31.
 template <bool BT, bool BP, bool WDT, bool WDP, bool MASKED>

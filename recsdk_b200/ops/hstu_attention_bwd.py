@@ -20,8 +20,9 @@ from .hstu_attention import hstu_mask, time_buckets
 
 
 def hstu_attn_bwd(dout, q, k, v, q_offsets, k_offsets, alpha: float, scale: float, causal: bool, num_context,
-                  num_target, gs: int, ts, ts_w, ts_divisor: float, pos_w, max_len_k: Optional[int] = None):
-    """-> (dq, dk, dv, d_ts_w, d_pos_w)."""
+                  num_target, gs: int, ts, ts_w, ts_divisor: float, pos_w, max_len_k: Optional[int] = None,
+                  want_dts: bool = True, want_dpos: bool = True):
+    """-> (dq, dk, dv, d_ts_w, d_pos_w); the bias gradients are None when not wanted (or when there is no such bias)."""
     ok = (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[2] == 64 and v.shape[2] == 64 and k.shape[1] == q.shape[1]
           and (pos_w is None or pos_w.numel() <= 4096) and (ts_w is None or ts_w.numel() <= 192))
     if not ok:
@@ -41,8 +42,8 @@ def hstu_attn_bwd(dout, q, k, v, q_offsets, k_offsets, alpha: float, scale: floa
     dk = torch.empty(Tk, H, D, dtype=q.dtype, device=dev)
     dv = torch.empty(Tk, H, D, dtype=q.dtype, device=dev)
     ts_, tsw_, pw_ = f32(ts), f32(ts_w), f32(pos_w)
-    dtw = torch.zeros_like(tsw_) if (tsw_ is not None and ts_ is not None) else None
-    dpw = torch.zeros_like(pw_) if pw_ is not None else None
+    dtw = torch.zeros_like(tsw_) if (want_dts and tsw_ is not None and ts_ is not None) else None
+    dpw = torch.zeros_like(pw_) if (want_dpos and pw_ is not None) else None
     nc, nt = i32(num_context), i32(num_target)
     rc = _lib.lib().rb_hstu_attn_bwd(
         q.data_ptr(), q.stride(0), dout.data_ptr(), dout.stride(0), Tq, k.data_ptr(), v.data_ptr(), k.stride(0), Tk,

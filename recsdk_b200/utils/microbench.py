@@ -58,6 +58,7 @@ def main() -> None:
     ap.add_argument("--len", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=8)
     ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--bias-grads", default="both", choices=["both", "ts", "pos", "none"])
     ap.add_argument("--rows", type=int, default=10_000_000)
     ap.add_argument("--batch", type=int, default=65536)
     ap.add_argument("--tables", type=int, default=26)
@@ -100,12 +101,14 @@ def main() -> None:
         else:
             do = torch.randn_like(q)
             fn = lambda: hstu_attn_bwd(do, q, k, v, off, off, 0.125, 1.0 / L, True, None, None, 0, kw["ts"], kw["ts_w"],  # noqa: E731
-                                       0.301, kw["pos_w"], max_len_k=L)
+                                       0.301, kw["pos_w"], max_len_k=L, want_dts=a.bias_grads in ("both", "ts"),
+                                       want_dpos=a.bias_grads in ("both", "pos"))
             mm = 5
         ms = _time(fn, a.iters)
         pairs = S * H * (L * (L + 128) / 2)                     # causal (block-granular) score elements
         fl = pairs * D * 2 * mm
-        out.update(ms=ms, tflops=fl / ms / 1e9, score_elems_per_s=pairs / (ms / 1e3), shape=[S, L, H, D], bias=a.bias)
+        out.update(ms=ms, tflops=fl / ms / 1e9, score_elems_per_s=pairs / (ms / 1e3), shape=[S, L, H, D], bias=a.bias,
+                   **({"bias_grads": a.bias_grads} if a.what == "hstu_bwd" and a.bias else {}))
     elif a.what == "tbe_fwd":
         from ..ops import embedding_ops as E
 

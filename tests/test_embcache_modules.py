@@ -1,6 +1,7 @@
 """Multi-tier tables: a tiny device cache over the host table must train exactly like a plain full table
 (rows migrate between tiers with their optimizer state), survive save / load, and honour admission."""
 import numpy as np
+import pytest
 import torch
 
 from recsdk_b200.embcache import (AdmitAndEvictConfig, EmbCacheEmbeddingBagCollection, EmbCacheEmbeddingBagConfig,
@@ -21,14 +22,14 @@ def _batch(g, B=6):
     return KeyedJaggedTensor(["f0", "f1", "f2"], vals, lengths=lens)
 
 
-def _sharded(tables, cache_rows, opt=torch.optim.Adagrad, lr=0.1):
-    ebc = EmbCacheEmbeddingBagCollection(tables, 1, 6, [3, 3], device="cpu", embedding_optimizer_cls=opt)
-    return EmbCacheShardedEmbeddingBagCollection(ebc, ShardingEnv(1, 0, None), "cpu", ebc.optimizer_spec(lr=lr), cache_rows=cache_rows)
+def _sharded(tables, cache_rows, opt=torch.optim.Adagrad, lr=0.1, device="cpu"):
+    ebc = EmbCacheEmbeddingBagCollection(tables, 1, 6, [3, 3], device=device, embedding_optimizer_cls=opt)
+    return EmbCacheShardedEmbeddingBagCollection(ebc, ShardingEnv(1, 0, None), device, ebc.optimizer_spec(lr=lr), cache_rows=cache_rows)
 
 
 def _train(m, steps, seed=0):
     g = torch.Generator().manual_seed(seed)
-    w = torch.randn(40, generator=torch.Generator().manual_seed(9))
+    w = torch.randn(40, generator=torch.Generator().manual_seed(9)).to(m.device)
     losses = []
     for _ in range(steps):
         kt = m(_batch(g))
@@ -47,6 +48,18 @@ def test_small_cache_equals_big_cache():
         assert small.stats["swap_out"] > 0 and big.stats["swap_out"] == 0
         keys = list(range(60))
         assert torch.allclose(small.host_rows("t1", keys), big.host_rows("t1", keys), atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_small_cache_equals_big_cache_gpu():
+    """Same scenario with the cache tensors, the gather / scatter kernels and the lookup on the GPU."""
+    small = _sharded(_tables(), [40, 64], device="cuda")
+    big = _sharded(_tables(), [1001, 501], device="cuda")
+    la, lb = _train(small, 12), _train(big, 12)
+    assert np.allclose(la, lb, rtol=1e-4, atol=1e-5), (la, lb)
+    assert small.stats["swap_out"] > 0
+    keys = list(range(60))
+    assert torch.allclose(small.host_rows("t1", keys), big.host_rows("t1", keys), atol=1e-5)
 
 
 def test_save_load_roundtrip(tmp_path):
