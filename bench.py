@@ -116,6 +116,21 @@ def main() -> None:
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return
+    if args.impl == "torch":
+        # comparison arm: the same model and step in stock PyTorch + NCCL + cuBLAS (no code of this package)
+        if args.model == "dlrm":
+            from baseline.torch_dlrm import run as run_torch_dlrm
+
+            run_torch_dlrm(args, table_rows, ClockSampler)
+        elif args.model == "hstu":
+            from baseline.torch_hstu import run as run_torch_hstu
+
+            run_torch_hstu(args, ClockSampler)
+        else:
+            from baseline.torch_hstu import run_inference as run_torch_hstu_inference
+
+            run_torch_hstu_inference(args, ClockSampler)
+        return
     if args.model == "hstu":
         from recsdk_b200.models.hstu_bench import run_hstu_bench
 

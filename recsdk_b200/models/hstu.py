@@ -88,16 +88,23 @@ class HSTU(nn.Module):
         return hstu_ops.ln_mul(x, None, self.norm_out_w, self.norm_out_b)
 
     def forward(self, features: KeyedJaggedTensor, offsets: torch.Tensor, max_len: int,
-                timestamps: Optional[torch.Tensor] = None, global_tokens: Optional[int] = None):
+                timestamps: Optional[torch.Tensor] = None, global_tokens: Optional[int] = None,
+                predict_positions: Optional[torch.Tensor] = None):
+        """``predict_positions``: optional int64 indices of every token that is not the last of its sequence (the
+        positions that have a next item to predict); passing them from the host side of the input pipeline keeps
+        the step free of a device-to-host synchronisation."""
         emb = self.embedding(features)
         x0 = emb["item"].values().to(self.dtype)                      # [T, d]
         neg = emb["neg"].values().to(self.dtype)                      # [num_negatives, d]
         h = self.encode(x0, offsets, max_len, timestamps)
         # position t predicts the item at t + 1 of the same sequence
-        T = x0.shape[0]
-        last = torch.zeros(T, dtype=torch.bool, device=x0.device)
-        last[offsets[1:] - 1] = True
-        keep = (~last).nonzero(as_tuple=True)[0]
+        if predict_positions is not None:
+            keep = predict_positions
+        else:
+            T = x0.shape[0]
+            last = torch.zeros(T, dtype=torch.bool, device=x0.device)
+            last[offsets[1:] - 1] = True
+            keep = (~last).nonzero(as_tuple=True)[0]
         hq = h[keep]
         pos = x0[keep + 1]
         pos_logit = (hq.float() * pos.float()).sum(-1, keepdim=True)

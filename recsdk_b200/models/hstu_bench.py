@@ -27,7 +27,10 @@ def make_batch(B: int, gen: torch.Generator, n_items: int = 100_000_000, n_neg: 
     ts = ts - torch.repeat_interleave(ts[off[:-1]], ln)             # restart the clock per sequence
     lengths = torch.cat([ln, torch.tensor([n_neg] + [0] * (B - 1))])
     kjt = KeyedJaggedTensor(["item", "neg"], torch.cat([ids, neg]), lengths=lengths, stride=B)
-    return kjt, off, int(ln.max()), ts.float(), T
+    last = torch.zeros(T, dtype=torch.bool)
+    last[off[1:] - 1] = True
+    keep = (~last).nonzero(as_tuple=True)[0]                         # positions that have a next item to predict
+    return kjt, off, int(ln.max()), ts.float(), T, keep
 
 
 def build(device, env, cfg=None, capacity: int = 1 << 22, lr: float = 1e-3):
@@ -66,7 +69,7 @@ def run_hstu_bench(args) -> None:
     n_batches = args.steps + max(args.warmup, 3)
     host = [make_batch(B, gen, max_len=4096 if not args.small else 512) for _ in range(min(n_batches, 12))]
     pin = lambda t: t.pin_memory()  # noqa: E731
-    host = [(k.pin_memory(), pin(o), m, pin(ts), T) for (k, o, m, ts, T) in host]
+    host = [(k.pin_memory(), pin(o), m, pin(ts), T, pin(kp)) for (k, o, m, ts, T, kp) in host]
     dense_params = [p for p in model.parameters() if p.requires_grad and not getattr(p, "_in_backward_optimizers", False)]
     flat_ids = {id(m.flat_param) for m in opt.flat_modules}
 
@@ -80,10 +83,10 @@ def run_hstu_bench(args) -> None:
                 dist.all_reduce(p.grad)
 
     def step(i):
-        k, o, m, ts, T = host[i % len(host)]
+        k, o, m, ts, T, kp = host[i % len(host)]
         kd, od, td = k.to(dev, non_blocking=True), o.to(dev, non_blocking=True), ts.to(dev, non_blocking=True)
         opt.zero_grad()
-        loss = model(kd, od, m, td)
+        loss = model(kd, od, m, td, predict_positions=kp.to(dev, non_blocking=True))
         loss.backward()
         sync_grads()
         opt.step()
@@ -125,7 +128,7 @@ def run_hstu_bench(args) -> None:
         ts_ = t.clone()
         dist.all_reduce(ts_, op=dist.ReduceOp.SUM)
         ms, tokens = float(tm[0]), float(ts_[1])
-    h2d = sum(k.values().numel() * 8 + o.numel() * 8 + ts.numel() * 4 for (k, o, m, ts, T) in host) / len(host)
+    h2d = sum(k.values().numel() * 8 + o.numel() * 8 + ts.numel() * 4 + kp.numel() * 8 for (k, o, m, ts, T, kp) in host) / len(host)
     if rank == 0:
         val = tokens / (ms / 1e3)
         print(json.dumps({

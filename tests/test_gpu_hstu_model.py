@@ -49,7 +49,7 @@ def test_hstu_trains():
     cfg = HSTUConfig(num_layers=2, d_model=256, num_heads=4, head_dim=64, max_seq_len=512, num_negatives=64)
     model, opt = build(DEV, ShardingEnv(1, 0), cfg, capacity=1 << 14, lr=3e-3)
     gen = torch.Generator().manual_seed(0)
-    k, off, m, ts, T = make_batch(4, gen, n_items=2000, n_neg=64, max_len=512)
+    k, off, m, ts, T, _keep = make_batch(4, gen, n_items=2000, n_neg=64, max_len=512)
     losses = []
     for _ in range(12):
         opt.zero_grad()
