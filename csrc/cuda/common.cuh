@@ -223,6 +223,11 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, int a_mn_major, 
 // misc math
 // ----------------------------------------------------------------------------
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+// fp32 vector reduction into global memory: one 16-byte atomic instead of four scalar ones (address 16-byte aligned)
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {

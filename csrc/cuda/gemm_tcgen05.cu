@@ -215,9 +215,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         }
         if (p.epi == EPI_F32_ATOMIC) {
           float* o = reinterpret_cast<float*>(p.out) + m * p.ldc + n0;
+          if (full_chunk && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (full_chunk || n0 + j < p.N) atomicAdd(o + j, v[j]);
+            for (int j = 0; j < 32; j += 4) rb::red_add_v4(o + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) atomicAdd(o + j, v[j]);
+          }
           continue;
         }
         if (p.epi == EPI_F32) {

@@ -51,9 +51,7 @@ __device__ __forceinline__ bool attends(int pi, int j, int len, int causal, int 
   }
   return ok;
 }
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
+using rb::red_add_v4;
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 constexpr int POS_HIST = 4096;

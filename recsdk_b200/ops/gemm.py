@@ -88,11 +88,18 @@ def gemm16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool =
 
 
 def pick_splits(M: int, N: int, K: int, num_sms: int = 148) -> int:
-    """Split-K factor for a weight-gradient GEMM (small M x N, long contraction)."""
+    """Split-K factor for a weight-gradient GEMM (small M x N, long contraction) on the persistent kernel: work items
+    (tiles x splits) run in rounds of ``num_sms``; an item costs its k-blocks plus a fixed epilogue (the fp32 vector
+    reductions of a 128 x BN tile, about eight k-blocks' worth).  Pick the split count with the shortest schedule."""
     bn = 256 if N > 128 else (128 if N > 64 else 64)
     tiles = ((M + 127) // 128) * ((N + bn - 1) // bn)
     kb = (K + 63) // 64
-    if tiles >= num_sms:
+    if tiles >= num_sms or kb <= 8:
         return 1
-    s = max(1, min(kb, (2 * num_sms + tiles - 1) // tiles))
-    return s
+    best, best_cost = 1, None
+    for s in range(1, min(kb, 64) + 1):
+        rounds = (tiles * s + num_sms - 1) // num_sms
+        cost = rounds * ((kb + s - 1) // s + 8)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
