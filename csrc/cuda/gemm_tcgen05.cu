@@ -43,6 +43,7 @@ struct GemmParams {
   int epi;
   int is_bf16;
   float alpha;
+  float* colsum;          // optional [N] fp32: += column sums of the epilogue's output values (bias gradients)
   int* status;
 };
 
@@ -194,7 +195,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         rb::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + buf * BN + c * 32, r);
         rb::tmem_ld_wait();
         const int n0 = tn * BN + c * 32;
-        if (!row_ok || n0 >= p.N) continue;
+        if (n0 >= p.N || (!row_ok && p.colsum == nullptr)) continue;
         const bool full_chunk = (n0 + 32 <= p.N);
         float v[32];
 #pragma unroll
@@ -248,7 +249,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         } else if (p.epi == EPI_BF16_MASK || p.epi == EPI_BF16_DSILU) {
           const uint16_t* a = reinterpret_cast<const uint16_t*>(p.aux) + m * p.ld_aux + n0;
           uint16_t araw[32];
-          if (full_chunk && ((reinterpret_cast<uintptr_t>(a) & 15) == 0)) {
+          if (!row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) araw[j] = 0;
+          } else if (full_chunk && ((reinterpret_cast<uintptr_t>(a) & 15) == 0)) {
 #pragma unroll
             for (int j = 0; j < 4; ++j)
               reinterpret_cast<uint4*>(araw)[j] = __ldg(reinterpret_cast<const uint4*>(a) + j);
@@ -268,6 +272,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
               v[j] *= s * (1.f + x * (1.f - s));
             }
           }
+        }
+        if (p.colsum != nullptr) {
+          // column sums over the warp's 32 rows by recursive halving: after the step of width w a lane keeps the w
+          // columns selected by its lane bit; at the end lane l holds column l summed over all rows
+          float cs[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) cs[j] = row_ok ? v[j] : 0.f;
+#pragma unroll
+          for (int w = 16; w >= 1; w >>= 1) {
+            const bool upper = (lane & w) != 0;
+#pragma unroll
+            for (int j = 0; j < w; ++j) {
+              const float send = upper ? cs[j] : cs[j + w];
+              const float keep = upper ? cs[j + w] : cs[j];
+              cs[j] = keep + __shfl_xor_sync(0xffffffffu, send, w);
+            }
+          }
+          if (n0 + lane < p.N && cs[0] != 0.f) atomicAdd(p.colsum + n0 + lane, cs[0]);
+          if (!row_ok) continue;
         }
         uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + m * p.ldc + n0;
         uint32_t pk[16];
@@ -354,8 +377,9 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, in
 RB_API int rb_gemm16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
                      void* out, long long ldc, int M, int N, int K, const float* bias, const void* aux,
                      long long ld_aux, int epi, float alpha, int splits, int is_bf16, int num_sms,
-                     int* status, cudaStream_t stream) {
+                     float* colsum, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (colsum != nullptr && (epi == EPI_F32_ATOMIC || epi == EPI_F32)) return -5;   // column sums ride on the 16-bit epilogues
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return -3;
   const int bn = (N > 128) ? 256 : ((N > 64) ? 128 : 64);
@@ -379,7 +403,7 @@ RB_API int rb_gemm16(const void* A, long long lda, int a_mn, const void* B, long
   p.M = M; p.N = N; p.K = K;
   p.splits = splits; p.kb_per_split = kbps;
   p.out = out; p.ldc = ldc; p.bias = bias; p.aux = aux; p.ld_aux = ld_aux;
-  p.epi = epi; p.is_bf16 = is_bf16; p.alpha = alpha; p.status = status;
+  p.epi = epi; p.is_bf16 = is_bf16; p.alpha = alpha; p.colsum = colsum; p.status = status;
 
   const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * splits;
   if (num_sms <= 0) num_sms = 148;

@@ -67,19 +67,24 @@ class _FusedMLPFn(torch.autograd.Function):
             dz = dz * (acts[L] > 0).to(dz.dtype)
         nsm = 148
         dx = None
+        bias_done = False            # this layer's bias gradient already came out of the GEMM that produced dz
         for l in range(L - 1, -1, -1):
             x_l = acts[l]
             M = x_l.shape[0]
             N, Kp = mlp.w16[l].shape
             gemm.gemm16(dz, x_l, a_mn=True, b_mn=True, out=mlp.wgrad[l], epi=gemm.EPI_F32_ATOMIC,
                         splits=gemm.pick_splits(N, Kp, M, nsm))
-            if mlp.bgrad[l] is not None:
+            if mlp.bgrad[l] is not None and not bias_done:
                 dense_ops.colsum16(dz, mlp.bgrad[l])
+            bias_done = False
             if l > 0:
+                # dz of layer l-1 and, in the same epilogue, its column sums (= that layer's bias gradient)
+                cs = mlp.bgrad[l - 1] if dz.is_cuda else None
+                bias_done = cs is not None
                 if mlp.relu[l - 1]:
-                    dz = gemm.gemm16(dz, mlp.w16[l], b_mn=True, epi=gemm.EPI_RELU_MASK, aux=x_l)
+                    dz = gemm.gemm16(dz, mlp.w16[l], b_mn=True, epi=gemm.EPI_RELU_MASK, aux=x_l, colsum_out=cs)
                 else:
-                    dz = gemm.gemm16(dz, mlp.w16[l], b_mn=True)
+                    dz = gemm.gemm16(dz, mlp.w16[l], b_mn=True, colsum_out=cs)
             elif ctx.x_needs_grad:
                 dx = gemm.gemm16(dz, mlp.w16[l], b_mn=True)
         return dx, None, None, None

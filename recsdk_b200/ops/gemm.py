@@ -50,12 +50,14 @@ def _ref(a, b, a_mn, b_mn, bias, aux, epi, alpha, out, out_dtype):
 def gemm16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
            out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
            aux: Optional[torch.Tensor] = None, epi: int = EPI_NONE, alpha: float = 1.0,
-           splits: int = 1) -> torch.Tensor:
+           splits: int = 1, colsum_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = epi(alpha * A @ B^T)``; ``a``/``b`` are bf16 or fp16 2-D tensors with unit inner stride.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]`` when ``b_mn``).
     ``out`` may be a strided row view (e.g. a column slice of a wider buffer).  fp32 epilogues
     (``EPI_F32``, ``EPI_F32_ATOMIC``) need an fp32 ``out``; ``EPI_F32_ATOMIC`` accumulates into it.
+    ``colsum_out`` (fp32 ``[N]``, 16-bit epilogues only) accumulates the column sums of the output values - the bias
+    gradient when the output is a layer's ``dZ`` - inside the same epilogue.
     """
     assert a.dim() == 2 and b.dim() == 2 and a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16)
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
@@ -81,7 +83,7 @@ def gemm16(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool =
     rc = _lib.lib().rb_gemm16(
         a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
         out.data_ptr(), out.stride(0), M, N, K, _lib.ptr(bias), _lib.ptr(aux), ld_aux, epi, float(alpha),
-        int(splits), int(a.dtype == torch.bfloat16), _lib.num_sms(a.device),
+        int(splits), int(a.dtype == torch.bfloat16), _lib.num_sms(a.device), _lib.ptr(colsum_out),
         _lib.status_tensor(a.device).data_ptr(), _lib.stream_ptr(a.device))
     _lib.check(rc, "rb_gemm16")
     return out

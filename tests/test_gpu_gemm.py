@@ -67,3 +67,22 @@ def test_gemm_strided_output():
     _check(wide[:, 128:256], a.float() @ b.float().t(), 2e-2)
     assert wide[:, :128].abs().max().item() == 0 and wide[:, 256:].abs().max().item() == 0
     _lib.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K,epi", [(1000, 520, 256, 2), (8192, 1024, 512, 0), (77, 40, 64, 2)])
+def test_fused_column_sums(M, N, K, epi):
+    """The epilogue's column sums equal the column sums of the rounded output (bias gradient of the produced dZ)."""
+    from recsdk_b200.ops import gemm as G
+
+    torch.manual_seed(M)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    aux = torch.randn(M, N, device="cuda").bfloat16() if epi == 2 else None
+    cs = torch.zeros(N, dtype=torch.float32, device="cuda")
+    out = G.gemm16(a, b, epi=epi, aux=aux, colsum_out=cs)
+    ref = (a.float() @ b.float().t())
+    if epi == 2:
+        ref = ref * (aux.float() > 0)
+    assert torch.allclose(out.float(), ref, atol=0.5, rtol=2e-2)
+    assert torch.allclose(cs, ref.sum(0), atol=2e-2 * ref.abs().sum(0).max().item() / 10 + 1.0, rtol=2e-2)
