@@ -245,6 +245,9 @@ def main() -> None:
         one_step(i)
     sync_all()
     lc1 = _lib.launch_count
+    from recsdk_b200.utils import trace as _trace
+
+    _trace.reset()
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s0.record()
     for i in range(args.steps):
@@ -263,6 +266,12 @@ def main() -> None:
     launches = pipe.launches_per_step * args.steps if pipe._graph is not None and hasattr(pipe, "launches_per_step") \
         else (lc2 - lc1)
     kjt_bytes = host_batches[0].nbytes()
+    from recsdk_b200.utils import trace
+
+    phases = trace.report() if trace.ENABLED else None
+    if rank == 0 and phases:
+        print("phase timing (device time from each mark to the next, mean us): " +
+              json.dumps({k: round(v["mean_us"], 1) for k, v in phases.items()}), file=sys.stderr)
     if rank == 0:
         out = {
             "metric": "DLRM train samples/sec/box", "value": GB / (step_ms / 1e3), "unit": "samples/s",

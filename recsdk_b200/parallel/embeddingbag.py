@@ -30,6 +30,7 @@ from ..ops import _lib
 from ..ops import embedding_ops as E
 from ..optim import FusedOptimizerStub
 from ..sparse.jagged_tensor import KeyedJaggedTensor, KeyedTensor
+from ..utils import trace
 from .comm import PeerGroup, ShardingEnv
 
 
@@ -293,16 +294,22 @@ class ShardedEmbeddingBagCollection(nn.Module):
         assert B == cap_b or self.max_local_batch == 0 or B <= cap_b
         Bg = B * self.world
         row_bytes = B * 8
+        trace.mark("emb.id_push")
         self.peer.allgather_push_2d(self._gather_ids, idx.view(T, B), Bg * 8, self.rank * row_bytes)
+        trace.mark("emb.id_barrier")
         self.peer.barrier()
+        trace.mark("emb.sort")
         gathered = self._gather_ids.local.view(torch.int64)[: T * Bg]
         dctx.segments = self._sorter.run(self.layout, self.dev, gathered, None, Bg)
+        trace.mark("emb.sort_done")
         return dctx
 
     # --------------------------------------------------------------- compute
     def _lookup(self, dctx: EmbeddingDistContext) -> torch.Tensor:
         out = torch.empty(dctx.B_local, self.layout.total_D, dtype=self.out_dtype, device=self.device)
+        trace.mark("emb.lookup")
         E.tbe_forward(self.layout, self.dev, dctx.indices, dctx.offsets, dctx.B_local, self.pooling, self.w_dtype, out)
+        trace.mark("dense.forward")
         return out
 
     def _backward_update(self, dctx: EmbeddingDistContext, dout: torch.Tensor) -> None:
@@ -316,12 +323,16 @@ class ShardedEmbeddingBagCollection(nn.Module):
                                   dctx.global_offsets, self.pooling, self.weights, self.state1, self.state2,
                                   self.s_offsets, self.opt, self._step, self._bwd_ws)
             return
+        trace.mark("emb.grad_publish")
         gb = self._grad_buf.local.view(dout.dtype)[: dout.numel()].view(dout.shape)
         gb.copy_(dout)
+        trace.mark("emb.grad_barrier")
         self.peer.barrier()
+        trace.mark("emb.backward_update")
         E.tbe_backward_update(self.layout, self.dev, dctx.segments, self._grad_ptrs, self.layout.total_D, dout.dtype,
                               dctx.B_local, None, self.pooling, self.weights, self.state1, self.state2,
                               self.s_offsets, self.opt, self._step, self._bwd_ws)
+        trace.mark("dense.backward_rest")
 
     def _static_ptr(self, g: torch.Tensor) -> torch.Tensor:
         # under CUDA-graph capture the gradient tensor's address is stable across replays

@@ -24,6 +24,7 @@ from ..modules.embedding_modules import EmbeddingBagCollection
 from ..modules.hash_embeddingbag import HashEmbeddingBagCollection
 from ..ops import embedding_ops as E
 from ..optim import CombinedOptimizer
+from ..utils import trace
 from .comm import PeerGroup, ShardingEnv
 from .collective_embeddingbag import CollectiveShardedEmbeddingBagCollection
 from .embeddingbag import ParameterSharding, ShardedEmbeddingBagCollection
@@ -167,6 +168,7 @@ class DistributedModelParallel(nn.Module):
         """Average dense gradients over the data-parallel ranks (call between backward and step)."""
         if self.world == 1:
             return
+        trace.mark("dense.grad_allreduce")
         if self._grad_buf is not None:
             self.peer.allreduce_mean_f32(self._grad_buf, self._grad_elems, scale=1.0)
         for p in self.module.parameters():

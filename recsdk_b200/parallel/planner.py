@@ -74,8 +74,8 @@ class EmbeddingShardingPlanner:
     * tables whose constraint names a sharding type get it;
     * otherwise tables larger than ``row_wise_threshold_bytes`` (default: 1/8 of a GPU's budget or
       more than a fair share) are row-wise, tiny tables (< ``dp_threshold_bytes``) data-parallel when
-      allowed, and the rest table-wise, assigned largest-first to the least-loaded rank
-      (load = bytes, a proxy for both HBM use and lookup traffic).
+      allowed, and the rest table-wise, dealt out so that every rank owns the same number of them
+      (lookup / update work is per id, not per row) in snake order of size (bytes stay even too).
     """
 
     def __init__(self, topology: Optional[Topology] = None, constraints: Optional[Dict[str, ParameterConstraints]] = None,
@@ -120,8 +120,19 @@ class EmbeddingShardingPlanner:
                 tw.append((nb, c))
             else:
                 raise NotImplementedError("sharding type %r" % st)
-        for nb, c in sorted(tw, key=lambda x: -x[0]):
-            r = min(range(W), key=lambda i: load[i])
+        # Table-wise tables concentrate a whole feature's lookups and updates on their owner.  With the pull design a
+        # row-wise table costs no extra traffic, so only as many tables stay table-wise as can be dealt out evenly
+        # (the same number per rank); the largest left-overs become row-wise.  Dealing in snake order over the size
+        # ranking also evens out the bytes.
+        tw.sort(key=lambda x: -x[0])
+        extra = len(tw) % W
+        for nb, c in tw[:extra]:
+            out[c.name] = ParameterSharding("row_wise", row_partition="mod")
+            for r in range(W):
+                load[r] += nb / W
+        for i, (nb, c) in enumerate(tw[extra:]):
+            rnd, pos = divmod(i, W)
+            r = pos if rnd % 2 == 0 else W - 1 - pos
             load[r] += nb
             out[c.name] = ParameterSharding("table_wise", ranks=[r])
         if max(load) > self.topology.hbm_cap:

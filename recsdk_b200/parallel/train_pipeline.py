@@ -20,6 +20,9 @@ from torch.autograd.profiler import record_function
 from ..utils.data import Batch
 
 
+from ..utils import trace  # noqa: E402
+
+
 class TrainPipelineBase:
     """No overlap: fetch, copy, step.  Works on CPU as well."""
 
@@ -28,13 +31,18 @@ class TrainPipelineBase:
         self._return_loss = return_loss
 
     def _step(self, batch) -> Tuple[torch.Tensor, Any]:
+        trace.mark("step.zero_grad")
         self._optimizer.zero_grad()
+        trace.mark("step.input_dist")
         loss, out = self._model(batch)
+        trace.mark("dense.backward")
         loss.backward()
         sync = getattr(self._model, "sync_dense_grads", None)
         if sync is not None:
             sync()
+        trace.mark("step.optimizer")
         self._optimizer.step()
+        trace.mark("step.end")
         # hand back a graph-free loss: a live autograd graph would pin its AccumulateGrad nodes (and
         # the stream they were created on) across steps, which breaks a later CUDA-graph capture
         return loss.detach(), out
