@@ -55,8 +55,15 @@ using rb::red_add_v4;
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 constexpr int POS_HIST = 4096;
+// The CTA-level bias-gradient histograms are 64-bit fixed point (value * 2^36): integer atomics on shared memory are a
+// single instruction, while a float add there is a compare-and-swap loop that serialises on equal addresses.
+constexpr float FIX_SCALE = 68719476736.f;
+__device__ __forceinline__ void hist_add(long long* h, float v) {
+  atomicAdd(reinterpret_cast<unsigned long long*>(h), static_cast<unsigned long long>(__float2ll_rn(v * FIX_SCALE)));
+}
+__device__ __forceinline__ float hist_value(long long h) { return static_cast<float>(static_cast<double>(h) * (1.0 / 68719476736.0)); }
 constexpr int SMEM_BYTES = TILE * 8 /*K,V,2x(Q,dO),dS(2 chunks)*/ + 16 * 2 * 32 * 4 /*ts*/ + 768 /*ts_w*/ + 768 /*d ts_w*/ +
-                           POS_HIST * 4 + 256 /*barriers*/ + 16 * 64 * 4 /*distance-bias windows*/ + 1024;
+                           POS_HIST * 8 + 768 /*64-bit d ts_w*/ + 256 /*barriers*/ + 16 * 64 * 4 /*distance-bias windows*/ + 1024;
 
 // One warp's 32 (keys, one per thread) x 32 (queries, e) chunk: S^T, dP^T -> P^T, dS^T (packed bf16) and the bias
 // gradient partial sums.  With h = alpha (S + bias) / 2 and th = tanh(h):
@@ -67,7 +74,7 @@ constexpr int SMEM_BYTES = TILE * 8 /*K,V,2x(Q,dO),dS(2 chunks)*/ + 16 * 2 * 32 
 //       diagonals o and o + 32 of the 63, element (e, lane) lies on diagonal e - lane + 31.
 template <bool BT, bool BP, bool WDT, bool WDP, bool MASKED>
 __device__ __forceinline__ void bwd_chunk(const uint32_t (&rs)[16], const uint32_t (&rd)[16], uint32_t* pk, uint32_t* dk16, int e0,
-                                          int& run_bucket, float& run_sum, float ts_j, const float* my_ts, const float* tsw_s, float* dtsw_s, const float* my_pos,
+                                          int& run_bucket, float& run_sum, float ts_j, const float* my_ts, const float* tsw_s, long long* dtsw_s, const float* my_pos,
                                           int lane, float k_log, int cap, float half_alpha, float scale, float half_sa, int pi0,
                                           int i0, int j, int len_q, int len_k, int causal, int nctx, int ntgt, int gs,
                                           float& acc_lo, float& acc_hi) {
@@ -121,7 +128,7 @@ __device__ __forceinline__ void bwd_chunk(const uint32_t (&rs)[16], const uint32
       if (WDT) {
         const int bk = static_cast<int>((bkp[e >> 2] >> (8 * (e & 3))) & 0xffu);
         if (bk != run_bucket) {
-          if (run_bucket >= 0 && run_sum != 0.f) atomicAdd(dtsw_s + run_bucket, run_sum);
+          if (run_bucket >= 0 && run_sum != 0.f) hist_add(dtsw_s + run_bucket, run_sum);
           run_bucket = bk; run_sum = 0.f;
         }
         run_sum += ds;
@@ -172,9 +179,9 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* ds_s = smem + 6 * TILE;                                 // 2 chunks of [128 keys][64 q]
   float* ts_s = reinterpret_cast<float*>(smem + 8 * TILE);         // [4 warps][2][128]
   float* tsw_s = ts_s + 1024;                                      // [192]
-  float* dtsw_s = tsw_s + 192;                                     // [192]
-  float* dpos_s = dtsw_s + 192;                                    // [POS_HIST]
-  float* pos_s = dpos_s + POS_HIST;                                // [16 warps][64] distance-bias windows
+  long long* dtsw_s = reinterpret_cast<long long*>(tsw_s + 192);   // [192] fixed point
+  long long* dpos_s = dtsw_s + 192;                                // [POS_HIST] fixed point
+  float* pos_s = reinterpret_cast<float*>(dpos_s + POS_HIST);      // [16 warps][64] distance-bias windows
   uint64_t* bars = reinterpret_cast<uint64_t*>(pos_s + 16 * 64);
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = bars + 1;       // [2]
@@ -202,9 +209,9 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (warp == 2) { rb::tmem_alloc(tmem_slot, 512); rb::tmem_relinquish(); }
   for (int i = threadIdx.x; i < 192; i += blockDim.x) {
     tsw_s[i] = (p.ts_w && i <= p.num_buckets) ? p.ts_w[i] : 0.f;
-    dtsw_s[i] = 0.f;
+    dtsw_s[i] = 0;
   }
-  for (int i = threadIdx.x; i < POS_HIST; i += blockDim.x) dpos_s[i] = 0.f;
+  for (int i = threadIdx.x; i < POS_HIST; i += blockDim.x) dpos_s[i] = 0;
   rb::tc_fence_before();
   __syncthreads();
   rb::tc_fence_after();
@@ -343,8 +350,8 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (WDP) {
           const int hi_idx = min(p.pos_len, POS_HIST) - 1;
           const int base = pi0 - j0w - 31;
-          if (acc_lo != 0.f) atomicAdd(dpos_s + min(max(base + lane, 0), hi_idx), acc_lo);
-          if (acc_hi != 0.f) atomicAdd(dpos_s + min(max(base + lane + 32, 0), hi_idx), acc_hi);
+          if (acc_lo != 0.f) hist_add(dpos_s + min(max(base + lane, 0), hi_idx), acc_lo);
+          if (acc_hi != 0.f) hist_add(dpos_s + min(max(base + lane + 32, 0), hi_idx), acc_hi);
         }
         // P^T / dS^T overwrite S^T / dP^T columns that OTHER warps of this lane quarter read: wait until all
         // four column groups of the quarter have their chunks in registers (bounded, like every wait here)
@@ -388,7 +395,7 @@ hstu_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       rb::tc_fence_before();
       rb::mbar_arrive(dq_empty);
     }
-    if (WDT && run_bucket >= 0 && run_sum != 0.f) atomicAdd(dtsw_s + run_bucket, run_sum);
+    if (WDT && run_bucket >= 0 && run_sum != 0.f) hist_add(dtsw_s + run_bucket, run_sum);
     {
       bool ok = rb::mbar_wait(dkv_full, 0, abort_flag, p.status);
       if (!__all_sync(0xffffffffu, ok)) goto done;
@@ -424,8 +431,8 @@ done:
   __syncthreads();
   if (warp == 2) rb::tmem_dealloc(tmem, 512);
   // flush the bias-gradient histograms of this CTA
-  if (want_dts) for (int i = threadIdx.x; i <= p.num_buckets && i < 192; i += blockDim.x) if (dtsw_s[i] != 0.f) atomicAdd(p.d_ts_w + i, dtsw_s[i]);
-  if (want_dpos) for (int i = threadIdx.x; i < p.pos_len && i < POS_HIST; i += blockDim.x) if (dpos_s[i] != 0.f) atomicAdd(p.d_pos_w + i, dpos_s[i]);
+  if (want_dts) for (int i = threadIdx.x; i <= p.num_buckets && i < 192; i += blockDim.x) if (dtsw_s[i] != 0) atomicAdd(p.d_ts_w + i, hist_value(dtsw_s[i]));
+  if (want_dpos) for (int i = threadIdx.x; i < p.pos_len && i < POS_HIST; i += blockDim.x) if (dpos_s[i] != 0) atomicAdd(p.d_pos_w + i, hist_value(dpos_s[i]));
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
