@@ -3,9 +3,11 @@ from .configs import (POLICY_COUNT, POLICY_SHOW_CLICK, AdmitAndEvictConfig, EmbC
                       InitializerType, ShowClickParams)
 from .embedding_bag import (EmbCacheEmbeddingBagCollection, EmbCacheEmbeddingBagCollectionSharder,
                             EmbCacheShardedEmbeddingBagCollection, calculate_caches)
+from .embedding import EmbCacheEmbeddingCollection, EmbCacheEmbeddingCollectionSharder, EmbCacheShardedEmbeddingCollection
 from .saver import Saver
 from .train_pipeline import EmbCacheTrainPipelineSparseDist
 
 __all__ = ["POLICY_COUNT", "POLICY_SHOW_CLICK", "AdmitAndEvictConfig", "EmbCacheEmbeddingBagConfig", "EmbCacheEmbeddingConfig",
            "InitializerType", "ShowClickParams", "EmbCacheEmbeddingBagCollection", "EmbCacheEmbeddingBagCollectionSharder",
-           "EmbCacheShardedEmbeddingBagCollection", "calculate_caches", "Saver", "EmbCacheTrainPipelineSparseDist"]
+           "EmbCacheShardedEmbeddingBagCollection", "calculate_caches", "EmbCacheEmbeddingCollection", "EmbCacheEmbeddingCollectionSharder",
+           "EmbCacheShardedEmbeddingCollection", "Saver", "EmbCacheTrainPipelineSparseDist"]

@@ -7,7 +7,6 @@ touched since the previous save.  Reference: ``torchrec_embcache/saver.py:31-171
 """
 from __future__ import annotations
 
-import configparser
 import os
 import shutil
 from typing import List, Optional
@@ -18,6 +17,16 @@ import torch.distributed as dist
 from .train_pipeline import embcache_modules
 
 META = "meta.ini"
+
+
+def _read_meta(path: str) -> dict:
+    out = {}
+    with open(path) as f:
+        for line in f:
+            if "=" in line:
+                k, v = line.strip().split("=", 1)
+                out[k.strip()] = v.strip()
+    return out
 
 
 class Saver:
@@ -55,11 +64,8 @@ class Saver:
                     tables.append(t.name)
                     for r in range(world):
                         shutil.rmtree(os.path.join(out, t.name, "rank%d" % r), ignore_errors=True)
-            cp = configparser.ConfigParser()
-            cp["meta"] = {"world_size": str(world), "step": str(step), "incremental": str(int(incremental)),
-                          "tables": ",".join(tables)}
-            with open(os.path.join(out, META), "w") as f:
-                cp.write(f)
+            with open(os.path.join(out, META), "w") as f:            # plain ``key=value`` lines, as the reference writes them
+                f.write("incremental=%s\nsave_world_size=%d\nstep=%d\ntables=%s\n" % (incremental, world, step, ",".join(tables)))
         self._barrier()
         return out
 
@@ -67,9 +73,8 @@ class Saver:
         world, rank = self._world()
         if not os.path.exists(os.path.join(path, META)):
             raise FileNotFoundError("%s has no %s: not a finished checkpoint" % (path, META))
-        cp = configparser.ConfigParser()
-        cp.read(os.path.join(path, META))
-        if bool(int(cp["meta"].get("incremental", "0"))) != incremental:
+        meta = _read_meta(os.path.join(path, META))
+        if (meta.get("incremental", "False") == "True") != incremental:
             raise ValueError("checkpoint kind (full / incremental) does not match the request")
         for m in embcache_modules(module):
             if not incremental:
@@ -89,11 +94,10 @@ class Saver:
             full = os.path.join(path, d)
             if not os.path.exists(os.path.join(full, META)):
                 continue
-            cp = configparser.ConfigParser()
-            cp.read(os.path.join(full, META))
-            if incremental is not None and bool(int(cp["meta"].get("incremental", "0"))) != incremental:
+            meta = _read_meta(os.path.join(full, META))
+            if incremental is not None and (meta.get("incremental", "False") == "True") != incremental:
                 continue
-            step = int(cp["meta"].get("step", "0"))
+            step = int(meta.get("step", "0"))
             if step > best_step:
                 best, best_step = full, step
         return best

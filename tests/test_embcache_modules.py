@@ -127,3 +127,28 @@ def test_pipeline_prefetch_matches_sync():
         return losses
 
     assert np.allclose(run(True), run(False), rtol=1e-5)
+
+
+def test_sequence_collection_small_cache_equals_big_cache():
+    from recsdk_b200.embcache import EmbCacheEmbeddingCollection, EmbCacheEmbeddingConfig, EmbCacheShardedEmbeddingCollection
+
+    def build(cache_rows):
+        tabs = [EmbCacheEmbeddingConfig(num_embeddings=1000, embedding_dim=8, name="s0", feature_names=["f0"]),
+                EmbCacheEmbeddingConfig(num_embeddings=500, embedding_dim=8, name="s1", feature_names=["f1", "f2"])]
+        ec = EmbCacheEmbeddingCollection(tabs, 1, 6, [3, 3], device="cpu")
+        return EmbCacheShardedEmbeddingCollection(ec, ShardingEnv(1, 0, None), "cpu", ec.optimizer_spec(lr=0.1), cache_rows=cache_rows)
+
+    def train(m):
+        g = torch.Generator().manual_seed(0)
+        losses = []
+        for _ in range(10):
+            kjt = _batch(g)
+            out = m(kjt)
+            assert out["f1"].values().shape[0] == int(kjt["f1"].lengths().sum())
+            loss = sum((jt.values() * (i + 1)).sum(dim=1).pow(2).mean() for i, jt in enumerate(out.values()))
+            loss.backward()
+            losses.append(float(loss.detach()))
+        return losses
+
+    a, b = train(build([40, 64])), train(build([1001, 501]))
+    assert np.allclose(a, b, rtol=1e-5, atol=1e-6), (a, b)
