@@ -39,11 +39,12 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
-    ap.add_argument("--model", default="dlrm", choices=["dlrm", "hstu", "hstu-infer"])
+    ap.add_argument("--model", default="dlrm", choices=["dlrm", "hstu", "hstu-infer", "dcn"])
     ap.add_argument("--global-batch", type=int, default=65536)
     ap.add_argument("--small", action="store_true", help="tiny tables / batch for a quick functional check")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--table-seed", type=int, default=0)
+    ap.add_argument("--ckpt-every", type=int, default=500, help="dcn: incremental dump period in steps (0 = off)")
     ap.add_argument("--rows-scale", type=float, default=1.0,
                     help="shrink every table (profiling captures on a small case); 1.0 = the named config")
     return ap.parse_args()
@@ -122,6 +123,8 @@ def main() -> None:
             from baseline.torch_dlrm import run as run_torch_dlrm
 
             run_torch_dlrm(args, table_rows, ClockSampler)
+        elif args.model == "dcn":
+            print(json.dumps({"impl": "torch-nccl-baseline", "unavailable": "no stock-PyTorch arm for the dynamic hash table configuration"}))
         elif args.model == "hstu":
             from baseline.torch_hstu import run as run_torch_hstu
 
@@ -135,6 +138,11 @@ def main() -> None:
         from recsdk_b200.models.hstu_bench import run_hstu_bench
 
         run_hstu_bench(args)
+        return
+    if args.model == "dcn":
+        from recsdk_b200.models.dcn_bench import run_dcn_bench
+
+        run_dcn_bench(args)
         return
     if args.model == "hstu-infer":
         from recsdk_b200.models.hstu_bench import run_hstu_inference_bench
