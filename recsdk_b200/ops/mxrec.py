@@ -325,3 +325,70 @@ _def("split_embedding_codegen_forward_unweighted_cuda(Tensor dev_weights, Tensor
      "int pooling_mode, Tensor lxu_cache_locations, Tensor uvm_cache_stats, int output_dtype, bool is_experimental, "
      "Tensor? hash_indices=None, Tensor? offset_per_key=None, Tensor? rows_per_table=None) -> Tensor",
      split_embedding_codegen_forward_unweighted_cuda)
+
+
+# ------------------------------------------------------------------------------------------------ optional parity ops
+def hstu_fuxi(q, k, v, timestampBias=None, positionBias=None, mask=None, maskType: int = 0, maxSeqLen: int = 0, siluScale: float = 0.0,
+              layout: str = "normal", seqOffset: Optional[List[int]] = None):
+    """Fuxi variant: ``cat[(SiLU(QK^T) s m) V, (tsBias m) V, (posBias m) V]`` on the last dim (only the first part when no
+    bias is given).  ``layout`` "normal": ``[B,S,N,D]``; "jagged": ``[sum_len,N,D]`` with ``seqOffset``
+    (``hstu_dense_forward_fuxi/README.md`` of the reference).  PyTorch composition (fp32 math)."""
+    if maskType == 1:
+        raise NotImplementedError("upper-triangular masks are not supported")
+    scale = siluScale if siluScale != 0.0 else 1.0 / max(maxSeqLen, 1)
+
+    def one(qq, kk, vv, b):                                        # [L,N,D] each
+        L = qq.shape[0]
+        s = torch.einsum("ind,jnd->nij", qq.float(), kk.float())
+        if maskType == 0:
+            m = torch.tril(torch.ones(L, L, device=qq.device))[None]
+        elif maskType == 3:
+            m = mask[b, :, :L, :L].float()
+        else:
+            m = torch.ones(1, L, L, device=qq.device)
+        parts = [torch.einsum("nij,jnd->ind", torch.nn.functional.silu(s) * scale * m, vv.float())]
+        if timestampBias is not None or positionBias is not None:
+            tb = timestampBias[b, :L, :L].float()[None] if timestampBias is not None else torch.zeros(1, L, L, device=qq.device)
+            pb = positionBias[min(b, positionBias.shape[0] - 1), :L, :L].float()[None] if positionBias is not None \
+                else torch.zeros(1, L, L, device=qq.device)
+            parts.append(torch.einsum("nij,jnd->ind", (tb * m).expand(qq.shape[1], L, L), vv.float()))
+            parts.append(torch.einsum("nij,jnd->ind", (pb * m).expand(qq.shape[1], L, L), vv.float()))
+        return torch.cat(parts, dim=-1).to(qq.dtype)
+
+    if layout == "jagged":
+        offs = list(seqOffset)
+        return torch.cat([one(q[offs[b]:offs[b + 1]], k[offs[b]:offs[b + 1]], v[offs[b]:offs[b + 1]], b) for b in range(len(offs) - 1)])
+    return torch.stack([one(q[b], k[b], v[b], b) for b in range(q.shape[0])])
+
+
+def disentangle_attention(query_layer, key_layer, value_layer, pos_key_layer, pos_query_layer, relative_pos, attn_mask,
+                          pos_attr_type: str, score_scale: float):
+    """DeBERTa disentangled attention.  ``query/key/value`` ``[b,n,s,d]``, ``pos_key/pos_query`` ``[2s,n,d]``, ``relative_pos``
+    ``[1,1,s,s]`` int64, ``attn_mask`` ``[b,1,s,s]``; ``pos_attr_type`` in ``c2p``, ``p2c``, ``c2p|p2c``.
+    Returns ``(outputs, probs, weights)`` where ``weights`` is the pre-softmax score (content + position terms)
+    (``ai_core_op/disentangle_attention/v220/README.md`` of the reference).  PyTorch composition (fp32 math)."""
+    q, k, v = query_layer.float(), key_layer.float(), value_layer.float()
+    span = pos_key_layer.shape[0] // 2
+    score = torch.matmul(q, k.transpose(-1, -2)) * score_scale
+    rel = relative_pos.long()
+    kinds = pos_attr_type.split("|")
+    if "c2p" in kinds:
+        c2p_att = torch.einsum("bnqd,pnd->bnqp", q, pos_key_layer.float())
+        c2p_pos = torch.clamp(rel + span, 0, 2 * span - 1).expand(q.shape[0], q.shape[1], -1, -1)
+        score = score + torch.gather(c2p_att, -1, c2p_pos) * score_scale
+    if "p2c" in kinds:
+        p2c_att = torch.einsum("bnkd,pnd->bnkp", k, pos_query_layer.float())
+        p2c_pos = torch.clamp(-rel + span, 0, 2 * span - 1).expand(q.shape[0], q.shape[1], -1, -1)
+        score = score + torch.gather(p2c_att, -1, p2c_pos).transpose(-1, -2) * score_scale
+    keep = attn_mask.bool()
+    probs = torch.softmax(score.masked_fill(~keep, float("-inf")), dim=-1)
+    probs = torch.nan_to_num(probs).masked_fill(~keep, 0.0)
+    out = torch.matmul(probs, v)
+    dt = query_layer.dtype
+    return out.to(dt), probs.to(dt), score.to(dt)
+
+
+_def("hstu_fuxi(Tensor q, Tensor k, Tensor v, Tensor? timestampBias=None, Tensor? positionBias=None, Tensor? mask=None, int maskType=0, "
+     "int maxSeqLen=0, float siluScale=0.0, str layout=\"normal\", int[]? seqOffset=None) -> Tensor", hstu_fuxi)
+_def("disentangle_attention(Tensor query_layer, Tensor key_layer, Tensor value_layer, Tensor pos_key_layer, Tensor pos_query_layer, "
+     "Tensor relative_pos, Tensor attn_mask, str pos_attr_type, float score_scale) -> (Tensor, Tensor, Tensor)", disentangle_attention)

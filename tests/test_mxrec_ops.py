@@ -92,3 +92,31 @@ def test_in_linear_silu_and_small_ops():
         None, None, torch.tensor([5, 3]))
     t0, t1 = wflat[:20].view(5, 4), wflat[20:].view(3, 8)
     assert torch.allclose(out[0, :4], t0[0] + t0[4]) and torch.allclose(out[1, 4:], t1[2])
+
+
+def test_fuxi_and_disentangle():
+    torch.manual_seed(3)
+    B, S, N, D = 2, 6, 2, 8
+    q, k, v = (torch.randn(B, S, N, D) for _ in range(3))
+    tb, pb = torch.randn(B, S, S), torch.randn(1, S, S)
+    out = torch.ops.mxrec.hstu_fuxi(q, k, v, tb, pb, None, 0, S, 0.0, "normal", None)
+    assert out.shape == (B, S, N, 3 * D)
+    assert torch.allclose(out[..., :D], torch.ops.mxrec.hstu_dense(q, k, v, None, None, 0, S, 0.0), atol=1e-5)
+    m = torch.tril(torch.ones(S, S))
+    assert torch.allclose(out[0, :, 1, D:2 * D], (tb[0] * m) @ v[0, :, 1], atol=1e-5)
+    jag = torch.ops.mxrec.hstu_fuxi(q.reshape(B * S, N, D), k.reshape(B * S, N, D), v.reshape(B * S, N, D), None, None, None, 0, S, 0.0,
+                                    "jagged", [0, S, 2 * S])
+    assert torch.allclose(jag.view(B, S, N, D), out[..., :D], atol=1e-5)
+    # disentangled attention: with zero position projections it is plain masked softmax attention
+    qq, kk, vv = (torch.randn(B, N, S, D) for _ in range(3))
+    rel = (torch.arange(S)[:, None] - torch.arange(S)[None, :]).view(1, 1, S, S)
+    mask = torch.ones(B, 1, S, S)
+    z = torch.zeros(2 * S, N, D)
+    o, p, w = torch.ops.mxrec.disentangle_attention(qq, kk, vv, z, z, rel, mask, "c2p|p2c", 0.25)
+    ref = torch.softmax(qq @ kk.transpose(-1, -2) * 0.25, -1) @ vv
+    assert torch.allclose(o, ref, atol=1e-5) and torch.allclose(p.sum(-1), torch.ones(B, N, S), atol=1e-5)
+    pk = torch.randn(2 * S, N, D)
+    _, _, w2 = torch.ops.mxrec.disentangle_attention(qq, kk, vv, pk, z, rel, mask, "c2p", 0.25)
+    i, j = 4, 1
+    exp = (qq[0, 0, i] @ kk[0, 0, j] + qq[0, 0, i] @ pk[i - j + S, 0]) * 0.25
+    assert torch.allclose(w2[0, 0, i, j], exp, atol=1e-5)
