@@ -714,7 +714,11 @@ RB_API int rb_tbe_linearize(const void* shards, const void* indices, int idx64, 
   return static_cast<int>(cudaGetLastError());
 }
 
-// Temp-storage size for rb_sort_segments with up to n keys.
+struct IsOwnedKey {
+  __host__ __device__ __forceinline__ bool operator()(const long long& k) const { return k >= 0; }
+};
+
+// Temp-storage size for rb_sort_segments / rb_compact_owned with up to n keys.
 RB_API long long rb_sort_segments_temp_bytes(long long n) {
   size_t a = 0, b = 0, c = 0;
   cub::DeviceRadixSort::SortPairs(nullptr, a, (long long*)nullptr, (long long*)nullptr, (int*)nullptr,
@@ -722,9 +726,37 @@ RB_API long long rb_sort_segments_temp_bytes(long long n) {
   cub::DeviceRunLengthEncode::Encode(nullptr, b, (long long*)nullptr, (long long*)nullptr, (int*)nullptr,
                                      (int*)nullptr, static_cast<int>(n));
   cub::DeviceScan::ExclusiveSum(nullptr, c, (int*)nullptr, (int*)nullptr, static_cast<int>(n) + 1);
+  size_t d = 0, e = 0;
+  cub::DeviceSelect::If(nullptr, d, (long long*)nullptr, (long long*)nullptr, (int*)nullptr, static_cast<int>(n), IsOwnedKey());
+  cub::DeviceSelect::FlaggedIf(nullptr, e, (int*)nullptr, (long long*)nullptr, (int*)nullptr, (int*)nullptr, static_cast<int>(n),
+                               IsOwnedKey());
   size_t m = a > b ? a : b;
   m = m > c ? m : c;
+  m = m > d ? m : d;
+  m = m > e ? m : e;
   return static_cast<long long>(m + 256);
+}
+
+// Keep the (key, bag) pairs this rank owns (key >= 0), in their original order, in the first `count` entries of the
+// outputs and fill entries [count, cap) with the "not owned" key -1, so that a sort of `cap` entries replaces a sort
+// of all n.  cap is a host-side bound on the owned count; if it is exceeded the surplus pairs are dropped and
+// status[0] becomes RB_ERR_CAPACITY.  Outputs must have room for n entries.  No host synchronisation.
+__global__ void pad_owned_tail_kernel(long long* __restrict__ keys, int* __restrict__ bags, const int* __restrict__ count, int cap,
+                                      int* __restrict__ status) {
+  const int c = *count;
+  if (c > cap && blockIdx.x == 0 && threadIdx.x == 0) atomicExch(status, RB_ERR_CAPACITY);
+  for (int i = c + blockIdx.x * blockDim.x + threadIdx.x; i < cap; i += gridDim.x * blockDim.x) { keys[i] = -1; bags[i] = 0; }
+}
+
+RB_API int rb_compact_owned(const long long* keys, const int* bags, long long n, long long* keys_out, int* bags_out, int* count,
+                            int cap, void* temp, long long temp_bytes, int* status, cudaStream_t st) {
+  if (n == 0) return static_cast<int>(cudaMemsetAsync(count, 0, sizeof(int), st));
+  size_t tb = static_cast<size_t>(temp_bytes);
+  RB_CUDA_CHECK(cub::DeviceSelect::If(temp, tb, keys, keys_out, count, static_cast<int>(n), IsOwnedKey(), st));
+  tb = static_cast<size_t>(temp_bytes);
+  RB_CUDA_CHECK(cub::DeviceSelect::FlaggedIf(temp, tb, bags, keys, bags_out, count, static_cast<int>(n), IsOwnedKey(), st));
+  pad_owned_tail_kernel<<<64, 256, 0, st>>>(keys_out, bags_out, count, cap, status);
+  return static_cast<int>(cudaGetLastError());
 }
 
 // keys/vals -> sorted keys/vals, unique keys, segment offsets (exclusive scan of run lengths,

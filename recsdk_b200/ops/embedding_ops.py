@@ -154,9 +154,14 @@ class SegmentSorter:
         self.seg_offsets = torch.empty(n + 1, **i32)
         self.num_runs = torch.zeros(1, **i32)
         self.temp = torch.empty(self.temp_bytes, dtype=torch.uint8, device=device)
+        self.keys_owned: Optional[torch.Tensor] = None       # compaction outputs, allocated on first use
+        self.bags_owned: Optional[torch.Tensor] = None
+        self.owned_count = torch.zeros(1, **i32)
 
     def run(self, layout: TbeLayout, dev: dict, indices: torch.Tensor, offsets: Optional[torch.Tensor],
-            B_global: int) -> SortedSegments:
+            B_global: int, owned_cap: Optional[int] = None) -> SortedSegments:
+        """``owned_cap``: when the ids of all ranks were gathered, a host-side bound on how many of them this rank owns;
+        the owned pairs are compacted first and only ``owned_cap`` entries are sorted (an overflow raises the status word)."""
         nnz = indices.numel()
         assert nnz <= self.max_nnz
         L = _lib.lib()
@@ -165,7 +170,16 @@ class SegmentSorter:
                                 _lib.ptr(offsets), layout.T, B_global, nnz, layout.world, layout.rank,
                                 self.keys.data_ptr(), self.bags.data_ptr(), st)
         _lib.check(rc, "rb_tbe_linearize")
-        rc = L.rb_sort_segments(self.keys.data_ptr(), self.bags.data_ptr(), nnz, layout.key_bits,
+        keys_in, bags_in = self.keys, self.bags
+        if owned_cap is not None and owned_cap < nnz:
+            if self.keys_owned is None:
+                self.keys_owned, self.bags_owned = torch.empty_like(self.keys), torch.empty_like(self.bags)
+            rc = L.rb_compact_owned(self.keys.data_ptr(), self.bags.data_ptr(), nnz, self.keys_owned.data_ptr(),
+                                    self.bags_owned.data_ptr(), self.owned_count.data_ptr(), int(owned_cap), self.temp.data_ptr(),
+                                    self.temp_bytes, _lib.status_tensor(indices.device).data_ptr(), st)
+            _lib.check(rc, "rb_compact_owned")
+            keys_in, bags_in, nnz = self.keys_owned, self.bags_owned, int(owned_cap)
+        rc = L.rb_sort_segments(keys_in.data_ptr(), bags_in.data_ptr(), nnz, layout.key_bits,
                                 self.keys_sorted.data_ptr(), self.bags_sorted.data_ptr(), self.unique.data_ptr(),
                                 self.counts.data_ptr(), self.seg_offsets.data_ptr(), self.num_runs.data_ptr(),
                                 self.temp.data_ptr(), self.temp_bytes, st)

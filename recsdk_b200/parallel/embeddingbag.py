@@ -115,6 +115,7 @@ class ShardedEmbeddingBagCollection(nn.Module):
             kinds.append(k)
             owners.append((ps.ranks[0] if ps.ranks else 0) if k == E.SH_TABLE_WISE else 0)
         self.plan = plan
+        self._kinds, self._owners, self._feature_table = kinds, owners, feature_table
         self.layout = E.TbeLayout([t.embedding_dim for t in tables], [t.num_embeddings for t in tables], kinds,
                                   owners, self.world, self.rank, feature_table)
         for d in self.layout.dims:
@@ -300,9 +301,24 @@ class ShardedEmbeddingBagCollection(nn.Module):
         self.peer.barrier()
         trace.mark("emb.sort")
         gathered = self._gather_ids.local.view(torch.int64)[: T * Bg]
-        dctx.segments = self._sorter.run(self.layout, self.dev, gathered, None, Bg)
+        dctx.segments = self._sorter.run(self.layout, self.dev, gathered, None, Bg, owned_cap=self._owned_cap(Bg))
         trace.mark("emb.sort_done")
         return dctx
+
+    def _owned_cap(self, Bg: int) -> int:
+        """Bound on the ids of a gathered one-hot batch that this rank owns: all ids of its table-wise tables, twice the
+        fair share of the row-wise ones (hot ids cluster on a few residues), everything of replicated tables."""
+        exp = 0.0
+        for f in range(self.layout.T):
+            ti = self._feature_table[f]
+            k = self._kinds[ti]
+            if k == E.SH_TABLE_WISE:
+                exp += Bg if self._owners[ti] == self.rank else 0
+            elif k in (E.SH_ROW_MOD, E.SH_ROW_BLOCK):
+                exp += 2.0 * Bg / self.world
+            else:
+                exp += Bg
+        return int(min(self.layout.T * Bg, (int(exp) + 8191) // 1024 * 1024))
 
     # --------------------------------------------------------------- compute
     def _lookup(self, dctx: EmbeddingDistContext) -> torch.Tensor:
