@@ -19,6 +19,8 @@
 //  cust_op/framework/torch_plugin/torch_library/split_embedding_codegen_forward_unweighted/).
 #include <cub/cub.cuh>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -455,8 +457,8 @@ __device__ __forceinline__ void apply_row_update(const BwdArgs& a, const Tabs& t
 
 // (1) one half-warp per unique row; segments longer than long_threshold are split into chunks of
 //     LONG_CHUNK entries and queued for kernels (2) and (3).
-template <typename WT, typename GT, int NCH>
-__global__ void __launch_bounds__(256) tbe_bwd_short_kernel(const BwdArgs a) {
+template <typename WT, typename GT, int NCH, int MINB>
+__global__ void __launch_bounds__(256, MINB) tbe_bwd_short_kernel(const BwdArgs a) {
   extern __shared__ long long sm_tabs[];
   const Tabs tb = load_tabs(a, sm_tabs);
   const int hl = threadIdx.x & 15;
@@ -582,7 +584,15 @@ int launch_bwd(const BwdArgs& a, int max_runs, int num_sms, cudaStream_t st) {
   const int cap = num_sms * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  tbe_bwd_short_kernel<WT, GT, NCH><<<blocks, 256, smem, st>>>(a);
+  // resident CTAs per SM the kernel is compiled for: the kernel is bound by the latency of its dependent loads, so more
+  // half-warps in flight beat a spill-free register allocation (measured 2.94 -> 2.80 ms per DLRM-large step from 2 to 4);
+  // RECSDK_B200_TBE_BWD_MINB = 2 | 3 | 4 overrides it for tuning
+  static const int minb = [] { const char* e = getenv("RECSDK_B200_TBE_BWD_MINB"); return e ? atoi(e) : 4; }();
+  if (blocks == cap) blocks = num_sms * (minb >= 4 ? 16 : (minb == 3 ? 12 : 8));
+  if (blocks > (max_runs + 15) / 16) blocks = (max_runs + 15) / 16;
+  if (minb >= 4) tbe_bwd_short_kernel<WT, GT, NCH, 4><<<blocks, 256, smem, st>>>(a);
+  else if (minb == 3) tbe_bwd_short_kernel<WT, GT, NCH, 3><<<blocks, 256, smem, st>>>(a);
+  else tbe_bwd_short_kernel<WT, GT, NCH, 2><<<blocks, 256, smem, st>>>(a);
   tbe_bwd_long_chunk_kernel<GT, NCH><<<num_sms * 4, 256, smem, st>>>(a);
   tbe_bwd_long_final_kernel<WT, NCH><<<num_sms, 256, smem, st>>>(a);
   return static_cast<int>(cudaGetLastError());

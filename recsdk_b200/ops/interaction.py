@@ -87,13 +87,17 @@ class DotInteractionFunction(torch.autograd.Function):
         dot_interaction_fwd(x0, xs, F, out)
         ctx.save_for_backward(x0, xs)
         ctx.F, ctx.mask_x0 = F, mask_x0
+        # a producer may nominate the buffer its gradient should be written into (e.g. a peer-mapped buffer that other
+        # GPUs read): saves the consumer a copy
+        ctx.grad_buffer = getattr(xs, "_grad_out_buffer", None)
         return out
 
     @staticmethod
     def backward(ctx, dR: torch.Tensor):
         x0, xs = ctx.saved_tensors
         dx0 = torch.empty_like(x0)
-        dxs = torch.empty_like(xs)
+        gb = ctx.grad_buffer
+        dxs = gb if (gb is not None and gb.shape == xs.shape and gb.dtype == xs.dtype and gb.is_contiguous()) else torch.empty_like(xs)
         dot_interaction_bwd(x0, xs, dR if dR.stride(1) == 1 else dR.contiguous(), ctx.F, dx0, dxs, ctx.mask_x0)
         return dx0, dxs, None, None, None
 

@@ -341,7 +341,8 @@ class ShardedEmbeddingBagCollection(nn.Module):
             return
         trace.mark("emb.grad_publish")
         gb = self._grad_buf.local.view(dout.dtype)[: dout.numel()].view(dout.shape)
-        gb.copy_(dout)
+        if dout.data_ptr() != gb.data_ptr():           # the consumer may already have written into the published buffer
+            gb.copy_(dout)
         trace.mark("emb.grad_barrier")
         self.peer.barrier()
         trace.mark("emb.backward_update")
@@ -358,6 +359,8 @@ class ShardedEmbeddingBagCollection(nn.Module):
 
     def compute_and_output_dist(self, dctx: EmbeddingDistContext) -> KeyedTensor:
         out = _LookupFn.apply(self._anchor, self, dctx)
+        if self.world > 1:
+            out._grad_out_buffer = self._grad_buf.local.view(out.dtype)[: out.numel()].view(out.shape)
         return KeyedTensor(self.feature_names, self.layout.feature_dims, out)
 
     def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
