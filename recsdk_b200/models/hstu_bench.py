@@ -9,15 +9,38 @@ from __future__ import annotations
 import json
 import os
 
+from typing import Optional
+
 import torch
 import torch.distributed as dist
 
 
-def make_batch(B: int, gen: torch.Generator, n_items: int = 100_000_000, n_neg: int = 512, max_len: int = 4096):
+def draw_lengths(n: int, gen: torch.Generator, max_len: int = 4096) -> torch.Tensor:
+    """Sequence lengths: log-normal truncated to [16, max_len], mean about 1024."""
+    return torch.exp(torch.randn(n, generator=gen) * 0.75 + 6.65).clamp(16, max_len).long()
+
+
+def balance_sequences(lengths: torch.Tensor, world: int, per_rank: int):
+    """Deal ``world * per_rank`` sequences to ranks so that the attention cost (sum of squared lengths, plus a linear
+    term for the projections) is even: longest first, each to the least-loaded rank that still has room.  Returns the
+    list of index lists, one per rank.  With jagged batches the step time of a data-parallel job is the slowest rank's,
+    so an uneven deal wastes the other GPUs."""
+    cost = lengths.double() ** 2 + 2048.0 * lengths.double()
+    order = torch.argsort(cost, descending=True).tolist()
+    load, out = [0.0] * world, [[] for _ in range(world)]
+    for i in order:
+        r = min((r for r in range(world) if len(out[r]) < per_rank), key=lambda r: load[r])
+        out[r].append(i)
+        load[r] += float(cost[i])
+    return out
+
+
+def make_batch(B: int, gen: torch.Generator, n_items: int = 100_000_000, n_neg: int = 512, max_len: int = 4096,
+               lengths: Optional[torch.Tensor] = None):
     from ..sparse.jagged_tensor import KeyedJaggedTensor
     from ..utils.data import zipf_ids
 
-    ln = torch.exp(torch.randn(B, generator=gen) * 0.75 + 6.65).clamp(16, max_len).long()
+    ln = draw_lengths(B, gen, max_len) if lengths is None else lengths.long()
     T = int(ln.sum())
     ids = zipf_ids(T, n_items, 1.05, gen)
     neg = torch.randint(0, n_items, (n_neg,), generator=gen)
@@ -66,21 +89,34 @@ def run_hstu_bench(args) -> None:
     B = 32 if not args.small else 4
     model, opt = build(dev, env, capacity=(1 << 22) if not args.small else (1 << 16))
     gen = torch.Generator().manual_seed(1234 + rank)
+    shared = torch.Generator().manual_seed(4321)                      # same on every rank: the global batch's lengths
     n_batches = args.steps + max(args.warmup, 3)
-    host = [make_batch(B, gen, max_len=4096 if not args.small else 512) for _ in range(min(n_batches, 12))]
+    max_len = 4096 if not args.small else 512
+    host = []
+    for _ in range(min(n_batches, 12)):
+        if world > 1:
+            # the input pipeline deals the global batch's sequences to ranks by attention cost
+            glob = draw_lengths(B * world, shared, max_len)
+            mine = balance_sequences(glob, world, B)[rank]
+            host.append(make_batch(B, gen, max_len=max_len, lengths=glob[mine]))
+        else:
+            host.append(make_batch(B, gen, max_len=max_len))
     pin = lambda t: t.pin_memory()  # noqa: E731
     host = [(k.pin_memory(), pin(o), m, pin(ts), T, pin(kp)) for (k, o, m, ts, T, kp) in host]
     dense_params = [p for p in model.parameters() if p.requires_grad and not getattr(p, "_in_backward_optimizers", False)]
     flat_ids = {id(m.flat_param) for m in opt.flat_modules}
 
     def sync_grads():
+        """Dense gradients: one all-reduce per flat MLP buffer, one for all small parameters together."""
         if world == 1:
             return
         for m in opt.flat_modules:
             dist.all_reduce(m.flat_grad)
-        for p in dense_params:
-            if id(p) not in flat_ids and p.grad is not None:
-                dist.all_reduce(p.grad)
+        small = [p for p in dense_params if id(p) not in flat_ids and p.grad is not None]
+        if small:
+            flat = torch.cat([p.grad.reshape(-1) for p in small])
+            dist.all_reduce(flat)
+            torch._foreach_copy_([p.grad for p in small], [c.view_as(p.grad) for c, p in zip(flat.split([p.numel() for p in small]), small)])
 
     def step(i):
         k, o, m, ts, T, kp = host[i % len(host)]
