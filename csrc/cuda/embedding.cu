@@ -896,3 +896,93 @@ RB_API int rb_copy_rows(const void* src, const long long* src_idx, void* dst, co
                                            dst_idx, n, v);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------
+// Pooled gather / scatter-add over the unique rows of a dynamic (hash) table:
+//   out[bag, :] = sum (or mean) over j in [offsets[bag], offsets[bag+1]) of rows[inverse[j], :]
+//   red[inverse[j], :] += g[bag, :] (/ len for mean)
+// rows / red are fp32 [n_unique, D] (D a multiple of 4); a group of G = min(32, pow2 >= D/4) lanes serves one bag,
+// 32 / G bags per warp, so the per-id rows are never materialised.
+// (dynamic_emb lookup_forward / lookup_backward of the reference: csrc/ops/pooling_embeddings, csrc/ops/look_backward.)
+template <typename OT>
+__global__ void pooled_gather_kernel(const float* __restrict__ rows, const long long* __restrict__ inverse,
+                                     const long long* __restrict__ offsets, long long bags, long long B, int D, int G, int mean,
+                                     OT* __restrict__ out, long long ld_out) {
+  const int lane = threadIdx.x & 31;
+  const int gl = lane & (G - 1);
+  const long long group = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / G;
+  if (group >= bags) return;
+  const long long beg = offsets[group], end = offsets[group + 1];
+  const float inv_len = (mean && end > beg) ? 1.f / static_cast<float>(end - beg) : 1.f;
+  for (int c = gl; c * 4 < D; c += G) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    long long j = beg;
+    for (; j + 1 < end; j += 2) {                                    // two rows in flight
+      const float4 a = *reinterpret_cast<const float4*>(rows + inverse[j] * D + c * 4);
+      const float4 b = *reinterpret_cast<const float4*>(rows + inverse[j + 1] * D + c * 4);
+      acc.x += a.x + b.x; acc.y += a.y + b.y; acc.z += a.z + b.z; acc.w += a.w + b.w;
+    }
+    if (j < end) {
+      const float4 a = *reinterpret_cast<const float4*>(rows + inverse[j] * D + c * 4);
+      acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+    }
+    OT* o = out + (group % B) * ld_out + (group / B) * D + c * 4;            // bag = feature * B + sample
+    o[0] = static_cast<OT>(acc.x * inv_len); o[1] = static_cast<OT>(acc.y * inv_len);
+    o[2] = static_cast<OT>(acc.z * inv_len); o[3] = static_cast<OT>(acc.w * inv_len);
+  }
+}
+
+template <typename GT>
+__global__ void pooled_scatter_add_kernel(const GT* __restrict__ g, long long ld_g, const long long* __restrict__ inverse,
+                                          const long long* __restrict__ offsets, long long bags, long long B, int D, int G, int mean,
+                                          float* __restrict__ red) {
+  const int lane = threadIdx.x & 31;
+  const int gl = lane & (G - 1);
+  const long long group = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / G;
+  if (group >= bags) return;
+  const long long beg = offsets[group], end = offsets[group + 1];
+  const float inv_len = (mean && end > beg) ? 1.f / static_cast<float>(end - beg) : 1.f;
+  for (int c = gl; c * 4 < D; c += G) {
+    const GT* gp = g + (group % B) * ld_g + (group / B) * D + c * 4;
+    const float x = static_cast<float>(gp[0]) * inv_len, y = static_cast<float>(gp[1]) * inv_len,
+                z = static_cast<float>(gp[2]) * inv_len, w = static_cast<float>(gp[3]) * inv_len;
+    for (long long j = beg; j < end; ++j) rb::red_add_v4(red + inverse[j] * D + c * 4, x, y, z, w);
+  }
+}
+
+static int pooled_group(int D) {
+  int g = 1;
+  while (g < 32 && g * 4 < D) g <<= 1;
+  return g;
+}
+
+// bags = F * B (feature-major); the pooled row of bag f * B + b is written to out[b * ld_out + f * D ...]
+RB_API int rb_pooled_gather(const float* rows, const long long* inverse, const long long* offsets, long long bags, long long B, int D,
+                            int mean, void* out, int out_dtype, long long ld_out, cudaStream_t st) {
+  if (bags == 0) return 0;
+  if (B <= 0) B = bags;
+  if (D % 4) return -1;
+  const int G = pooled_group(D);
+  const long long threads = bags * G;
+  const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
+  RB_O_DISPATCH(out_dtype, pooled_gather_kernel<OT><<<blocks, 256, 0, st>>>(rows, inverse, offsets, bags, B, D, G, mean,
+                                                                            reinterpret_cast<OT*>(out), ld_out));
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_pooled_scatter_add(const void* g, int g_dtype, long long ld_g, const long long* inverse, const long long* offsets,
+                                 long long bags, long long B, int D, int mean, float* red, cudaStream_t st) {
+  if (bags == 0) return 0;
+  if (B <= 0) B = bags;
+  if (D % 4) return -1;
+  const int G = pooled_group(D);
+  const long long threads = bags * G;
+  const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
+  switch (g_dtype) {
+    case DT_F32: pooled_scatter_add_kernel<float><<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(g), ld_g, inverse, offsets, bags, B, D, G, mean, red); break;
+    case DT_F16: pooled_scatter_add_kernel<__half><<<blocks, 256, 0, st>>>(reinterpret_cast<const __half*>(g), ld_g, inverse, offsets, bags, B, D, G, mean, red); break;
+    case DT_BF16: pooled_scatter_add_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(g), ld_g, inverse, offsets, bags, B, D, G, mean, red); break;
+    default: return -1;
+  }
+  return static_cast<int>(cudaGetLastError());
+}

@@ -43,6 +43,65 @@ class _DynamicLookupFn(torch.autograd.Function):
         return None, None, None, None
 
 
+class _DynamicPooledLookupFn(torch.autograd.Function):
+    """ids of ONE feature with bag offsets -> pooled rows ``[B, D]``; the per-id rows are never materialised: the pooled
+    gather reads the unique rows through the inverse index, the backward adds each bag's gradient to its unique rows
+    with 16-byte vector reductions, then the fused optimizer runs on the unique rows."""
+
+    @staticmethod
+    def forward(ctx, anchor: torch.Tensor, table: KeyValueTable, ids: torch.Tensor, offsets: torch.Tensor, batch: int, mean: bool,
+                training: bool, out_dtype: torch.dtype):
+        """``ids`` / ``offsets`` may span several features of the table (``offsets`` has ``F * batch + 1`` entries,
+        feature-major); the result is ``[batch, F * D]`` with feature ``f`` in columns ``[f * D, (f + 1) * D)``."""
+        from ..ops import _lib
+
+        uniq, inv = _unique(ids)
+        slots, rows = table.lookup(uniq, training)
+        rows = rows.float().contiguous()
+        D = rows.shape[1]
+        offsets = offsets.to(torch.int64).contiguous()
+        bags = offsets.numel() - 1
+        F = bags // batch
+        if rows.is_cuda and D % 4 == 0:
+            out = torch.empty(batch, F * D, dtype=out_dtype, device=rows.device)
+            rc = _lib.lib().rb_pooled_gather(rows.data_ptr(), inv.data_ptr(), offsets.data_ptr(), bags, batch, D, int(mean), out.data_ptr(),
+                                             _lib.dtype_code(out_dtype), out.stride(0), _lib.stream_ptr(rows.device))
+            _lib.check(rc, "rb_pooled_gather")
+        else:
+            lengths = offsets[1:] - offsets[:-1]
+            bag = torch.repeat_interleave(torch.arange(bags, device=rows.device), lengths)
+            out = torch.zeros(bags, D, dtype=torch.float32, device=rows.device).index_add_(0, bag, rows[inv])
+            if mean:
+                out = out / lengths.clamp(min=1).to(out.dtype)[:, None]
+            out = out.view(F, batch, D).permute(1, 0, 2).reshape(batch, F * D).to(out_dtype)
+        ctx.table, ctx.training, ctx.mean, ctx.batch = table, training, mean, batch
+        ctx.save_for_backward(slots, inv, offsets)
+        ctx.n_unique, ctx.D = uniq.numel(), D
+        return out
+
+    @staticmethod
+    def backward(ctx, g: torch.Tensor):
+        from ..ops import _lib
+
+        slots, inv, offsets = ctx.saved_tensors
+        if ctx.training and ctx.n_unique:
+            red = torch.zeros(ctx.n_unique, ctx.D, dtype=torch.float32, device=g.device)
+            bags = offsets.numel() - 1
+            if g.is_cuda and ctx.D % 4 == 0 and g.stride(1) == 1:
+                rc = _lib.lib().rb_pooled_scatter_add(g.data_ptr(), _lib.dtype_code(g.dtype), g.stride(0), inv.data_ptr(), offsets.data_ptr(),
+                                                      bags, ctx.batch, ctx.D, int(ctx.mean), red.data_ptr(), _lib.stream_ptr(g.device))
+                _lib.check(rc, "rb_pooled_scatter_add")
+            else:
+                lengths = offsets[1:] - offsets[:-1]
+                bag = torch.repeat_interleave(torch.arange(bags, device=g.device), lengths)
+                gg = g.float().view(ctx.batch, bags // ctx.batch, ctx.D).permute(1, 0, 2).reshape(bags, ctx.D)
+                if ctx.mean:
+                    gg = gg / lengths.clamp(min=1).to(gg.dtype)[:, None]
+                red.index_add_(0, inv, gg[bag])
+            ctx.table.update(slots, red)
+        return (None,) * 8
+
+
 class BatchedDynamicEmbeddingTablesV2(nn.Module):
     def __init__(self, table_options: List[DynamicEmbTableOptions], table_names: List[str],
                  pooling_mode: DynamicEmbPoolingMode = DynamicEmbPoolingMode.NONE,
@@ -101,17 +160,12 @@ class BatchedDynamicEmbeddingTablesV2(nn.Module):
             n = feature_splits[f]
             tab = self.tables[self.feature_table_map[f]]
             ids = indices[start:start + n]
-            rows = _DynamicLookupFn.apply(self._anchor, tab, ids, self.training)
             if self.pooling_mode == DynamicEmbPoolingMode.NONE:
-                outs.append(rows)
+                outs.append(_DynamicLookupFn.apply(self._anchor, tab, ids, self.training))
             else:
                 off = offsets[f * batch_size:(f + 1) * batch_size + 1] - start
-                lengths = off[1:] - off[:-1]
-                bag = torch.repeat_interleave(torch.arange(batch_size, device=rows.device), lengths)
-                pooled = torch.zeros(batch_size, rows.shape[1], dtype=rows.dtype, device=rows.device).index_add_(0, bag, rows)
-                if self.pooling_mode == DynamicEmbPoolingMode.MEAN:
-                    pooled = pooled / lengths.clamp(min=1).to(pooled.dtype)[:, None]
-                outs.append(pooled)
+                outs.append(_DynamicPooledLookupFn.apply(self._anchor, tab, ids, off, batch_size,
+                                                         self.pooling_mode == DynamicEmbPoolingMode.MEAN, self.training, self.output_dtype))
             start += n
         if self.pooling_mode == DynamicEmbPoolingMode.NONE:
             return torch.cat(outs, dim=0).to(self.output_dtype)

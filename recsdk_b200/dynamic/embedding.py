@@ -130,6 +130,8 @@ class DynamicEmbeddingBagCollection(_ShardedDynamicBase):
         return self.configs
 
     def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
+        if self.world == 1:
+            return self._forward_local(features)
         rows = self._sequence_rows(features)
         B = features.stride()
         lens = features.lengths().to(self.device)
@@ -146,3 +148,34 @@ class DynamicEmbeddingBagCollection(_ShardedDynamicBase):
             start += n
         feature_dims = [self.dims[t] for t in self.feature_table]
         return KeyedTensor(self.feature_names, feature_dims, torch.cat(outs, dim=1).to(self.output_dtype))
+
+    def _forward_local(self, features: KeyedJaggedTensor) -> KeyedTensor:
+        """One rank: pool straight from the unique rows (no per-id row tensor)."""
+        from .batched_dynamicemb_table import _DynamicPooledLookupFn
+
+        assert features.keys() == self.feature_names
+        B = features.stride()
+        ids = features.values().to(self.device).long()
+        offsets = features.offsets().to(self.device).long()
+        lk = self.lookup
+        if lk.training:
+            lk._update_score()
+        # features of one table are adjacent in the key order: one unique / lookup / pooled gather per table
+        outs, start, f = [], 0, 0
+        lpk = features.length_per_key()
+        F = len(self.feature_names)
+        while f < F:
+            ti = self.feature_table[f]
+            f1 = f
+            while f1 < F and self.feature_table[f1] == ti:
+                f1 += 1
+            n = sum(lpk[f:f1])
+            cfg = self.configs[ti]
+            off = offsets[f * B:f1 * B + 1] - start
+            mean = getattr(cfg, "pooling", PoolingType.SUM) == PoolingType.MEAN
+            outs.append(_DynamicPooledLookupFn.apply(lk._anchor, lk.tables[ti], ids[start:start + n], off, B, mean, lk.training,
+                                                     self.output_dtype))
+            start += n
+            f = f1
+        feature_dims = [self.dims[t] for t in self.feature_table]
+        return KeyedTensor(self.feature_names, feature_dims, torch.cat(outs, dim=1))
