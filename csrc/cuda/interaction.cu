@@ -18,6 +18,12 @@ namespace {
 
 constexpr int FMAX = 32;  // features padded to two m16 tiles
 
+// 16-byte asynchronous global -> shared copy (no register staging: a warp keeps its whole tile in flight)
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(rb::smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -64,8 +70,9 @@ interaction_fwd_kernel(const __nv_bfloat16* __restrict__ X0, long long ld0, cons
     __syncwarp();
     for (int i = lane; i < F * VPR; i += 32) {
       const int r = i / VPR, c = i % VPR;
-      *reinterpret_cast<uint4*>(xs + r * L::XS + c * 8) = (r == 0) ? __ldg(src0 + c) : __ldg(src + i - VPR);
+      cp_async16(xs + r * L::XS + c * 8, (r == 0) ? (src0 + c) : (src + i - VPR));
     }
+    cp_async_wait_all();
     __syncwarp();
     float acc[2][4][4];
 #pragma unroll
@@ -134,11 +141,12 @@ interaction_bwd_kernel(const __nv_bfloat16* __restrict__ X0, long long ld0, cons
     __syncwarp();
     for (int i = lane; i < F * VPR; i += 32) {
       const int r = i / VPR, c = i % VPR;
-      *reinterpret_cast<uint4*>(xs + r * L::XS + c * 8) = (r == 0) ? __ldg(src0 + c) : __ldg(src + i - VPR);
+      cp_async16(xs + r * L::XS + c * 8, (r == 0) ? (src0 + c) : (src + i - VPR));
     }
+    for (int i = lane; i < g_vec; i += 32) cp_async16(reinterpret_cast<uint4*>(gs) + i, g4 + i);
     for (int i = lane; i < (FMAX - F) * L::XS / 2; i += 32)
       reinterpret_cast<uint32_t*>(xs + F * L::XS)[i] = 0u;       // padding rows (the tile is reused as output)
-    for (int i = lane; i < g_vec; i += 32) reinterpret_cast<uint4*>(gs)[i] = __ldg(g4 + i);
+    cp_async_wait_all();
     __syncwarp();
     // symmetric dZ tile: zs[i][j] = dtri(max(i,j), min(i,j)), zero on the diagonal / padding
     for (int e = lane; e < FMAX * FMAX; e += 32) {
