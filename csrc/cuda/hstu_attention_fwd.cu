@@ -283,8 +283,9 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ok = ok && rb::mbar_wait(&p_empty[buf], ((t >> 1) & 1) ^ 1, abort_flag, p.status);
       if (!__all_sync(0xffffffffu, ok)) goto done;
       rb::tc_fence_after();
-      // fast path: a block strictly below the diagonal of an ordinary causal row block needs no mask
-      const bool full = p.causal && ntgt == 0 && (kb * BKV + BKV - 1 <= pi_lo) && (kb * BKV + BKV <= len_k);
+      // fast path: a key block that lies wholly in the history (before the targets), strictly below the diagonal of this
+      // row block, needs no mask - target rows see all of the history, ordinary rows everything up to themselves
+      const bool full = p.causal && (kb * BKV + BKV - 1 <= pi_lo) && (kb * BKV + BKV <= len_k - ntgt);
       {
         const int c = grp;
         uint32_t r[32];
