@@ -49,6 +49,7 @@ class OptimizerSpec:
     beta2: float = 0.999
     weight_decay: float = 0.0
     initial_accumulator_value: float = 0.0
+    accumulate_step: int = 1          # > 1: sum the row gradients of this many steps, then update once
 
     def state_elems_per_row(self, dim: int) -> int:
         return {OPT_SGD: 0, OPT_ROWWISE_ADAGRAD: 1, OPT_ADAGRAD: dim, OPT_ADAM: dim}[self.kind]

@@ -134,6 +134,7 @@ class CollectiveShardedEmbeddingBagCollection(nn.Module):
         self.world, self.rank, self.pg = env.world_size, env.rank, env.process_group
         self.input_pg = input_env.process_group if input_env is not None else None
         self._prepared: Dict[int, tuple] = {}
+        self._pending: Dict[int, list] = {}          # gradient accumulation: table -> [rows, grads, passes]
         self._prefetch_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
         self.opt = optimizer_spec or E.OptimizerSpec()
         self.hashed, self.out_dtype = hashed, out_dtype
@@ -348,6 +349,18 @@ class CollectiveShardedEmbeddingBagCollection(nn.Module):
         if self.world > 1 and self.kinds[ti] == E.SH_LOCAL:
             # replicated table: every replica applies the gradient of the global batch
             rows, grads = self._allgather_var(rows), self._allgather_var(grads.contiguous())
+        k = max(int(getattr(self.opt, "accumulate_step", 1)), 1)
+        if k > 1:
+            # gradient accumulation (the reference's GradientAccumulator, hybrid_torchrec/distributed/
+            # batched_embedding_kernel.py:111-230): keep the row gradients of k backward passes, then one exact update
+            pend = self._pending.setdefault(ti, [[], [], 0])
+            pend[0].append(rows)
+            pend[1].append(grads.detach().float())
+            pend[2] += 1
+            if pend[2] < k:
+                return
+            rows, grads = torch.cat(pend[0]), torch.cat(pend[1])
+            self._pending.pop(ti)
         apply_sparse_update(self.embedding_bags[self.tables[ti].name].weight, self.state[ti], rows, grads, self.opt,
                             max(self._step, 1))
 

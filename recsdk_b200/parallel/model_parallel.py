@@ -36,19 +36,29 @@ def _optimizer_spec_from_params(ebc: nn.Module, default: Optional[E.OptimizerSpe
     for p in ebc.parameters():
         classes = getattr(p, "_optimizer_classes", None)
         if classes:
-            cls, kw = classes[0], getattr(p, "_optimizer_kwargs", [{}])[0]
-            if issubclass(cls, torch.optim.Adagrad):
-                kind = E.OPT_ROWWISE_ADAGRAD if kw.get("rowwise", True) else E.OPT_ADAGRAD
-                return E.OptimizerSpec(kind=kind, lr=kw.get("lr", 0.01), eps=kw.get("eps", 1e-10),
-                                       weight_decay=kw.get("weight_decay", 0.0),
-                                       initial_accumulator_value=kw.get("initial_accumulator_value", 0.0))
-            if issubclass(cls, torch.optim.Adam):
-                b = kw.get("betas", (0.9, 0.999))
-                return E.OptimizerSpec(kind=E.OPT_ADAM, lr=kw.get("lr", 1e-3), eps=kw.get("eps", 1e-8), beta1=b[0],
-                                       beta2=b[1], weight_decay=kw.get("weight_decay", 0.0))
-            if issubclass(cls, torch.optim.SGD):
-                return E.OptimizerSpec(kind=E.OPT_SGD, lr=kw.get("lr", 0.01), weight_decay=kw.get("weight_decay", 0.0))
+            cls, kw = classes[0], dict(getattr(p, "_optimizer_kwargs", [{}])[0])
+            acc = int(kw.pop("accumulate_step", 1)) if kw.pop("use_accumulate", False) else 1
+            spec = _spec_of(cls, kw)
+            if spec is not None:
+                spec.accumulate_step = max(acc, 1)
+                return spec
     return default or E.OptimizerSpec()
+
+
+def _spec_of(cls, kw) -> Optional[E.OptimizerSpec]:
+    """Optimizer class + keyword arguments -> fused sparse optimizer spec (None for classes the fused update lacks)."""
+    if issubclass(cls, torch.optim.Adagrad):
+        kind = E.OPT_ROWWISE_ADAGRAD if kw.get("rowwise", True) else E.OPT_ADAGRAD
+        return E.OptimizerSpec(kind=kind, lr=kw.get("lr", 0.01), eps=kw.get("eps", 1e-10),
+                               weight_decay=kw.get("weight_decay", 0.0),
+                               initial_accumulator_value=kw.get("initial_accumulator_value", 0.0))
+    if issubclass(cls, torch.optim.Adam):
+        b = kw.get("betas", (0.9, 0.999))
+        return E.OptimizerSpec(kind=E.OPT_ADAM, lr=kw.get("lr", 1e-3), eps=kw.get("eps", 1e-8), beta1=b[0],
+                               beta2=b[1], weight_decay=kw.get("weight_decay", 0.0))
+    if issubclass(cls, torch.optim.SGD):
+        return E.OptimizerSpec(kind=E.OPT_SGD, lr=kw.get("lr", 0.01), weight_decay=kw.get("weight_decay", 0.0))
+    return None
 
 
 class DistributedModelParallel(nn.Module):
@@ -106,9 +116,13 @@ class DistributedModelParallel(nn.Module):
                     setattr(parent, name, sharded)
                     self.sharded_modules.append(sharded)
                     continue
+                fspec = _optimizer_spec_from_params(child, spec)
+                if fspec.accumulate_step > 1:
+                    raise NotImplementedError("gradient accumulation over several steps runs on the collective backend "
+                                              "(backend=\"collective\")")
                 sharded = ShardedEmbeddingBagCollection(
                     child.embedding_bag_configs(), entries, self.env, self.device,
-                    _optimizer_spec_from_params(child, spec), peer=self.peer, out_dtype=out_dtype,
+                    fspec, peer=self.peer, out_dtype=out_dtype,
                     max_local_batch=max_local_batch, one_hot=one_hot, init_weights=True)
                 if init_seed is not None:
                     sharded.reset_parameters(seed=init_seed)
