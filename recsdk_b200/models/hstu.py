@@ -61,7 +61,7 @@ class HSTULayer(nn.Module):
         hd = H * Dh
         xn = hstu_ops.ln_mul(x, None, self.norm_in_w, self.norm_in_b)
         uvqk = torch.nn.functional.silu(self.uvqk(xn))
-        u, v, q, k = uvqk[:, :hd], uvqk[:, hd:2 * hd], uvqk[:, 2 * hd:3 * hd], uvqk[:, 3 * hd:]
+        u, v, q, k = uvqk.split(hd, dim=1)                 # one split: its backward is a single concatenation
         T = x.shape[0]
         a = hstu_attention(q.unflatten(1, (H, Dh)), k.unflatten(1, (H, Dh)), v.unflatten(1, (H, Dh)), offsets,
                            max_len_q=max_len, alpha=1.0 / math.sqrt(Dh), scale=1.0 / max_len, causal=True,
