@@ -69,7 +69,12 @@ class PeerGroup:
         self.world = dist.get_world_size(self.pg) if self.pg is not None else 1
         self.rank = dist.get_rank(self.pg) if self.pg is not None else 0
         self.timeout_ms = int(timeout_ms)
-        self.use_multimem = os.environ.get("RECSDK_B200_MULTIMEM", "1") == "1"
+        # NVSwitch multicast (multimem.ld_reduce / multimem.st in the all-reduce) is opt-in: RECSDK_B200_MULTIMEM=1.
+        # Without it the peer buffers are not bound to a multicast object at all (plain peer loads / stores only), which
+        # is also what jobs whose ranks may leave need.
+        self.use_multimem = os.environ.get("RECSDK_B200_MULTIMEM", "0") == "1"
+        if not self.use_multimem:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         self._symm = None
         if self.world > 1:
             import torch.distributed._symmetric_memory as symm_mem
