@@ -115,7 +115,8 @@ def table_rows(seed: int, n: int = 26, lo: float = 1e4, hi: float = 4e7):
 def main() -> None:
     args = parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return
     if args.impl == "torch":
         # comparison arm: the same model and step in stock PyTorch + NCCL + cuBLAS (no code of this package)
