@@ -194,8 +194,12 @@ def run_hstu_inference_bench(args) -> None:
     from .hstu import HSTU, HSTUConfig
     from .hstu_inference import HSTURanker
 
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
+    if world > 1:                                           # serving replicas: every GPU holds the model and its own users
+        dist.init_process_group("nccl", device_id=dev)
     small = args.small
     users, cached, new, cands, page = (64, 2048, 128, 1024, 64) if not small else (4, 256, 64, 32, 64)
     cfg = HSTUConfig(num_layers=8 if not small else 2, d_model=512, num_heads=8, head_dim=64, max_seq_len=4096)
@@ -211,8 +215,8 @@ def run_hstu_inference_bench(args) -> None:
                         max_batch_size=users, max_seq_len=4096, dtype=torch.bfloat16, device=dev)
     kv = KVCacheManager.from_config(kvc)
     ranker = HSTURanker(model, kv)
-    uid = torch.arange(users, dtype=torch.int64) + 1000
-    gen = torch.Generator().manual_seed(7)
+    uid = torch.arange(users, dtype=torch.int64) + 1000 + rank * users
+    gen = torch.Generator().manual_seed(7 + rank)
 
     def ids_ts(n_per_user: int, t0: float):
         ids = torch.randint(0, n_items, (users, n_per_user), generator=gen)
@@ -256,6 +260,8 @@ def run_hstu_inference_bench(args) -> None:
     for i in range(W):
         request(i)
     torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
     _lib.check_status(dev)
     from bench import ClockSampler
 
@@ -275,21 +281,33 @@ def run_hstu_inference_bench(args) -> None:
         lat.append(a.elapsed_time(b))
     e1.record()
     torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize(dev)
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop()
     _lib.check_status(dev)
     lat_np = np.asarray(lat)
-    val = users * cands * args.steps / (ms / 1e3)
+    p50, p99 = float(np.percentile(lat_np, 50)), float(np.percentile(lat_np, 99))
+    if world > 1:                                           # slowest replica's time and latencies
+        t = torch.tensor([ms, p50, p99], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, p50, p99 = float(t[0]), float(t[1]), float(t[2])
+    val = users * cands * args.steps * world / (ms / 1e3)
     ids0, ts0 = reqs[0]
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
     print(json.dumps({
-        "metric": "HSTU ranking inference candidates/sec", "value": val, "unit": "candidates/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": W, "ms_per_step": ms / args.steps, "p50_ms": float(np.percentile(lat_np, 50)), "p99_ms": float(np.percentile(lat_np, 99)),
+        "metric": "HSTU ranking inference candidates/sec", "value": val, "unit": "candidates/s", "n_gpus": world, "steps": args.steps,
+        "warmup": W, "ms_per_step": ms / args.steps, "p50_ms": p50, "p99_ms": p99,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (uniform item ids, Exp time gaps), random-init weights",
         "config": {"model": "HSTU 8L d512 8x64" if not small else "HSTU 2L d512 8x64", "users": users, "cached_tokens": cached,
-                   "new_tokens": new, "candidates": cands, "page_size": page, "global_batch": users, "seq_len": total,
-                   "parallelism": "1 GPU", "l2": "KV pages read per request exceed L2 (%d MB)" % (users * total * 1024 * 2 * cfg.num_layers / 1e6)},
-        "e2e": {"value": val, "unit": "candidates/s", "h2d_bytes_per_step": int(ids0.numel() * 8 + ts0.numel() * 4),
-                "d2h_bytes_per_step": int(scores_host.numel() * 4),
+                   "new_tokens": new, "candidates": cands, "page_size": page, "global_batch": users * world, "seq_len": total,
+                   "parallelism": "%d serving replica(s), one per GPU" % world, "l2": "KV pages read per request exceed L2 (%d MB)" % (users * total * 1024 * 2 * cfg.num_layers / 1e6)},
+        "e2e": {"value": val, "unit": "candidates/s", "h2d_bytes_per_step": int(ids0.numel() * 8 + ts0.numel() * 4) * world,
+                "d2h_bytes_per_step": int(scores_host.numel() * 4) * world,
                 "note": "each request copies ids and timestamps from pinned memory and reads all scores back"},
         "gpu_launches": int(_lib.launch_count - lc0), "clocks": clocks, "impl": "ours"}))
