@@ -40,3 +40,20 @@ def bind_cpu(local_rank: Optional[int] = None, local_world_size: Optional[int] =
                 os.sched_setaffinity(0, before)
         return wrapped
     return deco
+
+
+def bind_rank_from_env(min_cores: int = 2) -> Optional[List[int]]:
+    """Pin this process to its rank's share of the cores (``LOCAL_RANK`` / ``LOCAL_WORLD_SIZE``) when there are several
+    local ranks and every rank would get at least ``min_cores``.  Opt-in: ``RECSDK_B200_BIND_CPU=1`` (on the 2-GPU HSTU
+    training benchmark it made no measurable difference, so it is off by default).
+    Returns the cores bound to, or None when nothing was changed."""
+    if os.environ.get("RECSDK_B200_BIND_CPU", "0") != "1":
+        return None
+    lws = int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("WORLD_SIZE", "1")))
+    lr = int(os.environ.get("LOCAL_RANK", "0"))
+    if lws <= 1:
+        return None
+    usable = sorted(os.sched_getaffinity(0))
+    if len(usable) // lws < min_cores:
+        return None
+    return bind_current_process(cores_for_rank(lr, lws, usable))

@@ -84,6 +84,9 @@ def run_hstu_bench(args) -> None:
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     if world > 1:
+        from ..common import bind_rank_from_env
+
+        bind_rank_from_env()                                # opt-in (RECSDK_B200_BIND_CPU=1): keep every rank on its own cores
         dist.init_process_group("nccl", device_id=dev)
     env = ShardingEnv(world, rank, dist.group.WORLD if world > 1 else None)
     B = 32 if not args.small else 4
