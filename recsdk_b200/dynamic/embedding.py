@@ -70,9 +70,17 @@ class _ShardedDynamicBase(nn.Module):
         feat = torch.repeat_interleave(torch.arange(F, device=ids.device), torch.tensor(lpk, device=ids.device))
         inv_dedup = None
         if self.use_index_dedup:
-            key = torch.stack([feat, ids], dim=1)
-            uniq, inv_dedup = torch.unique(key, dim=0, return_inverse=True)
-            feat, ids = uniq[:, 0].contiguous(), uniq[:, 1].contiguous()
+            # ids are feature-major, so the (feature, id) pairs de-duplicate with one 1-D unique per feature (a row-wise
+            # unique over pairs is far slower and this needs no assumption about the key range)
+            us, invs, fs, start, base = [], [], [], 0, 0
+            for f, n in enumerate(lpk):
+                u, inv = torch.unique(ids[start:start + n], return_inverse=True)
+                us.append(u)
+                invs.append(inv + base)
+                fs.append(torch.full((u.numel(),), f, dtype=feat.dtype, device=ids.device))
+                base += u.numel()
+                start += n
+            ids, inv_dedup, feat = torch.cat(us), torch.cat(invs), torch.cat(fs)
         dest = torch.remainder(ids, W)
         order = torch.argsort(dest * F + feat, stable=True)            # (destination, feature)-major
         send_ids = ids[order]

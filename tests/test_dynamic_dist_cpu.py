@@ -43,7 +43,7 @@ def _run(rank, world, pg, dump_dir=None):
     # DEBUG initialiser: a new key's row depends on the key only, so every sharding starts from the same table
     opts = {"tab": DynamicEmbTableOptions(initializer_args=DynamicEmbInitializerArgs(mode=DynamicEmbInitializerMode.DEBUG))}
     m = DynamicEmbeddingBagCollection(cfgs, opts, ShardingEnv(world, rank, pg), torch.device("cpu"), optimizer_type=OptimizerType.SGD,
-                                      learning_rate=1e-6)
+                                      learning_rate=1e-6, use_index_dedup=world > 1)
     w = torch.randn(16, generator=torch.Generator().manual_seed(3))
     losses = []
     for b in _batches():
