@@ -88,7 +88,8 @@ class _ShardedDynamicBase(nn.Module):
         recv_counts = torch.empty_like(counts)
         dist.all_to_all_single(recv_counts, counts.contiguous(), group=self.pg)
         in_splits = counts.sum(1).tolist()
-        out_splits = recv_counts.sum(1).tolist()
+        both = torch.cat([recv_counts.sum(1), recv_counts.sum(0)]).tolist()      # one host read for both split lists
+        out_splits, feature_splits = both[:W], both[W:]
         recv_ids = send_ids.new_empty(int(sum(out_splits)))
         dist.all_to_all_single(recv_ids, send_ids, out_splits, in_splits, group=self.pg)
         # owner side: regroup (source, feature) -> feature-major for the batched lookup
@@ -96,7 +97,7 @@ class _ShardedDynamicBase(nn.Module):
         seg_feat = torch.arange(F, device=ids.device).repeat(W)
         elem_feat = torch.repeat_interleave(seg_feat, rc)
         to_fm = torch.argsort(elem_feat, stable=True)
-        splits = recv_counts.sum(0).tolist()
+        splits = feature_splits
         rows_fm = self.lookup(recv_ids[to_fm], None, splits, 0)
         rows_sf = torch.empty_like(rows_fm)
         rows_sf[to_fm] = rows_fm                                        # differentiable scatter back
