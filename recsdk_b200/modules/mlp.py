@@ -16,6 +16,7 @@ from typing import List, Optional, Sequence
 import torch
 from torch import nn
 
+from ..ops import _lib
 from ..ops import dense_ops, gemm
 
 
@@ -65,7 +66,7 @@ class _FusedMLPFn(torch.autograd.Function):
         dz = dy if dy.stride(-1) == 1 else dy.contiguous()
         if mlp.relu[L - 1] and not ctx.grad_premasked:
             dz = dz * (acts[L] > 0).to(dz.dtype)
-        nsm = 148
+        nsm = _lib.num_sms(dz.device) if dz.is_cuda else 148
         dx = None
         bias_done = False            # this layer's bias gradient already came out of the GEMM that produced dz
         for l in range(L - 1, -1, -1):

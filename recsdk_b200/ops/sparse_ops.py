@@ -15,7 +15,8 @@ import torch
 
 from . import _lib
 
-_WS = {}
+_WS = {}      # scratch buffers per (device, purpose): reused by consecutive calls on ONE stream; callers that run these
+              # ops on several streams of a device at once must serialise them
 
 
 def _ws(device, name: str, n: int, dtype) -> torch.Tensor:
