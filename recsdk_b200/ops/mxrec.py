@@ -258,24 +258,12 @@ def split_embedding_codegen_forward_unweighted_cuda(dev_weights, uvm_weights, lx
                                                     hash_indices=None, offset_per_key=None, rows_per_table=None):
     """FBGEMM-TBE-compatible lookup over one flat weight buffer.  ``pooling_mode``: 0 sum, 1 mean, 2 none;
     ``hash_indices``, when given, replace ``indices`` (ids already mapped to rows)."""
-    from . import embedding_ops as E
+    from . import mxrec_tbe as T
 
-    idx = (hash_indices if hash_indices is not None else indices).long()
-    T = D_offsets.numel() - 1
-    dims = (D_offsets[1:] - D_offsets[:-1]).tolist()
-    B = (offsets.numel() - 1) // T
-    w_off = weights_offsets.tolist()
-    rows = list(rows_per_table.tolist()) if rows_per_table is not None else \
-        [((w_off[t + 1] if t + 1 < T else dev_weights.numel()) - w_off[t]) // dims[t] for t in range(T)]
-    tables = [dev_weights[w_off[t]: w_off[t] + rows[t] * dims[t]].view(rows[t], dims[t]) for t in range(T)]
-    if pooling_mode == 2:
-        off = offsets.tolist()
-        out = torch.zeros(idx.numel(), max_D, dtype=torch.float32, device=dev_weights.device)
-        for t in range(T):
-            a, b = off[t * B], off[(t + 1) * B]
-            out[a:b, : dims[t]] = tables[t][idx[a:b]].float()
-        return out
-    return E.reference_pooled_forward(tables, idx, offsets.long(), B, ["mean" if pooling_mode == 1 else "sum"] * T)
+    idx = hash_indices if hash_indices is not None else indices
+    geo = T._Geometry(dev_weights, weights_offsets, D_offsets, None, rows_per_table)
+    out_dtype = {0: torch.float32, 1: torch.float16, 5: torch.bfloat16}.get(int(output_dtype), torch.float32)
+    return T._forward(geo, dev_weights, idx, offsets.long(), int(pooling_mode), int(max_D), out_dtype)
 
 
 _def("hstu_dense(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, int max_seq_len=0, "
@@ -392,3 +380,65 @@ _def("hstu_fuxi(Tensor q, Tensor k, Tensor v, Tensor? timestampBias=None, Tensor
      "int maxSeqLen=0, float siluScale=0.0, str layout=\"normal\", int[]? seqOffset=None) -> Tensor", hstu_fuxi)
 _def("disentangle_attention(Tensor query_layer, Tensor key_layer, Tensor value_layer, Tensor pos_key_layer, Tensor pos_query_layer, "
      "Tensor relative_pos, Tensor attn_mask, str pos_attr_type, float score_scale) -> (Tensor, Tensor, Tensor)", disentangle_attention)
+
+
+# ------------------------------------------------------------------------------------------------ TBE training lookups
+def _def_autograd(name: str, schema_args: str, ret: str, fn) -> None:
+    """Ops whose implementation builds its own autograd node: the same function serves the Autograd key and the backends."""
+    if name in _REGISTERED:
+        return
+    _LIB.define(f"{name}({schema_args}) -> {ret}")
+    _LIB.impl(name, fn, "Autograd")
+    _LIB.impl(name, fn, "CompositeExplicitAutograd")
+    _REGISTERED.add(name)
+
+
+from . import mxrec_tbe as _tbe  # noqa: E402
+
+for _name, (_kind, _args) in _tbe.lookup_schemas().items():
+    _def_autograd(_name, _args, "Tensor", _tbe.make_lookup(_kind, _args))
+for _name, (_kind, _args) in _tbe.raw_backward_schemas().items():
+    _def(f"{_name}({_args}) -> Tensor", _tbe.make_raw_backward(_kind, _args))
+
+
+# ------------------------------------------------------------------------------------------------ v2 attention / distance variant
+def hstu_forward_v2(q, k, v, mask, rab, mask_type: int, max_seq_len: int, max_seq_len_k: Optional[int], silu_scale: Optional[float],
+                    seq_offset, seq_offset_k, num_context, num_target, target_group_size: Optional[int], alpha: Optional[float]):
+    """The second-generation jagged attention entry (``hstu_v2/hstu_forward_v2.cpp:72``): same math as ``hstu_jagged``; ``rab`` is
+    the materialised bias, ``silu_scale`` 0 / None means ``1 / max_seq_len``."""
+    return _jagged_common(q, k, v, mask, rab, mask_type, max_seq_len, silu_scale or 0.0, seq_offset,
+                          seq_offset if seq_offset_k is None else seq_offset_k, num_context, num_target, target_group_size or 0,
+                          1.0 if alpha is None else alpha)
+
+
+def hstu_backward_v2(grad, q, k, v, max_seqlen_q: int, max_seqlen_k: int, seq_offset_q, seq_offset_k, rab=None, num_context=None,
+                     num_target=None, scale: Optional[float] = 0.0, target_group_size: Optional[int] = 1, alpha: Optional[float] = 1.0,
+                     window_size_left: int = -1, window_size_right: int = -1):
+    """``(dq, dk, dv, drab)`` of the v2 attention (``hstu_v2/hstu_backward_v2.cpp:82``).  The window pair selects the mask:
+    ``(-1, 0)`` causal, ``(-1, -1)`` none; other windows are rejected, as no forward produces them."""
+    if (window_size_left, window_size_right) not in ((-1, 0), (-1, -1)):
+        raise NotImplementedError("sliding windows other than causal (-1, 0) and full (-1, -1) are not supported")
+    mask_type = 0 if window_size_right == 0 else 2
+    return _jagged_backward(grad, q, k, v, None, rab, mask_type, max_seqlen_q, scale or 0.0, seq_offset_q, seq_offset_k, num_context,
+                            num_target, target_group_size or 0, 1.0 if alpha is None else alpha)
+
+
+def distance_in_linear_silu(x, weight, bias, attr_dict: List[int]) -> List[torch.Tensor]:
+    """Forward of ``in_linear_silu`` that also returns the pre-activation ``x W^T + b`` as a fifth tensor, which the
+    stand-alone backward op consumes (``in_linear_silu/in_linear_silu.cpp:96-118``)."""
+    if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16):
+        z = gemm.gemm16(x.contiguous(), weight.contiguous(), bias=None if bias is None else bias.float())
+    else:
+        z = torch.nn.functional.linear(x.float(), weight.float(), None if bias is None else bias.float()).to(x.dtype)
+    y = torch.nn.functional.silu(z.float()).to(x.dtype)
+    return list(torch.split(y, list(attr_dict), dim=1)) + [z]
+
+
+_def("hstu_forward_v2(Tensor q, Tensor k, Tensor v, Tensor? mask, Tensor? rab, int mask_type, int max_seq_len, int? max_seq_len_k, "
+     "float? silu_scale, Tensor seq_offset, Tensor? seq_offset_k, Tensor? num_context, Tensor? num_target, int? target_group_size, "
+     "float? alpha) -> Tensor", hstu_forward_v2)
+_def("hstu_backward_v2(Tensor grad, Tensor q, Tensor k, Tensor v, int max_seqlen_q, int max_seqlen_k, Tensor seq_offset_q, "
+     "Tensor seq_offset_k, Tensor? rab=None, Tensor? num_context=None, Tensor? num_target=None, float? scale=0.0, "
+     "int? target_group_size=1, float? alpha=1.0, int window_size_left=-1, int window_size_right=-1) "
+     "-> (Tensor, Tensor, Tensor, Tensor)", hstu_backward_v2)
+_def("distance_in_linear_silu(Tensor x, Tensor weight, Tensor bias, int[] attr_dict) -> Tensor[]", distance_in_linear_silu)
