@@ -344,13 +344,16 @@ __global__ void hkv_update_kernel(HkvTable t, const long long* __restrict__ slot
         row[c] -= o.lr * gv / (sqrtf(a) + o.eps);
       }
     } else {
+      // Adam with decoupled weight decay, as the reference's Adam optimizer applies it
+      // (dynamic_emb csrc/dynamic_emb_op.cpp:1602 decay_factor = 1 - lr * weight_decay; csrc/ops/AdamW_update/AdamW_update_kernel.h:74)
+      const float decay = 1.f - o.lr * o.weight_decay;
       for (int c = lane; c < D; c += 32) {
-        const float gv = static_cast<float>(g[c]) + o.weight_decay * row[c];
+        const float gv = static_cast<float>(g[c]);
         const float m = o.beta1 * row[D + c] + (1.f - o.beta1) * gv;
         const float v = o.beta2 * row[2 * D + c] + (1.f - o.beta2) * gv * gv;
         row[D + c] = m;
         row[2 * D + c] = v;
-        row[c] -= (o.lr / o.bc1) * m / (sqrtf(v / o.bc2) + o.eps);
+        row[c] = row[c] * decay - (o.lr / o.bc1) * m / (sqrtf(v / o.bc2) + o.eps);
       }
     }
   }

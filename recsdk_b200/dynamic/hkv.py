@@ -412,11 +412,11 @@ class HostDynamicTable:
                 row[D:2 * D] += g * g
                 row[:D] -= lr * g / (np.sqrt(row[D:2 * D]) + eps)
             else:
-                gg = g + weight_decay * row[:D]
-                row[D:2 * D] = beta1 * row[D:2 * D] + (1 - beta1) * gg
-                row[2 * D:3 * D] = beta2 * row[2 * D:3 * D] + (1 - beta2) * gg * gg
+                # decoupled decay (dynamic_emb csrc/dynamic_emb_op.cpp:1602 of the reference)
+                row[D:2 * D] = beta1 * row[D:2 * D] + (1 - beta1) * g
+                row[2 * D:3 * D] = beta2 * row[2 * D:3 * D] + (1 - beta2) * g * g
                 bc1, bc2 = 1 - beta1 ** step, 1 - beta2 ** step
-                row[:D] -= (lr / bc1) * row[D:2 * D] / (np.sqrt(row[2 * D:3 * D] / bc2) + eps)
+                row[:D] = row[:D] * (1 - lr * weight_decay) - (lr / bc1) * row[D:2 * D] / (np.sqrt(row[2 * D:3 * D] / bc2) + eps)
 
     def export_batch(self, slot0: int = 0, count=None, min_score=None, with_values: bool = True):
         ks = [k for k in self.rows if min_score is None or self.score[k] >= min_score]

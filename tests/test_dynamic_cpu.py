@@ -121,3 +121,19 @@ def test_caching_with_disk_storage(tmp_path):
         for i, k in enumerate(ids.tolist()):
             seen[k] = out[i].detach() - 0.5
     assert disk.size() > 0 and m.table("t").table.size() <= 16
+
+
+def test_host_table_adam_weight_decay_is_decoupled():
+    """The reference's Adam multiplies the weights by ``1 - lr * weight_decay`` and keeps the decay out of the moments
+    (dynamic_emb ``csrc/dynamic_emb_op.cpp:1602``)."""
+    import torch
+    from recsdk_b200.dynamic.hkv import HostDynamicTable, InitializerArgs, InitMode, OptimizerType
+
+    t = HostDynamicTable(4, 64, optimizer=OptimizerType.ADAM, init=InitializerArgs(mode=InitMode.CONSTANT, value=0.5))
+    keys = torch.arange(1, 6, dtype=torch.int64)
+    slots = t.find_or_insert(keys)[0]
+    g = torch.full((5, 4), 0.25)
+    t.update(slots, g, lr=0.1, eps=1e-8, weight_decay=0.05, step=1)
+    want = 0.5 * (1 - 0.1 * 0.05) - 0.1 * 1.0 / (1.0 + 1e-8)      # m_hat / sqrt(v_hat) == 1 for a constant gradient
+    got = t.gather(slots)[:, :4]
+    assert torch.allclose(got, torch.full((5, 4), want), atol=1e-6)

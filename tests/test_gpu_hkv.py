@@ -106,6 +106,20 @@ def test_fused_update_on_slots(opt):
     _lib.check_status()
 
 
+def test_adam_weight_decay_is_decoupled():
+    D = 16
+    t = HKVTable(D, 256, DEV, optimizer=OptimizerType.ADAM, init=InitializerArgs(mode=InitMode.NORMAL, mean=0.0, std_dev=0.1, seed=9))
+    keys = _keys(40, seed=10)
+    slots, _, _ = t.find_or_insert(keys)
+    w = t.gather(slots).clone()
+    g = torch.randn(40, D, device=DEV)
+    t.update(slots, g, lr=0.1, eps=1e-8, weight_decay=0.05, step=1)
+    m, v = 0.1 * g, 0.001 * g * g
+    want = w * (1 - 0.1 * 0.05) - (0.1 / 0.1) * m / ((v / 0.001).sqrt() + 1e-8)
+    assert torch.allclose(t.gather(slots), want, atol=1e-5, rtol=1e-4)
+    _lib.check_status()
+
+
 def test_assign_accum_and_insert_and_evict():
     t = HKVTable(4, 256, DEV, init=InitializerArgs(mode=InitMode.CONSTANT, value=0.5))
     keys = _keys(50, seed=7)
