@@ -47,8 +47,57 @@ struct SwapInfoFuture {
   bool ready() { return fut.wait_for(std::chrono::seconds(0)) == std::future_status::ready; }
 };
 
+// future of a restore running on the shared helper pool; keeps the arrays alive until it finishes
+struct RestoreFuture {
+  std::future<int64_t> fut;
+  I64 unique_indices, unique_inverse, unique_offset;
+  py::array_t<int64_t> hash_indices;
+  void get() {
+    if (!fut.valid()) return;                      // already collected
+    int64_t bad;
+    { py::gil_scoped_release rel; bad = fut.get(); }
+    if (bad >= 0) throw std::out_of_range("restore: index out of range at position " + std::to_string(bad));
+  }
+  bool ready() { return !fut.valid() || fut.wait_for(std::chrono::seconds(0)) == std::future_status::ready; }
+};
+
+static ThreadPool& helper_pool() {
+  static ThreadPool pool(2);
+  return pool;
+}
+
+static void check_restore_args(const I64& ui, const I64& inv, const I64& uo, const std::vector<int64_t>& opt,
+                               const py::array_t<int64_t>& out) {
+  if (ui.ndim() != 1 || inv.ndim() != 1 || uo.ndim() != 1 || out.ndim() != 1) throw std::invalid_argument("restore: tensors must be 1-D");
+  if (out.size() != inv.size()) throw std::invalid_argument("restore: hash_indices length must equal unique_inverse length");
+  if (static_cast<size_t>(uo.size()) != opt.size() || opt.empty())
+    throw std::invalid_argument("restore: unique_offset length must equal offsets_per_table length");
+}
+
 PYBIND11_MODULE(_C_host, m) {
   m.doc() = "recsdk_b200 host engines";
+
+  m.def("restore", [](I64 ui, I64 inv, I64 uo, std::vector<int64_t> opt, py::array_t<int64_t, py::array::c_style> out) {
+    check_restore_args(ui, inv, uo, opt, out);
+    int64_t bad;
+    {
+      const int64_t* a = ui.data(); const int64_t* b = inv.data(); const int64_t* c = uo.data(); int64_t* o = out.mutable_data();
+      const int64_t nu = ui.size(), ni = inv.size(), nt = static_cast<int64_t>(opt.size()) - 1;
+      py::gil_scoped_release rel;
+      bad = restore_hash_indices(a, nu, b, ni, c, opt.data(), nt, o);
+    }
+    if (bad >= 0) throw std::out_of_range("restore: index out of range at position " + std::to_string(bad));
+  });
+  py::class_<RestoreFuture>(m, "RestoreFuture").def("get", &RestoreFuture::get).def("ready", &RestoreFuture::ready);
+  m.def("restore_async", [](I64 ui, I64 inv, I64 uo, std::vector<int64_t> opt, py::array_t<int64_t, py::array::c_style> out) {
+    check_restore_args(ui, inv, uo, opt, out);
+    auto f = std::make_unique<RestoreFuture>();
+    f->unique_indices = ui; f->unique_inverse = inv; f->unique_offset = uo; f->hash_indices = out;
+    const int64_t* a = ui.data(); const int64_t* b = inv.data(); const int64_t* c = uo.data(); int64_t* o = out.mutable_data();
+    const int64_t nu = ui.size(), ni = inv.size(), nt = static_cast<int64_t>(opt.size()) - 1;
+    f->fut = helper_pool().submit([=]() { return restore_hash_indices(a, nu, b, ni, c, opt.data(), nt, o); });
+    return f;
+  });
 
   // ------------------------------------------------------------------ ids processing
   py::class_<IdsMapper>(m, "IdsMapper")

@@ -170,4 +170,34 @@ inline void block_bucketize(const int64_t* lengths, const int64_t* indices, cons
   }
 }
 
+// Rebuild the per-id device-cache offsets after the swap planner assigned an offset to every unique key:
+// hash_indices[r] = unique_indices[unique_inverse[r] + unique_offset[t]] for the ids r of table t
+// (offsets_per_table[t] .. offsets_per_table[t+1]).  Returns the first bad position (or -1); nothing is written past it
+// for that table (the reference: torchrec_embcache csrc/ops/restore.cpp:17-70).
+inline int64_t restore_hash_indices(const int64_t* unique_indices, int64_t n_unique, const int64_t* unique_inverse, int64_t n_ids,
+                                    const int64_t* unique_offset, const int64_t* offsets_per_table, int64_t n_tables,
+                                    int64_t* hash_indices) {
+  int64_t bad = -1;
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int64_t t = 0; t < n_tables; ++t) {
+    const int64_t shift = unique_offset[t];
+    const int64_t r0 = offsets_per_table[t], r1 = offsets_per_table[t + 1];
+    if (r0 < 0 || r1 > n_ids || r0 > r1) {
+#pragma omp critical
+      bad = bad < 0 ? r0 : bad;
+      continue;
+    }
+    for (int64_t r = r0; r < r1; ++r) {
+      const int64_t g = unique_inverse[r] + shift;
+      if (g < 0 || g >= n_unique) {
+#pragma omp critical
+        bad = bad < 0 ? r : bad;
+        break;
+      }
+      hash_indices[r] = unique_indices[g];
+    }
+  }
+  return bad;
+}
+
 }  // namespace rbh

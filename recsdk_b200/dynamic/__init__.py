@@ -9,8 +9,10 @@ from .hkv import EvictStrategy, HKVTable, HostDynamicTable, InitializerArgs, Ini
 from .key_value_table import DiskStorage, KeyValueTable, Storage, TableStorage
 from .planner import (DynamicEmbeddingBagCollectionSharder, DynamicEmbeddingCollectionSharder, DynamicEmbeddingShardingPlanner,
                       DynamicEmbParameterConstraints, DynamicEmbParameterSharding)
+from .construct_twin_module import ConstructTwinModule, StaticTwin, generate_sparse_feature
 
 __all__ = [
+    "ConstructTwinModule", "StaticTwin", "generate_sparse_feature",
     "BatchedDynamicEmbeddingTablesV2", "DynamicEmbDump", "DynamicEmbLoad", "get_score", "incremental_dump", "set_score",
     "DynamicEmbCheckMode", "DynamicEmbInitializerArgs", "DynamicEmbInitializerMode", "DynamicEmbPoolingMode",
     "DynamicEmbScoreStrategy", "DynamicEmbTableOptions", "EmbOptimType", "convert_optimizer_type",

@@ -74,7 +74,25 @@ def _pow2_ceil(x: int) -> int:
     return p
 
 
-class HKVTable:
+class _VariableInterface:
+    """The remaining calls of the reference's table handle, stated over ``find`` / ``gather`` / ``export_batch``
+    (dynamic_emb ``csrc/dynamic_variable_base.h:99-251`` of the reference: ``find_and_initialize``, ``export_batch_matched``,
+    ``count_matched``)."""
+
+    def find_and_initialize(self, keys: torch.Tensor, value: float = 0.0, dtype: torch.dtype = torch.float32):
+        """Evaluation lookup: rows of resident keys, ``value`` for the others; nothing is inserted.  -> (rows, found)."""
+        slots, found = self.find(keys)
+        return self.gather(slots, dtype=dtype, missing_value=value), found
+
+    def export_batch_matched(self, threshold: int, slot0: int = 0, count: Optional[int] = None, with_values: bool = True):
+        """Entries whose score is at least ``threshold`` (the incremental-dump filter)."""
+        return self.export_batch(slot0, count, min_score=int(threshold), with_values=with_values)
+
+    def count_matched(self, threshold: int) -> int:
+        return int(self.export_batch(0, None, min_score=int(threshold), with_values=False)[0].numel())
+
+
+class HKVTable(_VariableInterface):
     def __init__(self, dim: int, capacity: int, device: torch.device, optimizer: OptimizerType = OptimizerType.SGD,
                  evict_strategy: EvictStrategy = EvictStrategy.LRU, max_capacity: Optional[int] = None,
                  max_load_factor: float = 0.5, hbm_rows: Optional[int] = None,
@@ -282,7 +300,7 @@ class HKVTable:
         return int(t.item())
 
 
-class HostDynamicTable:
+class HostDynamicTable(_VariableInterface):
     """Dictionary-backed table with the ``HKVTable`` interface (CPU execution and test oracle)."""
 
     def __init__(self, dim: int, capacity: int, optimizer: OptimizerType = OptimizerType.SGD,

@@ -4,10 +4,11 @@ from .configs import (POLICY_COUNT, POLICY_SHOW_CLICK, AdmitAndEvictConfig, EmbC
 from .embedding_bag import (EmbCacheEmbeddingBagCollection, EmbCacheEmbeddingBagCollectionSharder,
                             EmbCacheShardedEmbeddingBagCollection, calculate_caches)
 from .embedding import EmbCacheEmbeddingCollection, EmbCacheEmbeddingCollectionSharder, EmbCacheShardedEmbeddingCollection
+from .restore import RestoreTask, restore, restore_async
 from .saver import Saver
 from .train_pipeline import EmbCacheTrainPipelineSparseDist
 
 __all__ = ["POLICY_COUNT", "POLICY_SHOW_CLICK", "AdmitAndEvictConfig", "EmbCacheEmbeddingBagConfig", "EmbCacheEmbeddingConfig",
            "InitializerType", "ShowClickParams", "EmbCacheEmbeddingBagCollection", "EmbCacheEmbeddingBagCollectionSharder",
            "EmbCacheShardedEmbeddingBagCollection", "calculate_caches", "EmbCacheEmbeddingCollection", "EmbCacheEmbeddingCollectionSharder",
-           "EmbCacheShardedEmbeddingCollection", "Saver", "EmbCacheTrainPipelineSparseDist"]
+           "EmbCacheShardedEmbeddingCollection", "Saver", "EmbCacheTrainPipelineSparseDist", "RestoreTask", "restore", "restore_async"]

@@ -137,3 +137,18 @@ def test_host_table_adam_weight_decay_is_decoupled():
     want = 0.5 * (1 - 0.1 * 0.05) - 0.1 * 1.0 / (1.0 + 1e-8)      # m_hat / sqrt(v_hat) == 1 for a constant gradient
     got = t.gather(slots)[:, :4]
     assert torch.allclose(got, torch.full((5, 4), want), atol=1e-6)
+
+
+def test_variable_interface_eval_lookup_and_matched_export():
+    import torch
+    from recsdk_b200.dynamic.hkv import EvictStrategy, HostDynamicTable, InitializerArgs, InitMode
+
+    t = HostDynamicTable(4, 64, evict_strategy=EvictStrategy.CUSTOMIZED, init=InitializerArgs(mode=InitMode.CONSTANT, value=0.5))
+    t.find_or_insert(torch.tensor([3, 5, 9]), scores=torch.tensor([10, 20, 30]))
+    rows, found = t.find_and_initialize(torch.tensor([5, 7]), value=-1.0)
+    assert found.tolist() == [True, False]
+    assert torch.equal(rows, torch.tensor([[0.5] * 4, [-1.0] * 4]))
+    assert t.size() == 3                                          # the miss was not inserted
+    assert t.count_matched(20) == 2
+    keys, scores, vals, _ = t.export_batch_matched(20)
+    assert sorted(keys.tolist()) == [5, 9] and sorted(scores.tolist()) == [20, 30] and vals.shape == (2, 4)

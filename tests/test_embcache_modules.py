@@ -152,3 +152,34 @@ def test_sequence_collection_small_cache_equals_big_cache():
 
     a, b = train(build([40, 64])), train(build([1001, 501]))
     assert np.allclose(a, b, rtol=1e-5, atol=1e-6), (a, b)
+
+
+def test_restore_and_restore_async():
+    import pytest
+    import torch
+    from recsdk_b200.embcache import restore, restore_async
+
+    g = torch.Generator().manual_seed(0)
+    per_table = [torch.randint(0, 20, (n,), generator=g) for n in (50, 0, 31)]
+    uniq, inv, uoff, opt = [], [], [0], [0]
+    for ids in per_table:
+        u, i = torch.unique(ids, return_inverse=True)
+        uniq.append(u + 1000 * len(uoff))                         # stands for the cache offsets of the unique keys
+        inv.append(i)
+        uoff.append(uoff[-1] + u.numel())
+        opt.append(opt[-1] + ids.numel())
+    unique_indices, unique_inverse = torch.cat(uniq), torch.cat(inv)
+    unique_offset = torch.tensor(uoff, dtype=torch.int64)
+    want = torch.cat([u[i] for u, i in zip(uniq, inv)])
+    out = torch.full((unique_inverse.numel(),), -7, dtype=torch.int64)
+    assert restore(unique_indices, unique_inverse, unique_offset, opt, out) is out
+    assert torch.equal(out, want)
+    out2 = torch.zeros_like(out)
+    task = restore_async(unique_indices, unique_inverse, unique_offset, opt, out2)
+    assert torch.equal(task.get(), want) and task.ready()
+    bad = unique_inverse.clone()
+    bad[3] = 10_000
+    with pytest.raises(IndexError):
+        restore(unique_indices, bad, unique_offset, opt, out)
+    with pytest.raises(ValueError):
+        restore(unique_indices, unique_inverse, unique_offset[:-1], opt, out)
