@@ -5,6 +5,8 @@
 // Specs: cust_op/ascendc_op/ai_core_op/{ln_mul,norm_multiply_dropout,relative_attn_bias_time,
 // relative_attn_bias_pos,relative_attn_bias_backward,concat_2d_jagged,reverse_sequence,gather_for_rank1}/
 // */README.md and inference/kvcache_manager/src/kernels/*.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace {
@@ -86,6 +88,98 @@ ln_mul_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __
   }
   __syncthreads();
   for (int c = threadIdx.x; c < C; c += blockDim.x) { atomicAdd(dgamma + c, sg[c]); atomicAdd(dbeta + c, sb[c]); }
+}
+
+// bf16, C = NCH * 256 (256 or 512): every lane keeps its 8 * NCH columns of the row in registers (one 16-byte load per tensor and chunk), so
+// each input is read once; the per-column dgamma / dbeta partial sums stay in registers over all rows of the warp and are
+// combined through shared memory once per block.
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
+template <int NCH, bool DROP>
+__global__ void __launch_bounds__(128)
+ln_mul_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ u,
+                      const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mean,
+                      const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ du,
+                      float* __restrict__ dgamma, float* __restrict__ dbeta, long long rows, float drop, unsigned long long seed) {
+  constexpr int C = NCH * 256;
+  __shared__ __align__(16) float red[2][C];
+  __shared__ __align__(16) float gb[2][C];          // gamma, beta
+  const int lane = threadIdx.x & 31;
+  const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const float inv_keep = drop > 0.f ? 1.f / (1.f - drop) : 1.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) { gb[0][c] = gamma[c]; gb[1][c] = beta[c]; red[0][c] = 0.f; red[1][c] = 0.f; }
+  __syncthreads();
+  const volatile float* gmv = gb[0];               // volatile: keeps these loop-invariant loads out of registers
+  const volatile float* btv = gb[1];
+  float dg[NCH][8], db[NCH][8];
+#pragma unroll
+  for (int k = 0; k < NCH; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { dg[k][i] = 0.f; db[k][i] = 0.f; }
+  for (long long r = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps_total) {
+    float g[NCH][8], xh[NCH][8], uu[NCH][8];
+    const float m = mean[r], rs = rstd[r];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const long long e0 = r * C + k * 256 + lane * 8;
+      unpack8(*reinterpret_cast<const uint4*>(dy + e0), g[k]);
+      unpack8(*reinterpret_cast<const uint4*>(x + e0), xh[k]);
+      if (u) unpack8(*reinterpret_cast<const uint4*>(u + e0), uu[k]);
+    }
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (DROP) {
+          const unsigned long long e = static_cast<unsigned long long>(r) * C + k * 256 + lane * 8 + i;
+          g[k][i] = hash_u01(seed, e) < drop ? 0.f : g[k][i] * inv_keep;
+        }
+        if (!u) uu[k][i] = 1.f;
+        xh[k][i] = (xh[k][i] - m) * rs;
+        const float dn = g[k][i] * uu[k][i];
+        const float dng = dn * gmv[k * 256 + lane * 8 + i];
+        a += dng;
+        b += dng * xh[k][i];
+        dg[k][i] += dn * xh[k][i];
+        db[k][i] += dn;
+      }
+    }
+    a = rb::warp_sum(a) * (1.f / C); b = rb::warp_sum(b) * (1.f / C);
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const long long e0 = r * C + k * 256 + lane * 8;
+      float o[8], q[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float gmc = gmv[k * 256 + lane * 8 + i];
+        o[i] = rs * (g[k][i] * uu[k][i] * gmc - a - xh[k][i] * b);
+        q[i] = g[k][i] * (xh[k][i] * gmc + btv[k * 256 + lane * 8 + i]);
+      }
+      *reinterpret_cast<uint4*>(dx + e0) = pack8(o);
+      if (du) *reinterpret_cast<uint4*>(du + e0) = pack8(q);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < NCH; ++k)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      atomicAdd(&red[0][k * 256 + lane * 8 + i], dg[k][i]);
+      atomicAdd(&red[1][k * 256 + lane * 8 + i], db[k][i]);
+    }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) { atomicAdd(dgamma + c, red[0][c]); atomicAdd(dbeta + c, red[1][c]); }
 }
 
 // ------------------------------------------------------------------ relative attention bias
@@ -270,6 +364,18 @@ RB_API int rb_ln_mul_bwd(const void* dy, const void* x, const void* u, const flo
   if (rows == 0) return 0;
   const int blocks = (num_sms > 0 ? num_sms : 148) * 2;
   const size_t smem = sizeof(float) * 2 * C;
+  auto al16 = [](const void* p) { return (reinterpret_cast<unsigned long long>(p) & 15ull) == 0; };
+  if (dtype == 2 && (C == 256 || C == 512) && al16(dy) && al16(x) && al16(u) && al16(dx) && al16(du)) {
+    const __nv_bfloat16 *pdy = (const __nv_bfloat16*)dy, *px = (const __nv_bfloat16*)x, *pu = (const __nv_bfloat16*)u;
+    __nv_bfloat16 *pdx = (__nv_bfloat16*)dx, *pdu = (__nv_bfloat16*)du;
+    const int vb = static_cast<int>(std::min<long long>((num_sms > 0 ? num_sms : 148) * 3LL, (rows + 3) / 4));
+    const unsigned long long sd = (unsigned long long)seed;
+#define RB_LN_BWD(NCH_, DROP_) ln_mul_bwd_vec_kernel<NCH_, DROP_><<<vb, 128, 0, st>>>(pdy, px, pu, gamma, beta, mean, rstd, pdx, pdu, dgamma, dbeta, rows, drop, sd)
+    if (C == 256) { if (drop > 0.f) RB_LN_BWD(1, true); else RB_LN_BWD(1, false); }
+    else { if (drop > 0.f) RB_LN_BWD(2, true); else RB_LN_BWD(2, false); }
+#undef RB_LN_BWD
+    return static_cast<int>(cudaGetLastError());
+  }
   if (dtype == 0)
     ln_mul_bwd_kernel<float><<<blocks, 256, smem, st>>>((const float*)dy, (const float*)x, (const float*)u, gamma, beta, mean, rstd, (float*)dx, (float*)du, dgamma, dbeta, rows, C, drop, (unsigned long long)seed);
   else if (dtype == 2)

@@ -63,3 +63,26 @@ def test_ln_mul_and_token_mixing():
     assert torch.allclose(xg.grad.cpu(), xc.grad, atol=2e-3, rtol=2e-3)
     t = torch.randn(3, 32, 32, generator=g)
     _cmp(H.token_mixing, t, torch.ones(32), torch.zeros(32), tol=1e-4)
+
+
+@pytest.mark.parametrize("C", [256, 512, 384])
+@pytest.mark.parametrize("with_u", [True, False])
+def test_ln_mul_backward_bf16_all_gradients(C, with_u):
+    """bf16 rows of width 256 / 512 take the register-resident vector kernel, 384 the generic one; both against fp32 PyTorch."""
+    g = torch.Generator().manual_seed(C + int(with_u))
+    rows = 1000
+    x = torch.randn(rows, C, generator=g).bfloat16()
+    u = torch.randn(rows, C, generator=g).bfloat16() if with_u else None
+    ga, be = torch.randn(C, generator=g), torch.randn(C, generator=g)
+    dy = torch.randn(rows, C, generator=g).bfloat16()
+    leaves_g = [t.cuda().requires_grad_(True) if t is not None else None for t in (x, u, ga, be)]
+    leaves_c = [t.float().requires_grad_(True) if t is not None else None for t in (x, u, ga, be)]
+    H.ln_mul(*leaves_g).backward(dy.cuda())
+    xn = torch.nn.functional.layer_norm(leaves_c[0], (C,), leaves_c[2], leaves_c[3], 1e-5)
+    (xn * leaves_c[1] if with_u else xn).backward(dy.float())
+    for a, b, tol in zip(leaves_g, leaves_c, (0.05, 0.05, 0.02, 0.02)):
+        if a is None:
+            continue
+        ref = b.grad
+        err = (a.grad.float().cpu() - ref).abs().max().item()
+        assert err <= tol * max(1.0, ref.abs().max().item()), (err, ref.abs().max().item())
