@@ -950,6 +950,47 @@ __global__ void pooled_scatter_add_kernel(const GT* __restrict__ g, long long ld
   }
 }
 
+// Sorted form of the same reduction: the (unique row, bag) pairs arrive sorted by row, every group of G lanes owns CH
+// consecutive pairs and keeps a running sum while the row stays the same.  A row whose pairs all lie inside one group's
+// range is written with a plain store; only rows that span groups (the hot keys of a skewed batch) are accumulated with
+// vector reductions, one per group instead of one per id.  `red` must be zero where rows span groups (the caller zeroes it).
+template <typename GT, int CH>
+__global__ void pooled_segment_add_kernel(const GT* __restrict__ g, long long ld_g, const long long* __restrict__ keys,
+                                          const int* __restrict__ bags_sorted, const long long* __restrict__ offsets, long long n,
+                                          long long B, int D, int G, int mean, float* __restrict__ red) {
+  const int gl = threadIdx.x & (G - 1);
+  const long long group = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) / G;
+  const long long p0 = group * CH;
+  if (p0 >= n) return;
+  const long long p1 = (p0 + CH < n) ? p0 + CH : n;
+  for (int c = gl; c * 4 < D; c += G) {
+    long long cur = keys[p0];
+    bool starts_here = (p0 == 0) || (keys[p0 - 1] != cur);
+    float ax = 0.f, ay = 0.f, az = 0.f, aw = 0.f;
+#pragma unroll 4
+    for (long long p = p0; p < p1; ++p) {
+      const long long k = keys[p];
+      if (k != cur) {
+        float* o = red + cur * D + c * 4;
+        if (starts_here) *reinterpret_cast<float4*>(o) = make_float4(ax, ay, az, aw);
+        else rb::red_add_v4(o, ax, ay, az, aw);
+        cur = k; starts_here = true;
+        ax = ay = az = aw = 0.f;
+      }
+      const long long bag = bags_sorted[p];
+      float sc = 1.f;
+      if (mean) { const long long len = offsets[bag + 1] - offsets[bag]; sc = len > 0 ? 1.f / static_cast<float>(len) : 1.f; }
+      const GT* gp = g + (bag % B) * ld_g + (bag / B) * D + c * 4;
+      ax += static_cast<float>(gp[0]) * sc; ay += static_cast<float>(gp[1]) * sc;
+      az += static_cast<float>(gp[2]) * sc; aw += static_cast<float>(gp[3]) * sc;
+    }
+    const bool ends_here = (p1 == n) || (keys[p1] != cur);
+    float* o = red + cur * D + c * 4;
+    if (starts_here && ends_here) *reinterpret_cast<float4*>(o) = make_float4(ax, ay, az, aw);
+    else rb::red_add_v4(o, ax, ay, az, aw);
+  }
+}
+
 static int pooled_group(int D) {
   int g = 1;
   while (g < 32 && g * 4 < D) g <<= 1;
@@ -982,6 +1023,33 @@ RB_API int rb_pooled_scatter_add(const void* g, int g_dtype, long long ld_g, con
     case DT_F32: pooled_scatter_add_kernel<float><<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(g), ld_g, inverse, offsets, bags, B, D, G, mean, red); break;
     case DT_F16: pooled_scatter_add_kernel<__half><<<blocks, 256, 0, st>>>(reinterpret_cast<const __half*>(g), ld_g, inverse, offsets, bags, B, D, G, mean, red); break;
     case DT_BF16: pooled_scatter_add_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(g), ld_g, inverse, offsets, bags, B, D, G, mean, red); break;
+    default: return -1;
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Radix sort of (row, bag) pairs on the low `end_bit` bits of the row index; temp size: rb_sort_segments_temp_bytes(n).
+RB_API int rb_sort_pairs_i64_i32(const long long* keys_in, const int* vals_in, long long n, int end_bit, long long* keys_out,
+                                 int* vals_out, void* temp, long long temp_bytes, cudaStream_t st) {
+  if (n == 0) return 0;
+  size_t tb = static_cast<size_t>(temp_bytes);
+  return static_cast<int>(cub::DeviceRadixSort::SortPairs(temp, tb, keys_in, keys_out, vals_in, vals_out, static_cast<int>(n), 0,
+                                                          end_bit, st));
+}
+
+// red[row] (+)= sum of the gradients of the bags that used the row; keys / bags sorted by row (see the kernel above)
+RB_API int rb_pooled_segment_add(const void* g, int g_dtype, long long ld_g, const long long* keys_sorted, const int* bags_sorted,
+                                 const long long* offsets, long long n, long long B, int D, int mean, float* red, cudaStream_t st) {
+  if (n == 0) return 0;
+  if (D % 4) return -1;
+  constexpr int CH = 64;
+  const int G = pooled_group(D);
+  const long long groups = (n + CH - 1) / CH;
+  const unsigned blocks = static_cast<unsigned>((groups * G + 255) / 256);
+  switch (g_dtype) {
+    case DT_F32: pooled_segment_add_kernel<float, CH><<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(g), ld_g, keys_sorted, bags_sorted, offsets, n, B, D, G, mean, red); break;
+    case DT_F16: pooled_segment_add_kernel<__half, CH><<<blocks, 256, 0, st>>>(reinterpret_cast<const __half*>(g), ld_g, keys_sorted, bags_sorted, offsets, n, B, D, G, mean, red); break;
+    case DT_BF16: pooled_segment_add_kernel<__nv_bfloat16, CH><<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(g), ld_g, keys_sorted, bags_sorted, offsets, n, B, D, G, mean, red); break;
     default: return -1;
   }
   return static_cast<int>(cudaGetLastError());

@@ -43,6 +43,9 @@ class _DynamicLookupFn(torch.autograd.Function):
         return None, None, None, None
 
 
+_SORTED_REDUCE_MIN_IDS = int(__import__("os").environ.get("RECSDK_B200_SORTED_REDUCE_MIN_IDS", "65536"))
+
+
 class _DynamicPooledLookupFn(torch.autograd.Function):
     """ids of ONE feature with bag offsets -> pooled rows ``[B, D]``; the per-id rows are never materialised: the pooled
     gather reads the unique rows through the inverse index, the backward adds each bag's gradient to its unique rows
@@ -87,7 +90,29 @@ class _DynamicPooledLookupFn(torch.autograd.Function):
         if ctx.training and ctx.n_unique:
             red = torch.zeros(ctx.n_unique, ctx.D, dtype=torch.float32, device=g.device)
             bags = offsets.numel() - 1
-            if g.is_cuda and ctx.D % 4 == 0 and g.stride(1) == 1:
+            n = inv.numel()
+            if g.is_cuda and ctx.D % 4 == 0 and g.stride(1) == 1 and n >= _SORTED_REDUCE_MIN_IDS and bags < (1 << 31):
+                # large batches: sort the (unique row, bag) pairs by row and sum runs, so a hot row costs one reduction per
+                # 64 ids instead of one per id and rows used by few bags are written without atomics
+                from ..ops.sparse_ops import _ws
+
+                dev = g.device
+                L = _lib.lib()
+                lengths = offsets[1:] - offsets[:-1]
+                bag_of = torch.repeat_interleave(torch.arange(bags, dtype=torch.int32, device=dev), lengths, output_size=n)
+                keys_sorted = _ws(dev, "pool_keys", n, torch.int64)
+                bags_sorted = _ws(dev, "pool_bags", n, torch.int32)
+                tb = int(L.rb_sort_segments_temp_bytes(n))
+                temp = _ws(dev, "pool_sort_tmp", tb, torch.uint8)
+                st = _lib.stream_ptr(dev)
+                rc = L.rb_sort_pairs_i64_i32(inv.data_ptr(), bag_of.data_ptr(), n, max(1, int(ctx.n_unique).bit_length()),
+                                             keys_sorted.data_ptr(), bags_sorted.data_ptr(), temp.data_ptr(), tb, st)
+                _lib.check(rc, "rb_sort_pairs_i64_i32")
+                rc = L.rb_pooled_segment_add(g.data_ptr(), _lib.dtype_code(g.dtype), g.stride(0), keys_sorted.data_ptr(),
+                                             bags_sorted.data_ptr(), offsets.data_ptr(), n, ctx.batch, ctx.D, int(ctx.mean),
+                                             red.data_ptr(), st)
+                _lib.check(rc, "rb_pooled_segment_add")
+            elif g.is_cuda and ctx.D % 4 == 0 and g.stride(1) == 1:
                 rc = _lib.lib().rb_pooled_scatter_add(g.data_ptr(), _lib.dtype_code(g.dtype), g.stride(0), inv.data_ptr(), offsets.data_ptr(),
                                                       bags, ctx.batch, ctx.D, int(ctx.mean), red.data_ptr(), _lib.stream_ptr(g.device))
                 _lib.check(rc, "rb_pooled_scatter_add")

@@ -77,3 +77,39 @@ def test_select_range_lengths_gpu():
     rub, rinv, rnl, rno, ruo = S.dedup_input_indices(ids, offs, fo, 64)
     assert torch.equal(nl.cpu(), rnl) and torch.equal(no.cpu(), rno) and torch.equal(uo.cpu(), ruo)
     assert torch.equal(ub[inv].cpu(), ids)
+
+
+@pytest.mark.parametrize("mean", [False, True])
+@pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
+def test_pooled_segment_add_matches_index_add(mean, gdtype):
+    """Sorted run-length reduction of bag gradients onto unique rows (skewed ids: a few rows span many groups of 64 pairs)."""
+    from recsdk_b200.ops import _lib
+
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(3)
+    batch, F, D, U = 512, 3, 64, 2000
+    bags = batch * F
+    lengths = torch.randint(0, 9, (bags,), generator=g)
+    n = int(lengths.sum())
+    inv = torch.where(torch.rand(n, generator=g) < 0.3, torch.randint(0, 3, (n,), generator=g), torch.randint(0, U, (n,), generator=g))
+    offsets = torch.cat([torch.zeros(1, dtype=torch.long), lengths.cumsum(0)]).to(dev)
+    grad = torch.randn(batch, F * D, generator=g).to(gdtype).to(dev)
+    inv_d = inv.to(dev)
+    bag_of = torch.repeat_interleave(torch.arange(bags, dtype=torch.int32, device=dev), lengths.to(dev))
+    L = _lib.lib()
+    keys_sorted, bags_sorted = torch.empty_like(inv_d), torch.empty_like(bag_of)
+    tb = int(L.rb_sort_segments_temp_bytes(n))
+    temp = torch.empty(tb, dtype=torch.uint8, device=dev)
+    st = _lib.stream_ptr(dev)
+    _lib.check(L.rb_sort_pairs_i64_i32(inv_d.data_ptr(), bag_of.data_ptr(), n, U.bit_length(), keys_sorted.data_ptr(),
+                                       bags_sorted.data_ptr(), temp.data_ptr(), tb, st), "sort")
+    assert bool((keys_sorted[1:] >= keys_sorted[:-1]).all())
+    red = torch.zeros(U, D, device=dev)
+    _lib.check(L.rb_pooled_segment_add(grad.data_ptr(), _lib.dtype_code(gdtype), grad.stride(0), keys_sorted.data_ptr(),
+                                       bags_sorted.data_ptr(), offsets.data_ptr(), n, batch, D, int(mean), red.data_ptr(), st), "add")
+    gg = grad.float().view(batch, F, D).permute(1, 0, 2).reshape(bags, D)
+    if mean:
+        gg = gg / lengths.to(dev).clamp(min=1).float()[:, None]
+    want = torch.zeros(U, D, device=dev).index_add_(0, inv_d, gg[bag_of.long()])
+    torch.testing.assert_close(red, want, rtol=1e-4, atol=1e-3)
+    _lib.check_status()
