@@ -79,6 +79,7 @@ def test_select_range_lengths_gpu():
     assert torch.equal(ub[inv].cpu(), ids)
 
 
+@pytest.mark.gpu
 @pytest.mark.parametrize("mean", [False, True])
 @pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
 def test_pooled_segment_add_matches_index_add(mean, gdtype):
