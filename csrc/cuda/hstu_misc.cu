@@ -90,9 +90,9 @@ ln_mul_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __
   for (int c = threadIdx.x; c < C; c += blockDim.x) { atomicAdd(dgamma + c, sg[c]); atomicAdd(dbeta + c, sb[c]); }
 }
 
-// bf16, C = NCH * 256 (256 or 512): every lane keeps its 8 * NCH columns of the row in registers (one 16-byte load per tensor and chunk), so
-// each input is read once; the per-column dgamma / dbeta partial sums stay in registers over all rows of the warp and are
-// combined through shared memory once per block.
+// bf16, C = NCH * 256 (256 or 512): every lane keeps its 8 * NCH columns of the row packed in registers (one 16-byte load per
+// tensor and chunk), so each input is read once; the per-column dgamma / dbeta partial sums live in a per-warp slice of shared
+// memory (a lane owns its columns, so no atomics) and are combined once per block.
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -107,79 +107,89 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 template <int NCH, bool DROP>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 4)
 ln_mul_bwd_vec_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ u,
                       const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ mean,
                       const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ du,
                       float* __restrict__ dgamma, float* __restrict__ dbeta, long long rows, float drop, unsigned long long seed) {
   constexpr int C = NCH * 256;
-  __shared__ __align__(16) float red[2][C];
+  __shared__ __align__(16) float acc[4][2][C];      // per warp: dgamma / dbeta partial sums (a lane owns its columns)
   __shared__ __align__(16) float gb[2][C];          // gamma, beta
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  const float inv_keep = drop > 0.f ? 1.f / (1.f - drop) : 1.f;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) { gb[0][c] = gamma[c]; gb[1][c] = beta[c]; red[0][c] = 0.f; red[1][c] = 0.f; }
+  const float inv_keep = DROP ? 1.f / (1.f - drop) : 1.f;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) { gb[0][c] = gamma[c]; gb[1][c] = beta[c]; }
+  for (int c = threadIdx.x; c < 4 * 2 * C; c += blockDim.x) (&acc[0][0][0])[c] = 0.f;
   __syncthreads();
-  const volatile float* gmv = gb[0];               // volatile: keeps these loop-invariant loads out of registers
-  const volatile float* btv = gb[1];
-  float dg[NCH][8], db[NCH][8];
-#pragma unroll
-  for (int k = 0; k < NCH; ++k)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { dg[k][i] = 0.f; db[k][i] = 0.f; }
   for (long long r = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps_total) {
-    float g[NCH][8], xh[NCH][8], uu[NCH][8];
+    uint4 pg[NCH], px[NCH], pu[NCH];                // the row stays packed (bf16) in registers between the two passes
     const float m = mean[r], rs = rstd[r];
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       const long long e0 = r * C + k * 256 + lane * 8;
-      unpack8(*reinterpret_cast<const uint4*>(dy + e0), g[k]);
-      unpack8(*reinterpret_cast<const uint4*>(x + e0), xh[k]);
-      if (u) unpack8(*reinterpret_cast<const uint4*>(u + e0), uu[k]);
+      pg[k] = *reinterpret_cast<const uint4*>(dy + e0);
+      px[k] = *reinterpret_cast<const uint4*>(x + e0);
+      pu[k] = u ? *reinterpret_cast<const uint4*>(u + e0) : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
     }
     float a = 0.f, b = 0.f;
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
+      float g[8], xh[8], uu[8];
+      unpack8(pg[k], g); unpack8(px[k], xh); unpack8(pu[k], uu);
+      const float4 g0 = *reinterpret_cast<const float4*>(&gb[0][k * 256 + lane * 8]);
+      const float4 g1 = *reinterpret_cast<const float4*>(&gb[0][k * 256 + lane * 8 + 4]);
+      const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         if (DROP) {
           const unsigned long long e = static_cast<unsigned long long>(r) * C + k * 256 + lane * 8 + i;
-          g[k][i] = hash_u01(seed, e) < drop ? 0.f : g[k][i] * inv_keep;
+          g[i] = hash_u01(seed, e) < drop ? 0.f : g[i] * inv_keep;
         }
-        if (!u) uu[k][i] = 1.f;
-        xh[k][i] = (xh[k][i] - m) * rs;
-        const float dn = g[k][i] * uu[k][i];
-        const float dng = dn * gmv[k * 256 + lane * 8 + i];
+        const float dng = g[i] * uu[i] * gm[i];
         a += dng;
-        b += dng * xh[k][i];
-        dg[k][i] += dn * xh[k][i];
-        db[k][i] += dn;
+        b += dng * (xh[i] - m) * rs;
       }
     }
     a = rb::warp_sum(a) * (1.f / C); b = rb::warp_sum(b) * (1.f / C);
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
-      const long long e0 = r * C + k * 256 + lane * 8;
-      float o[8], q[8];
+      const int c0 = k * 256 + lane * 8;
+      const long long e0 = r * C + c0;
+      float g[8], xh[8], uu[8], o[8], q[8], sg[8], sb[8];
+      unpack8(pg[k], g); unpack8(px[k], xh); unpack8(pu[k], uu);
+      const float4 g0 = *reinterpret_cast<const float4*>(&gb[0][c0]), g1 = *reinterpret_cast<const float4*>(&gb[0][c0 + 4]);
+      const float4 b0 = *reinterpret_cast<const float4*>(&gb[1][c0]), b1 = *reinterpret_cast<const float4*>(&gb[1][c0 + 4]);
+      const float gm[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+      const float bt[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+      float4* ag = reinterpret_cast<float4*>(&acc[warp][0][c0]);
+      float4* ab = reinterpret_cast<float4*>(&acc[warp][1][c0]);
+      const float4 s0 = ag[0], s1 = ag[1], t0 = ab[0], t1 = ab[1];
+      sg[0] = s0.x; sg[1] = s0.y; sg[2] = s0.z; sg[3] = s0.w; sg[4] = s1.x; sg[5] = s1.y; sg[6] = s1.z; sg[7] = s1.w;
+      sb[0] = t0.x; sb[1] = t0.y; sb[2] = t0.z; sb[3] = t0.w; sb[4] = t1.x; sb[5] = t1.y; sb[6] = t1.z; sb[7] = t1.w;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float gmc = gmv[k * 256 + lane * 8 + i];
-        o[i] = rs * (g[k][i] * uu[k][i] * gmc - a - xh[k][i] * b);
-        q[i] = g[k][i] * (xh[k][i] * gmc + btv[k * 256 + lane * 8 + i]);
+        if (DROP) {
+          const unsigned long long e = static_cast<unsigned long long>(r) * C + c0 + i;
+          g[i] = hash_u01(seed, e) < drop ? 0.f : g[i] * inv_keep;
+        }
+        const float xn = (xh[i] - m) * rs;
+        const float dn = g[i] * uu[i];
+        o[i] = rs * (dn * gm[i] - a - xn * b);
+        q[i] = g[i] * (xn * gm[i] + bt[i]);
+        sg[i] += dn * xn;
+        sb[i] += dn;
       }
       *reinterpret_cast<uint4*>(dx + e0) = pack8(o);
       if (du) *reinterpret_cast<uint4*>(du + e0) = pack8(q);
+      ag[0] = make_float4(sg[0], sg[1], sg[2], sg[3]); ag[1] = make_float4(sg[4], sg[5], sg[6], sg[7]);
+      ab[0] = make_float4(sb[0], sb[1], sb[2], sb[3]); ab[1] = make_float4(sb[4], sb[5], sb[6], sb[7]);
     }
   }
-#pragma unroll
-  for (int k = 0; k < NCH; ++k)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      atomicAdd(&red[0][k * 256 + lane * 8 + i], dg[k][i]);
-      atomicAdd(&red[1][k * 256 + lane * 8 + i], db[k][i]);
-    }
   __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) { atomicAdd(dgamma + c, red[0][c]); atomicAdd(dbeta + c, red[1][c]); }
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    atomicAdd(dgamma + c, acc[0][0][c] + acc[1][0][c] + acc[2][0][c] + acc[3][0][c]);
+    atomicAdd(dbeta + c, acc[0][1][c] + acc[1][1][c] + acc[2][1][c] + acc[3][1][c]);
+  }
 }
 
 // ------------------------------------------------------------------ relative attention bias
@@ -368,7 +378,7 @@ RB_API int rb_ln_mul_bwd(const void* dy, const void* x, const void* u, const flo
   if (dtype == 2 && (C == 256 || C == 512) && al16(dy) && al16(x) && al16(u) && al16(dx) && al16(du)) {
     const __nv_bfloat16 *pdy = (const __nv_bfloat16*)dy, *px = (const __nv_bfloat16*)x, *pu = (const __nv_bfloat16*)u;
     __nv_bfloat16 *pdx = (__nv_bfloat16*)dx, *pdu = (__nv_bfloat16*)du;
-    const int vb = static_cast<int>(std::min<long long>((num_sms > 0 ? num_sms : 148) * 3LL, (rows + 3) / 4));
+    const int vb = static_cast<int>(std::min<long long>((num_sms > 0 ? num_sms : 148) * 4LL, (rows + 3) / 4));
     const unsigned long long sd = (unsigned long long)seed;
 #define RB_LN_BWD(NCH_, DROP_) ln_mul_bwd_vec_kernel<NCH_, DROP_><<<vb, 128, 0, st>>>(pdy, px, pu, gamma, beta, mean, rstd, pdx, pdu, dgamma, dbeta, rows, drop, sd)
     if (C == 256) { if (drop > 0.f) RB_LN_BWD(1, true); else RB_LN_BWD(1, false); }

@@ -4,6 +4,8 @@
     python -m recsdk_b200.utils.microbench hstu_fwd --seqs 8 --len 2048 --heads 8 [--bias]
     python -m recsdk_b200.utils.microbench hstu_bwd --seqs 8 --len 2048 --heads 8 [--bias]
     python -m recsdk_b200.utils.microbench tbe_fwd --rows 20000000 --batch 65536 --tables 26
+    python -m recsdk_b200.utils.microbench ln_mul_bwd --m 65536 --n 512
+    python -m recsdk_b200.utils.microbench pooled_bwd --batch 32768 --tables 40 --n 64
 
 Prints one JSON line with the measured time and the achieved rate against the measured peaks
 (``MEASURED_PEAKS.json`` at the repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).
@@ -47,7 +49,7 @@ def _time(fn, iters: int, warmup: int = 3) -> float:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "hstu_fwd", "hstu_bwd", "tbe_fwd", "interaction"])
+    ap.add_argument("what", choices=["gemm", "hstu_fwd", "hstu_bwd", "tbe_fwd", "interaction", "ln_mul_bwd", "pooled_bwd"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -123,6 +125,55 @@ def main() -> None:
         ms = _time(fn, a.iters)
         by = T * B * D * 2 * 2 + T * B * 8
         out.update(ms=ms, gbs=by / ms / 1e6, frac_of_peak=by / (ms / 1e3) / hbm)
+    elif a.what == "ln_mul_bwd":
+        from ..ops import hstu_ops as H
+
+        rows, C = a.m, a.n
+        x = torch.randn(rows, C, device=dev).bfloat16().requires_grad_(True)
+        u = torch.randn(rows, C, device=dev).bfloat16().requires_grad_(True)
+        ga, be = torch.randn(C, device=dev).requires_grad_(True), torch.randn(C, device=dev).requires_grad_(True)
+        y = H.ln_mul(x, u, ga, be)
+        dy = torch.randn_like(y)
+        fn = lambda: torch.autograd.grad(y, [x, u, ga, be], dy, retain_graph=True)  # noqa: E731
+        ms = _time(fn, a.iters)
+        by = rows * C * 2 * 5                                   # dy, x, u read; dx, du written
+        out.update(ms=ms, gbs=by / ms / 1e6, frac_of_peak=by / (ms / 1e3) / hbm, shape=[rows, C],
+                   note="includes the zero-fill of the two [C] parameter-gradient buffers")
+    elif a.what == "pooled_bwd":
+        # backward of the dynamic pooled lookup: (unique row, bag) pairs -> sorted runs -> per-row gradient sums
+        B, F, D = a.batch, a.tables, a.n
+        bags = B * F
+        g = torch.Generator(device="cpu").manual_seed(0)
+        lengths = torch.randint(1, 21, (bags,), generator=g)
+        n = int(lengths.sum())
+        zipf = torch.distributions.Pareto(torch.tensor(1.0), torch.tensor(0.2)).sample((n,)).long()      # heavy-tailed ids
+        uniq, inv = torch.unique(zipf, return_inverse=True)
+        U = uniq.numel()
+        inv, lengths = inv.to(dev), lengths.to(dev)
+        offsets = torch.cat([torch.zeros(1, dtype=torch.long, device=dev), lengths.cumsum(0)])
+        grad = torch.randn(B, F * D, device=dev).bfloat16()
+        bag_of = torch.repeat_interleave(torch.arange(bags, dtype=torch.int32, device=dev), lengths)
+        L = _lib.lib()
+        ks, bs = torch.empty_like(inv), torch.empty_like(bag_of)
+        tb = int(L.rb_sort_segments_temp_bytes(n))
+        temp = torch.empty(tb, dtype=torch.uint8, device=dev)
+        red = torch.zeros(U, D, device=dev)
+        st = _lib.stream_ptr(dev)
+
+        def fn():
+            red.zero_()
+            if a.splits > 1:                                    # --splits 2: the one-atomic-per-id kernel, for comparison
+                _lib.check(L.rb_pooled_scatter_add(grad.data_ptr(), 2, grad.stride(0), inv.data_ptr(), offsets.data_ptr(), bags, B, D, 0,
+                                                   red.data_ptr(), st), "scatter")
+                return
+            _lib.check(L.rb_sort_pairs_i64_i32(inv.data_ptr(), bag_of.data_ptr(), n, max(1, U.bit_length()), ks.data_ptr(), bs.data_ptr(),
+                                               temp.data_ptr(), tb, st), "sort")
+            _lib.check(L.rb_pooled_segment_add(grad.data_ptr(), 2, grad.stride(0), ks.data_ptr(), bs.data_ptr(), offsets.data_ptr(), n, B, D,
+                                               0, red.data_ptr(), st), "add")
+        ms = _time(fn, a.iters)
+        by = n * D * 2 + U * D * 4 * 2 + n * 12 * 2             # gradient rows gathered, red zeroed + written, pairs read + written once
+        out.update(ms=ms, ids=n, unique=U, gbs=by / ms / 1e6, frac_of_peak=by / (ms / 1e3) / hbm,
+                   kernel="scatter_add (atomics)" if a.splits > 1 else "sort + segment_add")
     else:
         from ..ops import interaction as I
 
