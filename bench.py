@@ -45,6 +45,9 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--table-seed", type=int, default=0)
     ap.add_argument("--ckpt-every", type=int, default=500, help="dcn: incremental dump period in steps (0 = off)")
+    ap.add_argument("--repeats", type=int, default=5, help="dlrm: how many times the K-step timed loop is repeated (median reported)")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="dlrm: skip the HSTU training / ranking-inference measurements that are appended to the JSON line")
     ap.add_argument("--rows-scale", type=float, default=1.0,
                     help="shrink every table (profiling captures on a small case); 1.0 = the named config")
     return ap.parse_args()
@@ -62,13 +65,23 @@ class ClockSampler:
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int) -> None:
-        self.idx, self.proc, self.lines = gpu_index, None, []
+    def __init__(self, gpu_index: int, period_ms: int = 50) -> None:
+        self.idx, self.proc, self.lines, self.period_ms = gpu_index, None, [], period_ms
+        self._t0 = self._t1 = None
+        self._stamps = []
+
+    def begin_window(self) -> None:
+        """Only samples taken between ``begin_window`` and ``end_window`` count (the sampler itself may start earlier,
+        so that nvidia-smi's start-up does not eat a short timed region)."""
+        self._t0 = time.time()
+
+    def end_window(self) -> None:
+        self._t1 = time.time()
 
     def start(self) -> None:
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                          "--format=csv,noheader,nounits", "-lms", str(self.period_ms)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -78,6 +91,7 @@ class ClockSampler:
     def _pump(self) -> None:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
+            self._stamps.append(time.time())
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -90,7 +104,11 @@ class ClockSampler:
             pass
         sm, smax, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        lines = self.lines
+        if self._t0 is not None:
+            t1 = self._t1 if self._t1 is not None else time.time()
+            lines = [ln for ln, ts in zip(self.lines, self._stamps) if self._t0 <= ts <= t1 + 0.05]
+        for ln in lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -110,6 +128,46 @@ def table_rows(seed: int, n: int = 26, lo: float = 1e4, hi: float = 4e7):
 
     rng = random.Random(seed)
     return [int(round(math.exp(rng.uniform(math.log(lo), math.log(hi))))) for _ in range(n)]
+
+
+def run_extras(args, world: int, rank: int, dev) -> dict:
+    """HSTU training (every N) and HSTU ranking inference (N = 1) measured after the DLRM run, on the same process group.
+    A failure here is reported inside the JSON line instead of losing the DLRM result."""
+    import copy
+    import traceback
+
+    out = {}
+    try:
+        from recsdk_b200.models.hstu_bench import measure_hstu_training
+
+        a = copy.copy(args)
+        a.steps, a.warmup = min(args.steps, 20), max(min(args.warmup, 5), 3)
+        r = measure_hstu_training(a, world, rank, dev)
+        out["hstu"] = {"tokens_per_s": r["value"], "ms_per_step": r["ms_per_step"], "steps": r["steps"], "warmup": r["warmup"],
+                       "e2e": r["e2e"], "config": r["config"], "gpu_launches": r["gpu_launches"], "final_loss": r["final_loss"],
+                       "clocks": r["clocks"], "scaling": "weak"}
+    except Exception as e:  # noqa: BLE001
+        traceback.print_exc()
+        out["hstu"] = {"error": "%s: %s" % (type(e).__name__, e)}
+    if world == 1:
+        try:
+            import gc
+
+            import torch
+
+            gc.collect()
+            torch.cuda.empty_cache()
+            from recsdk_b200.models.hstu_bench import measure_hstu_inference
+
+            a = copy.copy(args)
+            a.steps, a.warmup = min(args.steps, 20), 3
+            r = measure_hstu_inference(a, world, rank, dev)
+            out["hstu_ranking_inference"] = {"p50_ms": r["p50_ms"], "p99_ms": r["p99_ms"], "candidates_per_s": r["value"],
+                                             "steps": r["steps"], "config": r["config"], "e2e": r["e2e"]}
+        except Exception as e:  # noqa: BLE001
+            traceback.print_exc()
+            out["hstu_ranking_inference"] = {"error": "%s: %s" % (type(e).__name__, e)}
+    return out
 
 
 def main() -> None:
@@ -216,34 +274,36 @@ def main() -> None:
             torch.cuda.synchronize(dev)
 
     # ---------------- warm-up through the public API (also captures the graph) ----------------
-    n_warm = max(args.warmup, 3) + (4 if not args.no_graph else 0)
+    sampler = ClockSampler(local_rank, period_ms=20)
+    sampler.start()                                   # started early: nvidia-smi needs ~0.1 s before its first sample
+    W = max(args.warmup, 3)
+    capture_steps = 4 if not args.no_graph else 0     # graph mode: eager steps before the capture plus the capture itself
     last = None
-    for _ in range(n_warm):
+    for _ in range(W + capture_steps):
         loss, _ = pipe.progress(it)
         last = float(loss.item())
     sync_all()
     _lib.check_status(dev)
+    R = max(args.repeats, 1)
 
     # ---------------- e2e: public API, H2D every step, loss read back every step ----------------
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     sync_all()
-    lc0 = _lib.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        loss, _ = pipe.progress(it)
-        last = float(loss.item())
-    e1.record()
-    sync_all()
-    e2e_ms = e0.elapsed_time(e1) / args.steps
+    sampler.begin_window()
+    e2e_runs = []
+    for _ in range(R):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            loss, _ = pipe.progress(it)
+            last = float(loss.item())
+        e1.record()
+        sync_all()
+        e2e_runs.append(e0.elapsed_time(e1) / args.steps)
 
     # ---------------- device-timed: the train step alone from device-resident inputs ----------------
     dev_batches = [b.to(dev) for b in host_batches]
     torch.cuda.synchronize(dev)
     if pipe._graph is not None:
-        launches_per_step = getattr(pipe, "launches_per_step", None)
-
         def one_step(i):
             pipe._copy_into_static(dev_batches[i % len(dev_batches)])
             pipe._graph.replay()
@@ -253,27 +313,32 @@ def main() -> None:
     for i in range(3):
         one_step(i)
     sync_all()
-    lc1 = _lib.launch_count
     from recsdk_b200.utils import trace as _trace
 
     _trace.reset()
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record()
-    for i in range(args.steps):
-        one_step(i)
-    s1.record()
-    sync_all()
+    lc1 = _lib.launch_count
+    step_runs = []
+    for r in range(R):
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for i in range(args.steps):
+            one_step(i)
+        s1.record()
+        sync_all()
+        step_runs.append(s0.elapsed_time(s1) / args.steps)
     lc2 = _lib.launch_count
-    step_ms = s0.elapsed_time(s1) / args.steps
+    sampler.end_window()
     clocks = sampler.stop()
     _lib.check_status(dev)
 
-    t = torch.tensor([step_ms, e2e_ms], dtype=torch.float64, device=dev)
+    # per repeat: max over ranks; then the median repeat is the reported value
+    tr = torch.tensor([step_runs, e2e_runs], dtype=torch.float64, device=dev)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    step_ms, e2e_ms = float(t[0]), float(t[1])
+        dist.all_reduce(tr, op=dist.ReduceOp.MAX)
+    step_runs, e2e_runs = tr[0].tolist(), tr[1].tolist()
+    step_ms, e2e_ms = statistics.median(step_runs), statistics.median(e2e_runs)
     launches = pipe.launches_per_step * args.steps if pipe._graph is not None and hasattr(pipe, "launches_per_step") \
-        else (lc2 - lc1)
+        else (lc2 - lc1) // R
     kjt_bytes = host_batches[0].nbytes()
     from recsdk_b200.utils import trace
 
@@ -281,10 +346,26 @@ def main() -> None:
     if rank == 0 and phases:
         print("phase timing (device time from each mark to the next, mean us): " +
               json.dumps({k: round(v["mean_us"], 1) for k, v in phases.items()}), file=sys.stderr)
+    if world > 1:
+        tl = torch.tensor([last], dtype=torch.float64, device=dev)
+        dist.all_reduce(tl)                      # each rank's loss is its share of the global-batch mean
+        last = float(tl[0])
+    extras = {}
+    if not args.no_extra and not args.small and args.rows_scale == 1.0:
+        # the other half of the headline metric (HSTU training tokens/s at the same N) and, on one GPU, the ranking
+        # request latency: measured in the same invocation so that they reach the same record
+        del pipe, dmp, opt, model, dev_batches
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        extras = run_extras(args, world, rank, dev)
     if rank == 0:
         out = {
             "metric": "DLRM train samples/sec/box", "value": GB / (step_ms / 1e3), "unit": "samples/s",
-            "n_gpus": world, "steps": args.steps, "warmup": n_warm, "ms_per_step": step_ms,
+            "n_gpus": world, "steps": args.steps, "warmup": W, "graph_capture_steps": capture_steps, "ms_per_step": step_ms,
+            "repeats": {"n": R, "ms_per_step": [round(x, 4) for x in step_runs], "min": min(step_runs), "max": max(step_runs),
+                        "e2e_ms_per_step": [round(x, 4) for x in e2e_runs], "reported": "median"},
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (fp16 tables)",
             "data": "synthetic Zipf(1.1) ids, N(0,1) dense, Bernoulli(0.03) labels, random-init weights",
             "config": {"model": "DLRM-large" if not (args.small or args.rows_scale != 1.0) else "DLRM-debug-shrunk", "global_batch": GB,
@@ -296,6 +377,7 @@ def main() -> None:
                     "h2d_bytes_per_step": kjt_bytes * world, "d2h_bytes_per_step": 4 * world},
             "gpu_launches": int(launches), "final_loss": last, "clocks": clocks, "impl": "ours",
         }
+        out.update(extras)
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -70,14 +70,20 @@ def run_dcn_bench(args) -> None:
     dumps = {"count": 0, "keys": 0}
     score_floor = 0
 
+    reducer = None
+    if world > 1:
+        from ..parallel.comm import PeerGroup
+        from ..parallel.grad_reduce import DenseGradReducer
+
+        reducer = DenseGradReducer(PeerGroup(dist.group.WORLD, dev), model, overlap=True, average=False)
+
     def step(i):
         b = host[i % len(host)].to(dev, non_blocking=True)
         opt.zero_grad()
         loss, _ = model(b)
         loss.backward()
-        if world > 1:
-            for p in dense:
-                dist.all_reduce(p.grad)
+        if reducer is not None:
+            reducer.sync()
         opt.step()
         if ckpt_every and (i + 1) % ckpt_every == 0:
             out, _scores = incremental_dump(model, score_floor, env.process_group)

@@ -76,9 +76,6 @@ def build(device, env, cfg=None, capacity: int = 1 << 22, lr: float = 1e-3):
 
 
 def run_hstu_bench(args) -> None:
-    from ..ops import _lib
-    from ..parallel.comm import PeerGroup, ShardingEnv
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
@@ -88,6 +85,19 @@ def run_hstu_bench(args) -> None:
 
         bind_rank_from_env()                                # opt-in (RECSDK_B200_BIND_CPU=1): keep every rank on its own cores
         dist.init_process_group("nccl", device_id=dev)
+    out = measure_hstu_training(args, world, rank, dev)
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def measure_hstu_training(args, world: int, rank: int, dev, peer=None) -> dict:
+    """Times ``args.steps`` HSTU training steps after ``max(args.warmup, 3)`` warm-up steps on an initialised process
+    group; every rank returns the same result dictionary (times are the max over ranks, tokens the sum)."""
+    from ..ops import _lib
+    from ..parallel.comm import PeerGroup, ShardingEnv
+
     env = ShardingEnv(world, rank, dist.group.WORLD if world > 1 else None)
     B = 32 if not args.small else 4
     model, opt = build(dev, env, capacity=(1 << 22) if not args.small else (1 << 16))
@@ -109,17 +119,18 @@ def run_hstu_bench(args) -> None:
     dense_params = [p for p in model.parameters() if p.requires_grad and not getattr(p, "_in_backward_optimizers", False)]
     flat_ids = {id(m.flat_param) for m in opt.flat_modules}
 
+    reducer = None
+    if world > 1:
+        from ..parallel.grad_reduce import DenseGradReducer
+
+        peer = peer or PeerGroup(dist.group.WORLD, dev)
+        # dense gradients: one push all-reduce bucket per projection (launched from the end of that layer's backward, on a
+        # side stream) and one bucket for all small parameters
+        reducer = DenseGradReducer(peer, model, overlap=True, average=False)
+
     def sync_grads():
-        """Dense gradients: one all-reduce per flat MLP buffer, one for all small parameters together."""
-        if world == 1:
-            return
-        for m in opt.flat_modules:
-            dist.all_reduce(m.flat_grad)
-        small = [p for p in dense_params if id(p) not in flat_ids and p.grad is not None]
-        if small:
-            flat = torch.cat([p.grad.reshape(-1) for p in small])
-            dist.all_reduce(flat)
-            torch._foreach_copy_([p.grad for p in small], [c.view_as(p.grad) for c, p in zip(flat.split([p.numel() for p in small]), small)])
+        if reducer is not None:
+            reducer.sync()
 
     def step(i):
         k, o, m, ts, T, kp = host[i % len(host)]
@@ -168,23 +179,34 @@ def run_hstu_bench(args) -> None:
         dist.all_reduce(ts_, op=dist.ReduceOp.SUM)
         ms, tokens = float(tm[0]), float(ts_[1])
     h2d = sum(k.values().numel() * 8 + o.numel() * 8 + ts.numel() * 4 + kp.numel() * 8 for (k, o, m, ts, T, kp) in host) / len(host)
-    if rank == 0:
-        val = tokens / (ms / 1e3)
-        print(json.dumps({
-            "metric": "HSTU train tokens/sec", "value": val, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (log-normal lengths, Zipf(1.05) ids, Exp gaps), random-init weights",
-            "config": {"model": "HSTU 8L d512 8x64", "global_batch": B * world, "seq_len": "lognormal[16,4096] mean~1024",
-                       "parallelism": "dp%d dense + row-wise dynamic hash embedding" % world, "negatives": 512,
-                       "l2": "inputs larger than L2 (activations ~%d MB per layer)" % (tokens / args.steps / world * 2048 * 2 / 1e6)},
-            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": 4 * world,
-                    "note": "timed loop copies every batch from pinned host memory and reads the loss back each step"},
-            "gpu_launches": int(_lib.launch_count - lc0), "final_loss": last, "clocks": clocks, "impl": "ours"}))
-    if world > 1:
-        dist.destroy_process_group()
+    val = tokens / (ms / 1e3)
+    return {
+        "metric": "HSTU train tokens/sec", "value": val, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (log-normal lengths, Zipf(1.05) ids, Exp gaps), random-init weights",
+        "config": {"model": "HSTU 8L d512 8x64", "global_batch": B * world, "seq_len": "lognormal[16,4096] mean~1024",
+                   "parallelism": "dp%d dense + row-wise dynamic hash embedding" % world, "negatives": 512,
+                   "l2": "inputs larger than L2 (activations ~%d MB per layer)" % (tokens / args.steps / world * 2048 * 2 / 1e6)},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": 4 * world,
+                "note": "timed loop copies every batch from pinned host memory and reads the loss back each step"},
+        "gpu_launches": int(_lib.launch_count - lc0), "final_loss": last, "clocks": clocks, "impl": "ours"}
 
 
 def run_hstu_inference_bench(args) -> None:
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if world > 1:                                           # serving replicas: every GPU holds the model and its own users
+        dist.init_process_group("nccl", device_id=dev)
+    out = measure_hstu_inference(args, world, rank, dev)
+    if world > 1:
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(out))
+
+
+def measure_hstu_inference(args, world: int, rank: int, dev) -> dict:
     """HSTU ranking latency with a warm paged KV cache: ``users`` requests per batch, each with ``cached`` history
     tokens already in the cache, ``new`` fresh history tokens and ``cands`` candidates to score.  Every timed
     request copies its item ids and timestamps from pinned host memory, looks the embeddings up on the device,
@@ -197,12 +219,6 @@ def run_hstu_inference_bench(args) -> None:
     from .hstu import HSTU, HSTUConfig
     from .hstu_inference import HSTURanker
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
-    if world > 1:                                           # serving replicas: every GPU holds the model and its own users
-        dist.init_process_group("nccl", device_id=dev)
     small = args.small
     users, cached, new, cands, page = (64, 2048, 128, 1024, 64) if not small else (4, 256, 64, 32, 64)
     cfg = HSTUConfig(num_layers=8 if not small else 2, d_model=512, num_heads=8, head_dim=64, max_seq_len=4096)
@@ -298,11 +314,7 @@ def run_hstu_inference_bench(args) -> None:
         ms, p50, p99 = float(t[0]), float(t[1]), float(t[2])
     val = users * cands * args.steps * world / (ms / 1e3)
     ids0, ts0 = reqs[0]
-    if world > 1:
-        dist.destroy_process_group()
-    if rank != 0:
-        return
-    print(json.dumps({
+    return ({
         "metric": "HSTU ranking inference candidates/sec", "value": val, "unit": "candidates/s", "n_gpus": world, "steps": args.steps,
         "warmup": W, "ms_per_step": ms / args.steps, "p50_ms": p50, "p99_ms": p99,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -313,4 +325,4 @@ def run_hstu_inference_bench(args) -> None:
         "e2e": {"value": val, "unit": "candidates/s", "h2d_bytes_per_step": int(ids0.numel() * 8 + ts0.numel() * 4) * world,
                 "d2h_bytes_per_step": int(scores_host.numel() * 4) * world,
                 "note": "each request copies ids and timestamps from pinned memory and reads all scores back"},
-        "gpu_launches": int(_lib.launch_count - lc0), "clocks": clocks, "impl": "ours"}))
+        "gpu_launches": int(_lib.launch_count - lc0), "clocks": clocks, "impl": "ours"})

@@ -53,6 +53,8 @@ class _FusedMLPFn(torch.autograd.Function):
             y = gemm.gemm16(acts[-1], mlp.w16[l], bias=mlp.b32[l], epi=gemm.EPI_RELU if relu else gemm.EPI_NONE)
             acts.append(y)
         ctx.mlp = mlp
+        if any(ctx.needs_input_grad):          # a backward will follow this forward
+            mlp._pending_backward += 1
         ctx.grad_premasked = grad_premasked
         ctx.x_needs_grad = x.requires_grad
         ctx.save_for_backward(*acts)
@@ -88,6 +90,10 @@ class _FusedMLPFn(torch.autograd.Function):
                     dz = gemm.gemm16(dz, mlp.w16[l], b_mn=True, colsum_out=cs)
             elif ctx.x_needs_grad:
                 dx = gemm.gemm16(dz, mlp.w16[l], b_mn=True)
+        mlp._pending_backward -= 1
+        if mlp._grad_ready_hook is not None and mlp._pending_backward <= 0:
+            mlp._pending_backward = 0
+            mlp._grad_ready_hook(mlp)          # every weight gradient of this module is enqueued: its all-reduce may start
         return dx, None, None, None
 
 
@@ -126,7 +132,14 @@ class FusedMLP(nn.Module):
         self.flat_param = nn.Parameter(torch.zeros(off, dtype=torch.float32, device=device))
         self.register_buffer("flat_shadow", torch.zeros(off, dtype=dtype, device=device), persistent=False)
         self.register_buffer("flat_grad", torch.zeros(off, dtype=torch.float32, device=device), persistent=False)
+        self._pending_backward = 0
+        self._grad_ready_hook = None
         self.reset_parameters()
+
+    def set_grad_ready_hook(self, hook) -> None:
+        """``hook(module)`` runs at the end of this module's backward, once the last weight-gradient GEMM of the step is
+        enqueued (a module applied several times per step fires after its last backward)."""
+        self._grad_ready_hook = hook
 
     # -- views ----------------------------------------------------------------
     def _build_views(self) -> None:

@@ -107,6 +107,11 @@ class PeerGroup:
                 mc = 0
         return PeerBuffer(t, list(hdl.buffer_ptrs), mc, hdl)
 
+    def host_barrier(self) -> None:
+        """Host-side rendezvous of all ranks (set-up paths only)."""
+        if self.world > 1:
+            dist.barrier(group=self.pg)
+
     # -- collectives on the current stream ---------------------------------------
     def barrier(self, slot: int = 0) -> None:
         """Device-side barrier of all ranks, ordered with the current stream; never blocks the host."""

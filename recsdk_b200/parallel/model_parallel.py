@@ -14,6 +14,7 @@ Mirrors the role of TorchRec's DMP in the reference's user flow
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -66,7 +67,7 @@ class DistributedModelParallel(nn.Module):
                  plan: Optional[ShardingPlan] = None, sharders=None, peer: Optional[PeerGroup] = None,
                  sparse_optimizer: Optional[E.OptimizerSpec] = None, out_dtype: torch.dtype = torch.bfloat16,
                  max_local_batch: int = 0, one_hot: bool = False, init_seed: Optional[int] = None,
-                 backend: Optional[str] = None) -> None:
+                 backend: Optional[str] = None, overlap_grad_reduce: bool = True) -> None:
         """``backend``: ``"fused"`` (peer-memory kernels; CUDA only, the default there) or ``"collective"``
         (``torch.distributed`` all-to-all flow; any device, the default on CPU; required for hash tables)."""
         super().__init__()
@@ -88,10 +89,9 @@ class DistributedModelParallel(nn.Module):
             if isinstance(m, (ShardedEmbeddingBagCollection, CollectiveShardedEmbeddingBagCollection)) \
                     and m not in self.sharded_modules:
                 self.sharded_modules.append(m)
-        self._grad_buf = None
-        self._grad_elems = 0
-        self._rehome_dense_grads()
         self._sharded_param_ids = {id(p) for sm in self.sharded_modules for p in sm.parameters()}
+        self.overlap_grad_reduce = overlap_grad_reduce
+        self._build_grad_reducer()
         self._broadcast_dense()
 
     # ------------------------------------------------------------------ sharding
@@ -149,22 +149,17 @@ class DistributedModelParallel(nn.Module):
         return None
 
     # ------------------------------------------------------------- dense grads
-    def _flat_modules(self) -> List[nn.Module]:
-        return [m for m in self.module.modules() if hasattr(m, "flat_grad") and hasattr(m, "set_grad_buffer")]
-
-    def _rehome_dense_grads(self) -> None:
-        mods = self._flat_modules()
-        if self.world == 1 or not mods or self.device.type != "cuda":
+    def _build_grad_reducer(self) -> None:
+        """Dense gradients are summed over the data-parallel ranks by the bucketed push all-reduce; each flat module's
+        bucket starts on a side stream at the end of that module's backward (``overlap_grad_reduce``)."""
+        self._reducer = None
+        if self.world == 1 or self.device.type != "cuda" or self.peer is None:
             return
-        sizes = [(m.flat_grad.numel() + 63) // 64 * 64 for m in mods]
-        total = sum(sizes)
-        self._grad_buf = self.peer.alloc(total * 4, zero=True)
-        flat = self._grad_buf.local.view(torch.float32)
-        off = 0
-        for m, s in zip(mods, sizes):
-            m.set_grad_buffer(flat[off:off + m.flat_grad.numel()])
-            off += s
-        self._grad_elems = total
+        from .grad_reduce import DenseGradReducer
+
+        wire = torch.float32 if os.environ.get("RECSDK_B200_ALLREDUCE_WIRE", "bf16") == "fp32" else torch.bfloat16
+        self._reducer = DenseGradReducer(self.peer, self.module, exclude_param_ids=self._sharded_param_ids,
+                                         wire_dtype=wire, overlap=self.overlap_grad_reduce, average=False)
 
     @torch.no_grad()
     def _broadcast_dense(self) -> None:
@@ -182,9 +177,10 @@ class DistributedModelParallel(nn.Module):
         """Average dense gradients over the data-parallel ranks (call between backward and step)."""
         if self.world == 1:
             return
+        if self._reducer is not None:
+            self._reducer.sync()
+            return
         trace.mark("dense.grad_allreduce")
-        if self._grad_buf is not None:
-            self.peer.allreduce_mean_f32(self._grad_buf, self._grad_elems, scale=1.0)
         for p in self.module.parameters():
             if p.grad is not None and id(p) not in self._sharded_param_ids:
                 dist.all_reduce(p.grad, group=self.env.process_group)

@@ -59,6 +59,71 @@ def slice_batch(b: Batch, rank: int, world: int) -> Batch:
                  b.labels[rank * Bl:(rank + 1) * Bl].contiguous())
 
 
+def allreduce_case(world, rank, dev) -> bool:
+    """Push all-reduce (two-shot and one-shot, bf16 and fp32 on the wire) against ``dist.all_reduce``, several calls in a
+    row on the same buffers (flag epochs, staging parity), then a bandwidth figure for the two-shot form."""
+    from recsdk_b200.parallel.grad_reduce import DenseGradReducer
+
+    class Flat(torch.nn.Module):
+        def __init__(self, n):
+            super().__init__()
+            self.flat_param = torch.nn.Parameter(torch.zeros(n, device=dev))
+            self.register_buffer("flat_grad", torch.zeros(n, device=dev), persistent=False)
+
+    peer = PeerGroup(dist.group.WORLD, dev)
+    ok = True
+    for wire in (torch.bfloat16, torch.float32):
+        holder = torch.nn.Module()
+        holder.a = Flat(3_000_008)          # two-shot
+        holder.b = Flat(40_000)             # one-shot
+        holder.c = torch.nn.Parameter(torch.zeros(777, device=dev))   # small-parameter bucket
+        red = DenseGradReducer(peer, holder, wire_dtype=wire, overlap=False, average=True)
+        for it in range(4):
+            g = torch.Generator(device=dev).manual_seed(100 * it + rank)
+            want = []
+            for t in (holder.a.flat_grad, holder.b.flat_grad):
+                t.copy_(torch.randn(t.shape, generator=g, device=dev))
+                w = t.clone()
+                dist.all_reduce(w)
+                want.append(w / world)
+            holder.c.grad = torch.randn(777, generator=g, device=dev)
+            w = holder.c.grad.clone()
+            dist.all_reduce(w)
+            want.append(w / world)
+            red.sync()
+            torch.cuda.synchronize()
+            got = [holder.a.flat_grad, holder.b.flat_grad, holder.c.grad]
+            tol = 2e-2 if wire == torch.bfloat16 else 1e-5
+            for gt, wt in zip(got, want):
+                err = (gt - wt).abs().max().item()
+                if not err <= tol:
+                    ok = False
+                    print("rank %d allreduce wire=%s iter %d n=%d err %.3e" % (rank, wire, it, gt.numel(), err))
+        if wire == torch.bfloat16:
+            for blocks in (0, 48, 192, 384):
+                red.blocks = blocks
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                dist.barrier()
+                torch.cuda.synchronize()
+                for timed in (False, True):
+                    e0.record()
+                    for _ in range(20):
+                        red._launch(red.buckets[0])
+                        torch.cuda.current_stream().wait_event(red.buckets[0].done_event)
+                        red.buckets[0].launched = False
+                    e1.record()
+                    torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) / 20 * 1e3
+                n = holder.a.flat_grad.numel()
+                wire_bytes = 2 * (world - 1) / world * n * 2
+                if rank == 0:
+                    print("ALLREDUCE two-shot n=%d fp32 (%.1f MB), bf16 wire, grid %d: %.1f us per call, %.0f GB/s per direction per GPU"
+                          % (n, n * 4 / 1e6, blocks, us, wire_bytes / us / 1e3))
+            red.blocks = 0
+    _lib.check_status(dev)
+    return ok
+
+
 def main() -> int:
     world = int(os.environ["WORLD_SIZE"])
     rank = int(os.environ["RANK"])
@@ -68,6 +133,9 @@ def main() -> int:
     cuda_graph = "--graph" in sys.argv
     ok = True
     try:
+        if "--allreduce" in sys.argv:
+            ok = allreduce_case(world, rank, dev)
+            raise StopIteration
         data = RandomRecDataset(["f%d" % i for i in range(len(ROWS))], ROWS, GB, alpha=1.05, seed=3)
         batches = [data.make_batch() for _ in range(STEPS)]
         # --- single-GPU oracle on the full batch (every rank computes it; cheap)
@@ -117,6 +185,8 @@ def main() -> int:
             print("dense max |diff| %.3e  multicast=%s" % (derr, bool(peer.pads.multicast_ptr)))
         if derr > 2e-3:
             ok = False
+    except StopIteration:
+        pass
     except Exception as e:  # noqa: BLE001
         import traceback
 

@@ -11,8 +11,9 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(nproc, extra):
+def _run(nproc, extra, wire="fp32"):
     env = dict(os.environ)
+    env["RECSDK_B200_ALLREDUCE_WIRE"] = wire     # equality tests keep fp32 on the wire; bf16 has its own case
     env.setdefault("NCCL_NVLS_ENABLE", "0")
     env.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     env.setdefault("RECSDK_B200_MULTIMEM", "0")
@@ -30,4 +31,12 @@ def test_sharded_dlrm_matches_single_gpu(graph):
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     p = _run(min(n, 4) if min(n, 4) % 2 == 0 else 2, ["--graph"] if graph else [])
+    assert p.returncode == 0 and "MULTI_GPU_RESULT PASS" in p.stdout
+
+
+def test_push_allreduce_matches_nccl():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    p = _run(min(n, 8), ["--allreduce"])
     assert p.returncode == 0 and "MULTI_GPU_RESULT PASS" in p.stdout
