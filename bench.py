@@ -350,6 +350,7 @@ def main() -> None:
         tl = torch.tensor([last], dtype=torch.float64, device=dev)
         dist.all_reduce(tl)                      # each rank's loss is its share of the global-batch mean
         last = float(tl[0])
+    used_graph = pipe._graph is not None
     extras = {}
     if not args.no_extra and not args.small and args.rows_scale == 1.0:
         # the other half of the headline metric (HSTU training tokens/s at the same N) and, on one GPU, the ranking
@@ -370,8 +371,8 @@ def main() -> None:
             "data": "synthetic Zipf(1.1) ids, N(0,1) dense, Bernoulli(0.03) labels, random-init weights",
             "config": {"model": "DLRM-large" if not (args.small or args.rows_scale != 1.0) else "DLRM-debug-shrunk", "global_batch": GB,
                        "seq_len": None, "tables": 26, "embedding_dim": 128, "total_rows": int(sum(rows)),
-                       "parallelism": "dp%d dense + table-wise/row-wise embedding shards (peer-memory pull)" % world,
-                       "cuda_graph": pipe._graph is not None,
+                       "parallelism": "dp%d dense + table-wise/row-wise embedding shards (push exchange over NVLink peer memory)" % world,
+                       "cuda_graph": used_graph,
                        "l2": "inputs larger than L2: %.1f GB of tables + >126 MB activations per step" % (sum(rows) * 256 / 1e9)},
             "e2e": {"value": GB / (e2e_ms / 1e3), "unit": "samples/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": kjt_bytes * world, "d2h_bytes_per_step": 4 * world},

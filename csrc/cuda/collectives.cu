@@ -18,25 +18,13 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "peer.cuh"
+
+using namespace rbpeer;
 
 namespace cg = cooperative_groups;
 
 namespace {
-
-constexpr int MAX_RANKS = 16;
-
-struct PeerPtrs {
-  unsigned long long p[MAX_RANKS];
-};
-
-__device__ __forceinline__ void st_release_sys(int* addr, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
-  return v;
-}
 
 // One warp-sized team signals every peer and waits for every peer.  `slot` selects one of several
 // independent flag rows so different barriers of a step never alias.  Returns false on timeout.
@@ -167,12 +155,6 @@ __global__ void allreduce_f32_kernel(PeerPtrs bufs, float* mc_buf, PeerPtrs pads
   }
   grid.sync();
   if (blockIdx.x == 0 && !aborted) barrier_team(pads, epoch_word, rank, world, slot + 1, status, limit_ns);
-}
-
-inline PeerPtrs to_ptrs(const unsigned long long* host_ptrs, int world) {
-  PeerPtrs p;
-  for (int i = 0; i < MAX_RANKS; ++i) p.p[i] = (i < world) ? host_ptrs[i] : 0ull;
-  return p;
 }
 
 }  // namespace

@@ -22,65 +22,11 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "tbe_common.cuh"
+
+using namespace rbtbe;
 
 namespace {
-
-enum ShardKind : int { SH_LOCAL = 0, SH_TABLE_WISE = 1, SH_ROW_MOD = 2, SH_ROW_BLOCK = 3 };
-enum Pooling : int { POOL_SUM = 0, POOL_MEAN = 1, POOL_NONE = 2 };
-enum WDtype : int { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2 };
-enum OptType : int { OPT_SGD = 0, OPT_ROWWISE_ADAGRAD = 1, OPT_ADAGRAD = 2, OPT_ADAM = 3 };
-
-// One record per feature (bag group); features that share a table carry the same table fields.
-// `ptr_index` points into the flat pointer table
-// ptrs[ptr_index + rank]; for SH_LOCAL / SH_TABLE_WISE only entry `owner` is used.
-struct TableShard {
-  int kind;
-  int owner;
-  int D;
-  int D_offset;          // column offset of this table in the pooled output
-  long long rows;        // logical row count (bounds check)
-  long long block;       // rows per rank for SH_ROW_BLOCK
-  long long ptr_index;
-  long long key_base;    // first linear key of this table on its owner (backward)
-};
-
-template <typename T> struct Ld4;
-template <> struct Ld4<float> {
-  static __device__ __forceinline__ float4 ld(const float* p) { return *reinterpret_cast<const float4*>(p); }
-  static __device__ __forceinline__ void st(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
-};
-template <> struct Ld4<__half> {
-  static __device__ __forceinline__ float4 ld(const __half* p) {
-    uint2 u = *reinterpret_cast<const uint2*>(p);
-    float2 a = rb::unpack_f16(u.x), b = rb::unpack_f16(u.y);
-    return make_float4(a.x, a.y, b.x, b.y);
-  }
-  static __device__ __forceinline__ void st(__half* p, float4 v) {
-    *reinterpret_cast<uint2*>(p) = make_uint2(rb::pack_f16(v.x, v.y), rb::pack_f16(v.z, v.w));
-  }
-};
-template <> struct Ld4<__nv_bfloat16> {
-  static __device__ __forceinline__ float4 ld(const __nv_bfloat16* p) {
-    uint2 u = *reinterpret_cast<const uint2*>(p);
-    float2 a = rb::unpack_bf16(u.x), b = rb::unpack_bf16(u.y);
-    return make_float4(a.x, a.y, b.x, b.y);
-  }
-  static __device__ __forceinline__ void st(__nv_bfloat16* p, float4 v) {
-    *reinterpret_cast<uint2*>(p) = make_uint2(rb::pack_bf16(v.x, v.y), rb::pack_bf16(v.z, v.w));
-  }
-};
-
-__device__ __forceinline__ bool locate_row(const TableShard& ts, long long id, int world, int self,
-                                           int& rank, long long& row) {
-  if (id < 0 || id >= ts.rows) return false;
-  switch (ts.kind) {
-    case SH_ROW_MOD: rank = static_cast<int>(id % world); row = id / world; break;
-    case SH_ROW_BLOCK: rank = static_cast<int>(id / ts.block); row = id % ts.block; break;
-    case SH_TABLE_WISE: rank = ts.owner; row = id; break;
-    default: rank = self; row = id; break;
-  }
-  return true;
-}
 
 // ---------------------------------------------------------------------------
 // forward: one warp per bag (pooled) or per id (POOL_NONE)
@@ -180,40 +126,6 @@ __global__ void tbe_linearize_kernel(const TableShard* __restrict__ shards, cons
 // ---------------------------------------------------------------------------
 // one-hot fast forward: a half-warp per bag with 16-byte loads, G bags in flight per half-warp
 // ---------------------------------------------------------------------------
-template <typename T> struct Vec8;   // 8 consecutive elements <-> 8 floats
-template <> struct Vec8<float> {
-  static __device__ __forceinline__ void ld(const float* p, float (&v)[8]) {
-    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  }
-  static __device__ __forceinline__ void st(float* p, const float (&v)[8]) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
-  }
-};
-template <> struct Vec8<__half> {
-  static __device__ __forceinline__ void ld(const __half* p, float (&v)[8]) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
-    float2 a = rb::unpack_f16(u.x), b = rb::unpack_f16(u.y), c = rb::unpack_f16(u.z), d = rb::unpack_f16(u.w);
-    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
-  }
-  static __device__ __forceinline__ void st(__half* p, const float (&v)[8]) {
-    *reinterpret_cast<uint4*>(p) = make_uint4(rb::pack_f16(v[0], v[1]), rb::pack_f16(v[2], v[3]),
-                                              rb::pack_f16(v[4], v[5]), rb::pack_f16(v[6], v[7]));
-  }
-};
-template <> struct Vec8<__nv_bfloat16> {
-  static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float (&v)[8]) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
-    float2 a = rb::unpack_bf16(u.x), b = rb::unpack_bf16(u.y), c = rb::unpack_bf16(u.z), d = rb::unpack_bf16(u.w);
-    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
-  }
-  static __device__ __forceinline__ void st(__nv_bfloat16* p, const float (&v)[8]) {
-    *reinterpret_cast<uint4*>(p) = make_uint4(rb::pack_bf16(v[0], v[1]), rb::pack_bf16(v[2], v[3]),
-                                              rb::pack_bf16(v[4], v[5]), rb::pack_bf16(v[6], v[7]));
-  }
-};
-
 template <typename WT, typename OT, typename IT, int G>
 __global__ void __launch_bounds__(256)
 tbe_forward_onehot_kernel(const TableShard* __restrict__ shards, const long long* __restrict__ ptrs,
@@ -290,6 +202,11 @@ struct BwdArgs {
   float* long_accum;   // [long_cap][accum_ld] fp32 partial sums, all zero between launches
   int long_cap, chunk_cap, accum_ld, long_threshold;
   int* status;
+  // direct mode (push exchange): the gradient row of sorted entry j is direct_rows + sorted_bags[j] * direct_ld,
+  // in local memory; table_dims[n_tables] gives the row width
+  const void* direct_rows;
+  long long direct_ld;
+  const int* table_dims;
 };
 
 // per-kernel shared-memory copy of the small lookup tables
@@ -344,7 +261,9 @@ __device__ __forceinline__ void accumulate_range(const BwdArgs& a, const Tabs& t
     for (int u = 0; u < 4; ++u) {
       g[u] = nullptr;
       scale[u] = 1.f;
-      if (j + u < end) {
+      if (j + u < end && a.direct_rows) {
+        g[u] = reinterpret_cast<const GT*>(a.direct_rows) + static_cast<long long>(a.sorted_bags[j + u]) * a.direct_ld + hl * 8;
+      } else if (j + u < end) {
         const unsigned bag = static_cast<unsigned>(a.sorted_bags[j + u]);
         const unsigned f = bag / B_global;
         const unsigned bg = bag - f * B_global;
@@ -494,7 +413,7 @@ __global__ void __launch_bounds__(256, MINB) tbe_bwd_short_kernel(const BwdArgs 
       continue;
     }
     const int t = table_of_key(tb.key_cumsum, a.n_tables, key);
-    const int D = tb.f_D[static_cast<unsigned>(a.sorted_bags[beg]) / B_global];
+    const int D = a.direct_rows ? a.table_dims[t] : tb.f_D[static_cast<unsigned>(a.sorted_bags[beg]) / B_global];
     float acc[NCH][8], wpre[NCH][8], row_state;
 #pragma unroll
     for (int c = 0; c < NCH; ++c)
@@ -522,7 +441,8 @@ __global__ void __launch_bounds__(256) tbe_bwd_long_chunk_kernel(const BwdArgs a
     const int seg_beg = a.seg_offsets[s], seg_end = a.seg_offsets[s + 1];
     const int beg = seg_beg + item.y * LONG_CHUNK;
     const int end = min(seg_end, beg + LONG_CHUNK);
-    const int D = tb.f_D[static_cast<unsigned>(a.sorted_bags[seg_beg]) / B_global];
+    const int D = a.direct_rows ? a.table_dims[table_of_key(tb.key_cumsum, a.n_tables, a.unique_keys[s])]
+                                : tb.f_D[static_cast<unsigned>(a.sorted_bags[seg_beg]) / B_global];
     float acc[NCH][8];
 #pragma unroll
     for (int c = 0; c < NCH; ++c)
@@ -556,7 +476,7 @@ __global__ void __launch_bounds__(256) tbe_bwd_long_final_kernel(const BwdArgs a
     const int s = a.long_list[li];
     const long long key = a.unique_keys[s];
     const int t = table_of_key(tb.key_cumsum, a.n_tables, key);
-    const int D = tb.f_D[static_cast<unsigned>(a.sorted_bags[a.seg_offsets[s]]) / B_global];
+    const int D = a.direct_rows ? a.table_dims[t] : tb.f_D[static_cast<unsigned>(a.sorted_bags[a.seg_offsets[s]]) / B_global];
     float* src = a.long_accum + static_cast<long long>(li) * a.accum_ld;
     float acc[NCH][8], wpre[NCH][8], row_state;
     preload_row<WT, NCH>(a, tb, t, key - tb.key_cumsum[t], D, wpre, row_state, hl);
@@ -791,14 +711,15 @@ RB_API int rb_sort_segments(const long long* keys_in, const int* vals_in, long l
   return 0;
 }
 
-RB_API int rb_tbe_backward_update(
+static int tbe_backward_update_impl(
     const void* shards, const long long* key_cumsum, const long long* w_offsets, const long long* s_offsets,
     int T, int n_tables, int B_local, int world, const long long* grad_ptrs, long long ld_g, int g_dtype,
     const long long* offsets, int pooling, const int* sorted_bags, const long long* unique_keys,
     const int* seg_offsets, const int* num_runs, int max_runs, void* weights, int w_dtype, float* state1,
     float* state2, int opt_type, float lr, float eps, float beta1, float beta2, float weight_decay,
     float bias_c1, float bias_c2, int max_D, int* long_list, int* counters, void* chunk_list, float* long_accum,
-    int long_cap, int chunk_cap, int accum_ld, int long_threshold, int num_sms, int* status, cudaStream_t st) {
+    int long_cap, int chunk_cap, int accum_ld, int long_threshold, int num_sms, int* status, cudaStream_t st,
+    const void* direct_rows, long long direct_ld, const int* table_dims) {
   if (max_runs <= 0) return 0;
   BwdArgs a;
   a.shards = reinterpret_cast<const TableShard*>(shards);
@@ -812,6 +733,7 @@ RB_API int rb_tbe_backward_update(
   a.long_list = long_list; a.counters = counters; a.chunk_list = reinterpret_cast<int2*>(chunk_list);
   a.long_accum = long_accum; a.long_cap = long_cap; a.chunk_cap = chunk_cap; a.accum_ld = accum_ld;
   a.long_threshold = long_threshold; a.status = status;
+  a.direct_rows = direct_rows; a.direct_ld = direct_ld; a.table_dims = table_dims;
   if (num_sms <= 0) num_sms = 148;
   if (max_D % 8 || accum_ld < max_D) return -7;
   RB_CUDA_CHECK(cudaMemsetAsync(counters, 0, 2 * sizeof(int), st));
@@ -824,6 +746,38 @@ RB_API int rb_tbe_backward_update(
   }
   RB_W_DISPATCH(w_dtype, RB_G_DISPATCH(return dispatch_nch<WT, GT>(a, max_D, max_runs, num_sms, st)))
   return 0;
+}
+
+RB_API int rb_tbe_backward_update(
+    const void* shards, const long long* key_cumsum, const long long* w_offsets, const long long* s_offsets,
+    int T, int n_tables, int B_local, int world, const long long* grad_ptrs, long long ld_g, int g_dtype,
+    const long long* offsets, int pooling, const int* sorted_bags, const long long* unique_keys,
+    const int* seg_offsets, const int* num_runs, int max_runs, void* weights, int w_dtype, float* state1,
+    float* state2, int opt_type, float lr, float eps, float beta1, float beta2, float weight_decay,
+    float bias_c1, float bias_c2, int max_D, int* long_list, int* counters, void* chunk_list, float* long_accum,
+    int long_cap, int chunk_cap, int accum_ld, int long_threshold, int num_sms, int* status, cudaStream_t st) {
+  return tbe_backward_update_impl(shards, key_cumsum, w_offsets, s_offsets, T, n_tables, B_local, world, grad_ptrs, ld_g, g_dtype, offsets,
+                                 pooling, sorted_bags, unique_keys, seg_offsets, num_runs, max_runs, weights, w_dtype, state1, state2,
+                                 opt_type, lr, eps, beta1, beta2, weight_decay, bias_c1, bias_c2, max_D, long_list, counters,
+                                 chunk_list, long_accum, long_cap, chunk_cap, accum_ld, long_threshold, num_sms, status, st, nullptr, 0, nullptr);
+}
+
+// Same update with the gradient rows already in local memory (push exchange): the gradient of sorted entry j is the
+// row sorted_bags[j] of `direct_rows` (rows of direct_ld elements of g_dtype); table_dims[n_tables] = row widths.
+RB_API int rb_tbe_backward_update_rows(
+    const void* shards, const long long* key_cumsum, const long long* w_offsets, const long long* s_offsets,
+    int T, int n_tables, int B_local, int world, const long long* grad_ptrs, long long ld_g, int g_dtype,
+    const long long* offsets, int pooling, const int* sorted_bags, const long long* unique_keys,
+    const int* seg_offsets, const int* num_runs, int max_runs, void* weights, int w_dtype, float* state1,
+    float* state2, int opt_type, float lr, float eps, float beta1, float beta2, float weight_decay,
+    float bias_c1, float bias_c2, int max_D, int* long_list, int* counters, void* chunk_list, float* long_accum,
+    int long_cap, int chunk_cap, int accum_ld, int long_threshold, int num_sms, int* status, cudaStream_t st,
+    const void* direct_rows, long long direct_ld, const int* table_dims) {
+  if (!direct_rows || !table_dims) return -1;
+  return tbe_backward_update_impl(shards, key_cumsum, w_offsets, s_offsets, T, n_tables, B_local, world, grad_ptrs, ld_g, g_dtype, offsets,
+                                 pooling, sorted_bags, unique_keys, seg_offsets, num_runs, max_runs, weights, w_dtype, state1, state2,
+                                 opt_type, lr, eps, beta1, beta2, weight_decay, bias_c1, bias_c2, max_D, long_list, counters,
+                                 chunk_list, long_accum, long_cap, chunk_cap, accum_ld, long_threshold, num_sms, status, st, direct_rows, direct_ld, table_dims);
 }
 
 RB_API int rb_gather_rows(const void* src, const long long* idx, long long n, long long row_bytes, void* dst,

@@ -39,7 +39,8 @@ def _declare(lib: ctypes.CDLL) -> None:
 
 
 # kernels launched by one call of a launcher (default 1); used for the launch counter only
-_KERNELS_PER_CALL = {"rb_sort_segments": 8, "rb_sort_pairs_i64_i32": 4, "rb_tbe_backward_update": 2, "rb_sort_segments_temp_bytes": 0}
+_KERNELS_PER_CALL = {"rb_sort_segments": 8, "rb_sort_pairs_i64_i32": 4, "rb_tbe_backward_update": 2, "rb_tbe_backward_update_rows": 2, "rb_a2a_ctl_ints": 0, "rb_a2a_loc_ints": 0, "rb_a2a_loc_n_owned_index": 0,
+                     "rb_allreduce_push_staging_bytes": 0, "rb_allreduce_push_max_blocks": 0, "rb_sort_segments_temp_bytes": 0}
 launch_count = 0
 
 

@@ -258,6 +258,38 @@ def tbe_backward_update(layout: TbeLayout, dev: dict, seg: SortedSegments, grad_
     _lib.check(rc, "rb_tbe_backward_update")
 
 
+def tbe_backward_update_rows(layout: TbeLayout, dev: dict, seg: SortedSegments, grad_rows: torch.Tensor, ld_rows: int,
+                             table_dims: torch.Tensor, weights: torch.Tensor, state1: Optional[torch.Tensor],
+                             state2: Optional[torch.Tensor], s_offsets: torch.Tensor, opt: OptimizerSpec, step: int,
+                             ws: BackwardWorkspace, long_threshold: int = 256) -> None:
+    """The same fused segment-sum + optimizer with every gradient row already in local memory (push exchange):
+    ``seg.sorted_bags[j]`` is the row of ``grad_rows`` (stride ``ld_rows`` elements) that belongs to sorted entry ``j``."""
+    bc1 = 1.0 - opt.beta1 ** max(step, 1)
+    bc2 = 1.0 - opt.beta2 ** max(step, 1)
+    dummy = dev["key_cumsum"]
+    rc = _lib.lib().rb_tbe_backward_update_rows(
+        dev["shards"].data_ptr(), dev["key_cumsum"].data_ptr(), dev["w_offsets"].data_ptr(), s_offsets.data_ptr(),
+        layout.T, layout.n_tables, 1, 1, dummy.data_ptr(), 0, _lib.dtype_code(grad_rows.dtype), None,
+        POOL_SUM, seg.sorted_bags.data_ptr(), seg.unique_keys.data_ptr(), seg.seg_offsets.data_ptr(),
+        seg.num_runs.data_ptr(), seg.max_runs, weights.data_ptr(), _lib.dtype_code(weights.dtype),
+        _lib.ptr(state1), _lib.ptr(state2), opt.kind, opt.lr, opt.eps, opt.beta1, opt.beta2, opt.weight_decay,
+        bc1, bc2, layout.max_D, ws.long_list.data_ptr(), ws.counters.data_ptr(), ws.chunk_list.data_ptr(),
+        ws.long_accum.data_ptr(), ws.long_cap, ws.chunk_cap, ws.accum_ld, long_threshold,
+        _lib.num_sms(weights.device), _lib.status_tensor(weights.device).data_ptr(),
+        _lib.stream_ptr(weights.device), grad_rows.data_ptr(), ld_rows, table_dims.data_ptr())
+    _lib.check(rc, "rb_tbe_backward_update_rows")
+
+
+def pool_rows(rows: torch.Tensor, ld_rows: int, offsets: torch.Tensor, T: int, B: int, f_D: torch.Tensor, f_Doff: torch.Tensor,
+              mean: bool, out: torch.Tensor) -> torch.Tensor:
+    """``out[b, Doff[f]:Doff[f]+D[f]] = sum or mean over the ids j of bag (f, b) of rows[j, :D[f]]`` (fp32 accumulation)."""
+    rc = _lib.lib().rb_pool_rows(rows.data_ptr(), _lib.dtype_code(rows.dtype), ld_rows, offsets.data_ptr(), T, B, f_D.data_ptr(),
+                                 f_Doff.data_ptr(), int(mean), out.data_ptr(), _lib.dtype_code(out.dtype), out.stride(0),
+                                 _lib.stream_ptr(out.device))
+    _lib.check(rc, "rb_pool_rows")
+    return out
+
+
 def gather_rows(src: torch.Tensor, idx: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[i] = src[idx[i]]`` for a 2-D row-major ``src`` (HBM cache -> staging)."""
     if not src.is_cuda:

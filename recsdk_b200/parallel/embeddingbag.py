@@ -1,24 +1,27 @@
 """Sharded ``EmbeddingBagCollection`` on the fused peer-memory kernels.
 
-Every rank keeps its shard of every table in one flat, peer-mapped weight buffer.  A train step does
+Every rank keeps its shard of every table in one flat weight buffer.  With more than one GPU a train step is the push
+exchange of ``push_exchange.py`` / ``csrc/cuda/a2a_push.cu``:
 
-* ``input_dist``   push this rank's ids (and bag offsets) into every peer's gathered-id buffer and cross
-                   a device barrier; linearize + sort + run-length-encode the ids this rank owns,
-* ``forward``      one kernel pulls the rows of the local batch from whichever GPU owns them and writes
-                   the pooled result ``[B_local, sum(D)]`` (no id all-to-all, no pooled all-to-all),
-* ``backward``     publish the pooled-output gradient in a peer-mapped buffer, barrier, then one kernel
-                   per owner: pull the gradients of every bag that touched an owned row from the GPU
-                   that holds the sample, segment-sum them and apply the sparse optimizer in place.
+* ``input_dist``   route every local id to its owner and store (key, position) into the owner's dense receive list
+                   (counts travel through peer memory, no host sync); the owner gathers the requested rows from its
+                   own HBM and stores them straight into the requester's output - for one-hot features that is the
+                   feature-interaction input ``[B_local, sum(D)]``, for variable-length bags a per-id row list that the
+                   requester pools; the owner also sorts its received keys on a side stream for the backward,
+* ``forward``      wait for the rows of all owners (one flag per owner),
+* ``backward``     store the gradient row of every id into the owner's gradient list, then one kernel per owner
+                   segment-sums per unique row from local memory and applies the sparse optimizer in place.
 
 Sharding types: table-wise, row-wise (round-robin ``id % world`` like the reference's bucketize,
-``hybrid_torchrec/src/ids_process/bucketize.cpp:46,66``, or contiguous blocks) and data-parallel
-(replicated; gradients of a replicated table are summed by the owner-pull kernel on every rank).
+``hybrid_torchrec/src/ids_process/bucketize.cpp:46,66``, or contiguous blocks) and data-parallel (on several GPUs a
+data-parallel table is stored row-wise: same numerics, one update per row instead of a replicated one).
 The module contract (``input_dist`` / ``compute_and_output_dist`` / ``forward``) follows
 ``hybrid_torchrec/distributed/embeddingbag.py:481-693``.
 """
 from __future__ import annotations
 
 import dataclasses
+import os
 from typing import Dict, List, Optional
 
 import numpy as np
@@ -32,6 +35,7 @@ from ..optim import FusedOptimizerStub
 from ..sparse.jagged_tensor import KeyedJaggedTensor, KeyedTensor
 from ..utils import trace
 from .comm import PeerGroup, ShardingEnv
+from .push_exchange import MODE_ONE_HOT, MODE_POOLED, PH_GRADS, PH_ROWS, PushExchange
 
 
 @dataclasses.dataclass
@@ -61,6 +65,7 @@ class EmbeddingDistContext:
     B_local: int
     segments: Optional[E.SortedSegments] = None
     global_offsets: Optional[torch.Tensor] = None
+    one_hot: bool = False
 
 
 class _LookupFn(torch.autograd.Function):
@@ -112,6 +117,8 @@ class ShardedEmbeddingBagCollection(nn.Module):
             k = _kind_of(ps)
             if self.world == 1:
                 k = E.SH_LOCAL
+            elif k == E.SH_LOCAL:
+                k = E.SH_ROW_MOD          # several GPUs: a data-parallel table is stored row-wise (one update per row)
             kinds.append(k)
             owners.append((ps.ranks[0] if ps.ranks else 0) if k == E.SH_TABLE_WISE else 0)
         self.plan = plan
@@ -126,15 +133,12 @@ class ShardedEmbeddingBagCollection(nn.Module):
             raise ValueError("world_size > 1 needs a PeerGroup")
         itemsize = torch.empty(0, dtype=self.w_dtype).element_size()
         max_elems = int(self.layout.local_elems.max())
-        if self.world > 1:
-            self._wbuf = peer.alloc(max(max_elems, 1) * itemsize)
-            base_ptrs = self._wbuf.ptrs
-            flat = self._wbuf.local.view(self.w_dtype)
-        else:
-            flat = torch.empty(max(max_elems, 1), dtype=self.w_dtype, device=device)
-            self._wbuf = None
-            base_ptrs = [flat.data_ptr()]
+        # owners read their rows locally and push them, so the weights need no peer mapping
+        flat = torch.empty(max(int(self.layout.local_elems[self.rank]), 1), dtype=self.w_dtype, device=device)
+        base_ptrs = [0] * self.world
+        base_ptrs[self.rank] = flat.data_ptr()
         self.weights = flat
+        del max_elems
         self.dev = self.layout.device_tensors(device, base_ptrs, itemsize)
         # optimizer state
         L = self.layout
@@ -169,10 +173,9 @@ class ShardedEmbeddingBagCollection(nn.Module):
         self._anchor._in_backward_optimizers = True  # type: ignore[attr-defined]
         self._bwd_ws: Optional[E.BackwardWorkspace] = None
         self._sorter: Optional[E.SegmentSorter] = None
-        self._gather_ids: Optional[object] = None
-        self._gather_offs: Optional[object] = None
-        self._grad_buf: Optional[object] = None
-        self._grad_ptrs: Optional[torch.Tensor] = None
+        self._px: Optional[PushExchange] = None
+        self._px_one_hot = False
+        self.owned_cap_factor = float(os.environ.get("RECSDK_B200_OWNED_CAP_FACTOR", "3.0"))
         self._caps = (0, 0)
         self.max_local_batch, self.max_ids_per_rank = max_local_batch, max_ids_per_rank
         self.fused_optimizer = FusedOptimizerStub([h.weight for h in self.embedding_bags.values()], self.opt)
@@ -250,22 +253,75 @@ class ShardedEmbeddingBagCollection(nn.Module):
         return r
 
     # ------------------------------------------------------------ workspaces
-    def _ensure_capacity(self, B_local: int, nnz_local: int) -> None:
-        cap_b = max(self.max_local_batch, B_local)
-        cap_n = max(self.max_ids_per_rank, nnz_local)
-        if self._sorter is not None and self._caps[0] >= cap_b and self._caps[1] >= cap_n:
+    def _ensure_capacity(self, B_local: int, nnz_local: int, one_hot: bool) -> None:
+        if self.world == 1:
+            cap_b = max(self.max_local_batch, B_local)
+            cap_n = max(self.max_ids_per_rank, nnz_local)
+            if self._sorter is not None and self._caps[0] >= cap_b and self._caps[1] >= cap_n:
+                return
+            cap_n = (cap_n + 1) // 2 * 2
+            self._caps = (cap_b, cap_n)
+            self._sorter = E.SegmentSorter(cap_n, self.device)
+            self._bwd_ws = E.BackwardWorkspace(self.device, cap_n, self.layout.max_D)
             return
-        cap_n = (cap_n + 1) // 2 * 2
+        if self._px is not None:
+            if B_local > self._caps[0] or nnz_local > self._caps[1] or one_hot != self._px_one_hot:
+                raise ValueError("batch (%d samples, %d ids, one_hot=%s) exceeds what the exchange buffers were sized for "
+                                 "(%d samples, %d ids, one_hot=%s): pass max_local_batch / max_ids_per_rank"
+                                 % (B_local, nnz_local, one_hot, self._caps[0], self._caps[1], self._px_one_hot))
+            return
+        # Peer buffers are allocated collectively, so every rank must arrive at the same sizes: take the maximum over ranks
+        # of the first batch (one host-side exchange, set-up only) unless the caller gave explicit bounds.
+        import torch.distributed as dist
+
+        cap_b, cap_n = max(self.max_local_batch, B_local), max(self.max_ids_per_rank, nnz_local)
+        t = torch.tensor([cap_b, cap_n, 0 if self.max_ids_per_rank else 1], dtype=torch.int64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.env.process_group)
+        cap_b, cap_n, guessed = int(t[0]), int(t[1]), bool(t[2])
+        if guessed and not one_hot:
+            cap_n = int(cap_n * 1.5) + 1024         # variable-length bags: head-room over the first batch
+        cap_n = (cap_n + 7) // 8 * 8
         self._caps = (cap_b, cap_n)
-        T = self.layout.T
-        self._sorter = E.SegmentSorter(cap_n * self.world, self.device)
-        self._bwd_ws = E.BackwardWorkspace(self.device, cap_n * self.world, self.layout.max_D)
-        if self.world > 1:
-            self._gather_ids = self.peer.alloc(self.world * cap_n * 8)
-            self._gather_offs = self.peer.alloc(self.world * (T * cap_b + 2) * 8)
-            self._grad_buf = self.peer.alloc(cap_b * self.layout.total_D * 2 if self.out_dtype != torch.float32
-                                             else cap_b * self.layout.total_D * 4)
-            self._grad_ptrs = self._grad_buf.ptr_tensor(self.device)
+        L = self.layout
+        owned = self._owned_cap(cap_b * self.world, cap_n, one_hot)
+        out_item = torch.empty(0, dtype=self.out_dtype).element_size()
+        w_item = torch.empty(0, dtype=self.w_dtype).element_size()
+        self._row_ld = (L.max_D + 7) // 8 * 8
+        out_bytes = cap_b * L.total_D * out_item if one_hot else cap_n * self._row_ld * w_item
+        self._px = PushExchange(self.peer, self.device, cap_n, owned, self._row_ld, self.out_dtype, out_bytes)
+        self._px_one_hot = one_hot
+        self._bwd_ws = E.BackwardWorkspace(self.device, owned, L.max_D)
+        i32 = dict(dtype=torch.int32, device=self.device)
+        self._f_D = torch.tensor(L.feature_dims, **i32)
+        self._f_Doff = torch.tensor([int(x) for x in L.D_offsets[:-1]], **i32)
+        self._table_dims = torch.tensor(L.dims, **i32)
+        self._feature_table_dev = torch.tensor(L.feature_table, **i32)
+        kb = np.zeros((self.world, L.n_tables), dtype=np.int64)
+        if L.n_tables > 1:
+            kb[:, 1:] = np.cumsum(L.local_rows, axis=1)[:, :-1]
+        self._key_base_all = torch.from_numpy(kb).to(self.device)
+        if one_hot:
+            self._out_view = self._px.out_raw[: cap_b * L.total_D * out_item].view(self.out_dtype).view(cap_b, L.total_D)
+        else:
+            self._rows_view = self._px.out_raw[: cap_n * self._row_ld * w_item].view(self.w_dtype).view(cap_n, self._row_ld)
+
+    def _owned_cap(self, Bg: int, nnz_cap: int, one_hot: bool) -> int:
+        """Capacity of this rank's receive list.  One-hot: all ids of the table-wise tables it owns plus ``owned_cap_factor``
+        times the fair share of the row-wise ones (hot ids cluster on a few residues).  Variable-length bags:
+        ``owned_cap_factor`` times the ids one rank sends.  Never more than everything the job can send.  A step that
+        would exceed it sets ``RB_ERR_CAPACITY`` (polled by the train pipelines, which raise)."""
+        factor = self.owned_cap_factor
+        if not one_hot:
+            return int(min(self.world * nnz_cap, (int(factor * nnz_cap) + 8191) // 1024 * 1024))
+        need = [0.0] * self.world            # the same list on every rank: it depends on the plan only
+        for f in range(self.layout.T):
+            ti = self._feature_table[f]
+            if self._kinds[ti] == E.SH_TABLE_WISE:
+                need[self._owners[ti]] += Bg
+            else:
+                for r in range(self.world):
+                    need[r] += factor * Bg / self.world
+        return int(min(self.layout.T * Bg, (int(max(need)) + 8191) // 1024 * 1024))
 
     # ------------------------------------------------------------ input dist
     def input_dist(self, features: KeyedJaggedTensor) -> EmbeddingDistContext:
@@ -278,53 +334,47 @@ class ShardedEmbeddingBagCollection(nn.Module):
         one_hot = self.one_hot or bool(getattr(features, "one_hot", False))
         offsets = None if one_hot else features.offsets().contiguous()
         nnz = idx.numel()
-        self._ensure_capacity(B, nnz)
-        dctx = EmbeddingDistContext(idx, offsets, B)
-        T = self.layout.T
+        self._ensure_capacity(B, nnz, one_hot)
+        dctx = EmbeddingDistContext(idx, offsets, B, one_hot=one_hot)
+        L = self.layout
         if self.world == 1:
-            dctx.segments = self._sorter.run(self.layout, self.dev, idx, offsets, B)
+            dctx.segments = self._sorter.run(L, self.dev, idx, offsets, B)
             dctx.global_offsets = offsets
             return dctx
-        # --- multi-GPU: gather everyone's ids (and offsets) into every rank, then barrier
-        if not one_hot:
-            raise NotImplementedError("multi-GPU fused path currently takes one-hot (fixed-length-1) features; "
-                                      "use the collective backend for variable-length bags")
-        if idx.dtype != torch.int64:
-            idx = idx.long()
-        cap_b, _ = self._caps
-        assert B == cap_b or self.max_local_batch == 0 or B <= cap_b
-        Bg = B * self.world
-        row_bytes = B * 8
-        trace.mark("emb.id_push")
-        self.peer.allgather_push_2d(self._gather_ids, idx.view(T, B), Bg * 8, self.rank * row_bytes)
-        trace.mark("emb.id_barrier")
-        self.peer.barrier()
-        trace.mark("emb.sort")
-        gathered = self._gather_ids.local.view(torch.int64)[: T * Bg]
-        dctx.segments = self._sorter.run(self.layout, self.dev, gathered, None, Bg, owned_cap=self._owned_cap(Bg))
-        trace.mark("emb.sort_done")
+        px = self._px
+        px.join_sort()                  # a previous step without a backward: its sort must not race the new payload
+        trace.mark("emb.route_scatter")
+        px.route_scatter(idx, offsets, L.T, B, self.dev["shards"], self._key_base_all, self._feature_table_dev,
+                         L.n_tables, want_bags=not one_hot)
+        trace.mark("emb.serve_rows")
+        if one_hot:
+            px.serve_rows(self.dev["key_cumsum"], self.dev["w_offsets"], self._table_dims, self._f_Doff, L.n_tables, L.T,
+                          self.weights, self.out_dtype, L.total_D, True, B)
+        else:
+            px.serve_rows(self.dev["key_cumsum"], self.dev["w_offsets"], self._table_dims, None, L.n_tables, L.T,
+                          self.weights, self.w_dtype, self._row_ld, False, B)
+        if self.training and torch.is_grad_enabled():
+            dctx.segments = px.sort_received(L.key_bits)
+        trace.mark("emb.input_dist_done")
         return dctx
-
-    def _owned_cap(self, Bg: int) -> int:
-        """Bound on the ids of a gathered one-hot batch that this rank owns: all ids of its table-wise tables, twice the
-        fair share of the row-wise ones (hot ids cluster on a few residues), everything of replicated tables."""
-        exp = 0.0
-        for f in range(self.layout.T):
-            ti = self._feature_table[f]
-            k = self._kinds[ti]
-            if k == E.SH_TABLE_WISE:
-                exp += Bg if self._owners[ti] == self.rank else 0
-            elif k in (E.SH_ROW_MOD, E.SH_ROW_BLOCK):
-                exp += 2.0 * Bg / self.world
-            else:
-                exp += Bg
-        return int(min(self.layout.T * Bg, (int(exp) + 8191) // 1024 * 1024))
 
     # --------------------------------------------------------------- compute
     def _lookup(self, dctx: EmbeddingDistContext) -> torch.Tensor:
-        out = torch.empty(dctx.B_local, self.layout.total_D, dtype=self.out_dtype, device=self.device)
-        trace.mark("emb.lookup")
-        E.tbe_forward(self.layout, self.dev, dctx.indices, dctx.offsets, dctx.B_local, self.pooling, self.w_dtype, out)
+        L = self.layout
+        if self.world == 1:
+            out = torch.empty(dctx.B_local, L.total_D, dtype=self.out_dtype, device=self.device)
+            trace.mark("emb.lookup")
+            E.tbe_forward(L, self.dev, dctx.indices, dctx.offsets, dctx.B_local, self.pooling, self.w_dtype, out)
+            trace.mark("dense.forward")
+            return out
+        trace.mark("emb.wait_rows")
+        self._px.wait(PH_ROWS)
+        if dctx.one_hot:
+            out = self._out_view[: dctx.B_local]
+        else:
+            out = torch.empty(dctx.B_local, L.total_D, dtype=self.out_dtype, device=self.device)
+            E.pool_rows(self._rows_view, self._row_ld, dctx.offsets, L.T, dctx.B_local, self._f_D, self._f_Doff,
+                        self.pooling == E.POOL_MEAN, out)
         trace.mark("dense.forward")
         return out
 
@@ -339,16 +389,23 @@ class ShardedEmbeddingBagCollection(nn.Module):
                                   dctx.global_offsets, self.pooling, self.weights, self.state1, self.state2,
                                   self.s_offsets, self.opt, self._step, self._bwd_ws)
             return
-        trace.mark("emb.grad_publish")
-        gb = self._grad_buf.local.view(dout.dtype)[: dout.numel()].view(dout.shape)
-        if dout.data_ptr() != gb.data_ptr():           # the consumer may already have written into the published buffer
-            gb.copy_(dout)
-        trace.mark("emb.grad_barrier")
-        self.peer.barrier()
+        px = self._px
+        L = self.layout
+        if dctx.segments is None:
+            raise RuntimeError("backward through a lookup whose input_dist ran without gradients enabled")
+        g = dout if (dout.stride(-1) == 1 and dout.dtype == self.out_dtype) else dout.to(self.out_dtype).contiguous()
+        px.join_sort()
+        trace.mark("emb.grad_push")
+        if dctx.one_hot:
+            px.push_grads(g, MODE_ONE_HOT, self._f_D, self._f_Doff, L.T, dctx.B_local)
+        else:
+            px.push_grads(g, MODE_POOLED, self._f_D, self._f_Doff, L.T, dctx.B_local, dctx.offsets,
+                          self.pooling == E.POOL_MEAN)
+        trace.mark("emb.grad_wait")
+        px.wait(PH_GRADS)
         trace.mark("emb.backward_update")
-        E.tbe_backward_update(self.layout, self.dev, dctx.segments, self._grad_ptrs, self.layout.total_D, dout.dtype,
-                              dctx.B_local, None, self.pooling, self.weights, self.state1, self.state2,
-                              self.s_offsets, self.opt, self._step, self._bwd_ws)
+        E.tbe_backward_update_rows(L, self.dev, dctx.segments, px.grad_recv, px.g_ld, self._table_dims, self.weights,
+                                   self.state1, self.state2, self.s_offsets, self.opt, self._step, self._bwd_ws)
         trace.mark("dense.backward_rest")
 
     def _static_ptr(self, g: torch.Tensor) -> torch.Tensor:
@@ -359,8 +416,6 @@ class ShardedEmbeddingBagCollection(nn.Module):
 
     def compute_and_output_dist(self, dctx: EmbeddingDistContext) -> KeyedTensor:
         out = _LookupFn.apply(self._anchor, self, dctx)
-        if self.world > 1:
-            out._grad_out_buffer = self._grad_buf.local.view(out.dtype)[: out.numel()].view(out.shape)
         return KeyedTensor(self.feature_names, self.layout.feature_dims, out)
 
     def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:

@@ -124,6 +124,61 @@ def allreduce_case(world, rank, dev) -> bool:
     return ok
 
 
+def varlen_case(world, rank, dev) -> bool:
+    """Variable-length bags (sum and mean pooling) through the push exchange against the same collection on one GPU:
+    pooled outputs, then the tables after a backward with a fixed output gradient, two steps in a row."""
+    from recsdk_b200.modules.embedding_configs import PoolingType
+    from recsdk_b200.parallel.embeddingbag import ShardedEmbeddingBagCollection
+
+    peer = PeerGroup(dist.group.WORLD, dev)
+    ok = True
+    rows, dims = [3000, 257, 4096, 100], [64, 32, 64, 128]
+    Bg = 256
+    Bl = Bg // world
+    for pooling in (PoolingType.SUM, PoolingType.MEAN):
+        cfgs = [EmbeddingBagConfig(num_embeddings=r, embedding_dim=d, name="v%d" % i, feature_names=["g%d" % i],
+                                   data_type=DataType.FP32, pooling=pooling) for i, (r, d) in enumerate(zip(rows, dims))]
+        plan = {"v0": ParameterSharding("row_wise"), "v1": ParameterSharding("table_wise", ranks=[world - 1]),
+                "v2": ParameterSharding("row_wise", row_partition="block"), "v3": ParameterSharding("data_parallel")}
+        spec = E.OptimizerSpec(kind=E.OPT_ADAGRAD, lr=0.1, eps=1e-8)
+        ref = ShardedEmbeddingBagCollection(cfgs, {}, ShardingEnv(1, 0), dev, spec, out_dtype=torch.float32)
+        ref.reset_parameters(seed=5)
+        sh = ShardedEmbeddingBagCollection(cfgs, plan, ShardingEnv(world, rank, dist.group.WORLD), dev, spec, peer=peer,
+                                           out_dtype=torch.float32)
+        sh.reset_parameters(seed=5)
+        g = torch.Generator().manual_seed(99)
+        for step in range(2):
+            lens = torch.randint(0, 6, (len(rows), Bg), generator=g)
+            vals = torch.cat([torch.randint(0, rows[t], (int(lens[t].sum()),), generator=g) for t in range(len(rows))])
+            dout = torch.randn(Bg, sum(dims), generator=g)
+            full = KeyedJaggedTensor(["g%d" % i for i in range(len(rows))], vals.to(dev), lengths=lens.reshape(-1).to(dev), stride=Bg)
+            want = ref(full).values()
+            want.backward(dout.to(dev))
+            # this rank's samples
+            off = torch.cat([torch.zeros(1, dtype=torch.int64), lens.reshape(-1).cumsum(0)])
+            lv, ll = [], []
+            for t in range(len(rows)):
+                for b in range(rank * Bl, (rank + 1) * Bl):
+                    lv.append(vals[off[t * Bg + b]:off[t * Bg + b + 1]])
+                ll.append(lens[t, rank * Bl:(rank + 1) * Bl])
+            mine = KeyedJaggedTensor(["g%d" % i for i in range(len(rows))], torch.cat(lv).to(dev), lengths=torch.cat(ll).to(dev), stride=Bl)
+            got = sh(mine).values()
+            err = (got - want[rank * Bl:(rank + 1) * Bl]).abs().max().item()
+            got.backward(dout[rank * Bl:(rank + 1) * Bl].to(dev).contiguous())
+            torch.cuda.synchronize()
+            if not err <= 1e-5:
+                ok = False
+                print("rank %d varlen %s step %d pooled err %.3e" % (rank, pooling, step, err))
+        _lib.check_status(dev)
+        for c in cfgs:
+            err = (sh.full_table(c.name) - ref.full_table(c.name)).abs().max().item()
+            if rank == 0:
+                print("varlen %s table %s max |diff| %.3e" % (pooling.name, c.name, err))
+            if not err <= 1e-5:
+                ok = False
+    return ok
+
+
 def main() -> int:
     world = int(os.environ["WORLD_SIZE"])
     rank = int(os.environ["RANK"])
@@ -133,6 +188,9 @@ def main() -> int:
     cuda_graph = "--graph" in sys.argv
     ok = True
     try:
+        if "--varlen" in sys.argv:
+            ok = varlen_case(world, rank, dev)
+            raise StopIteration
         if "--allreduce" in sys.argv:
             ok = allreduce_case(world, rank, dev)
             raise StopIteration

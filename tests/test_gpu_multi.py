@@ -40,3 +40,11 @@ def test_push_allreduce_matches_nccl():
         pytest.skip("needs at least 2 GPUs")
     p = _run(min(n, 8), ["--allreduce"])
     assert p.returncode == 0 and "MULTI_GPU_RESULT PASS" in p.stdout
+
+
+def test_push_exchange_variable_length_bags():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    p = _run(min(n, 4) if min(n, 4) % 2 == 0 else 2, ["--varlen"])
+    assert p.returncode == 0 and "MULTI_GPU_RESULT PASS" in p.stdout
