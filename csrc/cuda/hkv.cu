@@ -45,6 +45,12 @@ struct HkvTable {
   int emb_dim;
   int evict_strategy;
   unsigned long long* size;
+  // Launch stamps: find_or_insert writes `epoch` into touch[slot] of every slot it returns, and never evicts a slot
+  // stamped with the current epoch.  Slot numbers handed out by one launch therefore stay valid for the kernels that
+  // consume them (gather, scatter, update): a later warp of the same launch cannot evict a key inserted or found by
+  // an earlier one.  touch may be null (no protection).
+  unsigned* touch;
+  unsigned epoch;
 };
 
 struct InitArgs {
@@ -149,9 +155,10 @@ __global__ void __launch_bounds__(256)
 hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ keys, long long n, int insert,
                           int update_score, const unsigned long long* __restrict__ scores_in,
                           long long* __restrict__ out_slots, unsigned char* __restrict__ out_status, InitArgs init,
-                          EvictOut ev, int* status) {
+                          EvictOut ev, int* status, const int* __restrict__ n_dev) {
   const int lane = threadIdx.x & 31;
   const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  if (n_dev && *n_dev < n) n = *n_dev;          // the number of keys may live on the device (no host read)
   for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; i < n; i += warps_total) {
     const unsigned long long key = keys[i];
     if (key == EMPTY_KEY) {
@@ -170,9 +177,10 @@ hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ key
     int pos = find_in_bucket(t, b, key, dg, d4, lane);
     unsigned char st = ST_FOUND;
     if (pos >= 0) {
-      if (update_score && lane == 0) {
+      if (lane == 0) {
         const long long s = b * BUCKET + pos;
-        t.scores[s] = new_score(t.evict_strategy, __ldcg(t.scores + s), false, scores_in, i);
+        if (update_score) t.scores[s] = new_score(t.evict_strategy, __ldcg(t.scores + s), false, scores_in, i);
+        if (insert && t.touch) t.touch[s] = t.epoch;
       }
     } else if (!insert) {
       st = ST_MISSING;
@@ -193,18 +201,24 @@ hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ key
         unsigned long long best = ~0ull;
         int best_pos = lane * 4;
 #pragma unroll
+        bool any_free = false;                   // a slot not handed out by this launch
         for (int j = 0; j < 4; ++j) {
-          const unsigned long long s = __ldcg(t.scores + b * BUCKET + lane * 4 + j);
-          if (s < best) { best = s; best_pos = lane * 4 + j; }
+          const long long sl = b * BUCKET + lane * 4 + j;
+          if (t.touch && __ldcg(t.touch + sl) == t.epoch) continue;
+          const unsigned long long s = __ldcg(t.scores + sl);
+          if (!any_free || s < best) { best = s; best_pos = lane * 4 + j; }
+          any_free = true;
         }
+        if (!any_free) best = ~0ull;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
           const unsigned long long ob = __shfl_xor_sync(0xffffffffu, best, o);
           const int op = __shfl_xor_sync(0xffffffffu, best_pos, o);
           if (ob < best || (ob == best && op < best_pos)) { best = ob; best_pos = op; }
         }
-        if (t.evict_strategy != EV_LRU && sc_new < best) {
-          st = ST_REJECTED;    // the newcomer scores lower than everything resident
+        const bool all_stamped = __ballot_sync(0xffffffffu, any_free) == 0u;
+        if (all_stamped || (t.evict_strategy != EV_LRU && sc_new < best)) {
+          st = ST_REJECTED;    // the newcomer scores lower than everything resident, or every slot was handed out by this launch
         } else {
           pos = best_pos;
           st = ST_EVICTED_OTHER;
@@ -231,6 +245,7 @@ hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ key
           t.keys[s] = key;
           t.scores[s] = sc_new;
           t.digests[s] = static_cast<unsigned char>(dg);
+          if (t.touch) t.touch[s] = t.epoch;
         }
       }
     }
@@ -441,9 +456,9 @@ inline int warp_grid(long long n, int num_sms) {
 
 }  // namespace
 
-// The table descriptor is passed as a flat array of 13 64-bit words (see recsdk_b200/dynamic/hkv.py):
+// The table descriptor is passed as a flat array of 15 64-bit words (see recsdk_b200/dynamic/hkv.py):
 // keys, scores, digests, locks, values_hbm, values_host, hbm_rows, capacity, num_buckets, row_dim, emb_dim,
-// evict_strategy, size
+// evict_strategy, size, touch (launch stamps, may be 0), epoch (stamp of the current launch)
 static HkvTable unpack(const long long* d) {
   HkvTable t;
   t.keys = reinterpret_cast<unsigned long long*>(d[0]);
@@ -455,6 +470,8 @@ static HkvTable unpack(const long long* d) {
   t.hbm_rows = d[6]; t.capacity = d[7]; t.num_buckets = d[8];
   t.row_dim = static_cast<int>(d[9]); t.emb_dim = static_cast<int>(d[10]); t.evict_strategy = static_cast<int>(d[11]);
   t.size = reinterpret_cast<unsigned long long*>(d[12]);
+  t.touch = reinterpret_cast<unsigned*>(d[13]);
+  t.epoch = static_cast<unsigned>(d[14]);
   return t;
 }
 
@@ -479,7 +496,26 @@ RB_API int rb_hkv_find_or_insert(const long long* desc, const void* keys, long l
   hkv_find_or_insert_kernel<<<warp_grid(n, num_sms), 256, 0, st>>>(
       t, reinterpret_cast<const unsigned long long*>(keys), n, insert, update_score,
       reinterpret_cast<const unsigned long long*>(scores_in), out_slots, reinterpret_cast<unsigned char*>(out_status), ia,
-      ev, status);
+      ev, status, nullptr);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Same with the key count on the device: the first min(n_max, *n_dev) keys are served (no host synchronisation between
+// the de-duplication that produced the count and the probe).
+RB_API int rb_hkv_find_or_insert_n(const long long* desc, const void* keys, long long n_max, const int* n_dev, int insert,
+                                   int update_score, const void* scores_in, long long* out_slots, void* out_status,
+                                   int init_mode, float lower, float upper, float mean, float stddev, float value,
+                                   long long seed, float state_init, void* ev_keys, void* ev_scores, float* ev_values,
+                                   int* ev_count, int ev_cap, int num_sms, int* status, cudaStream_t st) {
+  if (n_max == 0) return 0;
+  HkvTable t = unpack(desc);
+  InitArgs ia{init_mode, lower, upper, mean, stddev, value, static_cast<unsigned long long>(seed), state_init};
+  EvictOut ev{reinterpret_cast<unsigned long long*>(ev_keys), reinterpret_cast<unsigned long long*>(ev_scores), ev_values,
+              ev_count, ev_cap};
+  hkv_find_or_insert_kernel<<<warp_grid(n_max, num_sms), 256, 0, st>>>(
+      t, reinterpret_cast<const unsigned long long*>(keys), n_max, insert, update_score,
+      reinterpret_cast<const unsigned long long*>(scores_in), out_slots, reinterpret_cast<unsigned char*>(out_status), ia,
+      ev, status, n_dev);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -178,21 +178,44 @@ class BatchedDynamicEmbeddingTablesV2(nn.Module):
         EC (pooling NONE): -> [nnz, D]; EBC: -> [B, sum(D_f)]."""
         if self.training:
             self._update_score()
-        outs = []
-        start = 0
         F = len(self.feature_table_map)
+        starts = [0] * (F + 1)
         for f in range(F):
-            n = feature_splits[f]
-            tab = self.tables[self.feature_table_map[f]]
-            ids = indices[start:start + n]
-            if self.pooling_mode == DynamicEmbPoolingMode.NONE:
-                outs.append(_DynamicLookupFn.apply(self._anchor, tab, ids, self.training))
+            starts[f + 1] = starts[f] + feature_splits[f]
+        by_table: Dict[int, List[int]] = {}
+        for f, ti in enumerate(self.feature_table_map):
+            by_table.setdefault(ti, []).append(f)
+        outs: List[Optional[torch.Tensor]] = [None] * F
+        pooled = self.pooling_mode != DynamicEmbPoolingMode.NONE
+        # ONE unique / lookup / update per table and step: the features that share a table are looked up together, so a
+        # growing or evicting table never invalidates slots that another feature of the same step still holds, and the
+        # optimizer steps once per table
+        for ti, feats in by_table.items():
+            tab = self.tables[ti]
+            adjacent = feats == list(range(feats[0], feats[-1] + 1))
+            if adjacent:
+                ids = indices[starts[feats[0]]:starts[feats[-1] + 1]]
             else:
-                off = offsets[f * batch_size:(f + 1) * batch_size + 1] - start
-                outs.append(_DynamicPooledLookupFn.apply(self._anchor, tab, ids, off, batch_size,
-                                                         self.pooling_mode == DynamicEmbPoolingMode.MEAN, self.training, self.output_dtype))
-            start += n
-        if self.pooling_mode == DynamicEmbPoolingMode.NONE:
+                ids = torch.cat([indices[starts[f]:starts[f + 1]] for f in feats])
+            if not pooled:
+                rows = _DynamicLookupFn.apply(self._anchor, tab, ids, self.training)
+                pos = 0
+                for f in feats:
+                    outs[f] = rows[pos:pos + feature_splits[f]]
+                    pos += feature_splits[f]
+                continue
+            if adjacent:
+                off = offsets[feats[0] * batch_size:(feats[-1] + 1) * batch_size + 1] - starts[feats[0]]
+            else:
+                lens = torch.cat([offsets[f * batch_size + 1:(f + 1) * batch_size + 1] - offsets[f * batch_size:(f + 1) * batch_size]
+                                  for f in feats])
+                off = torch.cat([lens.new_zeros(1), lens.cumsum(0)])
+            out = _DynamicPooledLookupFn.apply(self._anchor, tab, ids, off, batch_size,
+                                               self.pooling_mode == DynamicEmbPoolingMode.MEAN, self.training, self.output_dtype)
+            D = self.dims[ti]
+            for k, f in enumerate(feats):
+                outs[f] = out[:, k * D:(k + 1) * D]
+        if not pooled:
             return torch.cat(outs, dim=0).to(self.output_dtype)
         return torch.cat(outs, dim=1).to(self.output_dtype)
 

@@ -29,7 +29,11 @@ class _ShardedDynamicBase(nn.Module):
                  env: Optional[ShardingEnv] = None, device: Optional[torch.device] = None,
                  optimizer_type: OptimizerType = OptimizerType.ROWWISE_ADAGRAD, learning_rate: float = 0.01,
                  eps: float = 1e-8, betas=(0.9, 0.999), weight_decay: float = 0.0, use_index_dedup: bool = False,
-                 output_dtype: torch.dtype = torch.float32, seed: int = 0) -> None:
+                 output_dtype: torch.dtype = torch.float32, seed: int = 0, peer=None, max_ids_per_rank: int = 0,
+                 backend: Optional[str] = None) -> None:
+        """``backend``: ``"fused"`` (push exchange over NVLink peer memory; CUDA with more than one rank, the default there)
+        or ``"collective"`` (``torch.distributed`` all-to-all; any device).  ``max_ids_per_rank`` bounds the ids one rank
+        sends per table and step on the fused backend (0: 1.5 x the largest first batch over all ranks)."""
         super().__init__()
         self.env = env or ShardingEnv(1, 0, None)
         self.world, self.rank, self.pg = self.env.world_size, self.env.rank, self.env.process_group
@@ -57,6 +61,69 @@ class _ShardedDynamicBase(nn.Module):
             opts, [t.name for t in tables], DynamicEmbPoolingMode.NONE, torch.float32, self.device, self.feature_table,
             learning_rate, eps, betas, weight_decay, seed=seed)
         self.output_dtype = output_dtype
+        self.max_ids_per_rank = int(max_ids_per_rank)
+        cuda_multi = self.world > 1 and self.device.type == "cuda"
+        self.backend = backend or ("fused" if cuda_multi and all(t.storage is None for t in self.lookup.tables)
+                                   and all(d % 8 == 0 for d in self.dims) else "collective")
+        if self.backend == "fused" and not cuda_multi:
+            self.backend = "collective"
+        self.peer = peer
+        self._exchanges: Dict[int, object] = {}
+        if self.backend == "fused" and self.peer is None:
+            from ..parallel.comm import PeerGroup
+
+            self.peer = PeerGroup(self.pg, self.device)
+
+    # -- table groups: features of one table are adjacent in the key order -------------------------------
+    def _groups(self, lpk: List[int]):
+        """-> [(table index, first feature, one-past-last feature, first id, number of ids)]"""
+        out, f, start, F = [], 0, 0, len(self.feature_names)
+        while f < F:
+            ti, f1 = self.feature_table[f], f
+            while f1 < F and self.feature_table[f1] == ti:
+                f1 += 1
+            n = sum(lpk[f:f1])
+            out.append((ti, f, f1, start, n))
+            start += n
+            f = f1
+        tabs = [g[0] for g in out]
+        if len(set(tabs)) != len(tabs):
+            raise ValueError("features of one table must be adjacent in the feature order")
+        return out
+
+    def _exchange(self, ti: int, n: int):
+        """The fused exchange of table ``ti``, created on first use (a collective set-up step: every rank arrives here
+        with the same table at its first batch)."""
+        ex = self._exchanges.get(ti)
+        if ex is None:
+            from .fused_exchange import FusedDynamicExchange, owned_capacity
+
+            cap_n = self.max_ids_per_rank
+            if not cap_n:
+                t = torch.tensor([n], dtype=torch.int64, device=self.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.pg)
+                cap_n = int(int(t[0]) * 1.5) + 1024
+            cap_n = (cap_n + 7) // 8 * 8
+            ex = FusedDynamicExchange(self.peer, self.lookup.tables[ti], self.device, cap_n,
+                                      owned_capacity(cap_n, self.world), self.output_dtype)
+            self._exchanges[ti] = ex
+        if n > ex.px.nnz_cap:
+            raise ValueError("table %s: %d ids in one batch, the exchange was sized for %d (max_ids_per_rank)"
+                             % (self.lookup.table_names[ti], n, ex.px.nnz_cap))
+        return ex
+
+    def _fused_sequence_rows(self, features: KeyedJaggedTensor) -> torch.Tensor:
+        from .fused_exchange import _FusedRowsFn
+
+        ids = features.values().to(self.device).long().contiguous()
+        lk = self.lookup
+        if lk.training:
+            lk._update_score()
+        outs = []
+        for ti, _f0, _f1, start, n in self._groups(features.length_per_key()):
+            ex = self._exchange(ti, n)
+            outs.append(_FusedRowsFn.apply(lk._anchor, ex, ids[start:start + n], lk.training))
+        return outs[0] if len(outs) == 1 else torch.cat(outs, dim=0)
 
     # -- rows for every id of the local KJT, in the KJT's own order: [nnz, D] ------------------------
     def _sequence_rows(self, features: KeyedJaggedTensor) -> torch.Tensor:
@@ -66,6 +133,8 @@ class _ShardedDynamicBase(nn.Module):
         lpk = features.length_per_key()
         if self.world == 1:
             return self.lookup(ids, None, lpk, features.stride())
+        if self.backend == "fused":
+            return self._fused_sequence_rows(features)
         W = self.world
         feat = torch.repeat_interleave(torch.arange(F, device=ids.device), torch.tensor(lpk, device=ids.device))
         inv_dedup = None
@@ -141,6 +210,8 @@ class DynamicEmbeddingBagCollection(_ShardedDynamicBase):
     def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
         if self.world == 1:
             return self._forward_local(features)
+        if self.backend == "fused":
+            return self._forward_fused(features)
         rows = self._sequence_rows(features)
         B = features.stride()
         lens = features.lengths().to(self.device)
@@ -157,6 +228,27 @@ class DynamicEmbeddingBagCollection(_ShardedDynamicBase):
             start += n
         feature_dims = [self.dims[t] for t in self.feature_table]
         return KeyedTensor(self.feature_names, feature_dims, torch.cat(outs, dim=1).to(self.output_dtype))
+
+    def _forward_fused(self, features: KeyedJaggedTensor) -> KeyedTensor:
+        """Several ranks on CUDA: one push exchange per table, pooled on the requesting GPU from the received rows."""
+        from .fused_exchange import _FusedPooledFn
+
+        assert features.keys() == self.feature_names
+        B = features.stride()
+        ids = features.values().to(self.device).long().contiguous()
+        offsets = features.offsets().to(self.device).long()
+        lk = self.lookup
+        if lk.training:
+            lk._update_score()
+        outs = []
+        for ti, f0, f1, start, n in self._groups(features.length_per_key()):
+            ex = self._exchange(ti, n)
+            off = (offsets[f0 * B:f1 * B + 1] - start).contiguous()
+            mean = getattr(self.configs[ti], "pooling", PoolingType.SUM) == PoolingType.MEAN
+            outs.append(_FusedPooledFn.apply(lk._anchor, ex, ids[start:start + n], off, f1 - f0, B, mean, lk.training,
+                                             self.output_dtype))
+        feature_dims = [self.dims[t] for t in self.feature_table]
+        return KeyedTensor(self.feature_names, feature_dims, outs[0] if len(outs) == 1 else torch.cat(outs, dim=1))
 
     def _forward_local(self, features: KeyedJaggedTensor) -> KeyedTensor:
         """One rank: pool straight from the unique rows (no per-id row tensor)."""

@@ -128,10 +128,14 @@ class HKVTable(_VariableInterface):
         self.values_host = torch.empty(max(host_rows, 1) * self.row_dim, dtype=torch.float32, pin_memory=True) \
             if host_rows > 0 else None
         self._size = torch.zeros(1, dtype=torch.int64, device=dev)
+        # launch stamps: a slot handed out by a find_or_insert launch is not evicted by a later warp of the same launch
+        self.touch = torch.zeros(cap, dtype=torch.int32, device=dev)
+        self._epoch = 0
         host_ptr = self.values_host.data_ptr() if self.values_host is not None else 0
         self._desc = np.asarray([self.keys.data_ptr(), self.scores.data_ptr(), self.digests.data_ptr(),
                                  self.locks.data_ptr(), self.values_hbm.data_ptr(), host_ptr, hbm, cap, self.num_buckets,
-                                 self.row_dim, self.dim, int(self.evict_strategy), self._size.data_ptr()], dtype=np.int64)
+                                 self.row_dim, self.dim, int(self.evict_strategy), self._size.data_ptr(),
+                                 self.touch.data_ptr(), 0], dtype=np.int64)
 
     def _d(self) -> int:
         return self._desc.ctypes.data
@@ -169,6 +173,9 @@ class HKVTable(_VariableInterface):
             scores = scores.contiguous()
             assert scores.dtype == torch.int64 and scores.numel() == n
         i = self.init
+        if insert:
+            self._epoch = self._epoch % 0x7FFFFFFF + 1       # never 0: freshly allocated stamps are 0
+            self._desc[14] = self._epoch
         rc = _lib.lib().rb_hkv_find_or_insert(
             self._d(), keys.data_ptr(), n, int(insert), int(update_score), _lib.ptr(scores), slots.data_ptr(),
             status.data_ptr(), int(i.mode), i.lower, i.upper, i.mean, i.std_dev, i.value, int(i.seed), i.state_init,
@@ -353,6 +360,7 @@ class HostDynamicTable(_VariableInterface):
         sc = scores.tolist() if scores is not None else [None] * len(ks)
         status = []
         evk, evs, evr = [], [], []
+        stamped = set()
         for k, s in zip(ks, sc):
             if k == EMPTY_KEY:
                 status.append(ST_MISSING)
@@ -360,22 +368,29 @@ class HostDynamicTable(_VariableInterface):
             if k in self.rows:
                 status.append(ST_FOUND)
                 self._touch(k, s, False)
+                stamped.add(k)
                 continue
             if len(self.rows) >= self.capacity:
-                victim = min(self.score, key=self.score.get)
+                # keys handed out by this call are never evicted by it (their slots are in use by the caller)
+                free = [q for q in self.score if q not in stamped]
+                if not free:
+                    status.append(ST_REJECTED)
+                    continue
+                victim = min(free, key=self.score.get)
                 evk.append(victim); evs.append(self.score.pop(victim)); evr.append(self.rows.pop(victim))
                 status.append(ST_EVICTED_OTHER)
             else:
                 status.append(ST_INSERTED)
             self.rows[k] = self._new_row(k)
             self._touch(k, s, True)
+            stamped.add(k)
         ev = None
         if evict_cap > 0:
             ev = (torch.tensor(evk, dtype=torch.int64), torch.tensor(evs, dtype=torch.int64),
                   torch.from_numpy(np.stack(evr)) if evr else torch.zeros(0, self.row_dim),
                   torch.tensor([len(evk)], dtype=torch.int32))
         st = torch.tensor(status, dtype=torch.uint8)
-        return torch.where(st == ST_MISSING, torch.full_like(keys, -1), keys), st, ev
+        return torch.where((st == ST_MISSING) | (st == ST_REJECTED), torch.full_like(keys, -1), keys), st, ev
 
     def find(self, keys: torch.Tensor, update_score: bool = False, scores=None):
         found = torch.tensor([k in self.rows for k in keys.tolist()], dtype=torch.bool)

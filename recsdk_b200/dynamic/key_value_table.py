@@ -222,6 +222,34 @@ class KeyValueTable:
             self._touched = unique_keys if self._touched is None else torch.cat([self._touched, unique_keys])
         return slots, rows
 
+    def lookup_slots_padded(self, keys: torch.Tensor, training: bool = True) -> torch.Tensor:
+        """Slots of a fixed-size key list whose unused entries hold the empty key (-1): no boolean indexing, no host
+        synchronisation (the table must not be able to grow any more: ``init_capacity == max_capacity``).  Admission on the
+        ``admit_threshold``-th sighting works on masks: keys on probation are replaced by the empty key, which every table
+        kernel skips.  Not available for tables with a storage tier below them."""
+        if self.storage is not None:
+            raise NotImplementedError("padded lookups do not serve tables with a storage tier")
+        t = self.table
+        if not training:
+            return t.find(keys)[0]
+        n = keys.numel()
+        empty = torch.full_like(keys, -1)
+        if self.probation is not None and n:
+            _, resident = t.find(keys)
+            cand = torch.where(resident, empty, keys)
+            pslots, _, _ = self.probation.find_or_insert(cand)
+            if isinstance(self.probation, HKVTable):
+                counts = self.probation.scores[pslots.clamp(min=0)]
+            else:
+                counts = torch.tensor([self.probation.score.get(k, 0) for k in cand.tolist()], dtype=torch.int64)
+            ok = (counts >= self.options.admit_threshold) & (pslots >= 0)
+            self.probation.erase(torch.where(ok, cand, empty))
+            keys = torch.where(resident | ok, keys, empty)
+        slots, _status, _ = t.find_or_insert(keys, self._scores_for(n))
+        if self.options.training:
+            self._touched = keys if self._touched is None else torch.cat([self._touched, keys])
+        return slots
+
     def _caching_lookup(self, keys: torch.Tensor) -> torch.Tensor:
         """cache.find -> storage.find for the misses -> insert_and_evict into the cache -> evicted rows back
         to storage (``KeyValueTableCachingFunction.lookup``, ``key_value_table.py:803-864``)."""
@@ -349,4 +377,4 @@ class KeyValueTable:
 
     def take_touched(self) -> Optional[torch.Tensor]:
         t, self._touched = self._touched, None
-        return t
+        return t if t is None else t[t != -1]

@@ -30,7 +30,7 @@ def make_batch(B: int, gen: torch.Generator, alpha: float = 1.2, key_bits: int =
     return Batch(torch.randn(B, 13, generator=gen), kjt, (torch.rand(B, generator=gen) < 0.03).float())
 
 
-def build(device, env, capacity: int, lr: float = 1e-3):
+def build(device, env, capacity: int, lr: float = 1e-3, max_ids_per_rank: int = 0):
     from ..dynamic import (DynamicEmbeddingBagCollection, DynamicEmbInitializerArgs, DynamicEmbInitializerMode, DynamicEmbScoreStrategy,
                            DynamicEmbTableOptions, OptimizerType)
     from ..modules.embedding_configs import EmbeddingBagConfig
@@ -41,7 +41,8 @@ def build(device, env, capacity: int, lr: float = 1e-3):
         initializer_args=DynamicEmbInitializerArgs(mode=DynamicEmbInitializerMode.UNIFORM, lower=-0.01, upper=0.01),
         score_strategy=DynamicEmbScoreStrategy.LFU, init_capacity=capacity, max_capacity=capacity, max_load_factor=0.9, admit_threshold=2)}
     emb = DynamicEmbeddingBagCollection(cfgs, opts, env, device, optimizer_type=OptimizerType.ROWWISE_ADAGRAD, learning_rate=0.01,
-                                        output_dtype=torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32)
+                                        output_dtype=torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32,
+                                        max_ids_per_rank=max_ids_per_rank)
     model = DCNv2Train(DCNv2(emb, 13, [512, 256, DIM], cross_layers=3, low_rank=0, deep_layer_sizes=[1024, 512, 256], device=device))
     dense = [p for n, p in model.named_parameters() if not n.startswith("model.sparse_arch.")]
     opt = torch.optim.Adam(dense, lr=lr, fused=torch.device(device).type == "cuda")
@@ -62,7 +63,7 @@ def run_dcn_bench(args) -> None:
     env = ShardingEnv(world, rank, dist.group.WORLD if world > 1 else None)
     GB = 32768 if not args.small else 1024
     B = GB // world
-    model, opt, emb, dense = build(dev, env, (1 << 27) if not args.small else (1 << 18))
+    model, opt, emb, dense = build(dev, env, (1 << 27) if not args.small else (1 << 18), max_ids_per_rank=F_SPARSE * B * 20)
     model.global_batch_size = GB
     gen = torch.Generator().manual_seed(77 + rank)
     host = [make_batch(B, gen).pin_memory() for _ in range(4)]

@@ -134,9 +134,15 @@ class DLRM(nn.Module):
     def hidden(self, dense_features: torch.Tensor, sparse_features) -> torch.Tensor:
         """Everything up to (excluding) the logit layer."""
         if self.fused:
+            # a sharded collection starts its exchange first (own stream), so the bottom MLP runs while ids and rows travel
+            dist_ctx = self.sparse_arch.input_dist(sparse_features) if getattr(self.sparse_arch, "split_dist", False) else None
             x = dense_ops.cast_pad(dense_features, self.dense_arch.in_padded, self.compute_dtype)
             d = self.dense_arch(x, grad_premasked=True)     # the interaction backward applies the ReLU mask
-            pooled = self._pooled(sparse_features)
+            if dist_ctx is not None:
+                kt = self.sparse_arch.compute_and_output_dist(dist_ctx)
+                pooled = kt.values() if isinstance(kt, KeyedTensor) else kt
+            else:
+                pooled = self._pooled(sparse_features)
             if pooled.dtype != self.compute_dtype:
                 pooled = pooled.to(self.compute_dtype)
             r = dot_interaction(d, pooled, self.F, self.inter_cols, mask_x0=True)

@@ -56,7 +56,7 @@ def make_batch(B: int, gen: torch.Generator, n_items: int = 100_000_000, n_neg: 
     return kjt, off, int(ln.max()), ts.float(), T, keep
 
 
-def build(device, env, cfg=None, capacity: int = 1 << 22, lr: float = 1e-3):
+def build(device, env, cfg=None, capacity: int = 1 << 22, lr: float = 1e-3, max_ids_per_rank: int = 0):
     from ..dynamic import (DynamicEmbeddingCollection, DynamicEmbInitializerArgs, DynamicEmbInitializerMode,
                            DynamicEmbScoreStrategy, DynamicEmbTableOptions, OptimizerType)
     from ..modules.embedding_configs import EmbeddingConfig
@@ -69,7 +69,9 @@ def build(device, env, cfg=None, capacity: int = 1 << 22, lr: float = 1e-3):
         initializer_args=DynamicEmbInitializerArgs(mode=DynamicEmbInitializerMode.NORMAL, mean=0.0, std_dev=0.02),
         score_strategy=DynamicEmbScoreStrategy.TIMESTAMP, init_capacity=capacity, max_capacity=capacity)}
     emb = DynamicEmbeddingCollection(ecfg, opts, env, device, optimizer_type=OptimizerType.ROWWISE_ADAGRAD,
-                                     learning_rate=0.01, use_index_dedup=True)
+                                     learning_rate=0.01, use_index_dedup=True, max_ids_per_rank=max_ids_per_rank,
+                                     # several GPUs: rows and their gradients cross NVLink in the model's compute dtype
+                                     output_dtype=torch.bfloat16 if env.world_size > 1 else torch.float32)
     model = HSTU(cfg, emb, device)
     opt = FusedDenseOptimizer(model, "adam", lr=lr)
     return model, opt
@@ -100,7 +102,8 @@ def measure_hstu_training(args, world: int, rank: int, dev, peer=None) -> dict:
 
     env = ShardingEnv(world, rank, dist.group.WORLD if world > 1 else None)
     B = 32 if not args.small else 4
-    model, opt = build(dev, env, capacity=(1 << 22) if not args.small else (1 << 16))
+    max_len = 4096 if not args.small else 512
+    model, opt = build(dev, env, capacity=(1 << 22) if not args.small else (1 << 16), max_ids_per_rank=B * max_len + 512)
     gen = torch.Generator().manual_seed(1234 + rank)
     shared = torch.Generator().manual_seed(4321)                      # same on every rank: the global batch's lengths
     n_batches = args.steps + max(args.warmup, 3)

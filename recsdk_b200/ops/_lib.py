@@ -152,6 +152,65 @@ STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "peer flag wait timed 
                 3: "index out of bounds", 4: "fixed-size buffer overflow"}
 
 
+class KernelStatusError(RuntimeError):
+    """A kernel of this library reported a problem through the device status word."""
+
+    def __init__(self, code: int) -> None:
+        super().__init__("recsdk_b200 kernel status %d: %s" % (code, STATUS_NAMES.get(code, "?")))
+        self.code = code
+
+
+class PeerTimeoutError(KernelStatusError):
+    """A bounded device-side wait for another rank ran out: the peer is late, has left or has failed.  The collectives
+    of the steps since then did not complete, so the job must stop or recover instead of training on."""
+
+
+class CapacityError(KernelStatusError):
+    """A fixed-size device buffer (an owner's receive list, a long-segment list) was too small for a batch and entries were
+    dropped; results of that step are incomplete.  Raise the bound named in the module's documentation."""
+
+
+def raise_for_status(code: int) -> None:
+    if code == 0:
+        return
+    if code == 2:
+        raise PeerTimeoutError(code)
+    if code == 4:
+        raise CapacityError(code)
+    raise KernelStatusError(code)
+
+
+class StatusPoller:
+    """Asynchronous watch on the status word: ``poll()`` every step costs one small device-to-host copy every ``every``
+    steps and no synchronisation; a non-zero word raises at the next check (at most ``2 * every`` steps late)."""
+
+    def __init__(self, device: torch.device, every: int = 16) -> None:
+        self.device, self.every = device, max(1, int(every))
+        self._host = torch.zeros(8, dtype=torch.int32).pin_memory() if torch.cuda.is_available() else None
+        self._event: Optional[torch.cuda.Event] = None
+        self._n = 0
+
+    def poll(self) -> None:
+        if self._host is None or self.device.type != "cuda":
+            return
+        self._n += 1
+        if self._n % self.every:
+            return
+        if self._event is not None:
+            self._event.synchronize()              # recorded `every` steps ago: long complete
+            code = int(self._host[0])
+            if code != 0:
+                status_tensor(self.device).zero_()
+                self._event = None
+                raise_for_status(code)
+        if torch.cuda.is_current_stream_capturing():
+            return
+        self._host.copy_(status_tensor(self.device), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self._event = ev
+
+
 def status_tensor(device: Optional[torch.device] = None) -> torch.Tensor:
     idx = torch.cuda.current_device() if device is None or device.index is None else device.index
     if idx not in _status:
@@ -166,4 +225,4 @@ def check_status(device: Optional[torch.device] = None, reset: bool = True) -> N
     if code != 0:
         if reset:
             st.zero_()
-        raise RuntimeError("recsdk_b200 kernel status %d: %s" % (code, STATUS_NAMES.get(code, "?")))
+        raise_for_status(code)

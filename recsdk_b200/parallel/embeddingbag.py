@@ -66,6 +66,8 @@ class EmbeddingDistContext:
     segments: Optional[E.SortedSegments] = None
     global_offsets: Optional[torch.Tensor] = None
     one_hot: bool = False
+    served: Optional[torch.cuda.Event] = None
+    sorted: Optional[torch.cuda.Event] = None
 
 
 class _LookupFn(torch.autograd.Function):
@@ -82,6 +84,8 @@ class _LookupFn(torch.autograd.Function):
 
 
 class ShardedEmbeddingBagCollection(nn.Module):
+    split_dist = True      # callers may run ``input_dist`` early and ``compute_and_output_dist(ctx)`` when the rows are needed
+
     def __init__(self, tables: List[EmbeddingBagConfig], plan: Dict[str, ParameterSharding], env: ShardingEnv,
                  device: torch.device, optimizer_spec: Optional[E.OptimizerSpec] = None,
                  peer: Optional[PeerGroup] = None, out_dtype: torch.dtype = torch.bfloat16,
@@ -342,20 +346,21 @@ class ShardedEmbeddingBagCollection(nn.Module):
             dctx.global_offsets = offsets
             return dctx
         px = self._px
-        px.join_sort()                  # a previous step without a backward: its sort must not race the new payload
-        trace.mark("emb.route_scatter")
-        px.route_scatter(idx, offsets, L.T, B, self.dev["shards"], self._key_base_all, self._feature_table_dev,
-                         L.n_tables, want_bags=not one_hot)
-        trace.mark("emb.serve_rows")
-        if one_hot:
-            px.serve_rows(self.dev["key_cumsum"], self.dev["w_offsets"], self._table_dims, self._f_Doff, L.n_tables, L.T,
-                          self.weights, self.out_dtype, L.total_D, True, B)
-        else:
-            px.serve_rows(self.dev["key_cumsum"], self.dev["w_offsets"], self._table_dims, None, L.n_tables, L.T,
-                          self.weights, self.w_dtype, self._row_ld, False, B)
-        if self.training and torch.is_grad_enabled():
-            dctx.segments = px.sort_received(L.key_bits)
-        trace.mark("emb.input_dist_done")
+        px.join()                       # the previous step's update (exchange stream) is ordered before this step
+        trace.mark("emb.input_dist")
+        with px.fork():
+            px.route_scatter(idx, offsets, L.T, B, self.dev["shards"], self._key_base_all, self._feature_table_dev,
+                             L.n_tables, want_bags=not one_hot)
+            if one_hot:
+                px.serve_rows(self.dev["key_cumsum"], self.dev["w_offsets"], self._table_dims, self._f_Doff, L.n_tables, L.T,
+                              self.weights, self.out_dtype, L.total_D, True, B)
+            else:
+                px.serve_rows(self.dev["key_cumsum"], self.dev["w_offsets"], self._table_dims, None, L.n_tables, L.T,
+                              self.weights, self.w_dtype, self._row_ld, False, B)
+            dctx.served = px.mark()
+            if self.training and torch.is_grad_enabled():
+                dctx.segments = px.sort_received(L.key_bits)
+                dctx.sorted = px.mark()
         return dctx
 
     # --------------------------------------------------------------- compute
@@ -368,6 +373,7 @@ class ShardedEmbeddingBagCollection(nn.Module):
             trace.mark("dense.forward")
             return out
         trace.mark("emb.wait_rows")
+        torch.cuda.current_stream(self.device).wait_event(dctx.served)
         self._px.wait(PH_ROWS)
         if dctx.one_hot:
             out = self._out_view[: dctx.B_local]
@@ -394,19 +400,28 @@ class ShardedEmbeddingBagCollection(nn.Module):
         if dctx.segments is None:
             raise RuntimeError("backward through a lookup whose input_dist ran without gradients enabled")
         g = dout if (dout.stride(-1) == 1 and dout.dtype == self.out_dtype) else dout.to(self.out_dtype).contiguous()
-        px.join_sort()
         trace.mark("emb.grad_push")
-        if dctx.one_hot:
-            px.push_grads(g, MODE_ONE_HOT, self._f_D, self._f_Doff, L.T, dctx.B_local)
-        else:
-            px.push_grads(g, MODE_POOLED, self._f_D, self._f_Doff, L.T, dctx.B_local, dctx.offsets,
-                          self.pooling == E.POOL_MEAN)
-        trace.mark("emb.grad_wait")
-        px.wait(PH_GRADS)
-        trace.mark("emb.backward_update")
-        E.tbe_backward_update_rows(L, self.dev, dctx.segments, px.grad_recv, px.g_ld, self._table_dims, self.weights,
-                                   self.state1, self.state2, self.s_offsets, self.opt, self._step, self._bwd_ws)
+        # Exchange stream (already past this step's sort, which must be complete on this rank before any peer can be
+        # released into the next step): push the gradient rows to their owners, wait for everyone's rows, update.  The
+        # caller's stream goes straight on with the rest of the dense backward.
+        with px.fork():
+            if dctx.one_hot:
+                px.push_grads(g, MODE_ONE_HOT, self._f_D, self._f_Doff, L.T, dctx.B_local)
+            else:
+                px.push_grads(g, MODE_POOLED, self._f_D, self._f_Doff, L.T, dctx.B_local, dctx.offsets,
+                              self.pooling == E.POOL_MEAN)
+            px.wait(PH_GRADS)
+            E.tbe_backward_update_rows(L, self.dev, dctx.segments, px.grad_recv, px.g_ld, self._table_dims, self.weights,
+                                       self.state1, self.state2, self.s_offsets, self.opt, self._step, self._bwd_ws)
+            px.mark()
+        if g.is_cuda:
+            g.record_stream(px.stream)
         trace.mark("dense.backward_rest")
+
+    def join_exchange(self) -> None:
+        """Order the current stream after the sparse update that runs on the exchange stream (end of a step)."""
+        if self._px is not None:
+            self._px.join()
 
     def _static_ptr(self, g: torch.Tensor) -> torch.Tensor:
         # under CUDA-graph capture the gradient tensor's address is stable across replays

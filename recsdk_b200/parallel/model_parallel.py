@@ -177,6 +177,9 @@ class DistributedModelParallel(nn.Module):
         """Average dense gradients over the data-parallel ranks (call between backward and step)."""
         if self.world == 1:
             return
+        for m in self.sharded_modules:
+            if hasattr(m, "join_exchange"):
+                m.join_exchange()
         if self._reducer is not None:
             self._reducer.sync()
             return

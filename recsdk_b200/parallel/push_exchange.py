@@ -76,8 +76,11 @@ class PushExchange:
         self.seg_offsets = torch.empty(n + 1, **i32)
         self.num_runs = torch.zeros(1, **i32)
         self.temp = torch.empty(self.temp_bytes, dtype=torch.uint8, device=device)
-        self.sort_stream = torch.cuda.Stream(device)
-        self._sort_done: Optional[torch.cuda.Event] = None
+        # the whole exchange runs on its own stream, so that dense work that does not depend on it (bottom MLP forward
+        # and backward) proceeds on the caller's stream meanwhile; single-block wait kernels precede every kernel that
+        # needs a peer's data, so no full grid ever spins
+        self.stream = torch.cuda.Stream(device)
+        self._pending: Optional[torch.cuda.Event] = None      # last work enqueued on the exchange stream
         self.nnz = 0
         torch.cuda.synchronize(device)
         peer.host_barrier()
@@ -110,6 +113,7 @@ class PushExchange:
                             self.entry_dst.data_ptr(), self.entry_bag.data_ptr() if want_bags else None,
                             self.ctl.ctypes.data, self.loc.data_ptr(), ns, self._status(), self._st())
         _lib.check(rc, "rb_a2a_route")
+        self.wait(PH_COUNTS)
         rc = L.rb_a2a_scatter(self.entry_key.data_ptr(), self.entry_meta.data_ptr(), self.entry_dst.data_ptr(),
                               self.entry_pos.data_ptr(), nnz, self.recv_keys_p.ctypes.data, self.recv_meta_p.ctypes.data,
                               self.owned_cap, self.ctl.ctypes.data, self.loc.data_ptr(), self.world, self.rank, ns,
@@ -120,6 +124,7 @@ class PushExchange:
     def serve_rows(self, key_cumsum: torch.Tensor, w_offsets: torch.Tensor, table_dims: torch.Tensor,
                    f_Doff: Optional[torch.Tensor], n_tables: int, T: int, weights: torch.Tensor, out_dtype: torch.dtype,
                    ld_out: int, one_hot: bool, B: int) -> None:
+        self.wait(PH_PAYLOAD)
         rc = _lib.lib().rb_a2a_serve_rows(
             self.recv_keys.data_ptr(), self.recv_meta.data_ptr(), self.owned_cap, key_cumsum.data_ptr(), w_offsets.data_ptr(),
             table_dims.data_ptr(), _lib.ptr(f_Doff), n_tables, T, weights.data_ptr(), _lib.dtype_code(weights.dtype),
@@ -129,27 +134,35 @@ class PushExchange:
         _lib.check(rc, "rb_a2a_serve_rows")
 
     def sort_received(self, key_bits: int) -> E.SortedSegments:
-        """Unique owned rows and their segments, on a side stream (the result is first needed in the backward).
-        Must be ordered after ``serve_rows`` (which pads the tail of the key list)."""
-        main = torch.cuda.current_stream(self.device)
-        ev = torch.cuda.Event()
-        ev.record(main)
-        with torch.cuda.stream(self.sort_stream):
-            self.sort_stream.wait_event(ev)
-            rc = _lib.lib().rb_sort_segments(self.recv_keys.data_ptr(), self.iota.data_ptr(), self.owned_cap, key_bits,
-                                             self.keys_sorted.data_ptr(), self.pos_sorted.data_ptr(), self.unique.data_ptr(),
-                                             self.counts.data_ptr(), self.seg_offsets.data_ptr(), self.num_runs.data_ptr(),
-                                             self.temp.data_ptr(), self.temp_bytes, self.sort_stream.cuda_stream)
-            _lib.check(rc, "rb_sort_segments")
-            done = torch.cuda.Event()
-            done.record(self.sort_stream)
-        self._sort_done = done
+        """Unique owned rows and their segments (the result is first needed in the backward).  Must be ordered after
+        ``serve_rows``, which pads the tail of the key list."""
+        rc = _lib.lib().rb_sort_segments(self.recv_keys.data_ptr(), self.iota.data_ptr(), self.owned_cap, key_bits,
+                                         self.keys_sorted.data_ptr(), self.pos_sorted.data_ptr(), self.unique.data_ptr(),
+                                         self.counts.data_ptr(), self.seg_offsets.data_ptr(), self.num_runs.data_ptr(),
+                                         self.temp.data_ptr(), self.temp_bytes, self._st())
+        _lib.check(rc, "rb_sort_segments")
         return E.SortedSegments(self.pos_sorted, self.unique, self.seg_offsets, self.num_runs, self.owned_cap)
 
-    def join_sort(self) -> None:
-        if self._sort_done is not None:
-            torch.cuda.current_stream(self.device).wait_event(self._sort_done)
-            self._sort_done = None
+    # ------------------------------------------------------------------ stream choreography
+    def fork(self) -> "torch.cuda.StreamContext":
+        """Context manager: the exchange stream, ordered after everything enqueued so far on the current stream."""
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self.stream.wait_event(ev)
+        return torch.cuda.stream(self.stream)
+
+    def mark(self) -> torch.cuda.Event:
+        """Record (on the exchange stream, inside ``fork()``) an event that ``join`` or a consumer waits for."""
+        ev = torch.cuda.Event()
+        ev.record(self.stream)
+        self._pending = ev
+        return ev
+
+    def join(self) -> None:
+        """The current stream waits for everything enqueued on the exchange stream."""
+        if self._pending is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._pending)
+            self._pending = None
 
     def wait(self, phase: int) -> None:
         rc = _lib.lib().rb_a2a_wait(self.ctl.ctypes.data, self.loc.data_ptr(), phase, self.world, self.rank, self._status(),

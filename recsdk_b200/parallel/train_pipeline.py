@@ -26,9 +26,16 @@ from ..utils import trace  # noqa: E402
 class TrainPipelineBase:
     """No overlap: fetch, copy, step.  Works on CPU as well."""
 
-    def __init__(self, model: torch.nn.Module, optimizer, device: torch.device, return_loss: bool = False) -> None:
+    def __init__(self, model: torch.nn.Module, optimizer, device: torch.device, return_loss: bool = False,
+                 status_poll_steps: int = 16) -> None:
         self._model, self._optimizer, self._device = model, optimizer, device
         self._return_loss = return_loss
+        # Kernels report dropped entries (a receive list that was too small) and peer timeouts through a device status
+        # word; the pipeline watches it without synchronising and raises (CapacityError / PeerTimeoutError) instead of
+        # training on with incomplete gradients.
+        from ..ops import _lib
+
+        self._status = _lib.StatusPoller(device, status_poll_steps) if device.type == "cuda" else None
 
     def _step(self, batch) -> Tuple[torch.Tensor, Any]:
         trace.mark("step.zero_grad")
@@ -50,14 +57,16 @@ class TrainPipelineBase:
     def progress(self, dataloader_iter: Iterator[Batch]):
         batch = next(dataloader_iter).to(self._device)
         loss, out = self._step(batch)
+        if self._status is not None:
+            self._status.poll()
         return (loss, out) if self._return_loss else out
 
 
 class TrainPipelineSparseDist(TrainPipelineBase):
     def __init__(self, model: torch.nn.Module, optimizer, device: torch.device, execute_all_batches: bool = True,
                  apply_jit: bool = False, return_loss: bool = False, cuda_graph: bool = False,
-                 graph_warmup_steps: int = 3) -> None:
-        super().__init__(model, optimizer, device, return_loss)
+                 graph_warmup_steps: int = 3, status_poll_steps: int = 16) -> None:
+        super().__init__(model, optimizer, device, return_loss, status_poll_steps)
         self._execute_all_batches = execute_all_batches
         self._cuda = device.type == "cuda"
         self._memcpy_stream = torch.cuda.Stream(device) if self._cuda else None
@@ -153,4 +162,6 @@ class TrainPipelineSparseDist(TrainPipelineBase):
         with record_function("## forward_backward_step ##"):
             loss, out = self._graph_step(batch) if self._use_graph else self._step(batch)
         self._steps_done += 1
+        if self._status is not None:
+            self._status.poll()
         return (loss, out) if self._return_loss else out

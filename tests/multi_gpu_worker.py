@@ -179,6 +179,64 @@ def varlen_case(world, rank, dev) -> bool:
     return ok
 
 
+def dynamic_case(world, rank, dev) -> bool:
+    """Dynamic hash-table collections (sequence and pooled, admission on the second sighting for the pooled one) on the
+    fused push exchange against the ``torch.distributed`` all-to-all backend: per-step outputs and the exported tables."""
+    from recsdk_b200.dynamic import (DynamicEmbeddingBagCollection, DynamicEmbeddingCollection, DynamicEmbInitializerArgs,
+                                     DynamicEmbInitializerMode, DynamicEmbScoreStrategy, DynamicEmbTableOptions, OptimizerType)
+    from recsdk_b200.modules.embedding_configs import EmbeddingConfig
+
+    env = ShardingEnv(world, rank, dist.group.WORLD)
+    ok = True
+    for cls in (DynamicEmbeddingCollection, DynamicEmbeddingBagCollection):
+        pooled = cls is DynamicEmbeddingBagCollection
+        cfg_cls = EmbeddingBagConfig if pooled else EmbeddingConfig
+
+        def make(backend):
+            cfgs = [cfg_cls(num_embeddings=1 << 16, embedding_dim=16, name="ta", feature_names=["fa", "fb"]),
+                    cfg_cls(num_embeddings=1 << 16, embedding_dim=16, name="tb", feature_names=["fc"])]
+            opts = {c.name: DynamicEmbTableOptions(
+                initializer_args=DynamicEmbInitializerArgs(mode=DynamicEmbInitializerMode.UNIFORM, lower=-0.1, upper=0.1),
+                score_strategy=DynamicEmbScoreStrategy.STEP, init_capacity=1 << 12, max_capacity=1 << 12,
+                admit_threshold=2 if pooled else 0) for c in cfgs}
+            return cls(cfgs, opts, env, dev, optimizer_type=OptimizerType.ADAGRAD, learning_rate=0.1, eps=1e-8, backend=backend,
+                       max_ids_per_rank=4096)
+
+        fused, coll = make("fused"), make("collective")
+        assert fused.backend == "fused" and coll.backend == "collective"
+        g = torch.Generator().manual_seed(1000 + rank)
+        B = 32
+        for step in range(5):
+            lens = torch.randint(0, 5, (3 * B,), generator=g)
+            ids = torch.randint(0, 600, (int(lens.sum()),), generator=g) * 7919 + 13
+            kjt = KeyedJaggedTensor(["fa", "fb", "fc"], ids.to(dev), lengths=lens.to(dev), stride=B)
+            of, oc = fused(kjt), coll(kjt)
+            if pooled:
+                vf, vc = of.values(), oc.values()
+            else:
+                vf = torch.cat([of[k].values() for k in ("fa", "fb", "fc")])
+                vc = torch.cat([oc[k].values() for k in ("fa", "fb", "fc")])
+            err = (vf.float() - vc.float()).abs().max().item() if vf.numel() else 0.0
+            if not err <= 1e-5:
+                ok = False
+                print("rank %d dynamic %s step %d output err %.3e" % (rank, cls.__name__, step, err))
+            w = torch.randn(vf.shape, generator=g).to(dev)
+            (vf * w).sum().backward()
+            (vc * w).sum().backward()
+        torch.cuda.synchronize()
+        _lib.check_status(dev)
+        for name in ("ta", "tb"):
+            ka, va, _ = fused.lookup.export_keys_values(name)
+            kb, vb, _ = coll.lookup.export_keys_values(name)
+            ia, ib = torch.argsort(ka), torch.argsort(kb)
+            same = ka.numel() == kb.numel() and torch.equal(ka[ia], kb[ib])
+            err = (va[ia] - vb[ib]).abs().max().item() if same and ka.numel() else (0.0 if same else float("inf"))
+            print("rank %d dynamic %s table %s: %d keys, max |diff| %.3e" % (rank, cls.__name__, name, ka.numel(), err))
+            if not err <= 1e-5:
+                ok = False
+    return ok
+
+
 def main() -> int:
     world = int(os.environ["WORLD_SIZE"])
     rank = int(os.environ["RANK"])
@@ -188,6 +246,9 @@ def main() -> int:
     cuda_graph = "--graph" in sys.argv
     ok = True
     try:
+        if "--dynamic" in sys.argv:
+            ok = dynamic_case(world, rank, dev)
+            raise StopIteration
         if "--varlen" in sys.argv:
             ok = varlen_case(world, rank, dev)
             raise StopIteration

@@ -132,3 +132,32 @@ def test_assign_accum_and_insert_and_evict():
     newk = _keys(5, seed=8) + (1 << 43)
     assert not t.assign(newk, torch.zeros(5, 4, device=DEV)).any() and t.size() == 50
     _lib.check_status()
+
+
+def test_slots_of_one_launch_are_never_evicted_by_that_launch():
+    """A full bucket under LFU with more new keys than slots in ONE launch: every key that got a slot keeps it (distinct
+    slots, rows hold that key's own initial values), the surplus is rejected - no newcomer evicts a key that an earlier warp
+    of the same launch inserted.  The next launch may evict them again."""
+    t = HKVTable(8, 128, DEV, evict_strategy=EvictStrategy.LFU, max_capacity=128, init=InitializerArgs(mode=InitMode.DEBUG))
+    keys = _keys(300, seed=5)
+    slots, st, _ = t.find_or_insert(keys)                 # all scores equal 1: ties everywhere
+    got = (st == ST_INSERTED) | (st == ST_EVICTED_OTHER)
+    assert int(got.sum()) == 128 and int((st == ST_REJECTED).sum()) == 172
+    assert (slots[~got] == -1).all() and slots[got].unique().numel() == 128
+    rows = t.gather(slots[got])
+    assert torch.equal(rows, (keys[got] % 100000).float()[:, None].expand(-1, 8))
+    # resident keys plus new ones in one launch: whatever the order in which the warps run, every slot the launch returns is
+    # still that key's slot at the end of the launch (distinct, holding that key's row)
+    more = _keys(50, seed=6) + (1 << 43)
+    both = torch.cat([keys[got], more])
+    s2, st2, _ = t.find_or_insert(both)
+    ok2 = s2 >= 0
+    assert int(ok2.sum()) == 128 and s2[ok2].unique().numel() == 128
+    assert torch.equal(t.gather(s2[ok2]), (both[ok2] % 100000).float()[:, None].expand(-1, 8))
+    f2, found2 = t.find(both)
+    assert torch.equal(found2, ok2) and torch.equal(f2[ok2], s2[ok2])
+    # a later launch is free to evict what the earlier one inserted
+    fresh = _keys(50, seed=7) + (1 << 44)
+    s3, st3, _ = t.find_or_insert(fresh, torch.full((50,), 1000, dtype=torch.int64, device=DEV))
+    assert (st3 == ST_EVICTED_OTHER).all() and s3.unique().numel() == 50
+    _lib.check_status()

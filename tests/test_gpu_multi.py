@@ -48,3 +48,11 @@ def test_push_exchange_variable_length_bags():
         pytest.skip("needs at least 2 GPUs")
     p = _run(min(n, 4) if min(n, 4) % 2 == 0 else 2, ["--varlen"])
     assert p.returncode == 0 and "MULTI_GPU_RESULT PASS" in p.stdout
+
+
+def test_fused_dynamic_exchange_matches_collective_backend():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    p = _run(min(n, 4) if min(n, 4) % 2 == 0 else 2, ["--dynamic"])
+    assert p.returncode == 0 and "MULTI_GPU_RESULT PASS" in p.stdout
