@@ -17,7 +17,7 @@ constexpr size_t COUNTS_OFFSET = 0;
 constexpr size_t TEMP_OFFSET = (COUNTS_BYTES + 255) / 256 * 256;
 constexpr size_t TEMP_BYTES = RB_NOALLOC_SCRATCH_BYTES - TEMP_OFFSET;
 
-constexpr int MAX_DEVICES = 64;
+constexpr int MAX_DEVICES = RB_NOALLOC_MAX_DEVICES;
 std::mutex g_mu;
 unsigned char* g_scratch_ptr[MAX_DEVICES] = {nullptr};
 
@@ -26,7 +26,7 @@ int scratch_for_current_device(unsigned char** out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (dev < 0 || dev >= MAX_DEVICES) return RB_NOALLOC_ERR_BAD_ARG;
+  if (dev < 0 || dev >= MAX_DEVICES) return RB_NOALLOC_ERR_DEVICE;
   std::lock_guard<std::mutex> lock(g_mu);
   if (g_scratch_ptr[dev] == nullptr) {
     void* p = nullptr;

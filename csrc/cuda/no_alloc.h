@@ -32,6 +32,8 @@
 #define RB_NOALLOC_ERR_TOO_LARGE (-20)   /* n exceeds RB_NOALLOC_MAX_KEYS */
 #define RB_NOALLOC_ERR_SCRATCH (-21)     /* the sort needs more workspace than the static array holds */
 #define RB_NOALLOC_ERR_BAD_ARG (-22)     /* null pointer / negative n / bad end_bit */
+#define RB_NOALLOC_ERR_DEVICE (-23)      /* the current device's ordinal is RB_NOALLOC_MAX_DEVICES or more */
+#define RB_NOALLOC_MAX_DEVICES 64        /* device ordinals served (one resolved scratch address each) */
 
 #ifdef __cplusplus
 extern "C" {
@@ -41,7 +43,8 @@ extern "C" {
 // unique_out [<= n] distinct keys in sorted order, seg_offsets [n + 1] with seg_offsets[i] the start of
 // run i and seg_offsets[num_runs] = n (entries past num_runs also hold n), num_runs [1].
 // All pointers are device pointers owned by the caller.  Returns 0, a cudaError_t (> 0) or one of the
-// RB_NOALLOC_ERR_* codes (< 0).  Output is identical to rb_sort_segments.
+// RB_NOALLOC_ERR_* codes (< 0).  For n > 0 the output is identical to rb_sort_segments.  For n == 0 this call
+// writes num_runs[0] = 0 and also seg_offsets[0] = 0 (rb_sort_segments leaves seg_offsets untouched then).
 __attribute__((visibility("default")))
 int rb_sort_segments_noalloc(const long long* keys_in, const int* vals_in, long long n, int end_bit,
                              long long* keys_out, int* vals_out, long long* unique_out, int* seg_offsets,

@@ -77,6 +77,32 @@ static void check_restore_args(const I64& ui, const I64& inv, const I64& uo, con
 PYBIND11_MODULE(_C_host, m) {
   m.doc() = "recsdk_b200 host engines";
 
+  // file-system layer under the checkpoint writers (file_system.h)
+  py::class_<LocalFileSystem>(m, "LocalFileSystem")
+      .def(py::init<bool>(), py::arg("strict_owner") = true)
+      .def("create_dir", &LocalFileSystem::create_dir)
+      .def("exists", &LocalFileSystem::exists)
+      .def("list_dir", &LocalFileSystem::list_dir)
+      .def("file_size", &LocalFileSystem::file_size)
+      .def("remove", &LocalFileSystem::remove)
+      .def("write", [](LocalFileSystem& fs, const std::string& path, py::bytes data, bool append) {
+        const std::string d = data;
+        fs.write(path, d.data(), d.size(), append);
+      }, py::arg("path"), py::arg("data"), py::arg("append") = false)
+      .def("read", [](LocalFileSystem& fs, const std::string& path, long long bytes, long long offset) {
+        const size_t n = bytes < 0 ? fs.file_size(path) - static_cast<size_t>(offset) : static_cast<size_t>(bytes);
+        std::string buf(n, '\0');
+        const size_t got = fs.read(path, buf.data(), n, static_cast<size_t>(offset));
+        buf.resize(got);
+        return py::bytes(buf);
+      }, py::arg("path"), py::arg("bytes") = -1, py::arg("offset") = 0);
+  m.def("validate_path", &validate_path_text);
+  m.def("file_system_for", [](const std::string& uri) {
+    std::string path;
+    make_file_system(uri, &path);
+    return path;
+  }, "path part of a checkpoint URI; raises for schemes without a registered file system");
+
   m.def("restore", [](I64 ui, I64 inv, I64 uo, std::vector<int64_t> opt, py::array_t<int64_t, py::array::c_style> out) {
     check_restore_args(ui, inv, uo, opt, out);
     int64_t bad;

@@ -18,6 +18,7 @@
 #include <unordered_set>
 
 #include "common.h"
+#include "file_system.h"
 
 namespace rbh {
 
@@ -167,6 +168,37 @@ class Initializer {
         break;
     }
   }
+  // Counter-based variant: the values are a pure function of (seed, key, column), so they depend neither on the order
+  // in which threads insert keys nor on how the table is sharded, and no generator state is shared between threads.
+  void fill_keyed(float* row, int dim, int64_t key) const {
+    const uint64_t base = mix64(static_cast<uint64_t>(key) ^ (c_.seed * 0x9E3779B97F4A7C15ULL + 0x632BE59BD9B4E019ULL));
+    auto u01 = [&](int col, uint32_t stream) {
+      const uint64_t x = mix64(base ^ (static_cast<uint64_t>(col) << 32) ^ stream);
+      return (static_cast<float>(x >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    };
+    switch (c_.type) {
+      case InitializerType::LINEAR:
+        for (int i = 0; i < dim; ++i) row[i] = dim > 1 ? c_.min + (c_.max - c_.min) * i / (dim - 1) : c_.min;
+        break;
+      case InitializerType::TRUNCATED_NORMAL:
+        for (int i = 0; i < dim; ++i) {
+          float v = 0.f;
+          for (uint32_t t = 0; t < 16; ++t) {
+            v = std::sqrt(-2.f * std::log(u01(i, 1 + 2 * t))) * std::cos(6.2831853f * u01(i, 2 + 2 * t));
+            if (std::fabs(v) <= 2.f) break;
+            v = std::fmin(std::fmax(v, -2.f), 2.f);
+          }
+          row[i] = c_.mean + c_.stddev * v;
+        }
+        break;
+      case InitializerType::UNIFORM:
+        for (int i = 0; i < dim; ++i) row[i] = c_.min + (c_.max - c_.min) * u01(i, 0);
+        break;
+      case InitializerType::CONSTANT:
+        for (int i = 0; i < dim; ++i) row[i] = c_.value;
+        break;
+    }
+  }
  private:
   InitializerConfig c_;
   std::mt19937_64 rng_;
@@ -223,7 +255,7 @@ class HostEmbTable {
         if (p) row = *p;
         else {
           row = pool_.alloc();
-          init_.fill(row, dim_);
+          init_.fill_keyed(row, dim_, keys[i]);          // per-key values: no shared generator under the shard locks
           std::fill(row + dim_, row + row_floats_, 0.f);
           sh.map.insert(keys[i], row);
         }
@@ -373,37 +405,19 @@ class FeatureFilter {
 
 // ============================================================================ files
 namespace fs {
-inline bool exists(const std::string& p) { struct stat st; return ::stat(p.c_str(), &st) == 0; }
-inline void mkdirs(const std::string& p) {
-  std::string cur;
-  for (size_t i = 0; i <= p.size(); ++i) {
-    if (i == p.size() || p[i] == '/') {
-      if (!cur.empty() && !exists(cur) && ::mkdir(cur.c_str(), 0750) != 0 && !exists(cur))
-        throw std::runtime_error("cannot create directory " + cur);
-    }
-    if (i < p.size()) cur.push_back(p[i]);
-  }
+// Every checkpoint file goes through the FileSystem layer (file_system.h): validated paths, no symbolic links, 0750 /
+// 0640 modes, 32 KiB chunked IO.  RECSDK_B200_FS_STRICT=0 relaxes the ownership checks (shared scratch directories).
+inline FileSystem& local() {
+  static LocalFileSystem inst(env_int("RECSDK_B200_FS_STRICT", 1, 0, 1) != 0);
+  return inst;
 }
-inline void check_path(const std::string& p) {
-  if (p.empty() || p.size() > 4096 || p.find("..") != std::string::npos) throw std::invalid_argument("invalid path: " + p);
-}
-// 32 KiB chunked IO like the reference's local file system
+inline bool exists(const std::string& p) { return local().exists(p); }
+inline void mkdirs(const std::string& p) { local().create_dir(p); }
+inline void check_path(const std::string& p) { validate_path_text(p); }
 inline void write_file(const std::string& p, const void* data, size_t bytes, bool append = false) {
-  std::ofstream f(p, std::ios::binary | (append ? std::ios::app : std::ios::trunc));
-  if (!f) throw std::runtime_error("cannot open for write: " + p);
-  const char* c = static_cast<const char*>(data);
-  for (size_t off = 0; off < bytes; off += 32768) f.write(c + off, static_cast<std::streamsize>(std::min<size_t>(32768, bytes - off)));
-  if (!f) throw std::runtime_error("write failed: " + p);
+  local().write(p, data, bytes, append);
 }
-inline std::vector<char> read_file(const std::string& p) {
-  std::ifstream f(p, std::ios::binary | std::ios::ate);
-  if (!f) throw std::runtime_error("cannot open for read: " + p);
-  const std::streamsize n = f.tellg();
-  f.seekg(0);
-  std::vector<char> buf(static_cast<size_t>(n));
-  for (std::streamsize off = 0; off < n; off += 32768) f.read(buf.data() + off, std::min<std::streamsize>(32768, n - off));
-  return buf;
-}
+inline std::vector<char> read_file(const std::string& p) { return local().read_all(p); }
 }  // namespace fs
 
 // One "slice" = <dir>/slice.attribute (raw int64s) + <dir>/slice.data (raw little-endian payload).

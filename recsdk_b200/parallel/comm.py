@@ -63,12 +63,14 @@ class PeerGroup:
 
     PAD_INTS = 64 * 16
 
-    def __init__(self, pg: Optional["dist.ProcessGroup"], device: torch.device, timeout_ms: int = 2000) -> None:
+    def __init__(self, pg: Optional["dist.ProcessGroup"], device: torch.device, timeout_ms: Optional[int] = None) -> None:
         self.pg = pg if pg is not None else (dist.group.WORLD if dist.is_initialized() else None)
         self.device = device
         self.world = dist.get_world_size(self.pg) if self.pg is not None else 1
         self.rank = dist.get_rank(self.pg) if self.pg is not None else 0
-        self.timeout_ms = int(timeout_ms)
+        # limit of every device-side wait for a peer: long enough for the start-up skew of a cold job (first launches page
+        # the kernels in), short enough that a lost rank surfaces as an error within seconds
+        self.timeout_ms = int(timeout_ms if timeout_ms is not None else os.environ.get("RECSDK_B200_PEER_TIMEOUT_MS", "10000"))
         # NVSwitch multicast (multimem.ld_reduce / multimem.st in the all-reduce) is opt-in: RECSDK_B200_MULTIMEM=1.
         # Without it the peer buffers are not bound to a multicast object at all (plain peer loads / stores only), which
         # is also what jobs whose ranks may leave need.

@@ -241,3 +241,44 @@ def test_disk_tier(tmp_path):
     assert np.allclose(got[0], rows[27])
     e.start()
     e.stop()
+
+
+def test_file_system_layer_validation_and_chunked_io(tmp_path):
+    """The checkpoint file-system layer: chunked round trip with offset reads and append, 0750 / 0640 modes, and the
+    refusals (parent-directory components, over-long paths, symbolic links on read and write, group-writable files,
+    unknown URI schemes)."""
+    import os
+    import stat
+
+    H = host()
+    fs = H.LocalFileSystem(True)
+    root = str(tmp_path / "ck" / "a" / "b")
+    fs.create_dir(root)
+    assert stat.S_IMODE(os.stat(root).st_mode) == 0o750
+    payload = bytes(range(256)) * 400                       # 102,400 bytes: several 32 KiB chunks
+    f = root + "/slice.data"
+    fs.write(f, payload)
+    assert fs.file_size(f) == len(payload) and stat.S_IMODE(os.stat(f).st_mode) == 0o640
+    assert fs.read(f) == payload and fs.read(f, 1000, 70000) == payload[70000:71000]
+    fs.write(f, b"tail", True)
+    assert fs.read(f, -1, len(payload)) == b"tail"
+    assert fs.list_dir(root) == ["slice.data"]
+    for bad in (root + "/../x", "a" * 2000, "", root + "/x\ny"):
+        with pytest.raises(ValueError):
+            H.validate_path(bad)
+    link = root + "/link.data"
+    os.symlink(f, link)
+    with pytest.raises(ValueError):
+        fs.read(link)
+    with pytest.raises(RuntimeError):
+        fs.write(link, b"x")
+    os.chmod(f, 0o664)
+    with pytest.raises(ValueError):
+        fs.read(f)                                          # writable by the group: not trusted
+    assert H.LocalFileSystem(False).read(f, 4, 0) == payload[:4]
+    assert H.file_system_for("file://" + root) == root
+    with pytest.raises(ValueError):
+        H.file_system_for("s3://bucket/ck")
+    os.unlink(link)
+    fs.remove(f)
+    assert not fs.exists(f)

@@ -90,3 +90,28 @@ def test_noalloc_rejects_oversize():
     vals = torch.zeros(n, dtype=torch.int32, device=dev)
     rc, _ = _noalloc(fn, keys, vals, 8)
     assert rc == ERR_TOO_LARGE
+
+
+def test_noalloc_empty_batch_and_second_device():
+    """An empty batch writes a run count of zero (and ``seg_offsets[0] = 0``) without touching the other outputs; on a
+    machine with a second GPU the same entry point resolves that device's own copy of the scratch array."""
+    fn = _load()
+    devices = [torch.device("cuda", i) for i in range(min(torch.cuda.device_count(), 2))]
+    for dev in devices:
+        with torch.cuda.device(dev):
+            seg = torch.full((1,), 7, dtype=torch.int32, device=dev)
+            nr = torch.full((1,), 7, dtype=torch.int32, device=dev)
+            rc = fn(None, None, 0, 8, None, None, None, seg.data_ptr(), nr.data_ptr(), torch.cuda.current_stream().cuda_stream)
+            assert rc == 0
+            torch.cuda.synchronize(dev)
+            assert int(nr.item()) == 0 and int(seg.item()) == 0
+            g = torch.Generator(device=dev).manual_seed(11)
+            keys = torch.randint(0, 300, (5000,), generator=g, device=dev, dtype=torch.int64)
+            vals = torch.arange(5000, device=dev, dtype=torch.int32)
+            rc, got = _noalloc(fn, keys, vals, 9)
+            assert rc == 0
+            want = _reference(keys, vals, 9)
+            torch.cuda.synchronize(dev)
+            runs = int(want[4].item())
+            assert int(got[4].item()) == runs and torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+            assert torch.equal(got[3][:runs + 1], want[3][:runs + 1])
