@@ -361,6 +361,18 @@ def main() -> None:
         dist.all_reduce(tl)                      # each rank's loss is its share of the global-batch mean
         last = float(tl[0])
     used_graph = pipe._graph is not None
+    selfcheck = None
+    if world > 1:
+        # correctness evidence next to the multi-GPU number: the fused backend against the library-collective backend
+        try:
+            from recsdk_b200.parallel.selfcheck import run_selfcheck
+
+            selfcheck = run_selfcheck(env, dmp.peer, dev)
+        except Exception as e:  # noqa: BLE001
+            import traceback
+
+            traceback.print_exc()
+            selfcheck = {"ok": False, "error": "%s: %s" % (type(e).__name__, e)}
     extras = {}
     if not args.no_extra and not args.small and args.rows_scale == 1.0:
         # the other half of the headline metric (HSTU training tokens/s at the same N) and, on one GPU, the ranking
@@ -390,6 +402,8 @@ def main() -> None:
                             "overlapped with the previous step) and a D2H copy of that step's loss, read on the host one step later"},
             "gpu_launches": int(launches), "final_loss": last, "clocks": clocks, "impl": "ours",
         }
+        if selfcheck is not None:
+            out["selfcheck"] = selfcheck
         out.update(extras)
         print(json.dumps(out))
     if world > 1:

@@ -337,6 +337,22 @@ PYBIND11_MODULE(_C_host, m) {
         auto f = new SwapInfoFuture{mg.compute_swap_info_async(t, std::move(k), step)};
         return std::unique_ptr<SwapInfoFuture>(f);
       })
+      .def("plan_batch_async", [](EmbcacheManager& mg, size_t t, I64 keys, int64_t step, bool count_stats, bool stamp, int64_t now) {
+        std::vector<int64_t> k(keys.data(), keys.data() + keys.size());
+        auto f = new SwapInfoFuture{mg.plan_batch_async(t, std::move(k), step, count_stats, stamp, now)};
+        return std::unique_ptr<SwapInfoFuture>(f);
+      })
+      // rows of `keys` written into caller memory (a pinned staging buffer): dst = address of [len(keys), row_floats] floats
+      .def("embedding_lookup_into", [](EmbcacheManager& mg, size_t t, I64 keys, uintptr_t dst, int64_t capacity_rows) {
+        if (keys.size() > capacity_rows) throw std::invalid_argument("staging buffer too small for this swap-in");
+        py::gil_scoped_release rel;
+        mg.embedding_lookup(t, keys.data(), keys.size(), reinterpret_cast<float*>(dst));
+      })
+      // host InsertOrAssign straight from caller memory (the pinned buffer a device-to-host copy filled)
+      .def("embedding_update_from", [](EmbcacheManager& mg, size_t t, I64 keys, uintptr_t src) {
+        py::gil_scoped_release rel;
+        mg.embedding_update(t, keys.data(), keys.size(), reinterpret_cast<const float*>(src));
+      })
       .def("embedding_lookup", [](EmbcacheManager& mg, size_t t, I64 keys) {
         const int rf = mg.host_table(t).row_floats();
         py::array_t<float> rows({static_cast<py::ssize_t>(keys.size()), static_cast<py::ssize_t>(rf)});

@@ -495,6 +495,36 @@ class EmbcacheManager {
         si.swapout_keys.size(), tc.ms());
     return si;
   }
+  // One native call per table and batch: distinct keys with their counts (admission statistics, last-seen timestamps),
+  // then the swap plan.  Replaces a host-side unique + per-key bookkeeping in the caller.
+  SwapInfo plan_batch(size_t t, std::vector<int64_t> keys, int64_t step, bool count_stats, bool stamp, int64_t now) {
+    if ((count_stats || stamp) && !keys.empty()) {
+      FlatMap<int64_t> cnt(keys.size() * 2 + 16);
+      std::vector<int64_t> uniq;
+      uniq.reserve(keys.size());
+      for (int64_t k : keys) {
+        int64_t* c = cnt.find(k);
+        if (c) ++*c;
+        else { cnt.insert(k, 1); uniq.push_back(k); }
+      }
+      if (count_stats) {
+        std::vector<int64_t> counts(uniq.size());
+        for (size_t i = 0; i < uniq.size(); ++i) counts[i] = *cnt.find(uniq[i]);
+        statistics_key_count(t, uniq.data(), static_cast<int64_t>(uniq.size()), counts.data(), nullptr);
+      }
+      if (stamp) {
+        std::vector<int64_t> ts(uniq.size(), now);
+        record_timestamp(t, uniq.data(), static_cast<int64_t>(uniq.size()), ts.data());
+      }
+    }
+    return compute_swap_info(t, std::move(keys), step);
+  }
+  std::future<SwapInfo> plan_batch_async(size_t t, std::vector<int64_t> keys, int64_t step, bool count_stats, bool stamp,
+                                         int64_t now) {
+    return pool_.submit([this, t, keys = std::move(keys), step, count_stats, stamp, now]() mutable {
+      return plan_batch(t, std::move(keys), step, count_stats, stamp, now);
+    });
+  }
   std::future<SwapInfo> compute_swap_info_async(size_t t, std::vector<int64_t> keys, int64_t step) {
     return pool_.submit([this, t, keys = std::move(keys), step]() mutable { return compute_swap_info(t, std::move(keys), step); });
   }

@@ -156,6 +156,17 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
                               for t in module.tables]
         self.swap_step = 0
         self.stats = {"swap_in": 0, "swap_out": 0}
+        # asynchronous swap state (CUDA): memcpy stream, pinned staging ring, host worker for lookups / updates
+        from concurrent.futures import ThreadPoolExecutor
+
+        self._memcpy_stream = torch.cuda.Stream(torch.device(device)) if torch.device(device).type == "cuda" else None
+        self._host_pool = ThreadPoolExecutor(max_workers=2)
+        self._pinned: Dict[tuple, torch.Tensor] = {}
+        self._out_busy: Dict[tuple, object] = {}
+        self._in_busy: Dict[tuple, object] = {}
+        self._upd_fut: List[Optional[object]] = [None] * len(module.tables)
+        self._step_done = self._step_done_prev = None
+        self._swap_ready = None
         with torch.no_grad():
             for ti, t in enumerate(self.tables):
                 self.embedding_bags[t.name].weight.zero_()
@@ -200,6 +211,165 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
             w = self.embedding_bags[self.tables[ti].name].weight.data
             w[0].fill_(self.default_value[ti])
 
+    # -- asynchronous swap (CUDA): pinned staging, copies and row kernels on a memcpy stream ---------------------
+    RING = 3                                     # staging sets in rotation: a set is reused three batches later
+
+    def _async_ready(self) -> bool:
+        return self.device.type == "cuda" and (self.world == 1 or self.input_pg is not None)
+
+    def _staging(self, kind: str, ti: int, slot: int, rows: int) -> torch.Tensor:
+        """Pinned host buffer ``[>= rows, row_floats]`` of table ``ti`` (grown geometrically, never per step)."""
+        key = (kind, ti, slot)
+        buf = self._pinned.get(key)
+        if buf is None or buf.shape[0] < rows:
+            rf = self.tables[ti].embedding_dim * (1 + self.optim_num)
+            cap = max(1024, int(rows * 1.5))
+            buf = torch.empty(cap, rf, dtype=torch.float32).pin_memory()
+            self._pinned[key] = buf
+        return buf
+
+    def record_batch_keys_async(self, lengths: torch.Tensor, ids_np: np.ndarray):
+        """Start the per-table batch planning on the native pool (distinct keys + counts for the admission filter,
+        last-seen timestamps, swap plan).  -> (futures, positions of each table's ids in ``ids_np``)."""
+        self.swap_step += 1
+        W, F, B = lengths.shape
+        seg = lengths.sum(dim=2).reshape(-1).cpu().numpy()
+        seg_off = np.concatenate([[0], np.cumsum(seg)])
+        tab_pos: List[List[np.ndarray]] = [[] for _ in self.tables]
+        for s_ in range(W):
+            for f in range(F):
+                tab_pos[self.feature_table[f]].append(np.arange(seg_off[s_ * F + f], seg_off[s_ * F + f + 1]))
+        pos = [np.concatenate(p) if p else np.zeros(0, dtype=np.int64) for p in tab_pos]
+        now = int(time.time())
+        futs = [self.manager.plan_batch_async(ti, ids_np[p], self.swap_step, self.admit[ti], self.evict[ti], now)
+                for ti, p in enumerate(pos)]
+        return futs, pos
+
+    def host_embedding_update_async(self, ti: int, keys: np.ndarray, staged: torch.Tensor, copied: "torch.cuda.Event"):
+        """Host InsertOrAssign of swapped-out rows once their device-to-host copy has landed in the pinned buffer."""
+        prev = self._upd_fut[ti]
+
+        def run():
+            if prev is not None:
+                prev.result()
+            copied.synchronize()
+            self.manager.embedding_update_from(ti, keys, staged.data_ptr())
+
+        fut = self._host_pool.submit(run)
+        self._upd_fut[ti] = fut
+        return fut
+
+    def host_embedding_lookup_async(self, ti: int, keys: np.ndarray, staged: torch.Tensor):
+        """Host FindOrInsert of the rows a batch swaps in, written into the pinned buffer; ordered after every earlier
+        update of the table (a key evicted by the previous batch may come straight back)."""
+        prev = self._upd_fut[ti]
+
+        def run():
+            if prev is not None:
+                prev.result()
+            self.manager.embedding_lookup_into(ti, keys, staged.data_ptr(), staged.shape[0])
+
+        return self._host_pool.submit(run)
+
+    def apply_swap_async(self, ti: int, info: Dict[str, np.ndarray], slot: int) -> None:
+        """Enqueue the swap traffic of one table on the memcpy stream (the caller has made it current): victims
+        gather -> pinned (D2H) -> host update on the pool; host lookup -> pinned -> H2D -> scatter."""
+        dev = self.device
+        so_k, so_o = info["swapout_keys"], info["swapout_offs"]
+        if so_k.size:
+            rows = self._gather_cache_rows(ti, torch.from_numpy(so_o).to(dev, non_blocking=True))
+            st = self._staging("out", ti, slot, so_k.size)
+            busy = self._out_busy.get((ti, slot))
+            if busy is not None:
+                busy.result()                                   # the update that last read this staging set is done
+            st[: so_k.size].copy_(rows, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._out_busy[(ti, slot)] = self.host_embedding_update_async(ti, so_k, st, ev)
+            self.stats["swap_out"] += int(so_k.size)
+        si_k, si_o = info["swapin_keys"], info["swapin_offs"]
+        if si_k.size:
+            st = self._staging("in", ti, slot, si_k.size)
+            busy = self._in_busy.get((ti, slot))
+            if busy is not None:
+                busy.synchronize()                              # the H2D copy that last read this staging set is done
+            self.host_embedding_lookup_async(ti, si_k, st).result()
+            rows = st[: si_k.size].to(dev, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._in_busy[(ti, slot)] = ev
+            self._scatter_cache_rows(ti, torch.from_numpy(si_o).to(dev, non_blocking=True), rows)
+            self.stats["swap_in"] += int(si_k.size)
+        if self.admit[ti]:
+            w = self.embedding_bags[self.tables[ti].name].weight.data
+            w[0].fill_(self.default_value[ti])
+
+    def post_input_dist_async(self, lengths: torch.Tensor, ids_host: torch.Tensor):
+        """Ids on the host -> device-cache slots, with the swap traffic on the memcpy stream.  The stream first waits for
+        the step that last trained the victims (``mark_step_done``), so it can run beside the current step's compute."""
+        ids_np = ids_host.numpy().astype(np.int64, copy=False)
+        lengths = lengths.cpu()
+        futs, pos = self.record_batch_keys_async(lengths, ids_np)
+        slot = self.swap_step % self.RING
+        out = np.empty_like(ids_np)
+        with torch.cuda.stream(self._memcpy_stream):
+            # Victims were last used by batch (this - 2) or earlier: wait for THAT step's backward, not for the step that
+            # is running now, whose rows the slot allocator protects.
+            if self._step_done_prev is not None:
+                self._memcpy_stream.wait_event(self._step_done_prev)
+            for ti, p in enumerate(pos):
+                info = futs[ti].get()
+                self.apply_swap_async(ti, info, slot)
+                out[p] = info["batch_offs"]
+            slots = torch.from_numpy(out).pin_memory().to(self.device, non_blocking=True)
+            lengths_dev = lengths.pin_memory().to(self.device, non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record()
+        self._swap_ready = ready
+        return slots, lengths_dev
+
+    def mark_step_done(self) -> None:
+        """Called by the pipeline after a step's backward is enqueued.  The swap that is planned next (for the batch after
+        the one now running) waits for the step BEFORE this one: that is the last step that can have trained its victims."""
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self._step_done_prev, self._step_done = self._step_done, ev
+
+    def wait_swap(self) -> None:
+        """The compute stream waits for the scatter of the batch it is about to look up."""
+        if self._swap_ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._swap_ready)
+            self._swap_ready = None
+
+    def drain_host_updates(self) -> None:
+        """Block until every pending host update has been applied (before a save, an eviction or a flush)."""
+        for f in self._upd_fut:
+            if f is not None:
+                f.result()
+
+    def prefetch_async(self, features_dev: KeyedJaggedTensor, features_host: KeyedJaggedTensor) -> None:
+        """Pipelined ``prefetch``: input distribution on the host copy of the batch (native bucketize; gloo exchange with
+        more than one rank), swap planning on the native pool, swap traffic on the memcpy stream - nothing here makes the
+        host wait for the compute stream."""
+        F, B = len(self.feature_names), features_host.stride()
+        new_lengths, new_ids, _perm = self._bucketize(features_host)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            recv_lengths = torch.empty_like(new_lengths)
+            dist.all_to_all_single(recv_lengths, new_lengths.contiguous(), group=self.input_pg)
+            in_splits = new_lengths.sum(dim=1).tolist()
+            out_splits = recv_lengths.view(self.world, -1).sum(dim=1).tolist()
+            recv_ids = new_ids.new_empty(int(sum(out_splits)))
+            dist.all_to_all_single(recv_ids, new_ids, out_splits, in_splits, group=self.input_pg)
+            new_lengths, new_ids = recv_lengths, recv_ids
+        lengths = new_lengths.view(self.world, F, B)
+        slots, lengths_dev = self.post_input_dist_async(lengths, new_ids)
+        orig = features_dev.lengths().view(F, B)
+        self._prepared[id(features_dev)] = (lengths_dev, slots, B, orig, self._swap_ready)
+        self._swap_ready = None
+
     def post_input_dist(self, lengths: torch.Tensor, ids: torch.Tensor):
         """Raw ids (this rank's share of the global batch) -> device-cache slots."""
         self.swap_step += 1
@@ -230,6 +400,15 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
             out[p] = info["batch_offs"]
         return torch.from_numpy(out).to(ids.device)
 
+    def forward(self, features: KeyedJaggedTensor) -> KeyedTensor:
+        ctx = self._prepared.get(id(features))
+        if ctx is not None and self.device.type == "cuda":
+            cur = torch.cuda.current_stream(self.device)
+            for t in ctx[:2]:                      # produced on a side stream, consumed here
+                if isinstance(t, torch.Tensor) and t.is_cuda:
+                    t.record_stream(cur)
+        return super().forward(features)
+
     def _apply_update(self, ti: int, rows: torch.Tensor, grads: torch.Tensor) -> None:
         if self.admit[ti]:                                   # slot 0 = "not admitted": never trained
             keep = rows != 0
@@ -238,6 +417,7 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
 
     # -- eviction / checkpoint helpers -------------------------------------------------------------------
     def host_embedding_evict(self) -> Dict[str, int]:
+        self.drain_host_updates()
         out = {}
         for ti, t in enumerate(self.full_tables):
             if self.evict[ti]:
@@ -247,6 +427,9 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
     @torch.no_grad()
     def embedding_to_host(self) -> None:
         """Write every device-resident row back to the host table (before a save)."""
+        self.drain_host_updates()
+        if self._memcpy_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self._memcpy_stream)
         for ti in range(len(self.tables)):
             keys, offs = self.manager.resident(ti)
             if keys.size:

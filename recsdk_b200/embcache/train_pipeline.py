@@ -1,19 +1,34 @@
 """Training pipeline for models with multi-tier (embcache) tables.
 
-While batch i runs forward / backward on the compute stream, batch i+1 is copied to the device, distributed to
-its owner ranks, its swap plan is computed on the native thread pool, the victims leave for host memory and the
-incoming rows arrive - all on side streams.  Every ``evict_step_interval`` steps the feature filter evicts stale
-features from all tiers.  Reference: ``torchrec_embcache/distributed/train_pipeline.py:226-293`` (signature),
+Stages per call of ``progress`` (CUDA), in the order they are issued:
+
+1. the compute stream waits for the swap of batch i (one event) and gets forward / backward / optimizer of batch i;
+2. while the GPU works on that, the host takes batch i+1: pinned host-to-device copy on the copy stream, input
+   distribution on the host copy of the ids (native bucketize; gloo exchange with several ranks), per-table batch
+   planning on the native thread pool (distinct keys, admission statistics, swap plan);
+3. the swap traffic of batch i+1 goes to the memcpy stream, which first waits for the backward of batch i-1 (the last
+   step that may have trained a victim): victims gather -> pinned buffer (``cudaMemcpyAsync`` D2H) -> host
+   ``embedding_update`` on a worker; host ``embedding_lookup`` -> pinned buffer -> ``cudaMemcpyAsync`` H2D -> scatter.
+
+The slot allocator never hands a batch a slot that the current or the previous batch uses, so the swap of batch i+1
+touches rows that batch i does not read or train.  Every ``evict_step_interval`` steps the feature filter evicts stale
+features from all tiers.  Without CUDA (or with several ranks and no host process group) the swap runs synchronously
+inside ``prefetch``.  ``LOCAL_UNIQUE_PARALLEL_BATCH_NUM`` (1..24, default 2) is validated like the reference does and
+bounds how many batches the host stages may run ahead.
+Reference: ``torchrec_embcache/distributed/train_pipeline.py:226-293`` (signature, environment check ``:274-290``),
 ``:574-633`` (fill), ``:656-731`` (progress), swap stages ``:424-537``.
 """
 from __future__ import annotations
 
+import os
 from typing import Any, Callable, Iterator, List, Optional
 
 import torch
 
 from ..parallel.train_pipeline import TrainPipelineBase
 from .configs import MIN_EVICT_STEP_INTERVAL
+
+MAX_LOCAL_UNIQUE_PARALLEL_BATCH_NUM = 24
 from .embedding_bag import EmbCacheShardedEmbeddingBagCollection
 
 
@@ -41,9 +56,18 @@ class EmbCacheTrainPipelineSparseDist(TrainPipelineBase):
         self._next = None
         self._exhausted = False
         self._steps = 0
+        raw = os.environ.get("LOCAL_UNIQUE_PARALLEL_BATCH_NUM", "2")
+        if not raw.isdigit():
+            raise ValueError("Param error, LOCAL_UNIQUE_PARALLEL_BATCH_NUM must be a number, but got %s." % raw)
+        self.local_unique_parallel_batch_num = int(raw)
+        if not 1 <= self.local_unique_parallel_batch_num <= MAX_LOCAL_UNIQUE_PARALLEL_BATCH_NUM:
+            raise ValueError("Param error: LOCAL_UNIQUE_PARALLEL_BATCH_NUM must be in [1, %d], but got %s."
+                             % (MAX_LOCAL_UNIQUE_PARALLEL_BATCH_NUM, raw))
+        self._async = self._cuda and all(m._async_ready() for m in self._mods)
 
     def _fetch(self, it: Iterator):
-        """Next batch: H2D copy on the copy stream, then the prefetch (input dist + swap) for every embcache module."""
+        """Next batch: H2D copy on the copy stream, then input dist + swap for every embcache module.  On the asynchronous
+        path nothing here waits for the compute stream, so it is called right after a step has been enqueued."""
         try:
             host_batch = next(it)
         except StopIteration:
@@ -52,30 +76,51 @@ class EmbCacheTrainPipelineSparseDist(TrainPipelineBase):
         if self._cuda:
             with torch.cuda.stream(self._copy_stream):
                 batch = host_batch.to(self._device, non_blocking=True)
-            torch.cuda.current_stream(self._device).wait_stream(self._copy_stream)
-            batch.record_stream(torch.cuda.current_stream(self._device))
+                copied = torch.cuda.Event()
+                copied.record()
         else:
-            batch = host_batch.to(self._device)
+            batch, copied = host_batch.to(self._device), None
         feats = self._features_of(batch)
+        if self._async:
+            host_feats = self._features_of(host_batch)
+            for m in self._mods:
+                m.prefetch_async(feats, host_feats)
+        else:
+            if copied is not None:
+                torch.cuda.current_stream(self._device).wait_event(copied)
+                batch.record_stream(torch.cuda.current_stream(self._device))
+                copied = None
+            for m in self._mods:
+                m.prefetch(feats)
+        return batch, copied
+
+    def _run_step(self, batch):
+        (self._zero or self._optimizer.zero_grad)()
+        loss, out = (self._fwd or self._model)(batch)
+        (self._bwd(loss) if self._bwd else loss.backward())
         for m in self._mods:
-            m.prefetch(feats)
-        return batch
+            m.mark_step_done()
+        sync = getattr(self._model, "sync_dense_grads", None)
+        if sync is not None:
+            sync()
+        self._optimizer.step()
+        return loss, out
 
     def progress(self, dataloader_iter: Iterator):
         if self._next is None and not self._exhausted:
             self._next = self._fetch(dataloader_iter)
         if self._next is None:
             raise StopIteration
-        batch = self._next
-        # batch i+1: copy, distribute and swap while batch i computes
-        self._next = self._fetch(dataloader_iter) if not self._exhausted else None
-        (self._zero or self._optimizer.zero_grad)()
-        loss, out = (self._fwd or self._model)(batch)
-        (self._bwd(loss) if self._bwd else loss.backward())
-        sync = getattr(self._model, "sync_dense_grads", None)
-        if sync is not None:
-            sync()
-        self._optimizer.step()
+        batch, copied = self._next
+        if self._async:
+            if copied is not None:
+                torch.cuda.current_stream(self._device).wait_event(copied)
+                batch.record_stream(torch.cuda.current_stream(self._device))
+            loss, out = self._run_step(batch)                  # batch i is on the GPU's queue ...
+            self._next = self._fetch(dataloader_iter) if not self._exhausted else None   # ... the host turns to batch i+1
+        else:
+            self._next = self._fetch(dataloader_iter) if not self._exhausted else None
+            loss, out = self._run_step(batch)
         self._steps += 1
         if self._evict_every and self._steps % self._evict_every == 0:
             for m in self._mods:

@@ -13,6 +13,7 @@ Reference counterparts: ``cust_op/ascendc_op/ai_core_op/lccl/v220/op_kernel/{gat
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import numpy as np
@@ -82,6 +83,8 @@ class PushExchange:
         self.stream = torch.cuda.Stream(device)
         self._pending: Optional[torch.cuda.Event] = None      # last work enqueued on the exchange stream
         self.nnz = 0
+        self.deterministic = os.environ.get("LCCL_DETERMINISTIC", "0").lower() in ("1", "true")
+        self._det_pos = self._det_meta = self._det_keys = None
         torch.cuda.synchronize(device)
         peer.host_barrier()
 
@@ -135,11 +138,29 @@ class PushExchange:
 
     def sort_received(self, key_bits: int) -> E.SortedSegments:
         """Unique owned rows and their segments (the result is first needed in the backward).  Must be ordered after
-        ``serve_rows``, which pads the tail of the key list."""
-        rc = _lib.lib().rb_sort_segments(self.recv_keys.data_ptr(), self.iota.data_ptr(), self.owned_cap, key_bits,
-                                         self.keys_sorted.data_ptr(), self.pos_sorted.data_ptr(), self.unique.data_ptr(),
-                                         self.counts.data_ptr(), self.seg_offsets.data_ptr(), self.num_runs.data_ptr(),
-                                         self.temp.data_ptr(), self.temp_bytes, self._st())
+        ``serve_rows``, which pads the tail of the key list.
+
+        Positions in the receive list are handed out by atomics, so the order of the entries of one row - and with it the
+        order of the floating-point additions of its gradient - changes from run to run.  ``LCCL_DETERMINISTIC=1`` (the
+        reference's switch for its fused gradient all-to-all, ``lccl/v220/op_kernel/all_uss_deterministic.h``) first
+        orders the entries by (source rank, feature, position in the source batch), then sorts stably by row: every
+        row's gradients are then summed in an order that depends on the batch only."""
+        L = _lib.lib()
+        keys_in, vals_in = self.recv_keys, self.iota
+        if self.deterministic:
+            if self._det_pos is None:
+                self._det_meta = torch.empty_like(self.recv_meta)
+                self._det_pos = torch.empty_like(self.iota)
+            rc = L.rb_sort_pairs_i64_i32(self.recv_meta.data_ptr(), self.iota.data_ptr(), self.owned_cap, 56,
+                                         self._det_meta.data_ptr(), self._det_pos.data_ptr(), self.temp.data_ptr(),
+                                         self.temp_bytes, self._st())
+            _lib.check(rc, "rb_sort_pairs_i64_i32")
+            self._det_keys = self.recv_keys.index_select(0, self._det_pos.long())
+            keys_in, vals_in = self._det_keys, self._det_pos
+        rc = L.rb_sort_segments(keys_in.data_ptr(), vals_in.data_ptr(), self.owned_cap, key_bits,
+                                self.keys_sorted.data_ptr(), self.pos_sorted.data_ptr(), self.unique.data_ptr(),
+                                self.counts.data_ptr(), self.seg_offsets.data_ptr(), self.num_runs.data_ptr(),
+                                self.temp.data_ptr(), self.temp_bytes, self._st())
         _lib.check(rc, "rb_sort_segments")
         return E.SortedSegments(self.pos_sorted, self.unique, self.seg_offsets, self.num_runs, self.owned_cap)
 

@@ -11,8 +11,9 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(nproc, extra, wire="fp32"):
+def _run(nproc, extra, wire="fp32", **more_env):
     env = dict(os.environ)
+    env.update(more_env)
     env["RECSDK_B200_ALLREDUCE_WIRE"] = wire     # equality tests keep fp32 on the wire; bf16 has its own case
     env.setdefault("NCCL_NVLS_ENABLE", "0")
     env.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -55,4 +56,14 @@ def test_fused_dynamic_exchange_matches_collective_backend():
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     p = _run(min(n, 4) if min(n, 4) % 2 == 0 else 2, ["--dynamic"])
+    assert p.returncode == 0 and "MULTI_GPU_RESULT PASS" in p.stdout
+
+
+def test_sharded_dlrm_deterministic_gradient_order():
+    """``LCCL_DETERMINISTIC=1``: the owner orders its received entries by (source, feature, position) before the stable sort
+    by row, so the sums do not depend on the arrival order; results still match the single-GPU run."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    p = _run(2, [], LCCL_DETERMINISTIC="1")
     assert p.returncode == 0 and "MULTI_GPU_RESULT PASS" in p.stdout
