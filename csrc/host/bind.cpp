@@ -394,7 +394,10 @@ PYBIND11_MODULE(_C_host, m) {
       })
       .def("save", [](EmbcacheManager& mg, const std::string& p, int rank, bool inc) { py::gil_scoped_release rel; mg.save(p, rank, inc); })
       .def("merge_files", [](EmbcacheManager& mg, const std::string& p, int world) { py::gil_scoped_release rel; mg.merge_files(p, world); })
-      .def("load", [](EmbcacheManager& mg, const std::string& p, int rank, int world) { py::gil_scoped_release rel; mg.load(p, rank, world); });
+      .def("load", [](EmbcacheManager& mg, const std::string& p, int rank, int world, bool incremental) {
+        py::gil_scoped_release rel;
+        mg.load(p, rank, world, incremental);
+      }, py::arg("path"), py::arg("rank"), py::arg("world"), py::arg("incremental") = false);
 
   // ------------------------------------------------------------------ kv cache
   py::class_<KVPageAllocator>(m, "KVPageAllocator")

@@ -11,6 +11,10 @@
 #include <sys/types.h>
 
 #include <algorithm>
+#include <cstdlib>
+#include <unordered_map>
+#include <thread>
+#include <condition_variable>
 #include <cmath>
 #include <fstream>
 #include <random>
@@ -211,23 +215,123 @@ class Initializer {
 class EmbMemoryPool {
  public:
   explicit EmbMemoryPool(int row_floats)
-      : row_floats_(row_floats), rows_per_slab_(env_int("EMB_MEMORY_POOL_SIZE", 102400, 1024, 1 << 24)) {}
+      : row_floats_(row_floats), rows_per_slab_(env_int("EMB_MEMORY_POOL_SIZE", 102400, 1024, 1 << 24)) {
+    // EMB_MEMORY_POOL_THREAD_NUM (1..1024, default 1) background threads keep spare slabs allocated and page-touched, so
+    // that the thread that exhausts a slab under a table lock never pays for the allocation and its page faults.
+    const char* e = std::getenv("EMB_MEMORY_POOL_THREAD_NUM");
+    int n = 1;
+    if (e && *e) {
+      char* end = nullptr;
+      const long v = std::strtol(e, &end, 10);
+      if (end == e || *end != '\0') throw std::runtime_error("env EMB_MEMORY_POOL_THREAD_NUM is not a valid number");
+      if (v < 1 || v > 1024) throw std::runtime_error("env EMB_MEMORY_POOL_THREAD_NUM should be in [1, 1024]");
+      n = static_cast<int>(v);
+    }
+    spare_target_ = static_cast<size_t>(n);
+    for (int i = 0; i < n; ++i) workers_.emplace_back([this] { refill_loop(); });
+  }
+  ~EmbMemoryPool() {
+    { std::lock_guard<std::mutex> lk(mu_); stop_ = true; }
+    cv_.notify_all();
+    for (auto& w : workers_) w.join();
+  }
+  EmbMemoryPool(const EmbMemoryPool&) = delete;
+  EmbMemoryPool& operator=(const EmbMemoryPool&) = delete;
+
   float* alloc() {
-    std::lock_guard<std::mutex> lk(mu_);
+    std::unique_lock<std::mutex> lk(mu_);
     if (!recycle_.empty()) { float* p = recycle_.back(); recycle_.pop_back(); return p; }
     if (slabs_.empty() || used_in_last_ == rows_per_slab_) {
-      slabs_.emplace_back(new float[static_cast<size_t>(rows_per_slab_) * row_floats_]);
+      if (!spares_.empty()) {
+        slabs_.push_back(std::move(spares_.back()));
+        spares_.pop_back();
+      } else {
+        slabs_.emplace_back(new float[slab_floats()]);        // the refill threads fell behind: allocate in place
+      }
       used_in_last_ = 0;
+      cv_.notify_one();
+    } else if (used_in_last_ * 2 == rows_per_slab_) {
+      cv_.notify_one();                                       // half way through the slab: make sure a spare is on its way
     }
     return slabs_.back().get() + static_cast<size_t>(used_in_last_++) * row_floats_;
   }
   void free(float* p) { std::lock_guard<std::mutex> lk(mu_); recycle_.push_back(p); }
-  size_t bytes() const { return slabs_.size() * static_cast<size_t>(rows_per_slab_) * row_floats_ * sizeof(float); }
+  size_t bytes() const {
+    std::lock_guard<std::mutex> lk(mu_);
+    return (slabs_.size() + spares_.size()) * slab_floats() * sizeof(float);
+  }
+  int refill_threads() const { return static_cast<int>(workers_.size()); }
+
  private:
+  size_t slab_floats() const { return static_cast<size_t>(rows_per_slab_) * row_floats_; }
+  void refill_loop() {
+    std::unique_lock<std::mutex> lk(mu_);
+    for (;;) {
+      cv_.wait(lk, [this] { return stop_ || (!slabs_.empty() && spares_.size() + pending_ < spare_target_); });
+      if (stop_) return;
+      ++pending_;
+      lk.unlock();
+      std::unique_ptr<float[]> slab(new float[slab_floats()]);
+      std::memset(slab.get(), 0, slab_floats() * sizeof(float));   // touch every page now, off the critical path
+      lk.lock();
+      --pending_;
+      spares_.push_back(std::move(slab));
+    }
+  }
   int row_floats_, rows_per_slab_, used_in_last_ = 0;
-  std::vector<std::unique_ptr<float[]>> slabs_;
+  std::vector<std::unique_ptr<float[]>> slabs_, spares_;
   std::vector<float*> recycle_;
-  std::mutex mu_;
+  mutable std::mutex mu_;
+  std::condition_variable cv_;
+  std::vector<std::thread> workers_;
+  size_t spare_target_ = 1, pending_ = 0;
+  bool stop_ = false;
+};
+
+// key -> row pointer map of one table shard.  ENABLE_FAST_HASHMAP (default on here; "0" / "false" selects
+// std::unordered_map, which is what the reference uses when the variable is unset) picks the open-addressing map;
+// FAST_HASHMAP_RESERVE_BUCKET_NUM (whole table; split evenly over the shards) pre-sizes it so that a table that is
+// expected to hold that many keys never rehashes under a lock.
+class RowMap {
+ public:
+  RowMap() : fast_(env_flag("ENABLE_FAST_HASHMAP", true)), flat_(reserve_per_shard()) {
+    if (!fast_) std_.reserve(reserve_per_shard());
+  }
+  float** find(int64_t k) {
+    if (fast_) return flat_.find(k);
+    auto it = std_.find(k);
+    return it == std_.end() ? nullptr : &it->second;
+  }
+  float* const* find(int64_t k) const { return const_cast<RowMap*>(this)->find(k); }
+  void insert(int64_t k, float* v) { if (fast_) flat_.insert(k, v); else std_[k] = v; }
+  void erase(int64_t k) { if (fast_) flat_.erase(k); else std_.erase(k); }
+  size_t size() const { return fast_ ? flat_.size() : std_.size(); }
+  void clear() { if (fast_) flat_.clear(); else std_.clear(); }
+  template <typename F>
+  void for_each(F&& f) const {
+    if (fast_) flat_.for_each(f);
+    else for (const auto& kv : std_) f(kv.first, kv.second);
+  }
+  bool fast() const { return fast_; }
+
+ private:
+  static bool env_flag(const char* name, bool def) {
+    const char* e = std::getenv(name);
+    if (!e || !*e) return def;
+    const std::string v(e);
+    return !(v == "0" || v == "false" || v == "False" || v == "FALSE" || v == "no");
+  }
+  static size_t reserve_per_shard() {
+    const char* e = std::getenv("FAST_HASHMAP_RESERVE_BUCKET_NUM");
+    if (!e || !*e) return 1024;
+    char* end = nullptr;
+    const unsigned long long v = std::strtoull(e, &end, 10);
+    if (end == e || *end != '\0') throw std::runtime_error("env FAST_HASHMAP_RESERVE_BUCKET_NUM is not a valid number");
+    return static_cast<size_t>(v / 16 + 16);
+  }
+  bool fast_;
+  FlatMap<float*> flat_;
+  std::unordered_map<int64_t, float*> std_;
 };
 
 // ============================================================================ host embedding table
@@ -298,6 +402,15 @@ class HostEmbTable {
     }
   }
 
+  // drop every key (rows go back to the pool's recycle bin)
+  void clear() {
+    for (auto& sh : shards_) {
+      std::lock_guard<std::mutex> lk(sh.mu);
+      sh.map.for_each([&](int64_t, float* const& r) { pool_.free(r); });
+      sh.map.clear();
+    }
+  }
+
   void export_all(std::vector<int64_t>& keys, std::vector<float>& rows) const {
     for (auto& sh : shards_) {
       std::lock_guard<std::mutex> lk(sh.mu);
@@ -306,7 +419,7 @@ class HostEmbTable {
   }
 
  private:
-  struct Shard { mutable std::mutex mu; FlatMap<float*> map; };
+  struct Shard { mutable std::mutex mu; RowMap map; };
   Shard& shard_of(int64_t k) { return shards_[mix64(static_cast<uint64_t>(k)) >> 60]; }
   const Shard& shard_of(int64_t k) const { return shards_[mix64(static_cast<uint64_t>(k)) >> 60]; }
   int dim_, optim_num_, row_floats_;
@@ -394,6 +507,11 @@ class FeatureFilter {
     }
   }
   int64_t size() const { std::lock_guard<std::mutex> lk(mu_); return static_cast<int64_t>(stats_.size()); }
+  void clear() { std::lock_guard<std::mutex> lk(mu_); stats_.clear(); latest_ts_ = 0; }
+  void erase(const int64_t* keys, int64_t n) {
+    std::lock_guard<std::mutex> lk(mu_);
+    for (int64_t i = 0; i < n; ++i) stats_.erase(keys[i]);
+  }
 
  private:
   struct Stat { int64_t count = 0; int64_t ts = -1; float score = 0.f; };
@@ -542,6 +660,10 @@ class EmbcacheManager {
     std::vector<int64_t> ev = tb.filter.evict();
     tb.swap.remove_keys(ev.data(), static_cast<int64_t>(ev.size()));
     tb.host.erase(ev.data(), static_cast<int64_t>(ev.size()));
+    if (cfgs_[t].is_incremental) {                 // replaying incremental checkpoints must not bring these keys back
+      std::lock_guard<std::mutex> lk(tb.mu);
+      for (int64_t k : ev) { tb.evicted.insert(k); tb.touched.erase(k); }
+    }
     return ev;
   }
   // forget every device-resident row of table t without writing it back (after a checkpoint load)
@@ -572,9 +694,16 @@ class EmbcacheManager {
           if (tb.touched.count(keys[i])) { k2.push_back(keys[i]); r2.insert(r2.end(), rows.begin() + i * rf, rows.begin() + (i + 1) * rf); }
         keys.swap(k2); rows.swap(r2);
       }
-      { std::lock_guard<std::mutex> lk(tb.mu); tb.touched.clear(); }
+      std::vector<int64_t> gone;
+      {
+        std::lock_guard<std::mutex> lk(tb.mu);
+        tb.touched.clear();
+        if (incremental) gone.assign(tb.evicted.begin(), tb.evicted.end());
+        tb.evicted.clear();
+      }
       const std::string base = path + "/" + cfgs_[t].table_name + "/rank" + std::to_string(rank);
       write_slice_i64(base + "/key", keys, false);
+      write_slice_i64(base + "/evicted_key", gone, false);    // incremental only: keys to erase when this delta is replayed
       const int64_t n = static_cast<int64_t>(keys.size());
       std::vector<float> col(static_cast<size_t>(n) * dim);
       static const char* names[3] = {"embedding", "momentum1", "momentum2"};
@@ -595,7 +724,7 @@ class EmbcacheManager {
     for (size_t t = 0; t < tables_.size(); ++t) {
       const std::string tdir = path + "/" + cfgs_[t].table_name;
       const int dim = tables_[t]->host.dim();
-      static const char* i64_parts[] = {"key", "admit_count/key", "admit_count", "evict_timestamp"};
+      static const char* i64_parts[] = {"key", "evicted_key", "admit_count/key", "admit_count", "evict_timestamp"};
       for (const char* part : i64_parts) {
         for (int r = 0; r < world; ++r) {
           auto v = read_slice_i64(tdir + "/rank" + std::to_string(r) + "/" + part);
@@ -614,10 +743,26 @@ class EmbcacheManager {
   }
 
   // every rank reads the merged files and keeps key % world == rank (world-size-elastic reload)
-  void load(const std::string& path, int rank, int world) {
+  // `incremental` false: a full restore - the host table and the filter state are reset first, so keys that are not in
+  // the checkpoint do not survive it.  true: a delta on top of the current state - its rows are inserted or overwritten
+  // and the keys it lists as evicted are erased.
+  void load(const std::string& path, int rank, int world, bool incremental = false) {
     for (size_t t = 0; t < tables_.size(); ++t) {
       Table& tb = *tables_[t];
       const std::string tdir = path + "/" + cfgs_[t].table_name;
+      if (!incremental) {
+        tb.host.clear();
+        tb.filter.clear();
+        std::lock_guard<std::mutex> lk(tb.mu);
+        tb.touched.clear();
+        tb.evicted.clear();
+      } else {
+        auto gone = read_slice_i64(tdir + "/evicted_key");
+        std::vector<int64_t> mine_gone;
+        for (int64_t k : gone) { int64_t m = k % world; if (m < 0) m += world; if (m == rank) mine_gone.push_back(k); }
+        tb.host.erase(mine_gone.data(), static_cast<int64_t>(mine_gone.size()));
+        tb.filter.erase(mine_gone.data(), static_cast<int64_t>(mine_gone.size()));
+      }
       auto keys = read_slice_i64(tdir + "/key");
       const int dim = tb.host.dim(), rf = tb.host.row_floats();
       std::vector<std::vector<float>> parts;
@@ -662,6 +807,7 @@ class EmbcacheManager {
     FeatureFilter filter;
     std::mutex mu;
     std::unordered_set<int64_t> touched;
+    std::unordered_set<int64_t> evicted;       // keys evicted / erased since the last save (incremental checkpoints)
   };
   std::vector<EmbConfig> cfgs_;
   std::vector<std::unique_ptr<Table>> tables_;

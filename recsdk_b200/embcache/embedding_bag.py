@@ -167,6 +167,8 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
         self._upd_fut: List[Optional[object]] = [None] * len(module.tables)
         self._step_done = self._step_done_prev = None
         self._swap_ready = None
+        self.record_timing = False               # tests: keep (batch, begin, end) CUDA events of every swap
+        self.swap_events: List[tuple] = []
         with torch.no_grad():
             for ti, t in enumerate(self.tables):
                 self.embedding_bags[t.name].weight.zero_()
@@ -317,14 +319,19 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
             # is running now, whose rows the slot allocator protects.
             if self._step_done_prev is not None:
                 self._memcpy_stream.wait_event(self._step_done_prev)
+            if self.record_timing:
+                t_begin = torch.cuda.Event(enable_timing=True)
+                t_begin.record()
             for ti, p in enumerate(pos):
                 info = futs[ti].get()
                 self.apply_swap_async(ti, info, slot)
                 out[p] = info["batch_offs"]
             slots = torch.from_numpy(out).pin_memory().to(self.device, non_blocking=True)
             lengths_dev = lengths.pin_memory().to(self.device, non_blocking=True)
-            ready = torch.cuda.Event()
+            ready = torch.cuda.Event(enable_timing=self.record_timing)
             ready.record()
+            if self.record_timing:
+                self.swap_events.append((self.swap_step, t_begin, ready))     # device-side span of this batch's swap traffic
         self._swap_ready = ready
         return slots, lengths_dev
 

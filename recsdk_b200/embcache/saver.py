@@ -82,7 +82,7 @@ class Saver:
             else:
                 m.embedding_to_host()
                 m.invalidate_device_cache()
-            m.manager.load(path, rank, world)
+            m.manager.load(path, rank, world, incremental)
         self._barrier()
 
     @staticmethod

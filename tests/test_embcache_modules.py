@@ -183,3 +183,23 @@ def test_restore_and_restore_async():
         restore(unique_indices, bad, unique_offset, opt, out)
     with pytest.raises(ValueError):
         restore(unique_indices, unique_inverse, unique_offset[:-1], opt, out)
+
+
+def test_full_restore_drops_keys_that_are_not_in_the_checkpoint(tmp_path):
+    """A non-incremental load resets the host table (and the filter) first: keys that the model met after the save do not
+    survive the restore."""
+    m = _sharded(_tables(), [40, 64])
+    _train(m, 4, seed=0)
+    saver = Saver()
+    out = saver.save(m, str(tmp_path))
+    m.embedding_to_host()
+    sizes = [m.manager.host_size(t) for t in range(2)]
+    g = torch.Generator().manual_seed(77)
+    for _ in range(4):                                     # ids from another range: new keys in both tables
+        lens = torch.randint(1, 4, (18,), generator=g)
+        vals = torch.randint(200, 400, (int(lens.sum()),), generator=g)
+        m(KeyedJaggedTensor(["f0", "f1", "f2"], vals, lengths=lens)).values().sum().backward()
+    m.embedding_to_host()
+    assert all(m.manager.host_size(t) > s for t, s in enumerate(sizes))
+    saver.load(m, out)
+    assert [m.manager.host_size(t) for t in range(2)] == sizes
