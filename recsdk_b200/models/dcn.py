@@ -17,6 +17,7 @@ import torch
 from torch import nn
 
 from ..ops import gemm
+from ..ops import model_ops
 from ..sparse.jagged_tensor import KeyedTensor
 
 
@@ -70,7 +71,7 @@ class CrossNet(nn.Module):
         n = len(self.u) if self.low_rank else len(self.w)
         for l in range(n):
             y = self.u[l](self.v[l](x)) if self.low_rank else self.w[l](x)
-            x = torch.addcmul(x, x0, y)                      # x0 * y + x in one pass
+            x = model_ops.dcn_cross_combine(x0, y, x)        # x0 * y + x: fused forward, one fused pass for all three gradients
         return x
 
 

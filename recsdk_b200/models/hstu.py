@@ -23,7 +23,7 @@ import torch
 from torch import nn
 
 from ..modules.mlp import FusedMLP
-from ..ops import hstu_ops
+from ..ops import hstu_ops, model_ops
 from ..ops.hstu_attention import hstu_attention
 from ..sparse.jagged_tensor import KeyedJaggedTensor
 
@@ -107,9 +107,6 @@ class HSTU(nn.Module):
             keep = (~last).nonzero(as_tuple=True)[0]
         hq = h[keep]
         pos = x0[keep + 1]
-        pos_logit = (hq.float() * pos.float()).sum(-1, keepdim=True)
-        neg_logit = hstu_ops.matmul_nt(hq, neg).float()
-        logits = torch.cat([pos_logit, neg_logit], dim=1)
-        nll = torch.logsumexp(logits, dim=1) - pos_logit.squeeze(1)
         denom = global_tokens if global_tokens else max(keep.numel(), 1)
-        return nll.sum() / denom
+        # one GEMM for the negative logits, then one fused pass: positive logit, log-sum-exp, loss and all gradients
+        return model_ops.sampled_softmax_loss(hq, pos, neg, 1.0 / denom)

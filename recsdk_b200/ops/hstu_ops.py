@@ -258,8 +258,10 @@ def gather_for_rank1(x: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
 
 
 def multislice_concat(x: torch.Tensor, slice_begin: List[int], slice_size: List[int]) -> torch.Tensor:
-    """Concatenate column slices ``x[:, b:b+n]`` of a 2-D tensor."""
-    return torch.cat([x[:, b:b + n] for b, n in zip(slice_begin, slice_size)], dim=1)
+    """Concatenate column slices ``x[:, b:b+n]`` of a 2-D tensor (one kernel launch on the GPU)."""
+    from .model_ops import multislice_concat as _msc
+
+    return _msc(x, [(int(b), int(b) + int(n)) for b, n in zip(slice_begin, slice_size)])
 
 
 def token_mixing(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, epsilon: float = 1e-7) -> torch.Tensor:

@@ -6,6 +6,13 @@
     python -m recsdk_b200.utils.microbench tbe_fwd --rows 20000000 --batch 65536 --tables 26
     python -m recsdk_b200.utils.microbench ln_mul_bwd --m 65536 --n 512
     python -m recsdk_b200.utils.microbench pooled_bwd --batch 32768 --tables 40 --n 64
+    python -m recsdk_b200.utils.microbench exchange --batch 65536 --tables 26 --rows 2000000      # push exchange, one rank
+    python -m recsdk_b200.utils.microbench allreduce --n 3000000                                   # push all-reduce, one rank
+    python -m recsdk_b200.utils.microbench sampled_softmax --m 32768 --k 512 --n 512
+
+``exchange`` and ``allreduce`` run the multi-GPU kernels with a world of one (every "peer" pointer is this GPU's own
+buffer): the same code path and memory traffic minus NVLink, which is what a single-GPU ncu capture can show; the
+NVLink figures come from the multi-GPU tests (``tests/multi_gpu_worker.py --allreduce``) and the benchmark's phase times.
 
 Prints one JSON line with the measured time and the achieved rate against the measured peaks
 (``MEASURED_PEAKS.json`` at the repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).
@@ -49,7 +56,8 @@ def _time(fn, iters: int, warmup: int = 3) -> float:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "hstu_fwd", "hstu_bwd", "tbe_fwd", "interaction", "ln_mul_bwd", "pooled_bwd"])
+    ap.add_argument("what", choices=["gemm", "hstu_fwd", "hstu_bwd", "tbe_fwd", "interaction", "ln_mul_bwd", "pooled_bwd",
+                                     "exchange", "allreduce", "sampled_softmax"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -174,6 +182,112 @@ def main() -> None:
         by = n * D * 2 + U * D * 4 * 2 + n * 12 * 2             # gradient rows gathered, red zeroed + written, pairs read + written once
         out.update(ms=ms, ids=n, unique=U, gbs=by / ms / 1e6, frac_of_peak=by / (ms / 1e3) / hbm,
                    kernel="scatter_add (atomics)" if a.splits > 1 else "sort + segment_add")
+    elif a.what == "exchange":
+        from ..modules.embedding_configs import DataType, EmbeddingBagConfig
+        from ..ops import embedding_ops as E
+        from ..parallel.comm import PeerGroup, ShardingEnv
+        from ..parallel.embeddingbag import ShardedEmbeddingBagCollection
+        from ..parallel.push_exchange import MODE_ONE_HOT, PH_GRADS, PH_ROWS
+        from ..sparse.jagged_tensor import KeyedJaggedTensor
+
+        B, T, D, R = a.batch, a.tables, 128, a.rows
+        cfgs = [EmbeddingBagConfig(num_embeddings=R, embedding_dim=D, name="t%d" % i, feature_names=["f%d" % i],
+                                   data_type=DataType.FP16) for i in range(T)]
+        m = ShardedEmbeddingBagCollection(cfgs, {}, ShardingEnv(1, 0), dev, E.OptimizerSpec(kind=E.OPT_ROWWISE_ADAGRAD),
+                                          peer=None, max_local_batch=B, one_hot=True)
+        # drive the multi-rank kernels with a world of one: same code, every peer pointer is local
+        peer = PeerGroup(None, dev)
+        g = torch.Generator().manual_seed(0)
+        from ..utils.data import zipf_ids
+
+        ids = torch.cat([zipf_ids(B, R, 1.1, g) for _ in range(T)]).to(dev)
+        # build the exchange by hand (``_ensure_capacity`` takes the single-rank shortcut otherwise)
+        from ..parallel.push_exchange import PushExchange
+        import numpy as np
+
+        L_ = m.layout
+        px = PushExchange(peer, dev, B * T, B * T, D, torch.bfloat16, B * L_.total_D * 2)
+        i32 = dict(dtype=torch.int32, device=dev)
+        f_D = torch.tensor(L_.feature_dims, **i32)
+        f_Doff = torch.tensor([int(x) for x in L_.D_offsets[:-1]], **i32)
+        tdims = torch.tensor(L_.dims, **i32)
+        ftab = torch.tensor(L_.feature_table, **i32)
+        kb = torch.from_numpy(np.concatenate([[0], np.cumsum(L_.local_rows[0])[:-1]]).astype(np.int64)).to(dev).view(1, -1).contiguous()
+        # world-1 shards are SH_LOCAL: locate_row keeps every id on this rank
+        dout = torch.randn(B, L_.total_D, device=dev).bfloat16()
+        ws = E.BackwardWorkspace(dev, B * T, D)
+        step = [0]
+
+        def fwd():
+            px.route_scatter(ids, None, T, B, m.dev["shards"], kb, ftab, L_.n_tables, want_bags=False)
+            px.serve_rows(m.dev["key_cumsum"], m.dev["w_offsets"], tdims, f_Doff, L_.n_tables, T, m.weights, torch.bfloat16,
+                          L_.total_D, True, B)
+            px.wait(PH_ROWS)
+
+        def bwd():
+            seg = px.sort_received(L_.key_bits)
+            px.push_grads(dout, MODE_ONE_HOT, f_D, f_Doff, T, B)
+            px.wait(PH_GRADS)
+            step[0] += 1
+            E.tbe_backward_update_rows(L_, m.dev, seg, px.grad_recv, px.g_ld, tdims, m.weights, m.state1, m.state2, m.s_offsets,
+                                       m.opt, step[0], ws)
+
+        def both():
+            fwd()
+            bwd()
+
+        fwd()
+        ms_f = _time(fwd, a.iters)
+        ms = _time(both, a.iters)
+        rows_bytes = B * T * D * 2
+        out.update(ms_forward=ms_f, ms_forward_backward=ms, entries=B * T,
+                   forward_gbs=2 * rows_bytes / ms_f / 1e6, forward_frac_of_peak=2 * rows_bytes / (ms_f / 1e3) / hbm,
+                   note="world of one: route + scatter + serve_rows (+ sort + push_grads + update_rows); bytes = rows read + written")
+    elif a.what == "allreduce":
+        class Flat(torch.nn.Module):
+            def __init__(self, n):
+                super().__init__()
+                self.flat_param = torch.nn.Parameter(torch.zeros(n, device=dev))
+                self.register_buffer("flat_grad", torch.randn(n, device=dev), persistent=False)
+
+        n = (a.n + 7) // 8 * 8
+        holder = torch.nn.Module()
+        holder.a = Flat(n)
+        # a world of one short-circuits the reducer class; call the kernel directly with self pointers
+        import numpy as np
+
+        L = _lib.lib()
+        sb = int(L.rb_allreduce_push_staging_bytes(n, 1, 1))
+        staging = torch.zeros(sb, dtype=torch.uint8, device=dev)
+        result = torch.zeros(sb, dtype=torch.uint8, device=dev)
+        flags = torch.zeros(2 * 16 * int(L.rb_allreduce_push_max_blocks()), dtype=torch.int32, device=dev)
+        epoch = torch.zeros(2, dtype=torch.int32, device=dev)
+        ps, pr, pf = (np.asarray([t.data_ptr()], dtype=np.uint64) for t in (staging, result, flags))
+        st = _lib.stream_ptr(dev)
+
+        def fn():
+            _lib.check(L.rb_allreduce_push(holder.a.flat_grad.data_ptr(), n, ps.ctypes.data, pr.ctypes.data, pf.ctypes.data,
+                                           epoch.data_ptr(), 1.0, 0, 1, 1, 0, 0, _lib.status_tensor(dev).data_ptr(), 1000, st),
+                       "rb_allreduce_push")
+
+        ms = _time(fn, a.iters)
+        by = n * 4 * 2 + n * 2 * 4          # fp32 read + write, bf16 staging and result written + read
+        out.update(ms=ms, n=n, gbs=by / ms / 1e6, frac_of_peak=by / (ms / 1e3) / hbm,
+                   note="two-shot push all-reduce, one rank looped back: local traffic only")
+    elif a.what == "sampled_softmax":
+        from ..ops import model_ops
+
+        M, d, N = a.m, a.k, a.n
+        h = torch.randn(M, d, device=dev).bfloat16().requires_grad_()
+        ep = torch.randn(M, d, device=dev).bfloat16()
+        en = torch.randn(N, d, device=dev).bfloat16()
+
+        def fn():
+            model_ops.sampled_softmax_loss(h, ep, en, 1.0 / M)
+
+        ms = _time(fn, a.iters)
+        by = M * d * 2 * 4 + M * N * 2 * 3
+        out.update(ms=ms, gbs=by / ms / 1e6, frac_of_peak=by / (ms / 1e3) / hbm, note="GEMM + fused loss/gradient pass (forward only timed)")
     else:
         from ..ops import interaction as I
 

@@ -1,0 +1,53 @@
+"""Fused model-level kernels against their fp32 PyTorch statements."""
+import pytest
+import torch
+
+from recsdk_b200.ops import model_ops
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("M,d,N", [(1000, 512, 512), (37, 64, 128), (4096, 256, 2048)])
+def test_sampled_softmax_loss_and_gradients(M, d, N):
+    g = torch.Generator().manual_seed(M + N)
+    h = (torch.randn(M, d, generator=g) * 0.5).to(DEV, torch.bfloat16).requires_grad_()
+    ep = (torch.randn(M, d, generator=g) * 0.5).to(DEV, torch.bfloat16).requires_grad_()
+    en = (torch.randn(N, d, generator=g) * 0.5).to(DEV, torch.bfloat16).requires_grad_()
+    scale = 1.0 / M
+    loss = model_ops.sampled_softmax_loss(h, ep, en, scale)
+    loss.backward()
+    hf, pf, nf = (t.detach().float().requires_grad_() for t in (h, ep, en))
+    pos = (hf * pf).sum(-1, keepdim=True)
+    neg = (hf @ nf.t()).to(torch.bfloat16).float()                     # the kernel reads the GEMM's bf16 logits
+    want = (torch.logsumexp(torch.cat([pos, neg], 1), 1) - pos.squeeze(1)).sum() * scale
+    want.backward()
+    assert abs(float(loss) - float(want)) <= 5e-3 * abs(float(want)) + 1e-4
+    for got, ref in ((h.grad, hf.grad), (ep.grad, pf.grad), (en.grad, nf.grad)):
+        err = (got.float() - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item() + 1e-6, err
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_dcn_cross_combine(dtype):
+    g = torch.Generator().manual_seed(2)
+    xs = [torch.randn(513, 264, generator=g).to(DEV, dtype).requires_grad_() for _ in range(3)]
+    y = model_ops.dcn_cross_combine(*xs)
+    w = torch.randn(513, 264, generator=g).to(DEV, dtype)
+    (y * w).sum().backward()
+    fs = [x.detach().float().requires_grad_() for x in xs]
+    yf = fs[0] * fs[1] + fs[2]
+    (yf * w.float()).sum().backward()
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-6
+    assert (y.float() - yf).abs().max().item() <= tol * yf.abs().max().item()
+    for x, f in zip(xs, fs):
+        assert (x.grad.float() - f.grad).abs().max().item() <= tol * f.grad.abs().max().item() + 1e-7
+
+
+def test_multislice_concat():
+    for dtype in (torch.float32, torch.bfloat16, torch.int64):
+        x = (torch.arange(77 * 50).view(77, 50) % 997).to(DEV).to(dtype)
+        sl = [(3, 10), (0, 1), (40, 50), (20, 20), (7, 31)]
+        got = model_ops.multislice_concat(x, sl)
+        want = torch.cat([x[:, a:b] for a, b in sl], dim=1)
+        assert torch.equal(got, want)
