@@ -55,11 +55,14 @@ __device__ __forceinline__ bool wait_flags(const int* ctl_local, int phase, int 
 }
 
 // Every block calls this after its last global store of the kernel; true in the block that finishes last.
+// One system-scope fence per block, issued by the thread that takes the ticket after the block barrier: the barrier
+// orders every thread's stores before that thread, and its fence is cumulative over them (a fence in every thread would
+// cost one membar.sys per thread for the same guarantee).
 __device__ __forceinline__ bool is_last_block(int* loc, int phase) {
   __shared__ int s_last;
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const int t = atomicAdd(loc + LOC_TICKET + phase, 1);
     s_last = (t == static_cast<int>(gridDim.x) - 1);
   }
@@ -67,11 +70,12 @@ __device__ __forceinline__ bool is_last_block(int* loc, int phase) {
   return s_last != 0;
 }
 
-// Last block only: raise flags[phase][me] = e at every rank and publish the epoch locally.
+// Last block only: raise flags[phase][me] = e at every rank and publish the epoch locally.  The release store at system
+// scope orders everything this block has observed (all blocks' tickets, hence their fenced stores) before the flag.
 __device__ __forceinline__ void signal_all(const PeerPtrs& ctl, int* loc, int phase, int e, int me, int world) {
   __syncthreads();
   if (threadIdx.x < world) {
-    __threadfence_system();
+    __threadfence_system();      // at most 16 threads of one block: cheap, and keeps the acquire side of the ticket chain explicit
     st_release_sys(reinterpret_cast<int*>(ctl.p[threadIdx.x]) + CTL_FLAGS + phase * MAX_RANKS + me, e);
   }
   if (threadIdx.x == 0) {

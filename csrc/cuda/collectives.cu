@@ -314,9 +314,8 @@ __device__ __forceinline__ void st_grad8(float* g, long long idx, long long n, c
 
 // raise flags[phase][me][block] = e at every rank
 __device__ __forceinline__ void ar_signal(const ArArgs& a, int phase, int e) {
-  __syncthreads();
+  __syncthreads();          // every thread's stores are ordered before the releasing threads; st.release.sys carries the fence
   if (threadIdx.x < a.world) {
-    __threadfence_system();
     int* f = reinterpret_cast<int*>(a.flags.p[threadIdx.x]) +
              (static_cast<long long>(phase) * MAX_RANKS + a.rank) * gridDim.x + blockIdx.x;
     st_release_sys(f, e);
@@ -377,13 +376,14 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_twoshot_kernel(const ArA
     const int p = (me + k) % world;
     WT* dst = reinterpret_cast<WT*>(a.staging.p[p]) + (static_cast<long long>(me) * slice) / AR_VEC;
     const long long base = static_cast<long long>(p) * slice;
-    for (long long el = first; el < slice; el += 2 * step) {
-      float v0[8], v1[8];
-      const long long el1 = el + step;
-      ld_grad8(a.grad, base + el, a.n, v0);
-      if (el1 < slice) ld_grad8(a.grad, base + el1, a.n, v1);
-      dst[el / AR_VEC] = W::from_f32(v0);
-      if (el1 < slice) dst[el1 / AR_VEC] = W::from_f32(v1);
+    for (long long el = first; el < slice; el += 4 * step) {      // four independent 32-byte loads in flight per thread
+      float v[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (el + u * step < slice) ld_grad8(a.grad, base + el + u * step, a.n, v[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (el + u * step < slice) dst[(el + u * step) / AR_VEC] = W::from_f32(v[u]);
     }
   }
   ar_signal(a, 0, e);
@@ -519,7 +519,7 @@ RB_API int rb_allreduce_push(float* grad, long long n, const unsigned long long*
   a.limit_ns = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
   const long long work = one_shot ? n : ((n + world - 1) / world);
   long long want = (work + AR_CHUNK - 1) / AR_CHUNK;
-  const int cap = blocks > 0 ? blocks : 96;
+  const int cap = blocks > 0 ? blocks : 128;
   if (want > cap) want = cap;
   if (blocks > 0) want = blocks;             // the grid is part of the flag layout: identical on every rank
   if (want > rb_allreduce_push_max_blocks()) return -1;

@@ -46,9 +46,79 @@ class IdsMapper {
   // Returns u.  Uses a per-call scratch map keyed by raw id.
   int64_t unique_and_lookup(const int64_t* ids, int64_t n, int64_t* hash_indices, int64_t* unique,
                             int64_t* unique_ids, int64_t* inverse) {
+    std::lock_guard<std::mutex> lk(mu_);
+    const int threads = std::max(1, std::min<int>(omp_get_max_threads(), static_cast<int>(n / 16384)));
+    if (threads <= 1) return unique_and_lookup_serial(ids, n, hash_indices, unique, unique_ids, inverse);
+    // Parallel form with the same outputs (distinct ids in first-seen order, slots handed out in that order):
+    //   1. every thread de-duplicates its contiguous chunk with a small private map (cache resident) and looks its
+    //      distinct ids up in the table map (read-only while this call holds the lock),
+    //   2. one pass over the chunks' distinct ids in chunk order assigns global positions: known ids are recognised
+    //      through a slot-indexed stamp array (no hashing), new ids are inserted,
+    //   3. every thread translates its chunk's local positions into global ones and fills the per-id outputs.
+    struct Chunk { std::vector<int64_t> uniq, slot, gpos; std::vector<int32_t> inv; };
+    std::vector<Chunk> ch(threads);
+    const int64_t per = (n + threads - 1) / threads;
+#pragma omp parallel for num_threads(threads) schedule(static, 1)
+    for (int t = 0; t < threads; ++t) {
+      const int64_t b = t * per, e = std::min<int64_t>(n, b + per);
+      Chunk& c = ch[t];
+      if (b >= e) continue;
+      FlatMap<int32_t> seen(static_cast<size_t>(e - b) + 1);
+      c.inv.resize(e - b);
+      c.uniq.reserve((e - b) / 2 + 16);
+      for (int64_t i = b; i < e; ++i) {
+        auto r = seen.insert(ids[i], static_cast<int32_t>(c.uniq.size()));
+        if (r.second) c.uniq.push_back(ids[i]);
+        c.inv[i - b] = *r.first;
+      }
+      c.slot.resize(c.uniq.size());
+      for (size_t k = 0; k < c.uniq.size(); ++k) {
+        const int64_t* p = map_.find(c.uniq[k]);
+        c.slot[k] = p ? *p : -1;
+      }
+    }
+    ++stamp_;
+    if (stamp_ == 0) { std::fill(slot_stamp_.begin(), slot_stamp_.end(), 0u); stamp_ = 1; }
+    int64_t u = 0;
+    for (int t = 0; t < threads; ++t) {
+      Chunk& c = ch[t];
+      c.gpos.resize(c.uniq.size());
+      for (size_t k = 0; k < c.uniq.size(); ++k) {
+        int64_t slot = c.slot[k];
+        if (slot < 0) slot = find_or_insert_unlocked(c.uniq[k]);   // new here, or inserted by an earlier chunk of this call
+        if (static_cast<size_t>(slot) >= slot_stamp_.size()) {
+          const size_t want = std::max<size_t>(slot2id_.size(), static_cast<size_t>(slot) + 1);
+          slot_stamp_.resize(want + want / 4 + 16, 0u);
+          slot_pos_.resize(slot_stamp_.size(), 0);
+        }
+        if (slot_stamp_[slot] == stamp_) {
+          c.gpos[k] = slot_pos_[slot];
+        } else {
+          slot_stamp_[slot] = stamp_;
+          slot_pos_[slot] = u;
+          unique_ids[u] = c.uniq[k];
+          unique[u] = slot;
+          c.gpos[k] = u++;
+        }
+      }
+    }
+#pragma omp parallel for num_threads(threads) schedule(static, 1)
+    for (int t = 0; t < threads; ++t) {
+      const int64_t b = t * per, e = std::min<int64_t>(n, b + per);
+      const Chunk& c = ch[t];
+      for (int64_t i = b; i < e; ++i) {
+        const int64_t pos = c.gpos[c.inv[i - b]];
+        inverse[i] = pos;
+        hash_indices[i] = unique[pos];
+      }
+    }
+    return u;
+  }
+
+  int64_t unique_and_lookup_serial(const int64_t* ids, int64_t n, int64_t* hash_indices, int64_t* unique,
+                                   int64_t* unique_ids, int64_t* inverse) {
     FlatMap<int64_t> seen(static_cast<size_t>(n) + 1);
     int64_t u = 0;
-    std::lock_guard<std::mutex> lk(mu_);
     for (int64_t i = 0; i < n; ++i) {
       auto r = seen.insert(ids[i], u);
       if (r.second) {
@@ -86,6 +156,9 @@ class IdsMapper {
   int64_t max_slots_;
   FlatMap<int64_t> map_;
   std::vector<int64_t> slot2id_;
+  std::vector<uint32_t> slot_stamp_;        // per slot: the call that last listed it among its distinct ids
+  std::vector<int64_t> slot_pos_;           // ... and its position in that call's distinct list
+  uint32_t stamp_ = 0;
   mutable std::mutex mu_;
 };
 
@@ -137,7 +210,14 @@ inline void block_bucketize(const int64_t* lengths, const int64_t* indices, cons
                             int64_t* new_lengths, int64_t* new_indices, float* new_weights,
                             int64_t* unbucketize_permute) {
   const int64_t FB = F * B;
-  std::vector<int64_t> offsets(FB + 1, 0);
+  // scratch that keeps its pages between calls (a fresh 8 * world * F * B byte vector per batch costs more in page
+  // faults than the bucketize itself)
+  static thread_local std::vector<int64_t> offsets_tl, new_offsets_tl;
+  offsets_tl.resize(FB + 1);
+  new_offsets_tl.resize(world * FB + 1);
+  int64_t* const offsets = offsets_tl.data();          // plain pointers: the OpenMP workers must see THIS thread's buffers
+  int64_t* const new_offsets = new_offsets_tl.data();
+  offsets[0] = 0;
   for (int64_t i = 0; i < FB; ++i) offsets[i + 1] = offsets[i] + lengths[i];
   std::fill(new_lengths, new_lengths + world * FB, 0);
   auto bucket_of = [&](int64_t f, int64_t id) -> int64_t {
@@ -150,12 +230,31 @@ inline void block_bucketize(const int64_t* lengths, const int64_t* indices, cons
     const int64_t f = fb / B;
     for (int64_t j = offsets[fb]; j < offsets[fb + 1]; ++j) ++new_lengths[bucket_of(f, indices[j]) * FB + fb];
   }
-  std::vector<int64_t> new_offsets(world * FB + 1, 0);
-  for (int64_t i = 0; i < world * FB; ++i) new_offsets[i + 1] = new_offsets[i] + new_lengths[i];
+  // exclusive prefix over world*FB counts: per-thread partial sums, then a short serial carry
+  const int64_t total = world * FB;
+  new_offsets[0] = 0;
+  {
+    const int nt = std::max(1, std::min<int>(omp_get_max_threads(), static_cast<int>(total / 65536) + 1));
+    const int64_t per = (total + nt - 1) / nt;
+    std::vector<int64_t> carry(nt + 1, 0);
+#pragma omp parallel for num_threads(nt) schedule(static, 1)
+    for (int t = 0; t < nt; ++t) {
+      int64_t run = 0;
+      for (int64_t i = t * per; i < std::min<int64_t>(total, (t + 1) * per); ++i) { new_offsets[i + 1] = run += new_lengths[i]; }
+      carry[t + 1] = run;
+    }
+    for (int t = 0; t < nt; ++t) carry[t + 1] += carry[t];
+#pragma omp parallel for num_threads(nt) schedule(static, 1)
+    for (int t = 1; t < nt; ++t)
+      for (int64_t i = t * per; i < std::min<int64_t>(total, (t + 1) * per); ++i) new_offsets[i + 1] += carry[t];
+  }
 #pragma omp parallel for schedule(static)
   for (int64_t fb = 0; fb < FB; ++fb) {
     const int64_t f = fb / B;
-    std::vector<int64_t> cursor(world);
+    int64_t cursor_small[64];                                  // no heap allocation per bag
+    std::vector<int64_t> cursor_big;
+    int64_t* cursor = cursor_small;
+    if (world > 64) { cursor_big.resize(world); cursor = cursor_big.data(); }
     for (int64_t w = 0; w < world; ++w) cursor[w] = new_offsets[w * FB + fb];
     for (int64_t j = offsets[fb]; j < offsets[fb + 1]; ++j) {
       const int64_t id = indices[j];

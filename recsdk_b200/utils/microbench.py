@@ -54,10 +54,82 @@ def _time(fn, iters: int, warmup: int = 3) -> float:
     return ts[len(ts) // 2]
 
 
+def host_engines(a) -> dict:
+    """Host id-processing engines (no GPU): this package's native ``IdsMapper`` / bucketize against the reference's own,
+    unmodified C++ (``baseline/build_ref_host.py`` builds ``baseline/_ref/libhybrid_cpp.so`` from the reference tree) on the
+    same ids: Zipf(1.1) ids of one table for the fused unique + lookup, a feature-major KJT for the bucketize."""
+    import time
+
+    import numpy as np
+
+    from ..host import host
+    from ..utils.data import zipf_ids
+
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    ref_so = os.path.join(root, "baseline", "_ref", "libhybrid_cpp.so")
+    have_ref = os.path.exists(ref_so)
+    if have_ref:
+        torch.ops.load_library(ref_so)
+    g = torch.Generator().manual_seed(0)
+    n, rows, world, F = a.batch * 26, a.rows, 8, 26
+    ids = zipf_ids(n, rows, 1.1, g)
+    ids_np = ids.numpy().astype(np.int64)
+
+    def best(fn, reps=a.iters):
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append((time.perf_counter() - t0) * 1e3)
+        return min(ts)
+
+    out = {"what": "host_engines", "ids": n, "distinct": int(np.unique(ids_np).size), "table_rows": rows,
+           "reference_library": ref_so if have_ref else None}
+    H = host()
+    # ---- fused unique + lookup: a fresh mapper per call measures insertion, a warm one measures the steady state
+    def ours_cold():
+        H.IdsMapper(rows).ids2indices_unique_out(ids_np)
+
+    warm = H.IdsMapper(rows)
+    warm.ids2indices_unique_out(ids_np)
+    out["ours_unique_lookup_cold_ms"] = best(ours_cold)
+    out["ours_unique_lookup_warm_ms"] = best(lambda: warm.ids2indices_unique_out(ids_np))
+    if have_ref:
+        def ref_cold():
+            torch.classes.hybrid.IdsMapper(rows, True).ids2indices_unique(ids)
+
+        rwarm = torch.classes.hybrid.IdsMapper(rows, True)
+        rwarm.ids2indices_unique(ids)
+        out["reference_unique_lookup_cold_ms"] = best(ref_cold)
+        out["reference_unique_lookup_warm_ms"] = best(lambda: rwarm.ids2indices_unique(ids))
+        a_, b_ = warm.ids2indices_unique_out(ids_np), rwarm.ids2indices_unique(ids)
+        out["same_distinct_count"] = int(np.asarray(a_[1]).size) == int(b_[1].numel())
+    # ---- bucketize of a feature-major KJT (one id per bag) over `world` ranks
+    B = a.batch
+    lengths = np.ones(F * B, dtype=np.int64)
+    out["ours_bucketize_ms"] = best(lambda: H.block_bucketize_sparse_features(lengths, ids_np, None, F, B, world, None, True))
+    if have_ref:
+        lt, block = torch.from_numpy(lengths), torch.full((F,), (rows + world - 1) // world, dtype=torch.int64)
+
+        def ref_bucketize():
+            torch.ops.hybrid.block_bucketize_sparse_features_cpu(lt, ids, False, True, block, world, None, None, None, 0, None,
+                                                                 False, False, False, False, None)
+
+        try:
+            out["reference_bucketize_ms"] = best(ref_bucketize)
+        except Exception as e:  # noqa: BLE001
+            out["reference_bucketize_error"] = "%s: %s" % (type(e).__name__, str(e)[:200])
+    for k in ("unique_lookup_cold", "unique_lookup_warm", "bucketize"):
+        if "reference_%s_ms" % k in out:
+            out["speedup_%s" % k] = out["reference_%s_ms" % k] / out["ours_%s_ms" % k]
+    out["threads"] = torch.get_num_threads()
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "hstu_fwd", "hstu_bwd", "tbe_fwd", "interaction", "ln_mul_bwd", "pooled_bwd",
-                                     "exchange", "allreduce", "sampled_softmax"])
+                                     "exchange", "allreduce", "sampled_softmax", "host_engines"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -74,6 +146,9 @@ def main() -> None:
     ap.add_argument("--tables", type=int, default=26)
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
+    if a.what == "host_engines":
+        print(json.dumps(host_engines(a)))
+        return
     from ..ops import _lib, gemm
 
     hbm, flops, src = _peaks()
