@@ -78,6 +78,94 @@ class _SideTensorKJT(KeyedJaggedTensor):
         return self._wrap(base, side)
 
 
+    # -- constructors / conversions that keep the side tensors ------------------------------------------------------
+    @classmethod
+    def from_lengths_sync(cls, keys: List[str], values: torch.Tensor, lengths: torch.Tensor, weights: Optional[torch.Tensor] = None,
+                          stride: Optional[int] = None, **side: Optional[torch.Tensor]):
+        return cls(keys, values, weights, lengths, None, stride, **side)
+
+    @classmethod
+    def from_offsets_sync(cls, keys: List[str], values: torch.Tensor, offsets: torch.Tensor, weights: Optional[torch.Tensor] = None,
+                          stride: Optional[int] = None, **side: Optional[torch.Tensor]):
+        return cls(keys, values, weights, None, offsets, stride, **side)
+
+    @classmethod
+    def empty_like(cls, kjt: KeyedJaggedTensor):
+        """No ids, same keys / stride / device; every side tensor empty."""
+        v = kjt.values()
+        z = torch.zeros(len(kjt.keys()) * kjt.stride(), dtype=torch.int64, device=v.device)
+        side = {n: v.new_zeros(0, dtype=torch.int64) for n in cls.PER_VALUE + cls.WHOLE}
+        return cls(kjt.keys(), v[:0], None, z, None, kjt.stride(), **side)
+
+    @classmethod
+    def concat(cls, kjts: List["_SideTensorKJT"]):
+        """Feature-wise concatenation (all inputs share the stride); per-id side tensors follow their ids, whole-batch side
+        tensors must be absent (they describe one batch and cannot be merged)."""
+        if not kjts:
+            raise ValueError("concat of an empty list")
+        base = KeyedJaggedTensor.concat(list(kjts))
+        side: Dict[str, Optional[torch.Tensor]] = {}
+        for n in cls.PER_VALUE:
+            ts = [getattr(k, "_" + n) for k in kjts]
+            if any(t is None for t in ts):
+                if any(t is not None for t in ts):
+                    raise ValueError("%s is set on some inputs only" % n)
+                side[n] = None
+            else:
+                side[n] = torch.cat(ts)
+        for n in cls.WHOLE:
+            if any(getattr(k, "_" + n) is not None for k in kjts):
+                raise ValueError("%s describes one batch and cannot be concatenated" % n)
+            side[n] = None
+        out = cls.__new__(cls)
+        out.__dict__.update(base.__dict__)
+        out._init_side(**side)
+        return out
+
+    def to_dict(self) -> Dict[str, "ExtendedJaggedTensor"]:
+        """Per key: an ``ExtendedJaggedTensor`` whose extras are this key's slice of every per-id side tensor."""
+        base = KeyedJaggedTensor.to_dict(self)
+        opk = self.offset_per_key()
+        out = {}
+        for i, k in enumerate(self.keys()):
+            jt = base[k]
+            extras = {n: t[opk[i]:opk[i + 1]] for n, t in self._side().items() if t is not None and n in self.PER_VALUE}
+            out[k] = ExtendedJaggedTensor(jt.values(), jt.weights_or_none(), jt._lengths, jt._offsets, extras)
+        return out
+
+    # -- what an all-to-all of this batch has to carry (labels and tensors in matching order) --------------------------
+    def dist_labels(self) -> List[str]:
+        return KeyedJaggedTensor.dist_labels(self) + [n for n in self.PER_VALUE if getattr(self, "_" + n) is not None]
+
+    def dist_tensors(self) -> List[torch.Tensor]:
+        return KeyedJaggedTensor.dist_tensors(self) + [getattr(self, "_" + n) for n in self.PER_VALUE
+                                                       if getattr(self, "_" + n) is not None]
+
+    def dist_splits(self, key_splits: List[int]) -> List[List[int]]:
+        """Send splits of every distributed tensor when the keys are dealt to ranks as ``key_splits`` (keys per rank):
+        lengths travel as ``keys * stride`` entries, values and every per-id side tensor as the ids of those keys."""
+        lpk, stride, start = self.length_per_key(), self.stride(), 0
+        len_splits, val_splits = [], []
+        for n in key_splits:
+            len_splits.append(n * stride)
+            val_splits.append(sum(lpk[start:start + n]))
+            start += n
+        return [len_splits] + [list(val_splits) for _ in range(len(self.dist_labels()) - 1)]
+
+    @classmethod
+    def dist_init(cls, keys: List[str], tensors: List[torch.Tensor], labels: List[str], stride: int):
+        """Rebuild a batch from the tensors an all-to-all delivered (``labels`` as produced by ``dist_labels``)."""
+        got = dict(zip(labels, tensors))
+        side = {n: got.get(n) for n in cls.PER_VALUE}
+        return cls(keys, got["values"], got.get("weights"), got["lengths"], None, stride, **side)
+
+    def __str__(self) -> str:
+        parts = ["%s(keys=%s, stride=%d, nnz=%d" % (type(self).__name__, self.keys(), self.stride(), self.values().numel())]
+        for n, t in self._side().items():
+            parts.append("%s=%s" % (n, "None" if t is None else tuple(t.shape)))
+        return ", ".join(parts) + ")"
+
+
 class KeyedJaggedTensorWithLookHelper(_SideTensorKJT):
     PER_VALUE = ("hash_indices", "unique_inverse")
     WHOLE = ("unique_indices", "unique_offset")
@@ -156,3 +244,49 @@ class ExtendedJaggedTensor(JaggedTensor):
         for t in self.extras.values():
             if t.is_cuda:
                 t.record_stream(stream)
+
+
+class KeyedExtendedJaggedTensor(_SideTensorKJT):
+    """KJT with one generic per-id side tensor ``extra`` (any dtype; e.g. labels or timestamps) and the argument checks
+    of the reference's class (``hybrid_torchrec/sparse/extended_jagged_tensor.py:69-235``): distinct keys, a positive
+    stride, per-key list arguments that are integer lists of the right length, ``extra`` aligned with the ids."""
+    PER_VALUE = ("extra",)
+
+    def __init__(self, keys, values, weights=None, lengths=None, offsets=None, stride=None, length_per_key=None, offset_per_key=None,
+                 extra=None) -> None:
+        self._validate_keys(keys)
+        self._validate_stride(stride)
+        self._validate_int_list(length_per_key, "length_per_key", len(keys))
+        self._validate_int_list(offset_per_key, "offset_per_key", len(keys) + 1)
+        if lengths is None and offsets is None:
+            raise ValueError("either lengths or offsets is required")
+        super().__init__(keys, values, weights, lengths, offsets, stride, length_per_key, offset_per_key)
+        self._init_side(extra=extra)
+
+    extra = property(lambda self: self._extra)
+
+    @staticmethod
+    def _validate_keys(keys) -> None:
+        if not isinstance(keys, (list, tuple)) or not all(isinstance(k, str) for k in keys):
+            raise TypeError("keys must be a list of strings")
+        if len(set(keys)) != len(keys):
+            raise ValueError("duplicate keys: %s" % sorted(k for k in set(keys) if list(keys).count(k) > 1))
+
+    @staticmethod
+    def _validate_stride(stride) -> None:
+        if stride is not None and (not isinstance(stride, int) or isinstance(stride, bool) or stride < 0):
+            raise ValueError("stride must be a non-negative int, got %r" % (stride,))
+
+    @staticmethod
+    def _validate_int_list(v, name: str, want_len: int) -> None:
+        if v is None:
+            return
+        if not isinstance(v, (list, tuple)) or not all(isinstance(x, int) and not isinstance(x, bool) for x in v):
+            raise TypeError("%s must be a list of ints" % name)
+        if len(v) != want_len:
+            raise ValueError("%s needs %d entries, got %d" % (name, want_len, len(v)))
+
+    def to_base(self) -> KeyedJaggedTensor:
+        """The plain KJT (side tensor dropped)."""
+        return KeyedJaggedTensor(self.keys(), self.values(), self.weights_or_none(), self.lengths_or_none(), self.offsets_or_none(),
+                                 self.stride())

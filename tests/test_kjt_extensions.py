@@ -32,3 +32,38 @@ def test_dedup_with_counts_and_extended_jt():
     assert d.values().tolist() == [5, 7, 9] and d.counts.tolist() == [2, 1, 3] and d.lengths().tolist() == [2, 1]
     e = ExtendedJaggedTensor(torch.arange(4.), lengths=torch.tensor([1, 3]), extras={"ts": torch.arange(4) + 50})
     assert e.to(torch.device("cpu")).extras["ts"].tolist() == [50, 51, 52, 53]
+
+
+def test_side_tensor_kjt_concat_dict_dist_roundtrip_and_validation():
+    import pytest
+    import torch
+
+    from recsdk_b200.sparse.kjt_extensions import (KeyedExtendedJaggedTensor, KeyedJaggedTensorWithCount,
+                                                   KeyedJaggedTensorWithTimestamp)
+
+    a = KeyedJaggedTensorWithCount.from_lengths_sync(["f0", "f1"], torch.tensor([5, 6, 7, 8, 9]), torch.tensor([1, 2, 0, 2]),
+                                                     counts=torch.tensor([1, 1, 2, 3, 1]))
+    b = KeyedJaggedTensorWithCount.from_lengths_sync(["f2"], torch.tensor([1, 2, 3]), torch.tensor([3, 0]), counts=torch.tensor([4, 4, 4]))
+    c = KeyedJaggedTensorWithCount.concat([a, b])
+    assert c.keys() == ["f0", "f1", "f2"] and c.counts.tolist() == [1, 1, 2, 3, 1, 4, 4, 4]
+    d = c.to_dict()
+    assert d["f1"].values().tolist() == [8, 9] and d["f1"].extras["counts"].tolist() == [3, 1]
+    # what an all-to-all carries, and the batch rebuilt from it
+    assert c.dist_labels() == ["lengths", "values", "counts"]
+    assert c.dist_splits([2, 1]) == [[4, 2], [5, 3], [5, 3]]
+    r = KeyedJaggedTensorWithCount.dist_init(c.keys(), c.dist_tensors(), c.dist_labels(), c.stride())
+    assert r.values().tolist() == c.values().tolist() and r.counts.tolist() == c.counts.tolist()
+    e = KeyedJaggedTensorWithTimestamp.empty_like(c)
+    assert e.values().numel() == 0 and e.stride() == 2 and e.timestamps.numel() == 0
+    assert "counts=(8,)" in str(c)
+    x = KeyedExtendedJaggedTensor(["k0", "k1"], torch.arange(4), lengths=torch.tensor([1, 1, 1, 1]), extra=torch.tensor([.1, .2, .3, .4]))
+    p0, p1 = x.split([1, 1])
+    assert p1.extra.tolist() == pytest.approx([.3, .4]) and x.to_base().keys() == ["k0", "k1"]
+    with pytest.raises(ValueError):
+        KeyedExtendedJaggedTensor(["k", "k"], torch.arange(2), lengths=torch.tensor([1, 1]))
+    with pytest.raises(TypeError):
+        KeyedExtendedJaggedTensor(["k"], torch.arange(2), lengths=torch.tensor([2]), length_per_key=[2.0])
+    with pytest.raises(ValueError):
+        KeyedExtendedJaggedTensor(["k"], torch.arange(2), lengths=torch.tensor([2]), extra=torch.arange(3))
+    with pytest.raises(ValueError):
+        KeyedExtendedJaggedTensor(["k"], torch.arange(2))
