@@ -106,3 +106,165 @@ def path_safe_check(name: str, value: Any, must_exist: bool = False) -> str:
     if must_exist:
         v.check_exists()
     return v.validate()
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Typed validators and the decorator form (reference: validator.py:99-196 para_checker_decorator, :199-330 Class / List /
+# Or / And / Option validators, :482-620 numeric validators, :720-780 FileValidator)
+# ----------------------------------------------------------------------------------------------------------------------
+class NumValidator(Validator):
+    """Number in a closed, open or half-open interval; ``bool`` is never a number here."""
+
+    def __init__(self, value: Any, name: str = "value", min_value=None, max_value=None, interval: str = "[]") -> None:
+        super().__init__(value, name)
+        if interval not in ("[]", "()", "(]", "[)"):
+            raise ValueError("interval must be one of [] () (] [)")
+        self.check_type(int, float)
+        lo_open, hi_open = interval[0] == "(", interval[1] == ")"
+        self.add(lambda v: (min_value is None or (v > min_value if lo_open else v >= min_value))
+                 and (max_value is None or (v < max_value if hi_open else v <= max_value)),
+                 "must be in %s%s, %s%s" % (interval[0], min_value, max_value, interval[1]))
+
+
+class IntValidator(NumValidator):
+    def __init__(self, value: Any, name: str = "value", min_value: Optional[int] = None, max_value: Optional[int] = None,
+                 interval: str = "[]") -> None:
+        super().__init__(value, name, min_value, max_value, interval)
+        self._checks.insert(0, (lambda v: isinstance(v, int) and not isinstance(v, bool), "must be an int"))
+
+
+class FloatValidator(NumValidator):
+    def __init__(self, value: Any, name: str = "value", min_value: Optional[float] = None, max_value: Optional[float] = None,
+                 interval: str = "[]") -> None:
+        super().__init__(value, name, min_value, max_value, interval)
+        self._checks.insert(0, (lambda v: isinstance(v, float), "must be a float"))
+
+
+class Convert2intValidator(IntValidator):
+    """A string (or number) that converts to an int inside the range; ``validate`` returns the int."""
+
+    def __init__(self, value: Any, name: str = "value", min_value: Optional[int] = None, max_value: Optional[int] = None) -> None:
+        try:
+            conv = int(value) if not isinstance(value, bool) else value
+        except (TypeError, ValueError):
+            conv = value
+        super().__init__(conv, name, min_value, max_value)
+
+
+class _Optional:
+    """Mixin: ``None`` passes."""
+
+    def validate(self):  # type: ignore[override]
+        return None if self.value is None else super().validate()  # type: ignore[misc]
+
+
+class OptionalIntValidator(_Optional, IntValidator):
+    pass
+
+
+class OptionalFloatValidator(_Optional, FloatValidator):
+    pass
+
+
+class OptionalStringValidator(_Optional, StringValidator):
+    pass
+
+
+class ClassValidator(Validator):
+    def __init__(self, value: Any, name: str = "value", classes=()) -> None:
+        super().__init__(value, name)
+        classes = tuple(classes) if isinstance(classes, (list, tuple)) else (classes,)
+        self.add(lambda v: isinstance(v, classes), "must be an instance of %s" % "/".join(c.__name__ for c in classes))
+
+
+class OptionValidator(Validator):
+    def __init__(self, value: Any, name: str = "value", options: Iterable = ()) -> None:
+        super().__init__(value, name)
+        self.check_in(options)
+
+
+class ListValidator(Validator):
+    """Every element passes ``sub_validator(element, name[i], **kwargs)``; optional length bounds."""
+
+    def __init__(self, value: Any, name: str = "value", sub_validator: type = Validator, min_len: int = 0,
+                 max_len: Optional[int] = None, **kwargs) -> None:
+        super().__init__(value, name)
+        self.check_type(list, tuple).check_length(min_len, max_len)
+
+        def all_ok(v):
+            for i, x in enumerate(v):
+                sub_validator(x, "%s[%d]" % (name, i), **kwargs).validate()
+            return True
+
+        self.add(all_ok, "has an invalid element")
+
+
+class OrValidator(Validator):
+    """Passes when at least one of the given validators passes."""
+
+    def __init__(self, value: Any, name: str = "value", options: Iterable[Validator] = ()) -> None:
+        super().__init__(value, name)
+        opts = list(options)
+        self.add(lambda _v: any(o.is_valid() for o in opts), "matches none of the accepted forms")
+
+
+class AndValidator(Validator):
+    def __init__(self, value: Any, name: str = "value", options: Iterable[Validator] = ()) -> None:
+        super().__init__(value, name)
+        opts = list(options)
+        self.add(lambda _v: all(o.is_valid() for o in opts), "fails one of the required checks")
+
+
+class FileValidator(StringValidator):
+    """An existing regular file that may be trusted as input: bounded size, not a symbolic link, owned by the caller (or
+    root), not writable by group / others."""
+
+    def __init__(self, value: Any, name: str = "file", max_len: int = 1024) -> None:
+        super().__init__(value, name, max_len)
+        self.add(lambda v: ".." not in v.replace("\\", "/").split("/"), "must not contain '..'")
+
+    def check_not_soft_link(self) -> "FileValidator":
+        return self.add(lambda v: not os.path.islink(v), "must not be a symbolic link")  # type: ignore[return-value]
+
+    def check_file_size(self, max_size: int = 1 << 40, min_size: int = 0) -> "FileValidator":
+        return self.add(lambda v: os.path.isfile(v) and min_size <= os.path.getsize(v) <= max_size,
+                        "must be a file of %d..%d bytes" % (min_size, max_size))  # type: ignore[return-value]
+
+    def check_user_group(self) -> "FileValidator":
+        return self.add(lambda v: os.stat(v).st_uid in (os.geteuid(), 0), "must be owned by the calling user or root")  # type: ignore[return-value]
+
+    def check_file_mode(self, unsupported_mode: int = 0o022) -> "FileValidator":
+        return self.add(lambda v: (os.stat(v).st_mode & unsupported_mode) == 0,
+                        "must not be writable by group or others")  # type: ignore[return-value]
+
+
+def para_checker_decorator(check_option_list: List[tuple]):
+    """``@para_checker_decorator([("lr", FloatValidator, {"min_value": 0.0}), (["a", "b"], ClassValidator, {"classes": int})])``
+    validates the named arguments of the decorated function (positional or keyword, defaults included) before the call.
+    Each option is ``(name or list of names, validator class, constructor keywords[, list of chain methods to call])``."""
+    import functools
+    import inspect
+
+    def deco(func):
+        sig = inspect.signature(func)
+
+        @functools.wraps(func)
+        def wrapper(*args, **kwargs):
+            bound = sig.bind(*args, **kwargs)
+            bound.apply_defaults()
+            for opt in check_option_list:
+                names, cls = opt[0], opt[1]
+                kw = dict(opt[2]) if len(opt) > 2 and opt[2] else {}
+                chain = list(opt[3]) if len(opt) > 3 and opt[3] else []
+                for n in (names if isinstance(names, (list, tuple)) else [names]):
+                    if n not in bound.arguments:
+                        raise ValidationError("%s() has no argument %r to validate" % (func.__name__, n))
+                    v = cls(bound.arguments[n], n, **kw)
+                    for m in chain:
+                        getattr(v, m)()
+                    v.validate()
+            return func(*args, **kwargs)
+
+        return wrapper
+
+    return deco

@@ -54,7 +54,7 @@ def run_selfcheck(env: ShardingEnv, peer: Optional[PeerGroup], device: torch.dev
     of = fused(kjt).values()
     kjt2 = KeyedJaggedTensor(["sf%d" % i for i in range(len(rows))], ids.clone(), lengths=ones.clone(), stride=local_batch)
     oc = coll(kjt2).values()
-    d_pooled = float((of.float() - oc.float()).abs().max())
+    d_pooled = float((of.detach().float() - oc.detach().float()).abs().max())
     of.backward(dout)
     oc.backward(dout)
     if hasattr(fused, "join_exchange"):
