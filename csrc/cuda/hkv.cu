@@ -51,7 +51,12 @@ struct HkvTable {
   // an earlier one.  touch may be null (no protection).
   unsigned* touch;
   unsigned epoch;
+  // counters[0..3]: keys inserted into an empty slot, keys that displaced a resident key, keys rejected, bucket-lock
+  // timeouts - accumulated over the table's life (may be null)
+  unsigned long long* counters;
 };
+
+constexpr unsigned LOCKED_STAMP = 0xFFFFFFFFu;     // touch value of a slot pinned by rb_hkv_lock: never a victim
 
 struct InitArgs {
   int mode;
@@ -170,7 +175,7 @@ hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ key
     const unsigned dg = digest_of(h);
     const bool need_lock = insert || update_score;
     if (need_lock && !lock_bucket(t.locks + b, lane, status)) {
-      if (lane == 0) { out_slots[i] = -1; if (out_status) out_status[i] = ST_LOCK_TIMEOUT; }
+      if (lane == 0) { out_slots[i] = -1; if (out_status) out_status[i] = ST_LOCK_TIMEOUT; if (t.counters) atomicAdd(t.counters + 3, 1ull); }
       continue;
     }
     const unsigned d4 = __ldcg(reinterpret_cast<const unsigned*>(t.digests + b * BUCKET) + lane);  // L2: L1 may be stale
@@ -180,7 +185,7 @@ hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ key
       if (lane == 0) {
         const long long s = b * BUCKET + pos;
         if (update_score) t.scores[s] = new_score(t.evict_strategy, __ldcg(t.scores + s), false, scores_in, i);
-        if (insert && t.touch) t.touch[s] = t.epoch;
+        if (insert && t.touch && t.touch[s] != LOCKED_STAMP) t.touch[s] = t.epoch;
       }
     } else if (!insert) {
       st = ST_MISSING;
@@ -204,7 +209,7 @@ hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ key
         bool any_free = false;                   // a slot not handed out by this launch
         for (int j = 0; j < 4; ++j) {
           const long long sl = b * BUCKET + lane * 4 + j;
-          if (t.touch && __ldcg(t.touch + sl) == t.epoch) continue;
+          if (t.touch) { const unsigned tv = __ldcg(t.touch + sl); if (tv == t.epoch || tv == LOCKED_STAMP) continue; }
           const unsigned long long s = __ldcg(t.scores + sl);
           if (!any_free || s < best) { best = s; best_pos = lane * 4 + j; }
           any_free = true;
@@ -253,6 +258,7 @@ hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ key
     if (lane == 0) {
       out_slots[i] = (st == ST_MISSING || st == ST_REJECTED) ? -1 : b * BUCKET + pos;
       if (out_status) out_status[i] = st;
+      if (t.counters && st >= ST_INSERTED && st <= ST_REJECTED) atomicAdd(t.counters + (st - ST_INSERTED), 1ull);
     }
   }
 }
@@ -281,12 +287,44 @@ hkv_erase_kernel(HkvTable t, const unsigned long long* __restrict__ keys, long l
   }
 }
 
+// pin == 1: resident keys become ineligible as eviction victims until unpinned (flags[i] = found; slots[i] = slot or -1);
+// pin == 0: the pin is lifted.  The reference's lock / unlock hide a key from concurrent writers for the same purpose:
+// rows that a caller holds pointers to must not be recycled under it (csrc/hkv_variable.h:178-190).
+__global__ void __launch_bounds__(256)
+hkv_pin_kernel(HkvTable t, const unsigned long long* __restrict__ keys, long long n, int pin, long long* __restrict__ out_slots,
+               unsigned char* __restrict__ flags, int* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; i < n; i += warps_total) {
+    const unsigned long long key = keys[i];
+    long long slot = -1;
+    if (key != EMPTY_KEY && t.touch) {
+      const unsigned long long h = hash64(key);
+      const long long b = static_cast<long long>(h & static_cast<unsigned long long>(t.num_buckets - 1));
+      if (lock_bucket(t.locks + b, lane, status)) {
+        const unsigned d4 = __ldcg(reinterpret_cast<const unsigned*>(t.digests + b * BUCKET) + lane);
+        const int pos = find_in_bucket(t, b, key, digest_of(h), d4, lane);
+        if (pos >= 0) {
+          slot = b * BUCKET + pos;
+          if (lane == 0) t.touch[slot] = pin ? LOCKED_STAMP : 0u;
+        }
+        unlock_bucket(t.locks + b, lane);
+      }
+    }
+    if (lane == 0) {
+      if (out_slots) out_slots[i] = slot;
+      if (flags) flags[i] = slot >= 0 ? 1 : 0;
+    }
+  }
+}
+
 __global__ void hkv_clear_kernel(HkvTable t) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long s = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; s < t.capacity; s += stride) {
     t.keys[s] = EMPTY_KEY;
     t.scores[s] = 0ull;
     t.digests[s] = static_cast<unsigned char>(EMPTY_DIGEST);
+    if (t.touch) t.touch[s] = 0u;
     if (s < t.num_buckets) t.locks[s] = 0;
     if (s == 0) *t.size = 0ull;
   }
@@ -456,9 +494,9 @@ inline int warp_grid(long long n, int num_sms) {
 
 }  // namespace
 
-// The table descriptor is passed as a flat array of 15 64-bit words (see recsdk_b200/dynamic/hkv.py):
+// The table descriptor is passed as a flat array of 16 64-bit words (see recsdk_b200/dynamic/hkv.py):
 // keys, scores, digests, locks, values_hbm, values_host, hbm_rows, capacity, num_buckets, row_dim, emb_dim,
-// evict_strategy, size, touch (launch stamps, may be 0), epoch (stamp of the current launch)
+// evict_strategy, size, touch (launch stamps, may be 0), epoch (stamp of the current launch), counters (may be 0)
 static HkvTable unpack(const long long* d) {
   HkvTable t;
   t.keys = reinterpret_cast<unsigned long long*>(d[0]);
@@ -472,6 +510,7 @@ static HkvTable unpack(const long long* d) {
   t.size = reinterpret_cast<unsigned long long*>(d[12]);
   t.touch = reinterpret_cast<unsigned*>(d[13]);
   t.epoch = static_cast<unsigned>(d[14]);
+  t.counters = reinterpret_cast<unsigned long long*>(d[15]);
   return t;
 }
 
@@ -516,6 +555,14 @@ RB_API int rb_hkv_find_or_insert_n(const long long* desc, const void* keys, long
       t, reinterpret_cast<const unsigned long long*>(keys), n_max, insert, update_score,
       reinterpret_cast<const unsigned long long*>(scores_in), out_slots, reinterpret_cast<unsigned char*>(out_status), ia,
       ev, status, n_dev);
+  return static_cast<int>(cudaGetLastError());
+}
+
+RB_API int rb_hkv_pin(const long long* desc, const void* keys, long long n, int pin, long long* out_slots, void* flags,
+                      int num_sms, int* status, cudaStream_t st) {
+  if (n == 0) return 0;
+  hkv_pin_kernel<<<warp_grid(n, num_sms), 256, 0, st>>>(unpack(desc), reinterpret_cast<const unsigned long long*>(keys), n, pin,
+                                                       out_slots, reinterpret_cast<unsigned char*>(flags), status);
   return static_cast<int>(cudaGetLastError());
 }
 

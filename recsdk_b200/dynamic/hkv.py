@@ -131,11 +131,13 @@ class HKVTable(_VariableInterface):
         # launch stamps: a slot handed out by a find_or_insert launch is not evicted by a later warp of the same launch
         self.touch = torch.zeros(cap, dtype=torch.int32, device=dev)
         self._epoch = 0
+        if not hasattr(self, "_counters"):             # life-time counters survive growth
+            self._counters = torch.zeros(4, dtype=torch.int64, device=dev)
         host_ptr = self.values_host.data_ptr() if self.values_host is not None else 0
         self._desc = np.asarray([self.keys.data_ptr(), self.scores.data_ptr(), self.digests.data_ptr(),
                                  self.locks.data_ptr(), self.values_hbm.data_ptr(), host_ptr, hbm, cap, self.num_buckets,
                                  self.row_dim, self.dim, int(self.evict_strategy), self._size.data_ptr(),
-                                 self.touch.data_ptr(), 0], dtype=np.int64)
+                                 self.touch.data_ptr(), 0, self._counters.data_ptr()], dtype=np.int64)
 
     def _d(self) -> int:
         return self._desc.ctypes.data
@@ -219,6 +221,50 @@ class HKVTable(_VariableInterface):
             self.scatter(slots, values[acc], 0, values.shape[1], accumulate=True)
         if (~acc).any():
             self.insert_and_evict(keys[~acc], values[~acc], None if scores is None else scores[~acc])
+
+    # ------------------------------------------------------------------ pointers, pins, counters
+    def _pointers(self, slots: torch.Tensor) -> torch.Tensor:
+        """Device address of the value row of every slot (0 for slot -1); rows beyond ``hbm_rows`` live in mapped host memory."""
+        rb = self.row_dim * 4
+        hbm = self.values_hbm.data_ptr() + slots * rb
+        if self.values_host is not None:
+            host = self.values_host.data_ptr() + (slots - self.hbm_rows) * rb
+            hbm = torch.where(slots < self.hbm_rows, hbm, host)
+        return torch.where(slots >= 0, hbm, torch.zeros_like(hbm))
+
+    def find_pointers(self, keys: torch.Tensor, update_score: bool = False, scores: Optional[torch.Tensor] = None):
+        """-> (row addresses [n] int64, found mask): what the fused optimizer-on-pointer kernels of the reference consume
+        (``csrc/hkv_variable.h:193-205``)."""
+        slots, found = self.find(keys, update_score, scores)
+        return self._pointers(slots), found
+
+    def find_or_insert_pointers(self, keys: torch.Tensor, scores: Optional[torch.Tensor] = None):
+        slots, status, _ = self.find_or_insert(keys, scores)
+        return self._pointers(slots), status
+
+    def _pin(self, keys: torch.Tensor, pin: bool):
+        keys = keys.contiguous()
+        n = keys.numel()
+        slots = torch.empty(n, dtype=torch.int64, device=self.device)
+        flags = torch.empty(n, dtype=torch.uint8, device=self.device)
+        rc = _lib.lib().rb_hkv_pin(self._d(), keys.data_ptr(), n, int(pin), slots.data_ptr(), flags.data_ptr(), self._sms(),
+                                   _lib.status_tensor(self.device).data_ptr(), self._st())
+        _lib.check(rc, "rb_hkv_pin")
+        return slots, flags.bool()
+
+    def lock(self, keys: torch.Tensor):
+        """Pin resident keys: until ``unlock`` they are never chosen as eviction victims, so row pointers handed out for
+        them stay valid.  -> (slots, found mask)."""
+        return self._pin(keys, True)
+
+    def unlock(self, keys: torch.Tensor):
+        return self._pin(keys, False)
+
+    def counters(self) -> Dict[str, int]:
+        """Life-time counts of the probe kernel's outcomes (a cheap health signal: a growing ``rejected`` or
+        ``lock_timeouts`` count means the table is too small or contended)."""
+        c = self._counters.tolist()
+        return {"inserted": c[0], "evicted_other": c[1], "rejected": c[2], "lock_timeouts": c[3]}
 
     def erase(self, keys: torch.Tensor) -> None:
         keys = keys.contiguous()

@@ -161,3 +161,28 @@ def test_slots_of_one_launch_are_never_evicted_by_that_launch():
     s3, st3, _ = t.find_or_insert(fresh, torch.full((50,), 1000, dtype=torch.int64, device=DEV))
     assert (st3 == ST_EVICTED_OTHER).all() and s3.unique().numel() == 50
     _lib.check_status()
+
+
+def test_pinned_keys_survive_eviction_pointers_and_counters():
+    t = HKVTable(8, 128, DEV, evict_strategy=EvictStrategy.LFU, max_capacity=128, init=InitializerArgs(mode=InitMode.DEBUG))
+    keys = _keys(128, seed=21)
+    slots, st, _ = t.find_or_insert(keys)                       # fills the single bucket, every score 1
+    assert (st == ST_INSERTED).all()
+    pinned = keys[:100]
+    pslots, found = t.lock(torch.cat([pinned, _keys(3, seed=22) + (1 << 45)]))
+    assert found[:100].all() and not found[100:].any() and torch.equal(pslots[:100], slots[:100])
+    # 60 newcomers with a high score: only the 28 unpinned residents can be displaced
+    new = _keys(60, seed=23) + (1 << 46)
+    _, st2, _ = t.find_or_insert(new, torch.full((60,), 1000, dtype=torch.int64, device=DEV))
+    assert int((st2 == ST_EVICTED_OTHER).sum()) == 28 and int((st2 == ST_REJECTED).sum()) == 32
+    assert t.find(pinned)[1].all()
+    ptrs, f = t.find_pointers(pinned[:5])
+    base, rb = t.values_hbm.data_ptr(), t.row_dim * 4
+    assert f.all() and torch.equal(ptrs, base + slots[:5] * rb)
+    t.unlock(pinned)
+    more = _keys(100, seed=24) + (1 << 47)
+    _, st3, _ = t.find_or_insert(more, torch.full((100,), 5000, dtype=torch.int64, device=DEV))
+    assert int((st3 == ST_EVICTED_OTHER).sum()) == 100          # pins lifted: everything resident was fair game
+    c = t.counters()
+    assert c["inserted"] == 128 and c["evicted_other"] == 128 and c["rejected"] == 32 and c["lock_timeouts"] == 0
+    _lib.check_status()
