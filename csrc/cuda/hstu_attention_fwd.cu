@@ -44,7 +44,39 @@ struct HstuFwdParams {
   int box_rows;              // rows per TMA box for K/V (64, or page_size when smaller)
   int bucket_cap;            // min(num_buckets, floor(log(7e16) / divisor)): replaces the clamp of |dt| from above
   int* status;
+  // dense operands of the reference's calling convention (both optional): an additive bias [B][H][S][S] and a
+  // multiplicative 0/1 mask of the same indexing; element (b, h, query position, key position) sits at
+  // base + b * stride_b + h * stride_h + position_q * ld + position_k (strides in elements; stride_h may be 0)
+  const void* dbias; int dbias_kind;      // 0 none, 1 bf16, 2 fp32
+  long long db_sb, db_sh, db_ld;
+  const void* dmask; int dmask_kind;      // 0 none, 1 uint8 / bool, 2 bf16, 3 fp32
+  long long dm_sb, dm_sh, dm_ld;
+  int dn_rows, dn_cols;                   // extent of the dense operands' last two dims: nothing is read outside it
 };
+
+// 8 consecutive elements of a dense operand row -> fp32 (vector load when the address is 16-byte aligned and all 8
+// are inside the row, element loads with a fill value otherwise)
+__device__ __forceinline__ void load_dense8(const void* base, int kind, long long off, int valid, float fill, float (&o)[8]) {
+  if (kind == 1) {                                          // bf16 (bias kind 1)
+    const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(base) + off;
+    if (valid >= 8 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+      float2 a = rb::unpack_bf16(u.x), b = rb::unpack_bf16(u.y), c = rb::unpack_bf16(u.z), d = rb::unpack_bf16(u.w);
+      o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y; o[4] = c.x; o[5] = c.y; o[6] = d.x; o[7] = d.y;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = i < valid ? __bfloat162float(p[i]) : fill;
+    }
+  } else if (kind == 2) {                                   // fp32
+    const float* p = reinterpret_cast<const float*>(base) + off;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = i < valid ? __ldg(p + i) : fill;
+  } else {                                                  // uint8
+    const unsigned char* p = reinterpret_cast<const unsigned char*>(base) + off;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = i < valid ? (p[i] ? 1.f : 0.f) : fill;
+  }
+}
 
 template <int D> struct FwdCfg {
   static constexpr int CH = D / 64;                       // 64-column swizzle chunks per row
@@ -293,12 +325,44 @@ hstu_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         rb::tmem_ld_wait();
         uint32_t pk[16];
         const int j0 = kb * BKV + c * 32;
+        if (p.dbias_kind && i_local < len_q && pi < p.dn_rows) {              // dense additive bias: this thread's 32 keys of its query row
+          const long long roff = static_cast<long long>(b) * p.db_sb + static_cast<long long>(h) * p.db_sh +
+                                 static_cast<long long>(pi) * p.db_ld + j0;
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            float bv[8];
+            load_dense8(p.dbias, p.dbias_kind, roff + e, min(len_k, p.dn_cols) - (j0 + e), 0.f, bv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[e + i] = __float_as_uint(__uint_as_float(r[e + i]) + bv[i]);
+          }
+        }
         if (full)
           activate_chunk<BT, BP, false>(r, pk, ts_i, my_ts, tsw_s, my_pos, lane, k_log, p.bucket_cap, half_alpha, p.scale, pi, j0,
                                         len_k, p.causal, nctx, ntgt, gs);
         else
           activate_chunk<BT, BP, true>(r, pk, ts_i, my_ts, tsw_s, my_pos, lane, k_log, p.bucket_cap, half_alpha, p.scale, pi, j0,
                                        len_k, p.causal, nctx, ntgt, gs);
+        if (p.dmask_kind) {                                 // dense 0/1 mask on the activated values
+          const long long roff = static_cast<long long>(b) * p.dm_sb + static_cast<long long>(h) * p.dm_sh +
+                                 static_cast<long long>(pi) * p.dm_ld + j0;
+          const int mk = p.dmask_kind == 1 ? 0 : (p.dmask_kind == 2 ? 1 : 2);    // load_dense8 kinds: 0 uint8, 1 bf16, 2 fp32
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            float mv[8];
+            if (i_local < len_q && pi < p.dn_rows) load_dense8(p.dmask, mk, roff + e, min(len_k, p.dn_cols) - (j0 + e), 0.f, mv);
+            else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) mv[i] = 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+              uint32_t w = pk[(e + i) >> 1];
+              if (mv[i] == 0.f) w &= 0xFFFF0000u;
+              if (mv[i + 1] == 0.f) w &= 0x0000FFFFu;
+              pk[(e + i) >> 1] = w;
+            }
+          }
+        }
         rb::tmem_st_32x16(T_P + buf * 64 + lane_sel + c * 16, pk);
       }
       rb::tmem_st_wait();
@@ -379,13 +443,15 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
 // q [Tq][ld_q], k / v [Tk][ld_k] bf16 with head h at columns h*D (D = 64 or 128), or - when page_ids is given -
 // kv_cache [pages][2][page_size][H*D] (k and v are then both the cache base).  Offsets are int32 device arrays.
 // Row strides in elements, multiples of 8.  Returns 0 / cudaError_t / negative argument error.
-RB_API int rb_hstu_attn_fwd(const void* q, long long ld_q, long long Tq, const void* k, const void* v, long long ld_k,
+static int hstu_attn_fwd_impl(const void* q, long long ld_q, long long Tq, const void* k, const void* v, long long ld_k,
                             long long Tk, const int* q_offsets, const int* k_offsets, int B, int H, int D,
                             int max_len_q, void* out, long long ld_o, float alpha, float scale, int causal,
                             const int* num_context, const int* num_target, int target_group_size, const float* ts,
                             const float* ts_w, int num_buckets, float ts_divisor, const float* pos_w, int pos_len,
                             const int* page_ids, const int* page_indptr, int page_size, long long num_pages,
-                            int* status, cudaStream_t st) {
+                            int* status, cudaStream_t st, const void* dbias, int dbias_kind, long long db_sb, long long db_sh,
+                            long long db_ld, const void* dmask, int dmask_kind, long long dm_sb, long long dm_sh,
+                            long long dm_ld, int dn_rows, int dn_cols) {
   if (B == 0 || H == 0 || max_len_q <= 0) return 0;
   if ((ld_q % 8) || (ld_k % 8) || (ld_o % 8) || (D != 64 && D != 128)) return -3;
   if (num_buckets >= 192) return -4;
@@ -399,6 +465,9 @@ RB_API int rb_hstu_attn_fwd(const void* q, long long ld_q, long long Tq, const v
     p.bucket_cap = num_buckets < hi ? num_buckets : hi;
   }
   p.page_ids = page_ids; p.page_indptr = page_indptr; p.page_size = page_size; p.status = status;
+  p.dbias = dbias; p.dbias_kind = dbias ? dbias_kind : 0; p.db_sb = db_sb; p.db_sh = db_sh; p.db_ld = db_ld;
+  p.dmask = dmask; p.dmask_kind = dmask ? dmask_kind : 0; p.dm_sb = dm_sb; p.dm_sh = dm_sh; p.dm_ld = dm_ld;
+  p.dn_rows = dn_rows; p.dn_cols = dn_cols;
   CUtensorMap tq, tk, tv;
   int rc = make_map(&tq, q, Tq, static_cast<long long>(H) * D, ld_q, 64);
   if (rc) return rc;
@@ -426,4 +495,35 @@ RB_API int rb_hstu_attn_fwd(const void* q, long long ld_q, long long Tq, const v
   if (D == 64) return RB_FWD(64);
   return RB_FWD(128);
 #undef RB_FWD
+}
+
+
+RB_API int rb_hstu_attn_fwd(const void* q, long long ld_q, long long Tq, const void* k, const void* v, long long ld_k,
+                            long long Tk, const int* q_offsets, const int* k_offsets, int B, int H, int D,
+                            int max_len_q, void* out, long long ld_o, float alpha, float scale, int causal,
+                            const int* num_context, const int* num_target, int target_group_size, const float* ts,
+                            const float* ts_w, int num_buckets, float ts_divisor, const float* pos_w, int pos_len,
+                            const int* page_ids, const int* page_indptr, int page_size, long long num_pages,
+                            int* status, cudaStream_t st) {
+  return hstu_attn_fwd_impl(q, ld_q, Tq, k, v, ld_k, Tk, q_offsets, k_offsets, B, H, D, max_len_q, out, ld_o, alpha, scale, causal,
+                            num_context, num_target, target_group_size, ts, ts_w, num_buckets, ts_divisor, pos_w, pos_len,
+                            page_ids, page_indptr, page_size, num_pages, status, st, nullptr, 0, 0, 0, 0, nullptr, 0, 0, 0, 0, 0, 0);
+}
+
+// Same forward with the dense operands of the reference's convention: attn_bias (bias_kind 1 bf16 / 2 fp32) added to
+// Q K^T before the activation and a 0/1 mask (mask_kind 1 uint8 / 2 bf16 / 3 fp32) multiplied onto the result; both are
+// indexed [batch][head][query position][key position] through element strides (a head stride of 0 broadcasts);
+// positions at or beyond dense_rows / dense_cols read as bias 0, mask 0.
+RB_API int rb_hstu_attn_fwd_dense(const void* q, long long ld_q, long long Tq, const void* k, const void* v, long long ld_k,
+                                  long long Tk, const int* q_offsets, const int* k_offsets, int B, int H, int D,
+                                  int max_len_q, void* out, long long ld_o, float alpha, float scale, int causal,
+                                  const int* num_context, const int* num_target, int target_group_size,
+                                  const void* attn_bias, int bias_kind, long long bias_stride_b, long long bias_stride_h,
+                                  long long bias_ld, const void* mask, int mask_kind, long long mask_stride_b,
+                                  long long mask_stride_h, long long mask_ld, int dense_rows, int dense_cols, int* status,
+                                  cudaStream_t st) {
+  return hstu_attn_fwd_impl(q, ld_q, Tq, k, v, ld_k, Tk, q_offsets, k_offsets, B, H, D, max_len_q, out, ld_o, alpha, scale, causal,
+                            num_context, num_target, target_group_size, nullptr, nullptr, 0, 1.f, nullptr, 0, nullptr, nullptr, 0,
+                            0, status, st, attn_bias, bias_kind, bias_stride_b, bias_stride_h, bias_ld, mask, mask_kind,
+                            mask_stride_b, mask_stride_h, mask_ld, dense_rows, dense_cols);
 }

@@ -80,8 +80,11 @@ def _i32(t: Optional[torch.Tensor], device) -> Optional[torch.Tensor]:
 def hstu_attn_fwd(q, k, v, q_offsets, k_offsets, max_len_q: int, alpha: float, scale: float, causal: bool = True,
                   num_context=None, num_target=None, target_group_size: int = 0, ts=None, ts_w=None,
                   ts_divisor: float = 0.301, pos_w=None, out: Optional[torch.Tensor] = None,
-                  page_ids=None, page_indptr=None, page_size: int = 0) -> torch.Tensor:
-    """Forward kernel launch.  ``q`` [Tq,H,D] (row stride may exceed H*D, e.g. a slice of a fused projection);
+                  page_ids=None, page_indptr=None, page_size: int = 0, attn_bias: Optional[torch.Tensor] = None,
+                  attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Forward kernel launch.  ``attn_bias`` / ``attn_mask``: dense ``[B, H or 1, S, S]`` operands indexed by (query
+    position, key position) - the bias (bf16 / fp32) is added to ``Q K^T`` before the activation, the 0/1 mask (bool /
+    uint8 / bf16 / fp32) multiplies the result; they replace the in-kernel time / position bias and are not paged.  ``q`` [Tq,H,D] (row stride may exceed H*D, e.g. a slice of a fused projection);
     ``k``/``v`` likewise, or - paged - both the cache tensor ``[pages, 2, page, H, D]``."""
     assert q.is_cuda and q.dtype == torch.bfloat16
     Tq, H, D = q.shape
@@ -106,6 +109,35 @@ def hstu_attn_fwd(q, k, v, q_offsets, k_offsets, max_len_q: int, alpha: float, s
     ts_, tsw_, pw_ = f32(ts), f32(ts_w), f32(pos_w)
     nc, nt = _i32(num_context, dev), _i32(num_target, dev)
     pid, pip = _i32(page_ids, dev), _i32(page_indptr, dev)
+    if attn_bias is not None or attn_mask is not None:
+        if paged or ts_ is not None or pw_ is not None:
+            raise ValueError("dense attn_bias / attn_mask cannot be combined with paged K/V or the in-kernel relative bias")
+
+        def dense(t, kinds):
+            if t is None:
+                return None, 0, 0, 0, 0
+            if t.dim() != 4 or t.shape[0] != B or t.shape[1] not in (1, H):
+                raise ValueError("dense operand must be [B, H or 1, S, S], got %s" % (tuple(t.shape),))
+            if t.dtype == torch.bool:
+                t = t.to(torch.uint8)
+            if t.dtype not in kinds:
+                t = t.to(torch.float32)
+            if t.stride(3) != 1:
+                t = t.contiguous()
+            keep.append(t)
+            return t.data_ptr(), kinds[t.dtype], t.stride(0), (t.stride(1) if t.shape[1] == H else 0), t.stride(2)
+
+        keep: list = []
+        bp_, bk_, bsb, bsh, bld = dense(attn_bias, {torch.bfloat16: 1, torch.float32: 2})
+        mp_, mk_, msb, msh, mld = dense(attn_mask, {torch.uint8: 1, torch.bfloat16: 2, torch.float32: 3})
+        rc = _lib.lib().rb_hstu_attn_fwd_dense(
+            q.data_ptr(), q.stride(0), Tq, kp, vp, ld_k, Tk, qo.data_ptr(), ko.data_ptr(), B, H, D, int(max_len_q),
+            out.data_ptr(), out.stride(0), float(alpha), float(scale), int(causal), _lib.ptr(nc), _lib.ptr(nt),
+            int(target_group_size), bp_, bk_, bsb, bsh, bld, mp_, mk_, msb, msh, mld,
+            min(t.shape[2] for t in keep), min(t.shape[3] for t in keep),
+            _lib.status_tensor(dev).data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(rc, "rb_hstu_attn_fwd_dense")
+        return out
     rc = _lib.lib().rb_hstu_attn_fwd(
         q.data_ptr(), q.stride(0), Tq, kp, vp, ld_k, Tk, qo.data_ptr(), ko.data_ptr(), B, H, D, int(max_len_q),
         out.data_ptr(), out.stride(0), float(alpha), float(scale), int(causal), _lib.ptr(nc), _lib.ptr(nt),

@@ -57,8 +57,51 @@ def _dense_ref(q, k, v, mask, attn_bias, mask_type, silu_scale, alpha=1.0):
     return torch.einsum("bnij,bjnd->bind", p.to(q.dtype).float(), v.float()).to(q.dtype)
 
 
+class _DenseBiasFn(torch.autograd.Function):
+    """Dense-layout HSTU attention with the reference's ``attn_bias`` / custom-mask operands: forward on the tcgen05 kernel
+    (the bias tile is read beside the S tile, the mask applied to P), gradients - including the bias gradient - from the
+    fp32 statement of the same math."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, attn_bias, mask, mask_type, scale):
+        from .hstu_attention import hstu_attn_fwd
+
+        B, S, N, D = q.shape
+        offs = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=q.device)
+        out = hstu_attn_fwd(q.reshape(B * S, N, D), k.reshape(B * S, N, D), v.reshape(B * S, N, D), offs, offs, S, 1.0, scale,
+                            causal=mask_type == 0, attn_bias=attn_bias, attn_mask=mask if mask_type == 3 else None)
+        ctx.save_for_backward(q, k, v, attn_bias if attn_bias is not None else q.new_zeros(0),
+                              mask if mask is not None else q.new_zeros(0))
+        ctx.meta = (mask_type, scale, attn_bias is not None, mask is not None)
+        return out.view(B, S, N, D)
+
+    @staticmethod
+    def backward(ctx, grad):
+        q, k, v, bias, mask = ctx.saved_tensors
+        mask_type, scale, has_b, has_m = ctx.meta
+        with torch.enable_grad():
+            qq, kk, vv = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+            bb = bias.detach().float().requires_grad_(True) if has_b else None
+            out = _dense_ref(qq, kk, vv, mask if has_m else None, bb, mask_type, scale)
+            gs = torch.autograd.grad(out, [qq, kk, vv] + ([bb] if has_b and ctx.needs_input_grad[3] else []), grad.float())
+        db = gs[3].to(bias.dtype) if has_b and ctx.needs_input_grad[3] else None
+        return gs[0].to(q.dtype), gs[1].to(k.dtype), gs[2].to(v.dtype), db, None, None, None
+
+
+def _dense_kernel_ok(q, k, attn_bias, mask, mask_type) -> bool:
+    B, S, N, D = q.shape
+    if not (q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and k.shape[1] == S and mask_type in (0, 2, 3)):
+        return False
+    for t in (attn_bias, mask if mask_type == 3 else None):
+        if t is not None and (t.dim() != 4 or t.shape[0] != B or t.shape[1] not in (1, N) or t.shape[2] != S or t.shape[3] != S):
+            return False
+    return not (mask_type == 3 and mask is None)
+
+
 def hstu_dense(q, k, v, mask=None, attn_bias=None, mask_type: int = 0, max_seq_len: int = 0, silu_scale: float = 0.0):
     B, S, N, D = q.shape
+    if (attn_bias is not None or mask_type == 3) and _dense_kernel_ok(q, k, attn_bias, mask, mask_type):
+        return _DenseBiasFn.apply(q, k, v, attn_bias, mask, mask_type, silu_scale if silu_scale != 0.0 else 1.0 / S)
     if attn_bias is None and mask_type in (0, 2) and q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and k.shape[1] == S:
         offs = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=q.device)
         out = hstu_attention(q.reshape(B * S, N, D), k.reshape(B * S, N, D), v.reshape(B * S, N, D), offs, max_len_q=S, alpha=1.0,
@@ -89,12 +132,45 @@ def _jagged_common(q, k, v, mask, attn_bias, mask_type, max_seq_len, silu_scale,
     if mask_type == 1:
         raise NotImplementedError("upper-triangular masks are not supported")
     scale = silu_scale if silu_scale != 0.0 else 1.0 / max(max_seq_len, 1)
+    if (attn_bias is not None or mask_type == 3) and seq_offset_k is seq_offset and q.is_cuda and q.dtype == torch.bfloat16 \
+            and q.shape[2] in (64, 128) and v.shape[2] == q.shape[2] and num_context is None and num_target is None \
+            and not (mask_type == 3 and (mask is None or mask.dim() != 4)):
+        # the reference's main convention (relative bias passed as attn_bias): forward on the kernel
+        return _JaggedBiasFn.apply(q, k, v, attn_bias, mask, mask_type, scale, seq_offset, max_seq_len, alpha)
     if attn_bias is not None or mask_type == 3:
-        # materialised bias / custom mask: padded fp32 path
+        # remaining combinations (delta queries, context / target masks with a dense bias): padded fp32 path
         return _jagged_ref_bias(q, k, v, mask, attn_bias, mask_type, scale, seq_offset, seq_offset_k, num_context, num_target,
                                 target_group_size, alpha)
     return hstu_attention(q, k, v, seq_offset, seq_offset_k, max_len_q=max_seq_len, alpha=alpha, scale=scale, causal=mask_type == 0,
                           num_context=num_context, num_target=num_target, target_group_size=target_group_size)
+
+
+class _JaggedBiasFn(torch.autograd.Function):
+    """Jagged HSTU attention with a padded dense ``attn_bias`` ``[B, N, S_max, S_max]`` and / or custom mask: forward on the
+    tcgen05 kernel, gradients from the fp32 statement."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, attn_bias, mask, mask_type, scale, offsets, max_seq_len, alpha):
+        from .hstu_attention import hstu_attn_fwd
+
+        out = hstu_attn_fwd(q, k, v, offsets, offsets, max_seq_len, alpha, scale, causal=mask_type == 0, attn_bias=attn_bias,
+                            attn_mask=mask if mask_type == 3 else None)
+        ctx.save_for_backward(q, k, v, attn_bias if attn_bias is not None else q.new_zeros(0),
+                              mask if mask is not None else q.new_zeros(0), offsets)
+        ctx.meta = (mask_type, scale, alpha, attn_bias is not None, mask is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        q, k, v, bias, mask, offsets = ctx.saved_tensors
+        mask_type, scale, alpha, has_b, has_m = ctx.meta
+        with torch.enable_grad():
+            qq, kk, vv = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+            bb = bias.detach().float().requires_grad_(True) if has_b else None
+            out = _jagged_ref_bias(qq, kk, vv, mask if has_m else None, bb, mask_type, scale, offsets, offsets, None, None, 0, alpha)
+            want_b = has_b and ctx.needs_input_grad[3]
+            gs = torch.autograd.grad(out, [qq, kk, vv] + ([bb] if want_b else []), grad.float())
+        return (gs[0].to(q.dtype), gs[1].to(k.dtype), gs[2].to(v.dtype), gs[3].to(bias.dtype) if want_b else None) + (None,) * 6
 
 
 def _jagged_ref_bias(q, k, v, mask, attn_bias, mask_type, scale, qo, ko, num_context, num_target, gs, alpha):

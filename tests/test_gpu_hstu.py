@@ -137,3 +137,55 @@ def test_bwd_targets_and_autograd():
     assert q.grad is not None and k.grad.abs().sum() > 0 and pw.grad.abs().sum() > 0
     torch.cuda.synchronize()
     _lib.check_status()
+
+
+@pytest.mark.parametrize("D,S,heads_in_bias,mask_type", [(64, 200, True, 0), (128, 256, False, 0), (64, 333, True, 3), (64, 128, False, 2)])
+def test_dense_attn_bias_and_custom_mask_on_the_kernel(D, S, heads_in_bias, mask_type):
+    """The reference's main calling convention - relative bias passed as a dense ``attn_bias`` [B,N,S,S], optionally a custom
+    0/1 mask (mask_type 3) - runs on the tcgen05 forward kernel; per-row relative error against the fp32 statement, and
+    gradients (q, k, v, attn_bias) through the op."""
+    import torch
+
+    from recsdk_b200.ops import mxrec  # noqa: F401  (registers torch.ops.mxrec)
+    from recsdk_b200.ops.mxrec import _dense_ref
+
+    dev = torch.device("cuda", 0)
+    B, N = 2, 4
+    g = torch.Generator().manual_seed(S + D)
+    q, k, v = (torch.randn(B, S, N, D, generator=g).mul_(0.5).to(dev, torch.bfloat16).requires_grad_() for _ in range(3))
+    bias = (torch.randn(B, N if heads_in_bias else 1, S, S, generator=g) * 0.5).to(dev, torch.bfloat16).requires_grad_()
+    mask = None
+    if mask_type == 3:
+        mask = (torch.rand(B, 1, S, S, generator=g) < 0.6).to(dev)
+    out = torch.ops.mxrec.hstu_dense(q, k, v, mask, bias, mask_type, S, 1.0 / S)
+    ref_in = [t.detach().float().requires_grad_() for t in (q, k, v, bias)]
+    want = _dense_ref(ref_in[0], ref_in[1], ref_in[2], mask, ref_in[3], mask_type, 1.0 / S)
+    err = (out.float() - want).abs().amax(dim=(-1,))                       # per (batch, row, head)
+    scale = want.abs().amax(dim=(-1,)).clamp_min(1e-3)
+    assert float((err / scale).max()) < 3e-2, float((err / scale).max())
+    w = torch.randn(out.shape, generator=g).to(dev)
+    (out.float() * w).sum().backward()
+    (want * w).sum().backward()
+    for got, ref in zip((q, k, v, bias), ref_in):
+        rel = (got.grad.float() - ref.grad).abs().max() / ref.grad.abs().max().clamp_min(1e-6)
+        assert float(rel) < 3e-2, float(rel)
+
+
+def test_jagged_attn_bias_on_the_kernel():
+    import torch
+
+    from recsdk_b200.ops import mxrec  # noqa: F401
+    from recsdk_b200.ops.mxrec import _jagged_ref_bias
+
+    dev = torch.device("cuda", 0)
+    lens, N, D, Smax = [70, 300, 129], 2, 64, 320
+    offs = torch.tensor([0, 70, 370, 499], dtype=torch.int32, device=dev)
+    T = int(offs[-1])
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(T, N, D, generator=g).mul_(0.5).to(dev, torch.bfloat16) for _ in range(3))
+    bias = (torch.randn(len(lens), N, Smax, Smax, generator=g) * 0.5).to(dev, torch.bfloat16)
+    out = torch.ops.mxrec.hstu_jagged.equal(q, k, v, None, bias, 0, Smax, 1.0 / Smax, offs, None, None, 0, 1.0, False)
+    want = _jagged_ref_bias(q, k, v, None, bias, 0, 1.0 / Smax, offs, offs, None, None, 0, 1.0)
+    err = (out.float() - want.float()).abs().amax(dim=-1)
+    scale = want.float().abs().amax(dim=-1).clamp_min(1e-3)
+    assert float((err / scale).max()) < 3e-2
