@@ -17,9 +17,10 @@ runs, is the numerical oracle of the fused GPU path, and is the "NCCL-only" base
 """
 from __future__ import annotations
 
+import dataclasses
 import os
 from concurrent.futures import ThreadPoolExecutor
-from typing import Dict, List, Optional
+from typing import Any, Dict, List, Optional
 
 import numpy as np
 import torch
@@ -119,6 +120,25 @@ class _PooledLookup(torch.autograd.Function):
             gr = gr / lengths[bag].clamp(min=1).to(gr.dtype)[:, None]
         mod._apply_update(ti, rows, gr)
         return None, None, None, None, None, None, None
+
+
+@dataclasses.dataclass
+class DistState:
+    """One batch's way through the five input-distribution stages of one sharded module (split -> lengths all-to-all ->
+    id all-to-all -> id mapping -> device copy).  Host tensors throughout; futures / work handles of the stage in flight."""
+    module: Any
+    features: Any
+    F: int
+    B: int
+    orig_lengths: Optional[torch.Tensor] = None
+    split_future: Any = None
+    send_lengths: Optional[torch.Tensor] = None
+    send_ids: Optional[torch.Tensor] = None
+    recv_lengths: Optional[torch.Tensor] = None
+    recv_ids: Optional[torch.Tensor] = None
+    ids_work: Any = None
+    post_future: Any = None
+    mapped_ids: Optional[torch.Tensor] = None
 
 
 class CollectiveShardedEmbeddingBagCollection(nn.Module):
@@ -397,6 +417,65 @@ class CollectiveShardedEmbeddingBagCollection(nn.Module):
                 col += t.embedding_dim
             out = out * scale
         return KeyedTensor(self.feature_names, self.layout.feature_dims, out.to(self.out_dtype))
+
+    # ----------------------------------------------------------------- staged input dist (multi-line host pipeline)
+    def stage_split(self, features: KeyedJaggedTensor) -> "DistState":
+        """Stage 1 of 5: bucketize the batch's ids by owner rank on the input thread pool (returns at once)."""
+        assert features.keys() == self.feature_names
+        st = DistState(module=self, features=features, F=len(self.feature_names), B=features.stride())
+        st.orig_lengths = features.lengths().view(st.F, st.B)
+        st.split_future = self._in_pool.submit(self._bucketize, features)
+        return st
+
+    def stage_send_lengths(self, st: "DistState") -> torch.Tensor:
+        """The ``[W, F*B]`` lengths this rank sends (waits for the bucketize future)."""
+        st.send_lengths, st.send_ids, _ = st.split_future.result()
+        st.split_future = None
+        return st.send_lengths
+
+    def stage_exchange_ids(self, st: "DistState", recv_lengths: torch.Tensor):
+        """Stage 3 of 5: start the id all-to-all on the host process group (asynchronous; ``st.ids_work``)."""
+        st.recv_lengths = recv_lengths.view(self.world, -1)
+        if self.world == 1:
+            st.recv_ids, st.ids_work = st.send_ids, None
+            return
+        in_splits = st.send_lengths.sum(dim=1).tolist()
+        out_splits = st.recv_lengths.sum(dim=1).tolist()
+        st.recv_ids = st.send_ids.new_empty(int(sum(out_splits)))
+        st.ids_work = dist.all_to_all_single(st.recv_ids, st.send_ids.contiguous(), out_splits, in_splits,
+                                             group=self.input_pg if self.input_pg is not None else self.pg, async_op=True)
+
+    def stage_post_input(self, st: "DistState") -> None:
+        """Stage 4 of 5: raw ids -> local slots on the post-input pool (hash tables; identity otherwise)."""
+        if st.ids_work is not None:
+            st.ids_work.wait()
+            st.ids_work = None
+        lengths3 = st.recv_lengths.view(self.world, st.F, st.B)
+        if self.hashed:
+            st.post_future = self._post_pool.submit(self.post_input_dist, lengths3, st.recv_ids)
+        else:
+            st.mapped_ids = st.recv_ids
+
+    def stage_to_device(self, st: "DistState", device_features: KeyedJaggedTensor, stream=None) -> None:
+        """Stage 5 of 5: pinned host buffers -> device on ``stream``; registers the result for ``forward``."""
+        if st.post_future is not None:
+            st.mapped_ids = st.post_future.result()
+            st.post_future = None
+        cuda = self.device.type == "cuda"
+
+        def up(t: torch.Tensor) -> torch.Tensor:
+            if not cuda:
+                return t
+            return t.pin_memory().to(self.device, non_blocking=True)
+
+        if cuda and stream is not None:
+            with torch.cuda.stream(stream):
+                lengths, ids, orig = up(st.recv_lengths), up(st.mapped_ids), up(st.orig_lengths)
+                ev = torch.cuda.Event()
+                ev.record(stream)
+        else:
+            lengths, ids, orig, ev = up(st.recv_lengths), up(st.mapped_ids), up(st.orig_lengths), None
+        self._prepared[id(device_features)] = (lengths.view(self.world, st.F, st.B), ids, st.B, orig, ev)
 
     # ----------------------------------------------------------------- pipelining
     def _prepare(self, features: KeyedJaggedTensor):
