@@ -182,7 +182,11 @@ class HostKVTaskHandle:
     def stream_wait_layer(self, layer_idx: int) -> None:
         """Make the current stream wait until layer ``layer_idx`` of an onboard task has landed in its pages."""
         if self.layer_events and self.layer_events[layer_idx] is not None:
-            torch.cuda.current_stream().wait_event(self.layer_events[layer_idx])
+            ev = self.layer_events[layer_idx]
+            if hasattr(ev, "storage"):                     # a layer of a native storage task
+                ev.wait(torch.cuda.current_stream())
+            else:
+                torch.cuda.current_stream().wait_event(ev)
 
 
 @dataclasses.dataclass
@@ -349,6 +353,103 @@ NPUKVCacheManager = GPUKVCacheManager   # the name the reference API uses for th
 
 
 # =============================================================================== host tier
+class _NativeLayerEvent:
+    """One layer of a transfer task of the native storage: ``query()`` like a CUDA event, ``wait(stream)`` for a stream."""
+
+    def __init__(self, storage: "NativeKVStorage", task: int, layer: int) -> None:
+        self.storage, self.task, self.layer = storage, task, layer
+
+    def query(self) -> bool:
+        rc = self.storage.query(self.task, self.layer)
+        if rc < 0:
+            raise RuntimeError("KV storage task %d layer %d: error %d" % (self.task, self.layer, rc))
+        return rc == 0
+
+    def wait(self, stream=None) -> None:
+        self.storage.stream_wait(self.task, self.layer, stream)
+
+
+class NativeKVStorage:
+    """The native host tier (``csrc/cuda/kv_storage.cu``): pinned chunk pool ``[chunk][layer][rows_per_chunk_layer][row]``,
+    four streams (H2D, scatter, gather, D2H), two staging slots per direction and one event per layer of every task.
+    ``pool`` is a tensor view of the pinned memory (for inspection, export and tests)."""
+
+    def __init__(self, device: torch.device, num_layers: int, num_chunks: int, rows_per_chunk_layer: int, row_elems: int,
+                 dtype: torch.dtype, stage_rows: int) -> None:
+        import ctypes
+
+        self.device, self.num_layers = device, num_layers
+        self._lib = _lib.lib()
+        item = torch.empty(0, dtype=dtype).element_size()
+        h = ctypes.c_void_p()
+        _lib.check(self._lib.rb_kvs_create(device.index or 0, num_layers, num_chunks, rows_per_chunk_layer, row_elems * item,
+                                           int(stage_rows), ctypes.byref(h)), "rb_kvs_create")
+        self._h = h
+        nbytes = int(self._lib.rb_kvs_pool_bytes(self._h))
+        buf = (ctypes.c_uint8 * nbytes).from_address(int(self._lib.rb_kvs_pool(self._h)))
+        self._buf = buf
+        self.pool = torch.frombuffer(buf, dtype=torch.uint8).view(dtype).view(num_chunks, num_layers, rows_per_chunk_layer, row_elems)
+        self.pool.zero_()
+
+    def register_cache(self, layer: int, rows: torch.Tensor) -> None:
+        _lib.check(self._lib.rb_kvs_register_cache(self._h, layer, rows.data_ptr()), "rb_kvs_register_cache")
+
+    def _transfer(self, fn, chunks: np.ndarray, rows: np.ndarray) -> Tuple[int, int]:
+        import ctypes
+
+        chunks = np.ascontiguousarray(chunks, dtype=np.int64)
+        rows = np.ascontiguousarray(rows, dtype=np.int64)
+        task = ctypes.c_int(-1)
+        rc = fn(self._h, chunks.ctypes.data, len(chunks), rows.ctypes.data, _lib.stream_ptr(self.device), ctypes.byref(task))
+        if rc < 0:
+            _lib.check(rc, "rb_kvs transfer")
+        return int(task.value), int(rc)
+
+    def onload(self, chunks: np.ndarray, dst_rows: np.ndarray) -> Tuple[int, int]:
+        """-> (task id, 0 or the error of the call that failed while launching)."""
+        return self._transfer(self._lib.rb_kvs_onload, chunks, dst_rows)
+
+    def offload(self, chunks: np.ndarray, src_rows: np.ndarray) -> Tuple[int, int]:
+        return self._transfer(self._lib.rb_kvs_offload, chunks, src_rows)
+
+    def query(self, task: int, layer: int = -1) -> int:
+        return int(self._lib.rb_kvs_task_query(self._h, task, layer))
+
+    def stream_wait(self, task: int, layer: int, stream=None) -> None:
+        st = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        _lib.check(self._lib.rb_kvs_task_stream_wait(self._h, task, layer, st), "rb_kvs_task_stream_wait")
+
+    def release(self, task: int, drain: bool = False) -> bool:
+        """-> True when the slot was given back (a running task is only released with ``drain``)."""
+        rc = int(self._lib.rb_kvs_task_release(self._h, task, 1 if drain else 0))
+        if rc > 1 or rc < 0:
+            _lib.check(rc, "rb_kvs_task_release")
+        return rc == 0
+
+    def inject_failure(self, countdown: int) -> None:
+        self._lib.rb_kvs_inject_failure(self._h, int(countdown))
+
+    def stats(self) -> Dict[str, int]:
+        import ctypes
+
+        out = (ctypes.c_longlong * 4)()
+        self._lib.rb_kvs_stats(self._h, out)
+        return {"h2d_bytes": out[0], "d2h_bytes": out[1], "copy_calls": out[2], "kernels": out[3]}
+
+    def close(self) -> None:
+        if self._h is not None:
+            self.pool = None
+            self._buf = None
+            self._lib.rb_kvs_destroy(self._h)
+            self._h = None
+
+    def __del__(self) -> None:  # noqa: D401
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+
 class NativeHostKVCacheManager(HostKVStorageManagerBase):
     """Pinned host chunk store, page-major: ``pool[chunk, layer, page_in_chunk, 2, page_size * heads * head_dim]``.
     A row of the flattened pool is one K or V page, the same unit as a row of the flattened device cache, so
@@ -365,7 +466,20 @@ class NativeHostKVCacheManager(HostKVStorageManagerBase):
         chunk_bytes_per_layer = 2 * cfg.offload_chunksize * hd * item
         self.num_chunks = max(1, int(cfg.host_capacity_per_layer // chunk_bytes_per_layer))
         self.index = host().HostChunkIndex(self.num_chunks, cfg.offload_chunksize)
-        self.pool = torch.zeros(self.num_chunks, cfg.num_layers, self.ppc, 2, self.row_elems, dtype=cfg.dtype, pin_memory=self.cuda)
+        # transfer engine: "staged" (CUDA default) = native storage with DMA copies through device staging buffers on four
+        # streams; "zero_copy" = one kernel per layer that reads / writes the pinned pool through the unified address space
+        self.transfer = str(cfg.extra_configs.get("host_transfer", "staged" if self.cuda else "zero_copy"))
+        if self.transfer not in ("staged", "zero_copy") or (self.transfer == "staged" and not self.cuda):
+            raise ValueError("host_transfer must be 'staged' (CUDA only) or 'zero_copy'")
+        self.native: Optional[NativeKVStorage] = None
+        if self.transfer == "staged":
+            stage_rows = int(cfg.extra_configs.get("staging_rows", max(2 * self.ppc, 2 * min(cfg.max_seq_len, 8192) // cfg.page_size)))
+            self.native = NativeKVStorage(self.device, cfg.num_layers, self.num_chunks, self.ppc * 2, self.row_elems, cfg.dtype,
+                                          stage_rows)
+            self.pool = self.native.pool.view(self.num_chunks, cfg.num_layers, self.ppc, 2, self.row_elems)
+        else:
+            self.pool = torch.zeros(self.num_chunks, cfg.num_layers, self.ppc, 2, self.row_elems, dtype=cfg.dtype,
+                                    pin_memory=self.cuda)
         self.pool_rows = self.pool.view(-1, self.row_elems)
         self.cache_rows: List[torch.Tensor] = []
         if self.cuda:
@@ -375,6 +489,9 @@ class NativeHostKVCacheManager(HostKVStorageManagerBase):
 
     def register_npu_cache_tables(self, cache_table_list: List[torch.Tensor]) -> None:
         self.cache_rows = [t.view(-1, self.row_elems) for t in cache_table_list]        # rows: (page, kv)
+        if self.native is not None:
+            for layer, rows in enumerate(self.cache_rows):
+                self.native.register_cache(layer, rows)
 
     def build_index_meta(self, user_ids, sequence_lengths) -> KVIndexMeta:
         return KVIndexMeta(user_ids.cpu().long(), sequence_lengths.cpu().int())
@@ -423,6 +540,16 @@ class NativeHostKVCacheManager(HostKVStorageManagerBase):
         if self.fail_next_onboard:
             self.fail_next_onboard = False
             raise RuntimeError("injected onboard failure")
+        if self.native is not None:
+            task, err = self.native.onload(np.concatenate([c for _u, _n, c, _p in jobs]),
+                                           np.concatenate([self._cache_rows_of(p) for _u, _n, _c, p in jobs]))
+            h.handle = task
+            if err:
+                self.native.release(task, drain=True)
+                raise RuntimeError("onboard copy failed while launching (CUDA error %d)" % err)
+            h.layer_events = [_NativeLayerEvent(self.native, task, layer) for layer in range(cfg.num_layers)]
+            h.status = HostKVTaskStatus.LAUNCHED
+            return h
         dst = self._idx(np.concatenate([self._cache_rows_of(p) for _u, _n, _c, p in jobs]))
         src_all = self._idx(np.stack([np.concatenate([self._pool_rows_of(c, layer) for _u, _n, c, _p in jobs])
                                       for layer in range(cfg.num_layers)]))
@@ -459,6 +586,9 @@ class NativeHostKVCacheManager(HostKVStorageManagerBase):
         if not self._poll(task_handle.layer_events, self.cfg.onload_timeout_ms):
             task_handle.status = HostKVTaskStatus.TIMEOUT
             return HostKVWaitResult(HostKVTaskStatus.TIMEOUT, HostKVStorageErrorCode.ONBOARD_TIMEOUT, "onboard timed out")
+        if self.native is not None and task_handle.handle is not None:
+            self.native.release(task_handle.handle)
+            task_handle.handle = None
         task_handle.status = HostKVTaskStatus.READY
         return HostKVWaitResult(HostKVTaskStatus.READY)
 
@@ -483,6 +613,13 @@ class NativeHostKVCacheManager(HostKVStorageManagerBase):
                              metadata={"plan": plan, "lengths": lengths, "starts": starts, "no_space": no_space})
         if not plan:
             h.status = HostKVTaskStatus.SKIPPED
+            return h
+        if self.native is not None:
+            task, err = self.native.offload(np.concatenate([c for _u, c, _p in plan]),
+                                            np.concatenate([self._cache_rows_of(p) for _u, _c, p in plan]))
+            h.handle = task
+            h.metadata["launch_error"] = err
+            h.layer_events = [_NativeLayerEvent(self.native, task, cfg.num_layers - 1)] if not err else []
             return h
         src = self._idx(np.concatenate([self._cache_rows_of(p) for _u, _c, p in plan]))
         dst_all = self._idx(np.stack([np.concatenate([self._pool_rows_of(c, layer) for _u, c, _p in plan])
@@ -513,6 +650,10 @@ class NativeHostKVCacheManager(HostKVStorageManagerBase):
                 self.offload_stream.synchronize()
             task_handle.status = HostKVTaskStatus.FAILED
             return HostKVWaitResult(HostKVTaskStatus.FAILED, HostKVStorageErrorCode.OFFLOAD_WAIT_FAILED, "injected copy failure")
+        if (task_handle.metadata or {}).get("launch_error"):
+            task_handle.status = HostKVTaskStatus.FAILED
+            return HostKVWaitResult(HostKVTaskStatus.FAILED, HostKVStorageErrorCode.OFFLOAD_WAIT_FAILED,
+                                    "offload copy failed while launching (CUDA error %d)" % task_handle.metadata["launch_error"])
         if not self._poll(task_handle.layer_events, self.cfg.offload_timeout_ms):
             task_handle.status = HostKVTaskStatus.TIMEOUT
             return HostKVWaitResult(HostKVTaskStatus.TIMEOUT, HostKVStorageErrorCode.OFFLOAD_TIMEOUT, "offload timed out")
@@ -524,8 +665,11 @@ class NativeHostKVCacheManager(HostKVStorageManagerBase):
         timed-out copy may still be writing, so the stream is drained before the chunks can be reused."""
         plan = task_handle.metadata.get("plan", []) if task_handle.metadata else []
         ok = task_handle.status == HostKVTaskStatus.READY
+        if self.native is not None and task_handle.handle is not None:
+            self.native.release(task_handle.handle, drain=not ok)
+            task_handle.handle = None
         if not ok and plan:
-            if self.cuda:
+            if self.cuda and self.native is None:
                 self.offload_stream.synchronize()
             for u, chunks, _p in plan:
                 self.index.rollback(u, len(chunks))

@@ -9,6 +9,7 @@
     python -m recsdk_b200.utils.microbench exchange --batch 65536 --tables 26 --rows 2000000      # push exchange, one rank
     python -m recsdk_b200.utils.microbench allreduce --n 3000000                                   # push all-reduce, one rank
     python -m recsdk_b200.utils.microbench sampled_softmax --m 32768 --k 512 --n 512
+    python -m recsdk_b200.utils.microbench kv_transfer --seqs 16 --len 4096 --heads 8             # host tier <-> device pages
 
 ``exchange`` and ``allreduce`` run the multi-GPU kernels with a world of one (every "peer" pointer is this GPU's own
 buffer): the same code path and memory traffic minus NVLink, which is what a single-GPU ncu capture can show; the
@@ -129,7 +130,7 @@ def host_engines(a) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "hstu_fwd", "hstu_bwd", "tbe_fwd", "interaction", "ln_mul_bwd", "pooled_bwd",
-                                     "exchange", "allreduce", "sampled_softmax", "host_engines"])
+                                     "exchange", "allreduce", "sampled_softmax", "host_engines", "kv_transfer"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -349,6 +350,77 @@ def main() -> None:
         by = n * 4 * 2 + n * 2 * 4          # fp32 read + write, bf16 staging and result written + read
         out.update(ms=ms, n=n, gbs=by / ms / 1e6, frac_of_peak=by / (ms / 1e3) / hbm,
                    note="two-shot push all-reduce, one rank looped back: local traffic only")
+    elif a.what == "kv_transfer":
+        # host tier of the paged KV cache: --seqs users of --len tokens, 8 layers, --heads x 64; both engines, both directions
+        import numpy as np
+
+        from ..inference.kvcache_manager import NativeKVStorage
+        from ..ops import embedding_ops as E
+
+        L, page, chunk, hd = 8, 32, 1024, a.heads * 64
+        ppc = chunk // page
+        n_chunks = a.seqs * (a.len // chunk)
+        row_elems = page * hd
+        n_pages = n_chunks * ppc
+        st = NativeKVStorage(dev, L, n_chunks, ppc * 2, row_elems, torch.bfloat16, 16 * ppc * 2)
+        cache = [torch.randn(n_pages * 2, row_elems, device=dev).bfloat16() for _ in range(L)]
+        for layer, c in enumerate(cache):
+            st.register_cache(layer, c)
+        chunks = np.arange(n_chunks, dtype=np.int64)
+        rows = np.random.default_rng(0).permutation(n_pages).astype(np.int64)
+        rows = np.stack([rows * 2, rows * 2 + 1], axis=1).reshape(-1)
+        by = n_chunks * L * ppc * 2 * row_elems * 2
+
+        def staged(fn):
+            def run():
+                task, err = fn(chunks, rows)
+                assert err == 0
+                st.stream_wait(task, L - 1)
+                run.tasks.append(task)
+            run.tasks = []
+            return run
+
+        res = {}
+        for name, fn in (("offload", staged(st.offload)), ("onload", staged(st.onload))):
+            ts = []
+            for _ in range(a.iters + 1):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                for t in fn.tasks:
+                    st.release(t)
+                fn.tasks.clear()
+                ts.append(e0.elapsed_time(e1))
+            res["staged_%s_ms" % name] = sorted(ts[1:])[len(ts[1:]) // 2]
+            res["staged_%s_gbs" % name] = by / res["staged_%s_ms" % name] / 1e6
+        pool_rows = st.pool.view(-1, row_elems)
+        per = ppc * 2
+        d_rows = torch.from_numpy(rows).to(dev)
+        pool_idx = [torch.from_numpy(((chunks[:, None] * L + layer) * per + np.arange(per)[None, :]).reshape(-1)).to(dev)
+                    for layer in range(L)]
+        for name in ("offload", "onload"):
+            def zc():
+                for layer in range(L):
+                    if name == "offload":
+                        E.copy_rows(cache[layer], d_rows, pool_rows, pool_idx[layer], dev)
+                    else:
+                        E.copy_rows(pool_rows, pool_idx[layer], cache[layer], d_rows, dev)
+            ts = []
+            for _ in range(a.iters + 1):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                zc()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            res["zero_copy_%s_ms" % name] = sorted(ts[1:])[len(ts[1:]) // 2]
+            res["zero_copy_%s_gbs" % name] = by / res["zero_copy_%s_ms" % name] / 1e6
+        out.update(res, bytes=by, chunks=n_chunks, layers=L, stats=st.stats(),
+                   note="pinned host pool <-> device pages; staged = DMA copies + scatter/gather kernels on four streams, "
+                        "zero_copy = one kernel per layer over mapped host memory; the link (PCIe / C2C) is the bound")
+        st.close()
     elif a.what == "sampled_softmax":
         from ..ops import model_ops
 

@@ -31,8 +31,8 @@ def _read(m, uid, layer, n):
     return k, v
 
 
-def _lifecycle(device, dtype):
-    m = KVCacheManager.from_config(_cfg(device, dtype))
+def _lifecycle_impl(device, dtype, **kw):
+    m = KVCacheManager.from_config(_cfg(device, dtype, **kw))
     u = torch.tensor([7, 9])
     meta, look = m.lookup_kvcache(u, torch.tensor([300, 40]))
     assert look.cached_lengths.tolist() == [0, 0]
@@ -78,10 +78,71 @@ def test_lifecycle_cpu():
     _lifecycle("cpu", torch.float32)
 
 
+def _lifecycle(device, dtype, **kw):
+    return _lifecycle_impl(device, dtype, **kw)
+
+
 @pytest.mark.gpu
-def test_lifecycle_gpu():
-    m = _lifecycle("cuda", torch.bfloat16)
+@pytest.mark.parametrize("transfer,staging_rows", [("staged", 0), ("staged", 8), ("zero_copy", 0)])
+def test_lifecycle_gpu(transfer, staging_rows):
+    """Same scenario through the native staged engine (DMA copies + scatter / gather kernels on four streams; 8 staging rows
+    = one chunk per piece, so that both slots are reused within a layer) and through the zero-copy kernel."""
+    extra = {"host_transfer": transfer}
+    if staging_rows:
+        extra["staging_rows"] = staging_rows
+    m = _lifecycle("cuda", torch.bfloat16, extra_configs=extra)
     assert m.host.pool.is_pinned()
+    if transfer == "staged":
+        st = m.host.native.stats()
+        chunk_layer_bytes = 2 * 128 * 128 * 2                           # k,v x 128 tokens x 128 values x 2 bytes
+        assert st["d2h_bytes"] == 2 * 2 * chunk_layer_bytes             # two chunks of user 7, two layers
+        assert st["h2d_bytes"] == st["d2h_bytes"] and st["copy_calls"] == 8 and st["kernels"] >= 4
+    else:
+        assert m.host.native is None
+
+
+@pytest.mark.gpu
+def test_staged_engine_injected_copy_failures_leave_the_context_usable():
+    """A copy call that reports an error (injected on the host: nothing faults on the device) fails the task, rolls the
+    chunks back, frees the task slot, and the retry succeeds."""
+    u = torch.tensor([1])
+    m = KVCacheManager.from_config(_cfg("cuda", torch.bfloat16))
+    meta, look = m.lookup_kvcache(u, torch.tensor([256]))
+    md = m.allocate_kvcache(meta, look)
+    truth = {}
+    for layer in range(2):
+        truth[layer] = _kv(256, layer, 3, "cuda", torch.bfloat16)
+        m.gpu.append_kvcache(layer, *truth[layer], md)
+    m.host.native.inject_failure(2)                                    # third D2H copy of the next transfer
+    m.offload_launch(meta, md)
+    res = m.offload_try_wait()
+    assert res.status == HostKVTaskStatus.FAILED and m.stats["offload_failures"] == 1
+    assert m.host.lookup_kvcache(meta)[1].tolist() == [0]
+    m.offload_launch(meta, md)
+    assert m.offload_try_wait().status == HostKVTaskStatus.READY
+    assert m.host.lookup_kvcache(meta)[1].tolist() == [256]
+    m.evict(u, for_host=False)
+    meta2, look2 = m.lookup_kvcache(u, torch.tensor([300]))
+    md2 = m.allocate_kvcache(meta2, look2)
+    m.host.native.inject_failure(0)                                    # first H2D copy
+    h = m.onboard_launch(meta2, look2, md2)
+    assert h.status == HostKVTaskStatus.FAILED and m.stats["onboard_failures"] == 1
+    m.revoke_failed_onboard(meta2, look2)
+    meta3, look3 = m.lookup_kvcache(u, torch.tensor([300]))
+    md3 = m.allocate_kvcache(meta3, look3)
+    h = m.onboard_launch(meta3, look3, md3)
+    assert m.onboard_wait(h).status == HostKVTaskStatus.READY
+    for layer in range(2):
+        h.stream_wait_layer(layer)
+        rk, rv = _read(m, 1, layer, 256)
+        assert torch.equal(rk, truth[layer][0]) and torch.equal(rv, truth[layer][1])
+    for _ in range(40):                                                # task slots are given back: far more transfers than slots
+        m.evict(u, for_host=False)
+        me, lo = m.lookup_kvcache(u, torch.tensor([256]))
+        mdx = m.allocate_kvcache(me, lo)
+        hx = m.onboard_launch(me, lo, mdx)
+        assert m.onboard_wait(hx).status == HostKVTaskStatus.READY
+    torch.cuda.synchronize()
 
 
 def test_injected_failures_and_policies():
