@@ -358,15 +358,20 @@ class _NativeLayerEvent:
 
     def __init__(self, storage: "NativeKVStorage", task: int, layer: int) -> None:
         self.storage, self.task, self.layer = storage, task, layer
+        self.done = False                 # seen complete: the task slot may have been given back since
 
     def query(self) -> bool:
+        if self.done:
+            return True
         rc = self.storage.query(self.task, self.layer)
         if rc < 0:
             raise RuntimeError("KV storage task %d layer %d: error %d" % (self.task, self.layer, rc))
-        return rc == 0
+        self.done = rc == 0
+        return self.done
 
     def wait(self, stream=None) -> None:
-        self.storage.stream_wait(self.task, self.layer, stream)
+        if not self.done:
+            self.storage.stream_wait(self.task, self.layer, stream)
 
 
 class NativeKVStorage:
