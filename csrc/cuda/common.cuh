@@ -267,3 +267,61 @@ __device__ __forceinline__ float warp_sum(float v) {
     cudaError_t _e = (expr);                  \
     if (_e != cudaSuccess) return (int)_e;    \
   } while (0)
+
+// Tensor-map encoding (driver entry point fetched through the runtime, no link against libcuda).
+//
+// `cuTensorMapEncodeTiled` is a driver call and needs a CUDA context current on the calling thread.  A thread whose
+// first CUDA action is such a call (e.g. an autograd worker whose first backward node is one of these kernels) has none:
+// the runtime binds the primary context only on ITS first call.  `rb_host::bind_context` therefore makes the context of
+// the device that owns `ptr` current when the thread has none.  A failed encode returns -(1000 + CUresult).
+namespace rb_host {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*CtxGetCurrentFn)(CUcontext*);
+
+inline void* driver_symbol(const char* name) {
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &sym, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) return nullptr;
+  return sym;
+}
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = reinterpret_cast<EncodeTiledFn>(driver_symbol("cuTensorMapEncodeTiled"));
+  return fn;
+}
+
+inline void bind_context(const void* ptr) {
+  thread_local bool bound = false;
+  if (bound) return;
+  static CtxGetCurrentFn get_current = reinterpret_cast<CtxGetCurrentFn>(driver_symbol("cuCtxGetCurrent"));
+  CUcontext ctx = nullptr;
+  if (get_current && get_current(&ctx) == CUDA_SUCCESS && ctx != nullptr) {
+    bound = true;
+    return;
+  }
+  cudaPointerAttributes at;
+  if (ptr && cudaPointerGetAttributes(&at, ptr) == cudaSuccess && at.type == cudaMemoryTypeDevice) cudaSetDevice(at.device);
+  cudaFree(nullptr);                 // binds the primary context of the thread's current device
+  bound = true;
+}
+
+// 2-D row-major tensor [rows][cols] of 16-bit elements (row stride `ld` elements), 128-byte swizzled boxes
+inline int make_map_2d(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_cols,
+                       int box_rows, bool is_bf16) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return -1;
+  bind_context(base);
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                        const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(1000 + static_cast<int>(r));
+}
+
+}  // namespace rb_host

@@ -435,28 +435,8 @@ done:
   if (want_dpos) for (int i = threadIdx.x; i < p.pos_len && i < POS_HIST; i += blockDim.x) if (dpos_s[i] != 0) atomicAdd(p.d_pos_w + i, hist_value(dpos_s[i]));
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void* sym = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
-      q != cudaDriverEntryPointSuccess) return nullptr;
-  return fn = reinterpret_cast<EncodeTiledFn>(sym);
-}
 int make_map(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return -1;
-  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t gstr[1] = {static_cast<cuuint64_t>(ld) * 2};
-  cuuint32_t box[2] = {64, 64};
-  cuuint32_t es[2] = {1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstr, box, es,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? 0 : -2;
+  return rb_host::make_map_2d(m, base, rows, cols, ld, 64, 64, true);
 }
 
 template <bool BT, bool BP, bool WDT, bool WDP>

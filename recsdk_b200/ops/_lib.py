@@ -114,6 +114,8 @@ def check(rc: int, what: str) -> None:
         return
     if rc > 0:
         raise RuntimeError("%s: CUDA error %d (%s)" % (what, rc, _cuda_err_name(rc)))
+    if rc <= -1000:
+        raise RuntimeError("%s: cuTensorMapEncodeTiled failed with CUresult %d" % (what, -rc - 1000))
     raise ValueError("%s: invalid arguments (code %d)" % (what, rc))
 
 

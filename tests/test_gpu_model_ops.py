@@ -51,3 +51,25 @@ def test_multislice_concat():
         got = model_ops.multislice_concat(x, sl)
         want = torch.cat([x[:, a:b] for a, b in sl], dim=1)
         assert torch.equal(got, want)
+
+
+def test_tensor_map_kernel_as_first_node_of_a_fresh_autograd_thread():
+    """A process whose very first backward node launches a TMA kernel: the autograd worker thread has made no CUDA runtime
+    call yet, so the tensor-map encode (a driver call) must bind the context itself."""
+    import subprocess
+    import sys
+
+    code = (
+        "import torch\n"
+        "from recsdk_b200.ops import model_ops\n"
+        "g = torch.Generator().manual_seed(0)\n"
+        "h = (torch.randn(777, 256, generator=g) * 0.5).to('cuda', torch.bfloat16).requires_grad_()\n"
+        "ep = (torch.randn(777, 256, generator=g) * 0.5).to('cuda', torch.bfloat16)\n"
+        "en = (torch.randn(512, 256, generator=g) * 0.5).to('cuda', torch.bfloat16).requires_grad_()\n"
+        "loss = model_ops.sampled_softmax_loss(h, ep, en, 1.0 / 777)\n"
+        "loss.backward()\n"
+        "torch.cuda.synchronize()\n"
+        "assert torch.isfinite(h.grad.float()).all() and torch.isfinite(en.grad.float()).all()\n"
+        "print('ok')\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
