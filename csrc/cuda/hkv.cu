@@ -81,6 +81,20 @@ __device__ __forceinline__ unsigned long long device_timestamp() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// one prefetch per 128 bytes of the `n_floats` floats starting at p, never beyond them (lanes 0..)
+__device__ __forceinline__ void prefetch_row(const float* p, int n_floats, int lane) {
+  if (lane * 128 < n_floats * 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p) + lane * 128));
+}
+// keys a warp takes per step: 32 when there is enough work for every warp, fewer (a power of two) for short lists so
+// that the keys still spread over all warps
+__device__ __forceinline__ int chunk_width(long long n, long long warps_total) {
+  int cw = 32;
+  while (cw > 1 && static_cast<long long>(cw) * warps_total > n) cw >>= 1;
+  return cw;
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 __device__ __forceinline__ float u01(unsigned long long seed, unsigned long long key, unsigned col, unsigned stream) {
   unsigned long long x = hash64(key ^ (seed * 0x9E3779B97F4A7C15ull) ^ (static_cast<unsigned long long>(col) << 32) ^ stream);
   return (static_cast<float>(x >> 40) + 0.5f) * (1.0f / 16777216.0f);
@@ -164,18 +178,39 @@ hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ key
   const int lane = threadIdx.x & 31;
   const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   if (n_dev && *n_dev < n) n = *n_dev;          // the number of keys may live on the device (no host read)
-  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; i < n; i += warps_total) {
-    const unsigned long long key = keys[i];
-    if (key == EMPTY_KEY) {
-      if (lane == 0) { out_slots[i] = -1; if (out_status) out_status[i] = ST_MISSING; }
-      continue;
+  // A find-only launch changes no key, digest or slot, so it takes no bucket lock even when it refreshes scores or
+  // stamps the slots it found (callers keep launches on one table in one stream).
+  const bool need_lock = insert != 0;
+  const bool stamp = insert || (update_score & 2);
+  const bool upd_score = (update_score & 1) != 0;
+  long long d_size = 0;                          // lane 0: outcome counts of this warp, flushed once at the end
+  unsigned long long c_out[4] = {0ull, 0ull, 0ull, 0ull};
+  // Keys are taken 32 at a time (one coalesced load; empty keys cost nothing more) and every lane prefetches the
+  // bucket head of its key, so the dependent loads of the serial per-key work below mostly hit L2.
+  const int cw = chunk_width(n, warps_total);
+  for (long long base = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * cw; base < n;
+       base += warps_total * cw) {
+    const long long il = base + lane;
+    const bool mine = lane < cw && il < n;
+    const unsigned long long kl = mine ? keys[il] : EMPTY_KEY;
+    if (kl == EMPTY_KEY) {
+      if (mine) { out_slots[il] = -1; if (out_status) out_status[il] = ST_MISSING; }
+    } else {
+      const long long bl = static_cast<long long>(hash64(kl) & static_cast<unsigned long long>(t.num_buckets - 1));
+      prefetch_l2(t.digests + bl * BUCKET);
+      if (need_lock) prefetch_l2(t.locks + bl);
     }
+    unsigned pending = __ballot_sync(0xffffffffu, kl != EMPTY_KEY);
+  while (pending) {
+    const int src = __ffs(pending) - 1;
+    pending &= pending - 1;
+    const unsigned long long key = __shfl_sync(0xffffffffu, kl, src);
+    const long long i = base + src;
     const unsigned long long h = hash64(key);
     const long long b = static_cast<long long>(h & static_cast<unsigned long long>(t.num_buckets - 1));
     const unsigned dg = digest_of(h);
-    const bool need_lock = insert || update_score;
     if (need_lock && !lock_bucket(t.locks + b, lane, status)) {
-      if (lane == 0) { out_slots[i] = -1; if (out_status) out_status[i] = ST_LOCK_TIMEOUT; if (t.counters) atomicAdd(t.counters + 3, 1ull); }
+      if (lane == 0) { out_slots[i] = -1; if (out_status) out_status[i] = ST_LOCK_TIMEOUT; c_out[3] += 1; }
       continue;
     }
     const unsigned d4 = __ldcg(reinterpret_cast<const unsigned*>(t.digests + b * BUCKET) + lane);  // L2: L1 may be stale
@@ -184,8 +219,8 @@ hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ key
     if (pos >= 0) {
       if (lane == 0) {
         const long long s = b * BUCKET + pos;
-        if (update_score) t.scores[s] = new_score(t.evict_strategy, __ldcg(t.scores + s), false, scores_in, i);
-        if (insert && t.touch && t.touch[s] != LOCKED_STAMP) t.touch[s] = t.epoch;
+        if (upd_score) t.scores[s] = new_score(t.evict_strategy, __ldcg(t.scores + s), false, scores_in, i);
+        if (stamp && t.touch && t.touch[s] != LOCKED_STAMP) t.touch[s] = t.epoch;
       }
     } else if (!insert) {
       st = ST_MISSING;
@@ -200,13 +235,13 @@ hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ key
       if (m) {
         pos = __shfl_sync(0xffffffffu, mine, __ffs(m) - 1);
         st = ST_INSERTED;
-        if (lane == 0) atomicAdd(t.size, 1ull);
+        if (lane == 0) d_size += 1;
       } else {
         // ---- bucket full: evict the lowest score
         unsigned long long best = ~0ull;
         int best_pos = lane * 4;
-#pragma unroll
         bool any_free = false;                   // a slot not handed out by this launch
+#pragma unroll
         for (int j = 0; j < 4; ++j) {
           const long long sl = b * BUCKET + lane * 4 + j;
           if (t.touch) { const unsigned tv = __ldcg(t.touch + sl); if (tv == t.epoch || tv == LOCKED_STAMP) continue; }
@@ -258,7 +293,16 @@ hkv_find_or_insert_kernel(HkvTable t, const unsigned long long* __restrict__ key
     if (lane == 0) {
       out_slots[i] = (st == ST_MISSING || st == ST_REJECTED) ? -1 : b * BUCKET + pos;
       if (out_status) out_status[i] = st;
-      if (t.counters && st >= ST_INSERTED && st <= ST_REJECTED) atomicAdd(t.counters + (st - ST_INSERTED), 1ull);
+      c_out[0] += st == ST_INSERTED; c_out[1] += st == ST_EVICTED_OTHER; c_out[2] += st == ST_REJECTED;
+    }
+  }
+  }
+  if (lane == 0) {
+    if (d_size) atomicAdd(t.size, static_cast<unsigned long long>(d_size));
+    if (t.counters) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (c_out[c]) atomicAdd(t.counters + c, c_out[c]);
     }
   }
 }
@@ -268,23 +312,38 @@ __global__ void __launch_bounds__(256)
 hkv_erase_kernel(HkvTable t, const unsigned long long* __restrict__ keys, long long n, int* status) {
   const int lane = threadIdx.x & 31;
   const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; i < n; i += warps_total) {
-    const unsigned long long key = keys[i];
-    if (key == EMPTY_KEY) continue;
-    const unsigned long long h = hash64(key);
-    const long long b = static_cast<long long>(h & static_cast<unsigned long long>(t.num_buckets - 1));
-    if (!lock_bucket(t.locks + b, lane, status)) continue;
-    const unsigned d4 = __ldcg(reinterpret_cast<const unsigned*>(t.digests + b * BUCKET) + lane);  // L2: L1 may be stale
-    const int pos = find_in_bucket(t, b, key, digest_of(h), d4, lane);
-    if (pos >= 0 && lane == 0) {
-      const long long s = b * BUCKET + pos;
-      t.keys[s] = EMPTY_KEY;
-      t.scores[s] = 0ull;
-      t.digests[s] = static_cast<unsigned char>(EMPTY_DIGEST);
-      atomicAdd(t.size, ~0ull);
+  long long erased = 0;                           // lane 0
+  const int cw = chunk_width(n, warps_total);
+  for (long long base = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * cw; base < n;
+       base += warps_total * cw) {
+    const long long il = base + lane;
+    const unsigned long long kl = (lane < cw && il < n) ? keys[il] : EMPTY_KEY;
+    if (kl != EMPTY_KEY) {
+      const long long bl = static_cast<long long>(hash64(kl) & static_cast<unsigned long long>(t.num_buckets - 1));
+      prefetch_l2(t.digests + bl * BUCKET);
+      prefetch_l2(t.locks + bl);
     }
-    unlock_bucket(t.locks + b, lane);
+    unsigned pending = __ballot_sync(0xffffffffu, kl != EMPTY_KEY);
+    while (pending) {
+      const int src = __ffs(pending) - 1;
+      pending &= pending - 1;
+      const unsigned long long key = __shfl_sync(0xffffffffu, kl, src);
+      const unsigned long long h = hash64(key);
+      const long long b = static_cast<long long>(h & static_cast<unsigned long long>(t.num_buckets - 1));
+      if (!lock_bucket(t.locks + b, lane, status)) continue;
+      const unsigned d4 = __ldcg(reinterpret_cast<const unsigned*>(t.digests + b * BUCKET) + lane);  // L2: L1 may be stale
+      const int pos = find_in_bucket(t, b, key, digest_of(h), d4, lane);
+      if (pos >= 0 && lane == 0) {
+        const long long s = b * BUCKET + pos;
+        t.keys[s] = EMPTY_KEY;
+        t.scores[s] = 0ull;
+        t.digests[s] = static_cast<unsigned char>(EMPTY_DIGEST);
+        erased += 1;
+      }
+      unlock_bucket(t.locks + b, lane);
+    }
   }
+  if (lane == 0 && erased) atomicAdd(t.size, static_cast<unsigned long long>(-erased));
 }
 
 // pin == 1: resident keys become ineligible as eviction victims until unpinned (flags[i] = found; slots[i] = slot or -1);
@@ -338,12 +397,23 @@ __global__ void hkv_gather_kernel(HkvTable t, const long long* __restrict__ slot
                                   OT* __restrict__ out, long long ld_out, float missing_value) {
   const int lane = threadIdx.x & 31;
   const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; i < n; i += warps_total) {
-    const long long s = slots[i];
+  // rows sit at random places of a table far larger than the TLB reach: the slot of the row after next is loaded and
+  // the next row's lines are prefetched while the current row is copied
+  long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  long long s = i < n ? slots[i] : -1;
+  long long s_next = i + warps_total < n ? slots[i + warps_total] : -1;
+  for (; i < n; i += warps_total) {
+    const long long s_after = i + 2 * warps_total < n ? slots[i + 2 * warps_total] : -1;
+    if (s_next >= 0) prefetch_row(row_ptr(t, s_next) + col0, cols, lane);
     OT* o = out + i * ld_out;
-    if (s < 0) { for (int c = lane; c < cols; c += 32) o[c] = static_cast<OT>(missing_value); continue; }
-    const float* src = row_ptr(t, s) + col0;
-    for (int c = lane; c < cols; c += 32) o[c] = static_cast<OT>(src[c]);
+    if (s < 0) {
+      for (int c = lane; c < cols; c += 32) o[c] = static_cast<OT>(missing_value);
+    } else {
+      const float* src = row_ptr(t, s) + col0;
+      for (int c = lane; c < cols; c += 32) o[c] = static_cast<OT>(src[c]);
+    }
+    s = s_next;
+    s_next = s_after;
   }
 }
 
@@ -373,8 +443,15 @@ __global__ void hkv_update_kernel(HkvTable t, const long long* __restrict__ slot
   const int lane = threadIdx.x & 31;
   const int D = t.emb_dim;
   const long long warps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; i < n; i += warps_total) {
-    const long long s = slots[i];
+  long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  long long s_cur = i < n ? slots[i] : -1;
+  long long s_next = i + warps_total < n ? slots[i + warps_total] : -1;
+  for (; i < n; i += warps_total) {
+    const long long s = s_cur;
+    const long long s_after = i + 2 * warps_total < n ? slots[i + 2 * warps_total] : -1;
+    if (s_next >= 0) prefetch_row(row_ptr(t, s_next), t.row_dim, lane);     // next row's lines while this one is updated
+    s_cur = s_next;
+    s_next = s_after;
     if (s < 0) continue;
     float* row = row_ptr(t, s);
     const GT* g = grads + i * ld_g;

@@ -159,7 +159,7 @@ class HKVTable(_VariableInterface):
         return self.size() / self.capacity
 
     def _probe(self, keys: torch.Tensor, insert: bool, update_score: bool, scores: Optional[torch.Tensor],
-               evict_cap: int = 0):
+               evict_cap: int = 0, stamp: bool = False, keep_epoch: bool = False):
         keys = keys.contiguous()
         assert keys.dtype == torch.int64 and keys.device == self.device
         n = keys.numel()
@@ -175,11 +175,12 @@ class HKVTable(_VariableInterface):
             scores = scores.contiguous()
             assert scores.dtype == torch.int64 and scores.numel() == n
         i = self.init
-        if insert:
+        if (insert and not keep_epoch) or stamp:
             self._epoch = self._epoch % 0x7FFFFFFF + 1       # never 0: freshly allocated stamps are 0
             self._desc[14] = self._epoch
         rc = _lib.lib().rb_hkv_find_or_insert(
-            self._d(), keys.data_ptr(), n, int(insert), int(update_score), _lib.ptr(scores), slots.data_ptr(),
+            self._d(), keys.data_ptr(), n, int(insert), int(bool(update_score)) | (2 if stamp else 0), _lib.ptr(scores),
+            slots.data_ptr(),
             status.data_ptr(), int(i.mode), i.lower, i.upper, i.mean, i.std_dev, i.value, int(i.seed), i.state_init,
             ev[0].data_ptr() if ev else None, ev[1].data_ptr() if ev else None, ev[2].data_ptr() if ev else None,
             ev[3].data_ptr() if ev else None, evict_cap, self._sms(), _lib.status_tensor(self.device).data_ptr(),
@@ -187,17 +188,22 @@ class HKVTable(_VariableInterface):
         _lib.check(rc, "rb_hkv_find_or_insert")
         return slots, status, ev
 
-    def find(self, keys: torch.Tensor, update_score: bool = False, scores: Optional[torch.Tensor] = None
-             ) -> Tuple[torch.Tensor, torch.Tensor]:
-        """-> (slots [-1 when missing], found mask)."""
-        slots, _status, _ = self._probe(keys, False, update_score, scores)
+    def find(self, keys: torch.Tensor, update_score: bool = False, scores: Optional[torch.Tensor] = None,
+             stamp: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+        """-> (slots [-1 when missing], found mask).  Takes no bucket locks (a find changes no key or slot; keep the launches
+        on one table in one stream).  ``stamp`` opens a new launch stamp and marks the found slots with it: a following
+        ``find_or_insert(..., keep_epoch=True)`` will not evict them - together the two calls are one find-or-insert in
+        which only the (few) missing keys pay for locks."""
+        slots, _status, _ = self._probe(keys, False, update_score, scores, stamp=stamp)
         return slots, slots >= 0
 
-    def find_or_insert(self, keys: torch.Tensor, scores: Optional[torch.Tensor] = None, evict_cap: int = 0):
+    def find_or_insert(self, keys: torch.Tensor, scores: Optional[torch.Tensor] = None, evict_cap: int = 0,
+                       keep_epoch: bool = False):
         """-> (slots, status, evicted) where evicted = (keys, scores, rows, count) or None.  Keys must be
-        distinct within one call.  Grows the table first when the load factor would exceed the limit."""
+        distinct within one call.  Grows the table first when the load factor would exceed the limit.  ``keep_epoch``
+        continues the launch stamp of the preceding ``find(..., stamp=True)``."""
         self.maybe_grow(keys.numel())
-        return self._probe(keys, True, True, scores, evict_cap)
+        return self._probe(keys, True, True, scores, evict_cap, keep_epoch=keep_epoch)
 
     def insert_and_evict(self, keys: torch.Tensor, values: torch.Tensor, scores: Optional[torch.Tensor] = None):
         """Insert (or overwrite) full rows; returns what had to be evicted to make room."""
@@ -401,12 +407,13 @@ class HostDynamicTable(_VariableInterface):
         else:
             self.score[key] = given if given is not None else (1 if new else self.score.get(key, 1))
 
-    def find_or_insert(self, keys: torch.Tensor, scores: Optional[torch.Tensor] = None, evict_cap: int = 0):
+    def find_or_insert(self, keys: torch.Tensor, scores: Optional[torch.Tensor] = None, evict_cap: int = 0,
+                       keep_epoch: bool = False):
         ks = keys.tolist()
         sc = scores.tolist() if scores is not None else [None] * len(ks)
         status = []
         evk, evs, evr = [], [], []
-        stamped = set()
+        stamped = set(getattr(self, "_stamped", ())) if keep_epoch else set()
         for k, s in zip(ks, sc):
             if k == EMPTY_KEY:
                 status.append(ST_MISSING)
@@ -438,8 +445,16 @@ class HostDynamicTable(_VariableInterface):
         st = torch.tensor(status, dtype=torch.uint8)
         return torch.where((st == ST_MISSING) | (st == ST_REJECTED), torch.full_like(keys, -1), keys), st, ev
 
-    def find(self, keys: torch.Tensor, update_score: bool = False, scores=None):
-        found = torch.tensor([k in self.rows for k in keys.tolist()], dtype=torch.bool)
+    def find(self, keys: torch.Tensor, update_score: bool = False, scores=None, stamp: bool = False):
+        ks = keys.tolist()
+        found = torch.tensor([k in self.rows for k in ks], dtype=torch.bool)
+        if update_score:
+            sc = scores.tolist() if scores is not None else [None] * len(ks)
+            for k, s in zip(ks, sc):
+                if k in self.rows:
+                    self._touch(k, s, False)
+        if stamp:
+            self._stamped = {k for k in ks if k in self.rows}
         slots = torch.where(found, keys, torch.full_like(keys, -1))
         return slots, found
 

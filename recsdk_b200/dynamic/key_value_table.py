@@ -195,6 +195,8 @@ class KeyValueTable:
             return slots, rows
         keys = unique_keys
         admitted_mask = None
+        if self.probation is not None and n and self.storage is None:
+            return self._lookup_with_admission(unique_keys, default)
         if self.probation is not None and n:
             _, resident = t.find(keys)
             cand = keys[~resident]
@@ -222,6 +224,40 @@ class KeyValueTable:
             self._touched = unique_keys if self._touched is None else torch.cat([self._touched, unique_keys])
         return slots, rows
 
+    def _admit(self, keys: torch.Tensor, resident: torch.Tensor) -> torch.Tensor:
+        """Keys that are not resident are counted on probation; -> mask of the ones that reach ``admit_threshold`` now
+        (they leave the probation table).  Masks only: no boolean indexing, no host synchronisation."""
+        empty = torch.full_like(keys, -1)
+        cand = torch.where(resident, empty, keys)
+        pslots, _, _ = self.probation.find_or_insert(cand)
+        if isinstance(self.probation, HKVTable):
+            counts = self.probation.scores[pslots.clamp(min=0)]
+        else:
+            counts = torch.tensor([self.probation.score.get(k, 0) for k in cand.tolist()], dtype=torch.int64)
+        ok = (counts >= self.options.admit_threshold) & (pslots >= 0)
+        self.probation.erase(torch.where(ok, cand, empty))
+        return ok
+
+    def _find_then_insert(self, keys: torch.Tensor) -> torch.Tensor:
+        """Slots of ``keys`` with admission: ONE lock-free pass finds the resident keys, refreshes their scores and stamps
+        their slots; only the keys admitted now go through the locked insert (same launch stamp, so it cannot evict what
+        the first pass found)."""
+        t, n = self.table, keys.numel()
+        scores = self._scores_for(n)
+        slots, resident = t.find(keys, update_score=True, scores=scores, stamp=True)
+        ok = self._admit(keys, resident)
+        new_slots, _status, _ = t.find_or_insert(torch.where(ok, keys, torch.full_like(keys, -1)), scores, keep_epoch=True)
+        return torch.where(resident, slots, new_slots)
+
+    def _lookup_with_admission(self, unique_keys: torch.Tensor, default: float) -> Tuple[torch.Tensor, torch.Tensor]:
+        slots = self._find_then_insert(unique_keys)
+        rows = self.table.gather(slots, 0, self.dim, missing_value=default)
+        if self.record_metrics:
+            self.metrics["lookups"] += unique_keys.numel()
+        if self.options.training:
+            self._touched = unique_keys if self._touched is None else torch.cat([self._touched, unique_keys])
+        return slots, rows
+
     def lookup_slots_padded(self, keys: torch.Tensor, training: bool = True) -> torch.Tensor:
         """Slots of a fixed-size key list whose unused entries hold the empty key (-1): no boolean indexing, no host
         synchronisation (the table must not be able to grow any more: ``init_capacity == max_capacity``).  Admission on the
@@ -233,19 +269,10 @@ class KeyValueTable:
         if not training:
             return t.find(keys)[0]
         n = keys.numel()
-        empty = torch.full_like(keys, -1)
         if self.probation is not None and n:
-            _, resident = t.find(keys)
-            cand = torch.where(resident, empty, keys)
-            pslots, _, _ = self.probation.find_or_insert(cand)
-            if isinstance(self.probation, HKVTable):
-                counts = self.probation.scores[pslots.clamp(min=0)]
-            else:
-                counts = torch.tensor([self.probation.score.get(k, 0) for k in cand.tolist()], dtype=torch.int64)
-            ok = (counts >= self.options.admit_threshold) & (pslots >= 0)
-            self.probation.erase(torch.where(ok, cand, empty))
-            keys = torch.where(resident | ok, keys, empty)
-        slots, _status, _ = t.find_or_insert(keys, self._scores_for(n))
+            slots = self._find_then_insert(keys)
+        else:
+            slots, _status, _ = t.find_or_insert(keys, self._scores_for(n))
         if self.options.training:
             self._touched = keys if self._touched is None else torch.cat([self._touched, keys])
         return slots
