@@ -7,7 +7,8 @@ ids ``:587-625``), ``sharding/rw_sequence_sharding.py:34-104``.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+import os
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
@@ -60,16 +61,52 @@ class _SeqLookup(torch.autograd.Function):
         return None, None, None, None
 
 
+def local_unique_kjt(features: KeyedJaggedTensor) -> Tuple[KeyedJaggedTensor, torch.Tensor]:
+    """Every feature's ids de-duplicated over the local batch: -> (KJT of the unique ids - all of a feature's ids sit in its
+    first bag -, index of every original id in the reduced value list).  Host tensors."""
+    F, B = len(features.keys()), features.stride()
+    values = features.values().cpu().long()
+    lpk = features.length_per_key()
+    lengths = torch.zeros(F * B, dtype=torch.int64)
+    uniq, inv, start, base = [], [], 0, 0
+    for f, n in enumerate(lpk):
+        u, i = torch.unique(values[start:start + n], return_inverse=True)
+        uniq.append(u)
+        inv.append(i + base)
+        lengths[f * B] = u.numel()
+        base += u.numel()
+        start += n
+    reduced = KeyedJaggedTensor(features.keys(), torch.cat(uniq) if uniq else values, lengths=lengths, stride=B)
+    return reduced, (torch.cat(inv) if inv else torch.zeros(0, dtype=torch.int64))
+
+
 class EmbCacheShardedEmbeddingCollection(EmbCacheShardedEmbeddingBagCollection):
     def __init__(self, module: EmbCacheEmbeddingBagCollection, env: ShardingEnv, device, optimizer_spec: Optional[E.OptimizerSpec] = None,
                  cache_rows: Optional[List[int]] = None, threads: int = 4) -> None:
         super().__init__(module, env, device, optimizer_spec, cache_rows, threads)
         self._perm: Dict[int, torch.Tensor] = {}
+        self._sent: Dict[int, List[int]] = {}
+        # DO_EC_LOCAL_UNIQUE (true / 1 / yes): every feature's ids are de-duplicated on the sending rank before the id
+        # exchange, so an id that occurs many times in the local batch crosses the network once, is swapped in once and its
+        # row comes back once (sequence embeddings only: torchrec_embcache/distributed/sharding/rw_sharding.py:109-111)
+        self.do_local_unique = os.environ.get("DO_EC_LOCAL_UNIQUE", "False").lower() in ("true", "1", "yes")
 
     def _bucketize(self, features: KeyedJaggedTensor):
-        nl, ni, perm = super()._bucketize(features)
+        if self.do_local_unique:
+            reduced, inv = local_unique_kjt(features)
+            nl, ni, perm_r = super()._bucketize(reduced)
+            perm = perm_r[inv]                                 # bucket order of the unique ids -> every original position
+        else:
+            nl, ni, perm = super()._bucketize(features)
         self._perm[id(features)] = perm
+        self._sent[id(features)] = nl.sum(dim=1).tolist()
         return nl, ni, perm
+
+    def prefetch_async(self, features_dev: KeyedJaggedTensor, features_host: KeyedJaggedTensor) -> None:
+        super().prefetch_async(features_dev, features_host)
+        ctx = self._prepared[id(features_dev)]
+        self._prepared[id(features_dev)] = ctx[:4] + (self._perm.pop(id(features_host)), ctx[4])
+        self._sent[id(features_dev)] = self._sent.pop(id(features_host))
 
     def _prepare(self, features: KeyedJaggedTensor):
         ctx = super()._prepare(features)
@@ -106,6 +143,9 @@ class EmbCacheShardedEmbeddingCollection(EmbCacheShardedEmbeddingBagCollection):
         return out
 
     def _sent_counts(self, features: KeyedJaggedTensor) -> List[int]:
+        sent = self._sent.pop(id(features), None)              # recorded when the batch was bucketized
+        if sent is not None:
+            return sent
         dest = torch.remainder(features.values().cpu().long(), self.world)
         return torch.bincount(dest, minlength=self.world).tolist()
 

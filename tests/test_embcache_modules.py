@@ -154,6 +154,54 @@ def test_sequence_collection_small_cache_equals_big_cache():
     assert np.allclose(a, b, rtol=1e-5, atol=1e-6), (a, b)
 
 
+def test_ec_local_unique_matches_plain_exchange(monkeypatch):
+    """DO_EC_LOCAL_UNIQUE: the ids are de-duplicated per feature before the exchange; outputs, losses and the trained rows
+    are the same, and fewer ids are swapped / looked up."""
+    from recsdk_b200.embcache import EmbCacheEmbeddingCollection, EmbCacheEmbeddingConfig, EmbCacheShardedEmbeddingCollection
+    from recsdk_b200.embcache.embedding import local_unique_kjt
+
+    def build():
+        tabs = [EmbCacheEmbeddingConfig(num_embeddings=50, embedding_dim=8, name="s0", feature_names=["f0"]),
+                EmbCacheEmbeddingConfig(num_embeddings=30, embedding_dim=8, name="s1", feature_names=["f1", "f2"])]
+        ec = EmbCacheEmbeddingCollection(tabs, 1, 6, [3, 3], device="cpu")
+        return EmbCacheShardedEmbeddingCollection(ec, ShardingEnv(1, 0, None), "cpu", ec.optimizer_spec(lr=0.1), cache_rows=[64, 64])
+
+    def batch(g):
+        lengths = torch.randint(1, 5, (18,), generator=g)
+        n = int(lengths.sum())
+        values = torch.randint(0, 25, (n,), generator=g)               # small id range: many repeats inside a batch
+        return KeyedJaggedTensor(["f0", "f1", "f2"], values, lengths=lengths, stride=6)
+
+    def train(m):
+        g = torch.Generator().manual_seed(5)
+        losses, outs, looked_up = [], None, 0
+        for _ in range(6):
+            kjt = batch(g)
+            out = m(kjt)
+            looked_up += m._last_slots if hasattr(m, "_last_slots") else 0
+            loss = sum((jt.values() * (i + 1)).sum(dim=1).pow(2).mean() for i, jt in enumerate(out.values()))
+            loss.backward()
+            losses.append(float(loss.detach()))
+            outs = {k: v.values().detach().clone() for k, v in out.items()}
+        return losses, outs
+
+    monkeypatch.delenv("DO_EC_LOCAL_UNIQUE", raising=False)
+    plain = build()
+    assert not plain.do_local_unique
+    a, oa = train(plain)
+    monkeypatch.setenv("DO_EC_LOCAL_UNIQUE", "yes")
+    uniq = build()
+    assert uniq.do_local_unique
+    b, ob = train(uniq)
+    assert np.allclose(a, b, rtol=1e-5, atol=1e-6), (a, b)
+    for k in oa:
+        assert torch.allclose(oa[k], ob[k], rtol=1e-5, atol=1e-6)
+    kjt = batch(torch.Generator().manual_seed(1))
+    red, inv = local_unique_kjt(kjt)
+    assert torch.equal(red.values()[inv], kjt.values()) and red.values().numel() < kjt.values().numel()
+    assert red.length_per_key() == [int(torch.unique(kjt[k].values()).numel()) for k in ("f0", "f1", "f2")]
+
+
 def test_restore_and_restore_async():
     import pytest
     import torch
