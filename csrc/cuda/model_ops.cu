@@ -257,3 +257,101 @@ RB_API int rb_multislice_concat(const void* in, long long ld_in, void* out, long
       ld_out * elem_bytes, rows, off, elem_bytes, sl);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Disentangled attention (DeBERTa): score[b,n,q,k] = (QK^T[q,k] + C2P[q, clamp(rel[q,k] + span)] + P2C[k, clamp(span - rel[k,q])]) * scale,
+// masked softmax over k.  The three products come from plain GEMMs; this kernel fuses the two gathers, the scale, the
+// mask, the softmax and both outputs (pre-softmax score and probabilities) into one pass over a row.
+// One block per (b, n, q) row; the row lives in shared memory between the passes.
+// Role in the reference: cust_op/framework/torch_plugin/torch_library/disentangle_attention/DisentangleAttenFusion.cpp.
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256) disentangle_softmax_kernel(
+    const T* __restrict__ qk, const T* __restrict__ c2p, const T* __restrict__ p2c, const long long* __restrict__ rel,
+    const unsigned char* __restrict__ mask, long long mask_sb, int N, int S, int P, int span, float scale,
+    T* __restrict__ probs, T* __restrict__ score) {
+  extern __shared__ float row_sm[];
+  __shared__ float red[8];
+  const long long row = blockIdx.x;
+  const int q = static_cast<int>(row % S);
+  const long long bn = row / S;
+  const long long b = bn / N;
+  const T* qk_row = qk + row * S;
+  const T* c2p_row = c2p ? c2p + row * P : nullptr;
+  const T* p2c_bn = p2c ? p2c + bn * S * P : nullptr;
+  const long long* rel_row = rel + static_cast<long long>(q) * S;
+  const unsigned char* mask_row = mask + b * mask_sb + static_cast<long long>(q) * S;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float mx = -INFINITY;
+  for (int k = threadIdx.x; k < S; k += blockDim.x) {
+    const long long r = rel_row[k];
+    float sc = static_cast<float>(qk_row[k]);
+    if (c2p_row) {
+      long long i = r + span;
+      i = i < 0 ? 0 : (i > P - 1 ? P - 1 : i);
+      sc += static_cast<float>(c2p_row[i]);
+    }
+    if (p2c_bn) {
+      // the position-to-content term is gathered for (key, query) and transposed: its index uses rel[k][q]
+      long long i = span - rel[static_cast<long long>(k) * S + q];
+      i = i < 0 ? 0 : (i > P - 1 ? P - 1 : i);
+      sc += static_cast<float>(p2c_bn[static_cast<long long>(k) * P + i]);
+    }
+    sc *= scale;
+    score[row * S + k] = static_cast<T>(sc);
+    const float m = mask_row[k] ? sc : -INFINITY;
+    row_sm[k] = m;
+    mx = fmaxf(mx, m);
+  }
+  mx = warp_max(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int w = 1; w < (blockDim.x >> 5); ++w) mx = fmaxf(mx, red[w]);
+  __syncthreads();
+  float sum = 0.f;
+  for (int k = threadIdx.x; k < S; k += blockDim.x) {
+    const float v = row_sm[k];
+    const float e = v == -INFINITY ? 0.f : __expf(v - mx);
+    row_sm[k] = e;
+    sum += e;
+  }
+  sum = warp_sum_f(sum);
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  sum = 0.f;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) sum += red[w];
+  const float inv = sum > 0.f ? 1.f / sum : 0.f;        // a fully masked row gives zeros
+  for (int k = threadIdx.x; k < S; k += blockDim.x) probs[row * S + k] = static_cast<T>(row_sm[k] * inv);
+}
+
+}  // namespace
+
+// qk [B,N,S,S], c2p / p2c [B,N,S,P] (either may be null), rel [S,S] int64, mask [B or 1][S][S] bytes (mask_stride_b = 0
+// broadcasts one mask); probs / score [B,N,S,S]; all float tensors share `dtype` (0 fp32, 1 fp16, 2 bf16).
+RB_API int rb_disentangle_softmax(const void* qk, const void* c2p, const void* p2c, const long long* rel, const void* mask,
+                                  long long mask_stride_b, int B, int N, int S, int P, int span, float scale, int dtype,
+                                  void* probs, void* score, cudaStream_t st) {
+  const long long rows = static_cast<long long>(B) * N * S;
+  if (rows == 0) return 0;
+  if (rows > 0x7FFFFFFFll || S <= 0 || static_cast<size_t>(S) * 4 > 200 * 1024 || ((c2p || p2c) && P <= 0)) return -1;
+  const size_t smem = static_cast<size_t>(S) * sizeof(float);
+#define RB_DIS(T_)                                                                                                        \
+  do {                                                                                                                    \
+    if (smem > 48 * 1024)                                                                                                 \
+      RB_CUDA_CHECK(cudaFuncSetAttribute(disentangle_softmax_kernel<T_>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                         static_cast<int>(smem)));                                                        \
+    disentangle_softmax_kernel<T_><<<static_cast<unsigned>(rows), 256, smem, st>>>(                                       \
+        reinterpret_cast<const T_*>(qk), reinterpret_cast<const T_*>(c2p), reinterpret_cast<const T_*>(p2c), rel,         \
+        reinterpret_cast<const unsigned char*>(mask), mask_stride_b, N, S, P, span, scale, reinterpret_cast<T_*>(probs),  \
+        reinterpret_cast<T_*>(score));                                                                                    \
+  } while (0)
+  if (dtype == DT_F32) RB_DIS(float);
+  else if (dtype == DT_F16) RB_DIS(__half);
+  else if (dtype == DT_BF16) RB_DIS(__nv_bfloat16);
+  else return -1;
+#undef RB_DIS
+  return static_cast<int>(cudaGetLastError());
+}

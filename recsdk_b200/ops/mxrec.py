@@ -392,14 +392,105 @@ _def("split_embedding_codegen_forward_unweighted_cuda(Tensor dev_weights, Tensor
 
 
 # ------------------------------------------------------------------------------------------------ optional parity ops
+def _fuxi_kernels(q, k, v, tsb, pob, mask, mask_type: int, scale: float, offs: List[int], max_len: int):
+    """Fuxi forward on this library's kernels, ``q/k/v`` ``[T, N, D]`` bf16 with sequence offsets ``offs``: the SiLU part on
+    the tcgen05 attention kernel (causal flag or custom mask in the kernel), the two bias parts as masked-bias x V GEMMs on
+    the tcgen05 GEMM (one per sequence; per head when the custom mask differs between heads)."""
+    from .gemm import gemm16
+    from .hstu_attention import hstu_attn_fwd
+
+    T, N, D = q.shape
+    dev = q.device
+    offsets = torch.tensor(offs, dtype=torch.int32, device=dev)
+    part1 = hstu_attn_fwd(q, k, v, offsets, offsets, max_len, 1.0, scale, causal=mask_type == 0,
+                          attn_mask=mask if mask_type == 3 else None)
+    if tsb is None and pob is None:
+        return part1
+    out = torch.empty(T, N, 3 * D, dtype=q.dtype, device=dev)
+    out[:, :, :D] = part1
+    vf = v.reshape(T, N * D)
+    for b in range(len(offs) - 1):
+        lo, L = offs[b], offs[b + 1] - offs[b]
+        if L == 0:
+            continue
+        Lp = (L + 7) // 8 * 8
+        for part, bias in ((1, tsb), (2, pob)):
+            dst = out[lo:lo + L, :, part * D:(part + 1) * D]
+            if bias is None:
+                dst.zero_()
+                continue
+            bm = bias[min(b, bias.shape[0] - 1), :L, :L]
+            per_head = mask_type == 3 and mask.shape[1] > 1
+            heads = range(N) if per_head else (None,)
+            for h in heads:
+                a = torch.zeros(L, Lp, dtype=q.dtype, device=dev)              # row stride a multiple of 16 bytes for TMA
+                if mask_type == 0:
+                    a[:, :L] = torch.tril(bm)
+                elif mask_type == 3:
+                    a[:, :L] = bm * mask[b, h if per_head else 0, :L, :L].to(bm.dtype)
+                else:
+                    a[:, :L] = bm
+                if per_head:
+                    dst[:, h, :] = gemm16(a[:, :L], v[lo:lo + L, h, :], b_mn=True)
+                else:
+                    dst.copy_(gemm16(a[:, :L], vf[lo:lo + L], b_mn=True).view(L, N, D))
+    return out
+
+
+class _FuxiFn(torch.autograd.Function):
+    """Kernel forward; gradients from the fp32 statement (``_fuxi_ref``)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, tsb, pob, mask, mask_type, scale, offs, max_len):
+        ctx.save_for_backward(q, k, v, *(t if t is not None else q.new_zeros(0) for t in (tsb, pob, mask)))
+        ctx.meta = (mask_type, scale, offs, tsb is not None, pob is not None, mask is not None)
+        return _fuxi_kernels(q, k, v, tsb, pob, mask, mask_type, scale, offs, max_len)
+
+    @staticmethod
+    def backward(ctx, grad):
+        q, k, v, tsb, pob, mask = ctx.saved_tensors
+        mask_type, scale, offs, has_t, has_p, has_m = ctx.meta
+        with torch.enable_grad():
+            leaves = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+            tb = tsb.detach().float().requires_grad_(True) if has_t else None
+            pb = pob.detach().float().requires_grad_(True) if has_p else None
+            out = _fuxi_ref(leaves[0], leaves[1], leaves[2], tb, pb, mask if has_m else None, mask_type, scale, "jagged", offs)
+            wanted = leaves + [t for t in (tb, pb) if t is not None]
+            gs = list(torch.autograd.grad(out, wanted, grad.float()))
+        dq, dk, dv = (g.to(q.dtype) for g in gs[:3])
+        rest = gs[3:]
+        dt = rest.pop(0).to(tsb.dtype) if has_t else None
+        dp = rest.pop(0).to(pob.dtype) if has_p else None
+        return dq, dk, dv, dt, dp, None, None, None, None, None
+
+
 def hstu_fuxi(q, k, v, timestampBias=None, positionBias=None, mask=None, maskType: int = 0, maxSeqLen: int = 0, siluScale: float = 0.0,
               layout: str = "normal", seqOffset: Optional[List[int]] = None):
     """Fuxi variant: ``cat[(SiLU(QK^T) s m) V, (tsBias m) V, (posBias m) V]`` on the last dim (only the first part when no
     bias is given).  ``layout`` "normal": ``[B,S,N,D]``; "jagged": ``[sum_len,N,D]`` with ``seqOffset``
-    (``hstu_dense_forward_fuxi/README.md`` of the reference).  PyTorch composition (fp32 math)."""
+    (``hstu_dense_forward_fuxi/README.md`` of the reference).  bf16 CUDA inputs with head dim 64 / 128 run on the tcgen05
+    attention and GEMM kernels; everything else on the fp32 PyTorch statement."""
     if maskType == 1:
         raise NotImplementedError("upper-triangular masks are not supported")
     scale = siluScale if siluScale != 0.0 else 1.0 / max(maxSeqLen, 1)
+    D = q.shape[-1]
+    if q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and v.shape[-1] == D and (q.shape[-2] * D) % 8 == 0 \
+            and not (maskType == 3 and (mask is None or mask.dim() != 4)) \
+            and all(t is None or t.dtype == q.dtype for t in (timestampBias, positionBias)):
+        if layout == "jagged":
+            offs = [int(x) for x in seqOffset]
+            return _FuxiFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), timestampBias, positionBias, mask, maskType, scale,
+                                 offs, max(maxSeqLen, max(b - a for a, b in zip(offs, offs[1:]))))
+        B, S, N, _ = q.shape
+        offs = [i * S for i in range(B + 1)]
+        out = _FuxiFn.apply(q.reshape(B * S, N, D), k.reshape(B * S, N, D), v.reshape(B * S, N, D), timestampBias, positionBias, mask,
+                            maskType, scale, offs, S)
+        return out.view(B, S, N, -1)
+    return _fuxi_ref(q, k, v, timestampBias, positionBias, mask, maskType, scale, layout, seqOffset)
+
+
+def _fuxi_ref(q, k, v, timestampBias, positionBias, mask, maskType: int, scale: float, layout: str, seqOffset):
+    """The fuxi statement in fp32 PyTorch ops (oracle of the kernel path and its gradient)."""
 
     def one(qq, kk, vv, b):                                        # [L,N,D] each
         L = qq.shape[0]
@@ -425,8 +516,60 @@ def hstu_fuxi(q, k, v, timestampBias=None, positionBias=None, mask=None, maskTyp
     return torch.stack([one(q[b], k[b], v[b], b) for b in range(q.shape[0])])
 
 
+class _DisentangleFn(torch.autograd.Function):
+    """CUDA forward: the four products are plain (library) GEMMs in the input dtype, everything between them - both
+    relative-position gathers, scale, mask, softmax, the two matrix outputs - is one pass of ``rb_disentangle_softmax``.
+    Gradients come from the fp32 statement."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, pos_k, pos_q, rel, mask, kinds, scale):
+        from . import _lib
+
+        B, N, S, _ = q.shape
+        P = pos_k.shape[0]
+        qk = torch.matmul(q, k.transpose(-1, -2)).contiguous()
+        c2p = torch.matmul(q, pos_k.permute(1, 2, 0).to(q.dtype)).contiguous() if "c2p" in kinds else None      # [B,N,S,P]
+        p2c = torch.matmul(k, pos_q.permute(1, 2, 0).to(q.dtype)).contiguous() if "p2c" in kinds else None
+        rel2 = rel.reshape(S, S).long().contiguous()
+        m8 = (mask != 0).to(torch.uint8).reshape(-1, S, S).contiguous()
+        probs, score = torch.empty_like(qk), torch.empty_like(qk)
+        rc = _lib.lib().rb_disentangle_softmax(qk.data_ptr(), _lib.ptr(c2p), _lib.ptr(p2c), rel2.data_ptr(), m8.data_ptr(),
+                                               S * S if m8.shape[0] == B else 0, B, N, S, P, P // 2, float(scale),
+                                               _lib.dtype_code(q.dtype), probs.data_ptr(), score.data_ptr(),
+                                               _lib.stream_ptr(q.device))
+        _lib.check(rc, "rb_disentangle_softmax")
+        out = torch.matmul(probs, v)
+        ctx.save_for_backward(q, k, v, pos_k, pos_q, rel, mask)
+        ctx.meta = (kinds, scale)
+        return out, probs, score
+
+    @staticmethod
+    def backward(ctx, g_out, g_probs, g_score):
+        q, k, v, pos_k, pos_q, rel, mask = ctx.saved_tensors
+        kinds, scale = ctx.meta
+        with torch.enable_grad():
+            leaves = [t.detach().float().requires_grad_(True) for t in (q, k, v, pos_k, pos_q)]
+            outs = _disentangle_ref(*leaves, rel, mask, kinds, scale)
+            gs = torch.autograd.grad(outs, leaves, [g.float() for g in (g_out, g_probs, g_score)], allow_unused=True)
+        cast = [None if g is None else g.to(t.dtype) for g, t in zip(gs, (q, k, v, pos_k, pos_q))]
+        return cast[0], cast[1], cast[2], cast[3], cast[4], None, None, None, None
+
+
 def disentangle_attention(query_layer, key_layer, value_layer, pos_key_layer, pos_query_layer, relative_pos, attn_mask,
                           pos_attr_type: str, score_scale: float):
+    """DeBERTa disentangled attention; CUDA tensors run the fused gather / mask / softmax kernel between plain GEMMs, CPU
+    tensors the fp32 statement (``_disentangle_ref``, same contract)."""
+    if query_layer.is_cuda and query_layer.dtype in (torch.float32, torch.float16, torch.bfloat16) \
+            and key_layer.shape == query_layer.shape and relative_pos.numel() == query_layer.shape[2] ** 2 \
+            and attn_mask.numel() in (query_layer.shape[2] ** 2, query_layer.shape[0] * query_layer.shape[2] ** 2):
+        return _DisentangleFn.apply(query_layer, key_layer, value_layer, pos_key_layer, pos_query_layer, relative_pos, attn_mask,
+                                    pos_attr_type, score_scale)
+    return _disentangle_ref(query_layer, key_layer, value_layer, pos_key_layer, pos_query_layer, relative_pos, attn_mask,
+                            pos_attr_type, score_scale)
+
+
+def _disentangle_ref(query_layer, key_layer, value_layer, pos_key_layer, pos_query_layer, relative_pos, attn_mask,
+                     pos_attr_type: str, score_scale: float):
     """DeBERTa disentangled attention.  ``query/key/value`` ``[b,n,s,d]``, ``pos_key/pos_query`` ``[2s,n,d]``, ``relative_pos``
     ``[1,1,s,s]`` int64, ``attn_mask`` ``[b,1,s,s]``; ``pos_attr_type`` in ``c2p``, ``p2c``, ``c2p|p2c``.
     Returns ``(outputs, probs, weights)`` where ``weights`` is the pre-softmax score (content + position terms)

@@ -189,3 +189,41 @@ def test_jagged_attn_bias_on_the_kernel():
     err = (out.float() - want.float()).abs().amax(dim=-1)
     scale = want.float().abs().amax(dim=-1).clamp_min(1e-3)
     assert float((err / scale).max()) < 3e-2
+
+
+@pytest.mark.parametrize("mask_type,layout", [(0, "jagged"), (3, "jagged"), (2, "normal"), (0, "normal")])
+def test_fuxi_variant_on_the_kernels(mask_type, layout):
+    """``hstu_fuxi`` (SiLU attention + two bias-times-V parts) through the tcgen05 attention and GEMM kernels against the
+    fp32 statement, forward and gradients."""
+    import torch
+
+    from recsdk_b200.ops import mxrec  # noqa: F401
+    from recsdk_b200.ops.mxrec import _fuxi_ref
+
+    dev = torch.device("cuda", 0)
+    N, D, S = 2, 64, 160
+    g = torch.Generator().manual_seed(3 + mask_type)
+    if layout == "jagged":
+        offs = [0, 70, 229, 330]                                   # lengths 70, 159, 101 (not multiples of 8)
+        T, nb = offs[-1], 3
+        shape = (T, N, D)
+    else:
+        offs, nb = None, 2
+        shape = (nb, S, N, D)
+    q, k, v = ((torch.randn(*shape, generator=g) * 0.5).to(dev, torch.bfloat16).requires_grad_() for _ in range(3))
+    tsb = (torch.randn(nb, S, S, generator=g) * 0.3).to(dev, torch.bfloat16).requires_grad_()
+    pob = (torch.randn(1, S, S, generator=g) * 0.3).to(dev, torch.bfloat16).requires_grad_()
+    mask = (torch.rand(nb, N, S, S, generator=g) < 0.5).to(dev, torch.bfloat16) if mask_type == 3 else None
+    out = torch.ops.mxrec.hstu_fuxi(q, k, v, tsb, pob, mask, mask_type, S, 0.0, layout, offs)
+    refs = [t.detach().float().requires_grad_() for t in (q, k, v, tsb, pob)]
+    want = _fuxi_ref(*refs, mask, mask_type, 1.0 / S, layout, offs)
+    assert out.shape == want.shape and out.shape[-1] == 3 * D
+    err = (out.float() - want).abs().amax(dim=-1)
+    scale = want.abs().amax(dim=-1).clamp_min(1e-2)
+    assert float((err / scale).max()) < 4e-2, float((err / scale).max())
+    w = torch.randn(out.shape, generator=g).to(dev)
+    (out.float() * w).sum().backward()
+    (want * w).sum().backward()
+    for got, ref in zip((q, k, v, tsb, pob), refs):
+        rel = (got.grad.float() - ref.grad).abs().max() / ref.grad.abs().max().clamp_min(1e-6)
+        assert float(rel) < 3e-2, float(rel)

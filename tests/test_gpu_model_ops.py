@@ -73,3 +73,33 @@ def test_tensor_map_kernel_as_first_node_of_a_fresh_autograd_thread():
         "print('ok')\n")
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("dtype,kinds", [(torch.float32, "c2p|p2c"), (torch.bfloat16, "c2p|p2c"), (torch.float16, "c2p"), (torch.float32, "p2c")])
+def test_disentangle_attention_fused_softmax(dtype, kinds):
+    from recsdk_b200.ops import mxrec  # noqa: F401
+    from recsdk_b200.ops.mxrec import _disentangle_ref
+
+    b, n, s, d, span = 2, 3, 70, 32, 16
+    g = torch.Generator().manual_seed(9)
+    q, k, v = ((torch.randn(b, n, s, d, generator=g) * 0.5).to(DEV, dtype).requires_grad_() for _ in range(3))
+    pk, pq = ((torch.randn(2 * span, n, d, generator=g) * 0.5).to(DEV, dtype).requires_grad_() for _ in range(2))
+    pos = torch.arange(s)
+    rel = (pos[:, None] - pos[None, :] + torch.randint(-2, 3, (s, s), generator=g)).view(1, 1, s, s).to(DEV)   # not antisymmetric
+    mask = (torch.rand(b, 1, s, s, generator=g) < 0.8).to(DEV)
+    mask[0, 0, 5] = False                                              # a fully masked row
+    out, probs, score = torch.ops.mxrec.disentangle_attention(q, k, v, pk, pq, rel, mask, kinds, 0.1)
+    refs = [t.detach().float().requires_grad_() for t in (q, k, v, pk, pq)]
+    wo, wp, ws = _disentangle_ref(*refs, rel, mask, kinds, 0.1)
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    for got, want in ((out, wo), (probs, wp), (score, ws)):
+        assert got.dtype == dtype and got.shape == want.shape
+        assert (got.float() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+    assert float(probs[0, :, 5].abs().max()) == 0.0
+    w = torch.randn(out.shape, generator=g).to(DEV)
+    (out.float() * w).sum().backward()
+    (wo * w).sum().backward()
+    for got, ref in zip((q, k, v, pk, pq), refs):
+        if ref.grad is None:
+            continue
+        assert (got.grad.float() - ref.grad).abs().max().item() <= 3e-2 * max(1e-3, ref.grad.abs().max().item())
