@@ -78,7 +78,19 @@ class PeerGroup:
         if not self.use_multimem:
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         self._symm = None
-        if self.world > 1:
+        # who allocates and exchanges the peer buffers: PyTorch symmetric memory ("symm", default; also provides the
+        # multicast mapping) or this package's own CUDA-IPC bootstrap ("ipc", recsdk_b200/parallel/ipc.py)
+        self.backend = os.environ.get("RECSDK_B200_PEER_BACKEND", "symm")
+        if self.backend not in ("symm", "ipc"):
+            raise ValueError("RECSDK_B200_PEER_BACKEND must be 'symm' or 'ipc'")
+        self._ipc = None
+        if self.world > 1 and self.backend == "ipc":
+            from .ipc import IpcAllocator
+
+            if self.use_multimem:
+                raise ValueError("the ipc peer backend has no multicast mapping: unset RECSDK_B200_MULTIMEM")
+            self._ipc = IpcAllocator(self.pg, device, name="pg%s" % getattr(self.pg, "group_name", "world"))
+        elif self.world > 1:
             import torch.distributed._symmetric_memory as symm_mem
 
             self._symm = symm_mem
@@ -97,6 +109,9 @@ class PeerGroup:
             if zero:
                 t.zero_()
             return PeerBuffer(t, [t.data_ptr()], 0)
+        if self._ipc is not None:
+            b = self._ipc.alloc(nbytes)                     # zero-filled by the allocator
+            return PeerBuffer(b.local, b.ptrs, 0, b)
         t = self._symm.empty(nbytes, dtype=torch.uint8, device=self.device)
         if zero:
             t.zero_()

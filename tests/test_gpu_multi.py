@@ -67,3 +67,15 @@ def test_sharded_dlrm_deterministic_gradient_order():
         pytest.skip("needs at least 2 GPUs")
     p = _run(2, [], LCCL_DETERMINISTIC="1")
     assert p.returncode == 0 and "MULTI_GPU_RESULT PASS" in p.stdout
+
+
+def test_own_ipc_peer_backend():
+    """``RECSDK_B200_PEER_BACKEND=ipc``: the peer buffers come from this package's own CUDA-IPC bootstrap instead of PyTorch
+    symmetric memory; the push all-reduce and the sharded DLRM step give the same results on them."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    p = _run(min(n, 4), ["--allreduce"], RECSDK_B200_PEER_BACKEND="ipc")
+    assert p.returncode == 0 and "MULTI_GPU_RESULT PASS" in p.stdout
+    p = _run(2, [], RECSDK_B200_PEER_BACKEND="ipc")
+    assert p.returncode == 0 and "MULTI_GPU_RESULT PASS" in p.stdout
