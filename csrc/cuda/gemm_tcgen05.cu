@@ -10,8 +10,9 @@
 //   backward GEMMs of a linear layer (dX = dY * W, dW = dY^T * X) without transposes,
 // * split-K (fp32 atomic accumulation) serves dW, whose contraction is the batch.
 //
-// Roles in a 256-thread CTA: warp 0 = TMA producer, warp 1 = MMA issuer,
-// warp 2 = TMEM allocator, warps 4..7 = epilogue (TMEM lane quarter = warp % 4).
+// Roles in a 384-thread CTA: warp 0 = TMA producer, warp 1 = MMA issuer,
+// warp 2 = TMEM allocator, warps 4..11 = epilogue (TMEM lane quarter = warp % 4; warps 4..7 take the first half of the
+// columns, warps 8..11 the second; each keeps the next 32-column TMEM load in flight while it stores the current one).
 //
 // Covers the MLP / in_linear_silu / DCN-cross GEMMs of the framework (the reference
 // runs these through CATLASS/aclnn matmuls, e.g. cust_op/.../in_linear_silu).
@@ -21,6 +22,7 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
+constexpr int GEMM_THREADS = 384;      // 4 role warps + 8 epilogue warps (two per TMEM lane quarter, half of the columns each)
 
 enum Epi : int {
   EPI_BF16 = 0,        // out16 = acc (+bias)
@@ -41,6 +43,7 @@ struct GemmParams {
   const void* aux;
   long long ld_aux;
   int epi;
+  int tma_out;               // 16-bit output written by TMA stores from a shared-memory box (base / stride permit it)
   int is_bf16;
   float alpha;
   float* colsum;          // optional [N] fp32: += column sums of the epilogue's output values (bias gradients)
@@ -53,8 +56,11 @@ struct Cfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : ((BN == 128) ? 6 : 8);
-  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+  static constexpr int BAR_BYTES = (2 * STAGES + 8) * 8 + 16;
+  // epilogue staging for TMA stores: one [128 rows][64 columns] 16-bit box (128-byte swizzle) per epilogue group
+  static constexpr int OUT_BOX_BYTES = BM * 64 * 2;
+  static constexpr int OUT_GROUPS = (BN >= 128) ? 2 : 0;      // BN = 64 keeps the direct stores
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_GROUPS * OUT_BOX_BYTES + BAR_BYTES + 1024;
   static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
 };
 
@@ -64,18 +70,21 @@ __device__ __forceinline__ float to_f32_16(uint16_t raw, int is_bf16) {
 }
 
 template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-            const GemmParams p) {
+            const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint8_t* out_stage = smem + C::STAGES * C::STAGE_BYTES;                       // 1024-byte aligned
+  uint64_t* full = reinterpret_cast<uint64_t*>(out_stage + C::OUT_GROUPS * C::OUT_BOX_BYTES);
   uint64_t* empty = full + C::STAGES;
   uint64_t* tfull = empty + C::STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* obar_free = tempty + 2;          // per epilogue group: the staging box may be rewritten
+  uint64_t* obar_full = obar_free + 2;       // per epilogue group: all 128 rows of the box are written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(obar_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -88,12 +97,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     }
     for (int b = 0; b < 2; ++b) {
       rb::mbar_init(&tfull[b], 1);
-      rb::mbar_init(&tempty[b], 128);
+      rb::mbar_init(&tempty[b], GEMM_THREADS - 128);
+      rb::mbar_init(&obar_free[b], 1);
+      rb::mbar_init(&obar_full[b], 128);
     }
     *abort_flag = 0;
     rb::mbar_fence_init();
     rb::tma_prefetch_desc(&tma_a);
     rb::tma_prefetch_desc(&tma_b);
+    if (p.tma_out) rb::tma_prefetch_desc(&tma_c);
   }
   if (warp == 2) {
     rb::tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -176,7 +188,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     }
   } else if (warp >= 4) {
     // -------------------------------- epilogue --------------------------------
-    const int ew = warp & 3;
+    const int ew = warp & 3;                  // TMEM lane quarter this warp may read
+    const int eg = (warp - 4) >> 2;           // which half of the tile's columns
+    constexpr int CPG = BN / 64;              // 32-column chunks per warp
+    // TMA-store mode: the group's four warps assemble a [128][64] box in shared memory (two chunks), one thread stores it
+    const bool tma_out = C::OUT_GROUPS > 0 && p.tma_out != 0;
+    const bool box_leader = (ew == 0 && lane == 0);
+    uint8_t* my_box = out_stage + (C::OUT_GROUPS > 0 ? eg : 0) * C::OUT_BOX_BYTES;
+    uint32_t box_it = 0;
+    const uint64_t pol_out = rb::l2_policy_evict_first();      // the output is not read again by this kernel
     int acc_it = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++acc_it) {
       const int t = w / p.splits;
@@ -189,13 +209,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       rb::tc_fence_after();
       const long long m = static_cast<long long>(tm) * BM + ew * 32 + lane;
       const bool row_ok = m < p.M;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        rb::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + buf * BN + c * 32, r);
+      // the load of chunk i + 1 is in flight while chunk i is converted and stored
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + buf * BN + eg * (CPG * 32);
+      uint32_t ra[32], rb2[32];
+      rb::tmem_ld_32x32(t_row, ra);
+#pragma unroll
+      for (int ci = 0; ci < CPG; ++ci) {
         rb::tmem_ld_wait();
+        if (ci + 1 < CPG) rb::tmem_ld_32x32(t_row + (ci + 1) * 32, (ci & 1) ? ra : rb2);
+        const uint32_t (&r)[32] = (ci & 1) ? rb2 : ra;
+        const int c = eg * CPG + ci;
         const int n0 = tn * BN + c * 32;
-        if (n0 >= p.N || (!row_ok && p.colsum == nullptr)) continue;
+        const int box_n0 = tn * BN + (c & ~1) * 32;
+        // TMA mode: every thread of the group takes part in every box that starts inside the tensor (rows and columns
+        // beyond it are clipped by the store); direct mode: skip what is outside
+        if (tma_out ? (box_n0 >= p.N) : (n0 >= p.N || (!row_ok && p.colsum == nullptr))) continue;
         const bool full_chunk = (n0 + 32 <= p.N);
         float v[32];
 #pragma unroll
@@ -290,13 +318,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             }
           }
           if (n0 + lane < p.N && cs[0] != 0.f) atomicAdd(p.colsum + n0 + lane, cs[0]);
-          if (!row_ok) continue;
+          if (!row_ok && !tma_out) continue;
         }
-        uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + m * p.ldc + n0;
         uint32_t pk[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j)
           pk[j] = p.is_bf16 ? rb::pack_bf16(v[2 * j], v[2 * j + 1]) : rb::pack_f16(v[2 * j], v[2 * j + 1]);
+        if (tma_out) {
+          if ((ci & 1) == 0) {
+            // the previous box of this group must have been read out of shared memory by its store
+            if (box_leader) {
+              if (box_it > 0) rb::tma_store_wait_read();
+              rb::mbar_arrive(&obar_free[eg]);
+            }
+            if (!rb::mbar_wait(&obar_free[eg], box_it & 1, abort_flag, p.status)) goto done;
+          }
+          const int row = ew * 32 + lane;
+          uint8_t* dst = my_box + row * 128;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int q = ((ci & 1) * 4 + j) ^ (row & 7);                       // 128-byte swizzle: 16-byte unit ^ (row % 8)
+            *reinterpret_cast<uint4*>(dst + q * 16) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+          }
+          if ((ci & 1) == 1) {
+            rb::fence_proxy_async_smem();
+            rb::mbar_arrive(&obar_full[eg]);
+            if (box_leader) {
+              if (!rb::mbar_wait(&obar_full[eg], box_it & 1, abort_flag, p.status)) goto done;
+              rb::tma_store_2d_hint(&tma_c, my_box, box_n0, tm * BM, pol_out);
+              rb::tma_store_commit();
+            }
+            ++box_it;
+          }
+          continue;
+        }
+        uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + m * p.ldc + n0;
         if (full_chunk && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
           for (int j = 0; j < 4; ++j)
@@ -310,6 +366,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       rb::tc_fence_before();
       rb::mbar_arrive(&tempty[buf]);
     }
+    if (tma_out && box_leader) rb::tma_store_wait_all();        // shared memory stays valid until the stores have read it
   }
 done:
   __syncwarp();
@@ -328,7 +385,7 @@ int make_map_2d(CUtensorMap* map, const void* base, long long rows, long long co
 }
 
 template <int BN, bool A_MN, bool B_MN>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid, cudaStream_t st) {
   using C = Cfg<BN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -336,7 +393,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, in
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set = true;
   }
-  gemm_kernel<BN, A_MN, B_MN><<<grid, 256, C::SMEM_BYTES, st>>>(ta, tb, p);
+  gemm_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, C::SMEM_BYTES, st>>>(ta, tb, tc, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -372,7 +429,18 @@ RB_API int rb_gemm16(const void* A, long long lda, int a_mn, const void* B, long
   else      rc = make_map_2d(&tb, B, N, K, ldb, BK, bn, is_bf16);
   if (rc) return rc;
 
+  // 16-bit outputs with a TMA-compatible layout leave through TMA stores of [128][64] boxes (full 128-byte lines
+  // instead of 16-byte pieces per thread)
+  const bool out16 = !(epi == EPI_F32_ATOMIC || epi == EPI_F32);
+  const int tma_out = (out16 && bn >= 128 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) ? 1 : 0;
+  CUtensorMap tc = tb;
+  if (tma_out) {
+    rc = make_map_2d(&tc, out, M, N, ldc, 64, BM, is_bf16);
+    if (rc) return rc;
+  }
+
   GemmParams p;
+  p.tma_out = tma_out;
   p.M = M; p.N = N; p.K = K;
   p.splits = splits; p.kb_per_split = kbps;
   p.out = out; p.ldc = ldc; p.bias = bias; p.aux = aux; p.ld_aux = ld_aux;
@@ -383,10 +451,10 @@ RB_API int rb_gemm16(const void* A, long long lda, int a_mn, const void* B, long
   const int grid = tiles < num_sms ? tiles : num_sms;
 
 #define RB_DISPATCH(BN_)                                                                     \
-  if (a_mn && b_mn) return launch<BN_, true, true>(ta, tb, p, grid, stream);                 \
-  if (a_mn && !b_mn) return launch<BN_, true, false>(ta, tb, p, grid, stream);               \
-  if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, p, grid, stream);               \
-  return launch<BN_, false, false>(ta, tb, p, grid, stream);
+  if (a_mn && b_mn) return launch<BN_, true, true>(ta, tb, tc, p, grid, stream);                 \
+  if (a_mn && !b_mn) return launch<BN_, true, false>(ta, tb, tc, p, grid, stream);               \
+  if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, tc, p, grid, stream);               \
+  return launch<BN_, false, false>(ta, tb, tc, p, grid, stream);
   if (bn == 256) { RB_DISPATCH(256) }
   if (bn == 128) { RB_DISPATCH(128) }
   RB_DISPATCH(64)
