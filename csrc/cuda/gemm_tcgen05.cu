@@ -57,7 +57,7 @@ struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : ((BN == 128) ? 6 : 8);
   static constexpr int BAR_BYTES = (2 * STAGES + 8) * 8 + 16;
-  // epilogue staging for TMA stores: one [128 rows][64 columns] 16-bit box (128-byte swizzle) per epilogue group
+  // epilogue staging for TMA stores: two [128 rows][64 columns] 16-bit boxes (128-byte swizzle), used alternately
   static constexpr int OUT_BOX_BYTES = BM * 64 * 2;
   static constexpr int OUT_GROUPS = (BN >= 128) ? 2 : 0;      // BN = 64 keeps the direct stores
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_GROUPS * OUT_BOX_BYTES + BAR_BYTES + 1024;
@@ -72,7 +72,7 @@ __device__ __forceinline__ float to_f32_16(uint16_t raw, int is_bf16) {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-            const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
+            const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_x, const GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -99,13 +99,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       rb::mbar_init(&tfull[b], 1);
       rb::mbar_init(&tempty[b], GEMM_THREADS - 128);
       rb::mbar_init(&obar_free[b], 1);
-      rb::mbar_init(&obar_full[b], 128);
+      rb::mbar_init(&obar_full[b], GEMM_THREADS - 128);
     }
     *abort_flag = 0;
     rb::mbar_fence_init();
     rb::tma_prefetch_desc(&tma_a);
     rb::tma_prefetch_desc(&tma_b);
-    if (p.tma_out) rb::tma_prefetch_desc(&tma_c);
+    if (p.tma_out) { rb::tma_prefetch_desc(&tma_c); rb::tma_prefetch_desc(&tma_x); }
   }
   if (warp == 2) {
     rb::tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -189,14 +189,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   } else if (warp >= 4) {
     // -------------------------------- epilogue --------------------------------
     const int ew = warp & 3;                  // TMEM lane quarter this warp may read
-    const int eg = (warp - 4) >> 2;           // which half of the tile's columns
-    constexpr int CPG = BN / 64;              // 32-column chunks per warp
-    // TMA-store mode: the group's four warps assemble a [128][64] box in shared memory (two chunks), one thread stores it
+    const int eg = (warp - 4) >> 2;           // which 32-column half of every 64-column box
+    constexpr int CPG = BN / 64;              // boxes per tile = 32-column chunks per warp
+    // TMA mode: the eight warps assemble one [128][64] box at a time in one of two shared-memory buffers; one thread
+    // stores it (and, for the mask / SiLU-derivative epilogues, first loads the matching box of `aux` into the same
+    // buffer, one box ahead).  Box k lives in buffer k % 2; obar_free[u] completes when buffer u may be written (its
+    // previous store has read it, its aux box has landed), obar_full[u] when all 256 rows-halves are written.
     const bool tma_out = C::OUT_GROUPS > 0 && p.tma_out != 0;
-    const bool box_leader = (ew == 0 && lane == 0);
-    uint8_t* my_box = out_stage + (C::OUT_GROUPS > 0 ? eg : 0) * C::OUT_BOX_BYTES;
+    const bool tma_aux = tma_out && (p.epi == EPI_BF16_MASK || p.epi == EPI_BF16_DSILU);
+    const bool box_leader = (warp == 4 && lane == 0);
     uint32_t box_it = 0;
     const uint64_t pol_out = rb::l2_policy_evict_first();      // the output is not read again by this kernel
+    const int my_tiles = (total - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+    const uint32_t total_boxes = static_cast<uint32_t>(my_tiles) * CPG;
+    // leader: make buffer (k % 2) ready for box k
+    auto prepare_box = [&](uint32_t k) {
+      const int wk = blockIdx.x + static_cast<int>(k / CPG) * gridDim.x;
+      const int tk = wk / p.splits;
+      const int n0k = (tk % tiles_n) * BN + static_cast<int>(k % CPG) * 64;
+      uint64_t* bar = &obar_free[k & 1];
+      if (tma_aux && n0k < p.N) {
+        rb::mbar_expect_tx(bar, C::OUT_BOX_BYTES);
+        rb::tma_load_2d(out_stage + (k & 1) * C::OUT_BOX_BYTES, &tma_x, bar, n0k, (tk / tiles_n) * BM);
+      } else {
+        rb::mbar_arrive(bar);
+      }
+    };
+    if (tma_out && box_leader && total_boxes > 0) prepare_box(0);
     int acc_it = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++acc_it) {
       const int t = w / p.splits;
@@ -210,20 +229,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       const long long m = static_cast<long long>(tm) * BM + ew * 32 + lane;
       const bool row_ok = m < p.M;
       // the load of chunk i + 1 is in flight while chunk i is converted and stored
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + buf * BN + eg * (CPG * 32);
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + buf * BN + eg * 32;
       uint32_t ra[32], rb2[32];
       rb::tmem_ld_32x32(t_row, ra);
 #pragma unroll
       for (int ci = 0; ci < CPG; ++ci) {
         rb::tmem_ld_wait();
-        if (ci + 1 < CPG) rb::tmem_ld_32x32(t_row + (ci + 1) * 32, (ci & 1) ? ra : rb2);
+        if (ci + 1 < CPG) rb::tmem_ld_32x32(t_row + (ci + 1) * 64, (ci & 1) ? ra : rb2);
         const uint32_t (&r)[32] = (ci & 1) ? rb2 : ra;
-        const int c = eg * CPG + ci;
+        const int c = 2 * ci + eg;
         const int n0 = tn * BN + c * 32;
-        const int box_n0 = tn * BN + (c & ~1) * 32;
-        // TMA mode: every thread of the group takes part in every box that starts inside the tensor (rows and columns
-        // beyond it are clipped by the store); direct mode: skip what is outside
-        if (tma_out ? (box_n0 >= p.N) : (n0 >= p.N || (!row_ok && p.colsum == nullptr))) continue;
+        const int box_n0 = tn * BN + ci * 64;
+        const int row = ew * 32 + lane;
+        uint8_t* box_row = out_stage + (box_it & 1) * C::OUT_BOX_BYTES + row * 128;
+        if (tma_out) {
+          // every thread goes through the hand-offs of every box (uniform sequence); boxes that start beyond the tensor
+          // carry no data
+          if (box_leader && box_it + 1 < total_boxes) {
+            if (box_it >= 1) rb::tma_store_wait_read();          // the store of box k - 1 has read the other buffer
+            prepare_box(box_it + 1);
+          }
+          if (!rb::mbar_wait(&obar_free[box_it & 1], (box_it >> 1) & 1, abort_flag, p.status)) goto done;
+          if (box_n0 >= p.N) {
+            rb::mbar_arrive(&obar_full[box_it & 1]);
+            if (box_leader && !rb::mbar_wait(&obar_full[box_it & 1], (box_it >> 1) & 1, abort_flag, p.status)) goto done;
+            ++box_it;
+            continue;
+          }
+        } else if (n0 >= p.N || (!row_ok && p.colsum == nullptr)) {
+          continue;
+        }
         const bool full_chunk = (n0 + 32 <= p.N);
         float v[32];
 #pragma unroll
@@ -277,7 +312,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         } else if (p.epi == EPI_BF16_MASK || p.epi == EPI_BF16_DSILU) {
           const uint16_t* a = reinterpret_cast<const uint16_t*>(p.aux) + m * p.ld_aux + n0;
           uint16_t araw[32];
-          if (!row_ok) {
+          if (tma_aux) {
+            // the aux box sits in the output buffer (same swizzle); this thread reads the 64 bytes it will overwrite
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              reinterpret_cast<uint4*>(araw)[j] = *reinterpret_cast<const uint4*>(box_row + (((eg * 4 + j) ^ (row & 7)) << 4));
+          } else if (!row_ok) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) araw[j] = 0;
           } else if (full_chunk && ((reinterpret_cast<uintptr_t>(a) & 15) == 0)) {
@@ -325,31 +365,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         for (int j = 0; j < 16; ++j)
           pk[j] = p.is_bf16 ? rb::pack_bf16(v[2 * j], v[2 * j + 1]) : rb::pack_f16(v[2 * j], v[2 * j + 1]);
         if (tma_out) {
-          if ((ci & 1) == 0) {
-            // the previous box of this group must have been read out of shared memory by its store
-            if (box_leader) {
-              if (box_it > 0) rb::tma_store_wait_read();
-              rb::mbar_arrive(&obar_free[eg]);
-            }
-            if (!rb::mbar_wait(&obar_free[eg], box_it & 1, abort_flag, p.status)) goto done;
-          }
-          const int row = ew * 32 + lane;
-          uint8_t* dst = my_box + row * 128;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int q = ((ci & 1) * 4 + j) ^ (row & 7);                       // 128-byte swizzle: 16-byte unit ^ (row % 8)
-            *reinterpret_cast<uint4*>(dst + q * 16) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+          for (int j = 0; j < 4; ++j)                                           // 128-byte swizzle: 16-byte unit ^ (row % 8)
+            *reinterpret_cast<uint4*>(box_row + (((eg * 4 + j) ^ (row & 7)) << 4)) =
+                make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+          rb::fence_proxy_async_smem();
+          rb::mbar_arrive(&obar_full[box_it & 1]);
+          if (box_leader) {
+            if (!rb::mbar_wait(&obar_full[box_it & 1], (box_it >> 1) & 1, abort_flag, p.status)) goto done;
+            rb::tma_store_2d_hint(&tma_c, out_stage + (box_it & 1) * C::OUT_BOX_BYTES, box_n0, tm * BM, pol_out);
+            rb::tma_store_commit();
           }
-          if ((ci & 1) == 1) {
-            rb::fence_proxy_async_smem();
-            rb::mbar_arrive(&obar_full[eg]);
-            if (box_leader) {
-              if (!rb::mbar_wait(&obar_full[eg], box_it & 1, abort_flag, p.status)) goto done;
-              rb::tma_store_2d_hint(&tma_c, my_box, box_n0, tm * BM, pol_out);
-              rb::tma_store_commit();
-            }
-            ++box_it;
-          }
+          ++box_it;
           continue;
         }
         uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + m * p.ldc + n0;
@@ -385,7 +412,8 @@ int make_map_2d(CUtensorMap* map, const void* base, long long rows, long long co
 }
 
 template <int BN, bool A_MN, bool B_MN>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid, cudaStream_t st) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx, const GemmParams& p, int grid,
+           cudaStream_t st) {
   using C = Cfg<BN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -393,7 +421,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set = true;
   }
-  gemm_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, C::SMEM_BYTES, st>>>(ta, tb, tc, p);
+  gemm_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, C::SMEM_BYTES, st>>>(ta, tb, tc, tx, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -432,11 +460,18 @@ RB_API int rb_gemm16(const void* A, long long lda, int a_mn, const void* B, long
   // 16-bit outputs with a TMA-compatible layout leave through TMA stores of [128][64] boxes (full 128-byte lines
   // instead of 16-byte pieces per thread)
   const bool out16 = !(epi == EPI_F32_ATOMIC || epi == EPI_F32);
-  const int tma_out = (out16 && bn >= 128 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) ? 1 : 0;
-  CUtensorMap tc = tb;
+  const bool with_aux = (epi == EPI_BF16_MASK || epi == EPI_BF16_DSILU);
+  const int tma_out = (out16 && bn >= 128 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                       (!with_aux || (aux != nullptr && (ld_aux % 8) == 0 && (reinterpret_cast<uintptr_t>(aux) & 15) == 0)))
+                          ? 1 : 0;
+  CUtensorMap tc = tb, tx = tb;
   if (tma_out) {
     rc = make_map_2d(&tc, out, M, N, ldc, 64, BM, is_bf16);
     if (rc) return rc;
+    if (with_aux) {
+      rc = make_map_2d(&tx, aux, M, N, ld_aux, 64, BM, is_bf16);
+      if (rc) return rc;
+    }
   }
 
   GemmParams p;
@@ -451,10 +486,10 @@ RB_API int rb_gemm16(const void* A, long long lda, int a_mn, const void* B, long
   const int grid = tiles < num_sms ? tiles : num_sms;
 
 #define RB_DISPATCH(BN_)                                                                     \
-  if (a_mn && b_mn) return launch<BN_, true, true>(ta, tb, tc, p, grid, stream);                 \
-  if (a_mn && !b_mn) return launch<BN_, true, false>(ta, tb, tc, p, grid, stream);               \
-  if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, tc, p, grid, stream);               \
-  return launch<BN_, false, false>(ta, tb, tc, p, grid, stream);
+  if (a_mn && b_mn) return launch<BN_, true, true>(ta, tb, tc, tx, p, grid, stream);                 \
+  if (a_mn && !b_mn) return launch<BN_, true, false>(ta, tb, tc, tx, p, grid, stream);               \
+  if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, tc, tx, p, grid, stream);               \
+  return launch<BN_, false, false>(ta, tb, tc, tx, p, grid, stream);
   if (bn == 256) { RB_DISPATCH(256) }
   if (bn == 128) { RB_DISPATCH(128) }
   RB_DISPATCH(64)

@@ -137,6 +137,8 @@ def main() -> None:
     ap.add_argument("--a-mn", action="store_true")
     ap.add_argument("--b-mn", action="store_true")
     ap.add_argument("--splits", type=int, default=1)
+    ap.add_argument("--epi", default="relu", choices=["relu", "none", "mask"])
+    ap.add_argument("--colsum", action="store_true")
     ap.add_argument("--seqs", type=int, default=8)
     ap.add_argument("--len", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=8)
@@ -162,9 +164,16 @@ def main() -> None:
         if a.splits > 1:
             C = torch.zeros(a.m, a.n, device=dev)
             fn = lambda: gemm.gemm16(A, B, a_mn=a.a_mn, b_mn=a.b_mn, out=C, epi=gemm.EPI_F32_ATOMIC, splits=a.splits)  # noqa: E731
+        elif a.epi == "mask":                                  # input-gradient GEMM of a ReLU layer (+ fused bias gradient)
+            C = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=dev)
+            aux = torch.randn(a.m, a.n, device=dev).bfloat16()
+            cs = torch.zeros(a.n, device=dev) if a.colsum else None
+            fn = lambda: gemm.gemm16(A, B, a_mn=a.a_mn, b_mn=a.b_mn, out=C, aux=aux, epi=gemm.EPI_RELU_MASK, colsum_out=cs)  # noqa: E731
         else:
             C = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=dev)
-            fn = lambda: gemm.gemm16(A, B, a_mn=a.a_mn, b_mn=a.b_mn, out=C, bias=bias, epi=gemm.EPI_RELU)  # noqa: E731
+            cs = torch.zeros(a.n, device=dev) if a.colsum else None
+            fn = lambda: gemm.gemm16(A, B, a_mn=a.a_mn, b_mn=a.b_mn, out=C, bias=bias,  # noqa: E731
+                                     epi=gemm.EPI_RELU if a.epi == "relu" else gemm.EPI_NONE, colsum_out=cs)
         ms = _time(fn, a.iters)
         fl = 2.0 * a.m * a.n * a.k
         out.update(ms=ms, tflops=fl / ms / 1e9, frac_of_peak=fl / (ms / 1e3) / flops, shape=[a.m, a.n, a.k])
