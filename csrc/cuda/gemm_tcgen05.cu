@@ -16,6 +16,8 @@
 //
 // Covers the MLP / in_linear_silu / DCN-cross GEMMs of the framework (the reference
 // runs these through CATLASS/aclnn matmuls, e.g. cust_op/.../in_linear_silu).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -432,10 +434,31 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
 //   b_mn == 0: B is [N][K] with row stride ldb;  b_mn == 1: B is stored [K][N] with row stride ldb.
 // Row strides are in elements and must be multiples of 8; bases 16-byte aligned.
 // Returns 0, a cudaError_t, or a negative value for an argument / descriptor error.
+extern "C" int rb_gemm16_light(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn, void* out,
+                               long long ldc, int M, int N, int K, const float* bias, const void* aux, long long ld_aux, int epi,
+                               float alpha, int splits, int is_bf16, int num_sms, float* colsum, int* status,
+                               cudaStream_t stream);
+
+static int g_gemm_concurrent = -1;      // -1: not set (environment decides), 0 / 1: set by rb_gemm_set_concurrent
+
+// 1: other kernels run beside the GEMMs on side streams (multi-GPU exchange, all-reduce buckets): use the light variant
+// (gemm_tcgen05_light.cu), whose CTAs leave room on the SM; 0: a GEMM has the GPU to itself: use the full-size variant.
+RB_API int rb_gemm_set_concurrent(int on) {
+  g_gemm_concurrent = on ? 1 : 0;
+  return 0;
+}
+
 RB_API int rb_gemm16(const void* A, long long lda, int a_mn, const void* B, long long ldb, int b_mn,
                      void* out, long long ldc, int M, int N, int K, const float* bias, const void* aux,
                      long long ld_aux, int epi, float alpha, int splits, int is_bf16, int num_sms,
                      float* colsum, int* status, cudaStream_t stream) {
+  if (g_gemm_concurrent < 0) {
+    const char* e = getenv("RECSDK_B200_GEMM_CONCURRENT");
+    g_gemm_concurrent = e ? (atoi(e) != 0) : 0;
+  }
+  if (g_gemm_concurrent)
+    return rb_gemm16_light(A, lda, a_mn, B, ldb, b_mn, out, ldc, M, N, K, bias, aux, ld_aux, epi, alpha, splits, is_bf16, num_sms,
+                           colsum, status, stream);
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (colsum != nullptr && (epi == EPI_F32_ATOMIC || epi == EPI_F32)) return -5;   // column sums ride on the 16-bit epilogues
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))

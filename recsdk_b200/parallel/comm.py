@@ -94,6 +94,10 @@ class PeerGroup:
             import torch.distributed._symmetric_memory as symm_mem
 
             self._symm = symm_mem
+        if self.world > 1 and device.type == "cuda" and "RECSDK_B200_GEMM_CONCURRENT" not in os.environ:
+            # the exchange and the gradient buckets run on side streams beside the MLP GEMMs: use the GEMM variant whose CTAs
+            # leave room on the SM for their blocks
+            _lib.lib().rb_gemm_set_concurrent(1)
         pad = self.alloc(self.PAD_INTS * 4, zero=True)
         self.pads = pad
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)

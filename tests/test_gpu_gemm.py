@@ -12,6 +12,15 @@ def _rand(shape, dtype, seed):
     return (torch.randn(shape, generator=g, device="cuda") * 0.5).to(dtype)
 
 
+@pytest.fixture(params=["full", "light"], autouse=True)
+def gemm_variant(request):
+    """Every case runs on both GEMM variants: the full-size one (single GPU) and the light one that multi-GPU runs select
+    so that side-stream kernels fit beside a GEMM CTA."""
+    _lib.lib().rb_gemm_set_concurrent(1 if request.param == "light" else 0)
+    yield request.param
+    _lib.lib().rb_gemm_set_concurrent(0)
+
+
 def _check(out, ref, tol):
     err = (out.float() - ref.float()).abs().max().item()
     scale = ref.float().abs().max().item() + 1e-6
