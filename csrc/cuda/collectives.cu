@@ -369,8 +369,8 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_twoshot_kernel(const ArA
   __syncthreads();
   const int world = a.world, me = a.rank;
   const long long slice = ((a.n + world - 1) / world + AR_VEC - 1) / AR_VEC * AR_VEC;   // elements per slice
-  const long long step = static_cast<long long>(gridDim.x) * AR_CHUNK;
-  const long long first = static_cast<long long>(blockIdx.x) * AR_CHUNK + threadIdx.x * AR_VEC;
+  const long long step = static_cast<long long>(gridDim.x) * (blockDim.x * AR_VEC);
+  const long long first = static_cast<long long>(blockIdx.x) * (blockDim.x * AR_VEC) + threadIdx.x * AR_VEC;
   // loop 1: convert and push my contribution to every slice owner
   for (int k = 0; k < world; ++k) {
     const int p = (me + k) % world;
@@ -445,8 +445,8 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_oneshot_kernel(const ArA
   const int world = a.world, me = a.rank;
   const long long n_pad = (a.n + AR_VEC - 1) / AR_VEC * AR_VEC;
   const long long half = static_cast<long long>(e & 1) * world * n_pad;
-  const long long step = static_cast<long long>(gridDim.x) * AR_CHUNK;
-  const long long first = static_cast<long long>(blockIdx.x) * AR_CHUNK + threadIdx.x * AR_VEC;
+  const long long step = static_cast<long long>(gridDim.x) * (blockDim.x * AR_VEC);
+  const long long first = static_cast<long long>(blockIdx.x) * (blockDim.x * AR_VEC) + threadIdx.x * AR_VEC;
   for (long long el = first; el < n_pad; el += step) {
     float v[8];
     ld_grad8(a.grad, el, a.n, v);
@@ -518,20 +518,28 @@ RB_API int rb_allreduce_push(float* grad, long long n, const unsigned long long*
   a.epoch_word = epoch_word; a.scale = scale; a.rank = rank; a.world = world; a.status = status;
   a.limit_ns = static_cast<unsigned long long>(timeout_ms) * 1000000ull;
   const long long work = one_shot ? n : ((n + world - 1) / world);
-  long long want = (work + AR_CHUNK - 1) / AR_CHUNK;
-  const int cap = blocks > 0 ? blocks : 128;
+  // threads per block: 512, or 256 (RECSDK_B200_ALLREDUCE_THREADS; must be the same on every rank) for blocks small
+  // enough to share an SM with a GEMM CTA of the backward they overlap
+  static const int threads = [] {
+    const char* e = getenv("RECSDK_B200_ALLREDUCE_THREADS");
+    const int t = e ? atoi(e) : AR_THREADS;
+    return (t == 256 || t == 128) ? t : AR_THREADS;
+  }();
+  const long long chunk = static_cast<long long>(threads) * AR_VEC;
+  long long want = (work + chunk - 1) / chunk;
+  const int cap = blocks > 0 ? blocks : 128 * (AR_THREADS / threads);
   if (want > cap) want = cap;
   if (blocks > 0) want = blocks;             // the grid is part of the flag layout: identical on every rank
   if (want > rb_allreduce_push_max_blocks()) return -1;
   if (want < 1) want = 1;
   const int g = static_cast<int>(want);
   if (one_shot) {
-    if (wire_bf16) allreduce_oneshot_kernel<true><<<g, AR_THREADS, 0, st>>>(a);
-    else allreduce_oneshot_kernel<false><<<g, AR_THREADS, 0, st>>>(a);
+    if (wire_bf16) allreduce_oneshot_kernel<true><<<g, threads, 0, st>>>(a);
+    else allreduce_oneshot_kernel<false><<<g, threads, 0, st>>>(a);
   } else {
     if (!result) return -1;
-    if (wire_bf16) allreduce_twoshot_kernel<true><<<g, AR_THREADS, 0, st>>>(a);
-    else allreduce_twoshot_kernel<false><<<g, AR_THREADS, 0, st>>>(a);
+    if (wire_bf16) allreduce_twoshot_kernel<true><<<g, threads, 0, st>>>(a);
+    else allreduce_twoshot_kernel<false><<<g, threads, 0, st>>>(a);
   }
   return static_cast<int>(cudaGetLastError());
 }
