@@ -7,7 +7,7 @@ the flags of the reference's own ``CMakeLists.txt`` that matter for speed (``-O3
 ``baseline/_ref/libhybrid_cpp.so``, which ``python -m recsdk_b200.utils.microbench host_engines`` loads with
 ``torch.ops.load_library`` to time the reference's engines beside this package's on the same ids.
 
-    python baseline/build_ref_host.py [/path/to/reference]
+    python baseline/build_ref_host.py [/path/to/reference]        # or RECSDK_REFERENCE_ROOT=/path/to/reference
 """
 import os
 import subprocess
@@ -15,8 +15,21 @@ import sys
 import sysconfig
 
 
-def build(ref_root: str = "/root/reference", verbose: bool = True) -> str:
+def default_reference_root() -> str:
+    """The reference checkout: ``RECSDK_REFERENCE_ROOT``, else a ``reference`` directory beside this repository."""
+    env = os.environ.get("RECSDK_REFERENCE_ROOT")
+    if env:
+        return env
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return os.path.join(os.path.dirname(repo), "reference")
+
+
+def build(ref_root: str = "", verbose: bool = True) -> str:
     import torch
+
+    ref_root = ref_root or default_reference_root()
+    if not os.path.isdir(os.path.join(ref_root, "training")):
+        raise FileNotFoundError("no reference checkout at %r: set RECSDK_REFERENCE_ROOT" % ref_root)
     from torch.utils import cpp_extension as ce
 
     here = os.path.dirname(os.path.abspath(__file__))
@@ -54,4 +67,4 @@ def build(ref_root: str = "/root/reference", verbose: bool = True) -> str:
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else ""))
