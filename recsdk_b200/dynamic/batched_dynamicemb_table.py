@@ -149,6 +149,118 @@ class BatchedDynamicEmbeddingTablesV2(nn.Module):
         self._anchor = nn.Parameter(torch.zeros(1, device=self.device))
         self._anchor._in_backward_optimizers = True  # type: ignore[attr-defined]
         self._global_step = 0
+        self._enable_prefetch = False
+        self.num_prefetch_ahead = 0
+        self.prefetch_stream: Optional["torch.cuda.Stream"] = None
+        self._caching = any(t.storage is not None for t in self.tables)
+
+    # ---------------------------------------------------------------- accessors of the reference module
+    @property
+    def caches(self) -> List[KeyValueTable]:
+        """Tables that front a storage tier (their device table is the cache)."""
+        return [t for t in self.tables if t.storage is not None]
+
+    def split_embedding_weights(self) -> List[torch.Tensor]:
+        """One ``[live rows, dim]`` tensor per table (a snapshot: dynamic tables have no fixed weight matrix)."""
+        return [self.export_keys_values(n)[1] for n in self.table_names]
+
+    def reset_cache_states(self) -> None:
+        """Write the cached rows back and zero the cache metrics."""
+        self.flush()
+        for t in self.tables:
+            for k in t.metrics:
+                t.metrics[k] = 0
+
+    # ---------------------------------------------------------------- memory report
+    def memory_report(self) -> List[Dict[str, object]]:
+        """Per table: capacity, live rows, and the bytes its rows take in total / on the device / on the host, split into
+        embedding and optimizer state - what the reference prints at construction (``_print_memory_consume``,
+        ``batched_dynamicemb_table.py:272-363``)."""
+        out = []
+        for t in self.tables:
+            tab = t.table
+            cap = int(getattr(tab, "capacity", 0) or 0)
+            hbm_rows = int(getattr(tab, "hbm_rows", cap) if getattr(tab, "hbm_rows", None) is not None else cap)
+            hbm_rows = min(hbm_rows, cap)
+            host_rows = cap - hbm_rows
+            eb, sb = 4 * t.dim, 4 * t.state_dim
+
+            def split(rows: int) -> Dict[str, int]:
+                return {"total": rows * (eb + sb), "embedding": rows * eb, "optim_state": rows * sb}
+
+            out.append({"table": t.name, "dim": t.dim, "optim_state_dim": t.state_dim, "capacity": cap,
+                        "size": int(t.table.size()) if hasattr(t.table, "size") else 0,
+                        "total_bytes": split(cap), "hbm_bytes": split(hbm_rows), "host_bytes": split(host_rows),
+                        "index_bytes": cap * (8 + 8 + 1 + 4) + (cap // 128) * 4,      # keys, scores, digests, stamps, bucket locks
+                        "storage_tier": type(t.storage).__name__ if t.storage is not None else None})
+        return out
+
+    def print_memory_consume(self) -> str:
+        rows = self.memory_report()
+        unit, name = (1 << 20, "MB") if any(r["total_bytes"]["total"] >= (1 << 20) for r in rows) else (1 << 10, "KB")
+        head = "%-20s %14s %14s %14s %14s" % ("table (%s)" % name, "total", "hbm", "host", "index")
+        lines = [head] + ["%-20s %14d %14d %14d %14d" % (r["table"], r["total_bytes"]["total"] // unit, r["hbm_bytes"]["total"] // unit,
+                                                         r["host_bytes"]["total"] // unit, r["index_bytes"] // unit) for r in rows]
+        text = "\n".join(lines)
+        print(text)
+        return text
+
+    # ---------------------------------------------------------------- prefetch
+    @property
+    def enable_prefetch(self) -> bool:
+        return self._enable_prefetch
+
+    @enable_prefetch.setter
+    def enable_prefetch(self, value: bool) -> None:
+        self._enable_prefetch = bool(value)
+        self.num_prefetch_ahead = 0
+
+    def prefetch(self, indices: torch.Tensor, offsets: torch.Tensor, forward_stream=None,
+                 batch_size_per_feature_per_rank=None, feature_splits: Optional[List[int]] = None) -> None:
+        """Bring the rows of a coming batch from the storage tier into the device cache ahead of its ``forward`` (sequence
+        embeddings only, as in the reference: ``batched_dynamicemb_table.py:940-1001``).  Runs on the caller's current
+        stream, which must differ from ``forward_stream``; ``forward`` then finds its keys resident.  ``feature_splits``
+        gives the ids per feature when several tables share the module (default: all ids belong to table 0's features in
+        order of ``feature_table_map`` with equal bags)."""
+        if self.pooling_mode != DynamicEmbPoolingMode.NONE:
+            raise RuntimeError("only support prefetch for sequence embedding.")
+        if not self._enable_prefetch:
+            raise RuntimeError("Prefetch is not enabled.")
+        if indices.is_cuda and forward_stream is not None:
+            cur = torch.cuda.current_stream(indices.device)
+            if self.prefetch_stream is None:
+                self.prefetch_stream = cur
+            if cur == forward_stream:
+                raise RuntimeError("prefetch_stream and forward_stream should not be the same stream.")
+            indices.record_stream(cur)
+            offsets.record_stream(cur)
+        self.num_prefetch_ahead += 1
+        if not self._caching:
+            return                                       # nothing below the device table: prefetch has nothing to move
+        F = len(self.feature_table_map)
+        if feature_splits is None:
+            if F == 1:
+                feature_splits = [indices.numel()]
+            else:
+                B = (offsets.numel() - 1) // F
+                feature_splits = [int(offsets[(f + 1) * B] - offsets[f * B]) for f in range(F)]
+        start = 0
+        by_table: Dict[int, List[torch.Tensor]] = {}
+        for f, n in enumerate(feature_splits):
+            by_table.setdefault(self.feature_table_map[f], []).append(indices[start:start + n])
+            start += n
+        for ti, parts in by_table.items():
+            t = self.tables[ti]
+            if t.storage is None:
+                continue
+            keys = torch.unique(torch.cat(parts) if len(parts) > 1 else parts[0])
+            if self.training and t.options.score_strategy == DynamicEmbScoreStrategy.STEP:
+                # rows touched by a prefetch carry the score of the step that will use them
+                saved, t.score_value = t.score_value, self._global_step + self.num_prefetch_ahead
+                t._caching_lookup(keys.to(self.device).long())
+                t.score_value = saved
+            else:
+                t._caching_lookup(keys.to(self.device).long())
 
     # ---------------------------------------------------------------- scores
     def _update_score(self) -> None:
@@ -178,6 +290,8 @@ class BatchedDynamicEmbeddingTablesV2(nn.Module):
         EC (pooling NONE): -> [nnz, D]; EBC: -> [B, sum(D_f)]."""
         if self.training:
             self._update_score()
+        if self._enable_prefetch and self.num_prefetch_ahead > 0:
+            self.num_prefetch_ahead -= 1
         F = len(self.feature_table_map)
         starts = [0] * (F + 1)
         for f in range(F):

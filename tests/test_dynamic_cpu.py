@@ -152,3 +152,47 @@ def test_variable_interface_eval_lookup_and_matched_export():
     assert t.count_matched(20) == 2
     keys, scores, vals, _ = t.export_batch_matched(20)
     assert sorted(keys.tolist()) == [5, 9] and sorted(scores.tolist()) == [20, 30] and vals.shape == (2, 4)
+
+
+def test_batched_tables_prefetch_memory_report_and_accessors(tmp_path):
+    """Module-level surface of the batched dynamic tables: prefetch brings storage-tier rows into the cache ahead of the
+    forward (sequence mode, opt-in), the memory report splits rows into embedding / optimizer state per tier."""
+    from recsdk_b200.dynamic.batched_dynamicemb_table import BatchedDynamicEmbeddingTablesV2
+    from recsdk_b200.dynamic.dynamicemb_config import DynamicEmbPoolingMode
+
+    disk = DiskStorage("t", [str(tmp_path / "d0")], 8 + 8)                       # dim 8 + Adagrad state 8
+    o = DynamicEmbTableOptions(initializer_args=DynamicEmbInitializerArgs(mode=DynamicEmbInitializerMode.DEBUG), caching=True,
+                               external_storage=disk, max_capacity=16, init_capacity=16)
+    o.dim, o.optimizer_type = 8, OptimizerType.ADAGRAD
+    m = BatchedDynamicEmbeddingTablesV2([o], ["t"], DynamicEmbPoolingMode.NONE, device=torch.device("cpu"), learning_rate=0.5)
+    assert m.caches == m.tables and m.table_names == ["t"]
+    rep = m.memory_report()[0]
+    assert rep["capacity"] == 16 and rep["dim"] == 8 and rep["optim_state_dim"] == 8
+    assert rep["total_bytes"] == {"total": 16 * 64, "embedding": 16 * 32, "optim_state": 16 * 32}
+    assert rep["storage_tier"] is not None and "t" in m.print_memory_consume()
+    ids = torch.arange(0, 12, dtype=torch.int64)
+    off = torch.arange(0, 13, dtype=torch.int64)
+    with pytest.raises(RuntimeError, match="not enabled"):
+        m.prefetch(ids, off)
+    # fill the table and push the first keys down to the storage tier
+    for base in (0, 12, 24):
+        out = m(torch.arange(base, base + 12, dtype=torch.int64), off, [12], 12)
+        out.sum().backward()
+    assert disk.size() > 0
+    m.set_record_cache_metrics(True)
+    m.enable_prefetch = True
+    m.prefetch(ids, off)                                                         # keys 0..11 come back from the disk tier
+    assert m.num_prefetch_ahead == 1 and m.tables[0].metrics["storage_hits"] > 0
+    hits_before = m.tables[0].metrics["storage_hits"]
+    rows = m(ids, off, [12], 12)
+    assert m.num_prefetch_ahead == 0
+    assert m.tables[0].metrics["storage_hits"] == hits_before                    # the forward found everything in the cache
+    assert torch.allclose(rows[:, 0], ids.float() % 100000 - 0.5)                # DEBUG init = key, one SGD-like step of 0.5 ... Adagrad
+    pooled = BatchedDynamicEmbeddingTablesV2([o], ["t"], DynamicEmbPoolingMode.SUM, device=torch.device("cpu"))
+    pooled.enable_prefetch = True
+    with pytest.raises(RuntimeError, match="sequence"):
+        pooled.prefetch(ids, off)
+    w = m.split_embedding_weights()
+    assert len(w) == 1 and w[0].shape[1] == 8
+    m.reset_cache_states()
+    assert m.tables[0].metrics["storage_hits"] == 0
