@@ -120,3 +120,28 @@ def test_fuxi_and_disentangle():
     i, j = 4, 1
     exp = (qq[0, 0, i] @ kk[0, 0, j] + qq[0, 0, i] @ pk[i - j + S, 0]) * 0.25
     assert torch.allclose(w2[0, 0, i, j], exp, atol=1e-5)
+
+
+def test_hstu_ops_accept_the_reference_operator_range():
+    """fp32 / fp16 / bf16 inputs, D_qk != D_v, jagged and dense, with gradients (served by the fp32 statement wherever the
+    tcgen05 kernels do not apply)."""
+    import pytest
+
+    g = torch.Generator().manual_seed(0)
+    offs = torch.tensor([0, 5, 12])
+    for dt in (torch.float32, torch.float16, torch.bfloat16):
+        q = torch.randn(12, 2, 24, generator=g).to(dt).requires_grad_()
+        k = torch.randn(12, 2, 24, generator=g).to(dt).requires_grad_()
+        v = torch.randn(12, 2, 16, generator=g).to(dt).requires_grad_()
+        o = torch.ops.mxrec.hstu_jagged.equal(q, k, v, None, None, 0, 7, 0.0, offs, None, None, 0, 1.0, False)
+        assert o.shape == (12, 2, 16) and o.dtype == dt
+        o.float().sum().backward()
+        assert all(t.grad is not None and torch.isfinite(t.grad.float()).all() for t in (q, k, v))
+        od = torch.ops.mxrec.hstu_dense(q[:10].view(2, 5, 2, 24), k[:10].view(2, 5, 2, 24), v[:10].view(2, 5, 2, 16), None, None, 0, 5, 0.0)
+        assert od.shape == (2, 5, 2, 16)
+        # causal: the first token of every sequence only sees itself
+        q0 = q.detach().float()[0]
+        want0 = torch.nn.functional.silu((q0 * k.detach().float()[0]).sum(-1)) / 7.0
+        assert torch.allclose(o.detach().float()[0], want0[:, None] * v.detach().float()[0], atol=2e-2, rtol=2e-2)
+    with pytest.raises(NotImplementedError):
+        torch.ops.mxrec.hstu_dense(q[:10].view(2, 5, 2, 24), k[:10].view(2, 5, 2, 24), v[:10].view(2, 5, 2, 16), None, None, 1, 5, 0.0)
