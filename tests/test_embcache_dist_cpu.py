@@ -81,3 +81,55 @@ def test_two_ranks_match_one_and_checkpoint_reshards():
         Saver().load(m, path)
         keys = list(range(50))
         assert torch.allclose(m.host_rows("t1", keys), ref_m.host_rows("t1", keys), atol=1e-6)
+
+
+# ------------------------------------------------------------------------------------------ sequence collection, two ranks
+def _seq_tables():
+    from recsdk_b200.embcache import EmbCacheEmbeddingConfig
+
+    return [EmbCacheEmbeddingConfig(num_embeddings=1000, embedding_dim=8, name="s0", feature_names=["f0"]),
+            EmbCacheEmbeddingConfig(num_embeddings=500, embedding_dim=8, name="s1", feature_names=["f1"])]
+
+
+def _seq_run(rank, world, pg):
+    from recsdk_b200.embcache import EmbCacheEmbeddingCollection, EmbCacheShardedEmbeddingCollection
+
+    ec = EmbCacheEmbeddingCollection(_seq_tables(), world, B // world, [3, 3], device="cpu")
+    m = EmbCacheShardedEmbeddingCollection(ec, ShardingEnv(world, rank, pg), "cpu", ec.optimizer_spec(lr=0.1), cache_rows=[64, 64])
+    losses = []
+    for b in _global_batches():
+        kjt = _local(b, rank, world)
+        out = m(kjt)
+        assert out["f0"].values().shape[0] == int(kjt["f0"].lengths().sum())
+        loss = sum((jt.values() * (i + 1)).sum(dim=1).pow(2).sum() for i, jt in enumerate(out.values())) / B
+        loss.backward()
+        losses.append(loss.detach())
+    return m, torch.stack(losses)
+
+
+def _seq_worker(rank, world, init_file, unique, ret):
+    if unique:
+        os.environ["DO_EC_LOCAL_UNIQUE"] = "1"
+    else:
+        os.environ.pop("DO_EC_LOCAL_UNIQUE", None)
+    dist.init_process_group("gloo", init_method="file://" + init_file, rank=rank, world_size=world)
+    try:
+        m, losses = _seq_run(rank, world, dist.group.WORLD)
+        assert m.do_local_unique == unique
+        dist.all_reduce(losses)
+        if rank == 0:
+            ret["losses"] = losses.tolist()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_collection_two_ranks_with_and_without_local_unique():
+    """Rows come back to the rank and position that asked for them; de-duplicating each feature's ids before the exchange
+    (DO_EC_LOCAL_UNIQUE) changes the traffic, not the result."""
+    os.environ.pop("DO_EC_LOCAL_UNIQUE", None)
+    _, ref = _seq_run(0, 1, None)
+    for unique in (False, True):
+        with tempfile.TemporaryDirectory() as d:
+            ret = mp.Manager().dict()
+            mp.spawn(_seq_worker, args=(2, os.path.join(d, "init"), unique, ret), nprocs=2, join=True)
+            assert np.allclose(ret["losses"], ref.tolist(), rtol=1e-5, atol=1e-6), (unique, ret["losses"], ref.tolist())
