@@ -120,7 +120,12 @@ class DistributedModelParallel(nn.Module):
                 if fspec.accumulate_step > 1:
                     raise NotImplementedError("gradient accumulation over several steps runs on the collective backend "
                                               "(backend=\"collective\")")
-                sharded = ShardedEmbeddingBagCollection(
+                from .grouped_embeddingbag import GroupedShardedEmbeddingBagCollection, needs_grouping
+
+                # tables of one collection that differ in storage dtype or pooling: one fused collection per group
+                cls = GroupedShardedEmbeddingBagCollection if needs_grouping(child.embedding_bag_configs()) \
+                    else ShardedEmbeddingBagCollection
+                sharded = cls(
                     child.embedding_bag_configs(), entries, self.env, self.device,
                     fspec, peer=self.peer, out_dtype=out_dtype,
                     max_local_batch=max_local_batch, one_hot=one_hot, init_weights=True)

@@ -140,3 +140,45 @@ def test_bce_head_and_colsum_and_adam():
     dense_ops.adam_flat(pc, g.cpu(), mc, vc, None, 1e-2, 0.9, 0.999, 1e-8, 0.0, 1)
     assert torch.allclose(p.cpu(), pc, atol=1e-6, rtol=1e-5)
     assert torch.allclose(sh.float().cpu(), pc, atol=1e-2, rtol=1e-2)
+
+
+def test_grouped_collection_mixed_dtype_and_pooling():
+    """Tables of one collection that differ in storage dtype and pooling: one fused collection per group behind one module;
+    pooled columns come back in the order of the original features; every group trains."""
+    from recsdk_b200.parallel.grouped_embeddingbag import GroupedShardedEmbeddingBagCollection, needs_grouping
+
+    torch.manual_seed(1)
+    spec = [(50, 16, DataType.FP32, PoolingType.SUM), (300, 32, DataType.FP16, PoolingType.SUM),
+            (70, 16, DataType.FP32, PoolingType.MEAN), (90, 8, DataType.FP32, PoolingType.SUM)]       # group of t0 is not contiguous
+    cfgs = [EmbeddingBagConfig(num_embeddings=r, embedding_dim=d, name="t%d" % i, feature_names=["f%d" % i], data_type=dt,
+                               pooling=p) for i, (r, d, dt, p) in enumerate(spec)]
+    assert needs_grouping(cfgs) and not needs_grouping(cfgs[:1])
+    opt = E.OptimizerSpec(kind=E.OPT_SGD, lr=0.5)
+    m = GroupedShardedEmbeddingBagCollection(cfgs, {}, ShardingEnv(1, 0), torch.device(DEV), opt, out_dtype=torch.float32)
+    assert len(m.groups) == 3
+    B = 21
+    lens = torch.randint(0, 4, (4 * B,))
+    vals = torch.cat([torch.randint(0, spec[t][0], (int(lens[t * B:(t + 1) * B].sum()),)) for t in range(4)])
+    kjt = KeyedJaggedTensor(["f0", "f1", "f2", "f3"], vals.to(DEV), lengths=lens.to(DEV), stride=B)
+    w0 = [m.table_weight("t%d" % i).detach().float().cpu().clone() for i in range(4)]
+    kt = m(kjt)
+    assert kt.keys() == ["f0", "f1", "f2", "f3"] and kt.length_per_key() == [16, 32, 16, 8]
+    out = kt.values()
+    off = torch.cat([torch.zeros(1, dtype=torch.int64), lens.cumsum(0)])
+    col = 0
+    for t, (r, d, dt, p) in enumerate(spec):
+        lt = lens[t * B:(t + 1) * B]
+        o = torch.cat([torch.zeros(1, dtype=torch.int64), lt.cumsum(0)])
+        ref = E.reference_pooled_forward([w0[t]], vals[off[t * B]:off[(t + 1) * B]], o, B,
+                                         E.POOL_MEAN if p == PoolingType.MEAN else E.POOL_SUM)
+        tol = 2e-3 if dt == DataType.FP16 else 1e-5
+        assert torch.allclose(out[:, col:col + d].cpu(), ref, atol=tol, rtol=tol), "feature %d" % t
+        col += d
+    out.sum().backward()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    for t in range(4):
+        touched = torch.zeros(spec[t][0], dtype=torch.bool)
+        touched[vals[off[t * B]:off[(t + 1) * B]]] = True
+        got = m.table_weight("t%d" % t).detach().float().cpu()
+        assert not torch.allclose(got[touched], w0[t][touched]) and torch.equal(got[~touched], w0[t][~touched])
