@@ -24,10 +24,10 @@ from recsdk_b200.sparse.jagged_tensor import KeyedJaggedTensor  # noqa: E402
 
 
 class Model(torch.nn.Module):
-    def __init__(self, tables):
+    def __init__(self, tables, device):
         super().__init__()
         self.ebc = EmbeddingBagCollection(tables, device=torch.device("meta"))       # rows live in the hash tables only
-        self.top = torch.nn.Linear(sum(t.embedding_dim for t in tables), 1)
+        self.top = torch.nn.Linear(sum(t.embedding_dim for t in tables), 1).to(device)
 
     def forward(self, kjt):
         return self.top(self.ebc(kjt).values().float()).pow(2).mean()
@@ -37,7 +37,7 @@ def build(tables, device):
     cons = {t.name: DynamicEmbParameterConstraints(use_dynamicemb=True, dynamicemb_options=DynamicEmbTableOptions())
             for t in tables}
     planner = DynamicEmbeddingShardingPlanner(tables, cons, Topology(world_size=1, compute_device=device.type))
-    model = Model(tables)
+    model = Model(tables, device)
     sharders = [DynamicEmbeddingCollectionSharder(), DynamicEmbeddingBagCollectionSharder({"learning_rate": 0.1})]
     return DistributedModelParallel(model, device=device, plan=planner.plan(model, sharders), sharders=sharders, backend="collective")
 
