@@ -601,6 +601,22 @@ _def("disentangle_attention(Tensor query_layer, Tensor key_layer, Tensor value_l
      "Tensor relative_pos, Tensor attn_mask, str pos_attr_type, float score_scale) -> (Tensor, Tensor, Tensor)", disentangle_attention)
 
 
+# ------------------------------------------------------------------------------------------------ row IO by address, sparse optimizers
+from . import by_address as _by_address  # noqa: E402
+
+_def("embedding_lookup_by_address(Tensor address, int embedding_dim, Tensor region) -> Tensor",
+     lambda address, embedding_dim, region: _by_address.embedding_lookup_by_address(address, embedding_dim, region))
+_def("embedding_update_by_address(Tensor address, Tensor embedding, int update_type, Tensor(a!) region) -> ()",
+     lambda address, embedding, update_type, region: _by_address.embedding_update_by_address(address, embedding, update_type, region))
+_def("lazy_adam(Tensor gradient, Tensor indices, Tensor(a!) input_m, Tensor(b!) input_v, Tensor(c!) input_var, float lr, "
+     "float beta1=0.9, float beta2=0.999, float epsilon=1e-08) -> ()",
+     lambda gradient, indices, input_m, input_v, input_var, lr, beta1=0.9, beta2=0.999, epsilon=1e-8:
+     (_by_address.lazy_adam(gradient, indices, input_m, input_v, input_var, lr, beta1, beta2, epsilon), None)[1])
+_def("sgd(Tensor gradient, Tensor indices, Tensor(a!) input_var, float lr, float weightDecay=0.0) -> ()",
+     lambda gradient, indices, input_var, lr, weightDecay=0.0:
+     (_by_address.sgd(gradient, indices, input_var, lr, weightDecay), None)[1])
+
+
 # ------------------------------------------------------------------------------------------------ TBE training lookups
 def _def_autograd(name: str, schema_args: str, ret: str, fn) -> None:
     """Ops whose implementation builds its own autograd node: the same function serves the Autograd key and the backends."""
