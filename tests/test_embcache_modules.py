@@ -251,3 +251,38 @@ def test_full_restore_drops_keys_that_are_not_in_the_checkpoint(tmp_path):
     assert all(m.manager.host_size(t) > s for t, s in enumerate(sizes))
     saver.load(m, out)
     assert [m.manager.host_size(t) for t in range(2)] == sizes
+
+
+def test_cache_sizing_follows_the_device_budget(monkeypatch):
+    """Rows in the device cache: never below what two in-flight batches can touch, scaled up by the budget
+    (``EMBCACHE_SIZE_ON_DEVICE_MEM``), never beyond the table; the declaration validates its tables."""
+    from recsdk_b200.embcache.embedding_bag import MAX_CACHE_BYTES, _cache_budget_bytes, calculate_caches
+
+    big = EmbCacheEmbeddingBagConfig(name="big", embedding_dim=16, num_embeddings=10_000_000, feature_names=["a"])
+    small = EmbCacheEmbeddingBagConfig(name="small", embedding_dim=16, num_embeddings=100, feature_names=["b"])
+    floor = [3 * 2 * 64 * 2, 1 * 2 * 64 * 2]                                 # hot * 2 * batch * world
+    monkeypatch.setenv("EMBCACHE_SIZE_ON_DEVICE_MEM", "1")                    # a budget below the floor: the floor holds
+    assert calculate_caches([big, small], 2, 64, [3, 1], 1) == [floor[0], 101]
+    min_bytes = sum(r * 16 * 4 * 2 for r in floor)
+    monkeypatch.setenv("EMBCACHE_SIZE_ON_DEVICE_MEM", str(4 * min_bytes))     # four times the floor: every table x 4
+    assert calculate_caches([big, small], 2, 64, [3, 1], 1) == [4 * floor[0], 101]
+    assert calculate_caches([big], 2, 64, [0], 0)[0] >= 2 * 64 * 2            # a zero hot size counts as one id per bag
+    monkeypatch.setenv("EMBCACHE_SIZE_ON_DEVICE_MEM", "not a number")
+    assert _cache_budget_bytes() == 16 << 30
+    monkeypatch.setenv("EMBCACHE_SIZE_ON_DEVICE_MEM", str(1 << 40))
+    assert _cache_budget_bytes() == MAX_CACHE_BYTES
+    monkeypatch.delenv("EMBCACHE_SIZE_ON_DEVICE_MEM")
+    decl = EmbCacheEmbeddingBagCollection([big, small], world_size=2, batch_size=64, multi_hot_sizes=[3, 1])
+    assert decl.embedding_bag_configs() == [big, small] and decl.is_weighted() is False
+    assert decl.cache_rows(1)[1] == 101 and decl.cache_rows(1)[0] <= 10_000_001
+    assert decl.optimizer_spec(lr=0.1).lr == 0.1
+    for bad in (dict(is_weighted=True), dict(multi_hot_sizes=[1]), dict(embedding_optimizer_cls=torch.optim.RMSprop)):
+        kw = dict(world_size=1, batch_size=8, multi_hot_sizes=[1, 1])
+        kw.update(bad)
+        with pytest.raises(ValueError):
+            EmbCacheEmbeddingBagCollection([big, small], **kw).optimizer_spec()
+    with pytest.raises(ValueError, match="duplicate"):
+        EmbCacheEmbeddingBagCollection([big, big], world_size=1, batch_size=8, multi_hot_sizes=[1, 1])
+    odd = EmbCacheEmbeddingBagConfig(name="odd", embedding_dim=12, num_embeddings=10, feature_names=["c"])
+    with pytest.raises(ValueError, match="multiple of 8"):
+        EmbCacheEmbeddingBagCollection([odd], world_size=1, batch_size=8, multi_hot_sizes=[1])
