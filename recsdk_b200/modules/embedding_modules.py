@@ -18,6 +18,20 @@ from ..sparse.jagged_tensor import JaggedTensor, KeyedJaggedTensor, KeyedTensor
 from .embedding_configs import EmbeddingBagConfig, EmbeddingConfig, PoolingType, data_type_to_dtype
 
 
+class TableDict(nn.ModuleDict):
+    """``nn.ModuleDict`` for per-table holders that accepts every table name.  The stock container refuses keys that are
+    also names of its own methods (``items``, ``keys``, ``values``, ``pop`` ...), and ``items`` is what recommendation
+    models call their largest table.  Entries are reached by subscript (``d["items"]``), the ``state_dict`` prefix is the
+    table name as usual; attribute access keeps meaning the container's method."""
+
+    def __setitem__(self, key: str, module: nn.Module) -> None:
+        if not isinstance(key, str) or not key or "." in key:
+            raise KeyError("table name must be a non-empty string without '.', got %r" % (key,))
+        if not isinstance(module, nn.Module):
+            raise TypeError("%s is not a Module" % type(module).__name__)
+        self._modules[key] = module
+
+
 def _init_table(w: torch.Tensor, cfg) -> None:
     if w.device.type == "meta":
         return
@@ -35,7 +49,7 @@ class EmbeddingBagCollection(nn.Module):
         self._configs = list(tables)
         self._is_weighted = is_weighted
         self._device = torch.device(device) if device is not None else torch.device("cpu")
-        self.embedding_bags = nn.ModuleDict()
+        self.embedding_bags = TableDict()
         names = set()
         self._feature_names: List[str] = []
         self._feature_table: List[str] = []
@@ -95,7 +109,7 @@ class EmbeddingCollection(nn.Module):
         self._configs = list(tables)
         self._device = torch.device(device) if device is not None else torch.device("cpu")
         self._need_indices = need_indices
-        self.embeddings = nn.ModuleDict()
+        self.embeddings = TableDict()
         self._feature_names: List[str] = []
         self._feature_table: List[str] = []
         dims = {c.embedding_dim for c in self._configs}

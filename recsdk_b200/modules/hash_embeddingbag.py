@@ -20,7 +20,7 @@ from torch import nn
 from ..host import host
 from ..sparse.jagged_tensor import KeyedJaggedTensor, KeyedTensor
 from .embedding_configs import EmbeddingBagConfig, PoolingType, validate_hash_table_config
-from .embedding_modules import EmbeddingBagCollection, _init_table
+from .embedding_modules import EmbeddingBagCollection, TableDict, _init_table
 
 
 class EvictStrategy(enum.Enum):
@@ -80,7 +80,7 @@ class HashEmbeddingBagCollection(EmbeddingBagCollection):
         self._configs = list(tables)
         self._is_weighted = False
         self._device = torch.device(device) if device is not None else torch.device("cpu")
-        self.embedding_bags = nn.ModuleDict()
+        self.embedding_bags = TableDict()
         self._feature_names, self._feature_table = [], []
         seen = set()
         for cfg in self._configs:

@@ -29,6 +29,7 @@ from torch import nn
 
 from ..host import host
 from ..modules.embedding_configs import EmbeddingBagConfig, PoolingType, data_type_to_dtype
+from ..modules.embedding_modules import TableDict
 from ..ops import embedding_ops as E
 from ..optim import FusedOptimizerStub
 from ..sparse.jagged_tensor import KeyedJaggedTensor, KeyedTensor
@@ -176,7 +177,7 @@ class CollectiveShardedEmbeddingBagCollection(nn.Module):
             self.owners.append((ps.ranks[0] if ps.ranks else 0) if k == E.SH_TABLE_WISE else 0)
         self.layout = E.TbeLayout([t.embedding_dim for t in tables], [t.num_embeddings for t in tables], self.kinds,
                                   self.owners, self.world, self.rank, self.feature_table)
-        self.embedding_bags = nn.ModuleDict()
+        self.embedding_bags = TableDict()
         self.state: List[Dict[str, torch.Tensor]] = []
         for ti, t in enumerate(tables):
             rows = int(self.layout.local_rows[self.rank, ti])

@@ -29,6 +29,7 @@ import torch
 from torch import nn
 
 from ..modules.embedding_configs import EmbeddingBagConfig, PoolingType, data_type_to_dtype
+from ..modules.embedding_modules import TableDict
 from ..ops import _lib
 from ..ops import embedding_ops as E
 from ..optim import FusedOptimizerStub
@@ -162,7 +163,7 @@ class ShardedEmbeddingBagCollection(nn.Module):
             self.s_offsets = self.dev["w_offsets"]
         self._step = 0
         # per-table parameter views (state_dict / user access); updates are fused in backward
-        self.embedding_bags = nn.ModuleDict()
+        self.embedding_bags = TableDict()
         for ti, t in enumerate(tables):
             off, rows = L.table_slice(self.rank, ti)
             holder = nn.Module()

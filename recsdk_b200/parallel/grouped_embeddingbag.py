@@ -15,6 +15,7 @@ import torch
 from torch import nn
 
 from ..modules.embedding_configs import EmbeddingBagConfig
+from ..modules.embedding_modules import TableDict
 from ..ops import embedding_ops as E
 from ..sparse.jagged_tensor import KeyedJaggedTensor, KeyedTensor
 from .comm import PeerGroup, ShardingEnv
@@ -68,7 +69,7 @@ class GroupedShardedEmbeddingBagCollection(nn.Module):
             idx.extend(range(start_of[i], start_of[i] + self.feature_dims[i]))
         self._identity = idx == list(range(col))
         self.register_buffer("_col_index", torch.tensor(idx, dtype=torch.int64, device=device), persistent=False)
-        self.embedding_bags = nn.ModuleDict()
+        self.embedding_bags = TableDict()
         for g in self.groups:
             for name, holder in g.embedding_bags.items():
                 self.embedding_bags[name] = holder
