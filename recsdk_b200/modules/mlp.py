@@ -45,7 +45,7 @@ class MLP(nn.Module):
 
 class _FusedMLPFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x: torch.Tensor, mlp: "FusedMLP", grad_premasked: bool, _flat: torch.Tensor):
+    def forward(ctx, x: torch.Tensor, mlp: "FusedMLP", grad_premasked: bool, _flat: torch.Tensor, grad_mode: bool = True):
         acts = [x]
         L = mlp.num_layers
         for l in range(L):
@@ -53,7 +53,11 @@ class _FusedMLPFn(torch.autograd.Function):
             y = gemm.gemm16(acts[-1], mlp.w16[l], bias=mlp.b32[l], epi=gemm.EPI_RELU if relu else gemm.EPI_NONE)
             acts.append(y)
         ctx.mlp = mlp
-        if any(ctx.needs_input_grad):          # a backward will follow this forward
+        # A backward will follow this forward.  ``needs_input_grad`` stays true for the parameters under ``torch.no_grad()``
+        # (and grad mode always reads "off" inside a Function), so the caller passes the grad mode it ran under: an
+        # evaluation pass must not leave the counter raised, or the gradient-ready hook would never fire again.
+        ctx.counted = bool(grad_mode) and any(ctx.needs_input_grad)
+        if ctx.counted:
             mlp._pending_backward += 1
         ctx.grad_premasked = grad_premasked
         ctx.x_needs_grad = x.requires_grad
@@ -90,11 +94,12 @@ class _FusedMLPFn(torch.autograd.Function):
                     dz = gemm.gemm16(dz, mlp.w16[l], b_mn=True, colsum_out=cs)
             elif ctx.x_needs_grad:
                 dx = gemm.gemm16(dz, mlp.w16[l], b_mn=True)
-        mlp._pending_backward -= 1
+        if ctx.counted:
+            mlp._pending_backward -= 1
         if mlp._grad_ready_hook is not None and mlp._pending_backward <= 0:
             mlp._pending_backward = 0
             mlp._grad_ready_hook(mlp)          # every weight gradient of this module is enqueued: its all-reduce may start
-        return dx, None, None, None
+        return dx, None, None, None, None
 
 
 class FusedMLP(nn.Module):
@@ -218,4 +223,4 @@ class FusedMLP(nn.Module):
         """``x`` is ``[B, in_padded]`` in the compute dtype.  ``grad_premasked`` promises that the
         incoming gradient of a ReLU-terminated MLP is already multiplied by the ReLU mask."""
         assert x.shape[1] == self.in_padded, "expected %d (padded) input columns" % self.in_padded
-        return _FusedMLPFn.apply(x, self, grad_premasked, self.flat_param)
+        return _FusedMLPFn.apply(x, self, grad_premasked, self.flat_param, torch.is_grad_enabled())
