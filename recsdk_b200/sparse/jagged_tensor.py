@@ -161,9 +161,11 @@ class KeyedJaggedTensor:
         for k in kjts:
             keys += k.keys()
         ws = [k.weights_or_none() for k in kjts]
-        return KeyedJaggedTensor(keys, torch.cat([k.values() for k in kjts]),
-                                 torch.cat(ws) if all(w is not None for w in ws) else None,
-                                 lengths=torch.cat([k.lengths() for k in kjts]), stride=kjts[0].stride())
+        out = KeyedJaggedTensor(keys, torch.cat([k.values() for k in kjts]),
+                                torch.cat(ws) if all(w is not None for w in ws) else None,
+                                lengths=torch.cat([k.lengths() for k in kjts]), stride=kjts[0].stride())
+        out.one_hot = all(k.one_hot for k in kjts)
+        return out
 
     # -- accessors ------------------------------------------------------------
     def keys(self) -> List[str]:
@@ -230,10 +232,10 @@ class KeyedJaggedTensor:
             end = start + seg
             keys = self._keys[start:end]
             v0, v1 = opk[start], opk[end]
-            out.append(KeyedJaggedTensor(
+            out.append(self._carry(KeyedJaggedTensor(
                 keys, self._values[v0:v1], None if self._weights is None else self._weights[v0:v1],
                 lengths=self.lengths()[start * B:end * B], stride=B,
-                length_per_key=self.length_per_key()[start:end]))
+                length_per_key=self.length_per_key()[start:end])))
             start = end
         return out
 
@@ -244,9 +246,10 @@ class KeyedJaggedTensor:
         vals = [self._values[opk[i]:opk[i + 1]] for i in indices]
         ws = None if self._weights is None else [self._weights[opk[i]:opk[i + 1]] for i in indices]
         idx = indices_tensor if indices_tensor is not None else torch.tensor(indices, dtype=torch.int64, device=lens.device)
-        return KeyedJaggedTensor(
-            keys, torch.cat(vals) if vals else self._values[:0], None if ws is None else torch.cat(ws),
-            lengths=lens[idx].reshape(-1), stride=B, length_per_key=[self.length_per_key()[i] for i in indices])
+        return self._carry(KeyedJaggedTensor(
+            keys, torch.cat(vals) if vals else self._values[:0],
+            None if ws is None else (torch.cat(ws) if ws else self._weights[:0]),
+            lengths=lens[idx].reshape(-1), stride=B, length_per_key=[self.length_per_key()[i] for i in indices]))
 
     def __getitem__(self, key: str) -> JaggedTensor:
         i = self._key_indices()[key]
