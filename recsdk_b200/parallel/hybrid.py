@@ -66,7 +66,9 @@ class HybridHashEmbeddingBagCollectionSharder(HybridEmbeddingBagCollectionSharde
 
 
 def get_default_hybrid_sharders(host_env: ShardingEnv) -> List[Any]:
-    return [HybridHashEmbeddingBagCollectionSharder(host_env), HybridEmbeddingBagCollectionSharder(host_env)]
+    """The two sharders in the reference's order (``hybrid_torchrec/distributed/sharding_plan.py:18-28``); ``handles`` tells
+    the plain and the hash-mapped collection apart, so the order carries no meaning."""
+    return [HybridEmbeddingBagCollectionSharder(host_env), HybridHashEmbeddingBagCollectionSharder(host_env)]
 
 
 class HybridStage(enum.IntEnum):
