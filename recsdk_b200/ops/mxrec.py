@@ -516,6 +516,37 @@ def _fuxi_ref(q, k, v, timestampBias, positionBias, mask, maskType: int, scale: 
     return torch.stack([one(q[b], k[b], v[b], b) for b in range(q.shape[0])])
 
 
+def hstu_dense_backward_fuxi(grad, q, k, v, mask=None, biasPosition=None, biasTimestamp=None, layout: str = "jagged", maskType: int = 0,
+                             maxSeqLen: int = 0, siluScale: float = 0.0, seqOffset: Optional[List[int]] = None):
+    """Backward of ``hstu_fuxi`` in the jagged layout (``hstu_dense_backward_fuxi/HstuDenseNpuFusionFuxi.cpp:161-164`` of the
+    reference): ``grad`` is ``[sum_len, N, D]`` or, with biases, ``[sum_len, N, 3D]`` (SiLU part, timestamp part, position part).
+    -> ``(dq, dk, dv, d_biasPosition, d_biasTimestamp)``; the bias gradients are summed over the heads (and over the batch for a
+    position bias shared by the batch), empty tensors when no bias was given.  fp32 autograd over the statement of the forward."""
+    if layout != "jagged":
+        raise ValueError("hstu_dense_backward_fuxi supports the jagged layout only")
+    if seqOffset is None:
+        raise ValueError("the jagged layout needs seqOffset")
+    if maskType == 1:
+        raise NotImplementedError("upper-triangular masks are not supported")
+    if maskType == 3 and mask is None:
+        raise ValueError("maskType 3 (custom) needs a mask")
+    scale = siluScale if siluScale != 0.0 else 1.0 / max(maxSeqLen, 1)
+    with torch.enable_grad():
+        leaves = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+        tb = biasTimestamp.detach().float().requires_grad_(True) if biasTimestamp is not None else None
+        pb = biasPosition.detach().float().requires_grad_(True) if biasPosition is not None else None
+        out = _fuxi_ref(leaves[0], leaves[1], leaves[2], tb, pb, mask, maskType, scale, "jagged", [int(x) for x in seqOffset])
+        if out.shape != grad.shape:
+            raise ValueError("grad has shape %s, the forward output %s" % (tuple(grad.shape), tuple(out.shape)))
+        wanted = leaves + [t for t in (pb, tb) if t is not None]
+        gs = list(torch.autograd.grad(out, wanted, grad.float()))
+    dq, dk, dv = (g.to(q.dtype) for g in gs[:3])
+    rest = gs[3:]
+    dp = rest.pop(0).to(biasPosition.dtype) if pb is not None else q.new_zeros(0)
+    dt = rest.pop(0).to(biasTimestamp.dtype) if tb is not None else q.new_zeros(0)
+    return dq, dk, dv, dp, dt
+
+
 class _DisentangleFn(torch.autograd.Function):
     """CUDA forward: the four products are plain (library) GEMMs in the input dtype, everything between them - both
     relative-position gathers, scale, mask, softmax, the two matrix outputs - is one pass of ``rb_disentangle_softmax``.
@@ -597,6 +628,9 @@ def _disentangle_ref(query_layer, key_layer, value_layer, pos_key_layer, pos_que
 
 _def("hstu_fuxi(Tensor q, Tensor k, Tensor v, Tensor? timestampBias=None, Tensor? positionBias=None, Tensor? mask=None, int maskType=0, "
      "int maxSeqLen=0, float siluScale=0.0, str layout=\"normal\", int[]? seqOffset=None) -> Tensor", hstu_fuxi)
+_def("hstu_dense_backward_fuxi(Tensor grad, Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? biasPosition=None, "
+     "Tensor? biasTimestamp=None, str layout=\"jagged\", int maskType=0, int maxSeqLen=0, float siluScale=0.0, int[]? seqOffset=None) "
+     "-> (Tensor, Tensor, Tensor, Tensor, Tensor)", hstu_dense_backward_fuxi)
 _def("disentangle_attention(Tensor query_layer, Tensor key_layer, Tensor value_layer, Tensor pos_key_layer, Tensor pos_query_layer, "
      "Tensor relative_pos, Tensor attn_mask, str pos_attr_type, float score_scale) -> (Tensor, Tensor, Tensor)", disentangle_attention)
 

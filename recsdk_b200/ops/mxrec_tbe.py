@@ -373,7 +373,7 @@ def make_lookup(kind: int, schema_args: str):
 
 _RAW_HEAD = ("Tensor grad_output, Tensor(a!) dev_weights, Tensor(b!) uvm_weights, Tensor lxu_cache_weights, Tensor weights_placements, "
              "Tensor weights_offsets, Tensor D_offsets, SymInt max_D, Tensor hash_size_cumsum, int total_hash_size_bits, Tensor indices, "
-             "Tensor offsets, int pooling_mode, Tensor lxu_cache_locations, int unused_, int max_segment_length_per_warp, "
+             "Tensor offsets, {multi}int pooling_mode, Tensor lxu_cache_locations, int unused_, int max_segment_length_per_warp, "
              "bool stochastic_rounding, int info_B_num_bits, int info_B_mask_int64, bool use_uniq_cache_locations, "
              "bool use_homogeneous_placements, ")
 _RAW_UNIQ = ("Tensor[] grad_accumulate, Tensor grad_accumulate_offsets, Tensor? hash_indices=None, Tensor? unique_ids=None, "
@@ -382,17 +382,24 @@ _RAW_UNIQ = ("Tensor[] grad_accumulate, Tensor grad_accumulate_offsets, Tensor? 
 
 
 def raw_backward_schemas() -> Dict[str, Tuple[int, str]]:
-    return {
-        "split_embedding_backward_codegen_adagrad_unweighted_exact_cuda": (
-            _ADAGRAD, _RAW_HEAD + _M1 + _RAW_UNIQ + "float eps=0, float learning_rate=0, bool use_optimize=True"),
-        "split_embedding_backward_codegen_rowwise_adagrad_unweighted_exact_cuda": (
-            _ROWWISE, _RAW_HEAD + _M1 + _RAW_UNIQ + "float eps=0, float learning_rate=0, bool use_optimize=True"),
-        "split_embedding_backward_codegen_adam_unweighted_exact_cuda": (
-            _ADAM, _RAW_HEAD + _M1 + _M2 + _RAW_UNIQ + "float eps=0, float learning_rate=0, float beta1=0, float beta2=0, int iter=0, "
-            "bool use_optimize=True"),
-        "split_embedding_backward_codegen_sgd_unweighted_exact_cuda": (
-            _SGD, _RAW_HEAD + _RAW_UNIQ + "float learning_rate=0, bool use_optimize=True"),
-    }
+    """name -> (optimizer kind, schema).  The ``*_grad_aggregation`` forms carry the id lists of the accumulated steps and
+    their unique results (``backward_codegen_{adagrad,adam,sgd}_unweighted_exact_grad_aggregation.cpp`` of the reference); the
+    rows of earlier steps are found through their non-zero sums in ``grad_accumulate``, so those lists are accepted and unused."""
+    out: Dict[str, Tuple[int, str]] = {}
+    for agg in (False, True):
+        sfx = "_grad_aggregation" if agg else ""
+        head = _RAW_HEAD.format(multi="Tensor indices_multi_step, Tensor offsets_multi_step, " if agg else "")
+        uniq = _RAW_UNIQ + (_UNIQ_MULTI if agg else "")
+        out["split_embedding_backward_codegen_adagrad_unweighted_exact_cuda" + sfx] = (
+            _ADAGRAD, head + _M1 + uniq + "float eps=0, float learning_rate=0, bool use_optimize=True")
+        out["split_embedding_backward_codegen_adam_unweighted_exact_cuda" + sfx] = (
+            _ADAM, head + _M1 + _M2 + uniq + "float eps=0, float learning_rate=0, float beta1=0, float beta2=0, int iter=0, "
+            "bool use_optimize=True")
+        out["split_embedding_backward_codegen_sgd_unweighted_exact_cuda" + sfx] = (
+            _SGD, head + uniq + "float learning_rate=0, bool use_optimize=True")
+    out["split_embedding_backward_codegen_rowwise_adagrad_unweighted_exact_cuda"] = (
+        _ROWWISE, _RAW_HEAD.format(multi="") + _M1 + _RAW_UNIQ + "float eps=0, float learning_rate=0, bool use_optimize=True")
+    return out
 
 
 def make_raw_backward(kind: int, schema_args: str):

@@ -120,13 +120,16 @@ HOST_BACKEND_METHODS = ["register_npu_cache_tables", "build_index_meta", "lookup
                         "offload_kvcache_launch", "offload_kvcache_wait", "finish_task", "cancel_task", "evict", "evict_all"]
 
 MXREC_OPS = ["hstu_dense", "hstu_dense_backward", "hstu_jagged", "hstu_jagged_backward", "hstu_paged", "hstu_forward_v2", "hstu_backward_v2",
-             "hstu_fuxi", "in_linear_silu", "distance_in_linear_silu", "in_linear_silu_backward", "relative_attn_bias_pos",
+             "hstu_fuxi", "hstu_dense_backward_fuxi", "in_linear_silu", "distance_in_linear_silu", "in_linear_silu_backward", "relative_attn_bias_pos",
              "relative_attn_bias_time", "relative_attn_bias_time_with_index", "relative_attn_bias_time_backward", "ln_mul",
              "norm_multiply_dropout", "token_mixing", "concat_2d_jagged", "split_2d_jagged", "multislice_concat", "gather_for_rank1",
              "index_select_for_rank1_backward", "reverse_sequence", "disentangle_attention",
              "split_embedding_codegen_forward_unweighted_cuda", "split_embedding_codegen_lookup_adagrad_function",
              "split_embedding_codegen_lookup_adam_function", "split_embedding_codegen_lookup_sgd_function",
              "split_embedding_codegen_lookup_rowwise_adagrad_function"]
+MXREC_OPS += ["split_embedding_codegen_lookup_%s_function_grad_aggregation" % k for k in ("adagrad", "adam", "sgd")]
+MXREC_OPS += ["split_embedding_backward_codegen_%s_unweighted_exact_cuda" % k for k in ("adagrad", "adam", "sgd", "rowwise_adagrad")]
+MXREC_OPS += ["split_embedding_backward_codegen_%s_unweighted_exact_cuda_grad_aggregation" % k for k in ("adagrad", "adam", "sgd")]
 
 
 def _resolve(path):

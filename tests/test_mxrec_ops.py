@@ -145,3 +145,36 @@ def test_hstu_ops_accept_the_reference_operator_range():
         assert torch.allclose(o.detach().float()[0], want0[:, None] * v.detach().float()[0], atol=2e-2, rtol=2e-2)
     with pytest.raises(NotImplementedError):
         torch.ops.mxrec.hstu_dense(q[:10].view(2, 5, 2, 24), k[:10].view(2, 5, 2, 24), v[:10].view(2, 5, 2, 16), None, None, 1, 5, 0.0)
+
+
+def test_fuxi_backward_operator_matches_autograd():
+    """``hstu_dense_backward_fuxi`` (jagged layout): gradients of q, k, v and of both biases equal autograd through
+    ``hstu_fuxi``; the position bias shared by the batch gets one summed gradient; without biases the last two are empty."""
+    torch.manual_seed(0)
+    offs, N, D = [0, 5, 9], 2, 8
+    q, k, v = (torch.randn(9, N, D, requires_grad=True) for _ in range(3))
+    tb, pb = torch.randn(2, 6, 6, requires_grad=True), torch.randn(1, 6, 6, requires_grad=True)
+    out = torch.ops.mxrec.hstu_fuxi(q, k, v, tb, pb, None, 0, 6, 0.0, "jagged", offs)
+    assert out.shape == (9, N, 3 * D)
+    g = torch.randn_like(out)
+    want = torch.autograd.grad(out, [q, k, v, pb, tb], g)
+    got = torch.ops.mxrec.hstu_dense_backward_fuxi(g, q.detach(), k.detach(), v.detach(), None, pb.detach(), tb.detach(), "jagged", 0, 6,
+                                                   0.0, offs)
+    for a, b in zip(got, want):
+        assert a.shape == b.shape
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    mask = (torch.rand(2, 1, 6, 6) > 0.3).float()
+    out = torch.ops.mxrec.hstu_fuxi(q, k, v, None, None, mask, 3, 6, 0.25, "jagged", offs)
+    want = torch.autograd.grad(out, [q, k, v], torch.ones_like(out))
+    got = torch.ops.mxrec.hstu_dense_backward_fuxi(torch.ones_like(out), q.detach(), k.detach(), v.detach(), mask, None, None, "jagged", 3, 6,
+                                                   0.25, offs)
+    assert got[3].numel() == 0 and got[4].numel() == 0
+    for a, b in zip(got[:3], want):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    import pytest
+
+    with pytest.raises(ValueError):
+        torch.ops.mxrec.hstu_dense_backward_fuxi(g, q.detach(), k.detach(), v.detach(), layout="normal", seqOffset=offs)
+    with pytest.raises(ValueError):
+        torch.ops.mxrec.hstu_dense_backward_fuxi(g[:, :, :D], q.detach(), k.detach(), v.detach(), None, pb.detach(), tb.detach(), "jagged", 0,
+                                                 6, 0.0, offs)

@@ -161,6 +161,31 @@ def test_raw_backward_returns_row_gradients():
         torch.testing.assert_close(p["dev_weights"][s: s + r * d].view(r, d), want, rtol=1e-5, atol=1e-6)
 
 
+def test_raw_backward_grad_aggregation_accumulates_then_applies():
+    """The raw ``*_grad_aggregation`` backward: a first call with ``use_optimize=False`` only adds to ``grad_accumulate``, the
+    second applies both steps at once; results equal one SGD step on twice the gradient."""
+    dev = torch.device("cpu")
+    p = _problem(dev, seed=7)
+    _, dense_grads, tabs = _dense_reference(p, 0)
+    e = torch.empty(0)
+    acc = [torch.zeros(r * d) for r, d in zip(ROWS, DIMS)]
+    fn = torch.ops.mxrec.split_embedding_backward_codegen_sgd_unweighted_exact_cuda_grad_aggregation
+    head = [p["grad"], p["dev_weights"], e, e, e.int(), p["weights_offsets"], p["D_offsets"], max(DIMS), p["hash_size_cumsum"], 8, p["idx"],
+            p["offsets"], p["idx"], p["offsets"], 0, e.int(), 0, 32, False, 0, 0, False, True]
+    w0 = p["dev_weights"].clone()
+    first = fn(*head, acc, torch.zeros(3, dtype=torch.long), learning_rate=0.1, use_optimize=False)
+    torch.testing.assert_close(p["dev_weights"], w0)
+    for t, (s, r, d) in enumerate(zip(p["starts"], ROWS, DIMS)):
+        torch.testing.assert_close(first[s: s + r * d].view(r, d), dense_grads[t], rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(acc[t].view(r, d), dense_grads[t], rtol=1e-5, atol=1e-6)
+    fn(*head, acc, torch.zeros(3, dtype=torch.long), learning_rate=0.1, use_optimize=True)
+    for t, (s, r, d) in enumerate(zip(p["starts"], ROWS, DIMS)):
+        torch.testing.assert_close(p["dev_weights"][s: s + r * d].view(r, d), tabs[t].detach() - 0.2 * dense_grads[t], rtol=1e-5, atol=1e-6)
+        assert float(acc[t].abs().sum()) == 0.0
+    for kind in ("adagrad", "adam"):
+        assert hasattr(torch.ops.mxrec, "split_embedding_backward_codegen_%s_unweighted_exact_cuda_grad_aggregation" % kind)
+
+
 def test_v2_attention_and_distance_linear():
     torch.manual_seed(0)
     lens = [5, 9, 3]
