@@ -131,6 +131,8 @@ def _jagged_common(q, k, v, mask, attn_bias, mask_type, max_seq_len, silu_scale,
                    target_group_size, alpha):
     if mask_type == 1:
         raise NotImplementedError("upper-triangular masks are not supported")
+    # both are optional in the operator schema (None = the default)
+    target_group_size, alpha = (0 if target_group_size is None else int(target_group_size)), (1.0 if alpha is None else float(alpha))
     scale = silu_scale if silu_scale != 0.0 else 1.0 / max(max_seq_len, 1)
     if (attn_bias is not None or mask_type == 3) and seq_offset_k is seq_offset and q.is_cuda and q.dtype == torch.bfloat16 \
             and q.shape[2] in (64, 128) and v.shape[2] == q.shape[2] and num_context is None and num_target is None \
@@ -212,6 +214,7 @@ def hstu_jagged_delta(q, k, v, mask=None, attn_bias=None, mask_type: int = 0, ma
 
 
 def _jagged_backward(grad, q, k, v, mask, attn_bias, mask_type, max_seq_len, silu_scale, qo, ko, num_context, num_target, gs, alpha):
+    gs, alpha = (0 if gs is None else int(gs)), (1.0 if alpha is None else float(alpha))     # both are optional in the schema
     scale = silu_scale if silu_scale != 0.0 else 1.0 / max(max_seq_len, 1)
     if attn_bias is None and mask_type in (0, 2):
         dq, dk, dv, _, _ = hstu_attn_bwd(grad, q, k, v, qo, ko, alpha, scale, mask_type == 0, num_context, num_target, gs, None, None,
@@ -249,6 +252,7 @@ def hstu_paged(q, k, v, kv_cache, mask=None, attn_bias=None, mask_type: int = 0,
     (``seq_offset_k``: total key lengths; ``seq_offset_t`` is unused: targets are given by ``num_target``)."""
     page_size = kv_cache.shape[2]
     N, D = q.shape[1], q.shape[2]
+    target_group_size, alpha = (0 if target_group_size is None else int(target_group_size)), (1.0 if alpha is None else float(alpha))
     qo, ko = seq_offset.to(torch.int64), seq_offset_k.to(torch.int64)
     lens_q, lens_k = qo[1:] - qo[:-1], ko[1:] - ko[:-1]
     bidx = torch.repeat_interleave(torch.arange(lens_q.numel(), device=q.device), lens_q)
@@ -310,16 +314,67 @@ def norm_multiply_dropout(x, u, weight, bias, eps: float = 1e-5, dropout_ratio: 
     return [hstu_ops.ln_mul(x, u, weight, bias, eps, dropout_ratio)]
 
 
-def concat_2d_jagged(max_seq_len: int, values_a, values_b, offsets_a, offsets_b):
-    return hstu_ops.concat_2d_jagged(values_a, values_b, offsets_a, offsets_b)
+def _jagged_pair_positions(offsets_a, offsets_b, n_prefix: int):
+    """Destination row of every row of A and of B in the per-sample layout ``[first n_prefix rows of B | A | rest of B]``
+    (``n_prefix`` is clipped to the sample's B length)."""
+    oa, ob = offsets_a.long(), offsets_b.long()
+    la, lb = oa[1:] - oa[:-1], ob[1:] - ob[:-1]
+    B = la.numel()
+    dev = oa.device
+    base = oa[:-1] + ob[:-1]
+    pre = lb.clamp(max=int(n_prefix))
+    sa = torch.repeat_interleave(torch.arange(B, device=dev), la)
+    ra = torch.arange(int(oa[-1]), device=dev) - oa[:-1][sa]
+    sb = torch.repeat_interleave(torch.arange(B, device=dev), lb)
+    rb = torch.arange(int(ob[-1]), device=dev) - ob[:-1][sb]
+    dst_a = base[sa] + pre[sa] + ra
+    dst_b = base[sb] + rb + torch.where(rb < pre[sb], torch.zeros_like(rb), la[sb])
+    return dst_a, dst_b
 
 
-def split_2d_jagged(values, max_seq_len: int, offsets_a, offsets_b) -> Tuple[torch.Tensor, torch.Tensor]:
-    return hstu_ops.split_2d_jagged(values, offsets_a, offsets_b)
+def concat_2d_jagged(maxSeqlen: int, valuesA, valuesB, offsetA, offsetB, isReplace: bool = False, nPrefixFromRight: int = 0):
+    """Per sample the rows of A followed by the rows of B; with ``nPrefixFromRight = n`` the first ``n`` rows of B come
+    first: ``[B[:n] | A | B[n:]]`` (``concat_2d_jagged/README.md`` of the reference; ``maxSeqlen`` and ``isReplace`` are
+    reserved there and have no effect)."""
+    if nPrefixFromRight < 0:
+        raise ValueError("nPrefixFromRight must not be negative")
+    if nPrefixFromRight == 0:
+        return hstu_ops.concat_2d_jagged(valuesA, valuesB, offsetA, offsetB)[0]
+    dst_a, dst_b = _jagged_pair_positions(offsetA, offsetB, nPrefixFromRight)
+    src = torch.cat([valuesA, valuesB])
+    order = torch.empty(src.shape[0], dtype=torch.long, device=src.device)
+    order[torch.cat([dst_a, dst_b])] = torch.arange(src.shape[0], device=src.device)
+    return src.index_select(0, order)
 
 
-def multislice_concat(x, concat_num: int, concat_size: List[int], slice_begin: List[int]):
-    return hstu_ops.multislice_concat(x, list(slice_begin)[:concat_num], list(concat_size)[:concat_num])
+def split_2d_jagged(values, maxSeqlen: int, offsetA, offsetB, dense_size: int = 0, nPrefixToRight: int = 0
+                    ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Inverse of ``concat_2d_jagged``: -> (A, B); ``nPrefixToRight`` rows at the head of every sample go back to the front
+    of B (``dense_size`` is reserved in the reference)."""
+    if nPrefixToRight < 0:
+        raise ValueError("nPrefixToRight must not be negative")
+    if nPrefixToRight == 0:
+        return hstu_ops.split_2d_jagged(values, offsetA, offsetB)
+    dst_a, dst_b = _jagged_pair_positions(offsetA, offsetB, nPrefixToRight)
+    return values.index_select(0, dst_a), values.index_select(0, dst_b)
+
+
+def multislice_concat(x, concat_num: int, concat_size: List[int], slice_begin: List[int], slice_length: List[int]) -> List[torch.Tensor]:
+    """``concat_num`` outputs; output ``i`` is the column-wise concatenation of the next ``concat_size[i]`` slices
+    ``x[:, begin:begin + length]`` taken in order from ``slice_begin`` / ``slice_length`` (``multislice_concat/README.md`` of the
+    reference).  One gather launch per output on the GPU."""
+    concat_size, slice_begin, slice_length = list(concat_size), list(slice_begin), list(slice_length)
+    if concat_num != len(concat_size) or sum(concat_size) != len(slice_begin) or len(slice_begin) != len(slice_length):
+        raise ValueError("concat_size needs concat_num entries and slice_begin / slice_length one entry per slice")
+    D = x.shape[1]
+    for b, n in zip(slice_begin, slice_length):
+        if b < 0 or n < 1 or b + n > D:
+            raise ValueError("slice [%d, %d) is outside the %d columns of the input" % (b, b + n, D))
+    out, at = [], 0
+    for k in concat_size:
+        out.append(hstu_ops.multislice_concat(x, slice_begin[at:at + k], slice_length[at:at + k]))
+        at += k
+    return out
 
 
 def index_select_for_rank1_backward(grad, x, index) -> List[torch.Tensor]:
@@ -347,22 +402,22 @@ _def("hstu_dense(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_b
 _def("hstu_dense_backward(Tensor grad, Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
      "int max_seq_len=0, float silu_scale=0.0) -> (Tensor, Tensor, Tensor, Tensor)", hstu_dense_backward)
 _def("hstu_jagged.equal(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, int max_seq_len=0, "
-     "float silu_scale=0.0, Tensor? seq_offset=None, Tensor? num_context=None, Tensor? num_target=None, int target_group_size=0, "
-     "float alpha=1.0, bool deterministic=False) -> Tensor", hstu_jagged_equal)
+     "float silu_scale=0.0, Tensor? seq_offset=None, Tensor? num_context=None, Tensor? num_target=None, int? target_group_size=0, "
+     "float? alpha=1.0, bool deterministic=False) -> Tensor", hstu_jagged_equal)
 _def("hstu_jagged.delta(Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, int max_seq_len=0, "
      "int max_seq_len_k=0, float silu_scale=0.0, Tensor? seq_offset=None, Tensor? seq_offset_k=None, Tensor? num_context=None, "
-     "Tensor? num_target=None, int target_group_size=0, float alpha=1.0, bool deterministic=False) -> Tensor", hstu_jagged_delta)
+     "Tensor? num_target=None, int? target_group_size=0, float? alpha=1.0, bool deterministic=False) -> Tensor", hstu_jagged_delta)
 _def("hstu_jagged_backward.equal(Tensor grad, Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
      "int max_seq_len=0, float silu_scale=0.0, Tensor? seq_offset=None, Tensor? num_context=None, Tensor? num_target=None, "
-     "int target_group_size=0, float alpha=1.0, bool deterministic=False) -> (Tensor, Tensor, Tensor, Tensor)", hstu_jagged_backward_equal)
+     "int? target_group_size=0, float? alpha=1.0, bool deterministic=False) -> (Tensor, Tensor, Tensor, Tensor)", hstu_jagged_backward_equal)
 _def("hstu_jagged_backward.delta(Tensor grad, Tensor q, Tensor k, Tensor v, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
      "int max_seq_len=0, int max_seq_len_k=0, float silu_scale=0.0, Tensor? seq_offset=None, Tensor? seq_offset_k=None, "
-     "Tensor? num_context=None, Tensor? num_target=None, int target_group_size=0, float alpha=1.0, bool deterministic=False) "
+     "Tensor? num_context=None, Tensor? num_target=None, int? target_group_size=0, float? alpha=1.0, bool deterministic=False) "
      "-> (Tensor, Tensor, Tensor, Tensor)", hstu_jagged_backward_delta)
 _def("hstu_paged(Tensor q, Tensor k, Tensor v, Tensor(a!) kv_cache, Tensor? mask=None, Tensor? attn_bias=None, int mask_type=0, "
      "int max_seq_len=0, int max_seq_len_k=0, float silu_scale=0.0, Tensor? seq_offset=None, Tensor? seq_offset_k=None, "
      "Tensor? seq_offset_t=None, Tensor? page_offsets=None, Tensor? page_ids=None, Tensor? last_page_len=None, Tensor? num_target=None, "
-     "int target_group_size=0, float alpha=1.0, bool deterministic=False) -> Tensor", hstu_paged)
+     "int? target_group_size=0, float? alpha=1.0, bool deterministic=False) -> Tensor", hstu_paged)
 _def("in_linear_silu(Tensor x, Tensor weight, Tensor? bias, int[] attr_dict) -> Tensor[]", in_linear_silu)
 _def("in_linear_silu_backward(Tensor x, Tensor weight, Tensor? bias, Tensor user_grad, Tensor value_grad, Tensor query_grad, "
      "Tensor key_grad, Tensor linear_output, int[] attr_dict) -> Tensor[]", in_linear_silu_backward)
@@ -377,10 +432,12 @@ _def("ln_mul(Tensor x, Tensor u, Tensor gamma, Tensor beta) -> Tensor", lambda x
 _def("norm_multiply_dropout(Tensor x, Tensor u, Tensor weight, Tensor bias, float eps=1e-05, float dropout_ratio=0.0) -> Tensor[]",
      norm_multiply_dropout)
 _def("token_mixing(Tensor x, Tensor gamma, Tensor beta, float epsilon=1e-07) -> Tensor", hstu_ops.token_mixing)
-_def("concat_2d_jagged(int max_seq_len, Tensor values_a, Tensor values_b, Tensor offsets_a, Tensor offsets_b) -> (Tensor, Tensor)",
-     concat_2d_jagged)
-_def("split_2d_jagged(Tensor values, int max_seq_len, Tensor offsets_a, Tensor offsets_b) -> (Tensor, Tensor)", split_2d_jagged)
-_def("multislice_concat(Tensor input, int concat_num, int[] concat_size, int[] slice_begin) -> Tensor", multislice_concat)
+_def("concat_2d_jagged(SymInt maxSeqlen, Tensor valuesA, Tensor valuesB, Tensor offsetA, Tensor offsetB, bool isReplace=False, "
+     "SymInt nPrefixFromRight=0) -> Tensor", concat_2d_jagged)
+_def("split_2d_jagged(Tensor values, SymInt maxSeqlen, Tensor offsetA, Tensor offsetB, SymInt dense_size=0, SymInt nPrefixToRight=0) "
+     "-> (Tensor, Tensor)", split_2d_jagged)
+_def("multislice_concat(Tensor input, int concat_num, int[] concat_size, int[] slice_begin, int[] slice_length) -> Tensor[]",
+     multislice_concat)
 _def("gather_for_rank1(Tensor x, Tensor index) -> Tensor", hstu_ops.gather_for_rank1)
 _def("index_select_for_rank1_backward(Tensor grad, Tensor x, Tensor index) -> Tensor[]", index_select_for_rank1_backward)
 _def("reverse_sequence(Tensor input, Tensor seq_lengths) -> Tensor", hstu_ops.reverse_sequence)

@@ -197,3 +197,247 @@ def test_operator_names_are_registered():
     assert missing == []
     assert hasattr(torch.ops.mxrec.hstu_jagged, "equal") and hasattr(torch.ops.mxrec.hstu_jagged, "delta")
     assert hasattr(torch.ops.mxrec.hstu_jagged_backward, "equal") and hasattr(torch.ops.mxrec.hstu_jagged_backward, "delta")
+
+
+# Operator -> (argument names in the reference's order, return type), taken from the ``m.def`` strings under
+# ``cust_op/framework/torch_plugin/torch_library/`` of the reference.
+OPERATOR_ARGUMENTS = {
+    'concat_2d_jagged': ('maxSeqlen valuesA valuesB offsetA offsetB isReplace nPrefixFromRight', 'Tensor'),
+    'disentangle_attention': (
+        'query_layer key_layer value_layer pos_key_layer pos_query_layer relative_pos attn_mask pos_attr_type '
+        'score_scale',
+        '(Tensor,Tensor,Tensor'),
+    'distance_in_linear_silu': ('x weight bias attr_dict', 'Tensor[]'),
+    'gather_for_rank1': ('x index', 'Tensor'),
+    'hstu_backward_v2': (
+        'grad q k v max_seqlen_q max_seqlen_k seq_offset_q seq_offset_k rab num_context num_target scale '
+        'target_group_size alpha window_size_left window_size_right',
+        '(Tensor,Tensor,Tensor,Tensor'),
+    'hstu_dense': ('q k v mask attn_bias mask_type max_seq_len silu_scale', 'Tensor'),
+    'hstu_dense_backward': ('grad q k v mask attn_bias mask_type max_seq_len silu_scale', '(Tensor,Tensor,Tensor,Tensor)'),
+    'hstu_dense_backward_fuxi': (
+        'grad q k v mask biasPosition biasTimestamp layout maskType maxSeqLen siluScale seqOffset',
+        '(Tensor,Tensor,Tensor,Tensor,Tensor'),
+    'hstu_forward_v2': (
+        'q k v mask rab mask_type max_seq_len max_seq_len_k silu_scale seq_offset seq_offset_k num_context '
+        'num_target target_group_size alpha',
+        'Tensor'),
+    'hstu_fuxi': ('q k v timestampBias positionBias mask maskType maxSeqLen siluScale layout seqOffset', 'Tensor'),
+    'hstu_jagged.delta': (
+        'q k v mask attn_bias mask_type max_seq_len max_seq_len_k silu_scale seq_offset seq_offset_k '
+        'num_context num_target target_group_size alpha deterministic',
+        'Tensor'),
+    'hstu_jagged.equal': (
+        'q k v mask attn_bias mask_type max_seq_len silu_scale seq_offset num_context num_target '
+        'target_group_size alpha deterministic',
+        'Tensor'),
+    'hstu_jagged_backward.delta': (
+        'grad q k v mask attn_bias mask_type max_seq_len max_seq_len_k silu_scale seq_offset seq_offset_k '
+        'num_context num_target target_group_size alpha',
+        '(Tensor,Tensor,Tensor,Tensor'),
+    'hstu_jagged_backward.equal': (
+        'grad q k v mask attn_bias mask_type max_seq_len silu_scale seq_offset num_context num_target '
+        'target_group_size alpha',
+        '(Tensor,Tensor,Tensor,Tensor'),
+    'hstu_paged': (
+        'q k v kv_cache mask attn_bias mask_type max_seq_len max_seq_len_k silu_scale seq_offset seq_offset_k '
+        'seq_offset_t page_offsets page_ids last_page_len num_target target_group_size alpha deterministic',
+        'Tensor'),
+    'in_linear_silu': ('x weight bias attr_dict', 'Tensor[]'),
+    'in_linear_silu_backward': ('x weight bias user_grad value_grad query_grad key_grad linear_output attr_dict', 'Tensor[]'),
+    'index_select_for_rank1_backward': ('grad x index', 'Tensor[]'),
+    'ln_mul': ('x u gamma beta', 'Tensor'),
+    'multislice_concat': ('input concat_num concat_size slice_begin slice_length', '(Tensor[])'),
+    'norm_multiply_dropout': ('x u weight bias eps dropout_ratio', 'Tensor[]'),
+    'relative_attn_bias_pos': ('rel_pos_bias identity past_valid_lens', 'Tensor'),
+    'relative_attn_bias_time': ('timestamps timestamps_weights bucket_divisor', 'Tensor'),
+    'relative_attn_bias_time_backward': ('rab_time_grad bucket_timestamps num_buckets', 'Tensor'),
+    'relative_attn_bias_time_with_index': ('timestamps timestamps_weights bucket_divisor', 'Tensor[]'),
+    'reverse_sequence': ('input seq_lengths', '(Tensor)'),
+    'split_2d_jagged': ('values maxSeqlen offsetA offsetB dense_size nPrefixToRight', '(Tensor,Tensor)'),
+    'split_embedding_backward_codegen_adagrad_unweighted_exact_cuda': (
+        'grad_output dev_weights uvm_weights lxu_cache_weights weights_placements weights_offsets D_offsets '
+        'max_D hash_size_cumsum total_hash_size_bits indices offsets pooling_mode lxu_cache_locations unused_ '
+        'max_segment_length_per_warp stochastic_rounding info_B_num_bits info_B_mask_int64 '
+        'use_uniq_cache_locations use_homogeneous_placements momentum1_dev momentum1_uvm momentum1_placements '
+        'momentum1_offsets grad_accumulate grad_accumulate_offsets hash_indices unique_ids unique_offsets '
+        'unique_inverse offset_per_key table_grad_accumulate_offsets eps learning_rate use_optimize',
+        'Tensor'),
+    'split_embedding_backward_codegen_adagrad_unweighted_exact_cuda_grad_aggregation': (
+        'grad_output dev_weights uvm_weights lxu_cache_weights weights_placements weights_offsets D_offsets '
+        'max_D hash_size_cumsum total_hash_size_bits indices offsets indices_multi_step offsets_multi_step '
+        'pooling_mode lxu_cache_locations unused_ max_segment_length_per_warp stochastic_rounding '
+        'info_B_num_bits info_B_mask_int64 use_uniq_cache_locations use_homogeneous_placements momentum1_dev '
+        'momentum1_uvm momentum1_placements momentum1_offsets grad_accumulate grad_accumulate_offsets '
+        'hash_indices unique_ids unique_offsets unique_inverse offset_per_key table_grad_accumulate_offsets '
+        'table_offsets_multi unique_multi_step unique_offset_multi_step unique_inverse_multi_step eps '
+        'learning_rate use_optimize',
+        'Tensor'),
+    'split_embedding_backward_codegen_adam_unweighted_exact_cuda': (
+        'grad_output dev_weights uvm_weights lxu_cache_weights weights_placements weights_offsets D_offsets '
+        'max_D hash_size_cumsum total_hash_size_bits indices offsets pooling_mode lxu_cache_locations unused_ '
+        'max_segment_length_per_warp stochastic_rounding info_B_num_bits info_B_mask_int64 '
+        'use_uniq_cache_locations use_homogeneous_placements momentum1_dev momentum1_uvm momentum1_placements '
+        'momentum1_offsets momentum2_dev momentum2_uvm momentum2_placements momentum2_offsets grad_accumulate '
+        'grad_accumulate_offsets hash_indices unique_ids unique_offsets unique_inverse offset_per_key '
+        'table_grad_accumulate_offsets eps learning_rate beta1 beta2 iter use_optimize',
+        'Tensor'),
+    'split_embedding_backward_codegen_adam_unweighted_exact_cuda_grad_aggregation': (
+        'grad_output dev_weights uvm_weights lxu_cache_weights weights_placements weights_offsets D_offsets '
+        'max_D hash_size_cumsum total_hash_size_bits indices offsets indices_multi_step offsets_multi_step '
+        'pooling_mode lxu_cache_locations unused_ max_segment_length_per_warp stochastic_rounding '
+        'info_B_num_bits info_B_mask_int64 use_uniq_cache_locations use_homogeneous_placements momentum1_dev '
+        'momentum1_uvm momentum1_placements momentum1_offsets momentum2_dev momentum2_uvm '
+        'momentum2_placements momentum2_offsets grad_accumulate grad_accumulate_offsets hash_indices '
+        'unique_ids unique_offsets unique_inverse offset_per_key table_grad_accumulate_offsets '
+        'table_offsets_multi unique_multi_step unique_offset_multi_step unique_inverse_multi_step eps '
+        'learning_rate beta1 beta2 iter use_optimize',
+        'Tensor'),
+    'split_embedding_backward_codegen_rowwise_adagrad_unweighted_exact_cuda': (
+        'grad_output dev_weights uvm_weights lxu_cache_weights weights_placements weights_offsets D_offsets '
+        'max_D hash_size_cumsum total_hash_size_bits indices offsets pooling_mode lxu_cache_locations unused_ '
+        'max_segment_length_per_warp stochastic_rounding info_B_num_bits info_B_mask_int64 '
+        'use_uniq_cache_locations use_homogeneous_placements momentum1_dev momentum1_uvm momentum1_placements '
+        'momentum1_offsets grad_accumulate grad_accumulate_offsets hash_indices unique_ids unique_offsets '
+        'unique_inverse offset_per_key table_grad_accumulate_offsets eps learning_rate use_optimize',
+        'Tensor'),
+    'split_embedding_backward_codegen_sgd_unweighted_exact_cuda': (
+        'grad_output dev_weights uvm_weights lxu_cache_weights weights_placements weights_offsets D_offsets '
+        'max_D hash_size_cumsum total_hash_size_bits indices offsets pooling_mode lxu_cache_locations unused_ '
+        'max_segment_length_per_warp stochastic_rounding info_B_num_bits info_B_mask_int64 '
+        'use_uniq_cache_locations use_homogeneous_placements grad_accumulate grad_accumulate_offsets '
+        'hash_indices unique_ids unique_offsets unique_inverse offset_per_key table_grad_accumulate_offsets '
+        'learning_rate use_optimize',
+        'Tensor'),
+    'split_embedding_backward_codegen_sgd_unweighted_exact_cuda_grad_aggregation': (
+        'grad_output dev_weights uvm_weights lxu_cache_weights weights_placements weights_offsets D_offsets '
+        'max_D hash_size_cumsum total_hash_size_bits indices offsets indices_multi_step offsets_multi_step '
+        'pooling_mode lxu_cache_locations unused_ max_segment_length_per_warp stochastic_rounding '
+        'info_B_num_bits info_B_mask_int64 use_uniq_cache_locations use_homogeneous_placements '
+        'grad_accumulate grad_accumulate_offsets hash_indices unique_ids unique_offsets unique_inverse '
+        'offset_per_key table_grad_accumulate_offsets table_offsets_multi unique_multi_step '
+        'unique_offset_multi_step unique_inverse_multi_step learning_rate use_optimize',
+        'Tensor'),
+    'split_embedding_codegen_forward_unweighted_cuda': (
+        'dev_weights uvm_weights lxu_cache_weights weights_placements weights_offsets D_offsets total_D max_D '
+        'indices offsets pooling_mode lxu_cache_locations uvm_cache_stats output_dtype is_experimental '
+        'hash_indices offset_per_key rows_per_table',
+        'Tensor'),
+    'split_embedding_codegen_lookup_adagrad_function': (
+        'placeholder_autograd_tensor dev_weights uvm_weights lxu_cache_weights weights_placements '
+        'weights_offsets D_offsets total_D max_D hash_size_cumsum total_hash_size_bits indices offsets '
+        'pooling_mode indice_weights feature_requires_grad lxu_cache_locations gradient_clipping max_gradient '
+        'stochastic_rounding momentum1_dev momentum1_uvm momentum1_placements momentum1_offsets '
+        'grad_accumulate grad_accumulate_offsets hash_indices unique_ids unique_offsets unique_inverse '
+        'table_grad_accumulate_offsets eps learning_rate output_dtype B_offsets '
+        'vbe_output_offsets_feature_rank vbe_B_offsets_rank_per_feature max_B max_B_feature_rank '
+        'vbe_output_size is_experimental use_uniq_cache_locations_bwd use_homogeneous_placements '
+        'uvm_cache_stats prev_iter_dev iter apply_global_weight_decay gwd_lower_bound use_optimize '
+        'rows_per_table',
+        'Tensor'),
+    'split_embedding_codegen_lookup_adagrad_function_grad_aggregation': (
+        'placeholder_autograd_tensor dev_weights uvm_weights lxu_cache_weights weights_placements '
+        'weights_offsets D_offsets total_D max_D hash_size_cumsum total_hash_size_bits indices offsets '
+        'indices_multi_step offsets_multi_step pooling_mode indice_weights feature_requires_grad '
+        'lxu_cache_locations gradient_clipping max_gradient stochastic_rounding momentum1_dev momentum1_uvm '
+        'momentum1_placements momentum1_offsets grad_accumulate grad_accumulate_offsets hash_indices '
+        'unique_ids unique_offsets unique_inverse table_grad_accumulate_offsets table_offsets_multi '
+        'unique_multi_step unique_offset_multi_step unique_inverse_multi_step eps learning_rate output_dtype '
+        'B_offsets vbe_output_offsets_feature_rank vbe_B_offsets_rank_per_feature max_B max_B_feature_rank '
+        'vbe_output_size is_experimental use_uniq_cache_locations_bwd use_homogeneous_placements '
+        'uvm_cache_stats prev_iter_dev iter apply_global_weight_decay gwd_lower_bound use_optimize '
+        'rows_per_table',
+        'Tensor'),
+    'split_embedding_codegen_lookup_adam_function': (
+        'placeholder_autograd_tensor dev_weights uvm_weights lxu_cache_weights weights_placements '
+        'weights_offsets D_offsets total_D max_D hash_size_cumsum total_hash_size_bits indices offsets '
+        'pooling_mode indice_weights feature_requires_grad lxu_cache_locations gradient_clipping max_gradient '
+        'stochastic_rounding momentum1_dev momentum1_uvm momentum1_placements momentum1_offsets momentum2_dev '
+        'momentum2_uvm momentum2_placements momentum2_offsets grad_accumulate grad_accumulate_offsets '
+        'hash_indices unique_ids unique_offsets unique_inverse table_grad_accumulate_offsets eps '
+        'learning_rate beta1 beta2 weight_decay iter output_dtype B_offsets vbe_output_offsets_feature_rank '
+        'vbe_B_offsets_rank_per_feature max_B max_B_feature_rank vbe_output_size is_experimental '
+        'use_uniq_cache_locations_bwd use_homogeneous_placements uvm_cache_stats prev_iter_dev '
+        'apply_global_weight_decay gwd_lower_bound use_optimize rows_per_table',
+        'Tensor'),
+    'split_embedding_codegen_lookup_adam_function_grad_aggregation': (
+        'placeholder_autograd_tensor dev_weights uvm_weights lxu_cache_weights weights_placements '
+        'weights_offsets D_offsets total_D max_D hash_size_cumsum total_hash_size_bits indices offsets '
+        'indices_multi_step offsets_multi_step pooling_mode indice_weights feature_requires_grad '
+        'lxu_cache_locations gradient_clipping max_gradient stochastic_rounding momentum1_dev momentum1_uvm '
+        'momentum1_placements momentum1_offsets momentum2_dev momentum2_uvm momentum2_placements '
+        'momentum2_offsets grad_accumulate grad_accumulate_offsets hash_indices unique_ids unique_offsets '
+        'unique_inverse table_grad_accumulate_offsets table_offsets_multi unique_multi_step '
+        'unique_offset_multi_step unique_inverse_multi_step eps learning_rate beta1 beta2 weight_decay iter '
+        'output_dtype B_offsets vbe_output_offsets_feature_rank vbe_B_offsets_rank_per_feature max_B '
+        'max_B_feature_rank vbe_output_size is_experimental use_uniq_cache_locations_bwd '
+        'use_homogeneous_placements uvm_cache_stats prev_iter_dev apply_global_weight_decay gwd_lower_bound '
+        'use_optimize rows_per_table',
+        'Tensor'),
+    'split_embedding_codegen_lookup_rowwise_adagrad_function': (
+        'placeholder_autograd_tensor dev_weights uvm_weights lxu_cache_weights weights_placements '
+        'weights_offsets D_offsets total_D max_D hash_size_cumsum total_hash_size_bits indices offsets '
+        'pooling_mode indice_weights feature_requires_grad lxu_cache_locations gradient_clipping max_gradient '
+        'stochastic_rounding momentum1_dev momentum1_uvm momentum1_placements momentum1_offsets eps '
+        'learning_rate weight_decay weight_decay_mode max_norm output_dtype B_offsets '
+        'vbe_output_offsets_feature_rank vbe_B_offsets_rank_per_feature max_B max_B_feature_rank '
+        'vbe_output_size is_experimental use_uniq_cache_locations_bwd use_homogeneous_placements '
+        'uvm_cache_stats prev_iter_dev iter apply_global_weight_decay gwd_lower_bound mixed_D grad_accumulate '
+        'grad_accumulate_offsets hash_indices unique_ids unique_offsets unique_inverse '
+        'table_grad_accumulate_offsets rows_per_table',
+        'Tensor'),
+    'split_embedding_codegen_lookup_sgd_function': (
+        'placeholder_autograd_tensor dev_weights uvm_weights lxu_cache_weights weights_placements '
+        'weights_offsets D_offsets total_D max_D hash_size_cumsum total_hash_size_bits indices offsets '
+        'pooling_mode indice_weights feature_requires_grad lxu_cache_locations gradient_clipping max_gradient '
+        'stochastic_rounding grad_accumulate grad_accumulate_offsets hash_indices unique_ids unique_offsets '
+        'unique_inverse table_grad_accumulate_offsets learning_rate output_dtype B_offsets '
+        'vbe_output_offsets_feature_rank vbe_B_offsets_rank_per_feature max_B max_B_feature_rank '
+        'vbe_output_size is_experimental use_uniq_cache_locations_bwd use_homogeneous_placements '
+        'uvm_cache_stats prev_iter_dev iter apply_global_weight_decay gwd_lower_bound use_optimize '
+        'rows_per_table',
+        'Tensor'),
+    'split_embedding_codegen_lookup_sgd_function_grad_aggregation': (
+        'placeholder_autograd_tensor dev_weights uvm_weights lxu_cache_weights weights_placements '
+        'weights_offsets D_offsets total_D max_D hash_size_cumsum total_hash_size_bits indices offsets '
+        'indices_multi_step offsets_multi_step pooling_mode indice_weights feature_requires_grad '
+        'lxu_cache_locations gradient_clipping max_gradient stochastic_rounding grad_accumulate '
+        'grad_accumulate_offsets hash_indices unique_ids unique_offsets unique_inverse '
+        'table_grad_accumulate_offsets table_offsets_multi unique_multi_step unique_offset_multi_step '
+        'unique_inverse_multi_step learning_rate output_dtype B_offsets vbe_output_offsets_feature_rank '
+        'vbe_B_offsets_rank_per_feature max_B max_B_feature_rank vbe_output_size is_experimental '
+        'use_uniq_cache_locations_bwd use_homogeneous_placements uvm_cache_stats prev_iter_dev iter '
+        'apply_global_weight_decay gwd_lower_bound use_optimize rows_per_table',
+        'Tensor'),
+    'token_mixing': ('x gamma beta epsilon', 'Tensor'),
+}
+
+
+@pytest.mark.parametrize("name", sorted(OPERATOR_ARGUMENTS))
+def test_operator_arguments_follow_the_reference(name):
+    import recsdk_b200.ops.mxrec  # noqa: F401
+
+    base, _, overload = name.partition(".")
+    op = getattr(getattr(torch.ops.mxrec, base), overload or "default")
+    want, returns = OPERATOR_ARGUMENTS[name]
+    want = want.split()
+    have = [a.name for a in op._schema.arguments]
+    assert have[: len(want)] == want
+    assert all(a.has_default_value() for a in op._schema.arguments[len(want):])        # additions must be optional
+    n_ret = returns.count("Tensor") if returns.startswith("(") else 1
+    assert len(op._schema.returns) == n_ret
+    assert ("[]" in returns) == ("List" in str(op._schema.returns[0].type))
+
+
+def test_optional_scalars_accept_none():
+    """``target_group_size`` and ``alpha`` are ``int?`` / ``float?`` in the reference's attention schemas."""
+    import recsdk_b200.ops.mxrec  # noqa: F401
+
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(7, 2, 16) for _ in range(3))
+    off = torch.tensor([0, 3, 7])
+    a = torch.ops.mxrec.hstu_jagged(q, k, v, None, None, 0, 4, 0.0, off, None, None, None, None)
+    assert torch.equal(a, torch.ops.mxrec.hstu_jagged(q, k, v, None, None, 0, 4, 0.0, off))
+    g = torch.ops.mxrec.hstu_jagged_backward(torch.ones_like(a), q, k, v, None, None, 0, 4, 0.0, off, None, None, None, None)
+    g2 = torch.ops.mxrec.hstu_jagged_backward(torch.ones_like(a), q, k, v, None, None, 0, 4, 0.0, off)
+    assert all(torch.equal(x, y) for x, y in zip(g, g2))

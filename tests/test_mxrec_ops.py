@@ -81,7 +81,8 @@ def test_in_linear_silu_and_small_ops():
     y = torch.ops.mxrec.ln_mul(x, torch.ones_like(x), torch.ones(12), torch.zeros(12))
     assert torch.allclose(y, torch.nn.functional.layer_norm(x, (12,)), atol=1e-5)
     assert torch.equal(torch.ops.mxrec.gather_for_rank1(b, torch.tensor([3, 1])), b[[3, 1]])
-    assert torch.equal(torch.ops.mxrec.multislice_concat(x, 2, [2, 3], [0, 5]), torch.cat([x[:, :2], x[:, 5:8]], 1))
+    two = torch.ops.mxrec.multislice_concat(x, 2, [2, 1], [0, 5, 3], [2, 3, 4])
+    assert len(two) == 2 and torch.equal(two[0], torch.cat([x[:, :2], x[:, 5:8]], 1)) and torch.equal(two[1], x[:, 3:7])
     r = torch.ops.mxrec.reverse_sequence(torch.arange(12.).view(2, 6, 1), torch.tensor([3, 6]))
     assert r[0, :3, 0].tolist() == [2, 1, 0] and r[1, :, 0].tolist() == [11, 10, 9, 8, 7, 6]
     # TBE-compatible lookup over one flat buffer
@@ -178,3 +179,43 @@ def test_fuxi_backward_operator_matches_autograd():
     with pytest.raises(ValueError):
         torch.ops.mxrec.hstu_dense_backward_fuxi(g[:, :, :D], q.detach(), k.detach(), v.detach(), None, pb.detach(), tb.detach(), "jagged", 0,
                                                  6, 0.0, offs)
+
+
+def test_jagged_concat_and_split_with_a_prefix_from_the_right():
+    """``concat_2d_jagged`` / ``split_2d_jagged`` in the reference's signature: per sample ``[B[:n] | A | B[n:]]`` and back."""
+    import pytest
+
+    a = torch.arange(1, 4).float()[:, None].repeat(1, 4)                  # rows 1, 2, 3
+    b = torch.arange(4, 8).float()[:, None].repeat(1, 4)                  # rows 4 .. 7
+    oa, ob = torch.tensor([0, 1, 2, 3]), torch.tensor([0, 1, 3, 4])
+    cat = torch.ops.mxrec.concat_2d_jagged(2, a, b, oa, ob)
+    assert cat[:, 0].tolist() == [1, 4, 2, 5, 6, 3, 7]
+    sa, sb = torch.ops.mxrec.split_2d_jagged(cat, 2, oa, ob)
+    assert torch.equal(sa, a) and torch.equal(sb, b)
+
+    def golden(n):
+        rows = []
+        for i in range(3):
+            bs = list(range(int(ob[i]), int(ob[i + 1])))
+            p = min(n, len(bs))
+            rows += [b[j] for j in bs[:p]] + [a[j] for j in range(int(oa[i]), int(oa[i + 1]))] + [b[j] for j in bs[p:]]
+        return torch.stack(rows)
+
+    for n in (1, 2, 5):
+        got = torch.ops.mxrec.concat_2d_jagged(2, a, b, oa, ob, False, n)
+        assert torch.equal(got, golden(n))
+        ra, rb = torch.ops.mxrec.split_2d_jagged(got, 2, oa, ob, 0, n)
+        assert torch.equal(ra, a) and torch.equal(rb, b)
+    assert torch.ops.mxrec.concat_2d_jagged(2, a, b, oa, ob, False, 1)[:, 0].tolist() == [4, 1, 5, 2, 6, 7, 3]
+    empty_b = torch.ops.mxrec.concat_2d_jagged(1, a, b[:0], oa, torch.zeros(4, dtype=torch.long), False, 3)
+    assert torch.equal(empty_b, a)
+    ag = a.clone().requires_grad_(True)
+    torch.ops.mxrec.concat_2d_jagged(2, ag, b, oa, ob, False, 1).sum().backward()
+    assert torch.equal(ag.grad, torch.ones_like(a))
+    with pytest.raises(ValueError):
+        torch.ops.mxrec.concat_2d_jagged(2, a, b, oa, ob, False, -1)
+    x = torch.arange(24.).view(2, 12)
+    with pytest.raises(ValueError):
+        torch.ops.mxrec.multislice_concat(x, 1, [1], [10], [4])
+    with pytest.raises(ValueError):
+        torch.ops.mxrec.multislice_concat(x, 2, [1], [0], [4])
