@@ -57,6 +57,83 @@ _OPT_STATE_ELEMS = {OptimizerType.SGD: lambda d: 0, OptimizerType.ADAGRAD: lambd
                     OptimizerType.ROWWISE_ADAGRAD: lambda d: 4}
 
 
+@dataclasses.dataclass
+class ShardingOption:
+    """One placement a table may take: what the planner chooses between."""
+    name: str
+    module_path: str
+    sharding_type: str
+    compute_kernel: str
+    rows: int
+    dim: int
+    is_dynamic: bool
+    rows_per_rank: int
+    hbm_bytes_per_rank: int
+
+
+class DynamicEmbeddingEnumerator:
+    """Lists the placements open to every table of a model: a dynamic table has exactly one (row-wise, round robin, the
+    ``DynamicEmb`` kernel, capacity aligned up to a power of two); a static table one per sharding type that its sharder and
+    its constraint allow.  ``DynamicEmbeddingShardingPlanner(..., enumerator=...)`` takes the optimizer-state size from the
+    options listed here.  Reference: ``dynamic_emb/distributed/planner/enumerators.py:92-230``."""
+
+    def __init__(self, topology: Topology, batch_size: Optional[int] = 512, constraints: Optional[Dict[str, ParameterConstraints]] = None,
+                 estimator=None, use_exact_enumerate_order: Optional[bool] = False) -> None:
+        if not isinstance(topology, Topology):
+            raise TypeError("topology must be a Topology")
+        if batch_size is not None and (not isinstance(batch_size, int) or isinstance(batch_size, bool) or batch_size < 1):
+            raise ValueError("batch_size must be a positive int")
+        if constraints is not None and not isinstance(constraints, dict):
+            raise TypeError("constraints must be a dict")
+        self.topology, self.batch_size = topology, batch_size
+        self.constraints = dict(constraints or {})
+        self.estimator = estimator
+        self.use_exact_enumerate_order = bool(use_exact_enumerate_order)
+        self.optimizer_type = OptimizerType.ROWWISE_ADAGRAD
+
+    def _options_of(self, path: str, cfg: BaseEmbeddingConfig, allowed: List[str]) -> List[ShardingOption]:
+        W = self.topology.world_size
+        cons = self.constraints.get(cfg.name)
+        item = {"FP32": 4, "FP16": 2, "BF16": 2}[cfg.data_type.value]
+        if cons is not None and getattr(cons, "use_dynamicemb", False):
+            o = cons.dynamicemb_options
+            rows = get_constraint_capacity(cfg.num_embeddings, W, o.bucket_capacity)
+            elems = cfg.embedding_dim + _OPT_STATE_ELEMS[self.optimizer_type](cfg.embedding_dim)
+            return [ShardingOption(cfg.name, path, "row_wise", DYNAMICEMB_KERNEL, cfg.num_embeddings, cfg.embedding_dim, True, rows,
+                                   rows * elems * 4)]
+        types = [t for t in (cons.sharding_types if cons is not None and cons.sharding_types else allowed) if t in allowed]
+        out = []
+        for t in types:
+            per = {"row_wise": (cfg.num_embeddings + W - 1) // W, "table_wise": cfg.num_embeddings,
+                   "data_parallel": cfg.num_embeddings}.get(t)
+            if per is None:
+                continue
+            out.append(ShardingOption(cfg.name, path, t, "fused", cfg.num_embeddings, cfg.embedding_dim, False, per,
+                                      per * (cfg.embedding_dim * item + 4)))
+        return out
+
+    def enumerate(self, module: nn.Module, sharders=None) -> List[ShardingOption]:
+        """Every (table, placement) pair, in module order (``use_exact_enumerate_order``) or sorted by module path."""
+        found = []
+        for path, m in module.named_modules():
+            if isinstance(m, EmbeddingBagCollection):
+                cfgs = m.embedding_bag_configs()
+            elif isinstance(m, EmbeddingCollection):
+                cfgs = m.embedding_configs()
+            else:
+                continue
+            allowed = ["row_wise", "table_wise", "data_parallel"]
+            for s in sharders or []:
+                mt = getattr(s, "module_type", None)
+                if mt is not None and isinstance(m, mt) and hasattr(s, "sharding_types"):
+                    allowed = list(s.sharding_types(self.topology.compute_device))
+                    break
+            found.append((path, [o for c in cfgs for o in self._options_of(path, c, allowed)]))
+        if not self.use_exact_enumerate_order:
+            found.sort(key=lambda x: x[0])
+        return [o for _p, opts in found for o in opts]
+
+
 class DynamicEmbeddingShardingPlanner:
     def __init__(self, eb_configs: List[BaseEmbeddingConfig], constraints: Optional[Dict[str, ParameterConstraints]] = None,
                  topology: Optional[Topology] = None, batch_size: Optional[int] = None, enumerator=None, storage_reservation=None,
@@ -67,6 +144,11 @@ class DynamicEmbeddingShardingPlanner:
         self.topology = topology or Topology()
         self.optimizer_type = optimizer_type
         self.debug = debug
+        self.enumerator = enumerator
+        if enumerator is not None and hasattr(enumerator, "optimizer_type"):
+            enumerator.optimizer_type = optimizer_type                 # both must size the optimizer state the same way
+            if not enumerator.constraints:
+                enumerator.constraints = dict(self.constraints)
         static = {k: v for k, v in self.constraints.items() if not getattr(v, "use_dynamicemb", False)}
         self._dynamic = {k: v for k, v in self.constraints.items() if getattr(v, "use_dynamicemb", False)}
         reserved = 0

@@ -130,8 +130,30 @@ class _SideTensorKJT(KeyedJaggedTensor):
         for i, k in enumerate(self.keys()):
             jt = base[k]
             extras = {n: t[opk[i]:opk[i + 1]] for n, t in self._side().items() if t is not None and n in self.PER_VALUE}
-            out[k] = ExtendedJaggedTensor(jt.values(), jt.weights_or_none(), jt._lengths, jt._offsets, extras)
+            out[k] = self._jt_class()._rebuild(jt.values(), jt.weights_or_none(), jt._lengths, jt._offsets, extras)
         return out
+
+    @classmethod
+    def _jt_class(cls):
+        return {"KeyedJaggedTensorWithCount": JaggedTensorWithCount,
+                "KeyedJaggedTensorWithTimestamp": JaggedTensorWithTimestamp}.get(cls.__name__, ExtendedJaggedTensor)
+
+    @classmethod
+    def from_jt_dict(cls, jt_dict: Dict[str, JaggedTensor]):
+        """Key-major concatenation of per-key jagged tensors; per-id side tensors are taken from each tensor's ``extras``
+        (all keys must carry the same ones)."""
+        keys = list(jt_dict.keys())
+        base = KeyedJaggedTensor.from_jt_dict(jt_dict)
+        side: Dict[str, Optional[torch.Tensor]] = {}
+        for n in cls.PER_VALUE:
+            ts = [getattr(jt_dict[k], "extras", {}).get(n) for k in keys]
+            if all(t is None for t in ts):
+                side[n] = None
+            elif any(t is None for t in ts):
+                raise ValueError("%s is set on some keys only" % n)
+            else:
+                side[n] = torch.cat(ts)
+        return cls(keys, base.values(), base.weights_or_none(), base.lengths(), None, base.stride(), **side)
 
     # -- what an all-to-all of this batch has to carry (labels and tensors in matching order) --------------------------
     def dist_labels(self) -> List[str]:
@@ -234,16 +256,46 @@ class ExtendedJaggedTensor(JaggedTensor):
             if t.shape[0] != values.shape[0]:
                 raise ValueError("extra %r must have one entry per value" % n)
 
+    @classmethod
+    def _rebuild(cls, values, weights, lengths, offsets, extras: Dict[str, torch.Tensor]):
+        return cls(values, weights, lengths, offsets, extras)
+
     def to(self, device: torch.device, non_blocking: bool = False) -> "ExtendedJaggedTensor":
         b = JaggedTensor.to(self, device, non_blocking)
-        return ExtendedJaggedTensor(b.values(), b.weights_or_none(), b._lengths, b._offsets,
-                                    {n: t.to(device, non_blocking=non_blocking) for n, t in self.extras.items()})
+        return self._rebuild(b.values(), b.weights_or_none(), b._lengths, b._offsets,
+                             {n: t.to(device, non_blocking=non_blocking) for n, t in self.extras.items()})
 
     def record_stream(self, stream) -> None:
         JaggedTensor.record_stream(self, stream)
         for t in self.extras.values():
             if t.is_cuda:
                 t.record_stream(stream)
+
+
+class JaggedTensorWithCount(ExtendedJaggedTensor):
+    """JaggedTensor whose ids carry their number of occurrences (``hybrid_torchrec/sparse/jagged_tensor_with_count.py:24-49``)."""
+
+    def __init__(self, values, weights=None, lengths=None, offsets=None, counts=None) -> None:
+        super().__init__(values, weights, lengths, offsets, {} if counts is None else {"counts": counts})
+
+    @classmethod
+    def _rebuild(cls, values, weights, lengths, offsets, extras):
+        return cls(values, weights, lengths, offsets, extras.get("counts"))
+
+    counts = property(lambda self: self.extras.get("counts"))
+
+
+class JaggedTensorWithTimestamp(ExtendedJaggedTensor):
+    """JaggedTensor whose ids carry a timestamp (``torchrec_embcache/sparse/jagged_tensor_with_timestamp.py:31-59``)."""
+
+    def __init__(self, values, weights=None, lengths=None, offsets=None, timestamps=None) -> None:
+        super().__init__(values, weights, lengths, offsets, {} if timestamps is None else {"timestamps": timestamps})
+
+    @classmethod
+    def _rebuild(cls, values, weights, lengths, offsets, extras):
+        return cls(values, weights, lengths, offsets, extras.get("timestamps"))
+
+    timestamps = property(lambda self: self.extras.get("timestamps"))
 
 
 class KeyedExtendedJaggedTensor(_SideTensorKJT):

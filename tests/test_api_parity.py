@@ -441,3 +441,99 @@ def test_optional_scalars_accept_none():
     g = torch.ops.mxrec.hstu_jagged_backward(torch.ones_like(a), q, k, v, None, None, 0, 4, 0.0, off, None, None, None, None)
     g2 = torch.ops.mxrec.hstu_jagged_backward(torch.ones_like(a), q, k, v, None, None, 0, 4, 0.0, off)
     assert all(torch.equal(x, y) for x, y in zip(g, g2))
+
+
+PACKAGE_EXPORTS = {
+    "recsdk_b200": ["HashEmbeddingBagCollection", "HashEmbeddingBagConfig", "HybridHashTable"],
+    "recsdk_b200.sparse": ["JaggedTensorWithCount", "KeyedJaggedTensorWithCount", "ExtendedJaggedTensor", "KeyedExtendedJaggedTensor",
+                           "JaggedTensorWithTimestamp", "KeyedJaggedTensorWithTimestamp", "JaggedTensor", "KeyedJaggedTensor", "KeyedTensor"],
+    "recsdk_b200.parallel": ["HybridTrainPipelineSparseDist", "get_default_hybrid_sharders"],
+    "recsdk_b200.embcache": ["Saver", "EmbCacheEmbeddingBagConfig", "EmbCacheEmbeddingConfig", "AdmitAndEvictConfig", "InitializerType",
+                             "EmbCacheEmbeddingBagCollection", "EmbCacheEmbeddingCollection", "EmbCacheTrainPipelineSparseDist",
+                             "EmbCacheEmbeddingBagCollectionSharder", "EmbCacheEmbeddingCollectionSharder"],
+    "recsdk_b200.dynamic": ["DynamicEmbInitializerMode", "DynamicEmbInitializerArgs", "DynamicEmbCheckMode", "DynamicEmbTableOptions",
+                            "DynamicEmbScoreStrategy", "DynamicEmbeddingCollectionSharder", "DynamicEmbeddingBagCollectionSharder",
+                            "DynamicEmbParameterConstraints", "DynamicEmbeddingShardingPlanner", "DynamicEmbeddingEnumerator", "DynamicEmbDump",
+                            "DynamicEmbLoad", "set_score", "get_score", "EmbOptimType", "__version__"],
+}
+
+
+@pytest.mark.parametrize("package", sorted(PACKAGE_EXPORTS))
+def test_packages_export_what_the_reference_packages_export(package):
+    """``hybrid_torchrec`` / ``hybrid_torchrec.sparse`` / ``hybrid_torchrec.distributed`` / ``torchrec_embcache(.distributed, .sparse)`` /
+    ``dynamic_emb`` ``__init__`` files of the reference."""
+    mod = importlib.import_module(package)
+    assert [n for n in PACKAGE_EXPORTS[package] if not hasattr(mod, n)] == []
+    with pytest.raises(AttributeError):
+        getattr(importlib.import_module("recsdk_b200"), "no_such_name")
+
+
+def test_jagged_tensors_with_counts_and_timestamps():
+    from recsdk_b200.sparse import (JaggedTensorWithCount, JaggedTensorWithTimestamp, KeyedJaggedTensorWithCount,
+                                    KeyedJaggedTensorWithTimestamp)
+
+    a = JaggedTensorWithCount(torch.tensor([1, 2, 3]), lengths=torch.tensor([2, 1]), counts=torch.tensor([5, 6, 7]))
+    b = JaggedTensorWithCount(torch.tensor([9]), lengths=torch.tensor([0, 1]), counts=torch.tensor([1]))
+    k = KeyedJaggedTensorWithCount.from_jt_dict({"a": a, "b": b})
+    assert k.counts.tolist() == [5, 6, 7, 1] and k.lengths().tolist() == [2, 1, 0, 1] and k.stride() == 2
+    back = k.to_dict()
+    assert isinstance(back["a"], JaggedTensorWithCount) and back["b"].counts.tolist() == [1] and back["a"].values().tolist() == [1, 2, 3]
+    assert isinstance(a.to(torch.device("cpu")), JaggedTensorWithCount) and JaggedTensorWithCount(torch.tensor([1]), lengths=torch.tensor([1])).counts is None
+    with pytest.raises(ValueError):
+        JaggedTensorWithCount(torch.tensor([1, 2]), lengths=torch.tensor([2]), counts=torch.tensor([1]))
+    with pytest.raises(ValueError):
+        KeyedJaggedTensorWithCount.from_jt_dict({"a": a, "b": JaggedTensorWithCount(torch.tensor([9]), lengths=torch.tensor([0, 1]))})
+    t = KeyedJaggedTensorWithTimestamp(keys=["a"], values=torch.tensor([1, 2]), lengths=torch.tensor([2]), timestamps=torch.tensor([10, 11]))
+    jt = t.to_dict()["a"]
+    assert isinstance(jt, JaggedTensorWithTimestamp) and jt.timestamps.tolist() == [10, 11]
+    again = KeyedJaggedTensorWithTimestamp.from_jt_dict({"a": jt})
+    assert again.timestamps.tolist() == [10, 11] and again.keys() == ["a"]
+
+
+def test_dynamic_enumerator_lists_the_placements():
+    from recsdk_b200.dynamic import (DynamicEmbeddingEnumerator, DynamicEmbeddingShardingPlanner, DynamicEmbParameterConstraints,
+                                     DynamicEmbTableOptions, OptimizerType)
+    from recsdk_b200.modules import EmbeddingBagCollection, EmbeddingBagConfig, EmbeddingCollection, EmbeddingConfig
+    from recsdk_b200.parallel import ParameterConstraints, Topology
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.z_bags = EmbeddingBagCollection([EmbeddingBagConfig(num_embeddings=1000, embedding_dim=16, name="stat"),
+                                                  EmbeddingBagConfig(num_embeddings=100_000, embedding_dim=16, name="dyn")],
+                                                 device=torch.device("meta"))
+            self.a_seq = EmbeddingCollection([EmbeddingConfig(num_embeddings=50, embedding_dim=8, name="seq")], device=torch.device("meta"))
+
+    cons = {"dyn": DynamicEmbParameterConstraints(use_dynamicemb=True, dynamicemb_options=DynamicEmbTableOptions()),
+            "stat": ParameterConstraints(sharding_types=["table_wise", "column_wise"])}
+    topo = Topology(world_size=4)
+    en = DynamicEmbeddingEnumerator(topo, 512, cons)
+    opts = en.enumerate(M())
+    by = {}
+    for o in opts:
+        by.setdefault(o.name, []).append(o)
+    assert [o.module_path for o in opts][0] == "a_seq"                     # sorted by module path unless the exact order is asked for
+    assert [o.sharding_type for o in by["seq"]] == ["row_wise", "table_wise", "data_parallel"]
+    assert [o.sharding_type for o in by["stat"]] == ["table_wise"] and by["stat"][0].rows_per_rank == 1000
+    d = by["dyn"]
+    assert len(d) == 1 and d[0].is_dynamic and d[0].compute_kernel == "DynamicEmb" and d[0].rows_per_rank == 32768
+    assert d[0].hbm_bytes_per_rank == 32768 * (16 + 4) * 4                   # row-wise Adagrad keeps 4 floats of state per row
+    exact = DynamicEmbeddingEnumerator(topo, 512, cons, use_exact_enumerate_order=True).enumerate(M())
+    assert exact[0].module_path == "z_bags"
+    planner = DynamicEmbeddingShardingPlanner(M().z_bags.embedding_bag_configs(), cons, topo, enumerator=DynamicEmbeddingEnumerator(topo),
+                                              optimizer_type=OptimizerType.ADAM)
+    assert planner.enumerator.optimizer_type == OptimizerType.ADAM and "dyn" in planner.enumerator.constraints
+    dyn = [o for o in planner.enumerator.enumerate(M()) if o.name == "dyn"][0]
+    assert dyn.hbm_bytes_per_rank == planner._dyn_plan["dyn"].hbm_bytes_per_rank == 32768 * 48 * 4
+
+    class RowWiseOnly:
+        module_type = EmbeddingCollection
+
+        def sharding_types(self, compute_device_type="cuda"):
+            return ["row_wise"]
+
+    only = DynamicEmbeddingEnumerator(topo).enumerate(M(), [RowWiseOnly()])
+    assert [o.sharding_type for o in only if o.name == "seq"] == ["row_wise"]
+    for bad in (dict(topology="cuda"), dict(topology=topo, batch_size=0), dict(topology=topo, constraints=[1])):
+        with pytest.raises((TypeError, ValueError)):
+            DynamicEmbeddingEnumerator(**bad)
