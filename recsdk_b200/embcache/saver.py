@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import os
 import shutil
+from datetime import datetime, timezone
 from typing import List, Optional
 
 import torch
@@ -17,6 +18,7 @@ import torch.distributed as dist
 from .train_pipeline import embcache_modules
 
 META = "meta.ini"
+TIMESTAMP_FORMAT = "%Y%m%d%H%M%S"          # name of a checkpoint directory in the reference's flow (``saver.py:24``)
 
 
 def _read_meta(path: str) -> dict:
@@ -48,7 +50,13 @@ class Saver:
         if not mods:
             raise ValueError("module holds no embcache tables")
         step = max(m.swap_step for m in mods)
-        out = os.path.join(path, "%s_%010d" % ("incremental" if incremental else "full", step))
+        # Two ways to name a checkpoint.  The reference's: the caller passes the checkpoint directory itself, named by a UTC
+        # timestamp (``Saver.timestamp_dir_name()``), and finds the newest one with ``get_latest_load_path(parent)``.  This
+        # package's: the caller passes the parent and the directory is named after the kind and the training step.
+        if Saver.is_timestamp_format(os.path.basename(os.path.normpath(path))):
+            out = path
+        else:
+            out = os.path.join(path, "%s_%010d" % ("incremental" if incremental else "full", step))
         if rank == 0:
             os.makedirs(out, exist_ok=True)
         self._barrier()
@@ -86,18 +94,33 @@ class Saver:
         self._barrier()
 
     @staticmethod
+    def is_timestamp_format(dir_name: str) -> bool:
+        """True for names like ``20250131235959`` (UTC, ``%Y%m%d%H%M%S``)."""
+        try:
+            datetime.strptime(dir_name, TIMESTAMP_FORMAT)
+            return len(dir_name) == 14
+        except (ValueError, TypeError):
+            return False
+
+    @staticmethod
+    def timestamp_dir_name() -> str:
+        return datetime.now(tz=timezone.utc).strftime(TIMESTAMP_FORMAT)
+
+    @staticmethod
     def get_latest_load_path(path: str, incremental: Optional[bool] = None) -> Optional[str]:
-        best, best_step = None, -1
+        """Newest finished checkpoint under ``path`` (None when there is none): the highest training step, and among
+        timestamp-named directories of equal step - or written without a step, as the reference writes them - the latest name."""
+        best, best_key = None, None
         if not os.path.isdir(path):
             return None
-        for d in os.listdir(path):
+        for d in sorted(os.listdir(path)):
             full = os.path.join(path, d)
             if not os.path.exists(os.path.join(full, META)):
                 continue
             meta = _read_meta(os.path.join(full, META))
             if incremental is not None and (meta.get("incremental", "False") == "True") != incremental:
                 continue
-            step = int(meta.get("step", "0"))
-            if step > best_step:
-                best, best_step = full, step
+            key = (int(meta.get("step", "-1")), d if Saver.is_timestamp_format(d) else "")
+            if best_key is None or key > best_key:
+                best, best_key = full, key
         return best

@@ -157,6 +157,8 @@ class HostKVTaskStatus(enum.Enum):
 
 
 class HostKVStorageErrorCode(str, enum.Enum):
+    SDK_IMPORT_FAILED = "sdk_import_failed"
+    SDK_INIT_FAILED = "sdk_init_failed"
     LOOKUP_FAILED = "lookup_failed"
     LOOKUP_MISSING_TOKENS = "lookup_missing_tokens"
     ONBOARD_TASK_NOT_FOUND = "onboard_task_not_found"
@@ -171,6 +173,7 @@ class HostKVStorageErrorCode(str, enum.Enum):
 
 @dataclasses.dataclass
 class HostKVTaskHandle:
+    backend: str = "native"
     user_ids: Optional[torch.Tensor] = None
     handle: Any = None
     status: HostKVTaskStatus = HostKVTaskStatus.UNINITIALIZED
@@ -192,10 +195,15 @@ class HostKVTaskHandle:
 @dataclasses.dataclass
 class HostKVWaitResult:
     status: HostKVTaskStatus
-    error_code: Optional[HostKVStorageErrorCode] = None
+    ready: Optional[bool] = None          # None: derived from the status (ready / event-ready / skipped count as ready)
     message: str = ""
     failed_mask: Optional[torch.Tensor] = None
     failed_user_ids: Optional[List[int]] = None
+    error_code: Optional[HostKVStorageErrorCode] = None
+
+    def __post_init__(self) -> None:
+        if self.ready is None:
+            self.ready = self.status in (HostKVTaskStatus.READY, HostKVTaskStatus.EVENT_READY, HostKVTaskStatus.SKIPPED)
 
 
 class HostKVStorageManagerBase(abc.ABC):
@@ -234,6 +242,15 @@ class HostKVStorageManagerBase(abc.ABC):
     @abc.abstractmethod
     def evict_all(self) -> None: ...
 
+    @staticmethod
+    def get_offload_handle_metadata(task_handle: HostKVTaskHandle) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """-> (user ids, start token of each user's offloaded range, tokens offloaded) of an offload task."""
+        md = task_handle.metadata or {}
+        uids = task_handle.user_ids if task_handle.user_ids is not None else torch.zeros(0, dtype=torch.int64)
+        n = uids.numel()
+        return (uids, torch.tensor(list(md.get("starts", [0] * n)), dtype=torch.int32),
+                torch.tensor(list(md.get("lengths", [0] * n)), dtype=torch.int32))
+
 
 def _np64(t: torch.Tensor) -> np.ndarray:
     return np.ascontiguousarray(t.detach().cpu().numpy().astype(np.int64))
@@ -258,6 +275,19 @@ class GPUKVCacheManager:
 
     def get_cache_table(self, layer: int) -> torch.Tensor:
         return self.cache[layer]
+
+    def get_cache_tables(self, layer_idx: int = -1):
+        """All per-layer cache tables (``layer_idx = -1``) or one of them."""
+        return [self.cache[l] for l in range(self.cfg.num_layers)] if layer_idx == -1 else self.cache[layer_idx]
+
+    def get(self, page_ids, last_page_lens, layer_idx: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """K and V ``[tokens, heads, head_dim]`` of one sequence: its pages in order, the last one cut at ``last_page_lens``."""
+        table = self.cache[layer_idx]
+        pages = torch.as_tensor(page_ids, device=table.device).long()
+        n = pages.numel() * self.cfg.page_size - (self.cfg.page_size - int(last_page_lens)) if pages.numel() else 0
+        k = table[pages, 0].reshape(-1, self.cfg.num_heads, self.cfg.head_dim)[:n].clone()
+        v = table[pages, 1].reshape(-1, self.cfg.num_heads, self.cfg.head_dim)[:n].clone()
+        return k, v
 
     def lookup(self, user_ids: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         s, l = self.impl.lookup(_np64(user_ids))
@@ -538,7 +568,7 @@ class NativeHostKVCacheManager(HostKVStorageManagerBase):
             if len(chunks) * cfg.offload_chunksize < need:
                 raise RuntimeError("host index lost chunks of user %d between lookup and onboard" % u)
             jobs.append((int(u), need, chunks, page_ids[indptr[b]: indptr[b] + need // cfg.page_size]))
-        h = HostKVTaskHandle(index_meta.user_ids, status=HostKVTaskStatus.SKIPPED, time_launched=time.time(), is_layerwise=True,
+        h = HostKVTaskHandle(user_ids=index_meta.user_ids, status=HostKVTaskStatus.SKIPPED, time_launched=time.time(), is_layerwise=True,
                              metadata={"jobs": [(u, n) for u, n, _c, _p in jobs]})
         if not jobs:
             return h
@@ -590,12 +620,21 @@ class NativeHostKVCacheManager(HostKVStorageManagerBase):
             return HostKVWaitResult(HostKVTaskStatus.SKIPPED)
         if not self._poll(task_handle.layer_events, self.cfg.onload_timeout_ms):
             task_handle.status = HostKVTaskStatus.TIMEOUT
-            return HostKVWaitResult(HostKVTaskStatus.TIMEOUT, HostKVStorageErrorCode.ONBOARD_TIMEOUT, "onboard timed out")
+            return HostKVWaitResult(HostKVTaskStatus.TIMEOUT, error_code=HostKVStorageErrorCode.ONBOARD_TIMEOUT, message="onboard timed out")
         if self.native is not None and task_handle.handle is not None:
             self.native.release(task_handle.handle)
             task_handle.handle = None
         task_handle.status = HostKVTaskStatus.READY
         return HostKVWaitResult(HostKVTaskStatus.READY)
+
+    def onboard_kvcache_wait_by_layer(self, task_handle: HostKVTaskHandle, layer_idx: int) -> HostKVWaitResult:
+        """Make the current stream wait for one layer of an onboard task (no host wait): the attention of layer ``layer_idx``
+        may then be enqueued while later layers are still in flight."""
+        if task_handle.status == HostKVTaskStatus.SKIPPED or not task_handle.layer_events:
+            return HostKVWaitResult(HostKVTaskStatus.SKIPPED)
+        if self.cuda:
+            task_handle.stream_wait_layer(layer_idx)
+        return HostKVWaitResult(HostKVTaskStatus.EVENT_READY)
 
     def offload_kvcache_launch(self, user_ids, start_indices, page_lists, index_meta=None, kvcache_metadata=None) -> HostKVTaskHandle:
         """Copy whole chunks (``start`` is chunk-aligned by construction) from device pages into new host chunks."""
@@ -614,7 +653,7 @@ class NativeHostKVCacheManager(HostKVStorageManagerBase):
             if n_tok > 0:
                 plan.append((int(u), chunks, np.asarray(pages[: n_chunks * self.ppc], dtype=np.int64)))
             lengths.append(n_tok)
-        h = HostKVTaskHandle(user_ids, status=HostKVTaskStatus.LAUNCHED, time_launched=time.time(),
+        h = HostKVTaskHandle(user_ids=user_ids, status=HostKVTaskStatus.LAUNCHED, time_launched=time.time(),
                              metadata={"plan": plan, "lengths": lengths, "starts": starts, "no_space": no_space})
         if not plan:
             h.status = HostKVTaskStatus.SKIPPED
@@ -648,22 +687,22 @@ class NativeHostKVCacheManager(HostKVStorageManagerBase):
         no_space = (task_handle.metadata or {}).get("no_space") or None
         code = HostKVStorageErrorCode.OFFLOAD_NO_SPACE if no_space else None
         if task_handle.status == HostKVTaskStatus.SKIPPED:
-            return HostKVWaitResult(HostKVTaskStatus.SKIPPED, code, failed_user_ids=no_space)
+            return HostKVWaitResult(HostKVTaskStatus.SKIPPED, error_code=code, failed_user_ids=no_space)
         if self.fail_next_offload:
             self.fail_next_offload = False
             if self.cuda:
                 self.offload_stream.synchronize()
             task_handle.status = HostKVTaskStatus.FAILED
-            return HostKVWaitResult(HostKVTaskStatus.FAILED, HostKVStorageErrorCode.OFFLOAD_WAIT_FAILED, "injected copy failure")
+            return HostKVWaitResult(HostKVTaskStatus.FAILED, error_code=HostKVStorageErrorCode.OFFLOAD_WAIT_FAILED, message="injected copy failure")
         if (task_handle.metadata or {}).get("launch_error"):
             task_handle.status = HostKVTaskStatus.FAILED
-            return HostKVWaitResult(HostKVTaskStatus.FAILED, HostKVStorageErrorCode.OFFLOAD_WAIT_FAILED,
-                                    "offload copy failed while launching (CUDA error %d)" % task_handle.metadata["launch_error"])
+            return HostKVWaitResult(HostKVTaskStatus.FAILED, error_code=HostKVStorageErrorCode.OFFLOAD_WAIT_FAILED,
+                                    message="offload copy failed while launching (CUDA error %d)" % task_handle.metadata["launch_error"])
         if not self._poll(task_handle.layer_events, self.cfg.offload_timeout_ms):
             task_handle.status = HostKVTaskStatus.TIMEOUT
-            return HostKVWaitResult(HostKVTaskStatus.TIMEOUT, HostKVStorageErrorCode.OFFLOAD_TIMEOUT, "offload timed out")
+            return HostKVWaitResult(HostKVTaskStatus.TIMEOUT, error_code=HostKVStorageErrorCode.OFFLOAD_TIMEOUT, message="offload timed out")
         task_handle.status = HostKVTaskStatus.READY
-        return HostKVWaitResult(HostKVTaskStatus.READY, code, failed_user_ids=no_space)
+        return HostKVWaitResult(HostKVTaskStatus.READY, error_code=code, failed_user_ids=no_space)
 
     def finish_task(self, task_handle: HostKVTaskHandle) -> List[int]:
         """-> per user 1 (offloaded) / 0 (not).  A failed, timed-out or cancelled task gives its chunks back; a
@@ -720,7 +759,12 @@ class KVCacheManager:
         meta = KVIndexMeta(user_ids.cpu().long(), sequence_lengths.cpu().int())
         ds, dl = self.gpu.lookup(meta.user_ids)
         if self.host is not None:
-            hs, hl = self.host.lookup_kvcache(meta)
+            got = self.host.lookup_kvcache(meta)
+            if isinstance(got, KVLookupResult):                       # a backend written against the reference's contract
+                hs = got.host_cached_start_indices if got.host_cached_start_indices is not None else got.cached_start_indices
+                hl = got.host_cached_lengths if got.host_cached_lengths is not None else got.cached_lengths
+            else:
+                hs, hl = got
         else:
             hs, hl = torch.zeros_like(ds), torch.zeros_like(dl)
         return meta, KVLookupResult.merge(meta.user_ids, ds, dl, hs, hl)
@@ -740,13 +784,13 @@ class KVCacheManager:
 
     def onboard_launch(self, index_meta, lookup_result, kvcache_metadata) -> HostKVTaskHandle:
         if self.host is None:
-            return HostKVTaskHandle(index_meta.user_ids, status=HostKVTaskStatus.SKIPPED)
+            return HostKVTaskHandle(user_ids=index_meta.user_ids, status=HostKVTaskStatus.SKIPPED)
         try:
             h = self.host.onboard_kvcache_launch(index_meta, lookup_result, kvcache_metadata)
         except Exception as e:  # noqa: BLE001 - the host tier is best effort under fail_open
             self.stats["onboard_failures"] += 1
-            self._fail("onboard", HostKVWaitResult(HostKVTaskStatus.FAILED, HostKVStorageErrorCode.ONBOARD_WAIT_FAILED, str(e)))
-            return HostKVTaskHandle(index_meta.user_ids, status=HostKVTaskStatus.FAILED,
+            self._fail("onboard", HostKVWaitResult(HostKVTaskStatus.FAILED, error_code=HostKVStorageErrorCode.ONBOARD_WAIT_FAILED, message=str(e)))
+            return HostKVTaskHandle(user_ids=index_meta.user_ids, status=HostKVTaskStatus.FAILED,
                                     metadata={"need": self._onboard_need(lookup_result)})
         kvcache_metadata.kv_onload_handle = h
         self.stats["onboarded_tokens"] += sum(n for _u, n in h.metadata["jobs"])

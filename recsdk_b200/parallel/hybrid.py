@@ -105,16 +105,7 @@ class HybridTrainPipelineSparseDist(TrainPipelineBase):
     def __init__(self, model: torch.nn.Module, optimizer, device, execute_all_batches: bool = True, apply_jit: bool = False,
                  return_loss: bool = False, pipe_n_batch: int = 6,
                  sparse_features_of: Callable[[Any], Any] = lambda batch: batch.sparse_features) -> None:
-        if not isinstance(pipe_n_batch, int) or isinstance(pipe_n_batch, bool):
-            raise ValueError("pipe_n_batch must be an int but got %s" % type(pipe_n_batch).__name__)
-        if not (1 <= pipe_n_batch <= MAX_PIPE_N_BATCH):
-            raise ValueError("pipe_n_batch must be in [1, %d]" % MAX_PIPE_N_BATCH)
-        if not isinstance(model, torch.nn.Module):
-            raise TypeError("model must be a torch.nn.Module, got %s" % type(model).__name__)
-        if apply_jit:
-            raise ValueError("apply_jit is not supported")
-        if not execute_all_batches:
-            raise ValueError("execute_all_batches cannot be False: batches already in the lines have had their ids exchanged")
+        self.param_check(model, torch.device(device), pipe_n_batch, apply_jit, execute_all_batches)
         super().__init__(model, optimizer, torch.device(device), return_loss)
         self._mods = [m for m in model.modules() if isinstance(m, CollectiveShardedEmbeddingBagCollection)]
         self._features_of = sparse_features_of
@@ -128,6 +119,26 @@ class HybridTrainPipelineSparseDist(TrainPipelineBase):
         self.stage_log: List[Tuple[int, int, str]] = []      # (training step, batch index, stage) when tracing is on
         self.trace_stages = False
         self._step_no = 0
+
+    def param_check(self, model: torch.nn.Module, device: torch.device, pipe_n_batch, apply_jit, execute_all_batches) -> None:
+        """Argument checks of the constructor (``hybrid_train_pipeline.py:240-268`` of the reference; the device may be any
+        ``torch.device`` here, CPU included, since the pipeline also runs on the gloo / CPU path)."""
+        if not isinstance(pipe_n_batch, int) or isinstance(pipe_n_batch, bool):
+            raise ValueError("pipe_n_batch must be an int but got %s" % type(pipe_n_batch).__name__)
+        if not (1 <= pipe_n_batch <= MAX_PIPE_N_BATCH):
+            raise ValueError("pipe_n_batch must be in [1, %d]" % MAX_PIPE_N_BATCH)
+        if not isinstance(model, torch.nn.Module):
+            raise TypeError("model must be a torch.nn.Module, got %s" % type(model).__name__)
+        if not isinstance(device, torch.device):
+            raise TypeError("device must be a torch.device, got %s" % type(device).__name__)
+        if apply_jit:
+            raise ValueError("apply_jit is not supported")
+        if not execute_all_batches:
+            raise ValueError("execute_all_batches cannot be False: batches already in the lines have had their ids exchanged")
+
+    def enque_context(self, line_id: int, context: HybridPipelineContext) -> None:
+        """Append a batch context to pipeline line ``line_id`` (``hybrid_train_pipeline.py:270-271`` of the reference)."""
+        self._lines[line_id % self._n].append(context)
 
     # ------------------------------------------------------------------ stages
     def _log(self, ctx: HybridPipelineContext, stage: HybridStage) -> None:

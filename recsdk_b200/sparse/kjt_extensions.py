@@ -78,6 +78,30 @@ class _SideTensorKJT(KeyedJaggedTensor):
         return self._wrap(base, side)
 
 
+    # -- the reference's generic forms (``extended_jagged_tensor.py:288-580``): the caller names the class to build ----------
+    def _as(self, constructor, kjt: "_SideTensorKJT"):
+        if constructor is None or constructor is type(kjt):
+            return kjt
+        side = {n: t for n, t in kjt._side().items() if t is not None}
+        return constructor(keys=kjt.keys(), values=kjt.values(), weights=kjt.weights_or_none(), lengths=kjt.lengths_or_none(),
+                           offsets=kjt.offsets_or_none(), stride=kjt.stride(), **side)
+
+    def split_extend(self, segments: List[int], constructor=None):
+        if len(segments) > len(self.keys()):
+            raise ValueError("len of segments should be <= len(keys)")
+        return [self._as(constructor, p) for p in self.split(segments)]
+
+    def permute_extend(self, indices: List[int], indices_tensor: Optional[torch.Tensor] = None, constructor=None,
+                       extra_permute_func=None):
+        out = self.permute(indices, indices_tensor)
+        if extra_permute_func is not None:
+            side = {n: (extra_permute_func(t) if t is not None and n in self.PER_VALUE else t) for n, t in out._side().items()}
+            out = self._wrap(out, side)
+        return self._as(constructor, out)
+
+    def pin_memory_extend(self, constructor=None):
+        return self._as(constructor, self.pin_memory())
+
     # -- constructors / conversions that keep the side tensors ------------------------------------------------------
     @classmethod
     def from_lengths_sync(cls, keys: List[str], values: torch.Tensor, lengths: torch.Tensor, weights: Optional[torch.Tensor] = None,
@@ -270,6 +294,11 @@ class ExtendedJaggedTensor(JaggedTensor):
         for t in self.extras.values():
             if t.is_cuda:
                 t.record_stream(stream)
+
+    @property
+    def extra(self) -> Optional[torch.Tensor]:
+        """The side tensor when there is exactly one (the reference's classes carry a single ``extra``); else None."""
+        return next(iter(self.extras.values())) if len(self.extras) == 1 else None
 
 
 class JaggedTensorWithCount(ExtendedJaggedTensor):

@@ -286,3 +286,33 @@ def test_cache_sizing_follows_the_device_budget(monkeypatch):
     odd = EmbCacheEmbeddingBagConfig(name="odd", embedding_dim=12, num_embeddings=10, feature_names=["c"])
     with pytest.raises(ValueError, match="multiple of 8"):
         EmbCacheEmbeddingBagCollection([odd], world_size=1, batch_size=8, multi_hot_sizes=[1])
+
+
+def test_checkpoints_in_timestamp_directories(tmp_path):
+    """The reference's flow: the caller names the checkpoint directory by a UTC timestamp and asks for the newest one
+    (``torchrec_embcache/saver.py:55-69``); files land directly in that directory."""
+    import os
+
+    assert Saver.is_timestamp_format("20250131235959") and Saver.is_timestamp_format(Saver.timestamp_dir_name())
+    for bad in ("full_0000000006", "2025013123595", "20251331000000", "", "2025-01-31"):
+        assert not Saver.is_timestamp_format(bad)
+    m = _sharded(_tables(), [40, 64])
+    saver = Saver()
+    _train(m, 3)
+    first = saver.save(m, str(tmp_path / "20250101000000"))
+    assert first == str(tmp_path / "20250101000000") and os.path.exists(os.path.join(first, "meta.ini"))
+    _train(m, 3, seed=1)
+    second = saver.save(m, str(tmp_path / "20250101000500"))
+    assert Saver.get_latest_load_path(str(tmp_path)) == second
+    # directories written without a step (the reference's meta.ini holds two lines only) are ordered by their names
+    for d in (first, second):
+        with open(os.path.join(d, "meta.ini")) as f:
+            lines = [ln for ln in f if not ln.startswith(("step=", "tables="))]
+        with open(os.path.join(d, "meta.ini"), "w") as f:
+            f.writelines(lines)
+    assert Saver.get_latest_load_path(str(tmp_path)) == second
+    ref_rows = m.host_rows("t0", list(range(60))).clone()
+    m2 = _sharded(_tables(), [40, 64])
+    saver.load(m2, Saver.get_latest_load_path(str(tmp_path)))
+    assert torch.allclose(m2.host_rows("t0", list(range(60))), ref_rows)
+    assert Saver.get_latest_load_path(str(tmp_path / "nowhere")) is None

@@ -89,3 +89,27 @@ def test_argument_checks():
         HybridTrainPipelineSparseDist(model, opt, torch.device("cpu"), execute_all_batches=False)
     with pytest.raises(TypeError):
         HybridTrainPipelineSparseDist("model", opt, torch.device("cpu"))
+
+
+def test_param_check_and_enque_context():
+    import pytest
+    import torch
+
+    from recsdk_b200.parallel.hybrid import HybridPipelineContext, HybridTrainPipelineSparseDist
+
+    model = torch.nn.Linear(2, 2)
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    pipe = HybridTrainPipelineSparseDist(model, opt, torch.device("cpu"), pipe_n_batch=2)
+    for bad, err in ((dict(pipe_n_batch=0), ValueError), (dict(pipe_n_batch=13), ValueError), (dict(pipe_n_batch=True), ValueError),
+                     (dict(apply_jit=True), ValueError), (dict(execute_all_batches=False), ValueError)):
+        kw = dict(pipe_n_batch=2, apply_jit=False, execute_all_batches=True)
+        kw.update(bad)
+        with pytest.raises(err):
+            pipe.param_check(model, torch.device("cpu"), kw["pipe_n_batch"], kw["apply_jit"], kw["execute_all_batches"])
+    with pytest.raises(TypeError):
+        pipe.param_check("model", torch.device("cpu"), 2, False, True)
+    with pytest.raises(TypeError):
+        pipe.param_check(model, "cpu", 2, False, True)
+    ctx = HybridPipelineContext.__new__(HybridPipelineContext)
+    pipe.enque_context(3, ctx)                               # line 3 of a two-line pipeline is line 1
+    assert len(pipe._lines[1]) == 1 and pipe._lines[1][0] is ctx and len(pipe._lines[0]) == 0

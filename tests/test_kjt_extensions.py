@@ -67,3 +67,28 @@ def test_side_tensor_kjt_concat_dict_dist_roundtrip_and_validation():
         KeyedExtendedJaggedTensor(["k"], torch.arange(2), lengths=torch.tensor([2]), extra=torch.arange(3))
     with pytest.raises(ValueError):
         KeyedExtendedJaggedTensor(["k"], torch.arange(2))
+
+
+def test_generic_forms_that_take_the_class_to_build():
+    """``split_extend`` / ``permute_extend`` / ``pin_memory_extend`` (``extended_jagged_tensor.py:288-580`` of the reference) and
+    the single ``extra`` of an extended jagged tensor."""
+    import pytest
+    import torch
+
+    from recsdk_b200.sparse import (ExtendedJaggedTensor, KeyedExtendedJaggedTensor, KeyedJaggedTensorWithCount)
+
+    k = KeyedJaggedTensorWithCount(["a", "b"], torch.tensor([1, 2, 3]), lengths=torch.tensor([2, 0, 0, 1]), counts=torch.tensor([7, 8, 9]))
+    head, tail = k.split_extend([1, 1])
+    assert isinstance(tail, KeyedJaggedTensorWithCount) and tail.counts.tolist() == [9] and head.counts.tolist() == [7, 8]
+    as_ext = k.split_extend([2], lambda **kw: KeyedExtendedJaggedTensor(kw["keys"], kw["values"], kw["weights"], kw["lengths"], kw["offsets"],
+                                                                         kw["stride"], extra=kw["counts"]))[0]
+    assert isinstance(as_ext, KeyedExtendedJaggedTensor) and as_ext.extra.tolist() == [7, 8, 9]
+    with pytest.raises(ValueError):
+        k.split_extend([1, 1, 1])
+    p = k.permute_extend([1, 0], None, None, extra_permute_func=lambda t: t * 10)
+    assert p.keys() == ["b", "a"] and p.values().tolist() == [3, 1, 2] and p.counts.tolist() == [90, 70, 80]
+    if torch.cuda.is_available():
+        assert k.pin_memory_extend().counts.is_pinned()
+    one = ExtendedJaggedTensor(torch.tensor([1, 2]), lengths=torch.tensor([2]), extras={"ts": torch.tensor([5, 6])})
+    assert one.extra.tolist() == [5, 6]
+    assert ExtendedJaggedTensor(torch.tensor([1]), lengths=torch.tensor([1])).extra is None

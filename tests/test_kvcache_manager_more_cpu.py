@@ -62,7 +62,9 @@ def test_merged_lookup_view():
                              torch.tensor([0, 256, 128]))
     assert r.cached_start_indices.tolist() == [0, 0, 0] and r.cached_lengths.tolist() == [100, 300, 128]
     assert r.npu_cached_lengths.tolist() == [100, 44, 0] and r.host_cached_lengths.tolist() == [0, 256, 128] and r.extra == {}
-    assert HostKVWaitResult(HostKVTaskStatus.TIMEOUT, HostKVStorageErrorCode.OFFLOAD_TIMEOUT).error_code.value == "offload_timeout"
+    r = HostKVWaitResult(HostKVTaskStatus.TIMEOUT, error_code=HostKVStorageErrorCode.OFFLOAD_TIMEOUT)
+    assert r.error_code.value == "offload_timeout" and r.ready is False and HostKVWaitResult(HostKVTaskStatus.EVENT_READY).ready
+    assert HostKVWaitResult(status=HostKVTaskStatus.FAILED, ready=True).ready is True       # an explicit value is kept
     h = HostKVTaskHandle()
     assert h.status == HostKVTaskStatus.UNINITIALIZED and h.layer_events is None
     h.stream_wait_layer(0)                                                 # nothing to wait for: a no-op
@@ -157,3 +159,41 @@ def test_revoke_failed_onboard_releases_the_reserved_prefix():
     merged = m.lookup_kvcache(torch.tensor([7]), torch.tensor([300]))[1]
     assert merged.cached_lengths.tolist() == [300] and merged.npu_cached_start_indices.tolist() == [256]
     assert isinstance(m.gpu.impl.pages_of(7), np.ndarray)
+
+
+def test_reference_contract_helpers():
+    """Names a backend or caller written against the reference's contract uses: per-layer tables, reading a sequence back,
+    waiting for one layer of an onboard, the metadata of an offload task, a host backend that answers with a ``KVLookupResult``."""
+    m = KVCacheManager.from_config(_cfg())
+    meta, look = m.lookup_kvcache(torch.tensor([7]), torch.tensor([300]))
+    md = m.allocate_kvcache(meta, look)
+    kv = _fill(m, md)
+    assert len(m.gpu.get_cache_tables()) == 2 and m.gpu.get_cache_tables(1) is not None
+    assert m.gpu.get_cache_tables(0).data_ptr() == m.gpu.get_cache_table(0).data_ptr()
+    pages = m.gpu.impl.pages_of(7)
+    k, v = m.gpu.get(pages, int(md.kv_last_page_len[0]), 1)
+    assert k.shape == (300, 2, 64) and torch.equal(k, kv[1][0]) and torch.equal(v, kv[1][1])
+    h = m.offload_launch(meta, md)
+    uids, starts, lengths = m.host.get_offload_handle_metadata(h)
+    assert (uids.tolist(), starts.tolist(), lengths.tolist()) == ([7], [0], [256])
+    assert m.offload_try_wait().ready
+    m.evict(torch.tensor([7]), for_npu=True, for_host=False)
+    meta, look = m.lookup_kvcache(torch.tensor([7]), torch.tensor([300]))
+    md = m.allocate_kvcache(meta, look)
+    task = m.onboard_launch(meta, look, md)
+    for layer in range(2):
+        assert m.host.onboard_kvcache_wait_by_layer(task, layer).status == HostKVTaskStatus.EVENT_READY
+    assert m.onboard_wait(task).ready
+    skipped = HostKVTaskHandle(backend="native", user_ids=torch.tensor([1]), status=HostKVTaskStatus.SKIPPED)
+    assert m.host.onboard_kvcache_wait_by_layer(skipped, 0).status == HostKVTaskStatus.SKIPPED and skipped.backend == "native"
+    empty = HostKVStorageManagerBase.get_offload_handle_metadata(HostKVTaskHandle())
+    assert [t.numel() for t in empty] == [0, 0, 0]
+
+    class Foreign(NativeHostKVCacheManager):
+        def lookup_kvcache(self, index_meta):
+            s, l = super().lookup_kvcache(index_meta)
+            return KVLookupResult(index_meta.user_ids, s, l, host_cached_start_indices=s, host_cached_lengths=l)
+
+    f = KVCacheManager(GPUKVCacheManager(_cfg()), Foreign(_cfg()))
+    assert f.lookup_kvcache(torch.tensor([3]), torch.tensor([10]))[1].host_cached_lengths.tolist() == [0]
+    assert "sdk_init_failed" in [c.value for c in HostKVStorageErrorCode]
