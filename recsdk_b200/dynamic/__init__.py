@@ -3,17 +3,32 @@ from .batched_dynamicemb_table import BatchedDynamicEmbeddingTablesV2
 from .dump_load import DynamicEmbDump, DynamicEmbLoad, get_score, incremental_dump, set_score
 from .dynamicemb_config import (DynamicEmbCheckMode, DynamicEmbInitializerArgs, DynamicEmbInitializerMode,
                                 DynamicEmbPoolingMode, DynamicEmbScoreStrategy, DynamicEmbTableOptions, EmbOptimType,
-                                convert_optimizer_type, get_constraint_capacity)
+                                convert_optimizer_type, get_constraint_capacity, aligned_capacity_per_rank, DistType,
+                                DynamicEmbDataType, DynamicEmbEvictStrategy, create_dynamicemb_table, dtype_to_bytes, dyn_emb_to_torch,
+                                get_optimizer_state_dim, next_power_of_2, torch_to_dyn_emb, validate_initializer_args)
 from .embedding import DynamicEmbeddingBagCollection, DynamicEmbeddingCollection
 from .hkv import EvictStrategy, HKVTable, HostDynamicTable, InitializerArgs, InitMode, OptimizerType
 from .key_value_table import DiskStorage, KeyValueTable, Storage, TableStorage
 from .planner import (DynamicEmbeddingBagCollectionSharder, DynamicEmbeddingCollectionSharder, DynamicEmbeddingEnumerator,
                       DynamicEmbeddingShardingPlanner, DynamicEmbParameterConstraints, DynamicEmbParameterSharding, ShardingOption)
 from .construct_twin_module import ConstructTwinModule, StaticTwin, generate_sparse_feature
+from .initializers import (BaseDynamicEmbInitializer, ConstantInitializer, DebugInitializer, NormalInitializer, TruncatedNormalInitializer,
+                           UniformInitializer, create_initializer)
+from .optimizers import (AdagradDynamicEmbeddingOptimizer, AdagradDynamicEmbeddingOptimizerV2, AdamDynamicEmbeddingOptimizer,
+                         AdamDynamicEmbeddingOptimizerV2, BaseDynamicEmbeddingOptimizer, BaseDynamicEmbeddingOptimizerV2, OptimizerArgs,
+                         RowWiseAdagradDynamicEmbeddingOptimizer, RowWiseAdagradDynamicEmbeddingOptimizerV2, SGDDynamicEmbeddingOptimizer,
+                         SGDDynamicEmbeddingOptimizerV2, create_optimizer, get_required_arg, string_to_opt_type)
 
 __version__ = "v25.09"          # the API level of the dynamic-embedding surface this package follows
 
 __all__ = [
+    "BaseDynamicEmbInitializer", "ConstantInitializer", "DebugInitializer", "NormalInitializer", "TruncatedNormalInitializer",
+    "UniformInitializer", "create_initializer", "AdagradDynamicEmbeddingOptimizer", "AdagradDynamicEmbeddingOptimizerV2",
+    "AdamDynamicEmbeddingOptimizer", "AdamDynamicEmbeddingOptimizerV2", "BaseDynamicEmbeddingOptimizer", "BaseDynamicEmbeddingOptimizerV2",
+    "OptimizerArgs", "RowWiseAdagradDynamicEmbeddingOptimizer", "RowWiseAdagradDynamicEmbeddingOptimizerV2", "SGDDynamicEmbeddingOptimizer",
+    "SGDDynamicEmbeddingOptimizerV2", "create_optimizer", "get_required_arg", "string_to_opt_type",
+    "aligned_capacity_per_rank", "DistType", "DynamicEmbDataType", "DynamicEmbEvictStrategy", "create_dynamicemb_table", "dtype_to_bytes",
+    "dyn_emb_to_torch", "get_optimizer_state_dim", "next_power_of_2", "torch_to_dyn_emb", "validate_initializer_args",
     "DynamicEmbeddingEnumerator", "ShardingOption", "ConstructTwinModule", "StaticTwin", "generate_sparse_feature",
     "BatchedDynamicEmbeddingTablesV2", "DynamicEmbDump", "DynamicEmbLoad", "get_score", "incremental_dump", "set_score",
     "DynamicEmbCheckMode", "DynamicEmbInitializerArgs", "DynamicEmbInitializerMode", "DynamicEmbPoolingMode",

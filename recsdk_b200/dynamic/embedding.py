@@ -20,7 +20,7 @@ from ..parallel.collective_embeddingbag import _AllToAll
 from ..parallel.comm import ShardingEnv
 from ..sparse.jagged_tensor import JaggedTensor, KeyedJaggedTensor, KeyedTensor
 from .batched_dynamicemb_table import BatchedDynamicEmbeddingTablesV2
-from .dynamicemb_config import DynamicEmbPoolingMode, DynamicEmbTableOptions, get_constraint_capacity
+from .dynamicemb_config import DynamicEmbPoolingMode, DynamicEmbTableOptions, aligned_capacity_per_rank
 from .hkv import OptimizerType
 
 
@@ -47,7 +47,7 @@ class _ShardedDynamicBase(nn.Module):
             o = options.get(t.name) or DynamicEmbTableOptions()
             o.dim = t.embedding_dim
             o.optimizer_type = optimizer_type
-            cap = get_constraint_capacity(t.num_embeddings, self.world, o.bucket_capacity)
+            cap = aligned_capacity_per_rank(t.num_embeddings, self.world, o.bucket_capacity)
             o.max_capacity = o.max_capacity or cap
             o.num_aligned_embedding_per_rank = cap
             if o.init_capacity is None:

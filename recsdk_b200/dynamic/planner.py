@@ -21,7 +21,7 @@ from ..modules.embedding_modules import EmbeddingBagCollection, EmbeddingCollect
 from ..parallel.comm import ShardingEnv
 from ..parallel.embeddingbag import ParameterSharding
 from ..parallel.planner import EmbeddingShardingPlanner, ParameterConstraints, ShardingPlan, Topology
-from .dynamicemb_config import DynamicEmbTableOptions, get_constraint_capacity
+from .dynamicemb_config import DynamicEmbTableOptions, aligned_capacity_per_rank
 from .embedding import DynamicEmbeddingBagCollection, DynamicEmbeddingCollection
 from .hkv import OptimizerType
 
@@ -97,7 +97,7 @@ class DynamicEmbeddingEnumerator:
         item = {"FP32": 4, "FP16": 2, "BF16": 2}[cfg.data_type.value]
         if cons is not None and getattr(cons, "use_dynamicemb", False):
             o = cons.dynamicemb_options
-            rows = get_constraint_capacity(cfg.num_embeddings, W, o.bucket_capacity)
+            rows = aligned_capacity_per_rank(cfg.num_embeddings, W, o.bucket_capacity)
             elems = cfg.embedding_dim + _OPT_STATE_ELEMS[self.optimizer_type](cfg.embedding_dim)
             return [ShardingOption(cfg.name, path, "row_wise", DYNAMICEMB_KERNEL, cfg.num_embeddings, cfg.embedding_dim, True, rows,
                                    rows * elems * 4)]
@@ -158,7 +158,7 @@ class DynamicEmbeddingShardingPlanner:
             if cfg is None:
                 raise KeyError("constraint for unknown table %r" % name)
             o = cons.dynamicemb_options
-            rows = get_constraint_capacity(cfg.num_embeddings, self.topology.world_size, o.bucket_capacity)
+            rows = aligned_capacity_per_rank(cfg.num_embeddings, self.topology.world_size, o.bucket_capacity)
             row_elems = cfg.embedding_dim + _OPT_STATE_ELEMS[self.optimizer_type](cfg.embedding_dim)
             need = rows * row_elems * 4
             hbm = need if not o.global_hbm_for_values else min(need, o.global_hbm_for_values // self.topology.world_size)

@@ -187,7 +187,7 @@ def test_keyed_tensor_from_list_and_regroup():
 def test_dynamic_config_helpers():
     from recsdk_b200.dynamic.dynamicemb_config import (DynamicEmbCheckMode, DynamicEmbInitializerArgs, DynamicEmbInitializerMode,
                                                        DynamicEmbTableOptions, EmbOptimType, convert_optimizer_type,
-                                                       get_constraint_capacity)
+                                                       aligned_capacity_per_rank)
     from recsdk_b200.dynamic import OptimizerType
 
     assert convert_optimizer_type(EmbOptimType.EXACT_ROWWISE_ADAGRAD) == OptimizerType.ROWWISE_ADAGRAD
@@ -196,9 +196,9 @@ def test_dynamic_config_helpers():
         with pytest.raises(ValueError):
             convert_optimizer_type(bad)
     assert int(DynamicEmbCheckMode.IGNORE) == 2
-    assert get_constraint_capacity(1000, 8) == 128                      # 125 rows per rank -> one bucket
-    assert get_constraint_capacity(1_000_000, 8) == 131072              # 125,000 -> next power of two
-    assert get_constraint_capacity(1025, 1) == 2048
+    assert aligned_capacity_per_rank(1000, 8) == 128                      # 125 rows per rank -> one bucket
+    assert aligned_capacity_per_rank(1_000_000, 8) == 131072              # 125,000 -> next power of two
+    assert aligned_capacity_per_rank(1025, 1) == 2048
     na = DynamicEmbInitializerArgs(mode=DynamicEmbInitializerMode.UNIFORM).to_native(num_embeddings_hint=10000, seed=5)
     assert math.isclose(na.upper, 0.01) and math.isclose(na.lower, -0.01) and na.seed == 5
     nb = DynamicEmbInitializerArgs(mode=DynamicEmbInitializerMode.UNIFORM, lower=-0.5).to_native()
