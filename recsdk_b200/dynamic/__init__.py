@@ -8,7 +8,8 @@ from .dynamicemb_config import (DynamicEmbCheckMode, DynamicEmbInitializerArgs, 
                                 get_optimizer_state_dim, next_power_of_2, torch_to_dyn_emb, validate_initializer_args)
 from .embedding import DynamicEmbeddingBagCollection, DynamicEmbeddingCollection
 from .hkv import EvictStrategy, HKVTable, HostDynamicTable, InitializerArgs, InitMode, OptimizerType
-from .key_value_table import DiskStorage, KeyValueTable, Storage, TableStorage
+from .key_value_table import (Cache, DiskStorage, KeyValueTable, KeyValueTableCachingFunction, KeyValueTableFunction, Storage, TableStorage,
+                              encode_checkpoint_file_path, encode_meta_json_file_path, find_files, update_cache)
 from .planner import (DynamicEmbeddingBagCollectionSharder, DynamicEmbeddingCollectionSharder, DynamicEmbeddingEnumerator,
                       DynamicEmbeddingShardingPlanner, DynamicEmbParameterConstraints, DynamicEmbParameterSharding, ShardingOption)
 from .construct_twin_module import ConstructTwinModule, StaticTwin, generate_sparse_feature
@@ -19,6 +20,11 @@ from .optimizers import (AdagradDynamicEmbeddingOptimizer, AdagradDynamicEmbeddi
                          RowWiseAdagradDynamicEmbeddingOptimizer, RowWiseAdagradDynamicEmbeddingOptimizerV2, SGDDynamicEmbeddingOptimizer,
                          SGDDynamicEmbeddingOptimizerV2, create_optimizer, get_required_arg, string_to_opt_type)
 
+# names of the reference's sharded modules and of its no-op fused optimizer handle (the update runs inside the backward)
+ShardedDynamicEmbeddingCollection = DynamicEmbeddingCollection
+ShardedDynamicEmbeddingBagCollection = DynamicEmbeddingBagCollection
+from ..optim import FusedOptimizerStub as DynamicEmbeddingFusedOptimizer  # noqa: E402
+
 __version__ = "v25.09"          # the API level of the dynamic-embedding surface this package follows
 
 __all__ = [
@@ -27,6 +33,8 @@ __all__ = [
     "AdamDynamicEmbeddingOptimizer", "AdamDynamicEmbeddingOptimizerV2", "BaseDynamicEmbeddingOptimizer", "BaseDynamicEmbeddingOptimizerV2",
     "OptimizerArgs", "RowWiseAdagradDynamicEmbeddingOptimizer", "RowWiseAdagradDynamicEmbeddingOptimizerV2", "SGDDynamicEmbeddingOptimizer",
     "SGDDynamicEmbeddingOptimizerV2", "create_optimizer", "get_required_arg", "string_to_opt_type",
+    "Cache", "KeyValueTableCachingFunction", "KeyValueTableFunction", "encode_checkpoint_file_path", "encode_meta_json_file_path", "find_files",
+    "update_cache", "ShardedDynamicEmbeddingCollection", "ShardedDynamicEmbeddingBagCollection", "DynamicEmbeddingFusedOptimizer",
     "aligned_capacity_per_rank", "DistType", "DynamicEmbDataType", "DynamicEmbEvictStrategy", "create_dynamicemb_table", "dtype_to_bytes",
     "dyn_emb_to_torch", "get_optimizer_state_dim", "next_power_of_2", "torch_to_dyn_emb", "validate_initializer_args",
     "DynamicEmbeddingEnumerator", "ShardingOption", "ConstructTwinModule", "StaticTwin", "generate_sparse_feature",

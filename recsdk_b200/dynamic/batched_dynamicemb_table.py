@@ -160,6 +160,18 @@ class BatchedDynamicEmbeddingTablesV2(nn.Module):
         """Tables that front a storage tier (their device table is the cache)."""
         return [t for t in self.tables if t.storage is not None]
 
+    @property
+    def optimizer(self):
+        """Row-level optimizer object with this module's current hyper-parameters (learning rate, eps, betas, weight decay,
+        iterations): the handle the reference exposes for exporting / restoring optimizer arguments."""
+        from .optimizers import OptimizerArgs, create_optimizer
+
+        t = self.tables[0]
+        opt = create_optimizer(t.optimizer, OptimizerArgs(learning_rate=t.lr, weight_decay=t.weight_decay, eps=t.eps, beta1=t.betas[0],
+                                                          beta2=t.betas[1], initial_accumulator_value=float(t._init.state_init)))
+        opt._iterations = int(t._step)
+        return opt
+
     def split_embedding_weights(self) -> List[torch.Tensor]:
         """One ``[live rows, dim]`` tensor per table (a snapshot: dynamic tables have no fixed weight matrix)."""
         return [self.export_keys_values(n)[1] for n in self.table_names]

@@ -49,6 +49,26 @@ class Storage(abc.ABC):
         return int(self.export_all()[0].numel())
 
 
+class Cache(abc.ABC):
+    """Contract of a device-side cache in front of a ``Storage`` (``dynamic_emb/distributed/types.py:152-227`` of the
+    reference): lookups report the keys they missed, inserts report what they evicted."""
+
+    @abc.abstractmethod
+    def find(self, unique_keys: torch.Tensor, unique_vals: torch.Tensor, founds: Optional[torch.Tensor] = None
+             ) -> Tuple[int, torch.Tensor, torch.Tensor]:
+        """Fill ``unique_vals`` rows of the resident keys -> (number missing, missing keys, their positions)."""
+
+    @abc.abstractmethod
+    def insert_and_evict(self, keys: torch.Tensor, values: torch.Tensor) -> Tuple[int, torch.Tensor, torch.Tensor, torch.Tensor]:
+        """-> (number evicted, evicted keys, evicted rows, evicted scores)."""
+
+    @abc.abstractmethod
+    def flush(self, storage: Optional[Storage] = None) -> None: ...
+
+    @abc.abstractmethod
+    def reset(self) -> None: ...
+
+
 class TableStorage(Storage):
     """Storage backed by another table object (host-resident ``HKVTable`` or ``HostDynamicTable``)."""
 
@@ -123,7 +143,7 @@ def file_names(save_dir: str, table: str, rank: int, world: int) -> Dict[str, st
     return {k: os.path.join(save_dir, "%s_emb_%s%s" % (table, k, sfx)) for k in ("keys", "values", "scores", "opt_values")}
 
 
-class KeyValueTable:
+class KeyValueTable(Cache):
     def __init__(self, name: str, options: DynamicEmbTableOptions, device: torch.device, lr: float = 0.01,
                  eps: float = 1e-8, betas=(0.9, 0.999), weight_decay: float = 0.0, seed: int = 0,
                  initial_accumulator_value: float = 0.0) -> None:
@@ -308,13 +328,14 @@ class KeyValueTable:
         self._step += 1
         self.table.update(slots, grads, self.lr, self.eps, self.betas[0], self.betas[1], self.weight_decay, self._step)
 
-    def flush(self) -> None:
-        """Write every cached row back to storage (before a dump)."""
-        if self.storage is None:
+    def flush(self, storage: Optional[Storage] = None) -> None:
+        """Write every cached row back to ``storage`` (default: this table's own storage tier; before a dump)."""
+        storage = storage if storage is not None else self.storage
+        if storage is None:
             return
         k, s, v, _ = self.table.export_batch()
         if k.numel():
-            self.storage.insert(k, v, s)
+            storage.insert(k, v, s)
 
     def size(self) -> int:
         return self.table.size() + (self.storage.size() if self.storage is not None else 0)
@@ -402,6 +423,248 @@ class KeyValueTable:
             total += int(k.numel())
         return total
 
+    # ------------------------------------------------------------------ key-addressed calls under the reference's names
+    # (``dynamic_emb/distributed/key_value_table.py:228-690``: find / insert / insert_and_evict / scores / shape queries)
+    def find(self, unique_keys: torch.Tensor, unique_vals: torch.Tensor, founds: Optional[torch.Tensor] = None
+             ) -> Tuple[int, torch.Tensor, torch.Tensor]:
+        """Rows ``[embedding | state]`` (as many columns as ``unique_vals`` has) of the resident keys are written into
+        ``unique_vals``; rows of absent keys are left as they are.  ``founds`` (bool, optional) receives the hit mask.
+        -> (number missing, missing keys, their positions in ``unique_keys``).  Nothing is inserted."""
+        slots, found = self.table.find(unique_keys, update_score=True, scores=self._scores_for(unique_keys.numel()))
+        cols = unique_vals.shape[1]
+        if cols:
+            rows = self.table.gather(slots, 0, cols)
+            unique_vals.copy_(torch.where(found[:, None], rows.to(unique_vals.dtype), unique_vals))
+        if founds is not None:
+            founds.copy_(found)
+        missing = ~found
+        idx = torch.nonzero(missing, as_tuple=True)[0]
+        return int(idx.numel()), unique_keys[missing], idx
+
+    def find_embeddings(self, unique_keys: torch.Tensor, unique_embs: torch.Tensor, founds: Optional[torch.Tensor] = None):
+        return self.find(unique_keys, unique_embs, founds)
+
+    def find_missed_keys(self, unique_keys: torch.Tensor, founds: Optional[torch.Tensor] = None):
+        return self.find(unique_keys, torch.empty(unique_keys.numel(), 0, device=unique_keys.device), founds)
+
+    def insert(self, keys: torch.Tensor, values: torch.Tensor, scores: Optional[torch.Tensor] = None) -> None:
+        """Insert or overwrite full rows (``values`` ``[n, <= row_dim]``); scores default to the table's current score."""
+        if scores is None:
+            scores = self._scores_for(keys.numel())
+        self.table.insert_and_evict(keys, values.float(), scores)
+
+    def insert_and_evict(self, keys: torch.Tensor, values: torch.Tensor) -> Tuple[int, torch.Tensor, torch.Tensor, torch.Tensor]:
+        _slots, _status, ev = self.table.insert_and_evict(keys, values.float(), self._scores_for(keys.numel()))
+        n = int(ev[3].item()) if ev is not None else 0
+        if self.record_metrics:
+            self.metrics["inserts"] += int(keys.numel())
+            self.metrics["evictions"] += n
+        if n == 0:
+            return 0, keys[:0], values[:0], torch.zeros(0, dtype=torch.int64, device=keys.device)
+        return n, ev[0][:n], ev[2][:n], ev[1][:n]
+
+    def update_by_keys(self, keys: torch.Tensor, grads: torch.Tensor, return_missing: bool = True):
+        """The reference's ``update(keys, grads)``: fused optimizer on the rows of the resident keys
+        -> (number missing, missing keys, their positions) or three Nones.  (``update`` here takes slots.)"""
+        slots, found = self.table.find(keys)
+        self.update(slots, grads)
+        if not return_missing:
+            return None, None, None
+        idx = torch.nonzero(~found, as_tuple=True)[0]
+        return int(idx.numel()), keys[~found], idx
+
+    def enable_update(self) -> bool:
+        return True
+
+    def set_score(self, score: int) -> None:
+        self.score_value = int(score)
+
+    score_update = False              # True while a lookup may refresh scores only (kept for API parity; unused here)
+
+    def update_timestamp(self) -> None:
+        self._timestamp = self.table.device_timestamp() if isinstance(self.table, HKVTable) else getattr(self.table, "_clock", 0)
+
+    def embedding_dtype(self) -> torch.dtype:
+        return self.options.embedding_dtype
+
+    def embedding_dim(self) -> int:
+        return self.dim
+
+    def value_dim(self) -> int:
+        return self.row_dim
+
+    def optim_state_dim(self) -> int:
+        return self.state_dim
+
+    def init_optimizer_state(self) -> float:
+        return float(self._init.state_init)
+
+    def key_type(self) -> torch.dtype:
+        return self.options.index_type
+
+    def value_type(self) -> torch.dtype:
+        return torch.float32
+
+    def capacity(self) -> int:
+        return int(self.options.max_capacity or getattr(self.table, "capacity", 0))
+
+    def evict_strategy(self) -> EvictStrategy:
+        return EvictStrategy(self.options.evict_strategy)
+
+    def reset(self) -> None:
+        """Drop every resident row (the storage tier, if any, is left alone)."""
+        self.table.clear()
+        if self.probation is not None:
+            self.probation.clear()
+
+    def cache_metrics(self) -> Optional[torch.Tensor]:
+        """[lookups, cache hits, inserts, evictions, storage hits] when recording is on, else None."""
+        if not self.record_metrics:
+            return None
+        m = self.metrics
+        return torch.tensor([m["lookups"], m["cache_hits"], m["inserts"], m["evictions"], m["storage_hits"]], dtype=torch.long)
+
+    def set_record_cache_metrics(self, record: bool) -> None:
+        self.record_metrics = bool(record)
+
+    def count_matched(self, threshold: int, num_matched: Optional[torch.Tensor] = None) -> int:
+        """Resident entries whose score is at least ``threshold`` (also written into ``num_matched[0]`` when given)."""
+        n = int(self.table.count_matched(int(threshold)))
+        if num_matched is not None:
+            num_matched.reshape(-1)[0] = n
+        return n
+
+    def export_batch_matched(self, threshold: int, batch_size: Optional[int] = None, search_offset: int = 0, d_count=None, d_keys=None,
+                             d_vals=None):
+        """Entries with score >= ``threshold`` among the slots ``[search_offset, search_offset + batch_size)``; written into
+        the given buffers when there are any -> (keys, scores, rows, slots)."""
+        k, sc, rows, slots = self.table.export_batch_matched(int(threshold), int(search_offset), batch_size)
+        n = int(k.numel())
+        if d_count is not None:
+            d_count.reshape(-1)[0] = n
+        if d_keys is not None and n:
+            d_keys[:n] = k.to(d_keys.device)
+        if d_vals is not None and n:
+            d_vals[:n, : rows.shape[1]] = rows.to(d_vals.device, d_vals.dtype)
+        return k, sc, rows, slots
+
     def take_touched(self) -> Optional[torch.Tensor]:
         t, self._touched = self._touched, None
         return t if t is None else t[t != -1]
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Stateless forms (``key_value_table.py:691-947`` of the reference): the lookup / update protocol of a storage alone and of
+# a cache in front of a storage, written over the two contracts above.
+# ----------------------------------------------------------------------------------------------------------------------
+def _storage_find(storage, keys: torch.Tensor, value_dim: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(rows, found) from either kind of lower tier: a ``Storage`` (``find(keys)``) or another key-value table (``find(keys, vals, founds)``)."""
+    if isinstance(storage, Cache):
+        vals = torch.zeros(keys.numel(), value_dim, device=keys.device)
+        found = torch.zeros(keys.numel(), dtype=torch.bool, device=keys.device)
+        storage.find(keys, vals, found)
+        return vals, found
+    return storage.find(keys)
+
+
+def update_cache(cache: Cache, storage: Storage, missing_keys: torch.Tensor, missing_values: torch.Tensor) -> None:
+    """Rows fetched from (or created in) the storage become resident; what the cache evicts for them goes back down."""
+    if missing_keys.numel() == 0:
+        return
+    n, ek, ev, es = cache.insert_and_evict(missing_keys, missing_values)
+    if n:
+        storage.insert(ek, ev, es)
+
+
+class KeyValueTableFunction:
+    """One table without a cache tier."""
+
+    @staticmethod
+    def lookup(storage: "KeyValueTable", unique_keys: torch.Tensor, unique_embs: torch.Tensor, training: bool = True,
+               initializer=None) -> None:
+        """Embeddings of ``unique_keys`` into ``unique_embs``; while training absent keys are created (drawn by the table's
+        own initialiser, or by ``initializer(buffer, indices, keys)`` when one is given), in evaluation they read as the
+        evaluation default."""
+        slots, rows = storage.lookup(unique_keys, training=training)
+        unique_embs.copy_(rows.to(unique_embs.dtype))
+        if training and initializer is not None:
+            n, _keys, idx = storage.find_missed_keys(unique_keys)
+            if n:
+                initializer(unique_embs, idx, unique_keys[idx])
+
+    @staticmethod
+    def update(storage: "KeyValueTable", unique_keys: torch.Tensor, unique_grads: torch.Tensor) -> None:
+        storage.update_by_keys(unique_keys, unique_grads, return_missing=False)
+
+
+class KeyValueTableCachingFunction:
+    """A cache table in front of a storage: hits are served by the cache, misses come up from the storage (or are created
+    there), evictions are written back."""
+
+    @staticmethod
+    def lookup(cache: "KeyValueTable", storage: Storage, unique_keys: torch.Tensor, unique_embs: torch.Tensor, training: bool = True
+               ) -> None:
+        dim = unique_embs.shape[1]
+        vals = torch.zeros(unique_keys.numel(), cache.value_dim(), device=unique_keys.device)
+        n, mk, idx = cache.find(unique_keys, vals)
+        if n:
+            rows, found = _storage_find(storage, mk, cache.value_dim())
+            rows = rows.to(vals.device).float()
+            if training and not bool(found.all()):
+                # new keys: the cache table draws them, then they are read back like any other row
+                slots, _st, _ev = cache.table.find_or_insert(mk[~found], cache._scores_for(int((~found).sum())))
+                rows[~found] = cache.table.gather(slots, 0, cache.value_dim())
+            vals[idx] = rows[:, : vals.shape[1]]
+            if training:
+                update_cache(cache, storage, mk, rows)
+        unique_embs.copy_(vals[:, :dim].to(unique_embs.dtype))
+
+    @staticmethod
+    def update(cache: "KeyValueTable", storage: Storage, unique_keys: torch.Tensor, unique_grads: torch.Tensor) -> None:
+        n, mk, idx = cache.update_by_keys(unique_keys, unique_grads)
+        if n and hasattr(storage, "update_by_keys"):
+            storage.update_by_keys(mk, unique_grads[idx], return_missing=False)
+
+    @staticmethod
+    def prefetch(cache: "KeyValueTable", storage: Storage, unique_keys: torch.Tensor) -> int:
+        """Bring the rows of ``unique_keys`` that the storage holds into the cache -> number of rows moved."""
+        n, mk, _idx = cache.find_missed_keys(unique_keys)
+        if not n:
+            return 0
+        rows, found = _storage_find(storage, mk, cache.value_dim())
+        if not bool(found.any()):
+            return 0
+        update_cache(cache, storage, mk[found], rows[found].to(mk.device).float())
+        return int(found.sum())
+
+
+def encode_meta_json_file_path(root_path: str, table_name: str) -> str:
+    return os.path.join(root_path, "%s_opt_args.json" % table_name)
+
+
+def encode_checkpoint_file_path(root_path: str, table_name: str, rank, world_size, item: str) -> str:
+    if item not in ("keys", "values", "scores", "opt_values"):
+        raise ValueError("Invalid item '%s'. Must be one of: keys, values, scores, opt_values" % item)
+    return os.path.join(root_path, "%s_emb_%s.rank_%s.world_size_%s" % (table_name, item, rank, world_size))
+
+
+def find_files(root_path: str, table_name: str, suffix: str) -> Tuple[List[str], int]:
+    """Checkpoint files of one kind (``emb_keys`` / ``emb_values`` / ``emb_scores`` / ``opt_values``) of a table, sorted by
+    rank -> (paths, world size they were written with)."""
+    import glob
+    import re
+
+    item = {"emb_keys": "keys", "emb_values": "values", "emb_scores": "scores", "opt_values": "opt_values"}.get(suffix)
+    if item is None:
+        raise RuntimeError("Invalid suffix: %s" % suffix)
+    rx = re.compile(r"\.rank_(\d+)\.world_size_(\d+)$")
+    hits = []
+    for f in glob.glob(encode_checkpoint_file_path(root_path, table_name, "*", "*", item)):
+        m = rx.search(f)
+        if m:
+            hits.append((int(m.group(1)), int(m.group(2)), f))
+    hits.sort()
+    worlds = {w for _r, w, _f in hits}
+    if len(worlds) > 1:
+        raise RuntimeError("files of table %s were written with different world sizes: %s" % (table_name, sorted(worlds)))
+    return [f for _r, _w, f in hits], (worlds.pop() if worlds else 0)

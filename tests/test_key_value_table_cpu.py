@@ -125,3 +125,109 @@ def test_custom_storage_only_needs_find_insert_export():
     _, rows = kv.lookup(_t(42, 43))
     assert rows[0].tolist() == [0.0, 1.0, 2.0, 3.0] and rows[1].tolist() == [1.0] * 4
     assert kv.table.rows[42].tolist() == list(range(8))                      # the full row, state included
+
+
+def test_key_addressed_calls_with_the_reference_names():
+    from recsdk_b200.dynamic import Cache, EvictStrategy
+
+    kv = KeyValueTable("t", _opts(), CPU, lr=0.5)
+    assert isinstance(kv, Cache)
+    assert (kv.embedding_dim(), kv.value_dim(), kv.optim_state_dim(), kv.capacity()) == (4, 8, 4, 128)
+    assert kv.embedding_dtype() == torch.float32 and kv.key_type() == torch.int64 and kv.value_type() == torch.float32
+    assert kv.evict_strategy() == EvictStrategy.CUSTOMIZED and kv.enable_update() and kv.init_optimizer_state() == 0.0
+    kv.set_score(7)
+    kv.insert(_t(1, 2), torch.arange(16.0).view(2, 8))
+    assert kv.table.score[1] == 7 and kv.table.rows[2].tolist() == list(range(8, 16))
+    vals = torch.full((3, 8), -1.0)
+    founds = torch.zeros(3, dtype=torch.bool)
+    n, mk, idx = kv.find(_t(2, 5, 1), vals, founds)
+    assert (n, mk.tolist(), idx.tolist(), founds.tolist()) == (1, [5], [1], [True, False, True])
+    assert vals[0].tolist() == list(range(8, 16)) and vals[1].tolist() == [-1.0] * 8 and kv.table.size() == 2      # nothing inserted
+    embs = torch.zeros(2, 4)
+    assert kv.find_embeddings(_t(1, 9), embs)[0] == 1 and embs[0].tolist() == [0.0, 1.0, 2.0, 3.0]
+    assert kv.find_missed_keys(_t(1, 2))[0] == 0
+    n, mk, idx = kv.update_by_keys(_t(1, 6), torch.ones(2, 4))
+    assert (n, mk.tolist(), idx.tolist()) == (1, [6], [1]) and kv.table.rows[1][4] == 5.0 and kv.update_by_keys(_t(1), torch.ones(1, 4), False) == (None,) * 3
+    assert kv.count_matched(7) == 2 and kv.count_matched(8) == 0
+    cnt = torch.zeros(1, dtype=torch.long)
+    kv.count_matched(1, cnt)
+    assert int(cnt) == 2
+    dk, dv, dc = torch.zeros(4, dtype=torch.long), torch.zeros(4, 8), torch.zeros(1, dtype=torch.long)
+    k, sc, rows, _ = kv.export_batch_matched(7, None, 0, dc, dk, dv)
+    assert int(dc) == 2 and sorted(dk[:2].tolist()) == [1, 2] and sorted(k.tolist()) == [1, 2] and dv[:2].abs().sum() > 0
+    kv.set_record_cache_metrics(True)
+    assert kv.cache_metrics().tolist() == [0, 0, 0, 0, 0]
+    small = KeyValueTable("s", _opts(max_capacity=16, init_capacity=16, bucket_capacity=16), CPU)
+    small.table.capacity = 2
+    small.set_record_cache_metrics(True)
+    small.insert(_t(1, 2), torch.ones(2, 8))
+    small.set_score(9)
+    n, ek, ev, es = small.insert_and_evict(_t(3), torch.full((1, 8), 3.0))
+    assert n == 1 and ek.numel() == 1 and ev.shape == (1, 8) and es.tolist() == [1] and small.cache_metrics()[3] == 1
+    assert small.insert_and_evict(_t(3), torch.full((1, 8), 4.0))[0] == 0
+    kv.update_timestamp()
+    kv.reset()
+    assert kv.table.size() == 0 and KeyValueTable("m", _opts(), CPU).cache_metrics() is None
+
+
+def test_stateless_lookup_and_update_protocols(tmp_path):
+    from recsdk_b200.dynamic import (KeyValueTableCachingFunction, KeyValueTableFunction, encode_checkpoint_file_path,
+                                     encode_meta_json_file_path, find_files, update_cache)
+
+    plain = KeyValueTable("p", _opts(), CPU, lr=0.5)
+    out = torch.zeros(2, 4)
+    KeyValueTableFunction.lookup(plain, _t(1, 2), out)
+    assert out.tolist() == [[1.0] * 4] * 2 and plain.table.size() == 2
+    ev = torch.full((1, 4), 5.0)
+    KeyValueTableFunction.lookup(plain, _t(3), ev, training=False)
+    assert ev.tolist() == [[0.0] * 4] and plain.table.size() == 2          # evaluation creates nothing
+    KeyValueTableFunction.update(plain, _t(1), torch.ones(1, 4))
+    assert plain.table.rows[1][0] == 0.5
+    marked = torch.zeros(1, 4)
+    KeyValueTableFunction.lookup(plain, _t(50), marked, initializer=lambda buf, idx, keys: buf.__setitem__(idx, 42.0))
+    assert plain.table.size() == 3 and marked.tolist() == [[1.0] * 4]      # the key was created by the table before the check
+    # a two-row cache in front of a storage table
+    cache = KeyValueTable("c", _opts(max_capacity=16, init_capacity=16, bucket_capacity=16), CPU, lr=0.5)
+    cache.table.capacity = 2
+    store = KeyValueTable("s", _opts(), CPU, lr=0.5)
+    store.insert(_t(7), torch.arange(8.0)[None])
+    embs = torch.zeros(3, 4)
+    KeyValueTableCachingFunction.lookup(cache, store, _t(7, 8, 9), embs)
+    assert embs[0].tolist() == [0.0, 1.0, 2.0, 3.0] and embs[1].tolist() == [1.0] * 4     # 7 came up from storage, 8 and 9 are new
+    assert cache.table.size() == 2 and store.table.size() >= 2                # the two-row cache spilled into the storage
+    KeyValueTableCachingFunction.update(cache, store, _t(7, 8, 9), torch.ones(3, 4))
+    total = {}
+    for t in (store.table, cache.table):
+        total.update({k: v.copy() for k, v in t.rows.items()})
+    assert all(total[k][4] == 1.0 for k in (8, 9)) and total[7][4] == 5.0    # every key got its update, in whichever tier it lives
+    moved = KeyValueTableCachingFunction.prefetch(cache, store, _t(*[k for k in (7, 8, 9) if k not in cache.table.rows]))
+    assert moved >= 1 and KeyValueTableCachingFunction.prefetch(cache, store, _t(1000)) == 0
+    update_cache(cache, store, _t(), torch.zeros(0, 8))                        # nothing to do
+    # file names
+    assert encode_meta_json_file_path("/c", "items") == "/c/items_opt_args.json"
+    assert encode_checkpoint_file_path("/c", "items", 1, 4, "scores") == "/c/items_emb_scores.rank_1.world_size_4"
+    try:
+        encode_checkpoint_file_path("/c", "items", 1, 4, "weights")
+        raise AssertionError("an unknown item must be refused")
+    except ValueError:
+        pass
+    plain.dump(str(tmp_path), 0, 2)
+    plain.dump(str(tmp_path), 1, 2)
+    files, world = find_files(str(tmp_path), "p", "emb_keys")
+    assert world == 2 and [f.rsplit("/", 1)[1] for f in files] == ["p_emb_keys.rank_0.world_size_2", "p_emb_keys.rank_1.world_size_2"]
+    assert find_files(str(tmp_path), "absent", "opt_values") == ([], 0)
+    try:
+        find_files(str(tmp_path), "p", "emb_weights")
+        raise AssertionError("an unknown suffix must be refused")
+    except RuntimeError:
+        pass
+
+
+def test_module_level_aliases_and_optimizer_handle():
+    from recsdk_b200.dynamic import (BatchedDynamicEmbeddingTablesV2, DynamicEmbeddingBagCollection, DynamicEmbeddingCollection,
+                                     DynamicEmbeddingFusedOptimizer, ShardedDynamicEmbeddingBagCollection, ShardedDynamicEmbeddingCollection)
+    from recsdk_b200.optim import FusedOptimizerStub
+
+    assert ShardedDynamicEmbeddingCollection is DynamicEmbeddingCollection and ShardedDynamicEmbeddingBagCollection is DynamicEmbeddingBagCollection
+    assert DynamicEmbeddingFusedOptimizer is FusedOptimizerStub
+    assert isinstance(getattr(BatchedDynamicEmbeddingTablesV2, "optimizer"), property)
