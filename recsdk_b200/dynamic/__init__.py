@@ -1,6 +1,8 @@
 """Dynamic (hash-table backed) embeddings: the ``dynamic_emb`` API surface on the GPU hash table."""
-from .batched_dynamicemb_table import BatchedDynamicEmbeddingTablesV2
-from .dump_load import DynamicEmbDump, DynamicEmbLoad, get_score, incremental_dump, set_score
+from .batched_dynamicemb_table import (BatchedDynamicEmbeddingTablesV2, DynamicEmbeddingBagFunction, DynamicEmbeddingFunctionV2,
+                                       dynamicemb_prefetch)
+from .dump_load import (DynamicEmbDump, DynamicEmbLoad, check_emb_collection_modules, find_dynamic_modules, find_sharded_modules,
+                        get_dynamic_emb_module, get_score, incremental_dump, set_score)
 from .dynamicemb_config import (DynamicEmbCheckMode, DynamicEmbInitializerArgs, DynamicEmbInitializerMode,
                                 DynamicEmbPoolingMode, DynamicEmbScoreStrategy, DynamicEmbTableOptions, EmbOptimType,
                                 convert_optimizer_type, get_constraint_capacity, aligned_capacity_per_rank, DistType,
@@ -33,7 +35,8 @@ __all__ = [
     "AdamDynamicEmbeddingOptimizer", "AdamDynamicEmbeddingOptimizerV2", "BaseDynamicEmbeddingOptimizer", "BaseDynamicEmbeddingOptimizerV2",
     "OptimizerArgs", "RowWiseAdagradDynamicEmbeddingOptimizer", "RowWiseAdagradDynamicEmbeddingOptimizerV2", "SGDDynamicEmbeddingOptimizer",
     "SGDDynamicEmbeddingOptimizerV2", "create_optimizer", "get_required_arg", "string_to_opt_type",
-    "Cache", "KeyValueTableCachingFunction", "KeyValueTableFunction", "encode_checkpoint_file_path", "encode_meta_json_file_path", "find_files",
+    "DynamicEmbeddingBagFunction", "DynamicEmbeddingFunctionV2", "dynamicemb_prefetch", "check_emb_collection_modules", "find_dynamic_modules",
+    "find_sharded_modules", "get_dynamic_emb_module", "Cache", "KeyValueTableCachingFunction", "KeyValueTableFunction", "encode_checkpoint_file_path", "encode_meta_json_file_path", "find_files",
     "update_cache", "ShardedDynamicEmbeddingCollection", "ShardedDynamicEmbeddingBagCollection", "DynamicEmbeddingFusedOptimizer",
     "aligned_capacity_per_rank", "DistType", "DynamicEmbDataType", "DynamicEmbEvictStrategy", "create_dynamicemb_table", "dtype_to_bytes",
     "dyn_emb_to_torch", "get_optimizer_state_dim", "next_power_of_2", "torch_to_dyn_emb", "validate_initializer_args",

@@ -127,6 +127,16 @@ class _DynamicPooledLookupFn(torch.autograd.Function):
         return (None,) * 8
 
 
+# the reference's names of the two autograd functions (``batched_dynamicemb_function.py:53-213`` pooled, ``:342-432`` sequence)
+DynamicEmbeddingFunctionV2 = _DynamicLookupFn
+DynamicEmbeddingBagFunction = _DynamicPooledLookupFn
+
+
+def dynamicemb_prefetch(module: "BatchedDynamicEmbeddingTablesV2", indices: torch.Tensor, offsets: torch.Tensor, forward_stream=None) -> None:
+    """Function form of ``module.prefetch`` (``batched_dynamicemb_function.py:284-325`` of the reference)."""
+    module.prefetch(indices, offsets, forward_stream)
+
+
 class BatchedDynamicEmbeddingTablesV2(nn.Module):
     def __init__(self, table_options: List[DynamicEmbTableOptions], table_names: List[str],
                  pooling_mode: DynamicEmbPoolingMode = DynamicEmbPoolingMode.NONE,

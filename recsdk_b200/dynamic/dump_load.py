@@ -19,6 +19,32 @@ def find_dynamic_modules(model: nn.Module) -> Dict[str, _ShardedDynamicBase]:
     return {path: m for path, m in model.named_modules() if isinstance(m, _ShardedDynamicBase)}
 
 
+def find_sharded_modules(module: nn.Module, path: str = "") -> List[Tuple[str, str, nn.Module]]:
+    """(path, name, module) of every sharded dynamic collection, paths rooted at ``"model"`` as in the reference's dump
+    layout (``dynamic_emb/distributed/dump_load.py:39-55``)."""
+    if not isinstance(module, nn.Module):
+        raise ValueError("param `module` must be an instance of torch.nn.Module, but got:%s" % type(module))
+    root = path + "model"
+    out = []
+    for p, m in module.named_modules():
+        if isinstance(m, _ShardedDynamicBase):
+            out.append((root + ("." + p if p else ""), p.rsplit(".", 1)[-1] if p else "model", m))
+    return out
+
+
+def get_dynamic_emb_module(model: nn.Module) -> List[nn.Module]:
+    """The batched table modules (``BatchedDynamicEmbeddingTablesV2``) below ``model`` (``dump_load.py:84-89``)."""
+    if not isinstance(model, nn.Module):
+        raise ValueError("param `model` must be an instance of torch.nn.Module, but got:%s" % type(model))
+    from .batched_dynamicemb_table import BatchedDynamicEmbeddingTablesV2
+
+    return [m for m in model.modules() if isinstance(m, BatchedDynamicEmbeddingTablesV2)]
+
+
+def check_emb_collection_modules(module: nn.Module, ret_list: List[nn.Module]) -> None:
+    ret_list.extend(get_dynamic_emb_module(module))
+
+
 def _barrier(pg) -> None:
     if dist.is_available() and dist.is_initialized():
         dist.barrier(group=pg)

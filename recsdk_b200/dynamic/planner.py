@@ -52,6 +52,11 @@ class DynamicEmbParameterSharding(ParameterSharding):
     aligned_rows_per_rank: int = 0
     hbm_bytes_per_rank: int = 0
 
+    def get_additional_fused_params(self) -> dict:
+        """The fields this class adds to ``ParameterSharding`` (handed to the compute kernel as fused parameters)."""
+        base = {f.name for f in dataclasses.fields(ParameterSharding)}
+        return {f.name: getattr(self, f.name) for f in dataclasses.fields(self) if f.name not in base}
+
 
 _OPT_STATE_ELEMS = {OptimizerType.SGD: lambda d: 0, OptimizerType.ADAGRAD: lambda d: d, OptimizerType.ADAM: lambda d: 2 * d,
                     OptimizerType.ROWWISE_ADAGRAD: lambda d: 4}

@@ -43,3 +43,41 @@ def test_planner_rewrites_and_dmp_shards():
         loss = dmp(kjt)
         loss.backward()
     assert float(dmp(kjt)) != first                      # rows are trained inside backward
+
+
+def test_module_finders_and_fused_params():
+    """``find_sharded_modules`` / ``get_dynamic_emb_module`` (``dump_load.py:39-89`` of the reference) and the extra fields a
+    dynamic plan entry hands to the compute kernel."""
+    import pytest
+    import torch
+
+    from recsdk_b200.dynamic import (BatchedDynamicEmbeddingTablesV2, DynamicEmbeddingCollection, DynamicEmbTableOptions, OptimizerType,
+                                     check_emb_collection_modules, find_sharded_modules, get_dynamic_emb_module)
+    from recsdk_b200.dynamic.planner import DynamicEmbParameterSharding
+    from recsdk_b200.modules import EmbeddingConfig
+    from recsdk_b200.parallel import ShardingEnv
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            cfg = [EmbeddingConfig(num_embeddings=1000, embedding_dim=8, name="t", feature_names=["f"])]
+            self.tower = torch.nn.Module()
+            self.tower.emb = DynamicEmbeddingCollection(cfg, {"t": DynamicEmbTableOptions()}, ShardingEnv(1, 0), torch.device("cpu"),
+                                                        optimizer_type=OptimizerType.SGD)
+            self.dense = torch.nn.Linear(8, 1)
+
+    net = Net()
+    found = find_sharded_modules(net)
+    assert [(p, n) for p, n, _m in found] == [("model.tower.emb", "emb")] and found[0][2] is net.tower.emb
+    mods = get_dynamic_emb_module(net)
+    assert len(mods) == 1 and isinstance(mods[0], BatchedDynamicEmbeddingTablesV2)
+    again = []
+    check_emb_collection_modules(net, again)
+    assert again == mods and mods[0].table_names == ["t"] and len(mods[0].tables) == 1
+    assert mods[0].optimizer.get_opt_args()["opt_type"] == "sgd"
+    for fn in (find_sharded_modules, get_dynamic_emb_module):
+        with pytest.raises(ValueError):
+            fn("not a module")
+    extra = DynamicEmbParameterSharding("row_wise", aligned_rows_per_rank=128).get_additional_fused_params()
+    assert sorted(extra) == ["aligned_rows_per_rank", "customized_compute_kernel", "dist_type", "dynamicemb_options", "hbm_bytes_per_rank"]
+    assert extra["dist_type"] == "roundrobin" and extra["customized_compute_kernel"] == "DynamicEmb"
