@@ -2,13 +2,15 @@
 from .comm import PeerGroup, ShardingEnv
 from .embeddingbag import ParameterSharding, ShardedEmbeddingBagCollection
 from .collective_embeddingbag import CollectiveShardedEmbeddingBagCollection
-from .hybrid import (HybridEmbeddingBagCollectionSharder, HybridHashEmbeddingBagCollectionSharder, HybridTrainPipelineSparseDist,
-                     get_default_hybrid_sharders)
+from .hybrid import (HybridEmbeddingBagCollectionSharder, HybridHashEmbeddingBagCollectionSharder, HybridPipelineContext,
+                     HybridShardedEmbeddingBagCollection, HybridShardedHashEmbeddingBagCollection, HybridStage, HybridTrainPipelineContext,
+                     HybridTrainPipelineSparseDist, TaskType, get_default_hybrid_sharders)
 from .model_parallel import DistributedModelParallel
 from .planner import EmbeddingShardingPlanner, ParameterConstraints, ShardingPlan, Topology
 from .train_pipeline import TrainPipelineBase, TrainPipelineSparseDist
 
 __all__ = ["PeerGroup", "ShardingEnv", "ParameterSharding", "ShardedEmbeddingBagCollection", "CollectiveShardedEmbeddingBagCollection",
            "HybridEmbeddingBagCollectionSharder", "HybridHashEmbeddingBagCollectionSharder", "HybridTrainPipelineSparseDist",
-           "get_default_hybrid_sharders", "DistributedModelParallel", "EmbeddingShardingPlanner", "ParameterConstraints", "ShardingPlan",
+           "HybridPipelineContext", "HybridShardedEmbeddingBagCollection", "HybridShardedHashEmbeddingBagCollection", "HybridStage",
+           "HybridTrainPipelineContext", "TaskType", "get_default_hybrid_sharders", "DistributedModelParallel", "EmbeddingShardingPlanner", "ParameterConstraints", "ShardingPlan",
            "Topology", "TrainPipelineBase", "TrainPipelineSparseDist"]

@@ -49,6 +49,10 @@ class HybridEmbeddingBagCollectionSharder:
     def handles(self, module, params: Dict[str, ParameterSharding]) -> bool:
         return isinstance(module, HashEmbeddingBagCollection) == self.hashed
 
+    def shardable_parameters(self, module) -> Dict[str, torch.nn.Parameter]:
+        """Table name -> weight of every table of the collection (what a planner may place)."""
+        return {c.name: module.embedding_bags[c.name].weight for c in module.embedding_bag_configs()}
+
     def shard(self, module, params: Dict[str, ParameterSharding], env: ShardingEnv, device=None):
         from .model_parallel import _optimizer_spec_from_params
 
@@ -63,6 +67,17 @@ class HybridEmbeddingBagCollectionSharder:
 class HybridHashEmbeddingBagCollectionSharder(HybridEmbeddingBagCollectionSharder):
     module_type = HashEmbeddingBagCollection
     hashed = True
+
+
+# names of the reference's sharded modules (``hybrid_torchrec/distributed/embeddingbag.py:93``, ``hash_embeddingbag.py:39``): one
+# class serves both here, the hash variant is the same module built with ``hashed=True``
+HybridShardedEmbeddingBagCollection = CollectiveShardedEmbeddingBagCollection
+
+
+class HybridShardedHashEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollection):
+    def __init__(self, *args, **kwargs) -> None:
+        kwargs["hashed"] = True
+        super().__init__(*args, **kwargs)
 
 
 def get_default_hybrid_sharders(host_env: ShardingEnv) -> List[Any]:
@@ -267,3 +282,8 @@ class HybridTrainPipelineSparseDist(TrainPipelineBase):
     def in_flight(self) -> int:
         """Batches read from the dataloader and not trained on yet."""
         return sum(1 for line in self._lines for c in line if c.host_batch is not None)
+
+
+# the reference's names for the stage enumeration and the per-batch context (``hybrid_train_pipeline.py:58-70``, ``:73-120``)
+TaskType = HybridStage
+HybridTrainPipelineContext = HybridPipelineContext

@@ -40,6 +40,8 @@ class _SideTensorKJT(KeyedJaggedTensor):
         out = self.__class__.__new__(self.__class__)
         out.__dict__.update(base.__dict__)
         out._init_side(**side)
+        if hasattr(self, "_unique_offset_host"):          # a host-side copy that travels with whole-batch side tensors
+            out._unique_offset_host = self._unique_offset_host
         return out
 
     def to(self, device: torch.device, non_blocking: bool = False):
@@ -214,18 +216,34 @@ class _SideTensorKJT(KeyedJaggedTensor):
 
 class KeyedJaggedTensorWithLookHelper(_SideTensorKJT):
     PER_VALUE = ("hash_indices", "unique_inverse")
-    WHOLE = ("unique_indices", "unique_offset")
+    WHOLE = ("unique_indices", "unique_offset", "unique_ids")
 
     def __init__(self, keys, values, weights=None, lengths=None, offsets=None, stride=None, length_per_key=None, offset_per_key=None,
-                 hash_indices=None, unique_indices=None, unique_offset=None, unique_inverse=None) -> None:
+                 hash_indices=None, unique_indices=None, unique_offset=None, unique_inverse=None, unique_ids=None,
+                 unique_offset_host=None) -> None:
         super().__init__(keys, values, weights, lengths, offsets, stride, length_per_key, offset_per_key)
-        self._init_side(hash_indices=hash_indices, unique_indices=unique_indices, unique_offset=unique_offset, unique_inverse=unique_inverse)
+        self._init_side(hash_indices=hash_indices, unique_indices=unique_indices, unique_offset=unique_offset, unique_inverse=unique_inverse,
+                        unique_ids=unique_ids)
+        self._unique_offset_host = None if unique_offset_host is None else list(unique_offset_host)
 
     @staticmethod
-    def from_kjt(kjt: KeyedJaggedTensor, hash_indices=None, unique_indices=None, unique_offset=None, unique_inverse=None):
+    def from_kjt(kjt: KeyedJaggedTensor, hash_indices=None, unique_indices=None, unique_offset=None, unique_inverse=None, unique_ids=None,
+                 unique_offset_host=None):
         return KeyedJaggedTensorWithLookHelper(kjt.keys(), kjt.values(), kjt.weights_or_none(), kjt.lengths_or_none(), kjt.offsets_or_none(),
                                                kjt.stride(), hash_indices=hash_indices, unique_indices=unique_indices,
-                                               unique_offset=unique_offset, unique_inverse=unique_inverse)
+                                               unique_offset=unique_offset, unique_inverse=unique_inverse, unique_ids=unique_ids,
+                                               unique_offset_host=unique_offset_host)
+
+    unique_ids = property(lambda self: self._unique_ids)
+
+    @property
+    def unique_offset_host(self):
+        """Per-table offsets of the unique list as a host list: the copy given at construction, else read from the tensor
+        (a device-to-host copy when it lives on the GPU)."""
+        host_copy = getattr(self, "_unique_offset_host", None)
+        if host_copy is not None:
+            return host_copy
+        return None if self._unique_offset is None else self._unique_offset.cpu().tolist()
 
     hash_indices = property(lambda self: self._hash_indices)
     unique_indices = property(lambda self: self._unique_indices)
