@@ -57,3 +57,29 @@ def bind_rank_from_env(min_cores: int = 2) -> Optional[List[int]]:
     if len(usable) // lws < min_cores:
         return None
     return bind_current_process(cores_for_rank(lr, lws, usable))
+
+
+def get_available_cpu_num_and_range():
+    """-> (number of usable cores, [(first, last) core of every physical package that holds usable cores]); the package of a
+    core is read from sysfs, all cores count as one package when that is not available
+    (``perf_factory/bind_cpu.py:13-56`` of the reference)."""
+    usable = sorted(os.sched_getaffinity(0))
+    groups = {}
+    for c in usable:
+        try:
+            with open("/sys/devices/system/cpu/cpu%d/topology/physical_package_id" % c) as f:
+                pkg = int(f.read().strip())
+        except (OSError, ValueError):
+            pkg = 0
+        groups.setdefault(pkg, []).append(c)
+    return len(usable), [(min(v), max(v)) for _k, v in sorted(groups.items())]
+
+
+def bind_cpu_task() -> Optional[List[int]]:
+    """Bind the calling process to its local rank's share of the usable cores (``LOCAL_RANK`` / ``LOCAL_WORLD_SIZE`` or the
+    Open MPI equivalents); nothing happens for a single local rank.  -> the cores bound to, or None."""
+    lws = int(os.environ.get("LOCAL_WORLD_SIZE", os.environ.get("OMPI_COMM_WORLD_LOCAL_SIZE", "1")))
+    lr = int(os.environ.get("LOCAL_RANK", os.environ.get("OMPI_COMM_WORLD_LOCAL_RANK", "0")))
+    if lws <= 1 or not (0 <= lr < lws):
+        return None
+    return bind_current_process(cores_for_rank(lr, lws))

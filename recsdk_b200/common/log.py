@@ -37,5 +37,47 @@ class LoggingProxy:
     def __getattr__(self, item):
         return getattr(self._logger, item)
 
+    # -- the reference's class-level form: ``LoggingProxy.set_instance("INFO"); LoggingProxy.error("...")`` -------------
+    _instance = None
+
+    @classmethod
+    def set_instance(cls, log_level: str = "INFO") -> None:
+        level = str(log_level).upper()
+        if level not in ("DEBUG", "INFO", "WARNING", "ERROR", "CRITICAL"):
+            raise ValueError("log level is not valid, only DEBUG / INFO / WARNING / ERROR / CRITICAL are allowed, but got %s" % log_level)
+        proxy = cls("recsdk_b200")
+        proxy.set_level(level)
+        cls._instance = proxy._logger
+
+
+def _class_level(name: str, **fixed):
+    def call(cls, msg, *args, **kwargs):
+        if cls._instance is None:
+            cls.set_instance(logging.getLevelName(_level_from_env()))
+        for k, v in fixed.items():
+            kwargs.setdefault(k, v)
+        getattr(cls._instance, name)(msg, *args, **kwargs)
+    return call
+
+
+class _ClassOrInstance:
+    """``LoggingProxy.info(...)`` on the class goes to the shared logger, ``proxy.info(...)`` on an object to that object's."""
+
+    def __init__(self, name: str, method: str, **fixed) -> None:
+        self.name, self.method, self.fixed = name, method, fixed
+
+    def __get__(self, obj, cls):
+        if obj is None:
+            return _class_level(self.method, **self.fixed).__get__(cls, type(cls))
+        target = getattr(obj._logger, self.method)
+        if not self.fixed:
+            return target
+        return lambda msg, *a, **k: target(msg, *a, **{**self.fixed, **k})
+
+
+for _n, _m, _kw in (("info", "info", {}), ("debug", "debug", {}), ("error", "error", {}), ("warning", "warning", {}),
+                    ("critical", "critical", {}), ("exception", "error", {"exc_info": True})):
+    setattr(LoggingProxy, _n, _ClassOrInstance(_n, _m, **_kw))
+
 
 logger = LoggingProxy()

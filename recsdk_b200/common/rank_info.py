@@ -58,3 +58,70 @@ def rank_info_from_table(path: str, rank: int) -> RankInfo:
             first = min(rr for rr, _d, h, _l in entries if h == host)
             return RankInfo(rank, len(entries), rank - first, lws, dev, host)
     raise KeyError("rank %d not in the rank table" % rank)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Getter functions under the reference's names (``communication/hccl/hccl_info.py:40-111``, ``hccl_mgmt.py``).  The launcher's
+# variables are read in this order: torchrun's (``RANK`` / ``WORLD_SIZE`` / ``LOCAL_WORLD_SIZE``), then Open MPI's.
+# ----------------------------------------------------------------------------------------------------------------------
+def _env_int(names, what: str, at_least: int) -> int:
+    for n in names:
+        v = os.environ.get(n)
+        if v is not None:
+            if not v.strip().lstrip("+").isdigit():
+                raise ValueError("the value should be number, but got the value: %s" % v)
+            if int(v) < at_least:
+                raise ValueError("the value must be greater than or equal to %d, but got %s" % (at_least, v))
+            return int(v)
+    raise RuntimeError("Environment variable %s has not been exported, please launch with torchrun or mpirun first" % what)
+
+
+def get_rank_id() -> int:
+    return _env_int(("RANK", "OMPI_COMM_WORLD_RANK"), "RANK", 0)
+
+
+def get_rank_size() -> int:
+    return _env_int(("WORLD_SIZE", "OMPI_COMM_WORLD_SIZE"), "WORLD_SIZE", 1)
+
+
+def get_local_rank_size() -> int:
+    return _env_int(("LOCAL_WORLD_SIZE", "OMPI_COMM_WORLD_LOCAL_SIZE"), "LOCAL_WORLD_SIZE", 1)
+
+
+def get_rank_to_device_dict() -> Dict[int, int]:
+    """rank -> device id: from the rank table named by ``RANK_TABLE_FILE`` when set, else local rank ``i`` -> the ``i``-th
+    entry of ``CUDA_VISIBLE_DEVICES`` (or ``i`` itself)."""
+    path = os.environ.get("RANK_TABLE_FILE", "")
+    if path:
+        with open(path) as f:
+            table = json.load(f)
+        out: Dict[int, int] = {}
+        for srv in table.get("server_list", []):
+            for d in srv.get("device", []):
+                if not str(d.get("rank_id", "")).isdigit():
+                    raise ValueError("rank table: rank_id wrong")
+                out[int(d["rank_id"])] = int(d["device_id"])
+        if not out:
+            raise ValueError("rank table holds no device")
+        return out
+    n = get_local_rank_size()
+    vis = [x for x in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if x.strip().isdigit()]
+    return {i: (int(vis[i]) if i < len(vis) else i) for i in range(n)}
+
+
+def get_device_id() -> int:
+    d = get_rank_to_device_dict()
+    dev = d.get(get_rank_id() % get_local_rank_size() if not os.environ.get("RANK_TABLE_FILE") else get_rank_id())
+    if dev is None:
+        raise RuntimeError("no device is assigned to rank %d" % get_rank_id())
+    return int(dev)
+
+
+def get_min_device_id() -> int:
+    return min(get_rank_to_device_dict().values())
+
+
+def get_device_list() -> List[int]:
+    """Device ids of this job on this host, in rank order."""
+    d = get_rank_to_device_dict()
+    return [d[r] for r in sorted(d)]

@@ -101,6 +101,29 @@ def str_safe_check(name: str, value: Any, pattern: Optional[str] = None, max_len
     return v.validate()
 
 
+def class_safe_check(name: str, value: Any, classes) -> Any:
+    """``value`` must be an instance of ``classes`` (a class or a tuple of classes)."""
+    classes = tuple(classes) if isinstance(classes, (list, tuple)) else (classes,)
+    return Validator(value, name).add(lambda v: isinstance(v, classes), "must be an instance of %s"
+                                      % "/".join(getattr(c, "__name__", str(c)) for c in classes)).validate()
+
+
+def dir_safe_check(name: str, directory: Any) -> str:
+    """An existing directory, given as a non-empty path of bounded length without ``..`` and not through a symbolic link."""
+    return DirectoryValidator(directory, name).check_exists().check_not_symlink().validate()
+
+
+def file_safe_check(name: str, path: Any, unsupported_mode: int = 0o022, min_size: int = 1, max_size: int = 1 << 40) -> str:
+    """An existing regular file that may be trusted as input: not a symbolic link, size within ``[min_size, max_size]``, none
+    of the ``unsupported_mode`` permission bits set (default: not writable by group / others), owned by the caller or root."""
+    v = StringValidator(path, name, 4096)
+    v.add(lambda p: os.path.isfile(p) and not os.path.islink(p), "must be an existing regular file, not a symbolic link")
+    v.add(lambda p: min_size <= os.path.getsize(p) <= max_size, "size must be in [%d, %d] bytes" % (min_size, max_size))
+    v.add(lambda p: (os.stat(p).st_mode & unsupported_mode) == 0, "must not have permission bits %o" % unsupported_mode)
+    v.add(lambda p: os.stat(p).st_uid in (os.getuid(), 0), "must be owned by the calling user or root")
+    return v.validate()
+
+
 def path_safe_check(name: str, value: Any, must_exist: bool = False) -> str:
     v = DirectoryValidator(value, name).check_not_symlink()
     if must_exist:

@@ -1,5 +1,5 @@
 """Multi-tier embedding tables: device-memory cache of hot rows over a host-DRAM table, admission / eviction."""
-from .configs import (POLICY_COUNT, POLICY_SHOW_CLICK, AdmitAndEvictConfig, EmbCacheEmbeddingBagConfig, EmbCacheEmbeddingConfig,
+from .configs import (POLICY_COUNT, POLICY_SHOW_CLICK, AdmitAndEvictConfig, AdmitAndEvictPolicyType, EmbCacheEmbeddingBagConfig, EmbCacheEmbeddingConfig,
                       InitializerType, ShowClickParams)
 from .embedding_bag import (EmbCacheEmbeddingBagCollection, EmbCacheEmbeddingBagCollectionSharder,
                             EmbCacheShardedEmbeddingBagCollection, calculate_caches)
@@ -8,7 +8,7 @@ from .restore import RestoreTask, restore, restore_async
 from .saver import Saver
 from .train_pipeline import EmbCacheTrainPipelineSparseDist
 
-__all__ = ["POLICY_COUNT", "POLICY_SHOW_CLICK", "AdmitAndEvictConfig", "EmbCacheEmbeddingBagConfig", "EmbCacheEmbeddingConfig",
+__all__ = ["POLICY_COUNT", "POLICY_SHOW_CLICK", "AdmitAndEvictConfig", "AdmitAndEvictPolicyType", "EmbCacheEmbeddingBagConfig", "EmbCacheEmbeddingConfig",
            "InitializerType", "ShowClickParams", "EmbCacheEmbeddingBagCollection", "EmbCacheEmbeddingBagCollectionSharder",
            "EmbCacheShardedEmbeddingBagCollection", "calculate_caches", "EmbCacheEmbeddingCollection", "EmbCacheEmbeddingCollectionSharder",
            "EmbCacheShardedEmbeddingCollection", "Saver", "EmbCacheTrainPipelineSparseDist", "RestoreTask", "restore", "restore_async"]

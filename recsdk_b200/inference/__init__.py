@@ -2,8 +2,10 @@
 from .kvcache_manager import (GPUKVCacheManager, HostKVStorageErrorCode, HostKVStorageManagerBase, HostKVTaskHandle,
                               HostKVTaskStatus, HostKVWaitResult, KVCacheConfig, KVCacheManager, KVCacheMetadata,
                               KVCacheOffloadMode, KVIndexMeta, KVLookupResult, NativeHostKVCacheManager, NPUKVCacheManager,
-                              get_kvcache_config)
+                              HostKVStorageBackend, HostKVStorageFailPolicy, copy_kvcache_metadata, get_kvcache_config,
+                              get_kvcache_metadata_buffer)
 
 __all__ = ["GPUKVCacheManager", "HostKVStorageErrorCode", "HostKVStorageManagerBase", "HostKVTaskHandle", "HostKVTaskStatus",
            "HostKVWaitResult", "KVCacheConfig", "KVCacheManager", "KVCacheMetadata", "KVCacheOffloadMode", "KVIndexMeta",
-           "KVLookupResult", "NativeHostKVCacheManager", "NPUKVCacheManager", "get_kvcache_config"]
+           "KVLookupResult", "NativeHostKVCacheManager", "NPUKVCacheManager", "get_kvcache_config", "HostKVStorageBackend", "HostKVStorageFailPolicy",
+           "copy_kvcache_metadata", "get_kvcache_metadata_buffer"]

@@ -145,6 +145,65 @@ class KVCacheMetadata:
     host_page_ids: Optional[np.ndarray] = None
 
 
+def get_kvcache_metadata_buffer(batch_size: int, num_new_tokens: int, num_pages: int, page_ids_npu_buffer: Optional[torch.Tensor] = None,
+                                metadata_npu_buffer: Optional[torch.Tensor] = None, device=None) -> KVCacheMetadata:
+    """A metadata record over preallocated (or given) buffers, sized for ``batch_size`` requests, ``num_new_tokens`` new
+    tokens and ``num_pages`` pages: the static buffers a captured graph reads while ``copy_kvcache_metadata`` refreshes them
+    (``kvcache_metadata.py:64-123`` of the reference; layout of the int32 buffer: page indptr ``[B+1]``, last-page lengths
+    ``[B]``, total lengths ``[B]``, total offsets ``[B+1]``, new-token count ``[1]``, new offsets ``[B+1]``, batch index
+    and position of every new token)."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    elif isinstance(device, int):
+        device = torch.device("cuda", device) if torch.cuda.is_available() else torch.device("cpu")
+    device = torch.device(device)
+    B, n = int(batch_size), int(num_new_tokens)
+    pages = page_ids_npu_buffer if page_ids_npu_buffer is not None else torch.empty(int(num_pages), dtype=torch.int32, device=device)
+    buf = metadata_npu_buffer if metadata_npu_buffer is not None else torch.empty(5 * B + 4 + 2 * n, dtype=torch.int32, device=device)
+    if buf.numel() < 5 * B + 4 + 2 * n:
+        raise ValueError("metadata buffer holds %d ints, %d are needed" % (buf.numel(), 5 * B + 4 + 2 * n))
+    tot_len, tot_off = buf.narrow(0, 2 * B + 1, B), buf.narrow(0, 3 * B + 1, B + 1)
+    return KVCacheMetadata(
+        page_ids_npu_buffer=pages, metadata_npu_buffer=buf, kv_indices=pages, kv_indptr=buf.narrow(0, 0, B + 1),
+        kv_last_page_len=buf.narrow(0, B + 1, B), total_history_lengths=tot_len, total_history_offsets=tot_off,
+        new_history_offsets=buf.narrow(0, 4 * B + 3, B + 1), batch_indices=buf.narrow(0, 5 * B + 4, n),
+        position=buf.narrow(0, 5 * B + 4 + n, n), new_history_nnz=n, new_history_nnz_npu=buf.narrow(0, 4 * B + 2, 1),
+        kv_seqlens=torch.empty_like(tot_len), kv_seqlen_offsets=torch.empty_like(tot_off), kv_onload_handle=None)
+
+
+def copy_kvcache_metadata(dst_metadata: KVCacheMetadata, src_metadata: KVCacheMetadata) -> None:
+    """Refresh preallocated metadata from a step's metadata: value lists are copied and zero-padded, offset lists are copied
+    and padded with their last entry (so the padding describes empty requests) (``kvcache_metadata.py:126-150``)."""
+    def copy_tensor(dst, src):
+        k = src.shape[0]
+        if k > dst.shape[0]:
+            raise ValueError("destination buffer holds %d entries, the source %d" % (dst.shape[0], k))
+        dst[:k].copy_(src, non_blocking=True)
+        dst[k:] = 0
+
+    def copy_offsets(dst, src):
+        k = src.shape[0]
+        if k > dst.shape[0]:
+            raise ValueError("destination buffer holds %d entries, the source %d" % (dst.shape[0], k))
+        dst[:k].copy_(src, non_blocking=True)
+        if k:
+            dst[k:] = src[-1]
+
+    d, s = dst_metadata, src_metadata
+    copy_tensor(d.kv_indices, s.kv_indices)
+    copy_offsets(d.kv_indptr, s.kv_indptr)
+    copy_tensor(d.kv_last_page_len, s.kv_last_page_len)
+    copy_tensor(d.batch_indices, s.batch_indices)
+    copy_tensor(d.position, s.position)
+    copy_tensor(d.new_history_nnz_npu, s.new_history_nnz_npu)
+    copy_offsets(d.total_history_offsets, s.total_history_offsets)
+    copy_offsets(d.new_history_offsets, s.new_history_offsets)
+    copy_tensor(d.kv_seqlens, s.kv_seqlens)
+    copy_offsets(d.kv_seqlen_offsets, s.kv_seqlen_offsets)
+    d.new_history_nnz = s.new_history_nnz
+    d.kv_onload_handle = s.kv_onload_handle
+
+
 class HostKVTaskStatus(enum.Enum):
     UNINITIALIZED = "uninitialized"
     SKIPPED = "skipped"

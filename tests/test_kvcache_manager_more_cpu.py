@@ -197,3 +197,30 @@ def test_reference_contract_helpers():
     f = KVCacheManager(GPUKVCacheManager(_cfg()), Foreign(_cfg()))
     assert f.lookup_kvcache(torch.tensor([3]), torch.tensor([10]))[1].host_cached_lengths.tolist() == [0]
     assert "sdk_init_failed" in [c.value for c in HostKVStorageErrorCode]
+
+
+def test_static_metadata_buffers_are_refreshed_from_a_step():
+    """``get_kvcache_metadata_buffer`` + ``copy_kvcache_metadata``: fixed-size buffers (what a captured graph reads) take a
+    step's metadata; value lists are zero-padded, offset lists repeat their last entry."""
+    from recsdk_b200.inference import copy_kvcache_metadata, get_kvcache_metadata_buffer
+
+    m = KVCacheManager.from_config(_cfg())
+    meta, look = m.lookup_kvcache(torch.tensor([7, 9]), torch.tensor([70, 40]))
+    md = m.allocate_kvcache(meta, look)
+    static = get_kvcache_metadata_buffer(batch_size=4, num_new_tokens=128, num_pages=24, device="cpu")
+    assert static.metadata_npu_buffer.numel() == 5 * 4 + 4 + 256 and static.kv_indices is static.page_ids_npu_buffer
+    assert static.kv_indptr.shape == (5,) and static.position.shape == (128,) and static.new_history_nnz == 128
+    copy_kvcache_metadata(static, md)
+    n = md.new_history_nnz
+    assert static.new_history_nnz == n == 110 and static.kv_indptr.tolist() == md.kv_indptr.tolist() + [int(md.kv_indptr[-1])] * 2
+    assert static.kv_last_page_len.tolist() == md.kv_last_page_len.tolist() + [0, 0]
+    assert static.position[:n].tolist() == md.position.tolist() and int(static.position[n:].abs().sum()) == 0
+    assert static.total_history_offsets.tolist() == [0, 70, 110, 110, 110] and static.kv_seqlens.tolist() == [70, 40, 0, 0]
+    assert int(static.new_history_nnz_npu) == n and static.kv_indices[: md.kv_indices.numel()].tolist() == md.kv_indices.tolist()
+    own = torch.zeros(5 * 2 + 4 + 2 * 8, dtype=torch.int32)
+    given = get_kvcache_metadata_buffer(2, 8, 4, torch.zeros(4, dtype=torch.int32), own, device="cpu")
+    assert given.metadata_npu_buffer is own and given.batch_indices.data_ptr() == own[14:].data_ptr()
+    with pytest.raises(ValueError):
+        get_kvcache_metadata_buffer(2, 8, 4, metadata_npu_buffer=torch.zeros(10, dtype=torch.int32), device="cpu")
+    with pytest.raises(ValueError):
+        copy_kvcache_metadata(get_kvcache_metadata_buffer(1, 8, 4, device="cpu"), md)      # two requests do not fit a batch of one

@@ -210,7 +210,7 @@ def test_dynamic_config_helpers():
 
 
 def test_admit_and_evict_config_switches():
-    from recsdk_b200.embcache.configs import POLICY_SHOW_CLICK, AdmitAndEvictConfig, ShowClickParams
+    from recsdk_b200.embcache.configs import POLICY_SHOW_CLICK, AdmitAndEvictConfig, AdmitAndEvictPolicyType, ShowClickParams
 
     off = AdmitAndEvictConfig()
     assert not off.is_admit_enabled() and not off.is_evict_enabled() and not off.is_feature_filter_enabled()
@@ -219,6 +219,17 @@ def test_admit_and_evict_config_switches():
     sc = AdmitAndEvictConfig(policy_type=POLICY_SHOW_CLICK, admit_threshold=5,
                              show_click_params=ShowClickParams(admit_threshold=-1.0, evict_percentage=0.2))
     assert not sc.is_admit_enabled() and sc.is_evict_enabled()         # the count threshold is ignored under show/click
+    ref_style = AdmitAndEvictConfig(admit_threshold=3, evict_threshold=0, evict_step_interval=0, policy_type=AdmitAndEvictPolicyType.POLICY_COUNT)
+    assert ref_style.is_feature_admit_enabled() and not ref_style.is_feature_evict_enabled() and ref_style.policy_type == "count"
+    assert not ref_style.is_showclick_policy() and not ref_style.is_showclick_filter_enabled()
+    both = AdmitAndEvictConfig(policy_type=AdmitAndEvictPolicyType.POLICY_SHOWCLICK, showclick_params=ShowClickParams(admit_threshold=2.0))
+    assert both.show_click_params is both.showclick_params and both.is_showclick_admit_enabled() and not both.is_showclick_evict_enabled()
+    assert both.is_feature_admit_enabled() and both.is_showclick_filter_enabled() and both.is_showclick_policy()
+    assert (ShowClickParams().beta, ShowClickParams().admit_threshold) == (0.0, 0.0)
+    assert AdmitAndEvictConfig(admit_threshold=None, evict_threshold=None).admit_threshold == -1
+    for wrong in (dict(admit_threshold=1.5), dict(not_admitted_default_value=1), dict(evict_threshold=True)):
+        with pytest.raises(TypeError):
+            AdmitAndEvictConfig(**wrong)
     for bad in (dict(policy_type="lru"), dict(admit_threshold=-2), dict(evict_step_interval=3),
                 dict(show_click_params=ShowClickParams(evict_percentage=1.5)),
                 dict(show_click_params=ShowClickParams(score_decay=0.0))):
