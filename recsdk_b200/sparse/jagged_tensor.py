@@ -221,6 +221,50 @@ class KeyedJaggedTensor:
             self._offset_per_key = out
         return self._offset_per_key
 
+    # -- small accessors of the TorchRec container that user code commonly calls ---------------------------------------
+    def index_per_key(self) -> Dict[str, int]:
+        return self._key_indices()
+
+    def variable_stride_per_key(self) -> bool:
+        """Every key has the same number of bags here (one per sample)."""
+        return False
+
+    def stride_per_key(self) -> List[int]:
+        return [self._stride] * len(self._keys)
+
+    def lengths_offset_per_key(self) -> List[int]:
+        """Start of every key's bags in ``lengths()`` (``[0, B, 2B, ...]``)."""
+        return [i * self._stride for i in range(len(self._keys) + 1)]
+
+    def inverse_indices_or_none(self):
+        return None
+
+    def flatten_lengths(self) -> "KeyedJaggedTensor":
+        return self._carry(KeyedJaggedTensor(self._keys, self._values, self._weights, self.lengths().reshape(-1), None, self._stride,
+                                             self._length_per_key, self._offset_per_key))
+
+    def sync(self) -> "KeyedJaggedTensor":
+        """Compute the host-side per-key lengths and offsets now (one device-to-host read for device tensors)."""
+        self.length_per_key()
+        self.offset_per_key()
+        return self
+
+    def unsync(self) -> "KeyedJaggedTensor":
+        self._length_per_key = None
+        self._offset_per_key = None
+        return self
+
+    @staticmethod
+    def empty_like(kjt: "KeyedJaggedTensor") -> "KeyedJaggedTensor":
+        """No ids, same keys, stride and device."""
+        v = kjt.values()
+        w = kjt.weights_or_none()
+        return KeyedJaggedTensor(kjt.keys(), v[:0], None if w is None else w[:0],
+                                 lengths=torch.zeros(len(kjt.keys()) * kjt.stride(), dtype=torch.int64, device=v.device), stride=kjt.stride())
+
+    def __len__(self) -> int:
+        return len(self._keys)
+
     def _key_indices(self) -> Dict[str, int]:
         return {k: i for i, k in enumerate(self._keys)}
 

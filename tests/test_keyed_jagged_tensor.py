@@ -69,3 +69,15 @@ def test_moves_and_dist_tensors():
     assert jt.offsets().tolist() == [0, 1, 4]
     if torch.cuda.is_available():
         assert k.pin_memory().values().is_pinned()
+
+
+def test_small_accessors():
+    k = _kjt(weighted=True)
+    assert k.index_per_key() == {"a": 0, "b": 1, "c": 2} and len(k) == 3 and not k.variable_stride_per_key()
+    assert k.stride_per_key() == [2, 2, 2] and k.lengths_offset_per_key() == [0, 2, 4, 6] and k.inverse_indices_or_none() is None
+    assert k.unsync()._length_per_key is None and k.sync()._offset_per_key == [0, 3, 4, 8]
+    two_d = KeyedJaggedTensor(["a", "b", "c"], k.values(), lengths=k.lengths().view(3, 2), stride=2)
+    assert two_d.flatten_lengths().lengths().shape == (6,) and two_d.flatten_lengths()["c"].values().tolist() == [5, 6, 7, 8]
+    e = KeyedJaggedTensor.empty_like(k)
+    assert e.keys() == k.keys() and e.stride() == 2 and e.values().numel() == 0 and e.lengths().tolist() == [0] * 6
+    assert e.weights().numel() == 0 and e["b"].values().numel() == 0
