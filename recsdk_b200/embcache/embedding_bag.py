@@ -422,6 +422,29 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
             rows, grads = rows[keep], grads[keep]
         super()._apply_update(ti, rows, grads)
 
+    # -- names of the reference's sharded module ----------------------------------------------------------
+    @property
+    def embcache_mgr(self):
+        """The native host-side manager (reference ``distributed/embedding_bag.py:593-595``)."""
+        return self.manager
+
+    @property
+    def config_list(self):
+        """The unsharded table configs (reference ``distributed/embedding_bag.py:597-599``)."""
+        return self.full_tables
+
+    def get_batched_embedding_kernels(self) -> List[List["CacheKernelView"]]:
+        """One group with one view over this rank's device cache: ``[0][0].weights_dev`` is the flat cache weight and
+        ``get_momentum()`` the optimizer-state tensors, which is what a saver reads before it writes rows back to the
+        host (reference ``distributed/embedding_bag.py:790-799`` returns its codegen modules for the same purpose)."""
+        return [[CacheKernelView(self)]]
+
+    def record_host_emb_update_times(self) -> None:
+        """Count one training step in the host tables' update counters, where the native manager keeps them."""
+        fn = getattr(self.manager, "record_embedding_update_times", None)
+        if fn is not None:
+            fn()
+
     # -- eviction / checkpoint helpers -------------------------------------------------------------------
     def host_embedding_evict(self) -> Dict[str, int]:
         self.drain_host_updates()
@@ -452,6 +475,51 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
         ti = [t.name for t in self.full_tables].index(name)
         self.embedding_to_host()
         return torch.from_numpy(self.manager.embedding_lookup(ti, np.asarray(keys, dtype=np.int64)))
+
+
+class CacheKernelView:
+    """Read-only view of a sharded cache module in the shape of a batched embedding kernel: the per-table device
+    weights, flat (``weights_dev``) or split (``split_embedding_weights``), and the optimizer state (``get_momentum``)."""
+
+    def __init__(self, module: "EmbCacheShardedEmbeddingBagCollection") -> None:
+        self._m = module
+
+    def split_embedding_weights(self) -> List[torch.Tensor]:
+        return [self._m.embedding_bags[t.name].weight.data for t in self._m.tables]
+
+    @property
+    def weights_dev(self) -> torch.Tensor:
+        ws = self.split_embedding_weights()
+        return torch.cat([w.reshape(-1) for w in ws]) if ws else torch.empty(0)
+
+    def get_momentum(self) -> List[torch.Tensor]:
+        """``optim_num`` flat tensors, each the concatenation over tables of that state slot."""
+        out = []
+        for k in ("state1", "state2")[: self._m.optim_num]:
+            out.append(torch.cat([self._m.state[ti][k].reshape(-1) for ti in range(len(self._m.tables))]))
+        return out
+
+
+class EmbCacheHashTable(nn.Module):
+    """One table whose ids are arbitrary 64-bit keys: an ``IdsMapper`` hands out rows in order of first sight and a plain
+    ``nn.EmbeddingBag`` holds them (reference ``distributed/embedding_bag.py:142-168``; the unsharded, single-process
+    form of a cached table, used to check the sharded one)."""
+
+    def __init__(self, config, device=None) -> None:
+        super().__init__()
+        from ..modules.ids_process import IdsMapper
+
+        self.config = config
+        self.ids2slot_dict = IdsMapper(config.num_embeddings, only_device_memory=False)
+        mode = getattr(getattr(config, "pooling", None), "name", "SUM").lower()
+        self.vector_table = nn.EmbeddingBag(config.num_embeddings, config.embedding_dim, mode=mode, device=device,
+                                            include_last_offset=True)
+        self.index = 0
+        self.register_parameter("weight", self.vector_table.weight)
+
+    def forward(self, input_feat: torch.Tensor, offsets: Optional[torch.Tensor] = None, per_sample_weights=None) -> torch.Tensor:
+        idx, _, _ = self.ids2slot_dict(input_feat.cpu())
+        return self.vector_table(idx.to(input_feat.device), offsets, per_sample_weights)
 
 
 class EmbCacheEmbeddingBagCollectionSharder:

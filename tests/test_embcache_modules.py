@@ -316,3 +316,28 @@ def test_checkpoints_in_timestamp_directories(tmp_path):
     saver.load(m2, Saver.get_latest_load_path(str(tmp_path)))
     assert torch.allclose(m2.host_rows("t0", list(range(60))), ref_rows)
     assert Saver.get_latest_load_path(str(tmp_path / "nowhere")) is None
+
+
+def test_reference_names_of_the_sharded_module():
+    from recsdk_b200.embcache import CacheKernelView, EmbCacheHashTable
+    from recsdk_b200.modules.embedding_configs import EmbeddingBagConfig
+
+    m = _sharded(_tables(), [40, 64], torch.optim.Adagrad)
+    _train(m, 2)
+    assert m.embcache_mgr is m.manager and [c.name for c in m.config_list] == ["t0", "t1"]
+    kernels = m.get_batched_embedding_kernels()
+    assert len(kernels) == 1 and isinstance(kernels[0][0], CacheKernelView)
+    k = kernels[0][0]
+    ws = k.split_embedding_weights()
+    assert [tuple(w.shape) for w in ws] == [(40, 8), (64, 16)]
+    assert k.weights_dev.numel() == 40 * 8 + 64 * 16
+    mom = k.get_momentum()
+    assert len(mom) == m.optim_num == 1 and mom[0].numel() == k.weights_dev.numel()
+    m.record_host_emb_update_times()                       # a no-op where the native manager keeps no such counter
+
+    cfg = EmbeddingBagConfig(num_embeddings=16, embedding_dim=4, name="h", feature_names=["f"])
+    ht = EmbCacheHashTable(cfg, torch.device("cpu"))
+    ids = torch.tensor([1 << 40, 7, 1 << 40, 99], dtype=torch.int64)
+    out = ht(ids, torch.tensor([0, 2, 4]))
+    w = ht.weight.detach()
+    assert torch.allclose(out[0], w[0] + w[1]) and torch.allclose(out[1], w[0] + w[2])    # slots in order of first sight
