@@ -106,9 +106,30 @@ class EmbCacheTrainPipelineSparseDist(TrainPipelineBase):
         self._optimizer.step()
         return loss, out
 
-    def progress(self, dataloader_iter: Iterator):
+    def attach(self, model: Optional[torch.nn.Module] = None) -> None:
+        """(Re-)bind the pipeline to ``model`` (or to the current one) and look its multi-tier modules up again."""
+        if model is not None:
+            self._model = model
+        self._mods = embcache_modules(self._model)
+        self._async = self._cuda and all(m._async_ready() for m in self._mods)
+
+    def fill_pipeline(self, dataloader_iter: Iterator) -> None:
+        """Stage the first batch (copy, input distribution, swap) without running a step; ``progress`` does this itself
+        on its first call."""
         if self._next is None and not self._exhausted:
             self._next = self._fetch(dataloader_iter)
+
+    def wait_pipeline_compute_swapinfo(self) -> None:
+        """Bring the staged batch's swap to rest: every pending host update applied, the memcpy stream drained.  Call it
+        before a save that happens in the middle of an epoch (while a next batch is staged), as with the reference
+        (``distributed/train_pipeline.py:733-735``); the swap plan itself is already complete when ``progress`` returns."""
+        for m in self._mods:
+            m.drain_host_updates()
+            if getattr(m, "_memcpy_stream", None) is not None:
+                m._memcpy_stream.synchronize()
+
+    def progress(self, dataloader_iter: Iterator):
+        self.fill_pipeline(dataloader_iter)
         if self._next is None:
             raise StopIteration
         batch, copied = self._next

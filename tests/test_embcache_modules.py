@@ -341,3 +341,50 @@ def test_reference_names_of_the_sharded_module():
     out = ht(ids, torch.tensor([0, 2, 4]))
     w = ht.weight.detach()
     assert torch.allclose(out[0], w[0] + w[1]) and torch.allclose(out[1], w[0] + w[2])    # slots in order of first sight
+
+
+def test_pipeline_save_in_the_middle_of_an_epoch(tmp_path):
+    """fill_pipeline / wait_pipeline_compute_swapinfo / attach: a save taken while the next batch is staged holds the rows
+    that the steps run so far have trained, and training goes on from the staged batch afterwards."""
+    class Model(torch.nn.Module):
+        def __init__(self, emb):
+            super().__init__()
+            self.emb = emb
+            self.w = torch.nn.Parameter(torch.randn(40, generator=torch.Generator().manual_seed(9)))
+
+        def forward(self, batch):
+            loss = (self.emb(batch.sparse_features).values() * self.w).sum(dim=1).pow(2).mean()
+            return loss, loss.detach()
+
+    class B:
+        def __init__(self, k):
+            self.sparse_features = k
+
+        def to(self, device, non_blocking=False):
+            return self
+
+    def run(save_at):
+        model = Model(_sharded(_tables(), [40, 64]))
+        opt = torch.optim.SGD([model.w], lr=0.01)
+        g = torch.Generator().manual_seed(3)
+        data = iter([B(_batch(g)) for _ in range(6)])
+        pipe = EmbCacheTrainPipelineSparseDist(model, opt, "cpu", "cpu", return_loss=True)
+        pipe.fill_pipeline(data)
+        assert pipe._next is not None
+        losses, snap = [], None
+        for i in range(6):
+            losses.append(float(pipe.progress(data)[0]))
+            if i == save_at:
+                pipe.wait_pipeline_compute_swapinfo()
+                Saver().save(model, str(tmp_path / ("ck%d" % save_at)))
+                snap = model.emb.host_rows("t1", list(range(60))).clone()
+        pipe.attach()
+        assert pipe._mods == [model.emb]
+        return losses, snap, model
+
+    la, snap, _ = run(2)
+    lb, _, _ = run(-1)
+    assert np.allclose(la, lb, rtol=1e-6)                  # the save does not disturb training
+    fresh = Model(_sharded(_tables(), [40, 64]))
+    Saver().load(fresh, Saver.get_latest_load_path(str(tmp_path / "ck2")) or str(tmp_path / "ck2"))
+    assert torch.allclose(fresh.emb.host_rows("t1", list(range(60))), snap, atol=1e-6)
