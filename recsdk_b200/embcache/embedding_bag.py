@@ -20,6 +20,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 from torch import nn
+from torch.autograd.profiler import record_function
 
 from ..host import host
 from ..modules.embedding_configs import PoolingType
@@ -243,8 +244,9 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
                 tab_pos[self.feature_table[f]].append(np.arange(seg_off[s_ * F + f], seg_off[s_ * F + f + 1]))
         pos = [np.concatenate(p) if p else np.zeros(0, dtype=np.int64) for p in tab_pos]
         now = int(time.time())
-        futs = [self.manager.plan_batch_async(ti, ids_np[p], self.swap_step, self.admit[ti], self.evict[ti], now)
-                for ti, p in enumerate(pos)]
+        with record_function("## _compute_swap_info_async ##"):
+            futs = [self.manager.plan_batch_async(ti, ids_np[p], self.swap_step, self.admit[ti], self.evict[ti], now)
+                    for ti, p in enumerate(pos)]
         return futs, pos
 
     def host_embedding_update_async(self, ti: int, keys: np.ndarray, staged: torch.Tensor, copied: "torch.cuda.Event"):
@@ -255,7 +257,8 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
             if prev is not None:
                 prev.result()
             copied.synchronize()
-            self.manager.embedding_update_from(ti, keys, staged.data_ptr())
+            with record_function("## _host_embedding_update ##"):
+                self.manager.embedding_update_from(ti, keys, staged.data_ptr())
 
         fut = self._host_pool.submit(run)
         self._upd_fut[ti] = fut
@@ -269,7 +272,8 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
         def run():
             if prev is not None:
                 prev.result()
-            self.manager.embedding_lookup_into(ti, keys, staged.data_ptr(), staged.shape[0])
+            with record_function("## host_embedding_lookup_async ##"):
+                self.manager.embedding_lookup_into(ti, keys, staged.data_ptr(), staged.shape[0])
 
         return self._host_pool.submit(run)
 
@@ -323,8 +327,10 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
                 t_begin = torch.cuda.Event(enable_timing=True)
                 t_begin.record()
             for ti, p in enumerate(pos):
-                info = futs[ti].get()
-                self.apply_swap_async(ti, info, slot)
+                with record_function("## wait_and_get_swap_info ##"):
+                    info = futs[ti].get()
+                with record_function("## swap_out / swapin_embs_optims_to_gpu ##"):
+                    self.apply_swap_async(ti, info, slot)
                 out[p] = info["batch_offs"]
             slots = torch.from_numpy(out).pin_memory().to(self.device, non_blocking=True)
             lengths_dev = lengths.pin_memory().to(self.device, non_blocking=True)
@@ -346,7 +352,8 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
     def wait_swap(self) -> None:
         """The compute stream waits for the scatter of the batch it is about to look up."""
         if self._swap_ready is not None:
-            torch.cuda.current_stream(self.device).wait_event(self._swap_ready)
+            with record_function("## wait_and_swapin ##"):
+                torch.cuda.current_stream(self.device).wait_event(self._swap_ready)
             self._swap_ready = None
 
     def drain_host_updates(self) -> None:
@@ -449,9 +456,10 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
     def host_embedding_evict(self) -> Dict[str, int]:
         self.drain_host_updates()
         out = {}
-        for ti, t in enumerate(self.full_tables):
-            if self.evict[ti]:
-                out[t.name] = int(self.manager.evict_features(ti).size)
+        with record_function("## feature_evict ##"):
+            for ti, t in enumerate(self.full_tables):
+                if self.evict[ti]:
+                    out[t.name] = int(self.manager.evict_features(ti).size)
         return out
 
     @torch.no_grad()

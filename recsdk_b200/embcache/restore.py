@@ -10,6 +10,7 @@ from __future__ import annotations
 from typing import Sequence
 
 import torch
+from torch.autograd.profiler import record_function
 
 from ..host import host
 
@@ -23,8 +24,9 @@ def _np(t: torch.Tensor, name: str):
 def restore(unique_indices: torch.Tensor, unique_inverse: torch.Tensor, unique_offset: torch.Tensor,
             offsets_per_table: Sequence[int], hash_indices: torch.Tensor) -> torch.Tensor:
     """Fills ``hash_indices`` in place and returns it."""
-    host().restore(_np(unique_indices, "unique_indices"), _np(unique_inverse, "unique_inverse"), _np(unique_offset, "unique_offset"),
-                   [int(x) for x in offsets_per_table], _np(hash_indices, "hash_indices"))
+    with record_function("## restore ##"):
+        host().restore(_np(unique_indices, "unique_indices"), _np(unique_inverse, "unique_inverse"), _np(unique_offset, "unique_offset"),
+                       [int(x) for x in offsets_per_table], _np(hash_indices, "hash_indices"))
     return hash_indices
 
 

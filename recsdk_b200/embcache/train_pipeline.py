@@ -24,6 +24,7 @@ import os
 from typing import Any, Callable, Iterator, List, Optional
 
 import torch
+from torch.autograd.profiler import record_function
 
 from ..parallel.train_pipeline import TrainPipelineBase
 from .configs import MIN_EVICT_STEP_INTERVAL
@@ -69,22 +70,25 @@ class EmbCacheTrainPipelineSparseDist(TrainPipelineBase):
         """Next batch: H2D copy on the copy stream, then input dist + swap for every embcache module.  On the asynchronous
         path nothing here waits for the compute stream, so it is called right after a step has been enqueued."""
         try:
-            host_batch = next(it)
+            with record_function("## get_next_batch ##"):
+                host_batch = next(it)
         except StopIteration:
             self._exhausted = True
             return None
-        if self._cuda:
-            with torch.cuda.stream(self._copy_stream):
-                batch = host_batch.to(self._device, non_blocking=True)
-                copied = torch.cuda.Event()
-                copied.record()
-        else:
-            batch, copied = host_batch.to(self._device), None
+        with record_function("## copy_batch_to_gpu ##"):
+            if self._cuda:
+                with torch.cuda.stream(self._copy_stream):
+                    batch = host_batch.to(self._device, non_blocking=True)
+                    copied = torch.cuda.Event()
+                    copied.record()
+            else:
+                batch, copied = host_batch.to(self._device), None
         feats = self._features_of(batch)
         if self._async:
             host_feats = self._features_of(host_batch)
-            for m in self._mods:
-                m.prefetch_async(feats, host_feats)
+            with record_function("## start_sparse_data_dist ##"):
+                for m in self._mods:
+                    m.prefetch_async(feats, host_feats)
         else:
             if copied is not None:
                 torch.cuda.current_stream(self._device).wait_event(copied)
@@ -95,15 +99,19 @@ class EmbCacheTrainPipelineSparseDist(TrainPipelineBase):
         return batch, copied
 
     def _run_step(self, batch):
-        (self._zero or self._optimizer.zero_grad)()
-        loss, out = (self._fwd or self._model)(batch)
-        (self._bwd(loss) if self._bwd else loss.backward())
-        for m in self._mods:
-            m.mark_step_done()
-        sync = getattr(self._model, "sync_dense_grads", None)
-        if sync is not None:
-            sync()
-        self._optimizer.step()
+        with record_function("## zero_grad ##"):
+            (self._zero or self._optimizer.zero_grad)()
+        with record_function("## forward ##"):
+            loss, out = (self._fwd or self._model)(batch)
+        with record_function("## backward ##"):
+            (self._bwd(loss) if self._bwd else loss.backward())
+            for m in self._mods:
+                m.mark_step_done()
+            sync = getattr(self._model, "sync_dense_grads", None)
+            if sync is not None:
+                sync()
+        with record_function("## optimizer ##"):
+            self._optimizer.step()
         return loss, out
 
     def attach(self, model: Optional[torch.nn.Module] = None) -> None:
@@ -135,8 +143,9 @@ class EmbCacheTrainPipelineSparseDist(TrainPipelineBase):
         batch, copied = self._next
         if self._async:
             if copied is not None:
-                torch.cuda.current_stream(self._device).wait_event(copied)
-                batch.record_stream(torch.cuda.current_stream(self._device))
+                with record_function("## wait_for_batch ##"):
+                    torch.cuda.current_stream(self._device).wait_event(copied)
+                    batch.record_stream(torch.cuda.current_stream(self._device))
             loss, out = self._run_step(batch)                  # batch i is on the GPU's queue ...
             self._next = self._fetch(dataloader_iter) if not self._exhausted else None   # ... the host turns to batch i+1
         else:

@@ -19,6 +19,7 @@ from collections import deque
 from typing import Any, Callable, Deque, Dict, Iterator, List, Optional, Tuple
 
 import torch
+from torch.autograd.profiler import record_function
 
 from ..modules.embedding_modules import EmbeddingBagCollection
 from ..modules.hash_embeddingbag import HashEmbeddingBagCollection
@@ -162,11 +163,13 @@ class HybridTrainPipelineSparseDist(TrainPipelineBase):
             self.stage_log.append((self._step_no, ctx.index, stage.name))
 
     def _start_split(self, it: Iterator) -> HybridPipelineContext:
-        ctx = HybridPipelineContext(index=self._n_read, host_batch=next(it, None))
+        with record_function("## get_next_batch ##"):
+            ctx = HybridPipelineContext(index=self._n_read, host_batch=next(it, None))
         self._n_read += 1
         if ctx.host_batch is not None:
-            feats = self._features_of(ctx.host_batch)
-            ctx.states = [m.stage_split(feats) for m in self._mods if _staged(m)]
+            with record_function("## start_sparse_data_dist ##"):
+                feats = self._features_of(ctx.host_batch)
+                ctx.states = [m.stage_split(feats) for m in self._mods if _staged(m)]
         self._log(ctx, HybridStage.SPLIT)
         return ctx
 
@@ -199,39 +202,45 @@ class HybridTrainPipelineSparseDist(TrainPipelineBase):
         self._log(ctx, HybridStage.FIRST_ALL2ALL)
 
     def _second_all2all(self, ctx: HybridPipelineContext) -> None:
-        for work, recv, cols in ctx.fused_splits:
-            if work is not None:
-                work.wait()
-            for st, c0, n in cols:
-                st.module.stage_exchange_ids(st, recv[:, c0:c0 + n].contiguous())
+        with record_function("## wait_sparse_data_dist ##"):
+            for work, recv, cols in ctx.fused_splits:
+                if work is not None:
+                    work.wait()
+                for st, c0, n in cols:
+                    st.module.stage_exchange_ids(st, recv[:, c0:c0 + n].contiguous())
         ctx.fused_splits = []
         self._log(ctx, HybridStage.SECOND_ALL2ALL)
 
     def _post_input(self, ctx: HybridPipelineContext) -> None:
-        for st in ctx.states:
-            st.module.stage_post_input(st)
+        with record_function("## _post_input_dist ##"):
+            for st in ctx.states:
+                st.module.stage_post_input(st)
         self._log(ctx, HybridStage.POST_INPUT)
 
     def _copy_to_device(self, ctx: HybridPipelineContext) -> None:
         if ctx.host_batch is not None and ctx.batch is None:
             assert ctx.stage == int(HybridStage.POST_INPUT), "copy stage reached before the id mapping stage"
-            if self._cuda:
-                torch.cuda.set_device(self._device)
-                with torch.cuda.stream(self._memcpy_stream):
-                    ctx.batch = ctx.host_batch.to(self._device, non_blocking=True)
-                    ctx.copy_event = torch.cuda.Event()
-                    ctx.copy_event.record(self._memcpy_stream)
-            else:
-                ctx.batch = ctx.host_batch.to(self._device)
-            feats = self._features_of(ctx.batch)
-            for st in ctx.states:
-                st.module.stage_to_device(st, feats, self._memcpy_stream)
-            staged = {id(st.module) for st in ctx.states}
-            for m in self._mods:                           # device-group modules: their own prefetch on the device batch
-                if id(m) not in staged:
-                    m.prefetch(feats)
-            ctx.states = []
+            with record_function("## copy_batch_to_gpu ##"):
+                self._copy_batch(ctx)
         self._log(ctx, HybridStage.COPY_TO_DEVICE)
+
+    def _copy_batch(self, ctx: HybridPipelineContext) -> None:
+        if self._cuda:
+            torch.cuda.set_device(self._device)
+            with torch.cuda.stream(self._memcpy_stream):
+                ctx.batch = ctx.host_batch.to(self._device, non_blocking=True)
+                ctx.copy_event = torch.cuda.Event()
+                ctx.copy_event.record(self._memcpy_stream)
+        else:
+            ctx.batch = ctx.host_batch.to(self._device)
+        feats = self._features_of(ctx.batch)
+        for st in ctx.states:
+            st.module.stage_to_device(st, feats, self._memcpy_stream)
+        staged = {id(st.module) for st in ctx.states}
+        for m in self._mods:                           # device-group modules: their own prefetch on the device batch
+            if id(m) not in staged:
+                m.prefetch(feats)
+        ctx.states = []
 
     _ADVANCE = {int(HybridStage.SPLIT): "_first_all2all", int(HybridStage.FIRST_ALL2ALL): "_second_all2all",
                 int(HybridStage.SECOND_ALL2ALL): "_post_input"}
@@ -262,9 +271,10 @@ class HybridTrainPipelineSparseDist(TrainPipelineBase):
             raise StopIteration
         line.popleft()
         if head.copy_event is not None:
-            cur = torch.cuda.current_stream(self._device)
-            cur.wait_event(head.copy_event)
-            head.batch.record_stream(cur)
+            with record_function("## wait_for_batch ##"):
+                cur = torch.cuda.current_stream(self._device)
+                cur.wait_event(head.copy_event)
+                head.batch.record_stream(cur)
         # the batch the next step trains on starts its copy now, so that it overlaps this step's compute
         if self._n > 1:
             self._copy_to_device(nxt[0])

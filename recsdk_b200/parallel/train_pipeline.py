@@ -38,17 +38,22 @@ class TrainPipelineBase:
         self._status = _lib.StatusPoller(device, status_poll_steps) if device.type == "cuda" else None
 
     def _step(self, batch) -> Tuple[torch.Tensor, Any]:
+        # profiler ranges carry the reference pipelines' names (hybrid_train_pipeline.py:282-319)
         trace.mark("step.zero_grad")
-        self._optimizer.zero_grad()
+        with record_function("## zero_grad ##"):
+            self._optimizer.zero_grad()
         trace.mark("step.input_dist")
-        loss, out = self._model(batch)
+        with record_function("## forward ##"):
+            loss, out = self._model(batch)
         trace.mark("dense.backward")
-        loss.backward()
-        sync = getattr(self._model, "sync_dense_grads", None)
-        if sync is not None:
-            sync()
+        with record_function("## backward ##"):
+            loss.backward()
+            sync = getattr(self._model, "sync_dense_grads", None)
+            if sync is not None:
+                sync()
         trace.mark("step.optimizer")
-        self._optimizer.step()
+        with record_function("## optimizer ##"):
+            self._optimizer.step()
         trace.mark("step.end")
         # hand back a graph-free loss: a live autograd graph would pin its AccumulateGrad nodes (and
         # the stream they were created on) across steps, which breaks a later CUDA-graph capture
@@ -84,7 +89,8 @@ class TrainPipelineSparseDist(TrainPipelineBase):
     # -- copy stage -------------------------------------------------------------
     def _start_copy(self, dataloader_iter: Iterator[Batch]):
         try:
-            host = next(dataloader_iter)
+            with record_function("## get_next_batch ##"):
+                host = next(dataloader_iter)
         except StopIteration:
             self._exhausted = True
             return None, None
