@@ -104,3 +104,6 @@ def swap_multi_tables(tables: List[torch.Tensor], swap_out_index: Optional[List[
                                          a_ho.ctypes.data, a_ii.ctypes.data, n_in.ctypes.data, a_hi.ctypes.data,
                                          _lib.num_sms(dev), _lib.status_tensor(dev).data_ptr(), _lib.stream_ptr(dev))
     _lib.check(rc, "rb_swap_multi_tables")
+
+
+rma_swap_multi_tables = swap_multi_tables        # name of the reference's operator (tf_plugin/src/ram_swap_multi_tables.cpp)
