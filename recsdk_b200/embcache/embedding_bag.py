@@ -447,10 +447,10 @@ class EmbCacheShardedEmbeddingBagCollection(CollectiveShardedEmbeddingBagCollect
         return [[CacheKernelView(self)]]
 
     def record_host_emb_update_times(self) -> None:
-        """Count one training step in the host tables' update counters, where the native manager keeps them."""
-        fn = getattr(self.manager, "record_embedding_update_times", None)
-        if fn is not None:
-            fn()
+        """Kept for pipelines written against the reference, which calls it once per host update: there, rows of evicted
+        features leave the host table only after a fixed number of further updates, so that swaps already planned do not
+        meet a missing row (``embcache_manager.cpp:1245-1252``).  Here ``host_embedding_evict`` first drains the pending
+        host updates and then removes the rows at once, so there is nothing to count."""
 
     # -- eviction / checkpoint helpers -------------------------------------------------------------------
     def host_embedding_evict(self) -> Dict[str, int]:

@@ -138,3 +138,34 @@ def block_bucketize_sparse_features_cpu(bucket_params: BucketParams):
     out = (torch.from_numpy(nl), torch.from_numpy(ni), None if w is None else torch.from_numpy(nw), None,
            torch.from_numpy(perm) if (p.sequence or p.do_unique) else None)
     return out + ((torch.from_numpy(counts),) if counts is not None else ())
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# ``torch.ops.hybrid.block_bucketize_sparse_features_cpu``: the operator form, with the reference's argument list
+# (``hybrid_torchrec/src/bind_torch_lib.cpp:11-19``, ``src/ids_process/bucketize.h:14-27``)
+# ----------------------------------------------------------------------------------------------------------------------
+_HYBRID_LIB = torch.library.Library("hybrid", "DEF")
+_HYBRID_LIB.define(
+    "block_bucketize_sparse_features_cpu(Tensor lengths, Tensor indices, bool bucketize_pos, bool sequence, Tensor block_sizes, "
+    "int bucket_size, Tensor? total_num_blocks=None, Tensor? weights=None, Tensor? batch_size_per_feature=None, int max_B=-1, "
+    "Tensor[]? block_bucketize_pos=None, bool return_bucket_mapping=False, bool keep_orig_idx=False, bool do_unique=False, "
+    "bool return_count=False, Tensor? labels=None) -> (Tensor, Tensor, Tensor?, Tensor?, Tensor?, Tensor?, Tensor)")
+
+
+def _block_bucketize_op(lengths, indices, bucketize_pos, sequence, block_sizes, bucket_size, total_num_blocks=None, weights=None,
+                        batch_size_per_feature=None, max_B=-1, block_bucketize_pos=None, return_bucket_mapping=False,
+                        keep_orig_idx=False, do_unique=False, return_count=False, labels=None):
+    """-> (new_lengths, new_indices, new_weights?, new_pos?, unbucketize_permute?, bucket_mapping?, counts); ``counts`` is
+    empty unless ``do_unique`` and ``return_count`` are set; ``bucket_mapping[i]`` is the bucket of input element ``i``."""
+    if block_bucketize_pos is not None:
+        raise NotImplementedError("explicit bucket boundaries are not supported: buckets are id % bucket_size")
+    out = block_bucketize_sparse_features_cpu(BucketParams(
+        lengths, indices, bool(bucketize_pos), bool(sequence), block_sizes, int(bucket_size), total_num_blocks, weights,
+        batch_size_per_feature, max(int(max_B), 0), None, bool(return_bucket_mapping), bool(keep_orig_idx), bool(do_unique),
+        bool(return_count), labels))
+    counts = out[5] if len(out) > 5 else torch.empty(0, dtype=torch.int64)
+    mapping = (indices.to(torch.int64) % int(bucket_size)) if return_bucket_mapping else None
+    return out[0], out[1], out[2], out[3], out[4], mapping, counts
+
+
+_HYBRID_LIB.impl("block_bucketize_sparse_features_cpu", _block_bucketize_op, "CPU")

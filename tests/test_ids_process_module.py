@@ -91,3 +91,24 @@ def test_hybrid_flow_names():
     assert moved.unique_ids.tolist() == [10**12, 7] and moved.unique_offset_host == [0, 2]
     bare = KeyedJaggedTensorWithLookHelper.from_kjt(kjt, unique_offset=torch.tensor([0, 2]))
     assert bare.unique_offset_host == [0, 2] and bare.unique_ids is None       # read from the tensor when no host copy was given
+
+
+def test_operator_form_of_block_bucketize():
+    """``torch.ops.hybrid.block_bucketize_sparse_features_cpu`` with the reference's argument list and 7-entry result."""
+    import recsdk_b200.modules.ids_process  # noqa: F401  (registers the operator)
+
+    lengths, ids = torch.tensor([2, 1, 1, 2]), torch.tensor([4, 7, 4, 9, 6, 7])          # 2 features x batch 2
+    op = torch.ops.hybrid.block_bucketize_sparse_features_cpu
+    nl, ni, nw, npos, perm, mapping, counts = op(lengths, ids, False, True, torch.tensor([1, 1]), 2, max_B=2, return_bucket_mapping=True)
+    assert nl.tolist() == [1, 1, 0, 1, 1, 0, 1, 1] and ni.tolist() == [4, 4, 6, 7, 9, 7]
+    assert nw is None and npos is None and torch.equal(ni[perm], ids)
+    assert mapping.tolist() == [0, 1, 0, 1, 0, 1] and counts.numel() == 0
+    nl, ni, _, _, perm, mapping, counts = op(lengths, ids, False, False, torch.tensor([1, 1]), 2, None, None, None, 2, None, False, False,
+                                             True, True)
+    assert ni.tolist() == [4, 6, 7, 9, 7] and counts[:, 0].tolist() == [2, 1, 1, 1, 1] and mapping is None
+    assert torch.equal(ni[perm], ids) and int(nl.sum()) == 5
+    w = torch.arange(6, dtype=torch.float32)
+    _, ni, nw, _, perm, _, _ = op(lengths, ids, False, True, torch.tensor([1, 1]), 2, weights=w, max_B=2)
+    assert torch.equal(nw[perm], w)
+    with pytest.raises(NotImplementedError):
+        op(lengths, ids, False, True, torch.tensor([1, 1]), 2, max_B=2, block_bucketize_pos=[torch.tensor([0, 5, 10])])
