@@ -395,3 +395,37 @@ class KeyedTensor:
 
     def __repr__(self) -> str:
         return "KeyedTensor(keys=%s, shape=%s)" % (self._keys, tuple(self._values.shape))
+
+
+class KJTList:
+    """A list of ``KeyedJaggedTensor`` that moves as one unit (one entry per sharding group of a module's input)."""
+
+    def __init__(self, features) -> None:
+        self.features = list(features)
+
+    def __len__(self) -> int:
+        return len(self.features)
+
+    def __getitem__(self, i: int) -> KeyedJaggedTensor:
+        return self.features[i]
+
+    def __iter__(self):
+        return iter(self.features)
+
+    def to(self, device: torch.device, non_blocking: bool = False) -> "KJTList":
+        return KJTList([f.to(device, non_blocking=non_blocking) for f in self.features])
+
+    def pin_memory(self) -> "KJTList":
+        return KJTList([f.pin_memory() for f in self.features])
+
+    def record_stream(self, stream) -> None:
+        for f in self.features:
+            f.record_stream(stream)
+
+
+def kjt_list_to_device(batch: KJTList, device: torch.device, non_blocking: bool = False) -> KJTList:
+    """Pin every entry and start its copy to ``device`` (reference ``hybrid_torchrec/distributed/embedding_types.py:15-31``)."""
+    if not isinstance(batch, KJTList):
+        raise ValueError("%s must be KJTList" % type(batch))
+    pin = torch.cuda.is_available()
+    return KJTList([(f.pin_memory() if pin else f).to(device, non_blocking=non_blocking) for f in batch.features])

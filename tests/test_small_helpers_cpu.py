@@ -343,3 +343,25 @@ def test_combined_optimizer_param_groups_and_state():
     co2 = CombinedOptimizer([AccumulateAdagrad([p], lr=0.1), AccumulateAdam([q], lr=0.01)])
     co2.load_state_dict(sd)
     assert set(sd) == {"0", "1"}
+
+
+def test_reference_constants_check_helper_and_kjt_list():
+    import pytest
+    import torch
+
+    from recsdk_b200 import constants as C
+    from recsdk_b200.sparse import KeyedJaggedTensor, KJTList, kjt_list_to_device
+
+    assert (C.MAX_NUM_EMBEDDINGS, C.MAX_EMBEDDINGS_DIM, C.EMBEDDINGS_DIM_ALIGNMENT) == (1000000000, 4096, 8)
+    assert (C.MAX_NUM_TABLES, C.MAX_MULTI_HOT_SIZE, C.MAX_WORLD_SIZE, C.MAX_BATCH_SIZE) == (10000, 102400, 10000, 102400)
+    assert C.MAX_CACHINE_MEM_SIZE == 64 << 30 and C.MAX_LOCAL_UNIQUE_PARALLEL_BATCH_NUM == 24
+    C.check(True, "fine")
+    with pytest.raises(ValueError, match="too many"):
+        C.check(False, "too many")
+    a = KeyedJaggedTensor(["f"], torch.tensor([1, 2, 3]), lengths=torch.tensor([2, 1]))
+    b = KeyedJaggedTensor(["g"], torch.tensor([4]), lengths=torch.tensor([0, 1]))
+    moved = kjt_list_to_device(KJTList([a, b]), torch.device("cpu"))
+    assert len(moved) == 2 and moved[0].values().tolist() == [1, 2, 3] and [k.keys() for k in moved] == [["f"], ["g"]]
+    assert len(KJTList([a]).to(torch.device("cpu"))) == 1
+    with pytest.raises(ValueError, match="must be KJTList"):
+        kjt_list_to_device([a, b], torch.device("cpu"))
